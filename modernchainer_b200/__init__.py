@@ -1,0 +1,15 @@
+"""modernchainer_b200: Python binding of the sm_100a training-step backend.
+
+The package mirrors the reference's Python surface (`chainer.Variable`, `F.*`, `O.Adam`,
+`GradScaler`; python/chainer/*.py and crates/modern-chainer-python/src/lib.rs in the
+reference) on top of the C ABI declared in include/mcb.h.  All arithmetic runs in
+libmcb.so on the GPU; importing the package works without a GPU, creating a Context
+does not.
+"""
+from . import _lib
+from .api import (BF16, F16, F32, I32, I64, U8, Adam, Arena, Context, DeviceArray, F, GradScaler, McbError, Model,
+                  Variable, autocast, bf16_bits_to_f32, device_count, f32_to_bf16_bits, no_grad, ops, zero_grad)
+
+__all__ = ["Context", "DeviceArray", "Variable", "F", "Adam", "GradScaler", "Model", "Arena", "McbError", "ops",
+           "no_grad", "autocast", "zero_grad", "device_count", "F32", "I64", "I32", "U8", "F16", "BF16",
+           "f32_to_bf16_bits", "bf16_bits_to_f32"]

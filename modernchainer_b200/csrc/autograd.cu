@@ -1,0 +1,1348 @@
+// Host side of the training step: define-by-run tape, the F.* operator table, the flat
+// parameter arena, Adam, GradScaler and the benchmark models.
+//
+// Mirrors the reference's public surface (Variable / F::* / Optimizer::update /
+// GradScaler::step; crates/modern-chainer-autograd/src/{variable,node,ops,host_ops}.rs,
+// crates/modern-chainer-optim/src/{lib,amp}.rs, crates/modern-chainer-nn/src/lib.rs) with a
+// different engine underneath:
+//   * fan-in gradients are accumulated in place when the pending tensor is uniquely owned
+//     (the reference allocates a new tensor per add, variable.rs:196,212);
+//   * gradients are kept on leaves only, not on every intermediate;
+//   * parameter gradients are produced straight into a flat arena when possible, and the
+//     walker reports each finished parameter so gradient buckets can be all-reduced while
+//     the rest of backward still runs;
+//   * no step of backward reads a value back to the host (the reference synchronises in
+//     SoftmaxCrossEntropy::backward, Sum/Mean::backward and every sum_to that is not the
+//     bias case, ops.rs:268-301,346-348 and cuda/src/ops.rs:893-918);
+//   * reshape is a view (a download/upload round trip in the reference, host_ops.rs:659-703).
+#include <cmath>
+#include <cstring>
+#include <functional>
+#include <memory>
+#include <unordered_map>
+#include <unordered_set>
+
+#include "autograd.h"
+
+namespace mcbag {
+
+static bool g_grad_enabled = true;
+static int g_autocast = -1;
+
+bool grad_enabled() { return g_grad_enabled; }
+int autocast() { return g_autocast; }
+void set_grad_enabled(bool on) { g_grad_enabled = on; }
+void set_autocast(int dt) { g_autocast = dt; }
+
+// ------------------------------------------------------------------ tensors
+int64_t Tensor::numel() const {
+    int64_t n = 1;
+    for (int64_t d : shape) n *= d;
+    return n;
+}
+
+mcb_status new_tensor(mcb_ctx *ctx, int dt, const std::vector<int64_t> &shape, Tensor *out) {
+    Tensor t;
+    t.dt = dt;
+    t.shape = shape;
+    void *p = nullptr;
+    MCB_TRY(mcb_alloc(ctx, (size_t)t.numel() * mcb_dtype_size(dt), &p));
+    t.buf = std::make_shared<Buf>(ctx, p);
+    t.ptr = p;
+    t.defined = true;
+    *out = t;
+    return MCB_OK;
+}
+
+Tensor view(const Tensor &t, const std::vector<int64_t> &shape) {
+    Tensor v = t;
+    v.shape = shape;
+    return v;
+}
+
+// returns `t` itself when it already has storage type `dt`, else a converted copy
+mcb_status to_dtype(mcb_ctx *ctx, const Tensor &t, int dt, Tensor *out) {
+    if (t.dt == dt) {
+        *out = t;
+        return MCB_OK;
+    }
+    MCB_TRY(new_tensor(ctx, dt, t.shape, out));
+    return mcb_cast(ctx, t.ptr, t.dt, out->ptr, dt, t.numel());
+}
+
+static bool is_float(int dt) { return dt == MCB_F32 || dt == MCB_BF16; }
+
+// ------------------------------------------------------------------ apply
+Var make_var(mcb_ctx *ctx, const Tensor &data, bool requires_grad) {
+    Var v = std::make_shared<VarImpl>();
+    v->ctx = ctx;
+    v->data = data;
+    v->requires_grad = requires_grad;
+    return v;
+}
+
+// wraps an op result: attaches the node only when grad mode is on and an input needs it
+static Var apply(mcb_ctx *ctx, const char *name, const Tensor &out, const std::vector<Var> &inputs, BackwardFn bwd) {
+    bool need = false;
+    for (auto &i : inputs) need = need || i->requires_grad;
+    Var v = make_var(ctx, out, g_grad_enabled && need);
+    if (v->requires_grad) {
+        auto n = std::make_shared<Node>();
+        n->name = name;
+        n->inputs = inputs;
+        n->backward = std::move(bwd);
+        v->node = n;
+    }
+    return v;
+}
+
+// ------------------------------------------------------------------ arena helpers
+static Tensor slot_view(const Var &v) {
+    Arena *a = v->arena;
+    Tensor t;
+    t.buf = a->g;
+    t.ptr = (float *)a->g->p + a->off[v->arena_idx];
+    t.dt = MCB_F32;
+    t.shape = v->data.shape;
+    t.defined = true;
+    return t;
+}
+
+// Where an op should write the gradient of input `v`: the arena slot when it is still empty
+// and nobody claimed it during this backward pass, otherwise a fresh tensor.
+static mcb_status grad_dst(const Var &v, Tensor *out, bool *direct) {
+    if (v->arena && !v->has_grad && !v->slot_claimed) {
+        v->slot_claimed = true;
+        v->arena->claimed.push_back(v.get());
+        *out = slot_view(v);
+        *direct = true;
+        return MCB_OK;
+    }
+    *direct = false;
+    return new_tensor(v->ctx, MCB_F32, v->data.shape, out);
+}
+
+// ------------------------------------------------------------------ backward walker
+static mcb_status accumulate_leaf(const Var &v, const Tensor &g) {
+    mcb_ctx *ctx = v->ctx;
+    if (v->arena) {
+        Tensor slot = slot_view(v);
+        Tensor gf;
+        MCB_TRY(to_dtype(ctx, g, MCB_F32, &gf));
+        if (!v->has_grad) {
+            if (gf.ptr != slot.ptr) MCB_TRY(mcb_memcpy_d2d(ctx, slot.ptr, gf.ptr, sizeof(float) * slot.numel()));
+        } else {
+            MCB_TRY(mcb_add_inplace(ctx, slot.ptr, gf.ptr, slot.numel(), MCB_F32));
+        }
+        v->grad = slot;
+        v->has_grad = true;
+        return arena_grad_ready(v->arena, v->arena_idx);
+    }
+    if (!v->has_grad) {
+        v->grad = g;
+        v->has_grad = true;
+        return MCB_OK;
+    }
+    if (v->grad.buf && v->grad.buf.use_count() == 1 && v->grad.dt == g.dt) {
+        return mcb_add_inplace(ctx, v->grad.ptr, g.ptr, g.numel(), g.dt);
+    }
+    Tensor sum;
+    int dt = (v->grad.dt == MCB_F32 || g.dt == MCB_F32) ? MCB_F32 : MCB_BF16;
+    MCB_TRY(new_tensor(ctx, dt, g.shape, &sum));
+    MCB_TRY(mcb_add_typed(ctx, v->grad.ptr, v->grad.dt, g.ptr, g.dt, sum.ptr, dt, g.numel()));
+    v->grad = sum;
+    return MCB_OK;
+}
+
+mcb_status backward(const Var &root) {
+    if (!root->requires_grad || !g_grad_enabled) return MCB_OK;
+    mcb_ctx *ctx = root->ctx;
+    // iterative post-order DFS (same visiting rule as Variable::backward, variable.rs:158-175)
+    std::vector<Var> order;
+    std::unordered_set<VarImpl *> seen;
+    std::vector<std::pair<Var, bool>> stack;
+    stack.emplace_back(root, false);
+    while (!stack.empty()) {
+        auto top = stack.back();
+        stack.pop_back();
+        if (top.second) {
+            order.push_back(top.first);
+            continue;
+        }
+        if (!seen.insert(top.first.get()).second) continue;
+        stack.emplace_back(top.first, true);
+        if (top.first->node)
+            for (auto &in : top.first->node->inputs) stack.emplace_back(in, false);
+    }
+    std::unordered_map<VarImpl *, Tensor> grads;
+    {
+        Tensor seed;
+        MCB_TRY(new_tensor(ctx, MCB_F32, root->data.shape, &seed));
+        MCB_TRY(mcb_fill(ctx, (float *)seed.ptr, 1.0f, seed.numel()));
+        if (root->data.dt != MCB_F32) {
+            Tensor s2;
+            MCB_TRY(to_dtype(ctx, seed, root->data.dt, &s2));
+            seed = s2;
+        }
+        grads[root.get()] = seed;
+    }
+    std::vector<Arena *> touched;
+    mcb_status st = MCB_OK;
+    for (auto it = order.rbegin(); it != order.rend() && st == MCB_OK; ++it) {
+        const Var &v = *it;
+        auto f = grads.find(v.get());
+        if (f == grads.end()) continue;
+        Tensor g = f->second;
+        grads.erase(f);
+        if (!v->node) {
+            if (v->arena && std::find(touched.begin(), touched.end(), v->arena) == touched.end()) touched.push_back(v->arena);
+            st = accumulate_leaf(v, g);
+            continue;
+        }
+        std::vector<Tensor> in_grads(v->node->inputs.size());
+        st = v->node->backward(g, in_grads);
+        if (st != MCB_OK) break;
+        g = Tensor(); // drop our reference so a pending tensor can be uniquely owned
+        for (size_t i = 0; i < in_grads.size(); ++i) {
+            const Var &in = v->node->inputs[i];
+            if (!in_grads[i].defined || !in->requires_grad) continue;
+            auto e = grads.find(in.get());
+            if (e == grads.end()) {
+                grads.emplace(in.get(), in_grads[i]);
+                continue;
+            }
+            Tensor &cur = e->second;
+            Tensor add = in_grads[i];
+            in_grads[i] = Tensor();
+            if (cur.buf && cur.buf.use_count() == 1 && cur.dt == add.dt) {
+                st = mcb_add_inplace(ctx, cur.ptr, add.ptr, cur.numel(), cur.dt);
+            } else if (add.buf && add.buf.use_count() == 1 && cur.dt == add.dt) {
+                st = mcb_add_inplace(ctx, add.ptr, cur.ptr, cur.numel(), cur.dt);
+                cur = add;
+            } else {
+                Tensor sum;
+                int dt = (cur.dt == MCB_F32 || add.dt == MCB_F32) ? MCB_F32 : MCB_BF16;
+                st = new_tensor(ctx, dt, cur.shape, &sum);
+                if (st == MCB_OK) st = mcb_add_typed(ctx, cur.ptr, cur.dt, add.ptr, add.dt, sum.ptr, dt, cur.numel());
+                cur = sum;
+            }
+            if (st != MCB_OK) break;
+        }
+    }
+    for (Arena *a : touched) {
+        for (VarImpl *c : a->claimed) c->slot_claimed = false;
+        a->claimed.clear();
+    }
+    return st;
+}
+
+// ------------------------------------------------------------------ F.*
+static mcb_status check_same_ctx(const Var &a, const Var &b) {
+    if (a->ctx != b->ctx) return mcb_fail(a->ctx, MCB_INVALID_ARGUMENT, "variables live on different contexts");
+    return MCB_OK;
+}
+
+static mcb_status f32_of(const Var &v, Tensor *out) { return to_dtype(v->ctx, v->data, MCB_F32, out); }
+
+// un-broadcast `g` to `shape` (Ops::sum_to); equal shapes alias, no copy
+static mcb_status sum_to_shape(mcb_ctx *ctx, const Tensor &g, const std::vector<int64_t> &shape, Tensor *out) {
+    if (g.shape == shape) {
+        *out = g;
+        return MCB_OK;
+    }
+    Tensor gf;
+    MCB_TRY(to_dtype(ctx, g, MCB_F32, &gf));
+    MCB_TRY(new_tensor(ctx, MCB_F32, shape, out));
+    return mcb_sum_to(ctx, (const float *)gf.ptr, gf.shape.data(), (int)gf.shape.size(), shape.data(), (int)shape.size(), (float *)out->ptr);
+}
+
+static mcb_status bin(mcb_ctx *ctx, int op, const Tensor &a, const Tensor &b, Tensor *out) {
+    std::vector<int64_t> os;
+    size_t r = std::max(a.shape.size(), b.shape.size());
+    os.resize(r);
+    for (size_t i = 0; i < r; ++i) {
+        int64_t x = i >= r - a.shape.size() ? a.shape[i - (r - a.shape.size())] : 1;
+        int64_t y = i >= r - b.shape.size() ? b.shape[i - (r - b.shape.size())] : 1;
+        if (x != y && x != 1 && y != 1) return mcb_fail(ctx, MCB_BROADCAST, "shapes do not broadcast");
+        os[i] = x == 1 ? y : x;
+    }
+    MCB_TRY(new_tensor(ctx, MCB_F32, os, out));
+    return mcb_binary(ctx, op, (const float *)a.ptr, a.shape.data(), (int)a.shape.size(), (const float *)b.ptr, b.shape.data(),
+                      (int)b.shape.size(), (float *)out->ptr);
+}
+static mcb_status scaled(mcb_ctx *ctx, const Tensor &x, double f, Tensor *out) {
+    MCB_TRY(new_tensor(ctx, MCB_F32, x.shape, out));
+    return mcb_scale(ctx, (const float *)x.ptr, f, (float *)out->ptr, x.numel());
+}
+// cast a gradient to the storage type of the input it belongs to
+static mcb_status like_input(mcb_ctx *ctx, const Tensor &g, const Var &in, Tensor *out) {
+    int want = is_float(in->data.dt) ? in->data.dt : MCB_F32;
+    return to_dtype(ctx, g, want, out);
+}
+
+mcb_status f_binary(int op, const Var &a, const Var &b, Var *out) {
+    MCB_TRY(check_same_ctx(a, b));
+    mcb_ctx *ctx = a->ctx;
+    if (!is_float(a->data.dt) || !is_float(b->data.dt)) return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "arithmetic needs floating-point operands");
+    Tensor res;
+    bool mixed = (a->data.dt != MCB_F32 || b->data.dt != MCB_F32);
+    if (op == MCB_ADD && a->data.shape == b->data.shape && mixed) {
+        // residual add with a low-precision operand: one pass, f32 result unless both are bf16
+        int odt = (a->data.dt == MCB_BF16 && b->data.dt == MCB_BF16) ? MCB_BF16 : MCB_F32;
+        MCB_TRY(new_tensor(ctx, odt, a->data.shape, &res));
+        MCB_TRY(mcb_add_typed(ctx, a->data.ptr, a->data.dt, b->data.ptr, b->data.dt, res.ptr, odt, res.numel()));
+    } else {
+        Tensor af, bf;
+        MCB_TRY(f32_of(a, &af));
+        MCB_TRY(f32_of(b, &bf));
+        MCB_TRY(bin(ctx, op, af, bf, &res));
+    }
+    Var av = a, bv = b;
+    *out = apply(ctx, "Binary", res, {a, b}, [ctx, op, av, bv](const Tensor &g, std::vector<Tensor> &gi) -> mcb_status {
+        const std::vector<int64_t> &as = av->data.shape, &bs = bv->data.shape;
+        Tensor ga, gb;
+        if (op == MCB_ADD || op == MCB_SUB) {
+            if (av->requires_grad) {
+                MCB_TRY(sum_to_shape(ctx, g, as, &ga));
+                MCB_TRY(like_input(ctx, ga, av, &gi[0]));
+            }
+            if (bv->requires_grad) {
+                Tensor t = g;
+                if (op == MCB_SUB) {
+                    Tensor gf;
+                    MCB_TRY(to_dtype(ctx, g, MCB_F32, &gf));
+                    MCB_TRY(scaled(ctx, gf, -1.0, &t));
+                }
+                MCB_TRY(sum_to_shape(ctx, t, bs, &gb));
+                MCB_TRY(like_input(ctx, gb, bv, &gi[1]));
+            }
+            return MCB_OK;
+        }
+        Tensor gf, af, bf;
+        MCB_TRY(to_dtype(ctx, g, MCB_F32, &gf));
+        MCB_TRY(f32_of(av, &af));
+        MCB_TRY(f32_of(bv, &bf));
+        if (op == MCB_MUL) {
+            if (av->requires_grad) {
+                Tensor t;
+                MCB_TRY(bin(ctx, MCB_MUL, gf, bf, &t));
+                MCB_TRY(sum_to_shape(ctx, t, as, &ga));
+                MCB_TRY(like_input(ctx, ga, av, &gi[0]));
+            }
+            if (bv->requires_grad) {
+                Tensor t;
+                MCB_TRY(bin(ctx, MCB_MUL, gf, af, &t));
+                MCB_TRY(sum_to_shape(ctx, t, bs, &gb));
+                MCB_TRY(like_input(ctx, gb, bv, &gi[1]));
+            }
+            return MCB_OK;
+        }
+        // div: ga = g / b ; gb = -(g * a) / (b * b)   (autograd/src/ops.rs:97-128)
+        if (av->requires_grad) {
+            Tensor t;
+            MCB_TRY(bin(ctx, MCB_DIV, gf, bf, &t));
+            MCB_TRY(sum_to_shape(ctx, t, as, &ga));
+            MCB_TRY(like_input(ctx, ga, av, &gi[0]));
+        }
+        if (bv->requires_grad) {
+            Tensor denom, numer, q, neg;
+            MCB_TRY(bin(ctx, MCB_MUL, bf, bf, &denom));
+            MCB_TRY(bin(ctx, MCB_MUL, gf, af, &numer));
+            MCB_TRY(bin(ctx, MCB_DIV, numer, denom, &q));
+            MCB_TRY(scaled(ctx, q, -1.0, &neg));
+            MCB_TRY(sum_to_shape(ctx, neg, bs, &gb));
+            MCB_TRY(like_input(ctx, gb, bv, &gi[1]));
+        }
+        return MCB_OK;
+    });
+    return MCB_OK;
+}
+
+mcb_status f_scale(const Var &x, double factor, Var *out) {
+    mcb_ctx *ctx = x->ctx;
+    Tensor xf, res;
+    MCB_TRY(f32_of(x, &xf));
+    MCB_TRY(scaled(ctx, xf, factor, &res));
+    Var xv = x;
+    *out = apply(ctx, "Scale", res, {x}, [ctx, factor, xv](const Tensor &g, std::vector<Tensor> &gi) -> mcb_status {
+        Tensor gf, t;
+        MCB_TRY(to_dtype(ctx, g, MCB_F32, &gf));
+        MCB_TRY(scaled(ctx, gf, factor, &t));
+        return like_input(ctx, t, xv, &gi[0]);
+    });
+    return MCB_OK;
+}
+
+// y = x * (*scalar) with the scalar resident on the device (GradScaler::scale_loss without a host value)
+mcb_status f_scale_by_device(const Var &x, const float *scalar, std::shared_ptr<Buf> keep, Var *out) {
+    mcb_ctx *ctx = x->ctx;
+    Tensor xf, res;
+    MCB_TRY(f32_of(x, &xf));
+    MCB_TRY(new_tensor(ctx, MCB_F32, xf.shape, &res));
+    MCB_TRY(mcb_mul_scalar_ptr(ctx, xf.ptr, scalar, res.ptr, xf.numel(), MCB_F32));
+    Var xv = x;
+    *out = apply(ctx, "ScaleLoss", res, {x}, [ctx, scalar, keep, xv](const Tensor &g, std::vector<Tensor> &gi) -> mcb_status {
+        Tensor gf, t;
+        MCB_TRY(to_dtype(ctx, g, MCB_F32, &gf));
+        MCB_TRY(new_tensor(ctx, MCB_F32, gf.shape, &t));
+        MCB_TRY(mcb_mul_scalar_ptr(ctx, gf.ptr, scalar, t.ptr, gf.numel(), MCB_F32));
+        return like_input(ctx, t, xv, &gi[0]);
+    });
+    return MCB_OK;
+}
+
+mcb_status f_unary(int op, const Var &x, Var *out) {
+    mcb_ctx *ctx = x->ctx;
+    if (op < MCB_EXP || op > MCB_NEG) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "unknown unary op %d", op);
+    Tensor xf, res;
+    MCB_TRY(f32_of(x, &xf));
+    MCB_TRY(new_tensor(ctx, MCB_F32, xf.shape, &res));
+    MCB_TRY(mcb_unary(ctx, op, (const float *)xf.ptr, (float *)res.ptr, xf.numel()));
+    Var xv = x;
+    *out = apply(ctx, "Unary", res, {x}, [ctx, op, xv, xf, res](const Tensor &g, std::vector<Tensor> &gi) -> mcb_status {
+        Tensor gf, t;
+        MCB_TRY(to_dtype(ctx, g, MCB_F32, &gf));
+        switch (op) {
+        case MCB_EXP: MCB_TRY(bin(ctx, MCB_MUL, gf, res, &t)); break;        // g * y
+        case MCB_LOG: MCB_TRY(bin(ctx, MCB_DIV, gf, xf, &t)); break;         // g / x
+        case MCB_SQRT: {                                                      // g / (2 y)
+            Tensor two_y;
+            MCB_TRY(scaled(ctx, res, 2.0, &two_y));
+            MCB_TRY(bin(ctx, MCB_DIV, gf, two_y, &t));
+            break;
+        }
+        case MCB_SIGMOID: {                                                   // g * y * (1 - y)
+            Tensor ones, om, ym;
+            MCB_TRY(new_tensor(ctx, MCB_F32, res.shape, &ones));
+            MCB_TRY(mcb_fill(ctx, (float *)ones.ptr, 1.0f, ones.numel()));
+            MCB_TRY(bin(ctx, MCB_SUB, ones, res, &om));
+            MCB_TRY(bin(ctx, MCB_MUL, res, om, &ym));
+            MCB_TRY(bin(ctx, MCB_MUL, gf, ym, &t));
+            break;
+        }
+        case MCB_NEG: MCB_TRY(scaled(ctx, gf, -1.0, &t)); break;
+        default: return mcb_fail(ctx, MCB_UNSUPPORTED, "backward of this unary op is not on the training path");
+        }
+        return like_input(ctx, t, xv, &gi[0]);
+    });
+    return MCB_OK;
+}
+
+static mcb_status f_act(const Var &x, bool gelu, Var *out) {
+    mcb_ctx *ctx = x->ctx;
+    if (!is_float(x->data.dt)) return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "activation needs a floating-point input");
+    Tensor res;
+    MCB_TRY(new_tensor(ctx, x->data.dt, x->data.shape, &res));
+    MCB_TRY((gelu ? mcb_gelu : mcb_relu)(ctx, x->data.ptr, res.ptr, res.numel(), x->data.dt));
+    Tensor xd = x->data;
+    *out = apply(ctx, gelu ? "GELU" : "ReLU", res, {x}, [ctx, gelu, xd](const Tensor &g, std::vector<Tensor> &gi) -> mcb_status {
+        Tensor gg;
+        MCB_TRY(to_dtype(ctx, g, xd.dt, &gg));
+        MCB_TRY(new_tensor(ctx, xd.dt, xd.shape, &gi[0]));
+        return (gelu ? mcb_gelu_backward : mcb_relu_backward)(ctx, xd.ptr, gg.ptr, gi[0].ptr, xd.numel(), xd.dt);
+    });
+    return MCB_OK;
+}
+mcb_status f_relu(const Var &x, Var *out) { return f_act(x, false, out); }
+mcb_status f_gelu(const Var &x, Var *out) { return f_act(x, true, out); }
+
+static mcb_status f_sum_mean(const Var &x, bool mean, Var *out) {
+    mcb_ctx *ctx = x->ctx;
+    Tensor xf, res;
+    MCB_TRY(f32_of(x, &xf));
+    MCB_TRY(new_tensor(ctx, MCB_F32, {}, &res));
+    int64_t n = xf.numel();
+    double factor = mean ? 1.0 / (double)(n > 1 ? n : 1) : 1.0;
+    // Mean = sum_all then scale(1/n): the f32 sum is rounded before the scale in the reference
+    if (mean) {
+        Tensor s;
+        MCB_TRY(new_tensor(ctx, MCB_F32, {}, &s));
+        MCB_TRY(mcb_sum_all(ctx, (const float *)xf.ptr, n, (float *)s.ptr));
+        MCB_TRY(mcb_scale(ctx, (const float *)s.ptr, factor, (float *)res.ptr, 1));
+    } else {
+        MCB_TRY(mcb_sum_all(ctx, (const float *)xf.ptr, n, (float *)res.ptr));
+    }
+    Var xv = x;
+    *out = apply(ctx, mean ? "Mean" : "Sum", res, {x}, [ctx, factor, xv](const Tensor &g, std::vector<Tensor> &gi) -> mcb_status {
+        Tensor gf, t;
+        MCB_TRY(to_dtype(ctx, g, MCB_F32, &gf));
+        MCB_TRY(new_tensor(ctx, MCB_F32, xv->data.shape, &t));
+        MCB_TRY(mcb_fill_from_scalar(ctx, (float *)t.ptr, (const float *)gf.ptr, factor, t.numel()));
+        return like_input(ctx, t, xv, &gi[0]);
+    });
+    return MCB_OK;
+}
+mcb_status f_sum(const Var &x, Var *out) { return f_sum_mean(x, false, out); }
+mcb_status f_mean(const Var &x, Var *out) { return f_sum_mean(x, true, out); }
+
+// ---- GEMM helpers ----------------------------------------------------------------------
+static bool use_bf16(mcb_ctx *ctx) { return g_autocast == MCB_BF16 || ctx->compute == MCB_COMPUTE_BF16; }
+static bool tc_shape_ok(int64_t m, int64_t n, int64_t k) { return m > 0 && (n % 8 == 0) && (k % 8 == 0) && n > 0 && k > 0; }
+
+// bf16 operand for `v`: the arena's shadow copy for parameters, the tensor itself when it is
+// already bf16, otherwise a converted copy
+static mcb_status bf16_of(const Var &v, Tensor *out) {
+    if (v->data.dt == MCB_BF16) {
+        *out = v->data;
+        return MCB_OK;
+    }
+    if (v->arena) {
+        MCB_TRY(arena_refresh_shadow(v->arena));
+        Tensor t;
+        t.buf = v->arena->shadow;
+        t.ptr = (__nv_bfloat16 *)v->arena->shadow->p + v->arena->off[v->arena_idx];
+        t.dt = MCB_BF16;
+        t.shape = v->data.shape;
+        t.defined = true;
+        *out = t;
+        return MCB_OK;
+    }
+    return to_dtype(v->ctx, v->data, MCB_BF16, out);
+}
+
+static int pick_split_k(mcb_ctx *ctx, int64_t m, int64_t n, int64_t k) {
+    int64_t tiles = ((m + 127) / 128) * ((n + 255) / 256);
+    int64_t kb = (k + 63) / 64;
+    if (tiles >= ctx->sm_count || kb < 8) return 1;
+    int64_t s = (ctx->sm_count + tiles - 1) / tiles;
+    if (s > kb / 4) s = kb / 4;
+    if (s < 1) s = 1;
+    if (s > 32) s = 32;
+    return (int)s;
+}
+
+struct LinearSaved {
+    Tensor x;      // activation as used by the forward GEMM (bf16 under autocast, else f32)
+    Tensor pre;    // pre-activation (linear_activation only)
+    bool bf16 = false;
+    int act = MCB_ACT_NONE;
+};
+
+// shared backward of linear / linear_activation: g is the gradient w.r.t. the op output
+static mcb_status linear_backward_impl(mcb_ctx *ctx, const Tensor &g_in, const LinearSaved &sv, const Var &x, const Var &w,
+                                       const Var &b, std::vector<Tensor> &gi) {
+    int64_t m = sv.x.numel() / sv.x.shape.back(), k = sv.x.shape.back(), n = w->data.shape[0];
+    int gdt = sv.bf16 ? MCB_BF16 : MCB_F32;
+    Tensor g;
+    MCB_TRY(to_dtype(ctx, g_in, gdt, &g));
+    if (sv.act != MCB_ACT_NONE) {
+        Tensor gp;
+        MCB_TRY(new_tensor(ctx, gdt, g.shape, &gp));
+        MCB_TRY((sv.act == MCB_ACT_GELU ? mcb_gelu_backward : mcb_relu_backward)(ctx, sv.pre.ptr, g.ptr, gp.ptr, g.numel(), gdt));
+        g = gp;
+    }
+    if (sv.bf16) {
+        if (x->requires_grad) {
+            Tensor wb;
+            MCB_TRY(bf16_of(w, &wb));
+            int xdt = is_float(x->data.dt) ? x->data.dt : MCB_F32;
+            MCB_TRY(new_tensor(ctx, xdt, x->data.shape, &gi[0]));
+            TcGemmParams p; // dx[m,k] = g[m,n] * W[n,k]
+            p.a = g.ptr; p.a_mn_major = 0; p.lda = n;
+            p.b = wb.ptr; p.b_mn_major = 1; p.ldb = k;
+            p.d = gi[0].ptr; p.out_dt = xdt; p.ldd = k;
+            p.m = m; p.n = k; p.k = n;
+            MCB_TRY(mcb_tc_gemm(ctx, p));
+        }
+        if (w->requires_grad) {
+            bool direct;
+            MCB_TRY(grad_dst(w, &gi[1], &direct));
+            TcGemmParams p; // dw[n,k] = g^T[n,m] * x[m,k]
+            p.a = g.ptr; p.a_mn_major = 1; p.lda = n;
+            p.b = sv.x.ptr; p.b_mn_major = 1; p.ldb = k;
+            p.d = gi[1].ptr; p.out_dt = MCB_F32; p.ldd = k;
+            p.m = n; p.n = k; p.k = m;
+            p.split_k = pick_split_k(ctx, n, k, m);
+            if (p.split_k > 1) {
+                p.accumulate = 1;
+                MCB_TRY(mcb_memset(ctx, gi[1].ptr, 0, sizeof(float) * n * k));
+            }
+            MCB_TRY(mcb_tc_gemm(ctx, p));
+        }
+    } else {
+        float *dx = nullptr, *dw = nullptr;
+        if (x->requires_grad) {
+            MCB_TRY(new_tensor(ctx, MCB_F32, x->data.shape, &gi[0]));
+            dx = (float *)gi[0].ptr;
+        }
+        if (w->requires_grad) {
+            bool direct;
+            MCB_TRY(grad_dst(w, &gi[1], &direct));
+            dw = (float *)gi[1].ptr;
+        }
+        MCB_TRY(mcb_linear_backward(ctx, (const float *)g.ptr, (const float *)sv.x.ptr, (const float *)w->data.ptr, dx, dw, nullptr, m, k, n));
+        if (x->requires_grad && x->data.dt == MCB_BF16) {
+            Tensor t;
+            MCB_TRY(to_dtype(ctx, gi[0], MCB_BF16, &t));
+            gi[0] = t;
+        }
+    }
+    if (b && b->requires_grad) {
+        bool direct;
+        MCB_TRY(grad_dst(b, &gi[2], &direct));
+        MCB_TRY(mcb_col_sum(ctx, g.ptr, gdt, m, n, (float *)gi[2].ptr));
+    }
+    return MCB_OK;
+}
+
+static mcb_status f_linear_impl(const Var &x, const Var &w, const Var &b, int act, Var *out) {
+    MCB_TRY(check_same_ctx(x, w));
+    mcb_ctx *ctx = x->ctx;
+    if (w->data.shape.size() != 2 || x->data.shape.empty() || x->data.shape.back() != w->data.shape[1])
+        return mcb_fail(ctx, MCB_SHAPE_MISMATCH, "linear: x [..., in] and weight [out, in] do not match");
+    if (b && (b->data.shape.size() != 1 || b->data.shape[0] != w->data.shape[0]))
+        return mcb_fail(ctx, MCB_SHAPE_MISMATCH, "linear: bias must be [out]");
+    if (!is_float(x->data.dt)) return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "linear needs a floating-point input");
+    int64_t k = w->data.shape[1], n = w->data.shape[0], m = x->data.numel() / (k > 0 ? k : 1);
+    std::vector<int64_t> oshape = x->data.shape;
+    oshape.back() = n;
+    auto sv = std::make_shared<LinearSaved>();
+    sv->act = act;
+    sv->bf16 = use_bf16(ctx) && tc_shape_ok(m, n, k);
+    Tensor res;
+    if (sv->bf16) {
+        Tensor wb;
+        MCB_TRY(to_dtype(ctx, x->data, MCB_BF16, &sv->x));
+        MCB_TRY(bf16_of(w, &wb));
+        MCB_TRY(new_tensor(ctx, MCB_BF16, oshape, &res));
+        TcGemmParams p; // y[m,n] = x[m,k] * W[n,k]^T + bias
+        p.a = sv->x.ptr; p.lda = k;
+        p.b = wb.ptr; p.ldb = k;
+        p.d = res.ptr; p.out_dt = MCB_BF16; p.ldd = n;
+        p.bias = b ? (const float *)b->data.ptr : nullptr;
+        p.m = m; p.n = n; p.k = k;
+        p.act = act;
+        if (act != MCB_ACT_NONE && g_grad_enabled) {
+            MCB_TRY(new_tensor(ctx, MCB_BF16, oshape, &sv->pre));
+            p.d_pre = sv->pre.ptr;
+        }
+        MCB_TRY(mcb_tc_gemm(ctx, p));
+    } else {
+        MCB_TRY(f32_of(x, &sv->x));
+        MCB_TRY(new_tensor(ctx, MCB_F32, oshape, &res));
+        const float *bp = b ? (const float *)b->data.ptr : nullptr;
+        if (act != MCB_ACT_NONE) {
+            MCB_TRY(new_tensor(ctx, MCB_F32, oshape, &sv->pre));
+            MCB_TRY(mcb_linear(ctx, (const float *)sv->x.ptr, (const float *)w->data.ptr, bp, (float *)sv->pre.ptr, m, k, n, MCB_ACT_NONE));
+            MCB_TRY((act == MCB_ACT_GELU ? mcb_gelu : mcb_relu)(ctx, sv->pre.ptr, res.ptr, res.numel(), MCB_F32));
+        } else {
+            MCB_TRY(mcb_linear(ctx, (const float *)sv->x.ptr, (const float *)w->data.ptr, bp, (float *)res.ptr, m, k, n, MCB_ACT_NONE));
+        }
+    }
+    std::vector<Var> ins = {x, w};
+    if (b) ins.push_back(b);
+    Var xv = x, wv = w, bv = b;
+    *out = apply(ctx, act ? "LinearActivation" : "Linear", res, ins, [ctx, sv, xv, wv, bv](const Tensor &g, std::vector<Tensor> &gi) -> mcb_status {
+        return linear_backward_impl(ctx, g, *sv, xv, wv, bv, gi);
+    });
+    if (!(*out)->requires_grad) sv->pre = Tensor();
+    return MCB_OK;
+}
+mcb_status f_linear(const Var &x, const Var &w, const Var &b, Var *out) { return f_linear_impl(x, w, b, MCB_ACT_NONE, out); }
+mcb_status f_linear_activation(const Var &x, const Var &w, const Var &b, int act, Var *out) {
+    if (act != MCB_ACT_RELU && act != MCB_ACT_GELU) return mcb_fail(x->ctx, MCB_INVALID_ARGUMENT, "linear_activation supports relu and gelu");
+    return f_linear_impl(x, w, b, act, out);
+}
+
+mcb_status f_matmul(const Var &a, const Var &b, Var *out) {
+    MCB_TRY(check_same_ctx(a, b));
+    mcb_ctx *ctx = a->ctx;
+    if (a->data.shape.size() != 2 || b->data.shape.size() != 2 || a->data.shape[1] != b->data.shape[0])
+        return mcb_fail(ctx, MCB_SHAPE_MISMATCH, "matmul expects [m,k] x [k,n]");
+    int64_t m = a->data.shape[0], k = a->data.shape[1], n = b->data.shape[1];
+    Tensor af, bf, res;
+    MCB_TRY(f32_of(a, &af));
+    MCB_TRY(f32_of(b, &bf));
+    MCB_TRY(new_tensor(ctx, MCB_F32, {m, n}, &res));
+    MCB_TRY(mcb_matmul(ctx, (const float *)af.ptr, (const float *)bf.ptr, (float *)res.ptr, m, k, n));
+    Var av = a, bv = b;
+    *out = apply(ctx, "MatMul", res, {a, b}, [ctx, af, bf, av, bv, m, k, n](const Tensor &g, std::vector<Tensor> &gi) -> mcb_status {
+        Tensor gf;
+        MCB_TRY(to_dtype(ctx, g, MCB_F32, &gf));
+        if (av->requires_grad) { // ga[m,k] = g[m,n] b^T[n,k]
+            Tensor t;
+            MCB_TRY(new_tensor(ctx, MCB_F32, {m, k}, &t));
+            SgemmParams p;
+            p.a = (const float *)gf.ptr; p.b = (const float *)bf.ptr; p.c = (float *)t.ptr;
+            p.m = m; p.n = k; p.k = n; p.as0 = n; p.as1 = 1; p.bs0 = 1; p.bs1 = n; p.ldc = k;
+            MCB_TRY(mcb_sgemm(ctx, p));
+            MCB_TRY(like_input(ctx, t, av, &gi[0]));
+        }
+        if (bv->requires_grad) { // gb[k,n] = a^T[k,m] g[m,n]
+            Tensor t;
+            MCB_TRY(new_tensor(ctx, MCB_F32, {k, n}, &t));
+            SgemmParams p;
+            p.a = (const float *)af.ptr; p.b = (const float *)gf.ptr; p.c = (float *)t.ptr;
+            p.m = k; p.n = n; p.k = m; p.as0 = 1; p.as1 = k; p.bs0 = n; p.bs1 = 1; p.ldc = n;
+            MCB_TRY(mcb_sgemm(ctx, p));
+            MCB_TRY(like_input(ctx, t, bv, &gi[1]));
+        }
+        return MCB_OK;
+    });
+    return MCB_OK;
+}
+
+mcb_status f_softmax(const Var &x, Var *out) {
+    mcb_ctx *ctx = x->ctx;
+    if (x->data.shape.size() != 2) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "softmax expects a 2-D input");
+    Tensor xf, res;
+    MCB_TRY(f32_of(x, &xf));
+    MCB_TRY(new_tensor(ctx, MCB_F32, xf.shape, &res));
+    int64_t rows = xf.shape[0], cols = xf.shape[1];
+    MCB_TRY(mcb_softmax(ctx, (const float *)xf.ptr, (float *)res.ptr, rows, cols));
+    Var xv = x;
+    *out = apply(ctx, "Softmax", res, {x}, [ctx, xf, xv, rows, cols](const Tensor &g, std::vector<Tensor> &gi) -> mcb_status {
+        Tensor gf, t;
+        MCB_TRY(to_dtype(ctx, g, MCB_F32, &gf));
+        MCB_TRY(new_tensor(ctx, MCB_F32, xf.shape, &t));
+        MCB_TRY(mcb_softmax_backward(ctx, (const float *)xf.ptr, (const float *)gf.ptr, (float *)t.ptr, rows, cols));
+        return like_input(ctx, t, xv, &gi[0]);
+    });
+    return MCB_OK;
+}
+
+mcb_status f_layer_norm(const Var &x, const Var &gamma, const Var &beta, double eps, Var *out) {
+    mcb_ctx *ctx = x->ctx;
+    if (x->data.shape.size() < 2) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "layer_norm expects rank >= 2");
+    int64_t dim = x->data.shape.back();
+    if (gamma->data.numel() != dim || beta->data.numel() != dim) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "layer_norm gamma/beta shape mismatch");
+    int64_t rows = dim ? x->data.numel() / dim : 0;
+    Tensor xf, res, mean, rstd;
+    MCB_TRY(f32_of(x, &xf));
+    int odt = (g_autocast == MCB_BF16) ? MCB_BF16 : MCB_F32; // under autocast the result only feeds low-precision GEMMs
+    MCB_TRY(new_tensor(ctx, odt, xf.shape, &res));
+    MCB_TRY(new_tensor(ctx, MCB_F32, {rows}, &mean));
+    MCB_TRY(new_tensor(ctx, MCB_F32, {rows}, &rstd));
+    MCB_TRY(mcb_layer_norm(ctx, (const float *)xf.ptr, (const float *)gamma->data.ptr, (const float *)beta->data.ptr, eps, res.ptr, odt,
+                           (float *)mean.ptr, (float *)rstd.ptr, rows, dim));
+    Var xv = x, gv = gamma, bv = beta;
+    *out = apply(ctx, "LayerNorm", res, {x, gamma, beta}, [ctx, xf, mean, rstd, xv, gv, bv, eps, rows, dim](const Tensor &g, std::vector<Tensor> &gi) -> mcb_status {
+        Tensor dx, dg, db;
+        bool d1, d2;
+        MCB_TRY(new_tensor(ctx, MCB_F32, xf.shape, &dx));
+        MCB_TRY(grad_dst(gv, &dg, &d1));
+        MCB_TRY(grad_dst(bv, &db, &d2));
+        MCB_TRY(mcb_layer_norm_backward(ctx, (const float *)xf.ptr, (const float *)gv->data.ptr, g.ptr, g.dt, eps, (const float *)mean.ptr,
+                                        (const float *)rstd.ptr, (float *)dx.ptr, (float *)dg.ptr, (float *)db.ptr, rows, dim));
+        MCB_TRY(like_input(ctx, dx, xv, &gi[0]));
+        gi[1] = dg;
+        gi[2] = db;
+        return MCB_OK;
+    });
+    return MCB_OK;
+}
+
+mcb_status f_softmax_cross_entropy(const Var &logits, const Var &target, Var *out) {
+    mcb_ctx *ctx = logits->ctx;
+    if (logits->data.shape.size() != 2) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "softmax_cross_entropy expects [batch, classes] logits");
+    int64_t n = logits->data.shape[0], c = logits->data.shape[1];
+    int ldt = target->data.dt;
+    if (ldt != MCB_I64 && ldt != MCB_I32 && ldt != MCB_U8) return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "labels must be i64, i32 or u8");
+    if (target->data.numel() != n) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "expected %lld targets, got %lld", (long long)n, (long long)target->data.numel());
+    Tensor res;
+    MCB_TRY(new_tensor(ctx, MCB_F32, {}, &res));
+    Tensor x = logits->data, lab = target->data;
+    if (x.dt == MCB_F32) {
+        MCB_TRY(mcb_softmax_cross_entropy(ctx, (const float *)x.ptr, lab.ptr, ldt, n, c, (float *)res.ptr));
+    } else {
+        Tensor xf;
+        MCB_TRY(to_dtype(ctx, x, MCB_F32, &xf));
+        MCB_TRY(mcb_softmax_cross_entropy(ctx, (const float *)xf.ptr, lab.ptr, ldt, n, c, (float *)res.ptr));
+    }
+    *out = apply(ctx, "SoftmaxCrossEntropy", res, {logits, target}, [ctx, x, lab, ldt, n, c](const Tensor &g, std::vector<Tensor> &gi) -> mcb_status {
+        // (softmax - onehot)/n times the upstream scalar, read on the device (no host round trip)
+        Tensor gf;
+        MCB_TRY(to_dtype(ctx, g, MCB_F32, &gf));
+        MCB_TRY(new_tensor(ctx, x.dt, x.shape, &gi[0]));
+        return mcb_sce_grad(ctx, x.ptr, gi[0].ptr, x.dt, lab.ptr, ldt, n, c, nullptr, (const float *)gf.ptr);
+    });
+    return MCB_OK;
+}
+
+// Loss head whose backward overwrites the logits buffer with their gradient instead of
+// allocating a second [n, classes] tensor.  Used by the decoder model, whose logits nobody
+// else reads: at vocabulary 32000 that buffer is the largest activation of the step.
+mcb_status f_sce_consuming(const Var &logits, const Var &target, Var *out) {
+    mcb_ctx *ctx = logits->ctx;
+    int64_t n = logits->data.shape[0], c = logits->data.shape[1];
+    int ldt = target->data.dt;
+    if (ldt != MCB_I64 && ldt != MCB_I32 && ldt != MCB_U8) return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "labels must be i64, i32 or u8");
+    if (target->data.numel() != n) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "expected %lld targets", (long long)n);
+    Tensor res;
+    MCB_TRY(new_tensor(ctx, MCB_F32, {}, &res));
+    Tensor x = logits->data, lab = target->data;
+    MCB_TRY(mcb_sce_grad(ctx, x.ptr, nullptr, x.dt, lab.ptr, ldt, n, c, (float *)res.ptr, nullptr)); // loss only
+    *out = apply(ctx, "SoftmaxCrossEntropy", res, {logits, target}, [ctx, x, lab, ldt, n, c](const Tensor &g, std::vector<Tensor> &gi) -> mcb_status {
+        Tensor gf;
+        MCB_TRY(to_dtype(ctx, g, MCB_F32, &gf));
+        MCB_TRY(mcb_sce_grad(ctx, x.ptr, x.ptr, x.dt, lab.ptr, ldt, n, c, nullptr, (const float *)gf.ptr));
+        gi[0] = x;
+        return MCB_OK;
+    });
+    return MCB_OK;
+}
+
+mcb_status f_embedding(const Var &ids, const Var &weight, Var *out) {
+    MCB_TRY(check_same_ctx(ids, weight));
+    mcb_ctx *ctx = ids->ctx;
+    int idt = ids->data.dt;
+    if (idt != MCB_I64 && idt != MCB_I32 && idt != MCB_U8) return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "ids must be i64, i32 or u8");
+    if (weight->data.shape.size() != 2) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "embedding weight must be [vocab, dim]");
+    if (ids->data.shape.size() != 1 && ids->data.shape.size() != 2) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "ids must have rank 1 or 2");
+    int64_t vocab = weight->data.shape[0], dim = weight->data.shape[1], n = ids->data.numel();
+    std::vector<int64_t> os = ids->data.shape;
+    os.push_back(dim);
+    Tensor res;
+    MCB_TRY(new_tensor(ctx, MCB_F32, os, &res));
+    MCB_TRY(mcb_embedding(ctx, ids->data.ptr, idt, n, (const float *)weight->data.ptr, vocab, dim, (float *)res.ptr));
+    Tensor idt_t = ids->data;
+    Var wv = weight;
+    *out = apply(ctx, "Embedding", res, {ids, weight}, [ctx, idt_t, wv, vocab, dim, n](const Tensor &g, std::vector<Tensor> &gi) -> mcb_status {
+        bool direct;
+        MCB_TRY(grad_dst(wv, &gi[1], &direct));
+        return mcb_embedding_backward(ctx, idt_t.ptr, idt_t.dt, n, g.ptr, g.dt, vocab, dim, (float *)gi[1].ptr, 0);
+    });
+    return MCB_OK;
+}
+
+mcb_status f_reshape(const Var &x, const std::vector<int64_t> &shape_in, Var *out) {
+    mcb_ctx *ctx = x->ctx;
+    std::vector<int64_t> shape = shape_in;
+    int64_t known = 1, infer = -1;
+    for (size_t i = 0; i < shape.size(); ++i) {
+        if (shape[i] == -1) {
+            if (infer >= 0) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "reshape: more than one -1");
+            infer = (int64_t)i;
+        } else known *= shape[i];
+    }
+    if (infer >= 0) shape[infer] = known ? x->data.numel() / known : 0;
+    int64_t n = 1;
+    for (int64_t d : shape) n *= d;
+    if (n != x->data.numel()) return mcb_fail(ctx, MCB_SHAPE_MISMATCH, "reshape changes the element count");
+    std::vector<int64_t> in_shape = x->data.shape;
+    *out = apply(ctx, "Reshape", view(x->data, shape), {x}, [in_shape](const Tensor &g, std::vector<Tensor> &gi) -> mcb_status {
+        gi[0] = view(g, in_shape);
+        return MCB_OK;
+    });
+    return MCB_OK;
+}
+
+mcb_status f_multi_head_attention(const Var &q, const Var &k, const Var &v, int64_t heads, bool causal, Var *out) {
+    mcb_ctx *ctx = q->ctx;
+    if (q->data.shape.size() != 3) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "attention expects [N, S, D]");
+    if (k->data.shape != q->data.shape || v->data.shape != q->data.shape) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "attention q/k/v shape mismatch");
+    int64_t n = q->data.shape[0], s = q->data.shape[1], d = q->data.shape[2];
+    if (heads <= 0 || d % heads) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "attention dimension must divide heads");
+    int dt = (q->data.dt == MCB_BF16 && k->data.dt == MCB_BF16 && v->data.dt == MCB_BF16) ? MCB_BF16 : MCB_F32;
+    Tensor qt, kt, vt, res, lse;
+    MCB_TRY(to_dtype(ctx, q->data, dt, &qt));
+    MCB_TRY(to_dtype(ctx, k->data, dt, &kt));
+    MCB_TRY(to_dtype(ctx, v->data, dt, &vt));
+    MCB_TRY(new_tensor(ctx, dt, q->data.shape, &res));
+    MCB_TRY(new_tensor(ctx, MCB_F32, {n, heads, s}, &lse));
+    MCB_TRY(mcb_attention(ctx, qt.ptr, kt.ptr, vt.ptr, res.ptr, (float *)lse.ptr, n, s, d, heads, causal, dt));
+    Var qv = q, kv = k, vv = v;
+    *out = apply(ctx, "MultiHeadAttention", res, {q, k, v}, [ctx, qt, kt, vt, res, lse, qv, kv, vv, n, s, d, heads, causal, dt](const Tensor &g, std::vector<Tensor> &gi) -> mcb_status {
+        Tensor gg, dq, dk, dv;
+        MCB_TRY(to_dtype(ctx, g, dt, &gg));
+        MCB_TRY(new_tensor(ctx, dt, qt.shape, &dq));
+        MCB_TRY(new_tensor(ctx, dt, qt.shape, &dk));
+        MCB_TRY(new_tensor(ctx, dt, qt.shape, &dv));
+        MCB_TRY(mcb_attention_backward(ctx, qt.ptr, kt.ptr, vt.ptr, res.ptr, gg.ptr, (const float *)lse.ptr, dq.ptr, dk.ptr, dv.ptr, n, s, d, heads, causal, dt));
+        MCB_TRY(like_input(ctx, dq, qv, &gi[0]));
+        MCB_TRY(like_input(ctx, dk, kv, &gi[1]));
+        MCB_TRY(like_input(ctx, dv, vv, &gi[2]));
+        return MCB_OK;
+    });
+    return MCB_OK;
+}
+
+mcb_status f_conv2d(const Var &x, const Var &w, const Var &b, int64_t stride, int64_t pad, Var *out) {
+    mcb_ctx *ctx = x->ctx;
+    if (x->data.shape.size() != 4 || w->data.shape.size() != 4) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "conv2d expects [N,C,H,W] and [O,C,KH,KW]");
+    int64_t n = x->data.shape[0], c = x->data.shape[1], h = x->data.shape[2], wd = x->data.shape[3];
+    int64_t o = w->data.shape[0], kh = w->data.shape[2], kw = w->data.shape[3];
+    if (c != w->data.shape[1]) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "conv2d channel mismatch");
+    if (b && b->data.numel() != o) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "conv2d bias size mismatch");
+    if (stride <= 0 || h + 2 * pad < kh || wd + 2 * pad < kw) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "conv2d: kernel larger than the padded input");
+    int64_t oh = (h + 2 * pad - kh) / stride + 1, ow = (wd + 2 * pad - kw) / stride + 1;
+    Tensor xf, res;
+    MCB_TRY(f32_of(x, &xf));
+    MCB_TRY(new_tensor(ctx, MCB_F32, {n, o, oh, ow}, &res));
+    MCB_TRY(mcb_conv2d(ctx, (const float *)xf.ptr, (const float *)w->data.ptr, b ? (const float *)b->data.ptr : nullptr, (float *)res.ptr, n, c, h, wd, o, kh, kw, stride, pad));
+    std::vector<Var> ins = {x, w};
+    if (b) ins.push_back(b);
+    Var xv = x, wv = w, bv = b;
+    *out = apply(ctx, "Conv2d", res, ins, [=](const Tensor &g, std::vector<Tensor> &gi) -> mcb_status {
+        Tensor gf;
+        MCB_TRY(to_dtype(ctx, g, MCB_F32, &gf));
+        float *dx = nullptr, *dw = nullptr, *db = nullptr;
+        bool direct;
+        if (xv->requires_grad) {
+            MCB_TRY(new_tensor(ctx, MCB_F32, xf.shape, &gi[0]));
+            dx = (float *)gi[0].ptr;
+        }
+        if (wv->requires_grad) {
+            MCB_TRY(grad_dst(wv, &gi[1], &direct));
+            dw = (float *)gi[1].ptr;
+        }
+        if (bv && bv->requires_grad) {
+            MCB_TRY(grad_dst(bv, &gi[2], &direct));
+            db = (float *)gi[2].ptr;
+        }
+        return mcb_conv2d_backward(ctx, (const float *)xf.ptr, (const float *)wv->data.ptr, (const float *)gf.ptr, dx, dw, db, n, c, h, wd, o, kh, kw, stride, pad);
+    });
+    return MCB_OK;
+}
+
+mcb_status f_max_pool2d(const Var &x, int64_t kernel, int64_t stride, int64_t pad, Var *out) {
+    mcb_ctx *ctx = x->ctx;
+    if (x->data.shape.size() != 4) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "pool2d expects [N,C,H,W]");
+    int64_t n = x->data.shape[0], c = x->data.shape[1], h = x->data.shape[2], w = x->data.shape[3];
+    if (stride <= 0 || h + 2 * pad < kernel || w + 2 * pad < kernel) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "pool2d: window larger than the padded input");
+    int64_t oh = (h + 2 * pad - kernel) / stride + 1, ow = (w + 2 * pad - kernel) / stride + 1;
+    Tensor xf, res;
+    MCB_TRY(f32_of(x, &xf));
+    MCB_TRY(new_tensor(ctx, MCB_F32, {n, c, oh, ow}, &res));
+    MCB_TRY(mcb_max_pool2d(ctx, (const float *)xf.ptr, (float *)res.ptr, n, c, h, w, kernel, stride, pad));
+    *out = apply(ctx, "Pool2d", res, {x}, [=](const Tensor &g, std::vector<Tensor> &gi) -> mcb_status {
+        Tensor gf;
+        MCB_TRY(to_dtype(ctx, g, MCB_F32, &gf));
+        MCB_TRY(new_tensor(ctx, MCB_F32, xf.shape, &gi[0]));
+        return mcb_max_pool2d_backward(ctx, (const float *)xf.ptr, (const float *)gf.ptr, (float *)gi[0].ptr, n, c, h, w, kernel, stride, pad);
+    });
+    return MCB_OK;
+}
+
+// ------------------------------------------------------------------ arena
+static int64_t align_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
+
+mcb_status arena_create(mcb_ctx *ctx, const std::vector<Var> &params, Arena **out) {
+    auto a = std::make_unique<Arena>();
+    a->ctx = ctx;
+    int64_t off = 0;
+    for (auto &p : params) {
+        if (p->arena) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "a parameter already belongs to an arena");
+        if (p->data.dt != MCB_F32) return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "arena parameters must be f32");
+        a->off.push_back(off);
+        a->size.push_back(p->data.numel());
+        off += align_up(p->data.numel(), 64); // 256-byte aligned slots: vector access and TMA bases stay legal
+    }
+    a->total = off;
+    auto mk = [&](size_t bytes, std::shared_ptr<Buf> *b) -> mcb_status {
+        void *p = nullptr;
+        MCB_TRY(mcb_alloc(ctx, bytes ? bytes : 16, &p));
+        *b = std::make_shared<Buf>(ctx, p);
+        return mcb_memset(ctx, p, 0, bytes);
+    };
+    MCB_TRY(mk(sizeof(float) * off, &a->p));
+    MCB_TRY(mk(sizeof(float) * off, &a->g));
+    MCB_TRY(mk(sizeof(float) * off, &a->m));
+    MCB_TRY(mk(sizeof(float) * off, &a->v));
+    MCB_TRY(mk(2 * (size_t)off, &a->shadow));
+    for (size_t i = 0; i < params.size(); ++i) {
+        auto &p = params[i];
+        float *dst = (float *)a->p->p + a->off[i];
+        MCB_TRY(mcb_memcpy_d2d(ctx, dst, p->data.ptr, sizeof(float) * a->size[i]));
+        Tensor t;
+        t.buf = a->p;
+        t.ptr = dst;
+        t.dt = MCB_F32;
+        t.shape = p->data.shape;
+        t.defined = true;
+        bool had = p->has_grad;
+        Tensor old_grad = p->grad;
+        p->data = t;
+        p->arena = a.get();
+        p->arena_idx = (int)i;
+        p->has_grad = false;
+        p->grad = Tensor();
+        if (had) MCB_TRY(accumulate_leaf(p, old_grad));
+        a->vars.push_back(p);
+        a->step.push_back(0);
+    }
+    a->shadow_valid = false;
+    *out = a.release();
+    return MCB_OK;
+}
+
+void arena_release(Arena *a) {
+    if (!a) return;
+    for (auto &v : a->vars) {
+        v->arena = nullptr; // data/grad views keep the buffers alive through their shared_ptr
+        v->arena_idx = -1;
+    }
+    delete a;
+}
+
+mcb_status arena_refresh_shadow(Arena *a) {
+    if (a->shadow_valid) return MCB_OK;
+    MCB_TRY(mcb_cast(a->ctx, a->p->p, MCB_F32, a->shadow->p, MCB_BF16, a->total));
+    a->shadow_valid = true;
+    return MCB_OK;
+}
+
+// ------------------------------------------------------------------ optimizers
+void zero_grad(const std::vector<Var> &params) {
+    for (auto &p : params) {
+        p->has_grad = false;
+        p->grad = Tensor();
+    }
+}
+
+mcb_status AdamOpt::update(const std::vector<Var> &params, const float *inv_scale_dev, double inv_scale_host, const int32_t *skip,
+                           const int32_t *step_dev) {
+    // arena fast path: every listed parameter lives in one arena, all have gradients and equal step counts
+    Arena *a = params.empty() ? nullptr : params[0]->arena;
+    bool flat = a != nullptr && params.size() == a->vars.size();
+    if (flat) {
+        for (size_t i = 0; i < params.size() && flat; ++i)
+            flat = params[i]->arena == a && params[i]->arena_idx == (int)i && params[i]->has_grad && a->step[i] == a->step[0];
+    }
+    if (flat) {
+        MCB_TRY(arena_wait_comm(a));
+        double inv = inv_scale_host * arena_grad_divisor(a);
+        int32_t t = a->step[0] + 1;
+        MCB_TRY(mcb_adam_flat_ex(ctx, (float *)a->p->p, a->g->p, MCB_F32, (float *)a->m->p, (float *)a->v->p, a->shadow->p, a->total, lr, beta1,
+                                 beta2, eps, t, inv, inv_scale_dev, skip, step_dev));
+        // the step counter advances on the host even if the device skips: a skipped step must not
+        // count, so callers that pass `skip` roll it back through rollback_step() once they know
+        for (auto &s : a->step) s = t;
+        a->shadow_valid = true;
+        return MCB_OK;
+    }
+    for (auto &p : params) {
+        if (!p->has_grad) continue; // parameters without a gradient are skipped (optim/src/lib.rs:87-89)
+        if (p->arena) {
+            Arena *pa = p->arena;
+            MCB_TRY(arena_wait_comm(pa));
+            int i = p->arena_idx;
+            int32_t t = ++pa->step[i];
+            int64_t off = pa->off[i];
+            MCB_TRY(mcb_adam_flat_ex(ctx, (float *)pa->p->p + off, (float *)pa->g->p + off, MCB_F32, (float *)pa->m->p + off, (float *)pa->v->p + off,
+                                     (__nv_bfloat16 *)pa->shadow->p + off, pa->size[i], lr, beta1, beta2, eps, t, inv_scale_host * arena_grad_divisor(pa),
+                                     inv_scale_dev, skip, step_dev));
+            continue;
+        }
+        AdamState &st = state[p.get()];
+        if (!st.m.defined) {
+            MCB_TRY(new_tensor(ctx, MCB_F32, p->data.shape, &st.m));
+            MCB_TRY(new_tensor(ctx, MCB_F32, p->data.shape, &st.v));
+            MCB_TRY(mcb_memset(ctx, st.m.ptr, 0, sizeof(float) * st.m.numel()));
+            MCB_TRY(mcb_memset(ctx, st.v.ptr, 0, sizeof(float) * st.v.numel()));
+        }
+        st.t += 1;
+        Tensor gf;
+        MCB_TRY(to_dtype(ctx, p->grad, MCB_F32, &gf));
+        MCB_TRY(mcb_adam_flat_ex(ctx, (float *)p->data.ptr, gf.ptr, MCB_F32, (float *)st.m.ptr, (float *)st.v.ptr, nullptr, p->data.numel(), lr, beta1, beta2,
+                                 eps, st.t, inv_scale_host, inv_scale_dev, skip, step_dev));
+    }
+    return MCB_OK;
+}
+
+void AdamOpt::rollback_step(const std::vector<Var> &params) {
+    for (auto &p : params) {
+        if (!p->has_grad) continue;
+        if (p->arena) {
+            if (p->arena->step[p->arena_idx] > 0) p->arena->step[p->arena_idx]--;
+        } else {
+            auto it = state.find(p.get());
+            if (it != state.end() && it->second.t > 0) it->second.t--;
+        }
+    }
+}
+
+AdamOpt::~AdamOpt() {}
+
+mcb_status scaler_create(mcb_ctx *ctx, double init_scale, double growth, double backoff, int interval, Scaler **out) {
+    auto s = std::make_unique<Scaler>();
+    s->ctx = ctx;
+    s->growth = growth;
+    s->backoff = backoff;
+    s->interval = interval;
+    void *p = nullptr;
+    MCB_TRY(mcb_alloc(ctx, 64, &p));
+    s->state = std::make_shared<Buf>(ctx, p);
+    float sc = (float)(init_scale < 1.0 ? 1.0 : init_scale); // with_scale clamps to >= 1 (amp.rs:27-30)
+    struct {
+        float f[2];
+        int i[4];
+    } init = {{sc, 1.0f / sc}, {0, 0, 0, 0}};
+    MCB_TRY(mcb_memcpy_h2d(ctx, p, &init, sizeof(init)));
+    MCB_TRY(mcb_sync(ctx)); // `init` is a stack object
+    *out = s.release();
+    return MCB_OK;
+}
+
+static mcb_status scaler_check(Scaler *s, const std::vector<Var> &params) {
+    mcb_ctx *ctx = s->ctx;
+    int *flag = s->state_i() + 1;
+    Arena *a = params.empty() ? nullptr : params[0]->arena;
+    bool flat = a != nullptr && params.size() == a->vars.size();
+    for (size_t i = 0; i < params.size() && flat; ++i) flat = params[i]->arena == a && params[i]->has_grad;
+    if (flat) {
+        MCB_TRY(arena_wait_comm(a));
+        return mcb_check_finite(ctx, a->g->p, MCB_F32, a->total, flag);
+    }
+    for (auto &p : params) {
+        if (!p->has_grad) continue;
+        if (p->arena) MCB_TRY(arena_wait_comm(p->arena));
+        MCB_TRY(mcb_check_finite(ctx, p->grad.ptr, p->grad.dt, p->grad.numel(), flag));
+    }
+    return MCB_OK;
+}
+
+mcb_status scaler_step(Scaler *s, AdamOpt *opt, const std::vector<Var> &params, bool sync, int32_t *applied) {
+    mcb_ctx *ctx = s->ctx;
+    // 1. inf/nan scan of the scaled gradients (before unscale, like has_non_finite_grad)
+    MCB_TRY(scaler_check(s, params));
+    // 2. unscale fused into the optimizer pass; the kernel changes nothing when the flag is set
+    // async: the device-resident count of applied steps drives the bias correction, so a skipped
+    // step does not advance it even though the host never learns about the skip
+    MCB_TRY(opt->update(params, s->state_f() + 1, 1.0, s->state_i() + 1, sync ? nullptr : s->state_i() + 3));
+    // 3. backoff / growth bookkeeping on the device
+    MCB_TRY(mcb_scaler_update(ctx, s->state_f(), s->state_i(), (float)s->growth, (float)s->backoff, s->interval));
+    if (!sync) return MCB_OK;
+    int found = 0;
+    MCB_TRY(mcb_memcpy_d2h(ctx, &found, s->state_i() + 2, sizeof(int)));
+    if (found) {
+        opt->rollback_step(params);
+        zero_grad(params); // the reference clears the gradients of a skipped step (amp.rs:71-76)
+    }
+    if (applied) *applied = found ? 0 : 1;
+    return MCB_OK;
+}
+
+// ------------------------------------------------------------------ initialisers and models
+// xorshift64* with polar Box-Muller, the reference's parameter RNG (core/src/rng.rs:14-56)
+struct Rng {
+    uint64_t state;
+    bool has_spare = false;
+    double spare = 0.0;
+    explicit Rng(uint64_t seed) : state((seed * 0x9E3779B97F4A7C15ull) | 1ull) {}
+    uint64_t next_u64() {
+        uint64_t x = state;
+        x ^= x >> 12;
+        x ^= x << 25;
+        x ^= x >> 27;
+        state = x;
+        return x * 0x2545F4914F6CDD1Dull;
+    }
+    double next_f64() { return (double)(next_u64() >> 11) * (1.0 / 9007199254740992.0); }
+    double normal() {
+        if (has_spare) {
+            has_spare = false;
+            return spare;
+        }
+        for (;;) {
+            double u = 2.0 * next_f64() - 1.0, v = 2.0 * next_f64() - 1.0, s = u * u + v * v;
+            if (s > 0.0 && s < 1.0) {
+                double f = std::sqrt(-2.0 * std::log(s) / s);
+                spare = v * f;
+                has_spare = true;
+                return u * f;
+            }
+        }
+    }
+    void fill(std::vector<float> &out, double mean, double std) {
+        for (auto &o : out) o = (float)(mean + std * normal());
+    }
+};
+
+static mcb_status param_from_host(mcb_ctx *ctx, const std::vector<float> &h, const std::vector<int64_t> &shape, Var *out) {
+    Tensor t;
+    MCB_TRY(new_tensor(ctx, MCB_F32, shape, &t));
+    MCB_TRY(mcb_memcpy_h2d(ctx, t.ptr, h.data(), sizeof(float) * h.size()));
+    MCB_TRY(mcb_sync(ctx)); // the host vector is released by the caller
+    *out = make_var(ctx, t, true);
+    return MCB_OK;
+}
+static mcb_status he_param(mcb_ctx *ctx, const std::vector<int64_t> &shape, int64_t fan_in, uint64_t seed, Var *out) {
+    int64_t n = 1;
+    for (int64_t d : shape) n *= d;
+    std::vector<float> h((size_t)n);
+    Rng r(seed);
+    r.fill(h, 0.0, std::sqrt(2.0 / (double)(fan_in > 1 ? fan_in : 1)));
+    return param_from_host(ctx, h, shape, out);
+}
+static mcb_status const_param(mcb_ctx *ctx, int64_t n, float value, Var *out) {
+    std::vector<float> h((size_t)n, value);
+    return param_from_host(ctx, h, {n}, out);
+}
+
+struct LinearL {
+    Var w, b;
+    mcb_status init(mcb_ctx *ctx, int64_t in, int64_t outf, uint64_t seed) {
+        MCB_TRY(he_param(ctx, {outf, in}, in, seed, &w));
+        return const_param(ctx, outf, 0.0f, &b);
+    }
+};
+
+mcb_status Model::create(mcb_ctx *ctx, int kind, const std::vector<int64_t> &cfg, Model **out) {
+    auto m = std::make_unique<Model>();
+    m->ctx = ctx;
+    m->kind = kind;
+    m->cfg = cfg;
+    auto need = [&](size_t n) -> mcb_status { return cfg.size() >= n ? MCB_OK : mcb_fail(ctx, MCB_INVALID_ARGUMENT, "model config too short"); };
+    auto lin = [&](int64_t in, int64_t o, uint64_t seed) -> mcb_status {
+        LinearL l;
+        MCB_TRY(l.init(ctx, in, o, seed));
+        m->params.push_back(l.w);
+        m->params.push_back(l.b);
+        return MCB_OK;
+    };
+    auto ln = [&](int64_t d) -> mcb_status {
+        Var g, b;
+        MCB_TRY(const_param(ctx, d, 1.0f, &g));
+        MCB_TRY(const_param(ctx, d, 0.0f, &b));
+        m->params.push_back(g);
+        m->params.push_back(b);
+        return MCB_OK;
+    };
+    if (kind == 0) { // MLP: Linear seeds 0, 1
+        MCB_TRY(need(3));
+        MCB_TRY(lin(cfg[0], cfg[1], 0));
+        MCB_TRY(lin(cfg[1], cfg[2], 1));
+    } else if (kind == 1) { // encoder block: ln1, MHA(q,k,v,o seeds 1..4), ln2, ffn seeds 5, 6
+        MCB_TRY(need(4));
+        int64_t d = cfg[0], ff = cfg[2];
+        MCB_TRY(ln(d));
+        for (uint64_t s = 1; s <= 4; ++s) MCB_TRY(lin(d, d, s));
+        MCB_TRY(ln(d));
+        MCB_TRY(lin(d, ff, 5));
+        MCB_TRY(lin(ff, d, 6));
+    } else if (kind == 2) { // CNN: conv seeds 0, 1 (fan_in = C*KH*KW), fc seed 2
+        MCB_TRY(need(5));
+        int64_t cin = cfg[0], c1 = cfg[1], c2 = cfg[2], hw = cfg[3], classes = cfg[4];
+        Var w, b;
+        MCB_TRY(he_param(ctx, {c1, cin, 3, 3}, cin * 9, 0, &w));
+        MCB_TRY(const_param(ctx, c1, 0.0f, &b));
+        m->params.push_back(w);
+        m->params.push_back(b);
+        MCB_TRY(he_param(ctx, {c2, c1, 3, 3}, c1 * 9, 1, &w));
+        MCB_TRY(const_param(ctx, c2, 0.0f, &b));
+        m->params.push_back(w);
+        m->params.push_back(b);
+        MCB_TRY(lin(c2 * (hw / 4) * (hw / 4), classes, 2));
+    } else if (kind == 3) { // decoder: one RNG stream in the order of Decoder::new (llm/src/decoder.rs:98-140)
+        MCB_TRY(need(6));
+        int64_t vocab = cfg[0], d = cfg[1], ff = cfg[3], layers = cfg[4];
+        Rng rng((uint64_t)cfg[5]);
+        auto mat = [&](int64_t r, int64_t c, double std) -> mcb_status {
+            std::vector<float> h((size_t)(r * c));
+            rng.fill(h, 0.0, std);
+            Var v;
+            MCB_TRY(param_from_host(ctx, h, {r, c}, &v));
+            m->params.push_back(v);
+            return MCB_OK;
+        };
+        auto vec = [&](int64_t n, float val) -> mcb_status {
+            Var v;
+            MCB_TRY(const_param(ctx, n, val, &v));
+            m->params.push_back(v);
+            return MCB_OK;
+        };
+        MCB_TRY(mat(vocab, d, 0.02));
+        double sd = std::sqrt(2.0 / (double)d), sff = std::sqrt(2.0 / (double)ff);
+        for (int64_t l = 0; l < layers; ++l) {
+            MCB_TRY(vec(d, 1.0f)); MCB_TRY(vec(d, 0.0f));            // ln1
+            for (int i = 0; i < 4; ++i) { MCB_TRY(mat(d, d, sd)); MCB_TRY(vec(d, 0.0f)); } // q k v o
+            MCB_TRY(vec(d, 1.0f)); MCB_TRY(vec(d, 0.0f));            // ln2
+            MCB_TRY(mat(ff, d, sd)); MCB_TRY(vec(ff, 0.0f));         // w1 b1
+            MCB_TRY(mat(d, ff, sff)); MCB_TRY(vec(d, 0.0f));         // w2 b2
+        }
+        MCB_TRY(vec(d, 1.0f)); MCB_TRY(vec(d, 0.0f));                // ln_f
+        MCB_TRY(mat(vocab, d, 0.02));                                // lm_head (untied, no bias)
+    } else {
+        return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "unknown model kind %d", kind);
+    }
+    *out = m.release();
+    return MCB_OK;
+}
+
+mcb_status Model::loss(const Var &input, const Var &target, Var *out) {
+    const std::vector<Var> &P = params;
+    const double eps = 1e-5;
+    if (kind == 0) {
+        Var h, a, logits;
+        MCB_TRY(f_linear(input, P[0], P[1], &h));
+        MCB_TRY(f_relu(h, &a));
+        MCB_TRY(f_linear(a, P[2], P[3], &logits));
+        return f_softmax_cross_entropy(logits, target, out);
+    }
+    if (kind == 1) {
+        int64_t heads = cfg[1];
+        bool causal = cfg[3] != 0;
+        if (input->data.shape.size() != 3) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "encoder block expects [N, S, D]");
+        int64_t b = input->data.shape[0], s = input->data.shape[1], d = input->data.shape[2];
+        Var n1, flat, q, k, v, q3, k3, v3, att, att2, o, o3, x1, n2, flat2, h, f2, f3, y, diff, sq;
+        MCB_TRY(f_layer_norm(input, P[0], P[1], eps, &n1));
+        MCB_TRY(f_reshape(n1, {b * s, d}, &flat));
+        MCB_TRY(f_linear(flat, P[2], P[3], &q));
+        MCB_TRY(f_linear(flat, P[4], P[5], &k));
+        MCB_TRY(f_linear(flat, P[6], P[7], &v));
+        MCB_TRY(f_reshape(q, {b, s, d}, &q3));
+        MCB_TRY(f_reshape(k, {b, s, d}, &k3));
+        MCB_TRY(f_reshape(v, {b, s, d}, &v3));
+        MCB_TRY(f_multi_head_attention(q3, k3, v3, heads, causal, &att));
+        MCB_TRY(f_reshape(att, {b * s, d}, &att2));
+        MCB_TRY(f_linear(att2, P[8], P[9], &o));
+        MCB_TRY(f_reshape(o, {b, s, d}, &o3));
+        MCB_TRY(f_binary(MCB_ADD, input, o3, &x1));
+        MCB_TRY(f_layer_norm(x1, P[10], P[11], eps, &n2));
+        MCB_TRY(f_reshape(n2, {b * s, d}, &flat2));
+        MCB_TRY(f_linear_activation(flat2, P[12], P[13], MCB_ACT_GELU, &h));
+        MCB_TRY(f_linear(h, P[14], P[15], &f2));
+        MCB_TRY(f_reshape(f2, {b, s, d}, &f3));
+        MCB_TRY(f_binary(MCB_ADD, x1, f3, &y));
+        MCB_TRY(f_binary(MCB_SUB, y, target, &diff));
+        MCB_TRY(f_binary(MCB_MUL, diff, diff, &sq));
+        return f_mean(sq, out);
+    }
+    if (kind == 2) {
+        Var c1, r1, p1, c2, r2, p2, flat, logits;
+        MCB_TRY(f_conv2d(input, P[0], P[1], 1, 1, &c1));
+        MCB_TRY(f_relu(c1, &r1));
+        MCB_TRY(f_max_pool2d(r1, 2, 2, 0, &p1));
+        MCB_TRY(f_conv2d(p1, P[2], P[3], 1, 1, &c2));
+        MCB_TRY(f_relu(c2, &r2));
+        MCB_TRY(f_max_pool2d(r2, 2, 2, 0, &p2));
+        MCB_TRY(f_reshape(p2, {p2->data.shape[0], -1}, &flat));
+        MCB_TRY(f_linear(flat, P[4], P[5], &logits));
+        return f_softmax_cross_entropy(logits, target, out);
+    }
+    // decoder (forward order of llm/src/decoder.rs:213-241, training form: full sequence, causal)
+    int64_t heads = cfg[2], layers = cfg[4];
+    if (input->data.shape.size() != 2) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "decoder expects ids [N, S]");
+    int64_t b = input->data.shape[0], s = input->data.shape[1], d = cfg[1];
+    Var ids, tgt, x;
+    MCB_TRY(f_reshape(input, {b * s}, &ids));
+    MCB_TRY(f_reshape(target, {b * s}, &tgt));
+    MCB_TRY(f_embedding(ids, P[0], &x));
+    size_t pi = 1;
+    for (int64_t l = 0; l < layers; ++l, pi += 16) {
+        Var n1, q, k, v, q3, k3, v3, att, att2, o, x1, n2, h, f2, x2;
+        MCB_TRY(f_layer_norm(x, P[pi + 0], P[pi + 1], eps, &n1));
+        MCB_TRY(f_linear(n1, P[pi + 2], P[pi + 3], &q));
+        MCB_TRY(f_linear(n1, P[pi + 4], P[pi + 5], &k));
+        MCB_TRY(f_linear(n1, P[pi + 6], P[pi + 7], &v));
+        MCB_TRY(f_reshape(q, {b, s, d}, &q3));
+        MCB_TRY(f_reshape(k, {b, s, d}, &k3));
+        MCB_TRY(f_reshape(v, {b, s, d}, &v3));
+        MCB_TRY(f_multi_head_attention(q3, k3, v3, heads, true, &att));
+        MCB_TRY(f_reshape(att, {b * s, d}, &att2));
+        MCB_TRY(f_linear(att2, P[pi + 8], P[pi + 9], &o));
+        MCB_TRY(f_binary(MCB_ADD, x, o, &x1));
+        MCB_TRY(f_layer_norm(x1, P[pi + 10], P[pi + 11], eps, &n2));
+        MCB_TRY(f_linear_activation(n2, P[pi + 12], P[pi + 13], MCB_ACT_GELU, &h));
+        MCB_TRY(f_linear(h, P[pi + 14], P[pi + 15], &f2));
+        MCB_TRY(f_binary(MCB_ADD, x1, f2, &x2));
+        x = x2;
+    }
+    Var nf, logits;
+    MCB_TRY(f_layer_norm(x, P[pi + 0], P[pi + 1], eps, &nf));
+    MCB_TRY(f_linear(nf, P[pi + 2], nullptr, &logits));
+    return f_sce_consuming(logits, tgt, out);
+}
+
+} // namespace mcbag

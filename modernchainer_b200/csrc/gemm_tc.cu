@@ -1,0 +1,502 @@
+// bf16 tensor-core GEMM for sm_100a: tcgen05.mma with the accumulator in TMEM, operands
+// staged in shared memory by per-CTA TMA loads, persistent warp-specialised CTAs.
+//
+//   D[M,N] (+)= A * B (+ bias) -> act,  f32 accumulate, D stored as bf16 or f32.
+//
+// Operand storage (both bf16):
+//   K-major  : [rows, K] with K contiguous  -> TMA box {64 k, rows} -> 128-byte swizzled rows
+//   MN-major : [K, rows] with rows contiguous -> TMA boxes {64 rows, 64 k}
+// so fprop (x W^T), dgrad (g W) and wgrad (g^T x) all read the tensors where they lie; no
+// transposed copy is ever made.
+//
+// CTA layout (192 threads): warp 0 issues TMA, warp 1 issues MMA and owns the TMEM
+// allocation, warps 2..5 drain the accumulator (one TMEM lane quarter each) and write D.
+// Two accumulators (2 x BN columns of TMEM) let the epilogue of tile i overlap the MMAs of
+// tile i+1.  A 4..6-deep smem ring decouples TMA from MMA.
+//
+// Every wait on an mbarrier is bounded by wall time; on expiry the CTA raises the device
+// error word, stops issuing work, and still frees its TMEM before returning.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "internal.h"
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64; // 64 bf16 = one 128-byte swizzle row
+constexpr int kThreads = 192;
+constexpr unsigned long long kWaitLimitNs = 2000000000ull; // 2 s
+
+struct TcArgs {
+    void *d;
+    void *d_pre;
+    const float *bias;
+    long long m, n, k, ldd;
+    int out_bf16, accumulate, act, split_k;
+    int a_mn, b_mn;
+    unsigned idesc;
+    int m_tiles, n_tiles, kb_total, kb_per_split;
+    unsigned int *err;
+};
+
+// ------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ unsigned smem_u32(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(unsigned long long *bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long *bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned long long *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_test(unsigned long long *bar, unsigned parity) {
+    unsigned ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok)
+                 : "r"(smem_u32(bar)), "r"(parity)
+                 : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+// bounded wait; returns false after the time limit or once another role aborted
+__device__ __forceinline__ bool mbar_wait(unsigned long long *bar, unsigned parity, volatile int *abort_flag,
+                                          unsigned int *err) {
+    if (mbar_test(bar, parity)) return true;
+    unsigned long long t0 = global_ns();
+    unsigned spins = 0;
+    for (;;) {
+        if (mbar_test(bar, parity)) return true;
+        if ((++spins & 63u) == 0) {
+            if (*abort_flag) return false;
+            if (global_ns() - t0 > kWaitLimitNs) {
+                *abort_flag = 1;
+                atomicOr(err, MCB_DEVERR_TIMEOUT);
+                return false;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(void *smem_dst, const CUtensorMap *map, unsigned long long *bar, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 :
+                 : "r"(smem_u32(smem_dst)), "l"((unsigned long long)map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(unsigned *smem_dst, unsigned ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_dealloc(unsigned taddr, unsigned ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(unsigned long long *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_mma(unsigned tmem_d, unsigned long long adesc, unsigned long long bdesc, unsigned idesc,
+                                       unsigned accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 :
+                 : "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(unsigned taddr, unsigned (&r)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor (sm_100 format): start address >> 4 in bits [0,14),
+// leading byte offset >> 4 in [16,30), stride byte offset >> 4 in [32,46), version 1 in
+// [46,48), layout type 2 (128-byte swizzle) in [61,64).
+__device__ __forceinline__ unsigned long long make_desc(unsigned smem_addr, unsigned lbo_bytes, unsigned sbo_bytes) {
+    unsigned long long d = 0;
+    d |= (unsigned long long)((smem_addr & 0x3FFFFu) >> 4);
+    d |= (unsigned long long)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+    d |= (unsigned long long)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+    d |= 1ull << 46;
+    d |= 2ull << 61;
+    return d;
+}
+
+__device__ __forceinline__ float gelu_f(float v) {
+    float v3 = v * v * v;
+    return 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v3)));
+}
+
+template <int BN> struct Cfg {
+    static constexpr int kStageBytes = (BM + BN) * BK * 2;
+    static constexpr int kStages = (BN == 256) ? 4 : (BN == 192 ? 5 : 6);
+    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(kThreads, 1)
+tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcArgs args) {
+    constexpr int kStages = Cfg<BN>::kStages;
+    constexpr int kABytes = BM * BK * 2, kBBytes = BN * BK * 2;
+    extern __shared__ unsigned char smem_raw[];
+    // operand tiles need 1024-byte alignment for the 128-byte swizzle pattern
+    unsigned char *tiles = (unsigned char *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    unsigned long long *bars = (unsigned long long *)(tiles + kStages * Cfg<BN>::kStageBytes);
+    unsigned long long *full_bar = bars, *empty_bar = bars + kStages;
+    unsigned long long *acc_full = bars + 2 * kStages, *acc_empty = acc_full + 2;
+    unsigned *tmem_slot = (unsigned *)(acc_empty + 2);
+    volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
+
+    int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(&acc_full[a], 1);
+            mbar_init(&acc_empty[a], 4);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    unsigned tmem_base = *tmem_slot;
+
+    long long tiles_mn = (long long)args.m_tiles * args.n_tiles;
+    long long work_total = tiles_mn * args.split_k;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- TMA producer
+        if (lane == 0) {
+            unsigned it = 0;
+            for (long long w = blockIdx.x; w < work_total; w += gridDim.x) {
+                long long t = w % tiles_mn;
+                int split = (int)(w / tiles_mn);
+                int m0 = (int)(t % args.m_tiles) * BM, n0 = (int)(t / args.m_tiles) * BN;
+                int kb0 = split * args.kb_per_split;
+                int kb1 = min(kb0 + args.kb_per_split, args.kb_total);
+                bool ok = true;
+                for (int kb = kb0; kb < kb1 && ok; ++kb, ++it) {
+                    int s = it % kStages;
+                    unsigned ph = (it / kStages) & 1u;
+                    ok = mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag, args.err);
+                    if (!ok) break;
+                    unsigned char *sa = tiles + s * Cfg<BN>::kStageBytes, *sb = sa + kABytes;
+                    mbar_expect_tx(&full_bar[s], kABytes + kBBytes);
+                    int k0 = kb * BK;
+                    if (!args.a_mn) {
+                        tma_load_2d(sa, &map_a, &full_bar[s], k0, m0);
+                    } else {
+#pragma unroll
+                        for (int b = 0; b < BM / 64; ++b) tma_load_2d(sa + b * 8192, &map_a, &full_bar[s], m0 + b * 64, k0);
+                    }
+                    if (!args.b_mn) {
+                        tma_load_2d(sb, &map_b, &full_bar[s], k0, n0);
+                    } else {
+#pragma unroll
+                        for (int b = 0; b < BN / 64; ++b) tma_load_2d(sb + b * 8192, &map_b, &full_bar[s], n0 + b * 64, k0);
+                    }
+                }
+                if (!ok) break;
+            }
+            // drain: wait until every load that was issued has been consumed (bounded), so no
+            // copy is still writing this CTA's shared memory when it exits
+            for (int s = 0; s < kStages; ++s) {
+                unsigned filled = (it > (unsigned)s) ? ((it - 1 - s) / kStages + 1) : 0; // times stage s was filled
+                if (filled == 0) continue;
+                if (!mbar_wait(&empty_bar[s], (filled - 1) & 1u, abort_flag, args.err)) break;
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            unsigned it = 0, tile_it = 0;
+            // descriptor geometry per operand
+            unsigned a_lbo = args.a_mn ? 8192u : 16u, a_sbo = 1024u, a_kstep = args.a_mn ? 2048u : 32u;
+            unsigned b_lbo = args.b_mn ? 8192u : 16u, b_sbo = 1024u, b_kstep = args.b_mn ? 2048u : 32u;
+            for (long long w = blockIdx.x; w < work_total; w += gridDim.x, ++tile_it) {
+                int split = (int)(w / tiles_mn);
+                int kb0 = split * args.kb_per_split;
+                int kb1 = min(kb0 + args.kb_per_split, args.kb_total);
+                int acc = tile_it & 1;
+                unsigned acc_ph = (tile_it >> 1) & 1u;
+                if (!mbar_wait(&acc_empty[acc], acc_ph ^ 1u, abort_flag, args.err)) break;
+                tc_fence_after();
+                unsigned tmem_d = tmem_base + (unsigned)(acc * BN);
+                bool ok = true;
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
+                    int s = it % kStages;
+                    unsigned ph = (it / kStages) & 1u;
+                    ok = mbar_wait(&full_bar[s], ph, abort_flag, args.err);
+                    if (!ok) break;
+                    tc_fence_after();
+                    unsigned sa = smem_u32(tiles + s * Cfg<BN>::kStageBytes), sb = sa + kABytes;
+#pragma unroll
+                    for (int j = 0; j < BK / 16; ++j) {
+                        unsigned long long ad = make_desc(sa + j * a_kstep, a_lbo, a_sbo);
+                        unsigned long long bd = make_desc(sb + j * b_kstep, b_lbo, b_sbo);
+                        tc_mma(tmem_d, ad, bd, args.idesc, (kb > kb0 || j > 0) ? 1u : 0u);
+                    }
+                    tc_commit(&empty_bar[s]); // frees the smem stage once these MMAs have read it
+                }
+                if (!ok) break;
+                tc_commit(&acc_full[acc]); // accumulator complete
+            }
+        }
+    } else {
+        // ---------------------------------------------------------------- epilogue (warps 2..5)
+        int q = warp & 3; // TMEM lane quarter this warp may access
+        unsigned tile_it = 0;
+        for (long long w = blockIdx.x; w < work_total; w += gridDim.x, ++tile_it) {
+            long long t = w % tiles_mn;
+            int split = (int)(w / tiles_mn);
+            int kb0 = split * args.kb_per_split;
+            bool has_k = kb0 < args.kb_total;
+            long long m0 = (t % args.m_tiles) * BM, n0 = (t / args.m_tiles) * (long long)BN;
+            int acc = tile_it & 1;
+            unsigned acc_ph = (tile_it >> 1) & 1u;
+            if (!mbar_wait(&acc_full[acc], acc_ph, abort_flag, args.err)) break;
+            tc_fence_after();
+            long long row = m0 + q * 32 + lane;
+            bool add_bias = args.bias != nullptr && split == 0;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                unsigned r[32];
+                unsigned taddr = tmem_base + ((unsigned)(q * 32) << 16) + (unsigned)(acc * BN + c0);
+                tmem_ld32(taddr, r);
+                tmem_ld_wait();
+                long long col0 = n0 + c0;
+                if (row < args.m && col0 < args.n && has_k) {
+                    float v[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+                    if (add_bias) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (col0 + j < args.n) v[j] += args.bias[col0 + j];
+                    }
+                    bool full = (col0 + 32 <= args.n);
+                    if (args.accumulate) {
+                        float *dst = (float *)args.d + row * args.ldd + col0;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (full || col0 + j < args.n) atomicAdd(dst + j, v[j]);
+                    } else if (args.out_bf16) {
+                        __nv_bfloat16 *dst = (__nv_bfloat16 *)args.d + row * args.ldd + col0;
+                        __nv_bfloat16 *pre = args.d_pre ? (__nv_bfloat16 *)args.d_pre + row * args.ldd + col0 : nullptr;
+                        if (pre) {
+                            if (full) {
+#pragma unroll
+                                for (int j = 0; j < 32; j += 8) {
+                                    uint4 pk;
+                                    __nv_bfloat162 p0 = __floats2bfloat162_rn(v[j], v[j + 1]), p1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+                                    __nv_bfloat162 p2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]), p3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+                                    pk.x = *(unsigned *)&p0; pk.y = *(unsigned *)&p1; pk.z = *(unsigned *)&p2; pk.w = *(unsigned *)&p3;
+                                    *(uint4 *)(pre + j) = pk;
+                                }
+                            } else {
+                                for (int j = 0; j < 32; ++j)
+                                    if (col0 + j < args.n) pre[j] = __float2bfloat16_rn(v[j]);
+                            }
+                        }
+                        if (args.act == MCB_ACT_GELU) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) v[j] = gelu_f(v[j]);
+                        } else if (args.act == MCB_ACT_RELU) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) v[j] = v[j] > 0.0f ? v[j] : 0.0f;
+                        }
+                        if (full) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 8) {
+                                uint4 pk;
+                                __nv_bfloat162 p0 = __floats2bfloat162_rn(v[j], v[j + 1]), p1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+                                __nv_bfloat162 p2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]), p3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+                                pk.x = *(unsigned *)&p0; pk.y = *(unsigned *)&p1; pk.z = *(unsigned *)&p2; pk.w = *(unsigned *)&p3;
+                                *(uint4 *)(dst + j) = pk;
+                            }
+                        } else {
+                            for (int j = 0; j < 32; ++j)
+                                if (col0 + j < args.n) dst[j] = __float2bfloat16_rn(v[j]);
+                        }
+                    } else {
+                        float *dst = (float *)args.d + row * args.ldd + col0;
+                        if (args.act == MCB_ACT_GELU) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) v[j] = gelu_f(v[j]);
+                        } else if (args.act == MCB_ACT_RELU) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) v[j] = v[j] > 0.0f ? v[j] : 0.0f;
+                        }
+                        if (full) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4) *(float4 *)(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                        } else {
+                            for (int j = 0; j < 32; ++j)
+                                if (col0 + j < args.n) dst[j] = v[j];
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[acc]);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, 512);
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// 2-D bf16 tensor map: inner (contiguous) extent `inner`, outer extent `outer`, row pitch `ld` elements
+mcb_status make_map(mcb_ctx *ctx, CUtensorMap *map, const void *base, long long inner, long long outer, long long ld,
+                    int box_inner, int box_outer) {
+    EncodeTiledFn enc = get_encode();
+    if (!enc) return mcb_fail(ctx, MCB_BACKEND, "cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return mcb_fail(ctx, MCB_BACKEND, "cuTensorMapEncodeTiled failed with %d", (int)r);
+    return MCB_OK;
+}
+
+template <int BN> mcb_status launch(mcb_ctx *ctx, const TcGemmParams &p) {
+    CUtensorMap map_a, map_b;
+    if (!p.a_mn_major) MCB_TRY(make_map(ctx, &map_a, p.a, p.k, p.m, p.lda, BK, BM));
+    else MCB_TRY(make_map(ctx, &map_a, p.a, p.m, p.k, p.lda, 64, BK));
+    if (!p.b_mn_major) MCB_TRY(make_map(ctx, &map_b, p.b, p.k, p.n, p.ldb, BK, BN));
+    else MCB_TRY(make_map(ctx, &map_b, p.b, p.n, p.k, p.ldb, 64, BK));
+    TcArgs a;
+    a.d = p.d;
+    a.d_pre = p.d_pre;
+    a.bias = p.bias;
+    a.m = p.m; a.n = p.n; a.k = p.k; a.ldd = p.ldd;
+    a.out_bf16 = p.out_dt == MCB_BF16;
+    a.accumulate = p.accumulate;
+    a.act = p.act;
+    a.a_mn = p.a_mn_major;
+    a.b_mn = p.b_mn_major;
+    a.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(p.a_mn_major ? 1 : 0) << 15) |
+              ((unsigned)(p.b_mn_major ? 1 : 0) << 16) | ((unsigned)(BN >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
+    a.m_tiles = (int)((p.m + BM - 1) / BM);
+    a.n_tiles = (int)((p.n + BN - 1) / BN);
+    a.kb_total = (int)((p.k + BK - 1) / BK);
+    int split = p.split_k < 1 ? 1 : p.split_k;
+    if (split > a.kb_total) split = a.kb_total > 0 ? a.kb_total : 1;
+    a.kb_per_split = (a.kb_total + split - 1) / split;
+    split = a.kb_total > 0 ? (a.kb_total + a.kb_per_split - 1) / a.kb_per_split : 1;
+    a.split_k = split;
+    a.err = ctx->d_err;
+    long long work = (long long)a.m_tiles * a.n_tiles * split;
+    int grid = (int)(work < ctx->sm_count ? work : ctx->sm_count);
+    static bool attr_set = false;
+    if (!attr_set) {
+        MCB_CUDA(ctx, cudaFuncSetAttribute(tc_gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::kSmemBytes));
+        attr_set = true;
+    }
+    tc_gemm_kernel<BN><<<grid, kThreads, Cfg<BN>::kSmemBytes, ctx->stream>>>(map_a, map_b, a);
+    MCB_LAUNCHED(ctx);
+    return MCB_OK;
+}
+
+} // namespace
+
+mcb_status mcb_tc_gemm(mcb_ctx *ctx, const TcGemmParams &p) {
+    if (p.m == 0 || p.n == 0) return MCB_OK;
+    ProfScope prof(ctx, MCB_PROF_GEMM_TC, 2.0 * (double)p.m * (double)p.n * (double)p.k,
+                   2.0 * ((double)p.m * p.k + (double)p.n * p.k) + (double)p.m * p.n * (p.out_dt == MCB_BF16 ? 2.0 : 4.0));
+    if (p.k == 0) {
+        if (p.accumulate) return MCB_OK;
+        return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "tensor-core GEMM needs k > 0");
+    }
+    if ((p.lda % 8) || (p.ldb % 8) || !mcb_aligned16(p.a) || !mcb_aligned16(p.b))
+        return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "tensor-core GEMM operands need 16-byte aligned bases and row pitches that are multiples of 8 elements");
+    if (p.out_dt != MCB_BF16 && p.out_dt != MCB_F32) return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "GEMM output must be bf16 or f32");
+    if (p.accumulate && p.out_dt != MCB_F32) return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "accumulating GEMM output must be f32");
+    if (p.split_k > 1 && !p.accumulate) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "split-K needs the accumulating epilogue");
+    // vector stores in the epilogue need ldd and d aligned; otherwise the scalar tail path is used per row
+    if ((p.out_dt == MCB_BF16 && ((p.ldd % 8) || !mcb_aligned16(p.d))) || (p.out_dt == MCB_F32 && !p.accumulate && ((p.ldd % 4) || !mcb_aligned16(p.d))))
+        return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "GEMM output needs a 16-byte aligned base and row pitch");
+    // tile width: fewest idle SMs in the last wave, wider tile on ties
+    long long m_tiles = (p.m + BM - 1) / BM;
+    int best_bn = 256;
+    double best_eff = -1.0;
+    const int cands[3] = {256, 192, 128};
+    int split = p.split_k < 1 ? 1 : p.split_k;
+    for (int i = 0; i < 3; ++i) {
+        int bn = cands[i];
+        long long work = m_tiles * ((p.n + bn - 1) / bn) * split;
+        long long waves = (work + ctx->sm_count - 1) / ctx->sm_count;
+        double useful = (double)p.n / (double)(((p.n + bn - 1) / bn) * bn);
+        double eff = useful * (double)work / (double)(waves * ctx->sm_count) * (bn == 128 ? 0.93 : 1.0);
+        if (eff > best_eff + 1e-9) {
+            best_eff = eff;
+            best_bn = bn;
+        }
+    }
+    if (best_bn == 256) return launch<256>(ctx, p);
+    if (best_bn == 192) return launch<192>(ctx, p);
+    return launch<128>(ctx, p);
+}
+
+extern "C" mcb_status mcb_gemm_bf16(mcb_ctx *ctx, const void *a, int32_t a_mn_major, const void *b, int32_t b_mn_major,
+                                    void *d, int32_t out_dt, const float *bias, int64_t m, int64_t n, int64_t k,
+                                    int32_t accumulate, int32_t split_k) {
+    MCB_CHECK_CTX(ctx);
+    TcGemmParams p;
+    p.a = a; p.b = b; p.d = d; p.bias = bias;
+    p.a_mn_major = a_mn_major; p.b_mn_major = b_mn_major;
+    p.out_dt = out_dt;
+    p.m = m; p.n = n; p.k = k;
+    p.lda = a_mn_major ? m : k;
+    p.ldb = b_mn_major ? n : k;
+    p.ldd = n;
+    p.accumulate = accumulate;
+    p.split_k = split_k;
+    return mcb_tc_gemm(ctx, p);
+}

@@ -1,0 +1,55 @@
+// Prototypes shared between the translation units of the library (not part of the C ABI).
+#pragma once
+#include "common.cuh"
+
+// Strided / batched exact-f32 GEMM:
+//   C[z][i*ldc + j] (+)= alpha * sum_d A[z][i*as0 + d*as1] * B[z][d*bs0 + j*bs1] (+ bias[j]) -> act
+// Batch index z in [0, batch) is split as (z / batch_inner, z % batch_inner) with separate
+// strides, so a [n, seq, heads*hd] tensor can be walked per (sample, head) without a copy.
+struct SgemmParams {
+    const float *a = nullptr, *b = nullptr;
+    float *c = nullptr;
+    const float *bias = nullptr;
+    long long m = 0, n = 0, k = 0;
+    long long as0 = 0, as1 = 0, bs0 = 0, bs1 = 0, ldc = 0;
+    long long batch = 1, batch_inner = 1;
+    long long a_bo = 0, a_bi = 0, b_bo = 0, b_bi = 0, c_bo = 0, c_bi = 0;
+    float alpha = 1.0f;
+    int act = MCB_ACT_NONE;
+    int accumulate = 0;
+};
+mcb_status mcb_sgemm(mcb_ctx *ctx, const SgemmParams &p);
+
+// Tensor-core GEMM with explicit leading dimensions and (sample, head) batching; see gemm_tc.cu.
+struct TcGemmParams {
+    const void *a = nullptr, *b = nullptr; // bf16
+    void *d = nullptr;
+    const float *bias = nullptr;
+    int a_mn_major = 0, b_mn_major = 0;
+    int out_dt = MCB_BF16;
+    long long m = 0, n = 0, k = 0;
+    long long lda = 0, ldb = 0, ldd = 0; // elements between consecutive rows of the stored matrices
+    int accumulate = 0;
+    int split_k = 1;
+    int act = MCB_ACT_NONE;
+    void *d_pre = nullptr; // optional second output: value before the activation (same dtype/ld as d)
+};
+mcb_status mcb_tc_gemm(mcb_ctx *ctx, const TcGemmParams &p);
+
+// reduce.cu
+mcb_status mcb_sce_grad(mcb_ctx *ctx, const void *logits, void *out, int32_t dt, const void *labels, int32_t label_dt,
+                        int64_t n, int64_t c, float *loss_out, const float *upstream);
+mcb_status mcb_sum_scaled(mcb_ctx *ctx, const float *x, int64_t n, double scale, float *out);
+// elementwise.cu
+// out[i] = (*scalar) * factor for all i (broadcast of a device scalar)
+mcb_status mcb_fill_from_scalar(mcb_ctx *ctx, float *out, const float *scalar, double factor, int64_t n);
+// out = x * (*scalar); x/out f32 or bf16
+mcb_status mcb_mul_scalar_ptr(mcb_ctx *ctx, const void *x, const float *scalar, void *out, int64_t n, int32_t dt);
+// out = a + b with per-operand storage types (f32 or bf16), same shape
+mcb_status mcb_add_typed(mcb_ctx *ctx, const void *a, int32_t a_dt, const void *b, int32_t b_dt, void *out, int32_t out_dt, int64_t n);
+// optim.cu
+mcb_status mcb_adam_flat_ex(mcb_ctx *ctx, float *p, const void *g, int32_t g_dt, float *m, float *v, void *p_bf16,
+                            int64_t n, double lr, double beta1, double beta2, double eps, int32_t step,
+                            double inv_scale, const float *inv_scale_dev, const int32_t *skip_flag, const int32_t *step_dev);
+// scaler state on the device: {scale, inv_scale} floats then {growth_tracker, found_inf, last_found_inf, applied_steps} ints
+mcb_status mcb_scaler_update(mcb_ctx *ctx, float *state_f, int *state_i, float growth, float backoff, int interval);

@@ -1,0 +1,657 @@
+// Reduction kernels of the training path: sum_all, sum_to / bias-gradient column sums,
+// softmax, LayerNorm forward/backward, softmax-cross-entropy (separate and fused),
+// embedding gather / scatter-add.  Row reductions use warp shuffles; cross-row
+// reductions are two-stage through a scratch buffer so results do not depend on
+// scheduling (no float atomics except the embedding scatter).
+#include "common.cuh"
+#include "internal.h"
+
+namespace {
+
+constexpr int kThreads = 256;
+
+// ------------------------------------------------------------------ sum_all
+__global__ void sum_partial_kernel(const float *__restrict__ x, long long n, double *__restrict__ partial) {
+    __shared__ double red[kThreads / 32];
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    long long stride = (long long)gridDim.x * blockDim.x;
+    float acc = 0.0f;
+    double accd = 0.0;
+    int cnt = 0;
+    for (; i < n; i += stride) {
+        acc += x[i];
+        if (++cnt == 64) { // bound the f32 run length, then carry on in f64
+            accd += (double)acc;
+            acc = 0.0f;
+            cnt = 0;
+        }
+    }
+    accd += (double)acc;
+    for (int o = 16; o > 0; o >>= 1) accd += __shfl_xor_sync(0xffffffffu, accd, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = accd;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double t = 0.0;
+        for (int w = 0; w < kThreads / 32; ++w) t += red[w];
+        partial[blockIdx.x] = t;
+    }
+}
+// out = (float)(scale * sum(partial[0..m))) in fixed order
+__global__ void sum_final_kernel(const double *__restrict__ partial, int m, double scale, float *__restrict__ out) {
+    if (threadIdx.x == 0 && blockIdx.x == 0) {
+        double t = 0.0;
+        for (int i = 0; i < m; ++i) t += partial[i];
+        out[0] = (float)(t * scale);
+    }
+}
+
+// ------------------------------------------------------------------ column sums
+// grid (ceil(cols/32), splits), block (32, 8).  partial[split][col].
+template <typename T>
+__global__ void col_sum_partial_kernel(const T *__restrict__ a, long long rows, long long cols, float *__restrict__ partial) {
+    __shared__ float tile[8][33];
+    long long col = (long long)blockIdx.x * 32 + threadIdx.x;
+    long long rows_per = (rows + gridDim.y - 1) / gridDim.y;
+    long long r0 = (long long)blockIdx.y * rows_per, r1 = r0 + rows_per < rows ? r0 + rows_per : rows;
+    float acc = 0.0f;
+    if (col < cols)
+        for (long long r = r0 + threadIdx.y; r < r1; r += 8) acc += Elem<T>::ld(a, r * cols + col);
+    tile[threadIdx.y][threadIdx.x] = acc;
+    __syncthreads();
+    if (threadIdx.y == 0 && col < cols) {
+        float t = 0.0f;
+#pragma unroll
+        for (int y = 0; y < 8; ++y) t += tile[y][threadIdx.x];
+        partial[(long long)blockIdx.y * cols + col] = t;
+    }
+}
+__global__ void col_sum_final_kernel(const float *__restrict__ partial, int splits, long long cols, float *__restrict__ out) {
+    long long col = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (col >= cols) return;
+    float t = 0.0f;
+    for (int s = 0; s < splits; ++s) t += partial[(long long)s * cols + col];
+    out[col] = t;
+}
+
+// ------------------------------------------------------------------ generic sum_to
+// one thread per output element, walking the reduced sub-space
+struct SumToWalk {
+    int out_rank;        // kept dims
+    long long kd[8];     // kept dim sizes (in source order)
+    long long ks[8];     // source stride of each kept dim
+    int red_rank;
+    long long rd[8];     // reduced dim sizes
+    long long rs[8];     // source stride of each reduced dim
+};
+__global__ void sum_to_walk_kernel(const float *__restrict__ a, SumToWalk w, long long n_out, long long n_red,
+                                   float *__restrict__ out) {
+    long long o = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (o >= n_out) return;
+    long long rest = o, base = 0;
+    for (int k = w.out_rank - 1; k >= 0; --k) {
+        long long c = rest % w.kd[k];
+        rest /= w.kd[k];
+        base += c * w.ks[k];
+    }
+    float acc = 0.0f;
+    for (long long r = 0; r < n_red; ++r) {
+        long long rr = r, off = base;
+        for (int k = w.red_rank - 1; k >= 0; --k) {
+            long long c = rr % w.rd[k];
+            rr /= w.rd[k];
+            off += c * w.rs[k];
+        }
+        acc += a[off];
+    }
+    out[o] = acc;
+}
+
+// ------------------------------------------------------------------ softmax
+__global__ void softmax_kernel(const float *__restrict__ x, float *__restrict__ out, long long cols) {
+    __shared__ float red[32];
+    const float *s = x + (long long)blockIdx.x * cols;
+    float *d = out + (long long)blockIdx.x * cols;
+    float mx = -INFINITY;
+    for (long long j = threadIdx.x; j < cols; j += blockDim.x) mx = fmaxf(mx, s[j]);
+    mx = block_max(mx, red);
+    float sum = 0.0f;
+    for (long long j = threadIdx.x; j < cols; j += blockDim.x) sum += expf(s[j] - mx);
+    sum = block_sum(sum, red);
+    float inv = 1.0f / sum;
+    for (long long j = threadIdx.x; j < cols; j += blockDim.x) d[j] = expf(s[j] - mx) * inv;
+}
+__global__ void softmax_backward_kernel(const float *__restrict__ x, const float *__restrict__ g,
+                                        float *__restrict__ out, long long cols) {
+    __shared__ float red[32];
+    const float *s = x + (long long)blockIdx.x * cols;
+    const float *gr = g + (long long)blockIdx.x * cols;
+    float *d = out + (long long)blockIdx.x * cols;
+    float mx = -INFINITY;
+    for (long long j = threadIdx.x; j < cols; j += blockDim.x) mx = fmaxf(mx, s[j]);
+    mx = block_max(mx, red);
+    float sum = 0.0f;
+    for (long long j = threadIdx.x; j < cols; j += blockDim.x) sum += expf(s[j] - mx);
+    sum = block_sum(sum, red);
+    float dot = 0.0f;
+    for (long long j = threadIdx.x; j < cols; j += blockDim.x) dot += (expf(s[j] - mx) / sum) * gr[j];
+    dot = block_sum(dot, red);
+    for (long long j = threadIdx.x; j < cols; j += blockDim.x) d[j] = (expf(s[j] - mx) / sum) * (gr[j] - dot);
+}
+
+// ------------------------------------------------------------------ layer norm
+// one warp per row; the row is read from L1/L2 on the second and third sweep.
+template <typename OutT>
+__global__ void layer_norm_kernel(const float *__restrict__ x, const float *__restrict__ gamma,
+                                  const float *__restrict__ beta, float eps, OutT *__restrict__ out,
+                                  float *__restrict__ mean_out, float *__restrict__ rstd_out, long long rows, int dim,
+                                  int vec) {
+    int lane = threadIdx.x & 31;
+    long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+    float inv_dim = 1.0f / (float)dim;
+    for (long long r = warp; r < rows; r += nwarps) {
+        const float *s = x + r * dim;
+        OutT *d = out + r * dim;
+        float sum = 0.0f;
+        if (vec) {
+            for (int j = lane; j < (dim >> 2); j += 32) {
+                float4 v = reinterpret_cast<const float4 *>(s)[j];
+                sum += (v.x + v.y) + (v.z + v.w);
+            }
+        } else {
+            for (int j = lane; j < dim; j += 32) sum += s[j];
+        }
+        float mean = warp_sum(sum) * inv_dim;
+        float var = 0.0f;
+        if (vec) {
+            for (int j = lane; j < (dim >> 2); j += 32) {
+                float4 v = reinterpret_cast<const float4 *>(s)[j];
+                float a = v.x - mean, b = v.y - mean, c = v.z - mean, e = v.w - mean;
+                var += (a * a + b * b) + (c * c + e * e);
+            }
+        } else {
+            for (int j = lane; j < dim; j += 32) {
+                float a = s[j] - mean;
+                var += a * a;
+            }
+        }
+        var = warp_sum(var) * inv_dim;
+        float rstd = 1.0f / sqrtf(var + eps);
+        if (lane == 0) {
+            if (mean_out) mean_out[r] = mean;
+            if (rstd_out) rstd_out[r] = rstd;
+        }
+        if (vec) {
+            for (int j = lane; j < (dim >> 2); j += 32) {
+                float4 v = reinterpret_cast<const float4 *>(s)[j];
+                float4 ga = reinterpret_cast<const float4 *>(gamma)[j], be = reinterpret_cast<const float4 *>(beta)[j];
+                float4 o = make_float4((v.x - mean) * rstd * ga.x + be.x, (v.y - mean) * rstd * ga.y + be.y,
+                                       (v.z - mean) * rstd * ga.z + be.z, (v.w - mean) * rstd * ga.w + be.w);
+                Elem<OutT>::st4(d, j, o);
+            }
+        } else {
+            for (int j = lane; j < dim; j += 32) Elem<OutT>::st(d, j, (s[j] - mean) * rstd * gamma[j] + beta[j]);
+        }
+    }
+}
+
+// dx per row plus per-warp partial sums of dgamma / dbeta kept in shared memory:
+// smem layout [warps][2][dim]; each block writes its reduced slice to partial[block][2][dim].
+template <typename GT>
+__global__ void layer_norm_backward_kernel(const float *__restrict__ x, const float *__restrict__ gamma,
+                                           const GT *__restrict__ g, float eps, const float *__restrict__ mean_in,
+                                           const float *__restrict__ rstd_in, float *__restrict__ dx,
+                                           float *__restrict__ partial, long long rows, int dim) {
+    extern __shared__ float acc[]; // [warps][2][dim]
+    int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    float *my_dg = acc + (size_t)w * 2 * dim, *my_db = my_dg + dim;
+    for (int j = lane; j < dim; j += 32) {
+        my_dg[j] = 0.0f;
+        my_db[j] = 0.0f;
+    }
+    long long warp = (long long)blockIdx.x * nw + w;
+    long long nwarps = (long long)gridDim.x * nw;
+    float fdim = (float)dim, inv_dim = 1.0f / fdim;
+    for (long long r = warp; r < rows; r += nwarps) {
+        const float *s = x + r * dim;
+        const GT *gs = g + r * dim;
+        float mean, rstd;
+        if (mean_in && rstd_in) {
+            mean = mean_in[r];
+            rstd = rstd_in[r];
+        } else {
+            float sum = 0.0f;
+            for (int j = lane; j < dim; j += 32) sum += s[j];
+            mean = warp_sum(sum) * inv_dim;
+            float var = 0.0f;
+            for (int j = lane; j < dim; j += 32) {
+                float a = s[j] - mean;
+                var += a * a;
+            }
+            rstd = 1.0f / sqrtf(warp_sum(var) * inv_dim + eps);
+        }
+        float sum_dy = 0.0f, sum_dy_norm = 0.0f;
+        for (int j = lane; j < dim; j += 32) {
+            float gv = Elem<GT>::ld(gs, j);
+            float norm = (s[j] - mean) * rstd;
+            float dy = gv * gamma[j];
+            sum_dy += dy;
+            sum_dy_norm += dy * norm;
+            my_dg[j] += gv * norm;
+            my_db[j] += gv;
+        }
+        sum_dy = warp_sum(sum_dy);
+        sum_dy_norm = warp_sum(sum_dy_norm);
+        for (int j = lane; j < dim; j += 32) {
+            float gv = Elem<GT>::ld(gs, j);
+            float norm = (s[j] - mean) * rstd;
+            float dy = gv * gamma[j];
+            dx[r * dim + j] = (fdim * dy - sum_dy - norm * sum_dy_norm) * rstd * inv_dim;
+        }
+    }
+    __syncthreads();
+    float *dst = partial + (size_t)blockIdx.x * 2 * dim;
+    for (int j = threadIdx.x; j < 2 * dim; j += blockDim.x) {
+        float t = 0.0f;
+        for (int ww = 0; ww < nw; ++ww) t += acc[(size_t)ww * 2 * dim + j];
+        dst[j] = t;
+    }
+}
+__global__ void layer_norm_params_final_kernel(const float *__restrict__ partial, int blocks, int dim,
+                                               float *__restrict__ dgamma, float *__restrict__ dbeta) {
+    int j = blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= 2 * dim) return;
+    float t = 0.0f;
+    for (int b = 0; b < blocks; ++b) t += partial[(size_t)b * 2 * dim + j];
+    if (j < dim) dgamma[j] = t;
+    else dbeta[j - dim] = t;
+}
+
+// ------------------------------------------------------------------ softmax cross entropy
+// per-thread online (max, sum) merged across the block
+template <typename T>
+__device__ __forceinline__ void row_max_sumexp(const T *__restrict__ row, long long c, float *red, float &mx_out,
+                                               float &sum_out) {
+    float m = -INFINITY, s = 0.0f;
+    for (long long j = threadIdx.x; j < c; j += blockDim.x) {
+        float v = Elem<T>::ld(row, j);
+        if (v > m) {
+            s = s * expf(m - v) + 1.0f;
+            m = v;
+        } else {
+            s += expf(v - m);
+        }
+    }
+    float M = block_max(m, red);
+    float contrib = (m == -INFINITY) ? 0.0f : s * expf(m - M);
+    sum_out = block_sum(contrib, red);
+    mx_out = M;
+}
+
+__global__ void sce_rows_kernel(const float *__restrict__ x, const void *__restrict__ labels, int label_dt,
+                                long long c, float *__restrict__ row_loss, unsigned int *err) {
+    __shared__ float red[32];
+    long long i = blockIdx.x;
+    long long lab = load_index(labels, label_dt, i);
+    if (lab < 0 || lab >= c) {
+        if (threadIdx.x == 0) {
+            atomicOr(err, MCB_DEVERR_LABEL);
+            row_loss[i] = 0.0f;
+        }
+        return;
+    }
+    const float *row = x + i * c;
+    float mx, sum;
+    row_max_sumexp<float>(row, c, red, mx, sum);
+    if (threadIdx.x == 0) row_loss[i] = (mx + logf(sum)) - row[lab];
+}
+__global__ void sce_final_kernel(const float *__restrict__ row_loss, long long n, float *__restrict__ loss) {
+    __shared__ double red[kThreads];
+    double acc = 0.0;
+    for (long long i = threadIdx.x; i < n; i += blockDim.x) acc += (double)row_loss[i];
+    red[threadIdx.x] = acc;
+    __syncthreads();
+    for (int o = blockDim.x >> 1; o > 0; o >>= 1) {
+        if ((int)threadIdx.x < o) red[threadIdx.x] += red[threadIdx.x + o];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) loss[0] = (float)(red[0] / (double)n);
+}
+// fused: row loss + in-place gradient, one DRAM read and one DRAM write of the logits
+// `out` may alias `x` (each block reads its whole row before it writes any of it).
+template <typename T>
+__global__ void sce_fused_kernel(const T *x, T *out, const void *__restrict__ labels, int label_dt, long long n,
+                                 long long c, float *__restrict__ row_loss, const float *__restrict__ upstream,
+                                 unsigned int *err) {
+    __shared__ float red[32];
+    long long i = blockIdx.x;
+    long long lab = load_index(labels, label_dt, i);
+    const T *row = x + i * c;
+    T *orow = out + i * c;
+    if (lab < 0 || lab >= c) {
+        if (threadIdx.x == 0) {
+            atomicOr(err, MCB_DEVERR_LABEL);
+            if (row_loss) row_loss[i] = 0.0f;
+        }
+        if (out)
+            for (long long j = threadIdx.x; j < c; j += blockDim.x) Elem<T>::st(orow, j, 0.0f);
+        return;
+    }
+    float mx, sum;
+    row_max_sumexp<T>(row, c, red, mx, sum);
+    float at_label = Elem<T>::ld(row, lab);
+    __syncthreads(); // every thread has read row[lab] before anyone overwrites it
+    if (threadIdx.x == 0 && row_loss) row_loss[i] = (mx + logf(sum)) - at_label;
+    if (!out) return; // loss only
+    float up = upstream ? upstream[0] : 1.0f;
+    float inv_sum = 1.0f / sum, k = up / (float)n;
+    bool vec = ((c & 3) == 0);
+    if (vec) {
+        for (long long j = threadIdx.x; j < (c >> 2); j += blockDim.x) {
+            float4 v = Elem<T>::ld4(row, j);
+            long long b = j << 2;
+            float4 p = make_float4(expf(v.x - mx) * inv_sum, expf(v.y - mx) * inv_sum, expf(v.z - mx) * inv_sum,
+                                   expf(v.w - mx) * inv_sum);
+            if (lab >= b && lab < b + 4) {
+                int o = (int)(lab - b);
+                if (o == 0) p.x -= 1.0f;
+                else if (o == 1) p.y -= 1.0f;
+                else if (o == 2) p.z -= 1.0f;
+                else p.w -= 1.0f;
+            }
+            Elem<T>::st4(orow, j, make_float4(p.x * k, p.y * k, p.z * k, p.w * k));
+        }
+    } else {
+        for (long long j = threadIdx.x; j < c; j += blockDim.x) {
+            float p = expf(Elem<T>::ld(row, j) - mx) * inv_sum;
+            if (j == lab) p -= 1.0f;
+            Elem<T>::st(orow, j, p * k);
+        }
+    }
+}
+
+// ------------------------------------------------------------------ embedding
+__global__ void embedding_kernel(const void *__restrict__ ids, int id_dt, long long n, const float *__restrict__ w,
+                                 long long vocab, int dim, float *__restrict__ out, unsigned int *err, int vec) {
+    int per_row = vec ? (dim >> 2) : dim;
+    long long total = n * per_row;
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    long long stride = (long long)gridDim.x * blockDim.x;
+    for (; i < total; i += stride) {
+        long long r = i / per_row;
+        int j = (int)(i - r * per_row);
+        long long id = load_index(ids, id_dt, r);
+        bool ok = id >= 0 && id < vocab;
+        if (!ok && j == 0) atomicOr(err, MCB_DEVERR_INDEX);
+        if (vec) {
+            float4 v = ok ? reinterpret_cast<const float4 *>(w + id * dim)[j] : make_float4(0.f, 0.f, 0.f, 0.f);
+            reinterpret_cast<float4 *>(out + r * dim)[j] = v;
+        } else {
+            out[r * dim + j] = ok ? w[id * dim + j] : 0.0f;
+        }
+    }
+}
+template <typename GT>
+__global__ void embedding_backward_kernel(const void *__restrict__ ids, int id_dt, long long n,
+                                          const GT *__restrict__ g, long long vocab, int dim, float *__restrict__ out,
+                                          unsigned int *err) {
+    long long total = n * dim;
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    long long stride = (long long)gridDim.x * blockDim.x;
+    for (; i < total; i += stride) {
+        long long r = i / dim;
+        int j = (int)(i - r * dim);
+        long long id = load_index(ids, id_dt, r);
+        if (id < 0 || id >= vocab) {
+            if (j == 0) atomicOr(err, MCB_DEVERR_INDEX);
+            continue;
+        }
+        atomicAdd(out + id * dim + j, Elem<GT>::ld(g, i));
+    }
+}
+
+bool index_dtype_ok(int dt) { return dt == MCB_I64 || dt == MCB_I32 || dt == MCB_U8; }
+
+} // namespace
+
+extern "C" {
+
+mcb_status mcb_sum_all(mcb_ctx *ctx, const float *x, int64_t n, float *out) {
+    MCB_CHECK_CTX(ctx);
+    int grid = mcb_grid_for(ctx, n, kThreads, 4);
+    void *scratch;
+    MCB_TRY(mcb_scratch(ctx, sizeof(double) * grid, &scratch));
+    sum_partial_kernel<<<grid, kThreads, 0, ctx->stream>>>(x, n, (double *)scratch);
+    MCB_LAUNCHED(ctx);
+    sum_final_kernel<<<1, 32, 0, ctx->stream>>>((const double *)scratch, grid, 1.0, out);
+    MCB_LAUNCHED(ctx);
+    return MCB_OK;
+}
+
+mcb_status mcb_col_sum(mcb_ctx *ctx, const void *a, int32_t dt, int64_t rows, int64_t cols, float *out) {
+    MCB_CHECK_CTX(ctx);
+    if (cols == 0) return MCB_OK;
+    if (rows == 0) return mcb_memset(ctx, out, 0, sizeof(float) * cols);
+    int col_tiles = (int)((cols + 31) / 32);
+    int splits = (int)((ctx->sm_count * 8 + col_tiles - 1) / col_tiles);
+    if (splits > (rows + 63) / 64) splits = (int)((rows + 63) / 64);
+    if (splits < 1) splits = 1;
+    void *scratch;
+    MCB_TRY(mcb_scratch(ctx, sizeof(float) * splits * cols, &scratch));
+    dim3 grid(col_tiles, splits), block(32, 8);
+    if (dt == MCB_F32)
+        col_sum_partial_kernel<float><<<grid, block, 0, ctx->stream>>>((const float *)a, rows, cols, (float *)scratch);
+    else if (dt == MCB_BF16)
+        col_sum_partial_kernel<__nv_bfloat16><<<grid, block, 0, ctx->stream>>>((const __nv_bfloat16 *)a, rows, cols, (float *)scratch);
+    else
+        return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "col_sum supports f32 and bf16");
+    MCB_LAUNCHED(ctx);
+    col_sum_final_kernel<<<(int)((cols + 255) / 256), 256, 0, ctx->stream>>>((const float *)scratch, splits, cols, out);
+    MCB_LAUNCHED(ctx);
+    return MCB_OK;
+}
+
+mcb_status mcb_sum_to(mcb_ctx *ctx, const float *a, const int64_t *ad, int32_t ar, const int64_t *td, int32_t tr,
+                      float *out) {
+    MCB_CHECK_CTX(ctx);
+    if (tr > ar || ar > 8 || tr < 0) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "sum_to target rank %d exceeds source rank %d", tr, ar);
+    int shift = ar - tr;
+    long long n_src = 1, n_out = 1;
+    for (int i = 0; i < ar; ++i) n_src *= ad[i];
+    for (int i = 0; i < tr; ++i) n_out *= td[i];
+    for (int i = 0; i < tr; ++i)
+        if (td[i] != 1 && td[i] != ad[i + shift]) return mcb_fail(ctx, MCB_SHAPE_MISMATCH, "sum_to target does not fold the source shape");
+    if (n_out == 0) return MCB_OK;
+    if (n_src == n_out) return mcb_memcpy_d2d(ctx, out, a, sizeof(float) * n_src); // equal shapes: a copy
+    if (n_src == 0) return mcb_memset(ctx, out, 0, sizeof(float) * n_out);
+    if (ar == 2 && tr == 1 && td[0] == ad[1]) return mcb_col_sum(ctx, a, MCB_F32, ad[0], ad[1], out);
+    if (n_out == 1) return mcb_sum_all(ctx, a, n_src, out);
+    // split source dims into kept and reduced
+    SumToWalk w;
+    w.out_rank = 0;
+    w.red_rank = 0;
+    long long stride = 1, n_red = 1;
+    long long sstr[8];
+    for (int i = ar - 1; i >= 0; --i) {
+        sstr[i] = stride;
+        stride *= ad[i];
+    }
+    for (int i = 0; i < ar; ++i) {
+        bool kept = i >= shift && td[i - shift] != 1;
+        if (kept) {
+            w.kd[w.out_rank] = ad[i];
+            w.ks[w.out_rank++] = sstr[i];
+        } else if (ad[i] != 1) {
+            w.rd[w.red_rank] = ad[i];
+            w.rs[w.red_rank++] = sstr[i];
+            n_red *= ad[i];
+        }
+    }
+    sum_to_walk_kernel<<<(int)((n_out + 127) / 128), 128, 0, ctx->stream>>>(a, w, n_out, n_red, out);
+    MCB_LAUNCHED(ctx);
+    return MCB_OK;
+}
+
+mcb_status mcb_softmax(mcb_ctx *ctx, const float *x, float *out, int64_t rows, int64_t cols) {
+    MCB_CHECK_CTX(ctx);
+    if (rows == 0 || cols == 0) return MCB_OK;
+    int threads = cols >= 1024 ? 256 : (cols >= 128 ? 128 : 32);
+    softmax_kernel<<<(unsigned)rows, threads, 0, ctx->stream>>>(x, out, cols);
+    MCB_LAUNCHED(ctx);
+    return MCB_OK;
+}
+mcb_status mcb_softmax_backward(mcb_ctx *ctx, const float *x, const float *g, float *out, int64_t rows, int64_t cols) {
+    MCB_CHECK_CTX(ctx);
+    if (rows == 0 || cols == 0) return MCB_OK;
+    int threads = cols >= 1024 ? 256 : (cols >= 128 ? 128 : 32);
+    softmax_backward_kernel<<<(unsigned)rows, threads, 0, ctx->stream>>>(x, g, out, cols);
+    MCB_LAUNCHED(ctx);
+    return MCB_OK;
+}
+
+mcb_status mcb_layer_norm(mcb_ctx *ctx, const float *x, const float *gamma, const float *beta, double eps, void *out,
+                          int32_t out_dt, float *mean, float *rstd, int64_t rows, int64_t dim) {
+    MCB_CHECK_CTX(ctx);
+    if (rows == 0 || dim == 0) return MCB_OK;
+    if (dim > INT32_MAX) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "layer_norm dim too large");
+    int vec = (dim % 4 == 0) && mcb_aligned16(x) && mcb_aligned16(out) && mcb_aligned16(gamma) && mcb_aligned16(beta);
+    ProfScope prof(ctx, MCB_PROF_NORM, 0.0, (double)rows * dim * (4.0 + (out_dt == MCB_BF16 ? 2.0 : 4.0)) + 8.0 * rows);
+    int grid = mcb_grid_for(ctx, rows, kThreads / 32, 16);
+    if (out_dt == MCB_F32)
+        layer_norm_kernel<float><<<grid, kThreads, 0, ctx->stream>>>(x, gamma, beta, (float)eps, (float *)out, mean, rstd, rows, (int)dim, vec);
+    else if (out_dt == MCB_BF16)
+        layer_norm_kernel<__nv_bfloat16><<<grid, kThreads, 0, ctx->stream>>>(x, gamma, beta, (float)eps, (__nv_bfloat16 *)out, mean, rstd, rows, (int)dim, vec);
+    else
+        return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "layer_norm output must be f32 or bf16");
+    MCB_LAUNCHED(ctx);
+    return MCB_OK;
+}
+
+mcb_status mcb_layer_norm_backward(mcb_ctx *ctx, const float *x, const float *gamma, const void *g, int32_t g_dt,
+                                   double eps, const float *mean, const float *rstd, float *dx, float *dgamma,
+                                   float *dbeta, int64_t rows, int64_t dim) {
+    MCB_CHECK_CTX(ctx);
+    if (dim == 0) return MCB_OK;
+    if (rows == 0) {
+        MCB_TRY(mcb_memset(ctx, dgamma, 0, sizeof(float) * dim));
+        return mcb_memset(ctx, dbeta, 0, sizeof(float) * dim);
+    }
+    // algorithmic bytes: read x and g, write dx, read the row statistics, write 2*dim parameter sums
+    ProfScope prof(ctx, MCB_PROF_NORM, 0.0, (double)rows * dim * (8.0 + (g_dt == MCB_BF16 ? 2.0 : 4.0)) + 8.0 * rows + 8.0 * dim);
+    const size_t smem_cap = 200 * 1024;
+    int warps = 8;
+    while (warps > 1 && (size_t)warps * 2 * dim * sizeof(float) > smem_cap) warps >>= 1;
+    size_t smem = (size_t)warps * 2 * dim * sizeof(float);
+    if (smem > smem_cap) return mcb_fail(ctx, MCB_UNSUPPORTED, "layer_norm_backward: dim %lld exceeds the shared-memory staging limit", (long long)dim);
+    int grid = mcb_grid_for(ctx, rows, warps, 2);
+    void *scratch;
+    MCB_TRY(mcb_scratch(ctx, sizeof(float) * (size_t)grid * 2 * dim, &scratch));
+    if (g_dt == MCB_F32) {
+        MCB_CUDA(ctx, cudaFuncSetAttribute(layer_norm_backward_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_cap));
+        layer_norm_backward_kernel<float><<<grid, warps * 32, smem, ctx->stream>>>(x, gamma, (const float *)g, (float)eps, mean, rstd, dx, (float *)scratch, rows, (int)dim);
+    } else if (g_dt == MCB_BF16) {
+        MCB_CUDA(ctx, cudaFuncSetAttribute(layer_norm_backward_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_cap));
+        layer_norm_backward_kernel<__nv_bfloat16><<<grid, warps * 32, smem, ctx->stream>>>(x, gamma, (const __nv_bfloat16 *)g, (float)eps, mean, rstd, dx, (float *)scratch, rows, (int)dim);
+    } else {
+        return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "layer_norm_backward grad must be f32 or bf16");
+    }
+    MCB_LAUNCHED(ctx);
+    layer_norm_params_final_kernel<<<(int)((2 * dim + 255) / 256), 256, 0, ctx->stream>>>((const float *)scratch, grid, (int)dim, dgamma, dbeta);
+    MCB_LAUNCHED(ctx);
+    return MCB_OK;
+}
+
+mcb_status mcb_softmax_cross_entropy(mcb_ctx *ctx, const float *logits, const void *labels, int32_t label_dt,
+                                     int64_t n, int64_t c, float *loss_out) {
+    MCB_CHECK_CTX(ctx);
+    if (!index_dtype_ok(label_dt)) return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "labels must be i64, i32 or u8");
+    if (n == 0) return mcb_memset(ctx, loss_out, 0, sizeof(float));
+    void *scratch;
+    MCB_TRY(mcb_scratch(ctx, sizeof(float) * n, &scratch));
+    int threads = c >= 4096 ? 512 : (c >= 256 ? 128 : 32);
+    sce_rows_kernel<<<(unsigned)n, threads, 0, ctx->stream>>>(logits, labels, label_dt, c, (float *)scratch, ctx->d_err);
+    MCB_LAUNCHED(ctx);
+    sce_final_kernel<<<1, kThreads, 0, ctx->stream>>>((const float *)scratch, n, loss_out);
+    MCB_LAUNCHED(ctx);
+    return MCB_OK;
+}
+
+mcb_status mcb_softmax_cross_entropy_backward(mcb_ctx *ctx, const float *logits, const void *labels,
+                                              int32_t label_dt, int64_t n, int64_t c, float *out) {
+    MCB_CHECK_CTX(ctx);
+    return mcb_sce_grad(ctx, logits, out, MCB_F32, labels, label_dt, n, c, nullptr, nullptr);
+}
+
+mcb_status mcb_softmax_ce_fused(mcb_ctx *ctx, void *logits, int32_t logits_dt, const void *labels, int32_t label_dt,
+                                int64_t n, int64_t c, float *loss_out, const float *upstream) {
+    MCB_CHECK_CTX(ctx);
+    return mcb_sce_grad(ctx, logits, logits, logits_dt, labels, label_dt, n, c, loss_out, upstream);
+}
+
+mcb_status mcb_embedding(mcb_ctx *ctx, const void *ids, int32_t id_dt, int64_t n, const float *weight, int64_t vocab,
+                         int64_t dim, float *out) {
+    MCB_CHECK_CTX(ctx);
+    if (!index_dtype_ok(id_dt)) return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "ids must be i64, i32 or u8");
+    if (n == 0 || dim == 0) return MCB_OK;
+    int vec = (dim % 4 == 0) && mcb_aligned16(weight) && mcb_aligned16(out);
+    long long total = n * (vec ? dim / 4 : dim);
+    embedding_kernel<<<mcb_grid_for(ctx, total, kThreads), kThreads, 0, ctx->stream>>>(ids, id_dt, n, weight, vocab, (int)dim, out, ctx->d_err, vec);
+    MCB_LAUNCHED(ctx);
+    return MCB_OK;
+}
+
+mcb_status mcb_embedding_backward(mcb_ctx *ctx, const void *ids, int32_t id_dt, int64_t n, const void *g,
+                                  int32_t g_dt, int64_t vocab, int64_t dim, float *out, int32_t accumulate) {
+    MCB_CHECK_CTX(ctx);
+    if (!index_dtype_ok(id_dt)) return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "ids must be i64, i32 or u8");
+    if (!accumulate) MCB_TRY(mcb_memset(ctx, out, 0, sizeof(float) * vocab * dim));
+    if (n == 0 || dim == 0) return MCB_OK;
+    int grid = mcb_grid_for(ctx, n * dim, kThreads);
+    if (g_dt == MCB_F32)
+        embedding_backward_kernel<float><<<grid, kThreads, 0, ctx->stream>>>(ids, id_dt, n, (const float *)g, vocab, (int)dim, out, ctx->d_err);
+    else if (g_dt == MCB_BF16)
+        embedding_backward_kernel<__nv_bfloat16><<<grid, kThreads, 0, ctx->stream>>>(ids, id_dt, n, (const __nv_bfloat16 *)g, vocab, (int)dim, out, ctx->d_err);
+    else
+        return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "embedding grad must be f32 or bf16");
+    MCB_LAUNCHED(ctx);
+    return MCB_OK;
+}
+
+} // extern "C"
+
+// gradient of the mean cross entropy (times *upstream), optionally with the loss, in one pass
+mcb_status mcb_sce_grad(mcb_ctx *ctx, const void *logits, void *out, int32_t dt, const void *labels, int32_t label_dt,
+                        int64_t n, int64_t c, float *loss_out, const float *upstream) {
+    if (!index_dtype_ok(label_dt)) return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "labels must be i64, i32 or u8");
+    if (n == 0) return loss_out ? mcb_memset(ctx, loss_out, 0, sizeof(float)) : MCB_OK;
+    if (c == 0) return MCB_OK;
+    void *scratch = nullptr;
+    if (loss_out) MCB_TRY(mcb_scratch(ctx, sizeof(float) * n, &scratch));
+    int threads = c >= 4096 ? 512 : (c >= 256 ? 128 : 32);
+    // algorithmic bytes: one read of the logits, one write of the gradient when requested
+    ProfScope prof(ctx, MCB_PROF_LOSS, 0.0, (double)n * c * (dt == MCB_BF16 ? 2.0 : 4.0) * (out ? 2.0 : 1.0) + 8.0 * n);
+    if (dt == MCB_F32)
+        sce_fused_kernel<float><<<(unsigned)n, threads, 0, ctx->stream>>>((const float *)logits, (float *)out, labels, label_dt, n, c, (float *)scratch, upstream, ctx->d_err);
+    else if (dt == MCB_BF16)
+        sce_fused_kernel<__nv_bfloat16><<<(unsigned)n, threads, 0, ctx->stream>>>((const __nv_bfloat16 *)logits, (__nv_bfloat16 *)out, labels, label_dt, n, c, (float *)scratch, upstream, ctx->d_err);
+    else
+        return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "logits must be f32 or bf16");
+    MCB_LAUNCHED(ctx);
+    if (loss_out) {
+        sce_final_kernel<<<1, kThreads, 0, ctx->stream>>>((const float *)scratch, n, loss_out);
+        MCB_LAUNCHED(ctx);
+    }
+    return MCB_OK;
+}
+
+// out = (float)(scale * sum(x)) as a device scalar
+mcb_status mcb_sum_scaled(mcb_ctx *ctx, const float *x, int64_t n, double scale, float *out) {
+    int grid = mcb_grid_for(ctx, n > 0 ? n : 1, kThreads, 4);
+    void *scratch;
+    MCB_TRY(mcb_scratch(ctx, sizeof(double) * grid, &scratch));
+    sum_partial_kernel<<<grid, kThreads, 0, ctx->stream>>>(x, n, (double *)scratch);
+    MCB_LAUNCHED(ctx);
+    sum_final_kernel<<<1, 32, 0, ctx->stream>>>((const double *)scratch, grid, scale, out);
+    MCB_LAUNCHED(ctx);
+    return MCB_OK;
+}

@@ -1,0 +1,75 @@
+"""CPU-side checks of the C-ABI library: it loads without a GPU, exports every symbol that
+include/mcb.h declares, refuses to create a context when no device exists (no CPU fallback),
+and its host-only helper works."""
+import ctypes as C
+import os
+import re
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from modernchainer_b200 import _lib, build
+    if not os.path.exists(_lib.LIB_PATH):
+        build.build()
+    return _lib.load()
+
+
+def test_every_declared_symbol_is_exported(lib):
+    from modernchainer_b200 import _lib
+    protos = _lib.parse_header()
+    assert len(protos) > 100
+    declared = set(re.findall(r"\b(mcb_[a-z0-9_]+)\s*\(", open(_lib.HEADER).read()))
+    declared -= {"mcb_status"}
+    for name in declared:
+        assert hasattr(lib, name), name
+        assert name in protos, name
+
+
+def test_no_cpu_fallback_without_device(lib):
+    if lib.mcb_device_count() > 0:
+        pytest.skip("a GPU is present")
+    h = C.c_void_p()
+    assert lib.mcb_ctx_create(0, C.byref(h)) == 8  # MCB_BACKEND
+    import modernchainer_b200 as mc
+    with pytest.raises(mc.McbError):
+        mc.Context(0)
+
+
+def test_product_never_imports_the_oracle():
+    pkg = os.path.join(ROOT, "modernchainer_b200")
+    for dirpath, _, files in os.walk(pkg):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".h", ".cpp")):
+                text = open(os.path.join(dirpath, f), errors="ignore").read()
+                assert "oracle" not in text.lower().replace("oracle/", "oracle/") or "import oracle" not in text, f
+                assert "mc_oracle" not in text, f
+                assert "from oracle" not in text and "import oracle" not in text, f
+
+
+def test_bucket_planner(lib):
+    sizes = np.array([10, 20, 30, 40, 50], np.int64)
+    out = np.zeros(5, np.int32)
+    nb = C.c_int32()
+    st = lib.mcb_dp_plan_buckets(sizes.ctypes.data_as(C.c_void_p), 5, 60, out.ctypes.data_as(C.c_void_p), C.byref(nb))
+    assert st == 0
+    # walked from the last tensor (first gradient ready in backward) to the first
+    assert out.tolist() == [2, 2, 2, 1, 0] and nb.value == 3
+    st = lib.mcb_dp_plan_buckets(sizes.ctypes.data_as(C.c_void_p), 5, 1000, out.ctypes.data_as(C.c_void_p), C.byref(nb))
+    assert out.tolist() == [0] * 5 and nb.value == 1
+    st = lib.mcb_dp_plan_buckets(sizes.ctypes.data_as(C.c_void_p), 5, 1, out.ctypes.data_as(C.c_void_p), C.byref(nb))
+    assert out.tolist() == [4, 3, 2, 1, 0] and nb.value == 5
+    assert lib.mcb_dp_plan_buckets(sizes.ctypes.data_as(C.c_void_p), 5, 0, out.ctypes.data_as(C.c_void_p), C.byref(nb)) == 5
+
+
+def test_host_bf16_helpers_match_oracle(oracle):
+    import modernchainer_b200 as mc
+    x = np.random.default_rng(0).standard_normal(4096).astype(np.float32) * 3
+    assert np.array_equal(mc.f32_to_bf16_bits(x), oracle.f32_to_bf16_bits(x))
+    assert np.array_equal(mc.bf16_bits_to_f32(mc.f32_to_bf16_bits(x)), oracle.round_bf16(x))

@@ -1,0 +1,320 @@
+"""GPU parity of the tape / optimizer / GradScaler surface against the CPU oracle's tape, with
+the reference's own test programs restated call for call:
+  crates/modern-chainer-autograd/tests/gradcheck.rs (inputs and tape semantics)
+  crates/modern-chainer-optim/tests/amp.rs, optimizer.rs
+  crates/modern-chainer-cuda/tests/cuda.rs:110-153, 764-803 (training loops: loss decreases)
+and full fwd+bwd+Adam steps of the four benchmark models at reduced sizes.
+
+f32 tolerance: 1e-5 relative, norm-wise per tensor (2e-5 where two reductions chain).
+bf16 autocast tolerance: gradients within 3e-2 and the loss within 2e-2 relative of the f32
+oracle (stated for AMP; bf16 has 8 significant bits and the block chains ~10 rounded GEMMs)."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def mc():
+    import modernchainer_b200 as m
+    return m
+
+
+@pytest.fixture(scope="module")
+def ctx(mc):
+    c = mc.Context(0)
+    yield c
+    c.close()
+
+
+def close(a, b, tol=1e-5):
+    a, b = np.asarray(a, np.float64), np.asarray(b, np.float64)
+    assert a.shape == b.shape, (a.shape, b.shape)
+    scale = max(np.abs(b).max(), 1e-30)
+    err = np.abs(a - b).max() / scale
+    assert err <= tol, f"relative error {err:.3e} > {tol}"
+
+
+def both(mc, ctx, oracle, data, shape, requires_grad=True):
+    arr = np.array(data, np.float32).reshape(shape)
+    return mc.Variable(ctx, arr, requires_grad=requires_grad), oracle.Variable(arr, requires_grad=requires_grad)
+
+
+CASES = {
+    "add_broadcast": (lambda F, xs: F.sum(F.add(xs[0], xs[1])), [([0.2, -0.4, 0.1, 0.3, 0.5, -0.2], (2, 3)), ([0.1, 0.2, -0.3], (3,))]),
+    "sub_broadcast": (lambda F, xs: F.sum(F.mul(F.sub(xs[0], xs[1]), xs[0])), [([0.2, -0.4, 0.1, 0.3, 0.5, -0.2], (2, 3)), ([0.1, 0.2, -0.3], (3,))]),
+    "mul": (lambda F, xs: F.sum(F.mul(xs[0], xs[1])), [([0.5, 1.2, -0.7, 0.3], (2, 2)), ([0.4, -0.9, 0.8, 1.1], (2, 2))]),
+    "div": (lambda F, xs: F.sum(F.div(xs[0], xs[1])), [([0.5, 1.2, -0.7, 0.3], (2, 2)), ([0.4, -0.9, 0.8, 1.1], (2, 2))]),
+    "matmul": (lambda F, xs: F.sum(F.matmul(xs[0], xs[1])), [([0.2, -0.1, 0.4, 0.3, 0.2, -0.5], (2, 3)), ([0.1, 0.2, -0.3, 0.4, 0.5, -0.2], (3, 2))]),
+    "relu": (lambda F, xs: F.sum(F.relu(xs[0])), [([-0.5, 0.2, 0.7, -1.2], (2, 2))]),
+    "sqrt": (lambda F, xs: F.sum(F.sqrt(xs[0])), [([0.25, 0.5, 1.0, 2.0], (4,))]),
+    "matmul_relu_chain": (lambda F, xs: F.sum(F.relu(F.add(F.matmul(xs[0], xs[1]), xs[2]))),
+                          [([0.2, -0.3, 0.5, 0.1, 0.7, -0.2], (2, 3)), ([0.1, -0.2, 0.3, 0.4, 0.5, -0.6], (3, 2)), ([0.1, -0.1], (2,))]),
+    "fused_linear": (lambda F, xs: F.sum(F.linear(xs[0], xs[1], xs[2])),
+                     [([0.2, -0.3, 0.5, 0.1, 0.7, -0.2], (2, 3)), ([0.1, -0.2, 0.3, 0.4, 0.5, -0.6], (2, 3)), ([0.1, -0.1], (2,))]),
+    "linear_gelu": (lambda F, xs: F.sum(F.linear_activation(xs[0], xs[1], xs[2], "gelu")),
+                    [([0.2, -0.3, 0.5, 0.1, 0.7, -0.2], (2, 3)), ([0.1, -0.2, 0.3, 0.4, 0.5, -0.6], (2, 3)), ([0.1, -0.1], (2,))]),
+    "softmax": (lambda F, xs: F.sum(F.mul(F.softmax(xs[0]), xs[0])), [([0.2, -0.4, 0.7, 0.1, 0.3, -0.2], (2, 3))]),
+    "layer_norm": (lambda F, xs: (lambda y: F.sum(F.mul(y, y)))(F.layer_norm(xs[0], xs[1], xs[2], 1e-5)),
+                   [([0.2, -0.4, 0.7, 0.1, 0.3, -0.2], (2, 3)), ([1.0, 0.9, 1.1], (3,)), ([0.1, -0.1, 0.0], (3,))]),
+    "exp": (lambda F, xs: F.sum(F.exp(xs[0])), [([0.2, -0.1, 0.4, 0.3], (2, 2))]),
+    "log": (lambda F, xs: F.sum(F.log(xs[0])), [([0.5, 1.2, 0.7, 2.0], (2, 2))]),
+    "sigmoid": (lambda F, xs: F.sum(F.sigmoid(xs[0])), [([0.2, -0.1, 0.4, 0.3], (2, 2))]),
+    "gelu": (lambda F, xs: F.sum(F.gelu(xs[0])), [([0.2, -0.3, 0.5, 0.1], (2, 2))]),
+    "scale_mean": (lambda F, xs: F.scale(F.mean(F.mul(xs[0], xs[0])), 3.0), [([0.2, -0.3, 0.5, 0.1], (2, 2))]),
+    "max_pool": (lambda F, xs: F.sum(F.max_pool2d(xs[0], 2, 2, 0)),
+                 [([0.1, 0.2, -0.3, 0.4, 0.5, -0.6, 0.7, 0.8, -0.9, 0.2, -0.1, 0.3, -0.4, 0.5, 0.6, -0.7, 0.8, -0.9], (1, 2, 3, 3))]),
+    "conv2d": (lambda F, xs: F.sum(F.conv2d(xs[0], xs[1], xs[2], 1, 0)),
+               [([0.1, 0.2, -0.3, 0.4, 0.5, -0.6, 0.7, 0.8, -0.9, 0.2, -0.1, 0.3, -0.4, 0.5, 0.6, -0.7, 0.8, -0.9], (1, 2, 3, 3)),
+                ([0.2, -0.1, 0.3, 0.4, -0.2, 0.1, 0.5, -0.3, 0.15, -0.25, 0.35, -0.45, 0.55, -0.65, 0.75, -0.85], (2, 2, 2, 2)), ([0.1, -0.2], (2,))]),
+    "reshape": (lambda F, xs: F.sum(F.mul(F.reshape(xs[0], (3, 2)), F.reshape(xs[0], (3, 2)))), [([0.2, -0.1, 0.3, 0.4, -0.5, 0.6], (2, 3))]),
+    "attention": (lambda F, xs: (lambda y: F.sum(F.mul(y, y)))(F.multi_head_attention(xs[0], xs[1], xs[2], 1, True)),
+                  [([0.2, -0.1, 0.4, 0.3], (1, 2, 2)), ([0.1, 0.2, -0.3, 0.4], (1, 2, 2)), ([0.5, -0.2, 0.3, 0.1], (1, 2, 2))]),
+    "fan_in": (lambda F, xs: F.sum(F.add(F.add(F.mul(xs[0], xs[0]), F.relu(xs[0])), F.scale(xs[0], 2.0))), [([0.2, -0.3, 0.5, 0.1], (2, 2))]),
+}
+
+
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_reference_gradcheck_programs(mc, ctx, oracle, name):
+    f, ins = CASES[name]
+    gv, ov = zip(*[both(mc, ctx, oracle, d, s) for d, s in ins])
+    gl, ol = f(mc.F, gv), f(oracle.F, ov)
+    close(gl.data.reshape(-1), ol.data.reshape(-1), 1e-6)
+    gl.backward()
+    ol.backward()
+    for a, b in zip(gv, ov):
+        assert (a.grad is None) == (b.grad is None)
+        close(a.grad, b.grad, 2e-5)
+
+
+def test_sce_and_embedding_programs(mc, ctx, oracle):
+    gl, ol = both(mc, ctx, oracle, [0.2, 1.3, -0.4, 0.5, -1.0, 0.8], (2, 3))
+    lab = np.array([1, 2], np.int64)
+    a = mc.F.softmax_cross_entropy(gl, mc.Variable.constant(ctx, lab))
+    b = oracle.F.softmax_cross_entropy(ol, oracle.Variable.constant(lab))
+    close(a.data.reshape(-1), b.data.reshape(-1), 1e-6)
+    mc.F.scale(a, 128.0).backward()
+    oracle.F.scale(b, 128.0).backward()
+    close(gl.grad, ol.grad)
+    gw, ow = both(mc, ctx, oracle, [0.1, 0.2, -0.3, 0.4, 0.5, -0.6], (3, 2))
+    ids = np.array([0, 2, 0], np.int64)
+    mc.F.sum(mc.F.embedding(mc.Variable.constant(ctx, ids), gw)).backward()
+    oracle.F.sum(oracle.F.embedding(oracle.Variable.constant(ids), ow)).backward()
+    close(gw.grad, ow.grad)
+
+
+def test_tape_semantics(mc, ctx):
+    F = mc.F
+    a = mc.Variable(ctx, np.array([1.0, 2.0], np.float32))
+    F.sum(a).backward()
+    F.sum(F.mul(a, a)).backward()
+    g = a.grad
+    assert abs(g[0] - 3.0) < 1e-6 and abs(g[1] - 5.0) < 1e-6  # gradients_accumulate: exact 3.0 / 5.0
+    a.cleargrad()
+    assert a.grad is None
+    with mc.no_grad():
+        y = F.relu(mc.Variable(ctx, np.array([1.0, -1.0], np.float32)))
+    assert y.is_leaf() and not y.requires_grad
+    a = mc.Variable(ctx, np.array([1.0, 2.0], np.float32))
+    b = F.mul(a, a)
+    b.unchain_backward()
+    b.backward()
+    assert a.grad is None
+    c = mc.Variable.constant(ctx, np.array([1.0, 2.0], np.float32))
+    d = mc.Variable(ctx, np.array([3.0, 4.0], np.float32))
+    F.sum(F.mul(c, d)).backward()
+    assert c.grad is None and np.array_equal(d.grad, [1.0, 2.0])
+
+
+def test_bad_label_surfaces_as_invalid_argument(mc, ctx):
+    x = mc.Variable(ctx, np.zeros((2, 3), np.float32))
+    loss = mc.F.softmax_cross_entropy(x, mc.Variable.constant(ctx, np.array([0, 3], np.int64)))
+    with pytest.raises(mc.McbError) as e:
+        _ = loss.data
+    assert e.value.status == 5
+    with pytest.raises(mc.McbError) as e:
+        mc.F.softmax_cross_entropy(x, mc.Variable.constant(ctx, np.array([0.0, 1.0], np.float32)))
+    assert e.value.status == 4
+
+
+# ------------------------------------------------------------------ optimizer / GradScaler
+def test_grad_scaler_literals(mc, ctx):
+    # crates/modern-chainer-optim/tests/amp.rs:14-66 with Adam in place of SGD for the update itself
+    p = mc.Variable(ctx, np.array([1.0], np.float32))
+    p.set_grad(np.array([np.inf], np.float32))
+    sc = mc.GradScaler(ctx, 1024.0)
+    opt = mc.Adam(ctx, 1.0)
+    assert sc.step(opt, [p]) is False
+    assert sc.scale == 512.0 and p.grad is None and p.data[0] == 1.0  # skipped: backoff, grads cleared, param untouched
+    p.set_grad(np.array([0.0], np.float32))
+    sc2 = mc.GradScaler(ctx, 1024.0, growth_interval=1)
+    assert sc2.step(opt, [p]) is True and sc2.scale == 2048.0
+    q = mc.Variable(ctx, np.array([1.0], np.float32))
+    q.set_grad(np.array([2048.0], np.float32))
+    sc3 = mc.GradScaler(ctx, 1024.0)
+    assert sc3.step(mc.Adam(ctx, 1.0), [q]) is True and sc3.growth_tracker == 1
+    assert abs(q.data[0] - 0.0) < 1e-5  # unscaled grad 2 -> first Adam step moves by lr * sign = 1
+    assert mc.GradScaler(ctx, 0.25).scale == 1.0  # with_scale clamps to >= 1
+
+
+def test_scaler_matches_oracle_over_steps_with_overflow(mc, ctx, oracle):
+    rng = np.random.default_rng(5)
+    w0 = rng.standard_normal((6, 4)).astype(np.float32)
+    gp, op_ = mc.Variable(ctx, w0), oracle.Variable(w0.copy())
+    gs, os_ = mc.GradScaler(ctx, 65536.0, growth_interval=3), oracle.GradScaler(65536.0, growth_interval=3)
+    gopt, oopt = mc.Adam(ctx, 1e-2), oracle.Adam(1e-2)
+    for step in range(9):
+        g = (rng.standard_normal((6, 4)) * 1e-3).astype(np.float32) * np.float32(gs.scale)
+        if step in (2, 5):
+            g[1, 2] = np.nan if step == 2 else -np.inf
+        gp.set_grad(g)
+        op_.grad = g.copy()
+        assert gs.step(gopt, [gp]) == os_.step(oopt, [op_])
+        assert gs.scale == os_.scale and gs.growth_tracker == os_.growth_tracker
+        assert np.array_equal(gp.data, op_.data)  # bit-exact, including the skipped steps
+        if gp.grad is not None:
+            mc.zero_grad([gp])
+
+
+def test_scaler_async_equals_sync(mc, ctx):
+    rng = np.random.default_rng(6)
+    w0 = rng.standard_normal(1000).astype(np.float32)
+    a, b = mc.Variable(ctx, w0), mc.Variable(ctx, w0.copy())
+    sa, sb = mc.GradScaler(ctx, 1024.0, growth_interval=2), mc.GradScaler(ctx, 1024.0, growth_interval=2)
+    oa, ob = mc.Adam(ctx, 1e-2), mc.Adam(ctx, 1e-2)
+    for step in range(6):
+        g = rng.standard_normal(1000).astype(np.float32)
+        if step == 1:
+            g[7] = np.inf
+        a.set_grad(g)
+        b.set_grad(g)
+        sa.step(oa, [a])
+        sb.step_async(ob, [b])
+    assert np.array_equal(a.data, b.data) and sa.scale == sb.scale and sa.growth_tracker == sb.growth_tracker
+
+
+def test_adam_fits_linear_regression(mc, ctx):
+    F = mc.F
+    rng_w = np.array([[0.3]], np.float32)
+    w, b = mc.Variable(ctx, rng_w), mc.Variable(ctx, np.zeros(1, np.float32))
+    opt = mc.Adam(ctx, 0.05)
+    x = mc.Variable(ctx, np.array([[1.0], [2.0], [3.0], [4.0]], np.float32))
+    t = mc.Variable.constant(ctx, np.array([[2.0], [4.0], [6.0], [8.0]], np.float32))
+    last = None
+    for i in range(1200):
+        d = F.sub(F.linear(x, w, b), t)
+        loss = F.mean(F.mul(d, d))
+        mc.zero_grad([w, b])
+        loss.backward()
+        opt.update([w, b])
+        if i % 100 == 99:
+            last = float(loss.data)
+            if last < 1e-4:
+                break
+    assert last < 1e-2
+
+
+# ------------------------------------------------------------------ full training steps of the benchmark models
+def run_step(mc, ctx, oracle, kind, cfg, omodel, x, y, y_is_label, arena, steps=2, lr=1e-3):
+    gm = mc.Model(ctx, kind, cfg)
+    gparams, oparams = gm.parameters(), omodel.parameters()
+    assert len(gparams) == len(oparams)
+    for a, b in zip(gparams, oparams):
+        assert np.array_equal(a.data, b.data)  # same seeded initialisation, bit for bit
+    if arena:
+        keep = mc.Arena(ctx, gparams)
+    gopt, oopt = mc.Adam(ctx, lr), oracle.Adam(lr)
+    gx = mc.Variable.constant(ctx, x)
+    gy = mc.Variable.constant(ctx, y)
+    ox, oy = oracle.Variable.constant(x), oracle.Variable.constant(y)
+    for step in range(steps):
+        mc.zero_grad(gparams)
+        oracle.zero_grad(oparams)
+        gl, ol = gm.loss(gx, gy), omodel.loss(ox, oy)
+        close(gl.data.reshape(-1), ol.data.reshape(-1), 2e-5)
+        gl.backward()
+        ol.backward()
+        for i, (a, b) in enumerate(zip(gparams, oparams)):
+            assert a.grad is not None, i
+            close(a.grad, b.grad, 5e-5)
+        gopt.update(gparams)
+        oopt.update(oparams)
+        for i, (a, b) in enumerate(zip(gparams, oparams)):
+            # Adam's first steps move every weight by ~lr regardless of gradient size; compare the update
+            close(a.data, b.data, 2e-5)
+
+
+@pytest.mark.parametrize("arena", [False, True])
+def test_mlp_step_c1(mc, ctx, oracle, arena):
+    rng = np.random.default_rng(1234)
+    x = rng.standard_normal((128, 784)).astype(np.float32)
+    y = rng.integers(0, 10, 128).astype(np.int64)
+    run_step(mc, ctx, oracle, "mlp", [784, 100, 10], oracle.MLP(), x, y, True, arena)
+
+
+@pytest.mark.parametrize("arena", [False, True])
+def test_encoder_block_step_f32(mc, ctx, oracle, arena):
+    rng = np.random.default_rng(1235)
+    d, heads, ff, s, b = 64, 4, 128, 24, 3
+    x = rng.standard_normal((b, s, d)).astype(np.float32)
+    t = rng.standard_normal((b, s, d)).astype(np.float32)
+    run_step(mc, ctx, oracle, "encoder", [d, heads, ff, 0], oracle.EncoderBlock(d, heads, ff), x, t, False, arena)
+
+
+def test_cnn_step_c3_reduced(mc, ctx, oracle):
+    rng = np.random.default_rng(1236)
+    x = rng.random((8, 3, 16, 16)).astype(np.float32)
+    y = rng.integers(0, 10, 8).astype(np.int64)
+    run_step(mc, ctx, oracle, "cnn", [3, 8, 16, 16, 10], oracle.CNN(3, 8, 16, 16, 10), x, y, True, True)
+
+
+def test_decoder_step_f32_reduced(mc, ctx, oracle):
+    rng = np.random.default_rng(1237)
+    vocab, d, heads, ff, layers, s, b = 97, 32, 4, 64, 2, 16, 2
+    ids = rng.integers(0, vocab, (b, s)).astype(np.int64)
+    tgt = np.concatenate([ids[:, 1:], rng.integers(0, vocab, (b, 1))], 1).astype(np.int64)
+    run_step(mc, ctx, oracle, "decoder", [vocab, d, heads, ff, layers, 0], oracle.Decoder(vocab, d, heads, ff, layers, 0), ids, tgt, True, True)
+
+
+def amp_step(mc, ctx, oracle, kind, cfg, omodel, x, y, steps=3):
+    gm = mc.Model(ctx, kind, cfg)
+    gparams, oparams = gm.parameters(), omodel.parameters()
+    keep = mc.Arena(ctx, gparams)
+    gopt, gs = mc.Adam(ctx, 1e-3), mc.GradScaler(ctx, 65536.0)
+    gx, gy = mc.Variable.constant(ctx, x), mc.Variable.constant(ctx, y)
+    ox, oy = oracle.Variable.constant(x), oracle.Variable.constant(y)
+    ol = omodel.loss(ox, oy)
+    ol.backward()
+    losses = []
+    for step in range(steps):
+        mc.zero_grad(gparams)
+        with mc.autocast(mc.BF16):
+            gl = gm.loss(gx, gy)
+        gs.scale_loss(gl).backward()
+        if step == 0:
+            lg, lo = float(gl.data), float(ol.data)
+            assert abs(lg - lo) <= 2e-2 * abs(lo), (lg, lo)
+            for i, (a, b) in enumerate(zip(gparams, oparams)):
+                g = a.grad / np.float32(65536.0)
+                err = np.abs(g - b.grad).max() / max(np.abs(b.grad).max(), 1e-30)
+                assert err <= 3e-2, (i, err)
+        assert gs.step(gopt, gparams) is True
+        losses.append(float(gl.data))
+    assert losses[-1] < losses[0]  # every step applied and the loss goes down (cuda.rs:764-803)
+    return losses
+
+
+def test_encoder_block_amp_c2_reduced(mc, ctx, oracle):
+    rng = np.random.default_rng(1238)
+    d, heads, ff, s, b = 128, 2, 256, 64, 4
+    x = rng.standard_normal((b, s, d)).astype(np.float32)
+    t = rng.standard_normal((b, s, d)).astype(np.float32)
+    amp_step(mc, ctx, oracle, "encoder", [d, heads, ff, 0], oracle.EncoderBlock(d, heads, ff), x, t)
+
+
+def test_decoder_amp_c4_reduced(mc, ctx, oracle):
+    rng = np.random.default_rng(1239)
+    vocab, d, heads, ff, layers, s, b = 512, 128, 2, 256, 2, 64, 2
+    ids = rng.integers(0, vocab, (b, s)).astype(np.int64)
+    tgt = np.concatenate([ids[:, 1:], rng.integers(0, vocab, (b, 1))], 1).astype(np.int64)
+    amp_step(mc, ctx, oracle, "decoder", [vocab, d, heads, ff, layers, 0], oracle.Decoder(vocab, d, heads, ff, layers, 0), ids, tgt)
