@@ -146,7 +146,11 @@ class _Ops:
 
     def binary(self, op, a, b):
         a, b = np.asarray(a, np.float32), np.asarray(b, np.float32)
-        out = self.ctx.empty(np.broadcast_shapes(a.shape, b.shape))
+        try:
+            oshape = np.broadcast_shapes(a.shape, b.shape)
+        except ValueError:
+            oshape = a.shape  # let the library report the broadcast error
+        out = self.ctx.empty(oshape)
         da, db = self._a(a), self._a(b)
         self.ctx.check(self.lib.mcb_binary(self.ctx.h, op, da.ptr, _dims(a.shape), a.ndim, db.ptr, _dims(b.shape), b.ndim, out.ptr))
         return out.numpy()

@@ -234,14 +234,24 @@ def run_step(mc, ctx, oracle, kind, cfg, omodel, x, y, y_is_label, arena, steps=
         close(gl.data.reshape(-1), ol.data.reshape(-1), 2e-5)
         gl.backward()
         ol.backward()
-        for i, (a, b) in enumerate(zip(gparams, oparams)):
-            assert a.grad is not None, i
-            close(a.grad, b.grad, 5e-5)
+        ggrads = [a.grad for a in gparams]
+        assert all(g is not None for g in ggrads)
+        # norm-wise per tensor, with a floor of 1e-2 of the largest gradient in the model: some
+        # gradients are exactly zero in exact arithmetic (the key-projection bias: softmax is
+        # shift invariant), so both sides hold only rounding noise there
+        floor = 1e-2 * max(float(np.abs(b.grad).max()) for b in oparams)
+        for i, (g, b) in enumerate(zip(ggrads, oparams)):
+            err = np.abs(g.astype(np.float64) - b.grad).max() / max(float(np.abs(b.grad).max()), floor)
+            assert err <= 5e-5, (i, err)
         gopt.update(gparams)
+        # Adam's first steps move every weight by ~lr whatever the gradient's size, so a 1e-5
+        # difference in a near-zero gradient is amplified; the optimizer itself is checked bit-exactly
+        # by giving the oracle the gradients the GPU produced
+        for g, b in zip(ggrads, oparams):
+            b.grad = g
         oopt.update(oparams)
         for i, (a, b) in enumerate(zip(gparams, oparams)):
-            # Adam's first steps move every weight by ~lr regardless of gradient size; compare the update
-            close(a.data, b.data, 2e-5)
+            assert np.array_equal(a.data, b.data), i
 
 
 @pytest.mark.parametrize("arena", [False, True])
@@ -292,14 +302,15 @@ def amp_step(mc, ctx, oracle, kind, cfg, omodel, x, y, steps=3):
             gl = gm.loss(gx, gy)
         gs.scale_loss(gl).backward()
         if step == 0:
-            lg, lo = float(gl.data), float(ol.data)
+            lg, lo = float(gl.data.reshape(-1)[0]), float(ol.data.reshape(-1)[0])
             assert abs(lg - lo) <= 2e-2 * abs(lo), (lg, lo)
+            floor = 1e-2 * max(float(np.abs(b.grad).max()) for b in oparams)
             for i, (a, b) in enumerate(zip(gparams, oparams)):
                 g = a.grad / np.float32(65536.0)
-                err = np.abs(g - b.grad).max() / max(np.abs(b.grad).max(), 1e-30)
+                err = np.abs(g - b.grad).max() / max(float(np.abs(b.grad).max()), floor)
                 assert err <= 3e-2, (i, err)
         assert gs.step(gopt, gparams) is True
-        losses.append(float(gl.data))
+        losses.append(float(gl.data.reshape(-1)[0]))
     assert losses[-1] < losses[0]  # every step applied and the loss goes down (cuda.rs:764-803)
     return losses
 
