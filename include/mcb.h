@@ -153,6 +153,28 @@ mcb_status mcb_layer_norm(mcb_ctx *ctx, const float *x, const float *gamma, cons
 mcb_status mcb_layer_norm_backward(mcb_ctx *ctx, const float *x, const float *gamma, const void *g, int32_t g_dt,
                                    double eps, const float *mean, const float *rstd, float *dx, float *dgamma,
                                    float *dbeta, int64_t rows, int64_t dim);
+/* LayerNorm backward for callers that must not allocate device memory.  It has no counterpart in
+ * the reference.  Some hosts give a plugin a stream and a fixed set of buffers and rule out
+ * cudaMalloc / cudaFree for good: a control loop with a latency budget, a process whose device
+ * memory is carved up once at start-up, a section that is being recorded and may not touch the
+ * address space.  mcb_layer_norm_backward is unusable there because its per-block partial sums of
+ * dgamma / dbeta live in scratch memory the context allocates on demand.  This variant runs the
+ * same kernels with those partial sums in a 2 MiB array that is part of the library image (every
+ * GPU that loads the library holds it until the process exits).  It takes no context, allocates
+ * nothing, and calls no allocating routine.
+ *   stream      the cudaStream_t to enqueue on; its device must be the current device
+ *   arguments   as mcb_layer_norm_backward; mean / rstd may be NULL (recomputed from x)
+ *   limit       dim <= 4096; larger dims return MCB_INVALID_ARGUMENT and enqueue nothing
+ * The first call on each device looks up the array's device address and raises the kernel's
+ * shared-memory limit; make that first call before any stream capture begins.  All calls share
+ * the one array: two calls that can overlap on the GPU (different streams, no ordering between
+ * them) race on it and must be serialised by the caller.  The array keeps whatever the previous
+ * call left, which is harmless: each call overwrites every slot it later reads.
+ * The message for a failed call is returned by mcb_noalloc_last_error() (per host thread). */
+mcb_status mcb_layer_norm_backward_noalloc(void *stream, const float *x, const float *gamma, const void *g,
+                                           int32_t g_dt, double eps, const float *mean, const float *rstd, float *dx,
+                                           float *dgamma, float *dbeta, int64_t rows, int64_t dim);
+const char *mcb_noalloc_last_error(void);
 /* Ops::softmax_cross_entropy / _backward, ops.rs:1039-1119; labels I64, I32 or U8.
  * loss_out: one f32 on the device. */
 mcb_status mcb_softmax_cross_entropy(mcb_ctx *ctx, const float *logits, const void *labels, int32_t label_dt,

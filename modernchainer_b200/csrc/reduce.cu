@@ -4,6 +4,8 @@
 // reductions are two-stage through a scratch buffer so results do not depend on
 // scheduling (no float atomics except the embedding scatter).
 #include "common.cuh"
+#include <cstdio>
+
 #include "internal.h"
 
 namespace {
@@ -653,5 +655,87 @@ mcb_status mcb_sum_scaled(mcb_ctx *ctx, const float *x, int64_t n, double scale,
     MCB_LAUNCHED(ctx);
     sum_final_kernel<<<1, 32, 0, ctx->stream>>>((const double *)scratch, grid, scale, out);
     MCB_LAUNCHED(ctx);
+    return MCB_OK;
+}
+
+// ------------------------------------------------------------------ allocation-free LayerNorm backward
+// The regular LayerNorm backward keeps its per-block partial sums of dgamma / dbeta in a scratch
+// buffer that the context allocates on demand.  Code that runs where device allocation is off
+// limits (a host that hands the library a stream and fixed buffers and forbids cudaMalloc: a
+// real-time loop, a plugin inside a process whose memory is fully pre-partitioned, a region that
+// is being recorded and must not change the address space) gets this variant instead: the same
+// kernels, with the partial sums in a fixed array that is part of the loaded module.
+namespace {
+constexpr int kNoAllocMaxDim = 4096;   // widest normalised dimension accepted
+constexpr int kNoAllocBlocks = 64;     // row-sweeping blocks (each writes one [2][dim] partial)
+// 64 * 2 * 4096 floats = 2 MiB per device that loads the library, held until the process exits
+static __device__ __align__(256) float g_ln_noalloc_scratch[kNoAllocBlocks * 2 * kNoAllocMaxDim];
+
+constexpr int kMaxDevices = 64;
+float *g_ln_noalloc_ptr[kMaxDevices];   // device address of the array, per device ordinal
+bool g_ln_noalloc_ready[kMaxDevices];
+std::mutex g_ln_noalloc_mu;
+thread_local char g_noalloc_error[256] = "";
+
+mcb_status noalloc_fail(mcb_status st, const char *msg, cudaError_t e = cudaSuccess) {
+    if (e != cudaSuccess) snprintf(g_noalloc_error, sizeof(g_noalloc_error), "%s: %s", msg, cudaGetErrorString(e));
+    else snprintf(g_noalloc_error, sizeof(g_noalloc_error), "%s", msg);
+    return st;
+}
+
+// One-time set-up for the current device.  In host code the array's name is only a stand-in for
+// the symbol, not a device address; the address a kernel can use comes from cudaGetSymbolAddress.
+mcb_status ln_noalloc_setup(int device, float **out) {
+    std::lock_guard<std::mutex> lk(g_ln_noalloc_mu);
+    if (!g_ln_noalloc_ready[device]) {
+        float *ptr = nullptr;
+        cudaError_t e = cudaGetSymbolAddress((void **)&ptr, g_ln_noalloc_scratch);
+        if (e != cudaSuccess) return noalloc_fail(MCB_BACKEND, "cudaGetSymbolAddress(layer-norm scratch)", e);
+        const int smem_cap = 200 * 1024;
+        e = cudaFuncSetAttribute(layer_norm_backward_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_cap);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(layer_norm_backward_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_cap);
+        if (e != cudaSuccess) return noalloc_fail(MCB_BACKEND, "cudaFuncSetAttribute(layer-norm backward)", e);
+        g_ln_noalloc_ptr[device] = ptr;
+        g_ln_noalloc_ready[device] = true;
+    }
+    *out = g_ln_noalloc_ptr[device];
+    return MCB_OK;
+}
+} // namespace
+
+extern "C" const char *mcb_noalloc_last_error(void) { return g_noalloc_error; }
+
+extern "C" mcb_status mcb_layer_norm_backward_noalloc(void *stream, const float *x, const float *gamma, const void *g,
+                                                      int32_t g_dt, double eps, const float *mean, const float *rstd,
+                                                      float *dx, float *dgamma, float *dbeta, int64_t rows, int64_t dim) {
+    g_noalloc_error[0] = 0;
+    if (rows < 0 || dim <= 0) return noalloc_fail(MCB_INVALID_ARGUMENT, "layer_norm_backward_noalloc: rows must be >= 0 and dim > 0");
+    if (dim > kNoAllocMaxDim)
+        return noalloc_fail(MCB_INVALID_ARGUMENT, "layer_norm_backward_noalloc: dim exceeds 4096, the size the built-in scratch array was laid out for");
+    if (g_dt != MCB_F32 && g_dt != MCB_BF16) return noalloc_fail(MCB_UNSUPPORTED_DTYPE, "layer_norm_backward_noalloc: grad must be f32 or bf16");
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return noalloc_fail(MCB_BACKEND, "cudaGetDevice", e);
+    if (device < 0 || device >= kMaxDevices) return noalloc_fail(MCB_UNSUPPORTED, "layer_norm_backward_noalloc: device ordinal above 63");
+    float *scratch = nullptr;
+    mcb_status st = ln_noalloc_setup(device, &scratch);
+    if (st != MCB_OK) return st;
+    cudaStream_t s = (cudaStream_t)stream;
+    int warps = 8;
+    while (warps > 1 && (size_t)warps * 2 * dim * sizeof(float) > (size_t)200 * 1024) warps >>= 1;
+    size_t smem = (size_t)warps * 2 * dim * sizeof(float);
+    int64_t want = (rows + warps - 1) / warps;
+    int grid = (int)(want < 1 ? 1 : (want > kNoAllocBlocks ? kNoAllocBlocks : want));
+    // Every block overwrites its whole [2][dim] slice and the second kernel reads exactly `grid`
+    // slices, so nothing left in the array by an earlier call is ever read: no clearing needed.
+    if (g_dt == MCB_F32)
+        layer_norm_backward_kernel<float><<<grid, warps * 32, smem, s>>>(x, gamma, (const float *)g, (float)eps, mean, rstd, dx, scratch, rows, (int)dim);
+    else
+        layer_norm_backward_kernel<__nv_bfloat16><<<grid, warps * 32, smem, s>>>(x, gamma, (const __nv_bfloat16 *)g, (float)eps, mean, rstd, dx, scratch, rows, (int)dim);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return noalloc_fail(MCB_BACKEND, "layer_norm_backward_noalloc launch", e);
+    layer_norm_params_final_kernel<<<(int)((2 * dim + 255) / 256), 256, 0, s>>>(scratch, grid, (int)dim, dgamma, dbeta);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return noalloc_fail(MCB_BACKEND, "layer_norm_backward_noalloc launch", e);
     return MCB_OK;
 }
