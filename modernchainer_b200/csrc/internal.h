@@ -36,6 +36,12 @@ struct TcGemmParams {
 };
 mcb_status mcb_tc_gemm(mcb_ctx *ctx, const TcGemmParams &p);
 
+// flash_attn.cu: fused bf16 attention, head_dim 64
+bool mcb_flash_supported(int64_t dim, int64_t heads, int32_t dt);
+mcb_status mcb_flash_forward(mcb_ctx *ctx, const void *q, const void *k, const void *v, void *out, float *lse, int64_t n, int64_t seq,
+                             int64_t dim, int64_t heads, int32_t causal);
+mcb_status mcb_flash_backward(mcb_ctx *ctx, const void *q, const void *k, const void *v, const void *out, const void *gout, const float *lse,
+                              void *dq, void *dk, void *dv, int64_t n, int64_t seq, int64_t dim, int64_t heads, int32_t causal);
 // reduce.cu
 mcb_status mcb_sce_grad(mcb_ctx *ctx, const void *logits, void *out, int32_t dt, const void *labels, int32_t label_dt,
                         int64_t n, int64_t c, float *loss_out, const float *upstream);

@@ -325,6 +325,24 @@ def test_attention_bf16_storage(ops, oracle):
         assert np.abs(a - r).max() <= np.abs(r).max() * 2.0 ** -6
 
 
+@pytest.mark.parametrize("n,s,h,causal", [(1, 64, 1, True), (2, 256, 3, True), (2, 256, 3, False), (1, 100, 2, True), (3, 130, 1, False),
+                                          (1, 1, 1, True), (1, 1024, 2, True)])
+def test_fused_attention_bf16_head_dim_64(ops, oracle, n, s, h, causal):
+    d = 64 * h
+    q, k, v, g = (oracle.round_bf16(randn(n, s, d)) for _ in range(4))
+    out, lse = ops.attention(q, k, v, h, causal, dt=5)
+    ref = oracle.attention(q, k, v, h, causal)
+    assert np.abs(out - ref).max() <= max(np.abs(ref).max(), 1e-3) * 2.0 ** -7
+    # log-sum-exp of the scaled scores, per (sample, head, query)
+    sc = np.einsum("nqhd,nkhd->nhqk", q.reshape(n, s, h, 64).astype(np.float64), k.reshape(n, s, h, 64).astype(np.float64)) / 8.0
+    if causal:
+        sc = np.where(np.tril(np.ones((s, s), bool)), sc, -np.inf)
+    ref_lse = np.log(np.exp(sc - sc.max(-1, keepdims=True)).sum(-1)) + sc.max(-1)
+    assert np.abs(lse - ref_lse).max() <= 2e-3
+    for a, r in zip(ops.attention_backward(q, k, v, g, h, causal, dt=5), oracle.attention_backward(q, k, v, g, h, causal)):
+        assert np.abs(a - r).max() <= max(np.abs(r).max(), 1e-3) * 2.0 ** -6, np.abs(a - r).max() / np.abs(r).max()
+
+
 @pytest.mark.parametrize("shape,wshape,stride,pad", [((1, 2, 3, 3), (2, 2, 2, 2), 1, 0), ((4, 3, 32, 32), (8, 3, 3, 3), 1, 1),
                                                      ((2, 5, 9, 7), (4, 5, 3, 3), 2, 1)])
 def test_conv2d(ops, oracle, shape, wshape, stride, pad):
