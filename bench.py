@@ -38,6 +38,7 @@ WORKLOADS = {
     "c2": dict(kind="encoder", d=512, heads=8, ff=2048, seq=256, batch=32, amp=True),
     "c1": dict(kind="mlp", sizes=(784, 100, 10), batch=128, amp=False),
     "c5": dict(kind="optimizer", n=125_000_000),
+    "gemm": dict(kind="gemm"),
 }
 PROF_CLASSES = ["gemm_tc", "gemm_f32", "attention", "optimizer", "norm", "loss", "elementwise", "reduce", "embedding", "conv"]
 
@@ -61,7 +62,7 @@ class ClockSampler:
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200", "-i", str(self.index)],
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.index)],
                                          stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
@@ -168,12 +169,16 @@ class Dist:
 # ------------------------------------------------------------------ our arm
 def run_ours(args, dist):
     import modernchainer_b200 as mc
-    name, cfg = args.workload, WORKLOADS[args.workload]
+    name, cfg = args.workload, dict(WORKLOADS[args.workload])
+    if args.layers and "layers" in cfg:
+        cfg["layers"] = args.layers  # reduced depth for profiler captures; not a benchmark configuration
     ctx = mc.Context(dist.local)
     lib = ctx.lib
     pk = peaks()
     if cfg["kind"] == "optimizer":
         return run_c5(args, dist, mc, ctx, pk)
+    if cfg["kind"] == "gemm":
+        return run_gemm(args, dist, mc, ctx, pk)
     if dist.world > 1:
         uid = (C.c_char * 128)()
         if dist.rank == 0:
@@ -230,16 +235,15 @@ def run_ours(args, dist):
         return float(out)
 
     first_loss = last_loss = None
+    sampler = ClockSampler(dist.local)
+    if dist.rank == 0:
+        sampler.start()  # nvidia-smi needs a moment before its first sample: start it ahead of the warm-up
     for i in range(args.warmup):
         l = one_step(x, y)
         if i == 0:
             first_loss = float(l.data)
     ctx.sync()
-
-    sampler = ClockSampler(dist.local)
     dist.barrier()
-    if dist.rank == 0:
-        sampler.start()
     launches0 = ctx.launch_count()
     e0, e1 = ctx.event(), ctx.event()
     ctx.sync()
@@ -319,10 +323,40 @@ def run_ours(args, dist):
     return result
 
 
+def run_gemm(args, dist, mc, ctx, pk):
+    """Single tcgen05 GEMM shape, timed alone (used for per-shape roofline numbers and ncu captures).
+    --gemm m,n,k[,a_mn,b_mn]: D[m,n] = A B with bf16 operands, bf16 output."""
+    lib = ctx.lib
+    f = [int(v) for v in args.gemm.split(",")]
+    m, n, k = f[:3]
+    a_mn, b_mn = (f[3], f[4]) if len(f) >= 5 else (0, 0)
+    rng = np.random.default_rng(0)
+    a = ctx.array(rng.standard_normal(m * k).astype(np.float32), mc.BF16)
+    b = ctx.array(rng.standard_normal(n * k).astype(np.float32), mc.BF16)
+    d = ctx.zeros((m * n,), mc.BF16)
+
+    def run():
+        ctx.check(lib.mcb_gemm_bf16(ctx.h, a.ptr, a_mn, b.ptr, b_mn, d.ptr, mc.BF16, None, m, n, k, 0, 1))
+    for _ in range(args.warmup):
+        run()
+    e0, e1 = ctx.event(), ctx.event()
+    ctx.record(e0)
+    for _ in range(args.steps):
+        run()
+    ctx.record(e1)
+    ms = ctx.elapsed_ms(e0, e1) / args.steps
+    tf = 2.0 * m * n * k / (ms / 1e3) / 1e12
+    return {"metric": "bf16 GEMM TFLOP/s", "value": tf, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"gemm m={m} n={n} k={k} a_mn={a_mn} b_mn={b_mn}"}, "gpu_launches": args.steps,
+            "roofline": {"bound": "tensor", "kernel": "tc_gemm_kernel", "achieved": tf, "peak": pk["tf_burst"], "unit": "TFLOP/s",
+                         "frac": tf / pk["tf_burst"], "traffic": None, "peak_source": pk["src"] + " (burst cuBLAS bf16)"}}
+
+
 def run_c5(args, dist, mc, ctx, pk):
     """Optimizer-path stress test: fused inf/nan check + unscale + Adam over a flat buffer."""
     lib = ctx.lib
-    n = WORKLOADS["c5"]["n"]
+    n = args.n_params or WORKLOADS["c5"]["n"]
     rng = np.random.default_rng(1238)
     scale = 65536.0
     p = ctx.array(rng.standard_normal(n, dtype=np.float32) * np.float32(0.02))
@@ -477,12 +511,15 @@ def run_reference(args, dist):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--workload", default="c4", choices=list(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--bucket-mb", type=int, default=32)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--n-params", type=int, default=0, help="c5 only: number of parameters (default 125M)")
+    ap.add_argument("--gemm", default="8192,3072,768", help="gemm workload: m,n,k[,a_mn,b_mn]")
+    ap.add_argument("--layers", type=int, default=0, help="c4 only: override the layer count (small cases for ncu captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     dist = Dist(args.gpus)
@@ -490,7 +527,7 @@ def main():
         res = run_reference(args, dist)
     else:
         res = run_ours(args, dist)
-        if res is not None and dist.world == 1 and not args.no_cpu_baseline:
+        if res is not None and dist.world == 1 and not args.no_cpu_baseline and args.workload in ("c1", "c2", "c4", "c5"):
             v, cores, desc = cpu_sample(args.workload)
             res["cpu_baseline"] = {"value": v, "unit": res["unit"], "cores": cores, "kind": "port", "sample": desc}
     if dist.rank == 0 and res is not None:

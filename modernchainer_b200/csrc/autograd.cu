@@ -552,7 +552,7 @@ static mcb_status linear_backward_impl(mcb_ctx *ctx, const Tensor &g_in, const L
             p.b = sv.x.ptr; p.b_mn_major = 1; p.ldb = k;
             p.d = gi[1].ptr; p.out_dt = MCB_F32; p.ldd = k;
             p.m = n; p.n = k; p.k = m;
-            p.split_k = pick_split_k(ctx, n, k, m);
+            mcb_tc_plan(ctx, n, k, m, true, false, 1, &p.bn, &p.split_k);
             if (p.split_k > 1) {
                 p.accumulate = 1;
                 MCB_TRY(mcb_memset(ctx, gi[1].ptr, 0, sizeof(float) * n * k));

@@ -33,7 +33,7 @@ struct TcArgs {
     void *d_pre;
     const float *bias;
     long long m, n, k, ldd;
-    int out_bf16, accumulate, act, split_k;
+    int out_bf16, accumulate, act, split_k, vec_red;
     int a_mn, b_mn;
     unsigned idesc;
     int m_tiles, n_tiles, kb_total, kb_per_split;
@@ -137,9 +137,13 @@ __device__ __forceinline__ unsigned long long make_desc(unsigned smem_addr, unsi
     return d;
 }
 
+// GELU for the bf16 epilogue: the hardware tanh approximation (relative error ~2^-11) is below
+// bf16 resolution and keeps the epilogue shorter than the MMA time of the next tile
 __device__ __forceinline__ float gelu_f(float v) {
     float v3 = v * v * v;
-    return 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v3)));
+    float t;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.7978845608028654f * (v + 0.044715f * v3)));
+    return 0.5f * v * (1.0f + t);
 }
 
 template <int BN> struct Cfg {
@@ -300,9 +304,18 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     bool full = (col0 + 32 <= args.n);
                     if (args.accumulate) {
                         float *dst = (float *)args.d + row * args.ldd + col0;
+                        if (full && args.vec_red) {
+                            // 128-bit reductions: a quarter of the L2 atomic operations of the scalar form
 #pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (full || col0 + j < args.n) atomicAdd(dst + j, v[j]);
+                            for (int j = 0; j < 32; j += 4)
+                                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + j), "f"(v[j]), "f"(v[j + 1]),
+                                             "f"(v[j + 2]), "f"(v[j + 3])
+                                             : "memory");
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (full || col0 + j < args.n) atomicAdd(dst + j, v[j]);
+                        }
                     } else if (args.out_bf16) {
                         __nv_bfloat16 *dst = (__nv_bfloat16 *)args.d + row * args.ldd + col0;
                         __nv_bfloat16 *pre = args.d_pre ? (__nv_bfloat16 *)args.d_pre + row * args.ldd + col0 : nullptr;
@@ -418,6 +431,7 @@ template <int BN> mcb_status launch(mcb_ctx *ctx, const TcGemmParams &p) {
     a.m = p.m; a.n = p.n; a.k = p.k; a.ldd = p.ldd;
     a.out_bf16 = p.out_dt == MCB_BF16;
     a.accumulate = p.accumulate;
+    a.vec_red = (p.ldd % 4 == 0) && mcb_aligned16(p.d);
     a.act = p.act;
     a.a_mn = p.a_mn_major;
     a.b_mn = p.b_mn_major;
@@ -462,26 +476,51 @@ mcb_status mcb_tc_gemm(mcb_ctx *ctx, const TcGemmParams &p) {
     // vector stores in the epilogue need ldd and d aligned; otherwise the scalar tail path is used per row
     if ((p.out_dt == MCB_BF16 && ((p.ldd % 8) || !mcb_aligned16(p.d))) || (p.out_dt == MCB_F32 && !p.accumulate && ((p.ldd % 4) || !mcb_aligned16(p.d))))
         return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "GEMM output needs a 16-byte aligned base and row pitch");
-    // tile width: fewest idle SMs in the last wave, wider tile on ties
-    long long m_tiles = (p.m + BM - 1) / BM;
-    int best_bn = 256;
-    double best_eff = -1.0;
+    int bn = p.bn, split = p.split_k < 1 ? 1 : p.split_k;
+    if (bn != 128 && bn != 192 && bn != 256) {
+        int s2 = split;
+        mcb_tc_plan(ctx, p.m, p.n, p.k, false, p.accumulate, split, &bn, &s2);
+    }
+    TcGemmParams q = p;
+    q.split_k = split;
+    if (bn == 256) return launch<256>(ctx, q);
+    if (bn == 192) return launch<192>(ctx, q);
+    return launch<128>(ctx, q);
+}
+
+// Picks the tile width (and, when the caller can zero the output and accept atomic accumulation,
+// the split of the reduction dimension) that minimises a cycle estimate for one CTA:
+//   waves * k_blocks_per_item * (2 * BN + 40)  +  exposed epilogue
+// where 2*BN is the issue time of the four K=16 MMAs of one 64-deep block at M=128.
+void mcb_tc_plan(mcb_ctx *ctx, int64_t m, int64_t n, int64_t k, bool allow_split, bool atomic_out, int fixed_split, int *bn_out,
+                 int *split_out) {
     const int cands[3] = {256, 192, 128};
-    int split = p.split_k < 1 ? 1 : p.split_k;
+    long long m_tiles = (m + BM - 1) / BM, kb_total = (k + BK - 1) / BK;
+    double best = 1e300;
+    int best_bn = 256, best_split = 1;
+    int max_split = allow_split ? 16 : 1;
     for (int i = 0; i < 3; ++i) {
         int bn = cands[i];
-        long long work = m_tiles * ((p.n + bn - 1) / bn) * split;
-        long long waves = (work + ctx->sm_count - 1) / ctx->sm_count;
-        double useful = (double)p.n / (double)(((p.n + bn - 1) / bn) * bn);
-        double eff = useful * (double)work / (double)(waves * ctx->sm_count) * (bn == 128 ? 0.93 : 1.0);
-        if (eff > best_eff + 1e-9) {
-            best_eff = eff;
-            best_bn = bn;
+        long long tiles = m_tiles * ((n + bn - 1) / bn);
+        for (int s = 1; s <= max_split; ++s) {
+            int sp = allow_split ? s : (fixed_split < 1 ? 1 : fixed_split);
+            if (sp > 1 && kb_total / sp < 4) break;
+            long long kb = (kb_total + sp - 1) / sp;
+            long long items = tiles * ((kb_total + kb - 1) / kb);
+            long long waves = (items + ctx->sm_count - 1) / ctx->sm_count;
+            bool atomics = atomic_out || sp > 1;
+            double epi = (atomics ? 12.0 : 5.0) * bn;
+            // with several waves the epilogue of all but the last tile hides behind the next tile's MMAs
+            double cost = (double)waves * (double)kb * (2.0 * bn + 40.0) + epi + (sp > 1 ? 300.0 * sp : 0.0);
+            if (cost < best - 1e-9) {
+                best = cost;
+                best_bn = bn;
+                best_split = sp;
+            }
         }
     }
-    if (best_bn == 256) return launch<256>(ctx, p);
-    if (best_bn == 192) return launch<192>(ctx, p);
-    return launch<128>(ctx, p);
+    *bn_out = best_bn;
+    *split_out = best_split;
 }
 
 extern "C" mcb_status mcb_gemm_bf16(mcb_ctx *ctx, const void *a, int32_t a_mn_major, const void *b, int32_t b_mn_major,
@@ -498,5 +537,11 @@ extern "C" mcb_status mcb_gemm_bf16(mcb_ctx *ctx, const void *a, int32_t a_mn_ma
     p.ldd = n;
     p.accumulate = accumulate;
     p.split_k = split_k;
+    if (split_k <= 0) { // let the library choose; splitting is only possible with the accumulating epilogue
+        int bn = 0, sp = 1;
+        mcb_tc_plan(ctx, m, n, k, accumulate != 0, accumulate != 0, 1, &bn, &sp);
+        p.bn = bn;
+        p.split_k = sp;
+    }
     return mcb_tc_gemm(ctx, p);
 }

@@ -31,10 +31,14 @@ struct TcGemmParams {
     long long lda = 0, ldb = 0, ldd = 0; // elements between consecutive rows of the stored matrices
     int accumulate = 0;
     int split_k = 1;
+    int bn = 0; // tile width 128 / 192 / 256, 0 = choose
     int act = MCB_ACT_NONE;
     void *d_pre = nullptr; // optional second output: value before the activation (same dtype/ld as d)
 };
 mcb_status mcb_tc_gemm(mcb_ctx *ctx, const TcGemmParams &p);
+// tile width and reduction split for an [m, n] output reduced over k (see gemm_tc.cu)
+void mcb_tc_plan(mcb_ctx *ctx, int64_t m, int64_t n, int64_t k, bool allow_split, bool atomic_out, int fixed_split, int *bn_out,
+                 int *split_out);
 
 // flash_attn.cu: fused bf16 attention, head_dim 64
 bool mcb_flash_supported(int64_t dim, int64_t heads, int32_t dt);
@@ -42,6 +46,11 @@ mcb_status mcb_flash_forward(mcb_ctx *ctx, const void *q, const void *k, const v
                              int64_t dim, int64_t heads, int32_t causal);
 mcb_status mcb_flash_backward(mcb_ctx *ctx, const void *q, const void *k, const void *v, const void *out, const void *gout, const float *lse,
                               void *dq, void *dk, void *dv, int64_t n, int64_t seq, int64_t dim, int64_t heads, int32_t causal);
+// layer_norm_fast.cu: register-resident rows; MCB_UNSUPPORTED (nothing launched) outside their range
+mcb_status mcb_ln_fast_forward(mcb_ctx *ctx, const float *x, const float *gamma, const float *beta, double eps, void *out, int32_t out_dt,
+                               float *mean, float *rstd, int64_t rows, int64_t dim);
+mcb_status mcb_ln_fast_backward(mcb_ctx *ctx, const float *x, const float *gamma, const void *g, int32_t g_dt, double eps, const float *mean,
+                                const float *rstd, float *dx, float *dgamma, float *dbeta, int64_t rows, int64_t dim);
 // reduce.cu
 mcb_status mcb_sce_grad(mcb_ctx *ctx, const void *logits, void *out, int32_t dt, const void *labels, int32_t label_dt,
                         int64_t n, int64_t c, float *loss_out, const float *upstream);

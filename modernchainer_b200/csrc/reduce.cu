@@ -67,6 +67,57 @@ __global__ void col_sum_partial_kernel(const T *__restrict__ a, long long rows, 
         partial[(long long)blockIdx.y * cols + col] = t;
     }
 }
+// grid (ceil(cols/128), splits), block 256 = 8 warps; lane l of every warp owns columns chunk*128 + 4l .. +3
+template <typename T>
+__global__ void __launch_bounds__(256) col_sum_vec_kernel(const T *__restrict__ a, long long rows, long long cols,
+                                                          float *__restrict__ partial) {
+    __shared__ float4 red[8][32];
+    int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    long long col = (long long)blockIdx.x * 128 + lane * 4;
+    long long rows_per = (rows + gridDim.y - 1) / gridDim.y;
+    long long r0 = (long long)blockIdx.y * rows_per, r1 = r0 + rows_per < rows ? r0 + rows_per : rows;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (col < cols) {
+        long long c4 = col >> 2, ld4 = cols >> 2;
+        for (long long r = r0 + w; r < r1; r += 8) {
+            float4 v = Elem<T>::ld4(a, r * ld4 + c4);
+            acc.x += v.x;
+            acc.y += v.y;
+            acc.z += v.z;
+            acc.w += v.w;
+        }
+    }
+    red[w][lane] = acc;
+    __syncthreads();
+    if (w == 0 && col < cols) {
+        float4 t = red[0][lane];
+#pragma unroll
+        for (int y = 1; y < 8; ++y) {
+            float4 u = red[y][lane];
+            t.x += u.x;
+            t.y += u.y;
+            t.z += u.z;
+            t.w += u.w;
+        }
+        reinterpret_cast<float4 *>(partial + (long long)blockIdx.y * cols)[col >> 2] = t;
+    }
+}
+// out[col] = sum over `parts` partial rows, in a fixed order; block (32, 8): 32 columns, 8 interleaved part groups
+__global__ void partial_sum_final_kernel(const float *__restrict__ partial, int parts, long long cols, float *__restrict__ out) {
+    __shared__ float red[8][33];
+    long long col = (long long)blockIdx.x * 32 + threadIdx.x;
+    float t = 0.0f;
+    if (col < cols)
+        for (int s = threadIdx.y; s < parts; s += 8) t += partial[(long long)s * cols + col];
+    red[threadIdx.y][threadIdx.x] = t;
+    __syncthreads();
+    if (threadIdx.y == 0 && col < cols) {
+        float u = 0.0f;
+#pragma unroll
+        for (int y = 0; y < 8; ++y) u += red[y][threadIdx.x];
+        out[col] = u;
+    }
+}
 __global__ void col_sum_final_kernel(const float *__restrict__ partial, int splits, long long cols, float *__restrict__ out) {
     long long col = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (col >= cols) return;
@@ -270,18 +321,59 @@ __global__ void layer_norm_params_final_kernel(const float *__restrict__ partial
 }
 
 // ------------------------------------------------------------------ softmax cross entropy
+// exp for softmax rows: full-precision expf for f32 logits (1e-5 parity with the CPU), the
+// hardware exp2 approximation for bf16 logits, whose own rounding is 2^-8
+template <typename T> __device__ __forceinline__ float row_exp(float v);
+template <> __device__ __forceinline__ float row_exp<float>(float v) { return expf(v); }
+template <> __device__ __forceinline__ float row_exp<__nv_bfloat16>(float v) { return __expf(v); }
+
 // per-thread online (max, sum) merged across the block
 template <typename T>
 __device__ __forceinline__ void row_max_sumexp(const T *__restrict__ row, long long c, float *red, float &mx_out,
                                                float &sum_out) {
     float m = -INFINITY, s = 0.0f;
-    for (long long j = threadIdx.x; j < c; j += blockDim.x) {
-        float v = Elem<T>::ld(row, j);
-        if (v > m) {
-            s = s * expf(m - v) + 1.0f;
-            m = v;
-        } else {
-            s += expf(v - m);
+    // 4 elements per load when the row is wide and aligned: one running-max update per group
+    bool vec = ((c & 3) == 0) && ((reinterpret_cast<uintptr_t>(row) & (4 * sizeof(T) - 1)) == 0);
+    bool vec8 = sizeof(T) == 2 && ((c & 7) == 0) && ((reinterpret_cast<uintptr_t>(row) & 15) == 0);
+    if (vec8) {
+        // bf16 rows: 16-byte loads, 8 logits per thread per step
+        const uint4 *r8 = reinterpret_cast<const uint4 *>(row);
+        for (long long j = threadIdx.x; j < (c >> 3); j += blockDim.x) {
+            uint4 raw = r8[j];
+            float f[8];
+            unsigned wds[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                f[2 * q] = __uint_as_float(wds[q] << 16);
+                f[2 * q + 1] = __uint_as_float(wds[q] & 0xFFFF0000u);
+            }
+            float gm = fmaxf(fmaxf(fmaxf(f[0], f[1]), fmaxf(f[2], f[3])), fmaxf(fmaxf(f[4], f[5]), fmaxf(f[6], f[7])));
+            if (gm > m) {
+                s *= row_exp<T>(m - gm);
+                m = gm;
+            }
+#pragma unroll
+            for (int q = 0; q < 8; ++q) s += row_exp<T>(f[q] - m);
+        }
+    } else if (vec) {
+        for (long long j = threadIdx.x; j < (c >> 2); j += blockDim.x) {
+            float4 v = Elem<T>::ld4(row, j);
+            float gm = fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w));
+            if (gm > m) {
+                s *= row_exp<T>(m - gm);
+                m = gm;
+            }
+            s += (row_exp<T>(v.x - m) + row_exp<T>(v.y - m)) + (row_exp<T>(v.z - m) + row_exp<T>(v.w - m));
+        }
+    } else {
+        for (long long j = threadIdx.x; j < c; j += blockDim.x) {
+            float v = Elem<T>::ld(row, j);
+            if (v > m) {
+                s = s * row_exp<T>(m - v) + 1.0f;
+                m = v;
+            } else {
+                s += row_exp<T>(v - m);
+            }
         }
     }
     float M = block_max(m, red);
@@ -347,13 +439,13 @@ __global__ void sce_fused_kernel(const T *x, T *out, const void *__restrict__ la
     if (!out) return; // loss only
     float up = upstream ? upstream[0] : 1.0f;
     float inv_sum = 1.0f / sum, k = up / (float)n;
-    bool vec = ((c & 3) == 0);
+    bool vec = ((c & 3) == 0) && (((reinterpret_cast<uintptr_t>(row) | reinterpret_cast<uintptr_t>(orow)) & (4 * sizeof(T) - 1)) == 0);
     if (vec) {
         for (long long j = threadIdx.x; j < (c >> 2); j += blockDim.x) {
             float4 v = Elem<T>::ld4(row, j);
             long long b = j << 2;
-            float4 p = make_float4(expf(v.x - mx) * inv_sum, expf(v.y - mx) * inv_sum, expf(v.z - mx) * inv_sum,
-                                   expf(v.w - mx) * inv_sum);
+            float4 p = make_float4(row_exp<T>(v.x - mx) * inv_sum, row_exp<T>(v.y - mx) * inv_sum, row_exp<T>(v.z - mx) * inv_sum,
+                                   row_exp<T>(v.w - mx) * inv_sum);
             if (lab >= b && lab < b + 4) {
                 int o = (int)(lab - b);
                 if (o == 0) p.x -= 1.0f;
@@ -365,7 +457,7 @@ __global__ void sce_fused_kernel(const T *x, T *out, const void *__restrict__ la
         }
     } else {
         for (long long j = threadIdx.x; j < c; j += blockDim.x) {
-            float p = expf(Elem<T>::ld(row, j) - mx) * inv_sum;
+            float p = row_exp<T>(Elem<T>::ld(row, j) - mx) * inv_sum;
             if (j == lab) p -= 1.0f;
             Elem<T>::st(orow, j, p * k);
         }
@@ -434,6 +526,23 @@ mcb_status mcb_col_sum(mcb_ctx *ctx, const void *a, int32_t dt, int64_t rows, in
     MCB_CHECK_CTX(ctx);
     if (cols == 0) return MCB_OK;
     if (rows == 0) return mcb_memset(ctx, out, 0, sizeof(float) * cols);
+    ProfScope prof(ctx, MCB_PROF_REDUCE, 0.0, (double)rows * cols * (dt == MCB_BF16 ? 2.0 : 4.0));
+    if ((cols % 4) == 0 && mcb_aligned16(a) && (dt == MCB_F32 || dt == MCB_BF16)) {
+        // wide path: each lane owns 4 consecutive columns (one 8/16-byte load per row), a warp 128 columns
+        int chunks = (int)((cols + 127) / 128);
+        int splits = (int)((ctx->sm_count * 4 + chunks - 1) / chunks);
+        if (splits > (rows + 31) / 32) splits = (int)((rows + 31) / 32);
+        if (splits < 1) splits = 1;
+        void *scratch;
+        MCB_TRY(mcb_scratch(ctx, sizeof(float) * splits * cols, &scratch));
+        dim3 grid(chunks, splits);
+        if (dt == MCB_F32) col_sum_vec_kernel<float><<<grid, 256, 0, ctx->stream>>>((const float *)a, rows, cols, (float *)scratch);
+        else col_sum_vec_kernel<__nv_bfloat16><<<grid, 256, 0, ctx->stream>>>((const __nv_bfloat16 *)a, rows, cols, (float *)scratch);
+        MCB_LAUNCHED(ctx);
+        partial_sum_final_kernel<<<(int)((cols + 31) / 32), dim3(32, 8), 0, ctx->stream>>>((const float *)scratch, splits, cols, out);
+        MCB_LAUNCHED(ctx);
+        return MCB_OK;
+    }
     int col_tiles = (int)((cols + 31) / 32);
     int splits = (int)((ctx->sm_count * 8 + col_tiles - 1) / col_tiles);
     if (splits > (rows + 63) / 64) splits = (int)((rows + 63) / 64);
@@ -518,6 +627,10 @@ mcb_status mcb_layer_norm(mcb_ctx *ctx, const float *x, const float *gamma, cons
     if (dim > INT32_MAX) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "layer_norm dim too large");
     int vec = (dim % 4 == 0) && mcb_aligned16(x) && mcb_aligned16(out) && mcb_aligned16(gamma) && mcb_aligned16(beta);
     ProfScope prof(ctx, MCB_PROF_NORM, 0.0, (double)rows * dim * (4.0 + (out_dt == MCB_BF16 ? 2.0 : 4.0)) + 8.0 * rows);
+    if (out_dt == MCB_F32 || out_dt == MCB_BF16) {
+        mcb_status fast = mcb_ln_fast_forward(ctx, x, gamma, beta, eps, out, out_dt, mean, rstd, rows, dim);
+        if (fast != MCB_UNSUPPORTED) return fast; // rows of up to 1024 aligned elements stay in registers
+    }
     int grid = mcb_grid_for(ctx, rows, kThreads / 32, 16);
     if (out_dt == MCB_F32)
         layer_norm_kernel<float><<<grid, kThreads, 0, ctx->stream>>>(x, gamma, beta, (float)eps, (float *)out, mean, rstd, rows, (int)dim, vec);
@@ -540,6 +653,10 @@ mcb_status mcb_layer_norm_backward(mcb_ctx *ctx, const float *x, const float *ga
     }
     // algorithmic bytes: read x and g, write dx, read the row statistics, write 2*dim parameter sums
     ProfScope prof(ctx, MCB_PROF_NORM, 0.0, (double)rows * dim * (8.0 + (g_dt == MCB_BF16 ? 2.0 : 4.0)) + 8.0 * rows + 8.0 * dim);
+    if (g_dt == MCB_F32 || g_dt == MCB_BF16) {
+        mcb_status fast = mcb_ln_fast_backward(ctx, x, gamma, g, g_dt, eps, mean, rstd, dx, dgamma, dbeta, rows, dim);
+        if (fast != MCB_UNSUPPORTED) return fast;
+    }
     const size_t smem_cap = 200 * 1024;
     int warps = 8;
     while (warps > 1 && (size_t)warps * 2 * dim * sizeof(float) > smem_cap) warps >>= 1;
