@@ -287,6 +287,13 @@ def run_ours(args, dist):
     ms_step = dist.max(ms_resident / args.steps)
     ms_step_e2e = dist.max(max(ms_e2e_dev, wall_e2e) / args.steps)
     global_batch = cfg["batch"] * dist.world
+    # replicas must stay bit-identical: same init, same reduced gradients, same update on every rank
+    in_sync = None
+    if dist.world > 1:
+        digest = [float(np.abs(params[i].data.astype(np.float64)).sum()) for i in (1, 3, len(params) - 1)]
+        in_sync = dist.max(max(digest)) == max(digest) and -dist.max(-min(digest)) == min(digest) and \
+            dist.max(digest[1]) == digest[1] and -dist.max(-digest[1]) == digest[1]
+        in_sync = dist.max(0.0 if in_sync else 1.0) == 0.0
     result = None
     if dist.rank == 0:
         psteps = min(args.steps, 3)
@@ -317,6 +324,7 @@ def run_ours(args, dist):
                     "d2h_bytes_per_step": 4, "ms_per_step": ms_step_e2e},
             "gpu_launches": int(launches), "clocks": clocks, "roofline": roof, "kernels": kernels,
             "model_tflops": step_flops(cfg) / (ms_step / 1e3) / 1e12, "loss_first": first_loss, "loss_last": last_loss,
+            "replicas_in_sync": in_sync,
         }
     if dist.world > 1:
         ctx.check(lib.mcb_dp_shutdown(ctx.h))
