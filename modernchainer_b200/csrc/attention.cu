@@ -116,7 +116,7 @@ mcb_status mcb_attention(mcb_ctx *ctx, const void *q, const void *k, const void 
         void *lse_buf = lse;
         Tmp own(ctx);
         if (!lse_buf) MCB_TRY(own.get(sizeof(float) * n * heads * seq, &lse_buf));
-        return mcb_flash_forward(ctx, q, k, v, out, (float *)lse_buf, n, seq, dim, heads, causal);
+        return mcb_flash_forward(ctx, q, k, v, out, (float *)lse_buf, n, seq, dim, heads, causal, dim, dim);
     }
     Tmp tmp(ctx);
     const float *qf, *kf, *vf;
@@ -160,7 +160,7 @@ mcb_status mcb_attention_backward(mcb_ctx *ctx, const void *q, const void *k, co
     ProfScope prof(ctx, MCB_PROF_ATTENTION, 10.0 * (double)n * heads * seq * seq * hd * (causal ? 0.5 : 1.0),
                    (double)total * (dt == MCB_BF16 ? 2.0 : 4.0) * 8.0);
     if (mcb_flash_supported(dim, heads, dt) && out && lse)
-        return mcb_flash_backward(ctx, q, k, v, out, gout, lse, dq, dk, dv, n, seq, dim, heads, causal);
+        return mcb_flash_backward(ctx, q, k, v, out, gout, lse, dq, dk, dv, n, seq, dim, heads, causal, dim, dim, dim);
     float scale = 1.0f / sqrtf((float)hd);
     Tmp tmp(ctx);
     const float *qf, *kf, *vf, *gf;

@@ -857,6 +857,122 @@ mcb_status f_multi_head_attention(const Var &q, const Var &k, const Var &v, int6
     return MCB_OK;
 }
 
+// ---- fused self-attention block input: q/k/v projections as ONE GEMM, attention on the packed result
+// y = MHA(x Wq^T + bq, x Wk^T + bk, x Wv^T + bv) for x [n*s, d].  Possible when the three weights (and the
+// three biases) lie back to back in a parameter arena, which mcb_arena_create arranges: the GEMM then reads
+// one [3d, d] operand, the attention kernels read q, k, v as column blocks of the [n*s, 3d] result (row pitch
+// 3d), and backward needs one dgrad GEMM (K = 3d) instead of three plus two fan-in additions, one wgrad GEMM
+// into the three adjacent gradient slots, and one bias column sum.  Returns MCB_UNSUPPORTED (nothing
+// enqueued) when the layout or the dtype does not allow it; callers then compose the unfused ops.
+static bool adjacent(const Var &a, const Var &b) {
+    return a->arena && a->arena == b->arena && a->arena->off[b->arena_idx] == a->arena->off[a->arena_idx] + a->data.numel() &&
+           a->data.numel() % 64 == 0;
+}
+
+mcb_status f_qkv_attention(const Var &x, const Var &wq, const Var &bq, const Var &wk, const Var &bk, const Var &wv, const Var &bv,
+                           int64_t n, int64_t s, int64_t heads, bool causal, Var *out) {
+    mcb_ctx *ctx = x->ctx;
+    if (!use_bf16(ctx) || x->data.shape.size() != 2) return MCB_UNSUPPORTED;
+    if (getenv("MCB_UNFUSED_QKV")) return MCB_UNSUPPORTED; // test knob: run the composed ops instead
+    int64_t d = x->data.shape[1], m = x->data.shape[0];
+    if (m != n * s || !mcb_flash_supported(d, heads, MCB_BF16) || !tc_shape_ok(m, 3 * d, d)) return MCB_UNSUPPORTED;
+    for (const Var &w : {wq, wk, wv})
+        if (w->data.shape != std::vector<int64_t>{d, d}) return MCB_UNSUPPORTED;
+    for (const Var &b : {bq, bk, bv})
+        if (!b || b->data.shape != std::vector<int64_t>{d}) return MCB_UNSUPPORTED;
+    if (!adjacent(wq, wk) || !adjacent(wk, wv) || !adjacent(bq, bk) || !adjacent(bk, bv)) return MCB_UNSUPPORTED;
+    Tensor xb, wb, qkv, o, lse;
+    MCB_TRY(to_dtype(ctx, x->data, MCB_BF16, &xb));
+    MCB_TRY(bf16_of(wq, &wb)); // shadow of wq; wk and wv follow it in memory
+    MCB_TRY(new_tensor(ctx, MCB_BF16, {m, 3 * d}, &qkv));
+    MCB_TRY(new_tensor(ctx, MCB_BF16, {m, d}, &o));
+    MCB_TRY(new_tensor(ctx, MCB_F32, {n, heads, s}, &lse));
+    {
+        TcGemmParams p; // qkv[m, 3d] = x[m, d] * Wqkv[3d, d]^T + bqkv
+        p.a = xb.ptr; p.lda = d;
+        p.b = wb.ptr; p.ldb = d;
+        p.d = qkv.ptr; p.out_dt = MCB_BF16; p.ldd = 3 * d;
+        p.bias = (const float *)bq->data.ptr;
+        p.m = m; p.n = 3 * d; p.k = d;
+        MCB_TRY(mcb_tc_gemm(ctx, p));
+    }
+    const __nv_bfloat16 *qp = (const __nv_bfloat16 *)qkv.ptr;
+    {
+        ProfScope prof(ctx, MCB_PROF_ATTENTION, 4.0 * (double)n * heads * s * s * 64 * (causal ? 0.5 : 1.0), 8.0 * (double)m * d);
+        MCB_TRY(mcb_flash_forward(ctx, qp, qp + d, qp + 2 * d, o.ptr, (float *)lse.ptr, n, s, d, heads, causal, 3 * d, d));
+    }
+    Var xv = x, wqv = wq, wkv = wk, wvv = wv, bqv = bq, bkv = bk, bvv = bv;
+    *out = apply(ctx, "QkvAttention", o, {x, wq, bq, wk, bk, wv, bv},
+                 [=](const Tensor &g_in, std::vector<Tensor> &gi) -> mcb_status {
+        Tensor g, dqkv;
+        MCB_TRY(to_dtype(ctx, g_in, MCB_BF16, &g));
+        MCB_TRY(new_tensor(ctx, MCB_BF16, {m, 3 * d}, &dqkv));
+        __nv_bfloat16 *dp = (__nv_bfloat16 *)dqkv.ptr;
+        const __nv_bfloat16 *qp = (const __nv_bfloat16 *)qkv.ptr; // the closure owns qkv, o and lse until backward has run
+        {
+            ProfScope prof(ctx, MCB_PROF_ATTENTION, 10.0 * (double)n * heads * s * s * 64 * (causal ? 0.5 : 1.0), 16.0 * (double)m * d);
+            MCB_TRY(mcb_flash_backward(ctx, qp, qp + d, qp + 2 * d, o.ptr, g.ptr, (const float *)lse.ptr, dp, dp + d, dp + 2 * d, n, s, d, heads,
+                                       causal, 3 * d, d, 3 * d));
+        }
+        if (xv->requires_grad) {
+            int xdt = is_float(xv->data.dt) ? xv->data.dt : MCB_F32;
+            MCB_TRY(new_tensor(ctx, xdt, xv->data.shape, &gi[0]));
+            TcGemmParams p; // dx[m, d] = dqkv[m, 3d] * Wqkv[3d, d]
+            p.a = dqkv.ptr; p.lda = 3 * d;
+            p.b = wb.ptr; p.b_mn_major = 1; p.ldb = d;
+            p.d = gi[0].ptr; p.out_dt = xdt; p.ldd = d;
+            p.m = m; p.n = d; p.k = 3 * d;
+            MCB_TRY(mcb_tc_gemm(ctx, p));
+        }
+        // weight gradients: one [3d, d] product, straight into the three adjacent arena slots when they are free
+        bool dq_, dk_, dv_;
+        Tensor tw[3], tb[3];
+        Var ws[3] = {wqv, wkv, wvv}, bs[3] = {bqv, bkv, bvv};
+        bool all_free = true;
+        for (int i = 0; i < 3; ++i) all_free = all_free && !ws[i]->has_grad && !ws[i]->slot_claimed && !bs[i]->has_grad && !bs[i]->slot_claimed;
+        Tensor dw, db;
+        if (all_free) {
+            MCB_TRY(grad_dst(wqv, &tw[0], &dq_));
+            MCB_TRY(grad_dst(wkv, &tw[1], &dk_));
+            MCB_TRY(grad_dst(wvv, &tw[2], &dv_));
+            MCB_TRY(grad_dst(bqv, &tb[0], &dq_));
+            MCB_TRY(grad_dst(bkv, &tb[1], &dk_));
+            MCB_TRY(grad_dst(bvv, &tb[2], &dv_));
+            dw = tw[0];
+            db = tb[0];
+        } else {
+            MCB_TRY(new_tensor(ctx, MCB_F32, {3 * d, d}, &dw));
+            MCB_TRY(new_tensor(ctx, MCB_F32, {3 * d}, &db));
+            for (int i = 0; i < 3; ++i) {
+                tw[i] = dw;
+                tw[i].ptr = (float *)dw.ptr + i * d * d;
+                tw[i].shape = {d, d};
+                tb[i] = db;
+                tb[i].ptr = (float *)db.ptr + i * d;
+                tb[i].shape = {d};
+            }
+        }
+        {
+            TcGemmParams p; // dWqkv[3d, d] = dqkv^T[3d, m] * x[m, d]
+            p.a = dqkv.ptr; p.a_mn_major = 1; p.lda = 3 * d;
+            p.b = xb.ptr; p.b_mn_major = 1; p.ldb = d;
+            p.d = dw.ptr; p.out_dt = MCB_F32; p.ldd = d;
+            p.m = 3 * d; p.n = d; p.k = m;
+            mcb_tc_plan(ctx, p.m, p.n, p.k, true, false, 1, &p.bn, &p.split_k);
+            if (p.split_k > 1) {
+                p.accumulate = 1;
+                MCB_TRY(mcb_memset(ctx, dw.ptr, 0, sizeof(float) * 3 * d * d));
+            }
+            MCB_TRY(mcb_tc_gemm(ctx, p));
+        }
+        MCB_TRY(mcb_col_sum(ctx, dqkv.ptr, MCB_BF16, m, 3 * d, (float *)db.ptr));
+        gi[1] = tw[0]; gi[3] = tw[1]; gi[5] = tw[2];
+        gi[2] = tb[0]; gi[4] = tb[1]; gi[6] = tb[2];
+        return MCB_OK;
+    });
+    return MCB_OK;
+}
+
 mcb_status f_conv2d(const Var &x, const Var &w, const Var &b, int64_t stride, int64_t pad, Var *out) {
     mcb_ctx *ctx = x->ctx;
     if (x->data.shape.size() != 4 || w->data.shape.size() != 4) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "conv2d expects [N,C,H,W] and [O,C,KH,KW]");
@@ -924,10 +1040,21 @@ mcb_status arena_create(mcb_ctx *ctx, const std::vector<Var> &params, Arena **ou
     for (auto &p : params) {
         if (p->arena) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "a parameter already belongs to an arena");
         if (p->data.dt != MCB_F32) return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "arena parameters must be f32");
-        a->off.push_back(off);
-        a->size.push_back(p->data.numel());
-        off += align_up(p->data.numel(), 64); // 256-byte aligned slots: vector access and TMA bases stay legal
     }
+    // Layout: all matrices (rank >= 2) in list order, then all vectors in list order.  Slots are
+    // padded to 64 elements (256 bytes) so vector access and TMA bases stay legal.  With the
+    // biases out of the way, consecutive weight matrices of equal width (the q, k, v projections)
+    // sit back to back and can be read as one [3d, d] operand; their biases likewise as one [3d].
+    a->off.assign(params.size(), 0);
+    a->size.assign(params.size(), 0);
+    for (int pass = 0; pass < 2; ++pass)
+        for (size_t i = 0; i < params.size(); ++i) {
+            bool matrix = params[i]->data.shape.size() >= 2;
+            if (matrix != (pass == 0)) continue;
+            a->off[i] = off;
+            a->size[i] = params[i]->data.numel();
+            off += align_up(params[i]->data.numel(), 64);
+        }
     a->total = off;
     auto mk = [&](size_t bytes, std::shared_ptr<Buf> *b) -> mcb_status {
         void *p = nullptr;
@@ -1278,14 +1405,19 @@ mcb_status Model::loss(const Var &input, const Var &target, Var *out) {
         Var n1, flat, q, k, v, q3, k3, v3, att, att2, o, o3, x1, n2, flat2, h, f2, f3, y, diff, sq;
         MCB_TRY(f_layer_norm(input, P[0], P[1], eps, &n1));
         MCB_TRY(f_reshape(n1, {b * s, d}, &flat));
-        MCB_TRY(f_linear(flat, P[2], P[3], &q));
-        MCB_TRY(f_linear(flat, P[4], P[5], &k));
-        MCB_TRY(f_linear(flat, P[6], P[7], &v));
-        MCB_TRY(f_reshape(q, {b, s, d}, &q3));
-        MCB_TRY(f_reshape(k, {b, s, d}, &k3));
-        MCB_TRY(f_reshape(v, {b, s, d}, &v3));
-        MCB_TRY(f_multi_head_attention(q3, k3, v3, heads, causal, &att));
-        MCB_TRY(f_reshape(att, {b * s, d}, &att2));
+        mcb_status fused = f_qkv_attention(flat, P[2], P[3], P[4], P[5], P[6], P[7], b, s, heads, causal, &att2);
+        if (fused == MCB_UNSUPPORTED) {
+            MCB_TRY(f_linear(flat, P[2], P[3], &q));
+            MCB_TRY(f_linear(flat, P[4], P[5], &k));
+            MCB_TRY(f_linear(flat, P[6], P[7], &v));
+            MCB_TRY(f_reshape(q, {b, s, d}, &q3));
+            MCB_TRY(f_reshape(k, {b, s, d}, &k3));
+            MCB_TRY(f_reshape(v, {b, s, d}, &v3));
+            MCB_TRY(f_multi_head_attention(q3, k3, v3, heads, causal, &att));
+            MCB_TRY(f_reshape(att, {b * s, d}, &att2));
+        } else {
+            MCB_TRY(fused);
+        }
         MCB_TRY(f_linear(att2, P[8], P[9], &o));
         MCB_TRY(f_reshape(o, {b, s, d}, &o3));
         MCB_TRY(f_binary(MCB_ADD, input, o3, &x1));
@@ -1323,14 +1455,19 @@ mcb_status Model::loss(const Var &input, const Var &target, Var *out) {
     for (int64_t l = 0; l < layers; ++l, pi += 16) {
         Var n1, q, k, v, q3, k3, v3, att, att2, o, x1, n2, h, f2, x2;
         MCB_TRY(f_layer_norm(x, P[pi + 0], P[pi + 1], eps, &n1));
-        MCB_TRY(f_linear(n1, P[pi + 2], P[pi + 3], &q));
-        MCB_TRY(f_linear(n1, P[pi + 4], P[pi + 5], &k));
-        MCB_TRY(f_linear(n1, P[pi + 6], P[pi + 7], &v));
-        MCB_TRY(f_reshape(q, {b, s, d}, &q3));
-        MCB_TRY(f_reshape(k, {b, s, d}, &k3));
-        MCB_TRY(f_reshape(v, {b, s, d}, &v3));
-        MCB_TRY(f_multi_head_attention(q3, k3, v3, heads, true, &att));
-        MCB_TRY(f_reshape(att, {b * s, d}, &att2));
+        mcb_status fused = f_qkv_attention(n1, P[pi + 2], P[pi + 3], P[pi + 4], P[pi + 5], P[pi + 6], P[pi + 7], b, s, heads, true, &att2);
+        if (fused == MCB_UNSUPPORTED) {
+            MCB_TRY(f_linear(n1, P[pi + 2], P[pi + 3], &q));
+            MCB_TRY(f_linear(n1, P[pi + 4], P[pi + 5], &k));
+            MCB_TRY(f_linear(n1, P[pi + 6], P[pi + 7], &v));
+            MCB_TRY(f_reshape(q, {b, s, d}, &q3));
+            MCB_TRY(f_reshape(k, {b, s, d}, &k3));
+            MCB_TRY(f_reshape(v, {b, s, d}, &v3));
+            MCB_TRY(f_multi_head_attention(q3, k3, v3, heads, true, &att));
+            MCB_TRY(f_reshape(att, {b * s, d}, &att2));
+        } else {
+            MCB_TRY(fused);
+        }
         MCB_TRY(f_linear(att2, P[pi + 8], P[pi + 9], &o));
         MCB_TRY(f_binary(MCB_ADD, x, o, &x1));
         MCB_TRY(f_layer_norm(x1, P[pi + 10], P[pi + 11], eps, &n2));

@@ -168,19 +168,26 @@ mcb_status mcb_dp_attach(mcb_ctx *ctx, mcb_arena *arena, int64_t bucket_bytes) {
     DpState *dp = (DpState *)ctx->dp;
     Arena *a = arena->a;
     int n = (int)a->vars.size();
+    // plan over the slots in arena order (the arena places matrices before vectors), so that every
+    // bucket is one contiguous range; walking from the arena's end meets the vectors (small, final
+    // only late in backward), then the last layers' matrices, which are the first to be ready
+    std::vector<int> order(n);
+    for (int i = 0; i < n; ++i) order[i] = i;
+    std::sort(order.begin(), order.end(), [&](int x, int y) { return a->off[x] < a->off[y]; });
     std::vector<int64_t> sizes(n);
-    for (int i = 0; i < n; ++i) sizes[i] = (i + 1 < n ? a->off[i + 1] : a->total) - a->off[i]; // padded slot sizes
+    for (int j = 0; j < n; ++j) sizes[j] = (j + 1 < n ? a->off[order[j + 1]] : a->total) - a->off[order[j]]; // padded slot sizes
     std::vector<int32_t> bo(n);
     int32_t nb = 0;
     MCB_TRY(mcb_dp_plan_buckets(sizes.data(), n, bucket_bytes / 4 > 0 ? bucket_bytes / 4 : 1, bo.data(), &nb));
-    a->bucket_of.assign(bo.begin(), bo.end());
+    a->bucket_of.assign(n, 0);
     a->bucket_begin.assign(nb, INT64_MAX);
     a->bucket_end.assign(nb, 0);
     a->bucket_size.assign(nb, 0);
-    for (int i = 0; i < n; ++i) {
-        int b = bo[i];
+    for (int j = 0; j < n; ++j) {
+        int b = bo[j], i = order[j];
+        a->bucket_of[i] = b;
         a->bucket_begin[b] = std::min(a->bucket_begin[b], a->off[i]);
-        a->bucket_end[b] = std::max(a->bucket_end[b], a->off[i] + sizes[i]);
+        a->bucket_end[b] = std::max(a->bucket_end[b], a->off[i] + sizes[j]);
         a->bucket_size[b] += 1;
     }
     a->bucket_pending = a->bucket_size;

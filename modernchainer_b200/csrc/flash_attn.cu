@@ -3,7 +3,9 @@
 // path (mma.sync m16n8k16 bf16 -> f32), operands staged in 128-byte-swizzled shared memory
 // with cp.async double buffering.
 //
-// q, k, v, o, grads: [n, seq, dim] bf16 with head h in columns h*64 .. h*64+63.
+// q, k, v, o, grads: [n, seq, dim] bf16 with head h in columns h*64 .. h*64+63.  Row pitches are
+// separate arguments (ldi for q/k/v, ldo for o/do, ldg for dq/dk/dv), so q, k, v may be the three
+// column blocks of one packed [n*seq, 3*dim] projection output and the gradients of one packed buffer.
 // lse: [n, heads, seq] f32, natural-log row log-sum-exp of the scaled scores.
 //
 // Backward is three kernels: delta = rowsum(dO * O); dK/dV per key tile (loop over query
@@ -125,13 +127,17 @@ __device__ __forceinline__ void store_rows(bf16 *g, long long ld, int row0, int 
 // ------------------------------------------------------------------ forward
 template <bool CAUSAL>
 __global__ void __launch_bounds__(kThreads) flash_fwd_kernel(const bf16 *__restrict__ Q, const bf16 *__restrict__ K, const bf16 *__restrict__ V,
-                                                             bf16 *__restrict__ O, float *__restrict__ LSE, int S, int D, int H,
+                                                             bf16 *__restrict__ O, float *__restrict__ LSE, int S, int D, int DO, int DG, int H,
                                                              float scale_log2) {
     __shared__ __align__(128) unsigned char smem[TILE_BYTES * 5];
     unsigned char *sQ = smem, *sK[2] = {smem + TILE_BYTES, smem + 3 * TILE_BYTES}, *sV[2] = {smem + 2 * TILE_BYTES, smem + 4 * TILE_BYTES};
     int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tig = lane & 3;
     int qt = blockIdx.x, n = blockIdx.y / H, h = blockIdx.y % H;
-    long long base = (long long)n * S * D + (long long)h * HD;
+    long long base = (long long)n * S * D + (long long)h * HD;      // q, k, v (row pitch D)
+    long long base_o = (long long)n * S * DO + (long long)h * HD;   // o, do (row pitch DO)
+    long long base_g = (long long)n * S * DG + (long long)h * HD;   // dq, dk, dv (row pitch DG)
+    (void)base_o;
+    (void)base_g;
     int q0 = qt * TILE;
     int ntiles = CAUSAL ? qt + 1 : (S + TILE - 1) / TILE;
     load_tile(sQ, Q + base + (long long)q0 * D, D, S - q0);
@@ -206,7 +212,7 @@ __global__ void __launch_bounds__(kThreads) flash_fwd_kernel(const bf16 *__restr
         inv[r] = t > 0.0f ? 1.0f / t : 0.0f;
         lse[r] = (t > 0.0f) ? m[r] * 0.6931471805599453f + logf(t) : -INFINITY;
     }
-    store_rows(O + base, D, q0 + warp * 16, S, o, inv[0], inv[1], lane);
+    store_rows(O + base_o, DO, q0 + warp * 16, S, o, inv[0], inv[1], lane);
     if (tig == 0) {
         long long lb = ((long long)n * H + h) * S;
         if (row0 < S) LSE[lb + row0] = lse[0];
@@ -234,19 +240,23 @@ __global__ void flash_delta_kernel(const bf16 *__restrict__ O, const bf16 *__res
 template <bool CAUSAL>
 __global__ void __launch_bounds__(kThreads) flash_dq_kernel(const bf16 *__restrict__ Q, const bf16 *__restrict__ K, const bf16 *__restrict__ V,
                                                             const bf16 *__restrict__ dO, const float *__restrict__ LSE,
-                                                            const float *__restrict__ DELTA, bf16 *__restrict__ dQ, int S, int D, int H,
+                                                            const float *__restrict__ DELTA, bf16 *__restrict__ dQ, int S, int D, int DO, int DG, int H,
                                                             float scale, float scale_log2) {
     __shared__ __align__(128) unsigned char smem[TILE_BYTES * 6];
     unsigned char *sQ = smem, *sdO = smem + TILE_BYTES;
     unsigned char *sK[2] = {smem + 2 * TILE_BYTES, smem + 4 * TILE_BYTES}, *sV[2] = {smem + 3 * TILE_BYTES, smem + 5 * TILE_BYTES};
     int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tig = lane & 3;
     int qt = blockIdx.x, n = blockIdx.y / H, h = blockIdx.y % H;
-    long long base = (long long)n * S * D + (long long)h * HD;
+    long long base = (long long)n * S * D + (long long)h * HD;      // q, k, v (row pitch D)
+    long long base_o = (long long)n * S * DO + (long long)h * HD;   // o, do (row pitch DO)
+    long long base_g = (long long)n * S * DG + (long long)h * HD;   // dq, dk, dv (row pitch DG)
+    (void)base_o;
+    (void)base_g;
     long long lb = ((long long)n * H + h) * S;
     int q0 = qt * TILE;
     int ntiles = CAUSAL ? qt + 1 : (S + TILE - 1) / TILE;
     load_tile(sQ, Q + base + (long long)q0 * D, D, S - q0);
-    load_tile(sdO, dO + base + (long long)q0 * D, D, S - q0);
+    load_tile(sdO, dO + base_o + (long long)q0 * DO, DO, S - q0);
     load_tile(sK[0], K + base, D, S);
     load_tile(sV[0], V + base, D, S);
     cp_async_commit();
@@ -296,7 +306,7 @@ __global__ void __launch_bounds__(kThreads) flash_dq_kernel(const bf16 *__restri
         if (j + 1 < ntiles) cp_async_wait<0>();
         __syncthreads();
     }
-    store_rows(dQ + base, D, q0 + warp * 16, S, dq, scale, scale, lane);
+    store_rows(dQ + base_g, DG, q0 + warp * 16, S, dq, scale, scale, lane);
 }
 
 // ------------------------------------------------------------------ backward: dK, dV
@@ -304,7 +314,7 @@ template <bool CAUSAL>
 __global__ void __launch_bounds__(kThreads) flash_dkv_kernel(const bf16 *__restrict__ Q, const bf16 *__restrict__ K, const bf16 *__restrict__ V,
                                                              const bf16 *__restrict__ dO, const float *__restrict__ LSE,
                                                              const float *__restrict__ DELTA, bf16 *__restrict__ dK, bf16 *__restrict__ dV,
-                                                             int S, int D, int H, float scale, float scale_log2) {
+                                                             int S, int D, int DO, int DG, int H, float scale, float scale_log2) {
     __shared__ __align__(128) unsigned char smem[TILE_BYTES * 4];
     __shared__ float sLse[2][TILE], sDelta[2][TILE];
     unsigned char *sQ[2] = {smem, smem + 2 * TILE_BYTES}, *sdO[2] = {smem + TILE_BYTES, smem + 3 * TILE_BYTES};
@@ -312,7 +322,11 @@ __global__ void __launch_bounds__(kThreads) flash_dkv_kernel(const bf16 *__restr
     unsigned char *sK = sQ[1], *sV = sdO[1];
     int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tig = lane & 3;
     int kt = blockIdx.x, n = blockIdx.y / H, h = blockIdx.y % H;
-    long long base = (long long)n * S * D + (long long)h * HD;
+    long long base = (long long)n * S * D + (long long)h * HD;      // q, k, v (row pitch D)
+    long long base_o = (long long)n * S * DO + (long long)h * HD;   // o, do (row pitch DO)
+    long long base_g = (long long)n * S * DG + (long long)h * HD;   // dq, dk, dv (row pitch DG)
+    (void)base_o;
+    (void)base_g;
     long long lb = ((long long)n * H + h) * S;
     int k0 = kt * TILE;
     int qtiles = (S + TILE - 1) / TILE;
@@ -320,7 +334,7 @@ __global__ void __launch_bounds__(kThreads) flash_dkv_kernel(const bf16 *__restr
     auto load_q = [&](int i, int st) {
         int q1 = i * TILE;
         load_tile(sQ[st], Q + base + (long long)q1 * D, D, S - q1);
-        load_tile(sdO[st], dO + base + (long long)q1 * D, D, S - q1);
+        load_tile(sdO[st], dO + base_o + (long long)q1 * DO, DO, S - q1);
         if (threadIdx.x < TILE) {
             int row = q1 + threadIdx.x;
             sLse[st][threadIdx.x] = row < S ? LSE[lb + row] * 1.4426950408889634f : 0.0f;
@@ -372,8 +386,8 @@ __global__ void __launch_bounds__(kThreads) flash_dkv_kernel(const bf16 *__restr
         if (i + 1 < qtiles) cp_async_wait<0>();
         __syncthreads();
     }
-    store_rows(dK + base, D, k0 + warp * 16, S, dk, scale, scale, lane);
-    store_rows(dV + base, D, k0 + warp * 16, S, dv, 1.0f, 1.0f, lane);
+    store_rows(dK + base_g, DG, k0 + warp * 16, S, dk, scale, scale, lane);
+    store_rows(dV + base_g, DG, k0 + warp * 16, S, dv, 1.0f, 1.0f, lane);
 }
 
 } // namespace
@@ -381,36 +395,40 @@ __global__ void __launch_bounds__(kThreads) flash_dkv_kernel(const bf16 *__restr
 bool mcb_flash_supported(int64_t dim, int64_t heads, int32_t dt) { return dt == MCB_BF16 && heads > 0 && dim == heads * HD; }
 
 mcb_status mcb_flash_forward(mcb_ctx *ctx, const void *q, const void *k, const void *v, void *out, float *lse, int64_t n, int64_t seq,
-                             int64_t dim, int64_t heads, int32_t causal) {
+                             int64_t dim, int64_t heads, int32_t causal, int64_t ldi, int64_t ldo) {
+    if (ldi % 8 || ldo % 8) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "fused attention needs row pitches that are multiples of 8");
     if (!mcb_aligned16(q) || !mcb_aligned16(k) || !mcb_aligned16(v) || !mcb_aligned16(out) || (dim % 8))
         return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "fused attention needs 16-byte aligned tensors");
     if (n * heads > 65535) return mcb_fail(ctx, MCB_UNSUPPORTED, "fused attention: n * heads > 65535");
     float scale_log2 = (1.0f / sqrtf((float)HD)) * 1.4426950408889634f;
     dim3 grid((unsigned)((seq + TILE - 1) / TILE), (unsigned)(n * heads));
     if (causal)
-        flash_fwd_kernel<true><<<grid, kThreads, 0, ctx->stream>>>((const bf16 *)q, (const bf16 *)k, (const bf16 *)v, (bf16 *)out, lse, (int)seq, (int)dim, (int)heads, scale_log2);
+        flash_fwd_kernel<true><<<grid, kThreads, 0, ctx->stream>>>((const bf16 *)q, (const bf16 *)k, (const bf16 *)v, (bf16 *)out, lse, (int)seq, (int)ldi, (int)ldo, (int)ldo, (int)heads, scale_log2);
     else
-        flash_fwd_kernel<false><<<grid, kThreads, 0, ctx->stream>>>((const bf16 *)q, (const bf16 *)k, (const bf16 *)v, (bf16 *)out, lse, (int)seq, (int)dim, (int)heads, scale_log2);
+        flash_fwd_kernel<false><<<grid, kThreads, 0, ctx->stream>>>((const bf16 *)q, (const bf16 *)k, (const bf16 *)v, (bf16 *)out, lse, (int)seq, (int)ldi, (int)ldo, (int)ldo, (int)heads, scale_log2);
     MCB_LAUNCHED(ctx);
     return MCB_OK;
 }
 
 mcb_status mcb_flash_backward(mcb_ctx *ctx, const void *q, const void *k, const void *v, const void *out, const void *gout, const float *lse,
-                              void *dq, void *dk, void *dv, int64_t n, int64_t seq, int64_t dim, int64_t heads, int32_t causal) {
+                              void *dq, void *dk, void *dv, int64_t n, int64_t seq, int64_t dim, int64_t heads, int32_t causal,
+                              int64_t ldi, int64_t ldo, int64_t ldg) {
+    (void)dim;
+    if (ldi % 8 || ldo % 8 || ldg % 8) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "fused attention needs row pitches that are multiples of 8");
     if (n * heads > 65535) return mcb_fail(ctx, MCB_UNSUPPORTED, "fused attention: n * heads > 65535");
     float scale = 1.0f / sqrtf((float)HD), scale_log2 = scale * 1.4426950408889634f;
     long long rows = n * heads * seq;
     void *delta = nullptr;
     MCB_TRY(mcb_alloc(ctx, sizeof(float) * rows, &delta));
-    flash_delta_kernel<<<(unsigned)((rows * 32 + 255) / 256), 256, 0, ctx->stream>>>((const bf16 *)out, (const bf16 *)gout, (float *)delta, (int)seq, (int)dim, (int)heads, rows);
+    flash_delta_kernel<<<(unsigned)((rows * 32 + 255) / 256), 256, 0, ctx->stream>>>((const bf16 *)out, (const bf16 *)gout, (float *)delta, (int)seq, (int)ldo, (int)heads, rows);
     ctx->launches++;
     dim3 grid((unsigned)((seq + TILE - 1) / TILE), (unsigned)(n * heads));
     if (causal) {
-        flash_dkv_kernel<true><<<grid, kThreads, 0, ctx->stream>>>((const bf16 *)q, (const bf16 *)k, (const bf16 *)v, (const bf16 *)gout, lse, (const float *)delta, (bf16 *)dk, (bf16 *)dv, (int)seq, (int)dim, (int)heads, scale, scale_log2);
-        flash_dq_kernel<true><<<grid, kThreads, 0, ctx->stream>>>((const bf16 *)q, (const bf16 *)k, (const bf16 *)v, (const bf16 *)gout, lse, (const float *)delta, (bf16 *)dq, (int)seq, (int)dim, (int)heads, scale, scale_log2);
+        flash_dkv_kernel<true><<<grid, kThreads, 0, ctx->stream>>>((const bf16 *)q, (const bf16 *)k, (const bf16 *)v, (const bf16 *)gout, lse, (const float *)delta, (bf16 *)dk, (bf16 *)dv, (int)seq, (int)ldi, (int)ldo, (int)ldg, (int)heads, scale, scale_log2);
+        flash_dq_kernel<true><<<grid, kThreads, 0, ctx->stream>>>((const bf16 *)q, (const bf16 *)k, (const bf16 *)v, (const bf16 *)gout, lse, (const float *)delta, (bf16 *)dq, (int)seq, (int)ldi, (int)ldo, (int)ldg, (int)heads, scale, scale_log2);
     } else {
-        flash_dkv_kernel<false><<<grid, kThreads, 0, ctx->stream>>>((const bf16 *)q, (const bf16 *)k, (const bf16 *)v, (const bf16 *)gout, lse, (const float *)delta, (bf16 *)dk, (bf16 *)dv, (int)seq, (int)dim, (int)heads, scale, scale_log2);
-        flash_dq_kernel<false><<<grid, kThreads, 0, ctx->stream>>>((const bf16 *)q, (const bf16 *)k, (const bf16 *)v, (const bf16 *)gout, lse, (const float *)delta, (bf16 *)dq, (int)seq, (int)dim, (int)heads, scale, scale_log2);
+        flash_dkv_kernel<false><<<grid, kThreads, 0, ctx->stream>>>((const bf16 *)q, (const bf16 *)k, (const bf16 *)v, (const bf16 *)gout, lse, (const float *)delta, (bf16 *)dk, (bf16 *)dv, (int)seq, (int)ldi, (int)ldo, (int)ldg, (int)heads, scale, scale_log2);
+        flash_dq_kernel<false><<<grid, kThreads, 0, ctx->stream>>>((const bf16 *)q, (const bf16 *)k, (const bf16 *)v, (const bf16 *)gout, lse, (const float *)delta, (bf16 *)dq, (int)seq, (int)ldi, (int)ldo, (int)ldg, (int)heads, scale, scale_log2);
     }
     ctx->launches += 2;
     cudaError_t e = cudaGetLastError();

@@ -43,9 +43,10 @@ void mcb_tc_plan(mcb_ctx *ctx, int64_t m, int64_t n, int64_t k, bool allow_split
 // flash_attn.cu: fused bf16 attention, head_dim 64
 bool mcb_flash_supported(int64_t dim, int64_t heads, int32_t dt);
 mcb_status mcb_flash_forward(mcb_ctx *ctx, const void *q, const void *k, const void *v, void *out, float *lse, int64_t n, int64_t seq,
-                             int64_t dim, int64_t heads, int32_t causal);
+                             int64_t dim, int64_t heads, int32_t causal, int64_t ldi, int64_t ldo);
 mcb_status mcb_flash_backward(mcb_ctx *ctx, const void *q, const void *k, const void *v, const void *out, const void *gout, const float *lse,
-                              void *dq, void *dk, void *dv, int64_t n, int64_t seq, int64_t dim, int64_t heads, int32_t causal);
+                              void *dq, void *dk, void *dv, int64_t n, int64_t seq, int64_t dim, int64_t heads, int32_t causal,
+                              int64_t ldi, int64_t ldo, int64_t ldg);
 // layer_norm_fast.cu: register-resident rows; MCB_UNSUPPORTED (nothing launched) outside their range
 mcb_status mcb_ln_fast_forward(mcb_ctx *ctx, const float *x, const float *gamma, const float *beta, double eps, void *out, int32_t out_dt,
                                float *mean, float *rstd, int64_t rows, int64_t dim);

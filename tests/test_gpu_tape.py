@@ -331,3 +331,40 @@ def test_decoder_amp_c4_reduced(mc, ctx, oracle):
     ids = rng.integers(0, vocab, (b, s)).astype(np.int64)
     tgt = np.concatenate([ids[:, 1:], rng.integers(0, vocab, (b, 1))], 1).astype(np.int64)
     amp_step(mc, ctx, oracle, "decoder", [vocab, d, heads, ff, layers, 0], oracle.Decoder(vocab, d, heads, ff, layers, 0), ids, tgt)
+
+
+@pytest.mark.parametrize("cfg", [(1000, 256, 4, 512, 2, 192, 2), (2048, 768, 12, 3072, 2, 1024, 8)])
+def test_fused_qkv_attention_matches_composed_ops(mc, ctx, cfg):
+    """The packed q/k/v projection + attention op against the same layer built from three
+    F.linear calls and F.multi_head_attention, both in bf16 on the GPU (same rounding points except
+    the order of the f32 accumulations): losses within 1e-3, gradients within 2e-2 per tensor.
+    The second case has the layer widths, sequence length and batch of the benchmark decoder."""
+    import os
+    rng = np.random.default_rng(4321)
+    vocab, d, heads, ff, layers, s, b = cfg
+    ids = rng.integers(0, vocab, (b, s)).astype(np.int64)
+    tgt = np.concatenate([ids[:, 1:], rng.integers(0, vocab, (b, 1))], 1).astype(np.int64)
+
+    def run(unfused):
+        if unfused:
+            os.environ["MCB_UNFUSED_QKV"] = "1"
+        else:
+            os.environ.pop("MCB_UNFUSED_QKV", None)
+        try:
+            m = mc.Model(ctx, "decoder", [vocab, d, heads, ff, layers, 0])
+            ps = m.parameters()
+            keep = mc.Arena(ctx, ps)
+            with mc.autocast(mc.BF16):
+                loss = m.loss(mc.Variable.constant(ctx, ids), mc.Variable.constant(ctx, tgt))
+            loss.backward()
+            return float(loss.data.reshape(-1)[0]), [p.grad for p in ps]
+        finally:
+            os.environ.pop("MCB_UNFUSED_QKV", None)
+
+    lf, gf = run(False)
+    lu, gu = run(True)
+    assert abs(lf - lu) <= 1e-3 * abs(lu), (lf, lu)
+    floor = 5e-2 * max(float(np.abs(g).max()) for g in gu)
+    for i, (a, r) in enumerate(zip(gf, gu)):
+        err = np.abs(a - r).max() / max(float(np.abs(r).max()), floor)
+        assert err <= 2e-2, (i, err)
