@@ -18,6 +18,8 @@
 // error word, stops issuing work, and still frees its TMEM before returning.
 #include <cuda.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 #include "internal.h"
 
@@ -477,6 +479,7 @@ mcb_status mcb_tc_gemm(mcb_ctx *ctx, const TcGemmParams &p) {
     if ((p.out_dt == MCB_BF16 && ((p.ldd % 8) || !mcb_aligned16(p.d))) || (p.out_dt == MCB_F32 && !p.accumulate && ((p.ldd % 4) || !mcb_aligned16(p.d))))
         return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "GEMM output needs a 16-byte aligned base and row pitch");
     int bn = p.bn, split = p.split_k < 1 ? 1 : p.split_k;
+    if (const char *force = getenv("MCB_TC_BN")) bn = atoi(force); // tuning knob: force the tile width
     if (bn != 128 && bn != 192 && bn != 256) {
         int s2 = split;
         mcb_tc_plan(ctx, p.m, p.n, p.k, false, p.accumulate, split, &bn, &s2);
