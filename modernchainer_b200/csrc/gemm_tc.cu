@@ -36,6 +36,8 @@ struct TcArgs {
     const float *bias;
     long long m, n, k, ldd;
     int out_bf16, accumulate, act, split_k, vec_red;
+    int tma_out;  // 1: the epilogue stages output boxes in shared memory and TMA writes (or adds) them
+    int bias_vec; // bias base is 16-byte aligned
     int a_mn, b_mn;
     unsigned idesc;
     int m_tiles, n_tiles, kb_total, kb_per_split;
@@ -113,6 +115,55 @@ __device__ __forceinline__ void tc_mma(unsigned tmem_d, unsigned long long adesc
                  : "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
                  : "memory");
 }
+// ---- CTA-pair (cta_group::2) forms: two CTAs of one cluster act as one 256-row MMA.  Barriers
+// sit at the same shared-memory offset in both CTAs; `mapa` turns a local barrier address into
+// the cluster address of the same barrier in the pair's leader (cluster rank 0).
+__device__ __forceinline__ unsigned leader_addr(const void *p) {
+    unsigned r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, 0;" : "=r"(r) : "r"(smem_u32(p)));
+    return r;
+}
+__device__ __forceinline__ unsigned cluster_rank() {
+    unsigned r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// arrive on a barrier of the leader CTA from either CTA of the pair
+__device__ __forceinline__ void mbar_arrive_leader(unsigned long long *bar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(leader_addr(bar)) : "memory");
+}
+// per-CTA TMA load whose completion bytes are counted on the LEADER's barrier (no multicast: the
+// data lands only in the issuing CTA's shared memory)
+__device__ __forceinline__ void tma_load_2d_pair(void *smem_dst, const CUtensorMap *map, unsigned long long *bar, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 :
+                 : "r"(smem_u32(smem_dst)), "l"((unsigned long long)map), "r"(leader_addr(bar)), "r"(x), "r"(y)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(unsigned *smem_dst, unsigned ncols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_dealloc_pair(unsigned taddr, unsigned ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// completion of the pair's MMAs arrives on the barrier at this offset in BOTH CTAs (mask 0b11)
+__device__ __forceinline__ void tc_commit_pair(unsigned long long *bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(smem_u32(bar)),
+                 "h"((unsigned short)3)
+                 : "memory");
+}
+__device__ __forceinline__ void tc_mma_pair(unsigned tmem_d, unsigned long long adesc, unsigned long long bdesc, unsigned idesc,
+                                            unsigned accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 :
+                 : "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+                 : "memory");
+}
 __device__ __forceinline__ void tmem_ld32(unsigned taddr, unsigned (&r)[32]) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
                  "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -125,6 +176,60 @@ __device__ __forceinline__ void tmem_ld32(unsigned taddr, unsigned (&r)[32]) {
                  : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// ---- output path: a warp stages a [32 rows x 128 bytes] box in shared memory (128-byte swizzle)
+// and one lane hands it to TMA, which writes whole rows and clips at the matrix edge.  Compared
+// with per-lane row-strided global stores this removes 32 separate L2 transactions per
+// instruction from the load/store unit.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, const void *smem_src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 :
+                 : "l"((unsigned long long)map), "r"(smem_u32(smem_src)), "r"(x), "r"(y)
+                 : "memory");
+}
+// same box, added to the f32 matrix in global memory (split-K and gradient accumulation)
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap *map, const void *smem_src, int x, int y) {
+    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+                 :
+                 : "l"((unsigned long long)map), "r"(smem_u32(smem_src)), "r"(x), "r"(y)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// all but the newest group have finished READING their shared-memory source
+__device__ __forceinline__ void bulk_wait_read1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ unsigned pack_bf16(float a, float b) {
+    __nv_bfloat162 p = __floats2bfloat162_rn(a, b);
+    return *(unsigned *)&p;
+}
+
+// Per-warp staging ring of two 4 KB boxes.  `issued` counts the boxes handed to TMA so far.
+struct StageRing {
+    unsigned char *base;
+    unsigned issued;
+};
+// Wait until the box about to be overwritten has been read, and return it.
+__device__ __forceinline__ unsigned char *ring_acquire(StageRing &rg, int lane) {
+    if (lane == 0) bulk_wait_read1();
+    __syncwarp();
+    return rg.base + (rg.issued & 1u) * 4096u;
+}
+// 16-byte piece `j` (0..7) of this lane's 128-byte row, at its swizzled position
+__device__ __forceinline__ void ring_put(unsigned char *box, int lane, int j, uint4 piece) {
+    *(uint4 *)(box + lane * 128 + ((j ^ (lane & 7)) << 4)) = piece;
+}
+__device__ __forceinline__ void ring_submit(StageRing &rg, unsigned char *box, const CUtensorMap *map, int x, int y, bool reduce, int lane) {
+    fence_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+        if (reduce) tma_reduce_add_2d(map, box, x, y);
+        else tma_store_2d(map, box, x, y);
+        bulk_commit();
+    }
+    ++rg.issued;
+}
 
 // Shared-memory matrix descriptor (sm_100 format): start address >> 4 in bits [0,14),
 // leading byte offset >> 4 in [16,30), stride byte offset >> 4 in [32,46), version 1 in
@@ -148,27 +253,42 @@ __device__ __forceinline__ float gelu_f(float v) {
     return 0.5f * v * (1.0f + t);
 }
 
-template <int BN> struct Cfg {
-    static constexpr int kStageBytes = (BM + BN) * BK * 2;
-    static constexpr int kStages = (BN == 256) ? 4 : (BN == 192 ? 5 : 6);
-    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+// PAIR = two CTAs of a cluster share one 256 x BN tile: each loads its own 128 rows of A and half
+// of the BN columns of B, so a CTA's shared-memory traffic per MMA flop is half that of the
+// single-CTA form (which is bound by shared-memory bandwidth, not by the tensor pipe).
+template <int BN, bool PAIR> struct Cfg {
+    static constexpr int kBRows = PAIR ? BN / 2 : BN; // B rows (output columns) staged per CTA
+    static constexpr int kStageBytes = (BM + kBRows) * BK * 2;
+    static constexpr int kStages = PAIR ? (BN == 128 ? 8 : 6) : (BN == 128 ? 6 : 4);
+    static constexpr int kOutStageBytes = 4 * 2 * 4096; // four epilogue warps x two 4 KB output boxes
+    static constexpr int kSmemBytes = kStages * kStageBytes + kOutStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+    static_assert(kSmemBytes <= 227 * 1024, "shared memory budget of one CTA");
 };
 
-template <int BN>
+template <int BN, bool PAIR>
 __global__ void __launch_bounds__(kThreads, 1)
-tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcArgs args) {
-    constexpr int kStages = Cfg<BN>::kStages;
-    constexpr int kABytes = BM * BK * 2, kBBytes = BN * BK * 2;
+tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               const __grid_constant__ CUtensorMap map_d, const __grid_constant__ CUtensorMap map_pre, TcArgs args) {
+    using C = Cfg<BN, PAIR>;
+    constexpr int kStages = C::kStages;
+    constexpr int kABytes = BM * BK * 2, kBBytes = C::kBRows * BK * 2;
     extern __shared__ unsigned char smem_raw[];
     // operand tiles need 1024-byte alignment for the 128-byte swizzle pattern
     unsigned char *tiles = (unsigned char *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    unsigned long long *bars = (unsigned long long *)(tiles + kStages * Cfg<BN>::kStageBytes);
+    unsigned char *out_stage = tiles + kStages * C::kStageBytes; // 1024-aligned: stage sizes are multiples of 8 KB
+    unsigned long long *bars = (unsigned long long *)(out_stage + C::kOutStageBytes);
     unsigned long long *full_bar = bars, *empty_bar = bars + kStages;
     unsigned long long *acc_full = bars + 2 * kStages, *acc_empty = acc_full + 2;
     unsigned *tmem_slot = (unsigned *)(acc_empty + 2);
     volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
 
     int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // rank inside the pair (0 = leader: arms the full barriers and issues the MMAs) and the
+    // persistent work stride: one work item per CTA, or per pair
+    const unsigned crank = PAIR ? cluster_rank() : 0u;
+    const long long w_first = PAIR ? (long long)(blockIdx.x >> 1) : (long long)blockIdx.x;
+    const long long w_stride = PAIR ? (long long)(gridDim.x >> 1) : (long long)gridDim.x;
+    constexpr int kTileM = PAIR ? 2 * BM : BM;
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
             mbar_init(&full_bar[s], 1);
@@ -176,17 +296,23 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(&acc_full[a], 1);
-            mbar_init(&acc_empty[a], 4);
+            mbar_init(&acc_empty[a], PAIR ? 8 : 4); // the leader also collects the peer's four epilogue warps
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
-        tmem_alloc(tmem_slot, 512);
-        tmem_relinquish();
+        if (PAIR) {
+            tmem_alloc_pair(tmem_slot, 512);
+            tmem_relinquish_pair();
+        } else {
+            tmem_alloc(tmem_slot, 512);
+            tmem_relinquish();
+        }
     }
     tc_fence_before();
     __syncthreads();
+    if (PAIR) cluster_sync_all(); // the peer's barriers exist before anything signals them
     tc_fence_after();
     unsigned tmem_base = *tmem_slot;
 
@@ -197,10 +323,11 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         // ---------------------------------------------------------------- TMA producer
         if (lane == 0) {
             unsigned it = 0;
-            for (long long w = blockIdx.x; w < work_total; w += gridDim.x) {
+            for (long long w = w_first; w < work_total; w += w_stride) {
                 long long t = w % tiles_mn;
                 int split = (int)(w / tiles_mn);
-                int m0 = (int)(t % args.m_tiles) * BM, n0 = (int)(t / args.m_tiles) * BN;
+                int m0 = (int)(t % args.m_tiles) * kTileM + (int)crank * BM;
+                int n0 = (int)(t / args.m_tiles) * BN + (int)crank * (PAIR ? BN / 2 : 0);
                 int kb0 = split * args.kb_per_split;
                 int kb1 = min(kb0 + args.kb_per_split, args.kb_total);
                 bool ok = true;
@@ -209,9 +336,27 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     unsigned ph = (it / kStages) & 1u;
                     ok = mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag, args.err);
                     if (!ok) break;
-                    unsigned char *sa = tiles + s * Cfg<BN>::kStageBytes, *sb = sa + kABytes;
-                    mbar_expect_tx(&full_bar[s], kABytes + kBBytes);
+                    unsigned char *sa = tiles + s * C::kStageBytes, *sb = sa + kABytes;
                     int k0 = kb * BK;
+                    if (PAIR) {
+                        // the leader's barrier counts the bytes of both CTAs' loads of this stage
+                        if (crank == 0) mbar_expect_tx(&full_bar[s], 2 * (kABytes + kBBytes));
+                        if (!args.a_mn) {
+                            tma_load_2d_pair(sa, &map_a, &full_bar[s], k0, m0);
+                        } else {
+#pragma unroll
+                            for (int b = 0; b < BM / 64; ++b) tma_load_2d_pair(sa + b * 8192, &map_a, &full_bar[s], m0 + b * 64, k0);
+                        }
+                        if (!args.b_mn) {
+                            tma_load_2d_pair(sb, &map_b, &full_bar[s], k0, n0);
+                        } else {
+#pragma unroll
+                            for (int b = 0; b < C::kBRows / 64; ++b)
+                                tma_load_2d_pair(sb + b * 8192, &map_b, &full_bar[s], n0 + b * 64, k0);
+                        }
+                        continue;
+                    }
+                    mbar_expect_tx(&full_bar[s], kABytes + kBBytes);
                     if (!args.a_mn) {
                         tma_load_2d(sa, &map_a, &full_bar[s], k0, m0);
                     } else {
@@ -234,15 +379,21 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 if (filled == 0) continue;
                 if (!mbar_wait(&empty_bar[s], (filled - 1) & 1u, abort_flag, args.err)) break;
             }
+            if (*abort_flag) {
+                // gave up: let copies that are still in flight land before this CTA can exit
+                unsigned long long t0 = global_ns();
+                while (global_ns() - t0 < 200000ull) {
+                }
+            }
         }
     } else if (warp == 1) {
-        // ---------------------------------------------------------------- MMA issuer
-        if (lane == 0) {
+        // ---------------------------------------------------------------- MMA issuer (the leader, in a pair)
+        if (lane == 0 && crank == 0) {
             unsigned it = 0, tile_it = 0;
             // descriptor geometry per operand
             unsigned a_lbo = args.a_mn ? 8192u : 16u, a_sbo = 1024u, a_kstep = args.a_mn ? 2048u : 32u;
             unsigned b_lbo = args.b_mn ? 8192u : 16u, b_sbo = 1024u, b_kstep = args.b_mn ? 2048u : 32u;
-            for (long long w = blockIdx.x; w < work_total; w += gridDim.x, ++tile_it) {
+            for (long long w = w_first; w < work_total; w += w_stride, ++tile_it) {
                 int split = (int)(w / tiles_mn);
                 int kb0 = split * args.kb_per_split;
                 int kb1 = min(kb0 + args.kb_per_split, args.kb_total);
@@ -258,35 +409,145 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     ok = mbar_wait(&full_bar[s], ph, abort_flag, args.err);
                     if (!ok) break;
                     tc_fence_after();
-                    unsigned sa = smem_u32(tiles + s * Cfg<BN>::kStageBytes), sb = sa + kABytes;
+                    unsigned sa = smem_u32(tiles + s * C::kStageBytes), sb = sa + kABytes;
 #pragma unroll
                     for (int j = 0; j < BK / 16; ++j) {
                         unsigned long long ad = make_desc(sa + j * a_kstep, a_lbo, a_sbo);
                         unsigned long long bd = make_desc(sb + j * b_kstep, b_lbo, b_sbo);
-                        tc_mma(tmem_d, ad, bd, args.idesc, (kb > kb0 || j > 0) ? 1u : 0u);
+                        if (PAIR) tc_mma_pair(tmem_d, ad, bd, args.idesc, (kb > kb0 || j > 0) ? 1u : 0u);
+                        else tc_mma(tmem_d, ad, bd, args.idesc, (kb > kb0 || j > 0) ? 1u : 0u);
                     }
-                    tc_commit(&empty_bar[s]); // frees the smem stage once these MMAs have read it
+                    // frees the smem stage (in both CTAs of a pair) once these MMAs have read it
+                    if (PAIR) tc_commit_pair(&empty_bar[s]);
+                    else tc_commit(&empty_bar[s]);
                 }
                 if (!ok) break;
-                tc_commit(&acc_full[acc]); // accumulator complete
+                // accumulator complete
+                if (PAIR) tc_commit_pair(&acc_full[acc]);
+                else tc_commit(&acc_full[acc]);
             }
         }
     } else {
         // ---------------------------------------------------------------- epilogue (warps 2..5)
         int q = warp & 3; // TMEM lane quarter this warp may access
         unsigned tile_it = 0;
-        for (long long w = blockIdx.x; w < work_total; w += gridDim.x, ++tile_it) {
+        StageRing rg;
+        rg.base = out_stage + q * 8192;
+        rg.issued = 0;
+        for (long long w = w_first; w < work_total; w += w_stride, ++tile_it) {
             long long t = w % tiles_mn;
             int split = (int)(w / tiles_mn);
             int kb0 = split * args.kb_per_split;
             bool has_k = kb0 < args.kb_total;
-            long long m0 = (t % args.m_tiles) * BM, n0 = (t / args.m_tiles) * (long long)BN;
+            // a pair's CTA holds its own 128 rows of the 256-row tile in its TMEM lanes, all BN columns
+            long long m0 = (t % args.m_tiles) * kTileM + (long long)crank * BM, n0 = (t / args.m_tiles) * (long long)BN;
             int acc = tile_it & 1;
             unsigned acc_ph = (tile_it >> 1) & 1u;
             if (!mbar_wait(&acc_full[acc], acc_ph, abort_flag, args.err)) break;
             tc_fence_after();
             long long row = m0 + q * 32 + lane;
             bool add_bias = args.bias != nullptr && split == 0;
+            if (args.tma_out) {
+                // ---- staged output: rows of this warp's 32-row slab go out as 128-byte swizzled boxes
+                const int y0 = (int)(m0 + q * 32);
+                const bool live = has_k && (long long)y0 < args.m;
+                if (args.out_bf16) {
+#pragma unroll 1
+                    for (int c0 = 0; c0 < BN; c0 += 64) {
+                        unsigned r0[32], r1[32];
+                        unsigned taddr = tmem_base + ((unsigned)(q * 32) << 16) + (unsigned)(acc * BN + c0);
+                        tmem_ld32(taddr, r0);
+                        tmem_ld32(taddr + 32u, r1);
+                        tmem_ld_wait();
+                        long long col0 = n0 + c0;
+                        if (!live || col0 >= args.n) continue;
+                        float v[64];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            v[j] = __uint_as_float(r0[j]);
+                            v[32 + j] = __uint_as_float(r1[j]);
+                        }
+                        if (add_bias) {
+                            if (args.bias_vec && col0 + 64 <= args.n) {
+                                const float4 *bp = (const float4 *)(args.bias + col0); // col0 is a multiple of 64
+#pragma unroll
+                                for (int j = 0; j < 16; ++j) {
+                                    float4 b4 = __ldg(bp + j);
+                                    v[4 * j] += b4.x; v[4 * j + 1] += b4.y; v[4 * j + 2] += b4.z; v[4 * j + 3] += b4.w;
+                                }
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 64; ++j)
+                                    if (col0 + j < args.n) v[j] += args.bias[col0 + j];
+                            }
+                        }
+                        if (args.d_pre) {
+                            unsigned char *box = ring_acquire(rg, lane);
+#pragma unroll
+                            for (int j = 0; j < 8; ++j)
+                                ring_put(box, lane, j,
+                                         make_uint4(pack_bf16(v[8 * j], v[8 * j + 1]), pack_bf16(v[8 * j + 2], v[8 * j + 3]),
+                                                    pack_bf16(v[8 * j + 4], v[8 * j + 5]), pack_bf16(v[8 * j + 6], v[8 * j + 7])));
+                            ring_submit(rg, box, &map_pre, (int)col0, y0, false, lane);
+                        }
+                        if (args.act == MCB_ACT_GELU) {
+#pragma unroll
+                            for (int j = 0; j < 64; ++j) v[j] = gelu_f(v[j]);
+                        } else if (args.act == MCB_ACT_RELU) {
+#pragma unroll
+                            for (int j = 0; j < 64; ++j) v[j] = v[j] > 0.0f ? v[j] : 0.0f;
+                        }
+                        unsigned char *box = ring_acquire(rg, lane);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            ring_put(box, lane, j,
+                                     make_uint4(pack_bf16(v[8 * j], v[8 * j + 1]), pack_bf16(v[8 * j + 2], v[8 * j + 3]),
+                                                pack_bf16(v[8 * j + 4], v[8 * j + 5]), pack_bf16(v[8 * j + 6], v[8 * j + 7])));
+                        ring_submit(rg, box, &map_d, (int)col0, y0, false, lane);
+                    }
+                } else {
+#pragma unroll 1
+                    for (int c0 = 0; c0 < BN; c0 += 32) {
+                        unsigned r[32];
+                        unsigned taddr = tmem_base + ((unsigned)(q * 32) << 16) + (unsigned)(acc * BN + c0);
+                        tmem_ld32(taddr, r);
+                        tmem_ld_wait();
+                        long long col0 = n0 + c0;
+                        if (!live || col0 >= args.n) continue;
+                        float v[32];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+                        if (add_bias) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (col0 + j < args.n) v[j] += args.bias[col0 + j];
+                        }
+                        if (!args.accumulate) {
+                            if (args.act == MCB_ACT_GELU) {
+#pragma unroll
+                                for (int j = 0; j < 32; ++j) v[j] = gelu_f(v[j]);
+                            } else if (args.act == MCB_ACT_RELU) {
+#pragma unroll
+                                for (int j = 0; j < 32; ++j) v[j] = v[j] > 0.0f ? v[j] : 0.0f;
+                            }
+                        }
+                        unsigned char *box = ring_acquire(rg, lane);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            ring_put(box, lane, j,
+                                     make_uint4(__float_as_uint(v[4 * j]), __float_as_uint(v[4 * j + 1]), __float_as_uint(v[4 * j + 2]),
+                                                __float_as_uint(v[4 * j + 3])));
+                        ring_submit(rg, box, &map_d, (int)col0, y0, args.accumulate != 0, lane);
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    if (PAIR) mbar_arrive_leader(&acc_empty[acc]);
+                    else mbar_arrive(&acc_empty[acc]);
+                }
+                continue;
+            }
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 unsigned r[32];
@@ -377,12 +638,24 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&acc_empty[acc]);
+            if (lane == 0) {
+                if (PAIR) mbar_arrive_leader(&acc_empty[acc]);
+                else mbar_arrive(&acc_empty[acc]);
+            }
         }
+        // output boxes still being read from this CTA's shared memory must be done before it exits
+        if (lane == 0) bulk_wait_all();
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 1) tmem_dealloc(tmem_base, 512);
+    if (PAIR) {
+        // neither CTA may exit (or free the shared TMEM allocation) while its peer can still signal
+        // its barriers or while the leader's MMAs can still read its operand tiles
+        cluster_sync_all();
+        if (warp == 1) tmem_dealloc_pair(tmem_base, 512);
+    } else if (warp == 1) {
+        tmem_dealloc(tmem_base, 512);
+    }
 }
 
 // ------------------------------------------------------------------ host side
@@ -420,11 +693,29 @@ mcb_status make_map(mcb_ctx *ctx, CUtensorMap *map, const void *base, long long 
     return MCB_OK;
 }
 
-template <int BN> mcb_status launch(mcb_ctx *ctx, const TcGemmParams &p) {
+// output matrix [m, n] with row pitch ldd, written in boxes of {128 bytes, 32 rows}
+mcb_status make_out_map(mcb_ctx *ctx, CUtensorMap *map, const void *base, bool bf16, long long n, long long m, long long ldd) {
+    EncodeTiledFn enc = get_encode();
+    if (!enc) return mcb_fail(ctx, MCB_BACKEND, "cuTensorMapEncodeTiled is not available from the driver");
+    const int es = bf16 ? 2 : 4;
+    cuuint64_t dims[2] = {(cuuint64_t)n, (cuuint64_t)m};
+    cuuint64_t strides[1] = {(cuuint64_t)ldd * es};
+    cuuint32_t box[2] = {(cuuint32_t)(128 / es), 32u};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void *>(base), dims,
+                     strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return mcb_fail(ctx, MCB_BACKEND, "cuTensorMapEncodeTiled (output) failed with %d", (int)r);
+    return MCB_OK;
+}
+
+template <int BN, bool PAIR> mcb_status launch(mcb_ctx *ctx, const TcGemmParams &p) {
+    using C = Cfg<BN, PAIR>;
+    constexpr int kTileM = PAIR ? 2 * BM : BM;
     CUtensorMap map_a, map_b;
     if (!p.a_mn_major) MCB_TRY(make_map(ctx, &map_a, p.a, p.k, p.m, p.lda, BK, BM));
     else MCB_TRY(make_map(ctx, &map_a, p.a, p.m, p.k, p.lda, 64, BK));
-    if (!p.b_mn_major) MCB_TRY(make_map(ctx, &map_b, p.b, p.k, p.n, p.ldb, BK, BN));
+    if (!p.b_mn_major) MCB_TRY(make_map(ctx, &map_b, p.b, p.k, p.n, p.ldb, BK, C::kBRows));
     else MCB_TRY(make_map(ctx, &map_b, p.b, p.n, p.k, p.ldb, 64, BK));
     TcArgs a;
     a.d = p.d;
@@ -438,8 +729,8 @@ template <int BN> mcb_status launch(mcb_ctx *ctx, const TcGemmParams &p) {
     a.a_mn = p.a_mn_major;
     a.b_mn = p.b_mn_major;
     a.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(p.a_mn_major ? 1 : 0) << 15) |
-              ((unsigned)(p.b_mn_major ? 1 : 0) << 16) | ((unsigned)(BN >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
-    a.m_tiles = (int)((p.m + BM - 1) / BM);
+              ((unsigned)(p.b_mn_major ? 1 : 0) << 16) | ((unsigned)(BN >> 3) << 17) | ((unsigned)(kTileM >> 4) << 24);
+    a.m_tiles = (int)((p.m + kTileM - 1) / kTileM);
     a.n_tiles = (int)((p.n + BN - 1) / BN);
     a.kb_total = (int)((p.k + BK - 1) / BK);
     int split = p.split_k < 1 ? 1 : p.split_k;
@@ -448,14 +739,62 @@ template <int BN> mcb_status launch(mcb_ctx *ctx, const TcGemmParams &p) {
     split = a.kb_total > 0 ? (a.kb_total + a.kb_per_split - 1) / a.kb_per_split : 1;
     a.split_k = split;
     a.err = ctx->d_err;
+    a.bias_vec = p.bias && mcb_aligned16(p.bias);
+    // TMA output needs a 16-byte aligned base and row pitch; only an accumulating f32 output may lack them
+    a.tma_out = mcb_aligned16(p.d) && (p.ldd * (a.out_bf16 ? 2 : 4)) % 16 == 0 && (!p.d_pre || mcb_aligned16(p.d_pre));
+    static const bool no_tma_out = getenv("MCB_TC_DIRECT_OUT") != nullptr; // tuning knob: per-lane global stores
+    if (no_tma_out) a.tma_out = 0;
+    CUtensorMap map_d, map_pre;
+    memset(&map_d, 0, sizeof(map_d));
+    memset(&map_pre, 0, sizeof(map_pre));
+    if (a.tma_out) {
+        MCB_TRY(make_out_map(ctx, &map_d, p.d, a.out_bf16, p.n, p.m, p.ldd));
+        if (p.d_pre) MCB_TRY(make_out_map(ctx, &map_pre, p.d_pre, a.out_bf16, p.n, p.m, p.ldd));
+    }
     long long work = (long long)a.m_tiles * a.n_tiles * split;
-    int grid = (int)(work < ctx->sm_count ? work : ctx->sm_count);
     static bool attr_set = false;
+    static int max_pairs = 0;
     if (!attr_set) {
-        MCB_CUDA(ctx, cudaFuncSetAttribute(tc_gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::kSmemBytes));
+        MCB_CUDA(ctx, cudaFuncSetAttribute(tc_gemm_kernel<BN, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
+        if (PAIR) {
+            // how many 2-CTA clusters can be resident at once (GPCs with an odd SM count leave one SM idle)
+            cudaLaunchConfig_t qc = {};
+            qc.gridDim = dim3(ctx->sm_count & ~1);
+            qc.blockDim = dim3(kThreads);
+            qc.dynamicSmemBytes = C::kSmemBytes;
+            cudaLaunchAttribute qa[1];
+            qa[0].id = cudaLaunchAttributeClusterDimension;
+            qa[0].val.clusterDim.x = 2;
+            qa[0].val.clusterDim.y = 1;
+            qa[0].val.clusterDim.z = 1;
+            qc.attrs = qa;
+            qc.numAttrs = 1;
+            int nc = 0;
+            MCB_CUDA(ctx, cudaOccupancyMaxActiveClusters(&nc, tc_gemm_kernel<BN, PAIR>, &qc));
+            max_pairs = nc > 0 ? nc : 1;
+            if (max_pairs > ctx->sm_count / 2) max_pairs = ctx->sm_count / 2;
+        }
         attr_set = true;
     }
-    tc_gemm_kernel<BN><<<grid, kThreads, Cfg<BN>::kSmemBytes, ctx->stream>>>(map_a, map_b, a);
+    if (!PAIR) {
+        int grid = (int)(work < ctx->sm_count ? work : ctx->sm_count);
+        tc_gemm_kernel<BN, false><<<grid, kThreads, C::kSmemBytes, ctx->stream>>>(map_a, map_b, map_d, map_pre, a);
+    } else {
+        int pairs = (int)(work < max_pairs ? work : max_pairs);
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2 * pairs);
+        cfg.blockDim = dim3(kThreads);
+        cfg.dynamicSmemBytes = C::kSmemBytes;
+        cfg.stream = ctx->stream;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeClusterDimension;
+        at[0].val.clusterDim.x = 2;
+        at[0].val.clusterDim.y = 1;
+        at[0].val.clusterDim.z = 1;
+        cfg.attrs = at;
+        cfg.numAttrs = 1;
+        MCB_CUDA(ctx, cudaLaunchKernelEx(&cfg, tc_gemm_kernel<BN, true>, map_a, map_b, map_d, map_pre, a));
+    }
     MCB_LAUNCHED(ctx);
     return MCB_OK;
 }
@@ -486,9 +825,17 @@ mcb_status mcb_tc_gemm(mcb_ctx *ctx, const TcGemmParams &p) {
     }
     TcGemmParams q = p;
     q.split_k = split;
-    if (bn == 256) return launch<256>(ctx, q);
-    if (bn == 192) return launch<192>(ctx, q);
-    return launch<128>(ctx, q);
+    int pair = p.pair;
+    if (const char *force = getenv("MCB_TC_PAIR")) pair = atoi(force); // tuning knob: 0 single CTA, 1 CTA pair
+    if (pair < 0) pair = (bn != 192 && p.m > 128) ? 1 : 0;
+    if (bn == 192) pair = 0; // half of 192 columns is not a whole number of 64-column boxes
+    if (pair) {
+        if (bn == 256) return launch<256, true>(ctx, q);
+        return launch<128, true>(ctx, q);
+    }
+    if (bn == 256) return launch<256, false>(ctx, q);
+    if (bn == 192) return launch<192, false>(ctx, q);
+    return launch<128, false>(ctx, q);
 }
 
 // Picks the tile width (and, when the caller can zero the output and accept atomic accumulation,

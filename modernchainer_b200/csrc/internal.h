@@ -32,6 +32,7 @@ struct TcGemmParams {
     int accumulate = 0;
     int split_k = 1;
     int bn = 0; // tile width 128 / 192 / 256, 0 = choose
+    int pair = -1; // 1 = two CTAs share a 256-row tile (cta_group::2), 0 = one CTA per 128-row tile, -1 = choose
     int act = MCB_ACT_NONE;
     void *d_pre = nullptr; // optional second output: value before the activation (same dtype/ld as d)
 };
