@@ -354,7 +354,19 @@ def run_gemm(args, dist, mc, ctx, pk):
     ctx.record(e1)
     ms = ctx.elapsed_ms(e0, e1) / args.steps
     tf = 2.0 * m * n * k / (ms / 1e3) / 1e12
+    # the same loop once more beside the device-side clock sampler: the SM clock these launches really ran at
+    import ctypes as C
+    dur_us = int(ms * 1e3 * args.steps * 1.2) + 300
+    ctx.check(lib.mcb_clock_trace_start(ctx.h, dur_us, max(10, dur_us // 100)))
+    for _ in range(args.steps):
+        run()
+    mhz = (C.c_double * 256)()
+    cnt = C.c_int32(0)
+    ctx.check(lib.mcb_clock_trace_read(ctx.h, mhz, 256, C.byref(cnt)))
+    tr = sorted(mhz[i] for i in range(cnt.value))
+    trace = {"median": tr[len(tr) // 2], "min": tr[0], "max": tr[-1], "samples": len(tr)} if tr else None
     return {"metric": "bf16 GEMM TFLOP/s", "value": tf, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "sm_mhz_trace": trace,
             "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": f"gemm m={m} n={n} k={k} a_mn={a_mn} b_mn={b_mn}"}, "gpu_launches": args.steps,
             "roofline": {"bound": "tensor", "kernel": "tc_gemm_kernel", "achieved": tf, "peak": pk["tf_burst"], "unit": "TFLOP/s",

@@ -109,6 +109,13 @@ enum { MCB_PROF_GEMM_TC = 0, MCB_PROF_GEMM_F32 = 1, MCB_PROF_ATTENTION = 2, MCB_
 mcb_status mcb_prof_enable(mcb_ctx *ctx, int32_t on); /* enabling also clears earlier records */
 mcb_status mcb_prof_read(mcb_ctx *ctx, int32_t klass, int64_t *launches_out, double *ms_out, double *flops_out,
                          double *bytes_out);
+/* SM clock trace for benchmarks (no counterpart in the reference).  _start launches a one-thread
+ * sampler on a stream of its own that records (wall-clock ns, SM cycle counter) every interval_us
+ * for duration_us (at most 5 s) and then ends by itself; kernels launched meanwhile on the
+ * context's stream run beside it.  _read waits for the sampler and returns the SM clock in MHz
+ * between consecutive samples (up to max_out values). */
+mcb_status mcb_clock_trace_start(mcb_ctx *ctx, int32_t duration_us, int32_t interval_us);
+mcb_status mcb_clock_trace_read(mcb_ctx *ctx, double *mhz_out, int32_t max_out, int32_t *n_out);
 /* CudaBackend::set_compute_type, backend.rs:489-497 */
 mcb_status mcb_set_compute_type(mcb_ctx *ctx, int32_t compute);
 

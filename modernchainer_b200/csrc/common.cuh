@@ -46,6 +46,10 @@ struct mcb_ctx {
     };
     std::vector<ProfRec> prof;
     std::vector<cudaEvent_t> ev_pool;
+    // SM clock trace (mcb_clock_trace_*): a one-thread sampler kernel on its own stream
+    cudaStream_t trace_stream = nullptr;
+    unsigned long long *trace_buf = nullptr; // [0] = samples written, then (globaltimer ns, clock64) pairs
+    int trace_cap = 0;
 };
 
 // RAII timing scope: when profiling is on, brackets the launches made inside it with events

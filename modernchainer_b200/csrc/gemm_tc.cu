@@ -9,10 +9,14 @@
 // so fprop (x W^T), dgrad (g W) and wgrad (g^T x) all read the tensors where they lie; no
 // transposed copy is ever made.
 //
-// CTA layout (192 threads): warp 0 issues TMA, warp 1 issues MMA and owns the TMEM
-// allocation, warps 2..5 drain the accumulator (one TMEM lane quarter each) and write D.
-// Two accumulators (2 x BN columns of TMEM) let the epilogue of tile i overlap the MMAs of
-// tile i+1.  A 4..6-deep smem ring decouples TMA from MMA.
+// CTA layout (224 threads): warp 0 issues the TMA copies of A and warp 6 those of B, warp 1
+// issues MMA and owns the TMEM allocation, warps 2..5 drain the accumulator (one TMEM lane
+// quarter each) and hand D to TMA in 128-byte-row boxes.  Two accumulators (2 x BN columns of
+// TMEM) let the epilogue of tile i overlap the MMAs of tile i+1.  A 4..8-deep smem ring
+// decouples TMA from MMA.  Each of the single-thread roles is latency-bound on its own
+// instruction stream (a runtime division in the MMA loop alone cost 20% of the tensor rate),
+// so their loops carry ring counters instead of dividing and the copies are split over two
+// threads.  Optionally two CTAs of a cluster pair up on one 256-row tile (cta_group::2).
 //
 // Every wait on an mbarrier is bounded by wall time; on expiry the CTA raises the device
 // error word, stops issuing work, and still frees its TMEM before returning.
@@ -27,7 +31,7 @@ namespace {
 
 constexpr int BM = 128;
 constexpr int BK = 64; // 64 bf16 = one 128-byte swizzle row
-constexpr int kThreads = 192;
+constexpr int kThreads = 224;
 constexpr unsigned long long kWaitLimitNs = 2000000000ull; // 2 s
 
 struct TcArgs {
@@ -41,6 +45,7 @@ struct TcArgs {
     int a_mn, b_mn;
     unsigned idesc;
     int m_tiles, n_tiles, kb_total, kb_per_split;
+    int stages; // depth of the operand ring actually used (tuning knob; at most the compiled depth)
     unsigned int *err;
 };
 
@@ -71,12 +76,13 @@ __device__ __forceinline__ unsigned long long global_ns() {
 }
 // bounded wait; returns false after the time limit or once another role aborted
 __device__ __forceinline__ bool mbar_wait(unsigned long long *bar, unsigned parity, volatile int *abort_flag,
-                                          unsigned int *err) {
+                                          unsigned int *err, unsigned sleep_ns = 0) {
     if (mbar_test(bar, parity)) return true;
     unsigned long long t0 = global_ns();
     unsigned spins = 0;
     for (;;) {
         if (mbar_test(bar, parity)) return true;
+        if (sleep_ns) __nanosleep(sleep_ns); // waits a whole tile long: leave the issue slots to the MMA warp
         if ((++spins & 63u) == 0) {
             if (*abort_flag) return false;
             if (global_ns() - t0 > kWaitLimitNs) {
@@ -163,6 +169,39 @@ __device__ __forceinline__ void tc_mma_pair(unsigned tmem_d, unsigned long long 
                  :
                  : "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
                  : "memory");
+}
+// forms for the MMA issue loop: descriptors as (low, high) words, barriers as shared-space addresses
+template <bool PAIR>
+__device__ __forceinline__ void tc_mma_words(unsigned tmem_d, unsigned a_lo, unsigned a_hi, unsigned b_lo, unsigned b_hi, unsigned idesc,
+                                             unsigned accumulate) {
+    if (PAIR)
+        asm volatile("{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %6, 0;\n\tmov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
+                     "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, p;\n\t}"
+                     :
+                     : "r"(tmem_d), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+                     : "memory");
+    else
+        asm volatile("{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %6, 0;\n\tmov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
+                     "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}"
+                     :
+                     : "r"(tmem_d), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+                     : "memory");
+}
+template <bool PAIR> __device__ __forceinline__ void tc_commit_addr(unsigned bar_addr) {
+    if (PAIR)
+        asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar_addr),
+                     "h"((unsigned short)3)
+                     : "memory");
+    else
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_addr) : "memory");
+}
+__device__ __forceinline__ bool mbar_test_addr(unsigned bar_addr, unsigned parity) {
+    unsigned ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok)
+                 : "r"(bar_addr), "r"(parity)
+                 : "memory");
+    return ok != 0;
 }
 __device__ __forceinline__ void tmem_ld32(unsigned taddr, unsigned (&r)[32]) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -286,12 +325,15 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // rank inside the pair (0 = leader: arms the full barriers and issues the MMAs) and the
     // persistent work stride: one work item per CTA, or per pair
     const unsigned crank = PAIR ? cluster_rank() : 0u;
-    const long long w_first = PAIR ? (long long)(blockIdx.x >> 1) : (long long)blockIdx.x;
-    const long long w_stride = PAIR ? (long long)(gridDim.x >> 1) : (long long)gridDim.x;
+    // 32-bit work indices (the host checks the item count): a 64-bit division per tile in a
+    // single-thread role is hundreds of cycles of pipeline bubble
+    const unsigned w_first = PAIR ? (blockIdx.x >> 1) : blockIdx.x;
+    const unsigned w_stride = PAIR ? (gridDim.x >> 1) : gridDim.x;
     constexpr int kTileM = PAIR ? 2 * BM : BM;
+    const unsigned nst = (unsigned)args.stages; // ring depth in use, <= kStages
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
-            mbar_init(&full_bar[s], 1);
+            mbar_init(&full_bar[s], 2); // one arming arrival per operand producer
             mbar_init(&empty_bar[s], 1);
         }
         for (int a = 0; a < 2; ++a) {
@@ -316,68 +358,68 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     tc_fence_after();
     unsigned tmem_base = *tmem_slot;
 
-    long long tiles_mn = (long long)args.m_tiles * args.n_tiles;
-    long long work_total = tiles_mn * args.split_k;
+    const unsigned tiles_mn = (unsigned)args.m_tiles * (unsigned)args.n_tiles;
+    const unsigned work_total = tiles_mn * (unsigned)args.split_k;
+    const unsigned m_tiles = (unsigned)args.m_tiles;
+    const bool one_split = args.split_k == 1;
 
-    if (warp == 0) {
-        // ---------------------------------------------------------------- TMA producer
+    if (warp == 0 || warp == 6) {
+        // ---------------------------------------------------------------- TMA producers
+        // Two single-thread producers, one per operand (warp 0: A, warp 6: B), so that the serial
+        // cost of waiting, arming and issuing copies is split over two instruction streams; each
+        // arms the full barrier with its own operand's bytes.
         if (lane == 0) {
+            const bool is_a = (warp == 0);
+            const CUtensorMap *map = is_a ? &map_a : &map_b;
+            const bool mn = is_a ? (args.a_mn != 0) : (args.b_mn != 0);
+            const int rows = is_a ? BM : C::kBRows;            // operand rows staged per CTA
+            const unsigned bytes = (unsigned)rows * BK * 2u;
+            const unsigned tile_off = is_a ? 0u : (unsigned)kABytes;
             unsigned it = 0;
-            for (long long w = w_first; w < work_total; w += w_stride) {
-                long long t = w % tiles_mn;
-                int split = (int)(w / tiles_mn);
-                int m0 = (int)(t % args.m_tiles) * kTileM + (int)crank * BM;
-                int n0 = (int)(t / args.m_tiles) * BN + (int)crank * (PAIR ? BN / 2 : 0);
+            int s = 0;
+            unsigned ph = 0;
+            bool ok = true;
+            for (unsigned w = w_first; w < work_total && ok; w += w_stride) {
+                int split = one_split ? 0 : (int)(w / tiles_mn);
+                unsigned t = w - (unsigned)split * tiles_mn;
+                const unsigned tn = t / m_tiles, tm = t - tn * m_tiles;
+                int r0 = is_a ? (int)tm * kTileM + (int)crank * BM : (int)tn * BN + (int)crank * (PAIR ? BN / 2 : 0);
                 int kb0 = split * args.kb_per_split;
                 int kb1 = min(kb0 + args.kb_per_split, args.kb_total);
-                bool ok = true;
-                for (int kb = kb0; kb < kb1 && ok; ++kb, ++it) {
-                    int s = it % kStages;
-                    unsigned ph = (it / kStages) & 1u;
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     ok = mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag, args.err);
                     if (!ok) break;
-                    unsigned char *sa = tiles + s * C::kStageBytes, *sb = sa + kABytes;
+                    unsigned char *dst = tiles + s * C::kStageBytes + tile_off;
+                    unsigned long long *fb = &full_bar[s];
                     int k0 = kb * BK;
                     if (PAIR) {
-                        // the leader's barrier counts the bytes of both CTAs' loads of this stage
-                        if (crank == 0) mbar_expect_tx(&full_bar[s], 2 * (kABytes + kBBytes));
-                        if (!args.a_mn) {
-                            tma_load_2d_pair(sa, &map_a, &full_bar[s], k0, m0);
+                        // the leader's barrier counts the bytes of both CTAs' copies of this operand
+                        if (crank == 0) mbar_expect_tx(fb, 2u * bytes);
+                        if (!mn) {
+                            tma_load_2d_pair(dst, map, fb, k0, r0);
                         } else {
-#pragma unroll
-                            for (int b = 0; b < BM / 64; ++b) tma_load_2d_pair(sa + b * 8192, &map_a, &full_bar[s], m0 + b * 64, k0);
+                            for (int b = 0; b < rows / 64; ++b) tma_load_2d_pair(dst + b * 8192, map, fb, r0 + b * 64, k0);
                         }
-                        if (!args.b_mn) {
-                            tma_load_2d_pair(sb, &map_b, &full_bar[s], k0, n0);
+                    } else {
+                        mbar_expect_tx(fb, bytes);
+                        if (!mn) {
+                            tma_load_2d(dst, map, fb, k0, r0);
                         } else {
-#pragma unroll
-                            for (int b = 0; b < C::kBRows / 64; ++b)
-                                tma_load_2d_pair(sb + b * 8192, &map_b, &full_bar[s], n0 + b * 64, k0);
+                            for (int b = 0; b < rows / 64; ++b) tma_load_2d(dst + b * 8192, map, fb, r0 + b * 64, k0);
                         }
-                        continue;
                     }
-                    mbar_expect_tx(&full_bar[s], kABytes + kBBytes);
-                    if (!args.a_mn) {
-                        tma_load_2d(sa, &map_a, &full_bar[s], k0, m0);
-                    } else {
-#pragma unroll
-                        for (int b = 0; b < BM / 64; ++b) tma_load_2d(sa + b * 8192, &map_a, &full_bar[s], m0 + b * 64, k0);
-                    }
-                    if (!args.b_mn) {
-                        tma_load_2d(sb, &map_b, &full_bar[s], k0, n0);
-                    } else {
-#pragma unroll
-                        for (int b = 0; b < BN / 64; ++b) tma_load_2d(sb + b * 8192, &map_b, &full_bar[s], n0 + b * 64, k0);
+                    if (++s == (int)nst) {
+                        s = 0;
+                        ph ^= 1u;
                     }
                 }
-                if (!ok) break;
             }
-            // drain: wait until every load that was issued has been consumed (bounded), so no
-            // copy is still writing this CTA's shared memory when it exits
-            for (int s = 0; s < kStages; ++s) {
-                unsigned filled = (it > (unsigned)s) ? ((it - 1 - s) / kStages + 1) : 0; // times stage s was filled
+            // drain: wait until every copy that was issued has been consumed (bounded), so none
+            // is still writing this CTA's shared memory when it exits
+            for (int d = 0; d < (int)nst; ++d) {
+                unsigned filled = (it > (unsigned)d) ? ((it - 1 - d) / nst + 1) : 0; // times stage d was filled
                 if (filled == 0) continue;
-                if (!mbar_wait(&empty_bar[s], (filled - 1) & 1u, abort_flag, args.err)) break;
+                if (!mbar_wait(&empty_bar[d], (filled - 1) & 1u, abort_flag, args.err)) break;
             }
             if (*abort_flag) {
                 // gave up: let copies that are still in flight land before this CTA can exit
@@ -389,42 +431,57 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     } else if (warp == 1) {
         // ---------------------------------------------------------------- MMA issuer (the leader, in a pair)
         if (lane == 0 && crank == 0) {
-            unsigned it = 0, tile_it = 0;
-            // descriptor geometry per operand
-            unsigned a_lbo = args.a_mn ? 8192u : 16u, a_sbo = 1024u, a_kstep = args.a_mn ? 2048u : 32u;
-            unsigned b_lbo = args.b_mn ? 8192u : 16u, b_sbo = 1024u, b_kstep = args.b_mn ? 2048u : 32u;
-            for (long long w = w_first; w < work_total; w += w_stride, ++tile_it) {
-                int split = (int)(w / tiles_mn);
+            // This thread's instruction stream is the critical path: every instruction between two
+            // MMAs costs a few cycles of tensor-pipe idle time.  So the loop carries ready-made
+            // descriptor words and barrier addresses and only adds small offsets to them.
+            unsigned tile_it = 0;
+            unsigned a_lbo = args.a_mn ? 8192u : 16u, a_kinc = (args.a_mn ? 2048u : 32u) >> 4;
+            unsigned b_lbo = args.b_mn ? 8192u : 16u, b_kinc = (args.b_mn ? 2048u : 32u) >> 4;
+            const unsigned long long a_desc0 = make_desc(smem_u32(tiles), a_lbo, 1024u);
+            const unsigned long long b_desc0 = make_desc(smem_u32(tiles) + kABytes, b_lbo, 1024u);
+            // only the 14-bit start-address field changes (operands sit below 256 KB, so no carry)
+            const unsigned a_hi = (unsigned)(a_desc0 >> 32), b_hi = (unsigned)(b_desc0 >> 32);
+            const unsigned a_lo0 = (unsigned)a_desc0, b_lo0 = (unsigned)b_desc0;
+            constexpr unsigned kStageInc = (unsigned)C::kStageBytes >> 4;
+            const unsigned full0 = smem_u32(full_bar), empty0 = smem_u32(empty_bar);
+            const unsigned idesc = args.idesc;
+            unsigned s = 0, soff = 0, ph = 0;
+            bool ok = true;
+            for (unsigned w = w_first; w < work_total && ok; w += w_stride, ++tile_it) {
+                int split = one_split ? 0 : (int)(w / tiles_mn);
                 int kb0 = split * args.kb_per_split;
-                int kb1 = min(kb0 + args.kb_per_split, args.kb_total);
+                int nkb = min(kb0 + args.kb_per_split, args.kb_total) - kb0;
                 int acc = tile_it & 1;
                 unsigned acc_ph = (tile_it >> 1) & 1u;
                 if (!mbar_wait(&acc_empty[acc], acc_ph ^ 1u, abort_flag, args.err)) break;
                 tc_fence_after();
-                unsigned tmem_d = tmem_base + (unsigned)(acc * BN);
-                bool ok = true;
-                for (int kb = kb0; kb < kb1; ++kb, ++it) {
-                    int s = it % kStages;
-                    unsigned ph = (it / kStages) & 1u;
-                    ok = mbar_wait(&full_bar[s], ph, abort_flag, args.err);
-                    if (!ok) break;
-                    tc_fence_after();
-                    unsigned sa = smem_u32(tiles + s * C::kStageBytes), sb = sa + kABytes;
+                const unsigned tmem_d = tmem_base + (unsigned)(acc * BN);
+                unsigned accum = 0; // the first MMA of a tile overwrites the accumulator
+                for (int i = 0; i < nkb; ++i) {
+                    if (!mbar_test_addr(full0 + s * 8u, ph)) {
+                        ok = mbar_wait(&full_bar[s], ph, abort_flag, args.err);
+                        if (!ok) break;
+                    }
+                    const unsigned al = a_lo0 + soff, bl = b_lo0 + soff;
 #pragma unroll
                     for (int j = 0; j < BK / 16; ++j) {
-                        unsigned long long ad = make_desc(sa + j * a_kstep, a_lbo, a_sbo);
-                        unsigned long long bd = make_desc(sb + j * b_kstep, b_lbo, b_sbo);
-                        if (PAIR) tc_mma_pair(tmem_d, ad, bd, args.idesc, (kb > kb0 || j > 0) ? 1u : 0u);
-                        else tc_mma(tmem_d, ad, bd, args.idesc, (kb > kb0 || j > 0) ? 1u : 0u);
+                        if (PAIR) tc_mma_words<true>(tmem_d, al + j * a_kinc, a_hi, bl + j * b_kinc, b_hi, idesc, j == 0 ? accum : 1u);
+                        else tc_mma_words<false>(tmem_d, al + j * a_kinc, a_hi, bl + j * b_kinc, b_hi, idesc, j == 0 ? accum : 1u);
                     }
+                    accum = 1u;
                     // frees the smem stage (in both CTAs of a pair) once these MMAs have read it
-                    if (PAIR) tc_commit_pair(&empty_bar[s]);
-                    else tc_commit(&empty_bar[s]);
+                    tc_commit_addr<PAIR>(empty0 + s * 8u);
+                    if (++s == nst) {
+                        s = 0;
+                        soff = 0;
+                        ph ^= 1u;
+                    } else {
+                        soff += kStageInc;
+                    }
                 }
                 if (!ok) break;
                 // accumulator complete
-                if (PAIR) tc_commit_pair(&acc_full[acc]);
-                else tc_commit(&acc_full[acc]);
+                tc_commit_addr<PAIR>(smem_u32(&acc_full[acc]));
             }
         }
     } else {
@@ -434,16 +491,17 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         StageRing rg;
         rg.base = out_stage + q * 8192;
         rg.issued = 0;
-        for (long long w = w_first; w < work_total; w += w_stride, ++tile_it) {
-            long long t = w % tiles_mn;
-            int split = (int)(w / tiles_mn);
+        for (unsigned w = w_first; w < work_total; w += w_stride, ++tile_it) {
+            int split = one_split ? 0 : (int)(w / tiles_mn);
+            unsigned t = w - (unsigned)split * tiles_mn;
             int kb0 = split * args.kb_per_split;
             bool has_k = kb0 < args.kb_total;
             // a pair's CTA holds its own 128 rows of the 256-row tile in its TMEM lanes, all BN columns
-            long long m0 = (t % args.m_tiles) * kTileM + (long long)crank * BM, n0 = (t / args.m_tiles) * (long long)BN;
+            const unsigned tn = t / m_tiles, tm = t - tn * m_tiles;
+            long long m0 = (long long)tm * kTileM + (long long)crank * BM, n0 = (long long)tn * BN;
             int acc = tile_it & 1;
             unsigned acc_ph = (tile_it >> 1) & 1u;
-            if (!mbar_wait(&acc_full[acc], acc_ph, abort_flag, args.err)) break;
+            if (!mbar_wait(&acc_full[acc], acc_ph, abort_flag, args.err, 100u)) break;
             tc_fence_after();
             long long row = m0 + q * 32 + lane;
             bool add_bias = args.bias != nullptr && split == 0;
@@ -739,7 +797,14 @@ template <int BN, bool PAIR> mcb_status launch(mcb_ctx *ctx, const TcGemmParams 
     split = a.kb_total > 0 ? (a.kb_total + a.kb_per_split - 1) / a.kb_per_split : 1;
     a.split_k = split;
     a.err = ctx->d_err;
+    if ((long long)a.m_tiles * a.n_tiles * split >= (1ll << 31) || p.m >= (1ll << 31) || p.n >= (1ll << 31) || p.k >= (1ll << 31))
+        return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "tensor-core GEMM: dimensions beyond 2^31 are not supported");
     a.bias_vec = p.bias && mcb_aligned16(p.bias);
+    a.stages = C::kStages;
+    if (const char *st = getenv("MCB_TC_STAGES")) {
+        int v = atoi(st);
+        if (v >= 2 && v < C::kStages) a.stages = v;
+    }
     // TMA output needs a 16-byte aligned base and row pitch; only an accumulating f32 output may lack them
     a.tma_out = mcb_aligned16(p.d) && (p.ldd * (a.out_bf16 ? 2 : 4)) % 16 == 0 && (!p.d_pre || mcb_aligned16(p.d_pre));
     static const bool no_tma_out = getenv("MCB_TC_DIRECT_OUT") != nullptr; // tuning knob: per-lane global stores
@@ -840,8 +905,8 @@ mcb_status mcb_tc_gemm(mcb_ctx *ctx, const TcGemmParams &p) {
 
 // Picks the tile width (and, when the caller can zero the output and accept atomic accumulation,
 // the split of the reduction dimension) that minimises a cycle estimate for one CTA:
-//   waves * k_blocks_per_item * (2 * BN + 40)  +  exposed epilogue
-// where 2*BN is the issue time of the four K=16 MMAs of one 64-deep block at M=128.
+//   waves * k_blocks_per_item * (4 * max(BN/2, 125) + 60)  +  exposed epilogue
+// where the first term is the time of the four K=16 MMAs of one 64-deep block at M=128.
 void mcb_tc_plan(mcb_ctx *ctx, int64_t m, int64_t n, int64_t k, bool allow_split, bool atomic_out, int fixed_split, int *bn_out,
                  int *split_out) {
     const int cands[3] = {256, 192, 128};
@@ -861,7 +926,10 @@ void mcb_tc_plan(mcb_ctx *ctx, int64_t m, int64_t n, int64_t k, bool allow_split
             bool atomics = atomic_out || sp > 1;
             double epi = (atomics ? 12.0 : 5.0) * bn;
             // with several waves the epilogue of all but the last tile hides behind the next tile's MMAs
-            double cost = (double)waves * (double)kb * (2.0 * bn + 40.0) + epi + (sp > 1 ? 300.0 * sp : 0.0);
+            // one K=16 MMA at M=128 takes bn/2 cycles but never less than ~125 (the A operand's 4 KB
+            // leave shared memory at 32 B/clk), so narrow tiles run the tensor pipe below its rate
+            double mma = bn / 2.0 > 125.0 ? bn / 2.0 : 125.0;
+            double cost = (double)waves * (double)kb * (4.0 * mma + 60.0) + epi + (sp > 1 ? 300.0 * sp : 0.0);
             if (cost < best - 1e-9) {
                 best = cost;
                 best_bn = bn;

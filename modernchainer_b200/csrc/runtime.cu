@@ -31,6 +31,30 @@ static size_t round_size(size_t bytes) {
     return (bytes + (2u << 20) - 1) & ~size_t((2u << 20) - 1);
 }
 
+// One thread samples (wall-clock ns, SM cycle counter) every `interval_ns` for `duration_ns`
+// (both bounded by the host).  Consecutive samples give the SM clock that kernels running
+// beside it on other streams actually saw, at a far finer grain than driver polling.
+__global__ void clock_trace_kernel(unsigned long long *buf, int cap, unsigned long long duration_ns, unsigned long long interval_ns) {
+    unsigned long long t0, t, next;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
+    next = t0;
+    int n = 0;
+    for (;;) {
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+        if (t >= next) {
+            if (n < cap) {
+                buf[1 + 2 * n] = t;
+                buf[2 + 2 * n] = (unsigned long long)clock64();
+                ++n;
+            }
+            next += interval_ns;
+        }
+        if (t - t0 >= duration_ns || n >= cap) break;
+        __nanosleep(200);
+    }
+    buf[0] = (unsigned long long)n;
+}
+
 extern "C" {
 
 int32_t mcb_device_count(void) {
@@ -72,6 +96,11 @@ void mcb_ctx_destroy(mcb_ctx *ctx) {
     for (auto &kv : ctx->free_blocks) cudaFree(kv.second);
     for (auto &kv : ctx->live) cudaFree(kv.first);
     if (ctx->scratch) cudaFree(ctx->scratch);
+    if (ctx->trace_stream) {
+        cudaStreamSynchronize(ctx->trace_stream);
+        cudaStreamDestroy(ctx->trace_stream);
+    }
+    if (ctx->trace_buf) cudaFree(ctx->trace_buf);
     cudaFree(ctx->d_err);
     cudaStreamDestroy(ctx->stream);
     delete ctx;
@@ -234,6 +263,46 @@ mcb_status mcb_prof_read(mcb_ctx *ctx, int32_t klass, int64_t *launches_out, dou
     if (ms_out) *ms_out = ms;
     if (flops_out) *flops_out = fl;
     if (bytes_out) *bytes_out = by;
+    return MCB_OK;
+}
+
+mcb_status mcb_clock_trace_start(mcb_ctx *ctx, int32_t duration_us, int32_t interval_us) {
+    MCB_CHECK_CTX(ctx);
+    if (duration_us < 1 || duration_us > 5000000 || interval_us < 1)
+        return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "clock trace: duration 1..5000000 us and interval >= 1 us");
+    int cap = duration_us / interval_us + 2;
+    if (cap > 1 << 20) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "clock trace: more than 2^20 samples");
+    MCB_CUDA(ctx, cudaSetDevice(ctx->device));
+    if (!ctx->trace_stream) MCB_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->trace_stream, cudaStreamNonBlocking));
+    MCB_CUDA(ctx, cudaStreamSynchronize(ctx->trace_stream));
+    if (cap > ctx->trace_cap) {
+        if (ctx->trace_buf) cudaFree(ctx->trace_buf);
+        ctx->trace_buf = nullptr;
+        ctx->trace_cap = 0;
+        MCB_CUDA(ctx, cudaMalloc(&ctx->trace_buf, (size_t)(1 + 2 * cap) * sizeof(unsigned long long)));
+        ctx->trace_cap = cap;
+    }
+    MCB_CUDA(ctx, cudaMemsetAsync(ctx->trace_buf, 0, sizeof(unsigned long long), ctx->trace_stream));
+    clock_trace_kernel<<<1, 1, 0, ctx->trace_stream>>>(ctx->trace_buf, cap, (unsigned long long)duration_us * 1000ull,
+                                                      (unsigned long long)interval_us * 1000ull);
+    MCB_LAUNCHED(ctx);
+    return MCB_OK;
+}
+
+mcb_status mcb_clock_trace_read(mcb_ctx *ctx, double *mhz_out, int32_t max_out, int32_t *n_out) {
+    MCB_CHECK_CTX(ctx);
+    if (!ctx->trace_stream || !ctx->trace_buf) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "clock trace was not started");
+    MCB_CUDA(ctx, cudaStreamSynchronize(ctx->trace_stream));
+    std::vector<unsigned long long> h((size_t)1 + 2 * ctx->trace_cap);
+    MCB_CUDA(ctx, cudaMemcpy(h.data(), ctx->trace_buf, h.size() * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
+    int n = (int)h[0], w = 0;
+    for (int i = 1; i < n && w < max_out; ++i) {
+        unsigned long long dt = h[1 + 2 * i] - h[1 + 2 * (i - 1)], dc = h[2 + 2 * i] - h[2 + 2 * (i - 1)];
+        if (dt == 0) continue;
+        if (mhz_out) mhz_out[w] = (double)dc / (double)dt * 1000.0;
+        ++w;
+    }
+    if (n_out) *n_out = w;
     return MCB_OK;
 }
 
