@@ -122,6 +122,15 @@ static mcb_status grad_dst(const Var &v, Tensor *out, bool *direct) {
     return new_tensor(v->ctx, MCB_F32, v->data.shape, out);
 }
 
+// While a node's backward runs, the walker exposes, per input, the gradient that is already
+// waiting for that input if the walker holds its only reference.  An op that can add into such
+// a tensor in place returns it as the input's gradient and the walker skips its own fan-in add.
+static const std::vector<const Tensor *> *g_pending = nullptr;
+static const Tensor *pending_grad(size_t input) {
+    if (!g_pending || input >= g_pending->size()) return nullptr;
+    return (*g_pending)[input];
+}
+
 // ------------------------------------------------------------------ backward walker
 static mcb_status accumulate_leaf(const Var &v, const Tensor &g) {
     mcb_ctx *ctx = v->ctx;
@@ -200,7 +209,18 @@ mcb_status backward(const Var &root) {
             continue;
         }
         std::vector<Tensor> in_grads(v->node->inputs.size());
+        std::vector<const Tensor *> pending(v->node->inputs.size(), nullptr);
+        for (size_t i = 0; i < pending.size(); ++i) {
+            const Var &in = v->node->inputs[i];
+            if (!in->requires_grad || in.get() == v.get()) continue;
+            bool repeated = false; // the same variable twice among the inputs: no in-place target
+            for (size_t j = 0; j < pending.size(); ++j) repeated |= (j != i && v->node->inputs[j].get() == in.get());
+            auto e = grads.find(in.get());
+            if (!repeated && e != grads.end() && e->second.buf && e->second.buf.use_count() == 1) pending[i] = &e->second;
+        }
+        g_pending = &pending;
         st = v->node->backward(g, in_grads);
+        g_pending = nullptr;
         if (st != MCB_OK) break;
         g = Tensor(); // drop our reference so a pending tensor can be uniquely owned
         for (size_t i = 0; i < in_grads.size(); ++i) {
@@ -212,6 +232,10 @@ mcb_status backward(const Var &root) {
                 continue;
             }
             Tensor &cur = e->second;
+            if (in_grads[i].ptr == cur.ptr && in_grads[i].buf == cur.buf) { // the op already added into the pending tensor
+                in_grads[i] = Tensor();
+                continue;
+            }
             Tensor add = in_grads[i];
             in_grads[i] = Tensor();
             if (cur.buf && cur.buf.use_count() == 1 && cur.dt == add.dt) {
@@ -279,6 +303,17 @@ static mcb_status like_input(mcb_ctx *ctx, const Tensor &g, const Var &in, Tenso
     int want = is_float(in->data.dt) ? in->data.dt : MCB_F32;
     return to_dtype(ctx, g, want, out);
 }
+// Same, except that an f32 gradient for the bf16 output of a Linear stays f32: that op's backward
+// rounds its incoming gradient to bf16 as its first step anyway (same values), and does so in the
+// pass that also produces the bias gradient, so rounding here would only add a kernel.
+static mcb_status like_input_lazy(mcb_ctx *ctx, const Tensor &g, const Var &in, Tensor *out) {
+    if (g.dt == MCB_F32 && in->data.dt == MCB_BF16 && in->node && !getenv("MCB_UNFUSED_BWD") &&
+        (!strcmp(in->node->name, "Linear") || !strcmp(in->node->name, "LinearActivation"))) {
+        *out = g;
+        return MCB_OK;
+    }
+    return like_input(ctx, g, in, out);
+}
 
 mcb_status f_binary(int op, const Var &a, const Var &b, Var *out) {
     MCB_TRY(check_same_ctx(a, b));
@@ -304,7 +339,7 @@ mcb_status f_binary(int op, const Var &a, const Var &b, Var *out) {
         if (op == MCB_ADD || op == MCB_SUB) {
             if (av->requires_grad) {
                 MCB_TRY(sum_to_shape(ctx, g, as, &ga));
-                MCB_TRY(like_input(ctx, ga, av, &gi[0]));
+                MCB_TRY(like_input_lazy(ctx, ga, av, &gi[0]));
             }
             if (bv->requires_grad) {
                 Tensor t = g;
@@ -314,7 +349,7 @@ mcb_status f_binary(int op, const Var &a, const Var &b, Var *out) {
                     MCB_TRY(scaled(ctx, gf, -1.0, &t));
                 }
                 MCB_TRY(sum_to_shape(ctx, t, bs, &gb));
-                MCB_TRY(like_input(ctx, gb, bv, &gi[1]));
+                MCB_TRY(like_input_lazy(ctx, gb, bv, &gi[1]));
             }
             return MCB_OK;
         }
@@ -524,11 +559,32 @@ static mcb_status linear_backward_impl(mcb_ctx *ctx, const Tensor &g_in, const L
     int64_t m = sv.x.numel() / sv.x.shape.back(), k = sv.x.shape.back(), n = w->data.shape[0];
     int gdt = sv.bf16 ? MCB_BF16 : MCB_F32;
     Tensor g;
-    MCB_TRY(to_dtype(ctx, g_in, gdt, &g));
+    // The bias gradient is the column sum of the bf16 gradient the GEMMs below read.  Whenever a
+    // pass over that gradient is needed anyway (a cast from f32, the activation's backward), the
+    // same pass leaves the column sums, and no separate reduction reads the matrix again.
+    const bool fuse = getenv("MCB_UNFUSED_BWD") == nullptr; // test knob: separate cast / activation-backward / column-sum kernels
+    const bool want_db = b && b->requires_grad;
+    bool db_done = false;
+    if (fuse && sv.bf16 && want_db && sv.act == MCB_ACT_NONE && g_in.dt == MCB_F32 && mcb_map_colsum_supported(g_in.ptr, nullptr, g_in.ptr, n)) {
+        bool direct;
+        MCB_TRY(grad_dst(b, &gi[2], &direct));
+        MCB_TRY(new_tensor(ctx, MCB_BF16, g_in.shape, &g));
+        MCB_TRY(mcb_map_colsum(ctx, 0, g_in.ptr, nullptr, g.ptr, m, n, (float *)gi[2].ptr));
+        db_done = true;
+    } else {
+        MCB_TRY(to_dtype(ctx, g_in, gdt, &g));
+    }
     if (sv.act != MCB_ACT_NONE) {
         Tensor gp;
         MCB_TRY(new_tensor(ctx, gdt, g.shape, &gp));
-        MCB_TRY((sv.act == MCB_ACT_GELU ? mcb_gelu_backward : mcb_relu_backward)(ctx, sv.pre.ptr, g.ptr, gp.ptr, g.numel(), gdt));
+        if (fuse && sv.bf16 && want_db && mcb_map_colsum_supported(sv.pre.ptr, g.ptr, gp.ptr, n)) {
+            bool direct;
+            MCB_TRY(grad_dst(b, &gi[2], &direct));
+            MCB_TRY(mcb_map_colsum(ctx, sv.act == MCB_ACT_GELU ? 1 : 2, sv.pre.ptr, g.ptr, gp.ptr, m, n, (float *)gi[2].ptr));
+            db_done = true;
+        } else {
+            MCB_TRY((sv.act == MCB_ACT_GELU ? mcb_gelu_backward : mcb_relu_backward)(ctx, sv.pre.ptr, g.ptr, gp.ptr, g.numel(), gdt));
+        }
         g = gp;
     }
     if (sv.bf16) {
@@ -577,7 +633,7 @@ static mcb_status linear_backward_impl(mcb_ctx *ctx, const Tensor &g_in, const L
             gi[0] = t;
         }
     }
-    if (b && b->requires_grad) {
+    if (want_db && !db_done) {
         bool direct;
         MCB_TRY(grad_dst(b, &gi[2], &direct));
         MCB_TRY(mcb_col_sum(ctx, g.ptr, gdt, m, n, (float *)gi[2].ptr));
@@ -719,9 +775,23 @@ mcb_status f_layer_norm(const Var &x, const Var &gamma, const Var &beta, double 
     *out = apply(ctx, "LayerNorm", res, {x, gamma, beta}, [ctx, xf, mean, rstd, xv, gv, bv, eps, rows, dim](const Tensor &g, std::vector<Tensor> &gi) -> mcb_status {
         Tensor dx, dg, db;
         bool d1, d2;
-        MCB_TRY(new_tensor(ctx, MCB_F32, xf.shape, &dx));
         MCB_TRY(grad_dst(gv, &dg, &d1));
         MCB_TRY(grad_dst(bv, &db, &d2));
+        // A gradient already waiting for x (the residual branch of a pre-norm block) takes dx in place
+        const Tensor *pend = getenv("MCB_UNFUSED_BWD") ? nullptr : pending_grad(0); // test knob: separate fan-in add
+        if (pend && pend->dt == MCB_F32 && xv->data.dt == MCB_F32 && pend->numel() == xf.numel()) {
+            mcb_status st = mcb_layer_norm_backward_ex(ctx, (const float *)xf.ptr, (const float *)gv->data.ptr, g.ptr, g.dt, eps,
+                                                       (const float *)mean.ptr, (const float *)rstd.ptr, (const float *)pend->ptr,
+                                                       (float *)pend->ptr, (float *)dg.ptr, (float *)db.ptr, rows, dim);
+            if (st != MCB_UNSUPPORTED) {
+                MCB_TRY(st);
+                gi[0] = *pend; // same storage: the walker sees that the sum is already in place
+                gi[1] = dg;
+                gi[2] = db;
+                return MCB_OK;
+            }
+        }
+        MCB_TRY(new_tensor(ctx, MCB_F32, xf.shape, &dx));
         MCB_TRY(mcb_layer_norm_backward(ctx, (const float *)xf.ptr, (const float *)gv->data.ptr, g.ptr, g.dt, eps, (const float *)mean.ptr,
                                         (const float *)rstd.ptr, (float *)dx.ptr, (float *)dg.ptr, (float *)db.ptr, rows, dim));
         MCB_TRY(like_input(ctx, dx, xv, &gi[0]));

@@ -226,6 +226,73 @@ mcb_status launch_map2(mcb_ctx *ctx, const void *x, const void *g, void *out, in
     return MCB_OK;
 }
 
+// ---- a bf16 [rows, cols] result and its column sums in one pass (the bias gradient of a Linear
+// is the column sum of exactly the bf16 gradient its GEMMs read, so both come from one read).
+//   MODE 0: out = bf16(a)            a f32            (cast of an f32 gradient)
+//   MODE 1: out = gelu'(a) * b       a = pre-activation, b = upstream gradient, both bf16
+//   MODE 2: out = relu'(a) * b
+// Lane l of a warp owns columns blockIdx.x*256 + 8l .. +7; the 8 warps of a block take rows
+// r0+w, r0+w+8, ...; partial[blockIdx.y][col] receives the block's sum of the ROUNDED outputs.
+template <int MODE>
+__global__ void __launch_bounds__(256) map_colsum_kernel(const void *__restrict__ a, const void *__restrict__ b,
+                                                         __nv_bfloat16 *__restrict__ out, long long rows, long long cols,
+                                                         float *__restrict__ partial) {
+    __shared__ float red[8][32][9];
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const long long col = (long long)blockIdx.x * 256 + lane * 8;
+    const long long rows_per = (rows + gridDim.y - 1) / gridDim.y;
+    const long long r0 = (long long)blockIdx.y * rows_per, r1 = r0 + rows_per < rows ? r0 + rows_per : rows;
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
+    if (col < cols) {
+#pragma unroll 2
+        for (long long r = r0 + w; r < r1; r += 8) {
+            const long long e = r * cols + col;
+            float v[8];
+            if (MODE == 0) {
+                const float4 *p = reinterpret_cast<const float4 *>((const float *)a + e);
+                float4 lo = p[0], hi = p[1];
+                v[0] = lo.x; v[1] = lo.y; v[2] = lo.z; v[3] = lo.w;
+                v[4] = hi.x; v[5] = hi.y; v[6] = hi.z; v[7] = hi.w;
+            } else {
+                uint4 xa = *reinterpret_cast<const uint4 *>((const __nv_bfloat16 *)a + e);
+                uint4 xb = *reinterpret_cast<const uint4 *>((const __nv_bfloat16 *)b + e);
+                const __nv_bfloat162 *pa = reinterpret_cast<const __nv_bfloat162 *>(&xa);
+                const __nv_bfloat162 *pb = reinterpret_cast<const __nv_bfloat162 *>(&xb);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    float2 fa = __bfloat1622float2(pa[j]), fb = __bfloat1622float2(pb[j]);
+                    v[2 * j] = MODE == 1 ? GeluB::f(fa.x, fb.x) : ReluB::f(fa.x, fb.x);
+                    v[2 * j + 1] = MODE == 1 ? GeluB::f(fa.y, fb.y) : ReluB::f(fa.y, fb.y);
+                }
+            }
+            uint4 o;
+            __nv_bfloat162 *po = reinterpret_cast<__nv_bfloat162 *>(&o);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                po[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+                float2 back = __bfloat1622float2(po[j]);
+                acc[2 * j] += back.x;
+                acc[2 * j + 1] += back.y;
+            }
+            *reinterpret_cast<uint4 *>(out + e) = o;
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) red[w][lane][j] = acc[j];
+    __syncthreads();
+    // 256 threads = 256 columns of this block: thread t sums column t over the 8 warps
+    const int cl = threadIdx.x >> 3, cj = threadIdx.x & 7;
+    const long long c = (long long)blockIdx.x * 256 + threadIdx.x;
+    if (c < cols) {
+        float t = 0.0f;
+#pragma unroll
+        for (int y = 0; y < 8; ++y) t += red[y][cl][cj];
+        partial[(long long)blockIdx.y * cols + c] = t;
+    }
+}
+
 template <int OP>
 mcb_status launch_binary(mcb_ctx *ctx, const float *a, const int64_t *ad, int ar, const float *b, const int64_t *bd,
                          int br, float *out) {
@@ -438,4 +505,30 @@ mcb_status mcb_add_typed(mcb_ctx *ctx, const void *a, int32_t a_dt, const void *
     else return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "typed add: unsupported storage combination");
     MCB_LAUNCHED(ctx);
     return MCB_OK;
+}
+
+bool mcb_map_colsum_supported(const void *a, const void *b, const void *out, int64_t cols) {
+    return cols > 0 && cols % 8 == 0 && mcb_aligned16(a) && (!b || mcb_aligned16(b)) && mcb_aligned16(out);
+}
+
+mcb_status mcb_map_colsum(mcb_ctx *ctx, int mode, const void *a, const void *b, void *out_bf16, int64_t rows, int64_t cols,
+                          float *colsum_out) {
+    if (!mcb_map_colsum_supported(a, b, out_bf16, cols)) return MCB_UNSUPPORTED;
+    if (rows == 0) return mcb_memset(ctx, colsum_out, 0, sizeof(float) * cols);
+    double bytes = (double)rows * cols * (mode == 0 ? 6.0 : 6.0);
+    ProfScope prof(ctx, MCB_PROF_ELEMENTWISE, 0.0, bytes);
+    int chunks = (int)((cols + 255) / 256);
+    int splits = (ctx->sm_count * 6 + chunks - 1) / chunks; // 256-thread blocks, about six per SM
+    if (splits > (rows + 15) / 16) splits = (int)((rows + 15) / 16);
+    if (splits < 1) splits = 1;
+    void *scratch;
+    MCB_TRY(mcb_scratch(ctx, sizeof(float) * (size_t)splits * cols, &scratch));
+    dim3 grid(chunks, splits);
+    __nv_bfloat16 *o = (__nv_bfloat16 *)out_bf16;
+    if (mode == 0) map_colsum_kernel<0><<<grid, 256, 0, ctx->stream>>>(a, b, o, rows, cols, (float *)scratch);
+    else if (mode == 1) map_colsum_kernel<1><<<grid, 256, 0, ctx->stream>>>(a, b, o, rows, cols, (float *)scratch);
+    else if (mode == 2) map_colsum_kernel<2><<<grid, 256, 0, ctx->stream>>>(a, b, o, rows, cols, (float *)scratch);
+    else return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "map_colsum: unknown mode %d", mode);
+    MCB_LAUNCHED(ctx);
+    return mcb_partial_sum_final(ctx, (const float *)scratch, splits, cols, colsum_out);
 }

@@ -52,7 +52,12 @@ mcb_status mcb_flash_backward(mcb_ctx *ctx, const void *q, const void *k, const 
 mcb_status mcb_ln_fast_forward(mcb_ctx *ctx, const float *x, const float *gamma, const float *beta, double eps, void *out, int32_t out_dt,
                                float *mean, float *rstd, int64_t rows, int64_t dim);
 mcb_status mcb_ln_fast_backward(mcb_ctx *ctx, const float *x, const float *gamma, const void *g, int32_t g_dt, double eps, const float *mean,
-                                const float *rstd, float *dx, float *dgamma, float *dbeta, int64_t rows, int64_t dim);
+                                const float *rstd, const float *addend, float *dx, float *dgamma, float *dbeta, int64_t rows, int64_t dim);
+// reduce.cu: LayerNorm backward that writes dx as addend + dx when `addend` is given (may alias dx);
+// MCB_UNSUPPORTED (nothing launched) where only the plain form exists
+mcb_status mcb_layer_norm_backward_ex(mcb_ctx *ctx, const float *x, const float *gamma, const void *g, int32_t g_dt, double eps,
+                                      const float *mean, const float *rstd, const float *addend, float *dx, float *dgamma,
+                                      float *dbeta, int64_t rows, int64_t dim);
 // reduce.cu
 mcb_status mcb_sce_grad(mcb_ctx *ctx, const void *logits, void *out, int32_t dt, const void *labels, int32_t label_dt,
                         int64_t n, int64_t c, float *loss_out, const float *upstream);
@@ -64,6 +69,14 @@ mcb_status mcb_fill_from_scalar(mcb_ctx *ctx, float *out, const float *scalar, d
 mcb_status mcb_mul_scalar_ptr(mcb_ctx *ctx, const void *x, const float *scalar, void *out, int64_t n, int32_t dt);
 // out = a + b with per-operand storage types (f32 or bf16), same shape
 mcb_status mcb_add_typed(mcb_ctx *ctx, const void *a, int32_t a_dt, const void *b, int32_t b_dt, void *out, int32_t out_dt, int64_t n);
+// one pass producing a bf16 [rows, cols] matrix and its column sums (of the rounded values):
+// mode 0: out = bf16(a), a f32;  mode 1: out = gelu'(a) * b;  mode 2: out = relu'(a) * b (a, b bf16).
+// Returns MCB_UNSUPPORTED (nothing launched) unless cols % 8 == 0 and all pointers are 16-byte aligned.
+mcb_status mcb_map_colsum(mcb_ctx *ctx, int mode, const void *a, const void *b, void *out_bf16, int64_t rows, int64_t cols,
+                          float *colsum_out);
+bool mcb_map_colsum_supported(const void *a, const void *b, const void *out, int64_t cols);
+// reduce.cu: out[col] = sum of `parts` rows of partial[parts, cols], fixed order
+mcb_status mcb_partial_sum_final(mcb_ctx *ctx, const float *partial, int parts, int64_t cols, float *out);
 // optim.cu
 mcb_status mcb_adam_flat_ex(mcb_ctx *ctx, float *p, const void *g, int32_t g_dt, float *m, float *v, void *p_bf16,
                             int64_t n, double lr, double beta1, double beta2, double eps, int32_t step,

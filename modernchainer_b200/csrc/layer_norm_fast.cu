@@ -31,15 +31,23 @@ __global__ void __launch_bounds__(kWarps * 32) ln_fwd_reg_kernel(const float *__
         ga[j] = ld4_or_zero(gamma, lane + 32 * j, dim4);
         be[j] = ld4_or_zero(beta, lane + 32 * j, dim4);
     }
+    // the next row of this warp is fetched while the current one is reduced and written, so two
+    // rows' loads are in flight per warp (one block per SM is resident: latency, not bandwidth, binds)
+    float4 v[NV];
+    if (warp < rows) {
+#pragma unroll
+        for (int j = 0; j < NV; ++j) v[j] = ld4_or_zero(x + warp * dim, lane + 32 * j, dim4);
+    }
     for (long long r = warp; r < rows; r += nwarps) {
-        const float *s = x + r * dim;
-        float4 v[NV];
+        float4 nx[NV];
+        const long long rn = r + nwarps;
+        if (rn < rows) {
+#pragma unroll
+            for (int j = 0; j < NV; ++j) nx[j] = ld4_or_zero(x + rn * dim, lane + 32 * j, dim4);
+        }
         float sum = 0.0f;
 #pragma unroll
-        for (int j = 0; j < NV; ++j) {
-            v[j] = ld4_or_zero(s, lane + 32 * j, dim4);
-            sum += (v[j].x + v[j].y) + (v[j].z + v[j].w);
-        }
+        for (int j = 0; j < NV; ++j) sum += (v[j].x + v[j].y) + (v[j].z + v[j].w);
         float mean = warp_sum(sum) * inv_dim;
         float var = 0.0f;
 #pragma unroll
@@ -61,13 +69,38 @@ __global__ void __launch_bounds__(kWarps * 32) ln_fwd_reg_kernel(const float *__
                 Elem<OutT>::st4(d, lane + 32 * j,
                                 make_float4((v[j].x - mean) * rstd * ga[j].x + be[j].x, (v[j].y - mean) * rstd * ga[j].y + be[j].y,
                                             (v[j].z - mean) * rstd * ga[j].z + be[j].z, (v[j].w - mean) * rstd * ga[j].w + be[j].w));
+        if (rn < rows) {
+#pragma unroll
+            for (int j = 0; j < NV; ++j) v[j] = nx[j];
+        }
     }
 }
 
+// upstream gradient as loaded (bf16 stays packed while it waits in the prefetch registers)
+template <typename T> struct RawG;
+template <> struct RawG<float> {
+    typedef float4 type;
+    static __device__ __forceinline__ type load(const float *p, int idx, int dim4) { return ld4_or_zero(p, idx, dim4); }
+    static __device__ __forceinline__ float4 unpack(type r) { return r; }
+};
+template <> struct RawG<__nv_bfloat16> {
+    typedef uint2 type;
+    static __device__ __forceinline__ type load(const __nv_bfloat16 *p, int idx, int dim4) {
+        return idx < dim4 ? reinterpret_cast<const uint2 *>(p)[idx] : make_uint2(0u, 0u);
+    }
+    static __device__ __forceinline__ float4 unpack(type r) {
+        float2 a = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162 *>(&r.x));
+        float2 b = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162 *>(&r.y));
+        return make_float4(a.x, a.y, b.x, b.y);
+    }
+};
+
+// `addend` (optional, may alias dx): a gradient already pending for the same input; dx is written as
+// addend + dx, which saves the separate fan-in add over the residual stream.
 template <typename GT, int NV>
 __global__ void __launch_bounds__(kWarps * 32) ln_bwd_reg_kernel(const float *__restrict__ x, const float *__restrict__ gamma,
                                                                   const GT *__restrict__ g, float eps, const float *__restrict__ mean_in,
-                                                                  const float *__restrict__ rstd_in, float *__restrict__ dx,
+                                                                  const float *__restrict__ rstd_in, const float *addend, float *dx,
                                                                   float *__restrict__ partial, long long rows, int dim) {
     __shared__ float acc[2 * 32 * NV * 4];
     int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
@@ -82,15 +115,34 @@ __global__ void __launch_bounds__(kWarps * 32) ln_bwd_reg_kernel(const float *__
         dga[j] = make_float4(0.f, 0.f, 0.f, 0.f);
         dbe[j] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    for (long long r = warp; r < rows; r += nwarps) {
-        const float *s = x + r * dim;
-        const GT *gs = g + r * dim;
-        float4 v[NV], gv[NV];
+    // rows are software-pipelined: the next row's x and g are requested before the current row is
+    // reduced, so each warp keeps two rows of loads in flight (one block per SM fits: latency binds)
+    float4 v[NV];
+    typename RawG<GT>::type graw[NV];
+    if (warp < rows) {
 #pragma unroll
         for (int j = 0; j < NV; ++j) {
-            v[j] = ld4_or_zero(s, lane + 32 * j, dim4);
-            gv[j] = ld4_or_zero(gs, lane + 32 * j, dim4);
+            v[j] = ld4_or_zero(x + warp * dim, lane + 32 * j, dim4);
+            graw[j] = RawG<GT>::load(g + warp * dim, lane + 32 * j, dim4);
         }
+    }
+    for (long long r = warp; r < rows; r += nwarps) {
+        float4 nx[NV], gv[NV], ad[NV];
+        typename RawG<GT>::type ng[NV];
+        const long long rn = r + nwarps;
+        if (rn < rows) {
+#pragma unroll
+            for (int j = 0; j < NV; ++j) {
+                nx[j] = ld4_or_zero(x + rn * dim, lane + 32 * j, dim4);
+                ng[j] = RawG<GT>::load(g + rn * dim, lane + 32 * j, dim4);
+            }
+        }
+        if (addend) {
+#pragma unroll
+            for (int j = 0; j < NV; ++j) ad[j] = ld4_or_zero(addend + r * dim, lane + 32 * j, dim4);
+        }
+#pragma unroll
+        for (int j = 0; j < NV; ++j) gv[j] = RawG<GT>::unpack(graw[j]);
         float mean, rstd;
         if (mean_in && rstd_in) {
             mean = mean_in[r];
@@ -141,8 +193,21 @@ __global__ void __launch_bounds__(kWarps * 32) ln_bwd_reg_kernel(const float *__
                 o.y = (fdim * gv[j].y * ga[j].y - sum_dy - v[j].y * sum_dy_norm) * k;
                 o.z = (fdim * gv[j].z * ga[j].z - sum_dy - v[j].z * sum_dy_norm) * k;
                 o.w = (fdim * gv[j].w * ga[j].w - sum_dy - v[j].w * sum_dy_norm) * k;
+                if (addend) { // gradient already pending for this input (residual branch): dx joins it
+                    o.x += ad[j].x;
+                    o.y += ad[j].y;
+                    o.z += ad[j].z;
+                    o.w += ad[j].w;
+                }
                 reinterpret_cast<float4 *>(d)[lane + 32 * j] = o;
             }
+        if (rn < rows) {
+#pragma unroll
+            for (int j = 0; j < NV; ++j) {
+                v[j] = nx[j];
+                graw[j] = ng[j];
+            }
+        }
     }
     // fold the warps' register sums in warp order 0..7 (fixed order: run-to-run identical results)
     float4 *acc_g = reinterpret_cast<float4 *>(acc), *acc_b = acc_g + 32 * NV;
@@ -211,14 +276,14 @@ void launch_fwd(int nv, int grid, cudaStream_t s, const float *x, const float *g
 }
 template <typename GT>
 void launch_bwd(int nv, int grid, cudaStream_t s, const float *x, const float *gamma, const GT *g, float eps, const float *mean,
-                const float *rstd, float *dx, float *partial, long long rows, int dim) {
+                const float *rstd, const float *addend, float *dx, float *partial, long long rows, int dim) {
     switch (nv) {
-    case 1: ln_bwd_reg_kernel<GT, 1><<<grid, kWarps * 32, 0, s>>>(x, gamma, g, eps, mean, rstd, dx, partial, rows, dim); break;
-    case 2: ln_bwd_reg_kernel<GT, 2><<<grid, kWarps * 32, 0, s>>>(x, gamma, g, eps, mean, rstd, dx, partial, rows, dim); break;
-    case 3: ln_bwd_reg_kernel<GT, 3><<<grid, kWarps * 32, 0, s>>>(x, gamma, g, eps, mean, rstd, dx, partial, rows, dim); break;
-    case 4: ln_bwd_reg_kernel<GT, 4><<<grid, kWarps * 32, 0, s>>>(x, gamma, g, eps, mean, rstd, dx, partial, rows, dim); break;
-    case 6: ln_bwd_reg_kernel<GT, 6><<<grid, kWarps * 32, 0, s>>>(x, gamma, g, eps, mean, rstd, dx, partial, rows, dim); break;
-    default: ln_bwd_reg_kernel<GT, 8><<<grid, kWarps * 32, 0, s>>>(x, gamma, g, eps, mean, rstd, dx, partial, rows, dim); break;
+    case 1: ln_bwd_reg_kernel<GT, 1><<<grid, kWarps * 32, 0, s>>>(x, gamma, g, eps, mean, rstd, addend, dx, partial, rows, dim); break;
+    case 2: ln_bwd_reg_kernel<GT, 2><<<grid, kWarps * 32, 0, s>>>(x, gamma, g, eps, mean, rstd, addend, dx, partial, rows, dim); break;
+    case 3: ln_bwd_reg_kernel<GT, 3><<<grid, kWarps * 32, 0, s>>>(x, gamma, g, eps, mean, rstd, addend, dx, partial, rows, dim); break;
+    case 4: ln_bwd_reg_kernel<GT, 4><<<grid, kWarps * 32, 0, s>>>(x, gamma, g, eps, mean, rstd, addend, dx, partial, rows, dim); break;
+    case 6: ln_bwd_reg_kernel<GT, 6><<<grid, kWarps * 32, 0, s>>>(x, gamma, g, eps, mean, rstd, addend, dx, partial, rows, dim); break;
+    default: ln_bwd_reg_kernel<GT, 8><<<grid, kWarps * 32, 0, s>>>(x, gamma, g, eps, mean, rstd, addend, dx, partial, rows, dim); break;
     }
 }
 
@@ -242,15 +307,15 @@ mcb_status mcb_ln_fast_forward(mcb_ctx *ctx, const float *x, const float *gamma,
 }
 
 mcb_status mcb_ln_fast_backward(mcb_ctx *ctx, const float *x, const float *gamma, const void *g, int32_t g_dt, double eps, const float *mean,
-                                const float *rstd, float *dx, float *dgamma, float *dbeta, int64_t rows, int64_t dim) {
-    if (!eligible(dim, x, gamma, g, dx) || rows == 0) return MCB_UNSUPPORTED;
+                                const float *rstd, const float *addend, float *dx, float *dgamma, float *dbeta, int64_t rows, int64_t dim) {
+    if (!eligible(dim, x, gamma, g, dx) || rows == 0 || (addend && !mcb_aligned16(addend))) return MCB_UNSUPPORTED;
     if (g_dt == MCB_BF16 && (dim % 8)) return MCB_UNSUPPORTED;
     int nv = pick_nv(dim);
     int grid = mcb_grid_for(ctx, rows, kWarps, 2);
     void *scratch;
     MCB_TRY(mcb_scratch(ctx, sizeof(float) * (size_t)grid * 2 * dim, &scratch));
-    if (g_dt == MCB_F32) launch_bwd<float>(nv, grid, ctx->stream, x, gamma, (const float *)g, (float)eps, mean, rstd, dx, (float *)scratch, rows, (int)dim);
-    else launch_bwd<__nv_bfloat16>(nv, grid, ctx->stream, x, gamma, (const __nv_bfloat16 *)g, (float)eps, mean, rstd, dx, (float *)scratch, rows, (int)dim);
+    if (g_dt == MCB_F32) launch_bwd<float>(nv, grid, ctx->stream, x, gamma, (const float *)g, (float)eps, mean, rstd, addend, dx, (float *)scratch, rows, (int)dim);
+    else launch_bwd<__nv_bfloat16>(nv, grid, ctx->stream, x, gamma, (const __nv_bfloat16 *)g, (float)eps, mean, rstd, addend, dx, (float *)scratch, rows, (int)dim);
     MCB_LAUNCHED(ctx);
     ln_params_final_kernel<<<(int)((2 * dim + 31) / 32), dim3(32, 8), 0, ctx->stream>>>((const float *)scratch, grid, (int)dim, dgamma, dbeta);
     MCB_LAUNCHED(ctx);

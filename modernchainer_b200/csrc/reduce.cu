@@ -79,6 +79,7 @@ __global__ void __launch_bounds__(256) col_sum_vec_kernel(const T *__restrict__ 
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     if (col < cols) {
         long long c4 = col >> 2, ld4 = cols >> 2;
+#pragma unroll 4
         for (long long r = r0 + w; r < r1; r += 8) {
             float4 v = Elem<T>::ld4(a, r * ld4 + c4);
             acc.x += v.x;
@@ -645,6 +646,16 @@ mcb_status mcb_layer_norm(mcb_ctx *ctx, const float *x, const float *gamma, cons
 mcb_status mcb_layer_norm_backward(mcb_ctx *ctx, const float *x, const float *gamma, const void *g, int32_t g_dt,
                                    double eps, const float *mean, const float *rstd, float *dx, float *dgamma,
                                    float *dbeta, int64_t rows, int64_t dim) {
+    return mcb_layer_norm_backward_ex(ctx, x, gamma, g, g_dt, eps, mean, rstd, nullptr, dx, dgamma, dbeta, rows, dim);
+}
+
+} // extern "C"
+
+// With `addend` (may alias dx) the input gradient is written as addend + dx; only the register-resident
+// kernel does that, so other shapes return MCB_UNSUPPORTED before anything is launched.
+mcb_status mcb_layer_norm_backward_ex(mcb_ctx *ctx, const float *x, const float *gamma, const void *g, int32_t g_dt, double eps,
+                                      const float *mean, const float *rstd, const float *addend, float *dx, float *dgamma,
+                                      float *dbeta, int64_t rows, int64_t dim) {
     MCB_CHECK_CTX(ctx);
     if (dim == 0) return MCB_OK;
     if (rows == 0) {
@@ -652,11 +663,13 @@ mcb_status mcb_layer_norm_backward(mcb_ctx *ctx, const float *x, const float *ga
         return mcb_memset(ctx, dbeta, 0, sizeof(float) * dim);
     }
     // algorithmic bytes: read x and g, write dx, read the row statistics, write 2*dim parameter sums
-    ProfScope prof(ctx, MCB_PROF_NORM, 0.0, (double)rows * dim * (8.0 + (g_dt == MCB_BF16 ? 2.0 : 4.0)) + 8.0 * rows + 8.0 * dim);
+    ProfScope prof(ctx, MCB_PROF_NORM, 0.0,
+                   (double)rows * dim * (8.0 + (g_dt == MCB_BF16 ? 2.0 : 4.0) + (addend ? 4.0 : 0.0)) + 8.0 * rows + 8.0 * dim);
     if (g_dt == MCB_F32 || g_dt == MCB_BF16) {
-        mcb_status fast = mcb_ln_fast_backward(ctx, x, gamma, g, g_dt, eps, mean, rstd, dx, dgamma, dbeta, rows, dim);
+        mcb_status fast = mcb_ln_fast_backward(ctx, x, gamma, g, g_dt, eps, mean, rstd, addend, dx, dgamma, dbeta, rows, dim);
         if (fast != MCB_UNSUPPORTED) return fast;
     }
+    if (addend) return MCB_UNSUPPORTED;
     const size_t smem_cap = 200 * 1024;
     int warps = 8;
     while (warps > 1 && (size_t)warps * 2 * dim * sizeof(float) > smem_cap) warps >>= 1;
@@ -679,6 +692,8 @@ mcb_status mcb_layer_norm_backward(mcb_ctx *ctx, const float *x, const float *ga
     MCB_LAUNCHED(ctx);
     return MCB_OK;
 }
+
+extern "C" {
 
 mcb_status mcb_softmax_cross_entropy(mcb_ctx *ctx, const float *logits, const void *labels, int32_t label_dt,
                                      int64_t n, int64_t c, float *loss_out) {
@@ -771,6 +786,14 @@ mcb_status mcb_sum_scaled(mcb_ctx *ctx, const float *x, int64_t n, double scale,
     sum_partial_kernel<<<grid, kThreads, 0, ctx->stream>>>(x, n, (double *)scratch);
     MCB_LAUNCHED(ctx);
     sum_final_kernel<<<1, 32, 0, ctx->stream>>>((const double *)scratch, grid, scale, out);
+    MCB_LAUNCHED(ctx);
+    return MCB_OK;
+}
+
+// out[col] = sum of `parts` rows of partial[parts, cols], in a fixed order (used by fused kernels
+// in other files that leave per-block column sums in the context's scratch buffer)
+mcb_status mcb_partial_sum_final(mcb_ctx *ctx, const float *partial, int parts, int64_t cols, float *out) {
+    partial_sum_final_kernel<<<(int)((cols + 31) / 32), dim3(32, 8), 0, ctx->stream>>>(partial, parts, cols, out);
     MCB_LAUNCHED(ctx);
     return MCB_OK;
 }

@@ -368,3 +368,41 @@ def test_fused_qkv_attention_matches_composed_ops(mc, ctx, cfg):
     for i, (a, r) in enumerate(zip(gf, gu)):
         err = np.abs(a - r).max() / max(float(np.abs(r).max()), floor)
         assert err <= 2e-2, (i, err)
+
+
+@pytest.mark.parametrize("cfg", [(1000, 256, 4, 512, 2, 192, 2), (2048, 768, 12, 3072, 2, 1024, 8)])
+def test_fused_backward_passes_match_separate_kernels(mc, ctx, cfg):
+    """Backward fusions of the bf16 path against the same tape with separate kernels
+    (MCB_UNFUSED_BWD): cast + bias column sum, activation backward + bias column sum, and LayerNorm
+    backward adding into the gradient already pending on the residual stream.  The fused kernels
+    round at the same points as the separate ones; what differs is only the grouping of f32 partial
+    sums, so the loss is identical and every gradient agrees to 1e-5 of its peak."""
+    import os
+    rng = np.random.default_rng(99)
+    vocab, d, heads, ff, layers, s, b = cfg
+    ids = rng.integers(0, vocab, (b, s)).astype(np.int64)
+    tgt = np.concatenate([ids[:, 1:], rng.integers(0, vocab, (b, 1))], 1).astype(np.int64)
+
+    def run(unfused):
+        if unfused:
+            os.environ["MCB_UNFUSED_BWD"] = "1"
+        else:
+            os.environ.pop("MCB_UNFUSED_BWD", None)
+        try:
+            m = mc.Model(ctx, "decoder", [vocab, d, heads, ff, layers, 0])
+            ps = m.parameters()
+            keep = mc.Arena(ctx, ps)
+            with mc.autocast(mc.BF16):
+                loss = m.loss(mc.Variable.constant(ctx, ids), mc.Variable.constant(ctx, tgt))
+            loss.backward()
+            return float(loss.data.reshape(-1)[0]), [p.grad for p in ps], [p.data.shape for p in ps]
+        finally:
+            os.environ.pop("MCB_UNFUSED_BWD", None)
+
+    lf, gf, shapes = run(False)
+    lu, gu, _ = run(True)
+    assert lf == lu
+    # sums over rows (bias, LayerNorm vectors) group their partial sums differently, and the weight
+    # gradients' split-K partial tiles are added in whatever order the CTAs finish: 1e-5 of the peak
+    for i, (a, r) in enumerate(zip(gf, gu)):
+        assert np.abs(a - r).max() <= 1e-5 * max(float(np.abs(r).max()), 1e-30), (i, shapes[i])
