@@ -146,6 +146,22 @@ struct GeluB {
         return g * (phi + x * dphi * coeff);
     }
 };
+// The same derivative for bf16 storage: the hardware tanh approximation (relative error about
+// 2^-11) is below the bf16 resolution of the result and keeps the kernel bound by memory, not by
+// the multi-instruction tanhf.
+struct GeluBLowp {
+    static __device__ __forceinline__ float f(float x, float g) {
+        const float k = 0.7978845608028654f;
+        float xx = x * x;
+        float c = k * (x + 0.044715f * xx * x);
+        float th;
+        asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(c));
+        float phi = 0.5f * (1.0f + th);
+        float dphi = 0.5f * (1.0f - th * th);
+        float coeff = k * (1.0f + 0.044715f * 3.0f * xx);
+        return g * (phi + x * dphi * coeff);
+    }
+};
 
 template <typename T, typename Fn> __global__ void map1_kernel(const T *__restrict__ x, T *__restrict__ out, long long n, int vec) {
     long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -263,8 +279,8 @@ __global__ void __launch_bounds__(256) map_colsum_kernel(const void *__restrict_
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     float2 fa = __bfloat1622float2(pa[j]), fb = __bfloat1622float2(pb[j]);
-                    v[2 * j] = MODE == 1 ? GeluB::f(fa.x, fb.x) : ReluB::f(fa.x, fb.x);
-                    v[2 * j + 1] = MODE == 1 ? GeluB::f(fa.y, fb.y) : ReluB::f(fa.y, fb.y);
+                    v[2 * j] = MODE == 1 ? GeluBLowp::f(fa.x, fb.x) : ReluB::f(fa.x, fb.x);
+                    v[2 * j + 1] = MODE == 1 ? GeluBLowp::f(fa.y, fb.y) : ReluB::f(fa.y, fb.y);
                 }
             }
             uint4 o;
@@ -408,6 +424,7 @@ mcb_status mcb_gelu(mcb_ctx *ctx, const void *x, void *out, int64_t n, int32_t d
 }
 mcb_status mcb_gelu_backward(mcb_ctx *ctx, const void *x, const void *g, void *out, int64_t n, int32_t dt) {
     MCB_CHECK_CTX(ctx);
+    if (dt == MCB_BF16) return launch_map2<GeluBLowp>(ctx, x, g, out, n, dt);
     return launch_map2<GeluB>(ctx, x, g, out, n, dt);
 }
 

@@ -124,6 +124,13 @@ __device__ __forceinline__ void store_rows(bf16 *g, long long ld, int row0, int 
     }
 }
 
+// 2^x on the special-function unit (about 2 ulp; the probabilities are rounded to bf16 right after)
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 // ------------------------------------------------------------------ forward
 template <bool CAUSAL>
 __global__ void __launch_bounds__(kThreads) flash_fwd_kernel(const bf16 *__restrict__ Q, const bf16 *__restrict__ K, const bf16 *__restrict__ V,
@@ -132,7 +139,8 @@ __global__ void __launch_bounds__(kThreads) flash_fwd_kernel(const bf16 *__restr
     __shared__ __align__(128) unsigned char smem[TILE_BYTES * 5];
     unsigned char *sQ = smem, *sK[2] = {smem + TILE_BYTES, smem + 3 * TILE_BYTES}, *sV[2] = {smem + 2 * TILE_BYTES, smem + 4 * TILE_BYTES};
     int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tig = lane & 3;
-    int qt = blockIdx.x, n = blockIdx.y / H, h = blockIdx.y % H;
+    // causal: late query tiles visit the most key tiles, so they are scheduled first
+    int qt = CAUSAL ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x, n = blockIdx.y / H, h = blockIdx.y % H;
     long long base = (long long)n * S * D + (long long)h * HD;      // q, k, v (row pitch D)
     long long base_o = (long long)n * S * DO + (long long)h * HD;   // o, do (row pitch DO)
     long long base_g = (long long)n * S * DG + (long long)h * HD;   // dq, dk, dv (row pitch DG)
@@ -185,11 +193,11 @@ __global__ void __launch_bounds__(kThreads) flash_fwd_kernel(const bf16 *__restr
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
             float mnew = fmaxf(m[r], mx);
             float msafe = (mnew == -INFINITY) ? 0.0f : mnew;
-            float corr = exp2f(m[r] - msafe);
+            float corr = fast_exp2(m[r] - msafe);
             float sum = 0.0f;
 #pragma unroll
             for (int nt = 0; nt < 8; ++nt) {
-                float p0 = exp2f(s[nt][2 * r] - msafe), p1 = exp2f(s[nt][2 * r + 1] - msafe);
+                float p0 = fast_exp2(s[nt][2 * r] - msafe), p1 = fast_exp2(s[nt][2 * r + 1] - msafe);
                 s[nt][2 * r] = p0;
                 s[nt][2 * r + 1] = p1;
                 sum += p0 + p1;
@@ -246,7 +254,8 @@ __global__ void __launch_bounds__(kThreads) flash_dq_kernel(const bf16 *__restri
     unsigned char *sQ = smem, *sdO = smem + TILE_BYTES;
     unsigned char *sK[2] = {smem + 2 * TILE_BYTES, smem + 4 * TILE_BYTES}, *sV[2] = {smem + 3 * TILE_BYTES, smem + 5 * TILE_BYTES};
     int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tig = lane & 3;
-    int qt = blockIdx.x, n = blockIdx.y / H, h = blockIdx.y % H;
+    // causal: late query tiles visit the most key tiles, so they are scheduled first
+    int qt = CAUSAL ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x, n = blockIdx.y / H, h = blockIdx.y % H;
     long long base = (long long)n * S * D + (long long)h * HD;      // q, k, v (row pitch D)
     long long base_o = (long long)n * S * DO + (long long)h * HD;   // o, do (row pitch DO)
     long long base_g = (long long)n * S * DG + (long long)h * HD;   // dq, dk, dv (row pitch DG)
@@ -294,7 +303,7 @@ __global__ void __launch_bounds__(kThreads) flash_dq_kernel(const bf16 *__restri
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 int r = e >> 1;
-                float p = exp2f(s[nt][e] * scale_log2 - lse2[r]);
+                float p = fast_exp2(s[nt][e] * scale_log2 - lse2[r]);
                 if (need_mask) {
                     int col = j * TILE + nt * 8 + 2 * tig + (e & 1);
                     int row = row0 + 8 * r;
@@ -372,7 +381,7 @@ __global__ void __launch_bounds__(kThreads) flash_dkv_kernel(const bf16 *__restr
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 int qc = nt * 8 + 2 * tig + (e & 1);
-                float p = exp2f(s[nt][e] * scale_log2 - sLse[st][qc]);
+                float p = fast_exp2(s[nt][e] * scale_log2 - sLse[st][qc]);
                 if (need_mask) {
                     int qrow = i * TILE + qc;
                     int krow = krow0 + 8 * (e >> 1);

@@ -237,18 +237,21 @@ __global__ void __launch_bounds__(kWarps * 32) ln_bwd_reg_kernel(const float *__
 
 __global__ void ln_params_final_kernel(const float *__restrict__ partial, int blocks, int dim, float *__restrict__ dgamma,
                                        float *__restrict__ dbeta) {
-    // block (32, 8): 32 of the 2*dim columns, 8 interleaved groups of per-block partials, fixed order
-    __shared__ float red[8][33];
+    // block (32, 32): 32 of the 2*dim columns, 32 interleaved groups of per-block partials, fixed order;
+    // the few loads of a thread are independent, so the kernel costs about one memory round trip
+    __shared__ float red[32][33];
     int j = blockIdx.x * 32 + threadIdx.x;
     float t = 0.0f;
-    if (j < 2 * dim)
-        for (int b = threadIdx.y; b < blocks; b += 8) t += partial[(size_t)b * 2 * dim + j];
+    if (j < 2 * dim) {
+#pragma unroll 4
+        for (int b = threadIdx.y; b < blocks; b += 32) t += partial[(size_t)b * 2 * dim + j];
+    }
     red[threadIdx.y][threadIdx.x] = t;
     __syncthreads();
     if (threadIdx.y == 0 && j < 2 * dim) {
         float u = 0.0f;
 #pragma unroll
-        for (int y = 0; y < 8; ++y) u += red[y][threadIdx.x];
+        for (int y = 0; y < 32; ++y) u += red[y][threadIdx.x];
         if (j < dim) dgamma[j] = u;
         else dbeta[j - dim] = u;
     }
@@ -317,7 +320,7 @@ mcb_status mcb_ln_fast_backward(mcb_ctx *ctx, const float *x, const float *gamma
     if (g_dt == MCB_F32) launch_bwd<float>(nv, grid, ctx->stream, x, gamma, (const float *)g, (float)eps, mean, rstd, addend, dx, (float *)scratch, rows, (int)dim);
     else launch_bwd<__nv_bfloat16>(nv, grid, ctx->stream, x, gamma, (const __nv_bfloat16 *)g, (float)eps, mean, rstd, addend, dx, (float *)scratch, rows, (int)dim);
     MCB_LAUNCHED(ctx);
-    ln_params_final_kernel<<<(int)((2 * dim + 31) / 32), dim3(32, 8), 0, ctx->stream>>>((const float *)scratch, grid, (int)dim, dgamma, dbeta);
+    ln_params_final_kernel<<<(int)((2 * dim + 31) / 32), dim3(32, 32), 0, ctx->stream>>>((const float *)scratch, grid, (int)dim, dgamma, dbeta);
     MCB_LAUNCHED(ctx);
     return MCB_OK;
 }

@@ -105,17 +105,19 @@ __global__ void __launch_bounds__(256) col_sum_vec_kernel(const T *__restrict__ 
 }
 // out[col] = sum over `parts` partial rows, in a fixed order; block (32, 8): 32 columns, 8 interleaved part groups
 __global__ void partial_sum_final_kernel(const float *__restrict__ partial, int parts, long long cols, float *__restrict__ out) {
-    __shared__ float red[8][33];
+    __shared__ float red[32][33];
     long long col = (long long)blockIdx.x * 32 + threadIdx.x;
+    const int groups = blockDim.y; // 8 or 32 interleaved groups of partial rows
     float t = 0.0f;
-    if (col < cols)
-        for (int s = threadIdx.y; s < parts; s += 8) t += partial[(long long)s * cols + col];
+    if (col < cols) {
+#pragma unroll 4
+        for (int s = threadIdx.y; s < parts; s += groups) t += partial[(long long)s * cols + col];
+    }
     red[threadIdx.y][threadIdx.x] = t;
     __syncthreads();
     if (threadIdx.y == 0 && col < cols) {
         float u = 0.0f;
-#pragma unroll
-        for (int y = 0; y < 8; ++y) u += red[y][threadIdx.x];
+        for (int y = 0; y < groups; ++y) u += red[y][threadIdx.x];
         out[col] = u;
     }
 }
@@ -540,7 +542,7 @@ mcb_status mcb_col_sum(mcb_ctx *ctx, const void *a, int32_t dt, int64_t rows, in
         if (dt == MCB_F32) col_sum_vec_kernel<float><<<grid, 256, 0, ctx->stream>>>((const float *)a, rows, cols, (float *)scratch);
         else col_sum_vec_kernel<__nv_bfloat16><<<grid, 256, 0, ctx->stream>>>((const __nv_bfloat16 *)a, rows, cols, (float *)scratch);
         MCB_LAUNCHED(ctx);
-        partial_sum_final_kernel<<<(int)((cols + 31) / 32), dim3(32, 8), 0, ctx->stream>>>((const float *)scratch, splits, cols, out);
+        partial_sum_final_kernel<<<(int)((cols + 31) / 32), dim3(32, 32), 0, ctx->stream>>>((const float *)scratch, splits, cols, out);
         MCB_LAUNCHED(ctx);
         return MCB_OK;
     }
@@ -793,7 +795,7 @@ mcb_status mcb_sum_scaled(mcb_ctx *ctx, const float *x, int64_t n, double scale,
 // out[col] = sum of `parts` rows of partial[parts, cols], in a fixed order (used by fused kernels
 // in other files that leave per-block column sums in the context's scratch buffer)
 mcb_status mcb_partial_sum_final(mcb_ctx *ctx, const float *partial, int parts, int64_t cols, float *out) {
-    partial_sum_final_kernel<<<(int)((cols + 31) / 32), dim3(32, 8), 0, ctx->stream>>>(partial, parts, cols, out);
+    partial_sum_final_kernel<<<(int)((cols + 31) / 32), dim3(32, 32), 0, ctx->stream>>>(partial, parts, cols, out);
     MCB_LAUNCHED(ctx);
     return MCB_OK;
 }
