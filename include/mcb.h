@@ -139,6 +139,11 @@ mcb_status mcb_gelu(mcb_ctx *ctx, const void *x, void *out, int64_t n, int32_t d
 mcb_status mcb_gelu_backward(mcb_ctx *ctx, const void *x, const void *g, void *out, int64_t n, int32_t dt);
 /* Ops::cast, ops.rs:322-417; f32<->bf16/f16 with round-to-nearest-even (core/src/dtype.rs:75-150) */
 mcb_status mcb_cast(mcb_ctx *ctx, const void *src, int32_t src_dt, void *dst, int32_t dst_dt, int64_t n);
+/* Ops::transpose2d, storage.rs / cpu/src/kernels.rs:306-330: out[c, r] = a[r, c] for a [rows, cols] f32 matrix */
+mcb_status mcb_transpose2d(mcb_ctx *ctx, const float *a, float *out, int64_t rows, int64_t cols);
+/* permute_data, autograd/src/host_ops.rs:703-735: output dim d takes source axis axes[d]; axes must be a
+ * permutation of 0..rank-1 ("invalid permute axes" otherwise), rank <= 8 */
+mcb_status mcb_permute(mcb_ctx *ctx, const float *a, const int64_t *dims, int32_t rank, const int32_t *axes, float *out);
 
 /* ------------------------------------------------------------------ ops: reductions */
 /* Ops::sum_all, ops.rs:872-891: deterministic two-stage reduction, f64 final sum */
@@ -303,6 +308,10 @@ mcb_status mcb_f_layer_norm(mcb_var *x, mcb_var *gamma, mcb_var *beta, double ep
 mcb_status mcb_f_softmax_cross_entropy(mcb_var *logits, mcb_var *target, mcb_var **out);
 mcb_status mcb_f_embedding(mcb_var *ids, mcb_var *weight, mcb_var **out);
 mcb_status mcb_f_reshape(mcb_var *x, const int64_t *dims, int32_t rank, mcb_var **out);
+/* Transpose2d, autograd/src/ops.rs:235-255 (2-D only; backward transposes the gradient) and
+ * PermuteOp, autograd/src/host_ops.rs:690-777 (backward applies the inverse permutation) */
+mcb_status mcb_f_transpose(mcb_var *x, mcb_var **out);
+mcb_status mcb_f_permute(mcb_var *x, const int32_t *axes, int32_t rank, mcb_var **out);
 mcb_status mcb_f_multi_head_attention(mcb_var *q, mcb_var *k, mcb_var *v, int64_t heads, int32_t causal,
                                       mcb_var **out);
 mcb_status mcb_f_conv2d(mcb_var *x, mcb_var *w, mcb_var *bias_or_null, int64_t stride, int64_t pad, mcb_var **out);
@@ -331,6 +340,25 @@ mcb_status mcb_scaler_scale_loss(mcb_scaler *s, mcb_var *loss, mcb_var **out);
 mcb_status mcb_scaler_step(mcb_scaler *s, mcb_adam *opt, mcb_var **params, int32_t n, int32_t *applied);
 mcb_status mcb_scaler_step_async(mcb_scaler *s, mcb_adam *opt, mcb_var **params, int32_t n);
 mcb_status mcb_scaler_state(mcb_scaler *s, double *scale_out, int32_t *growth_tracker_out, int32_t *last_found_inf);
+
+/* The rest of the Optimizer family on the same fused flat pass (optim/src/lib.rs:23-51 SGD, 122-160
+ * MomentumSGD, 162-214 AdamW).  The handle is the mcb_adam type so that mcb_adam_step, mcb_scaler_step and
+ * mcb_adam_release work for every kind.  `beta1` carries the momentum for MomentumSGD; unused fields are
+ * ignored.  AdamW subtracts (f32)(weight_decay*lr) * p_old after the Adam step, as the reference does. */
+enum { MCB_OPT_ADAM = 0, MCB_OPT_ADAMW = 1, MCB_OPT_SGD = 2, MCB_OPT_MOMENTUM_SGD = 3 };
+mcb_status mcb_opt_create(mcb_ctx *ctx, int32_t kind, double lr, double beta1, double beta2, double eps, double weight_decay,
+                          mcb_adam **out);
+/* learning rate used by the following steps (the schedules below are stateless functions of the step) */
+mcb_status mcb_opt_set_lr(mcb_adam *opt, double lr);
+mcb_status mcb_opt_get_lr(mcb_adam *opt, double *lr_out);
+/* clip_grad_norm, optim/src/lib.rs:216-243: global L2 norm over every listed parameter that has a gradient
+ * (squares in f32, sums in f64), gradients scaled in place by (f32)(max_norm/norm) when norm > max_norm;
+ * *norm_out receives the pre-clip norm (one 8-byte read-back).  max_norm <= 0 is InvalidArgument. */
+mcb_status mcb_clip_grad_norm(mcb_var **params, int32_t n, double max_norm, double *norm_out);
+/* LR schedules, optim/src/lib.rs:245-326 (pure host functions of the step) */
+double mcb_lr_linear_warmup_cosine(uint64_t step, uint64_t warmup_steps, uint64_t total_steps, double base_lr, double min_lr);
+double mcb_lr_step(uint64_t step, double base_lr, uint64_t step_size, double gamma);
+double mcb_lr_polynomial(uint64_t step, double base_lr, uint64_t total_steps, double power, double min_lr);
 
 /* The benchmark models, built from the nn initialisers (nn/src/lib.rs:38-73,141-147,185-191,
  * 246-271) and, for the decoder, the layout of llm/src/decoder.rs:98-140.

@@ -11,7 +11,7 @@ HEADER = os.path.join(ROOT, "include", "mcb.h")
 LIB_PATH = os.path.join(HERE, "libmcb.so")
 
 _SCALARS = {"int32_t": C.c_int32, "int64_t": C.c_int64, "double": C.c_double, "float": C.c_float,
-            "size_t": C.c_size_t, "mcb_status": C.c_int32}
+            "size_t": C.c_size_t, "mcb_status": C.c_int32, "uint64_t": C.c_uint64, "uint32_t": C.c_uint32}
 
 
 def parse_header(path=HEADER):

@@ -300,6 +300,26 @@ class _Ops:
         self.ctx.check(self.lib.mcb_matmul(self.ctx.h, da.ptr, db.ptr, out.ptr, a.shape[0], a.shape[1], b.shape[1]))
         return out.numpy()
 
+    def transpose2d(self, a):
+        a = np.asarray(a, np.float32)
+        if a.ndim != 2:
+            raise McbError(5, "transpose2d expects a 2-D tensor, got rank %d" % a.ndim)
+        da = self._a(a)
+        out = self.ctx.empty((a.shape[1], a.shape[0]))
+        self.ctx.check(self.lib.mcb_transpose2d(self.ctx.h, da.ptr, out.ptr, a.shape[0], a.shape[1]))
+        return out.numpy()
+
+    def permute(self, a, axes):
+        a = np.asarray(a, np.float32)
+        if len(axes) != a.ndim:
+            raise McbError(5, "permute rank mismatch")
+        da = self._a(a)
+        ax = (C.c_int32 * max(1, len(axes)))(*[int(v) for v in axes])
+        ok = sorted(int(v) for v in axes) == list(range(a.ndim))
+        out = self.ctx.empty(tuple(a.shape[int(v)] for v in axes) if ok else a.shape)
+        self.ctx.check(self.lib.mcb_permute(self.ctx.h, da.ptr, _dims(a.shape), a.ndim, ax, out.ptr))
+        return out.numpy()
+
     def linear(self, x, w, bias=None, act=0):
         x, w = np.asarray(x, np.float32), np.asarray(w, np.float32)
         dx, dw = self._a(x), self._a(w)
@@ -615,6 +635,15 @@ class _F:
         h = C.c_void_p()
         return _out(x.ctx, x.lib.mcb_f_reshape(x.h, _dims(shape), len(shape), C.byref(h)), h)
 
+    def transpose(self, x):
+        h = C.c_void_p()
+        return _out(x.ctx, x.lib.mcb_f_transpose(x.h, C.byref(h)), h)
+
+    def permute(self, x, axes):
+        h = C.c_void_p()
+        ax = (C.c_int32 * max(1, len(axes)))(*[int(v) for v in axes])
+        return _out(x.ctx, x.lib.mcb_f_permute(x.h, ax, len(axes), C.byref(h)), h)
+
     def multi_head_attention(self, q, k, v, heads, causal):
         h = C.c_void_p()
         return _out(q.ctx, q.lib.mcb_f_multi_head_attention(q.h, k.h, v.h, heads, int(causal), C.byref(h)), h)
@@ -668,6 +697,89 @@ class Adam:
     def update(self, params):
         arr, n = _handles(params)
         self.ctx.check(self.ctx.lib.mcb_adam_step(self.h, arr, n))
+
+    @property
+    def lr(self):
+        v = C.c_double()
+        self.ctx.check(self.ctx.lib.mcb_opt_get_lr(self.h, C.byref(v)))
+        return v.value
+
+    @lr.setter
+    def lr(self, value):
+        self.ctx.check(self.ctx.lib.mcb_opt_set_lr(self.h, float(value)))
+
+
+class _Opt(Adam):
+    """The other members of the Optimizer family (optim/src/lib.rs:23-51, 122-214) on the same handle."""
+    KIND = 0
+
+    def _create(self, ctx, lr, beta1, beta2, eps, weight_decay):
+        self.ctx = ctx
+        h = C.c_void_p()
+        ctx.check(ctx.lib.mcb_opt_create(ctx.h, self.KIND, lr, beta1, beta2, eps, weight_decay, C.byref(h)))
+        self.h = h
+
+
+class AdamW(_Opt):
+    KIND = 1
+
+    def __init__(self, ctx, lr, weight_decay, beta1=0.9, beta2=0.999, eps=1e-8):
+        self._create(ctx, lr, beta1, beta2, eps, weight_decay)
+
+
+class SGD(_Opt):
+    KIND = 2
+
+    def __init__(self, ctx, lr):
+        self._create(ctx, lr, 0.0, 0.0, 0.0, 0.0)
+
+
+class MomentumSGD(_Opt):
+    KIND = 3
+
+    def __init__(self, ctx, lr, momentum):
+        self._create(ctx, lr, momentum, 0.0, 0.0, 0.0)
+
+
+def clip_grad_norm(params, max_norm):
+    """clip_grad_norm (optim/src/lib.rs:216-243): returns the norm before clipping."""
+    arr, n = _handles(params)
+    ctx = params[0].ctx
+    out = C.c_double()
+    ctx.check(ctx.lib.mcb_clip_grad_norm(arr, n, float(max_norm), C.byref(out)))
+    return out.value
+
+
+class LinearWarmupCosineLR:
+    def __init__(self, warmup_steps, total_steps, base_lr, min_lr):
+        self.a = (int(warmup_steps), int(total_steps), float(base_lr), float(min_lr))
+
+    def get_lr(self, step):
+        return _lib.load().mcb_lr_linear_warmup_cosine(int(step), *self.a)
+
+
+class StepLR:
+    def __init__(self, base_lr, step_size, gamma):
+        self.a = (float(base_lr), int(step_size), float(gamma))
+
+    def get_lr(self, step):
+        return _lib.load().mcb_lr_step(int(step), *self.a)
+
+
+class ConstantLR:
+    def __init__(self, lr):
+        self.lr = float(lr)
+
+    def get_lr(self, step):
+        return self.lr
+
+
+class PolynomialLR:
+    def __init__(self, base_lr, total_steps, power, min_lr):
+        self.a = (float(base_lr), int(total_steps), float(power), float(min_lr))
+
+    def get_lr(self, step):
+        return _lib.load().mcb_lr_polynomial(int(step), *self.a)
 
 
 class GradScaler:

@@ -897,6 +897,46 @@ mcb_status f_reshape(const Var &x, const std::vector<int64_t> &shape_in, Var *ou
     return MCB_OK;
 }
 
+// shared by transpose and permute: f32 gather with the given axes; backward = inverse permutation
+static mcb_status permute_tensor(mcb_ctx *ctx, const Tensor &x, const std::vector<int32_t> &axes, Tensor *out) {
+    std::vector<int64_t> oshape(axes.size());
+    for (size_t i = 0; i < axes.size(); ++i) oshape[i] = x.shape[axes[i]];
+    Tensor xf;
+    MCB_TRY(to_dtype(ctx, x, MCB_F32, &xf));
+    MCB_TRY(new_tensor(ctx, MCB_F32, oshape, out));
+    if (axes.size() == 2 && axes[0] == 1 && axes[1] == 0)
+        return mcb_transpose2d(ctx, (const float *)xf.ptr, (float *)out->ptr, x.shape[0], x.shape[1]);
+    return mcb_permute(ctx, (const float *)xf.ptr, x.shape.data(), (int32_t)axes.size(), axes.data(), (float *)out->ptr);
+}
+
+mcb_status f_permute(const Var &x, const std::vector<int32_t> &axes, Var *out) {
+    mcb_ctx *ctx = x->ctx;
+    if (!is_float(x->data.dt)) return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "permute needs a floating-point input");
+    if (axes.size() != x->data.shape.size()) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "permute rank mismatch");
+    if (axes.size() > 8) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "permute supports up to 8 dimensions");
+    std::vector<int32_t> inverse(axes.size(), -1);
+    for (size_t i = 0; i < axes.size(); ++i) {
+        if (axes[i] < 0 || (size_t)axes[i] >= axes.size() || inverse[axes[i]] >= 0) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "invalid permute axes");
+        inverse[axes[i]] = (int32_t)i;
+    }
+    Tensor res;
+    MCB_TRY(permute_tensor(ctx, x->data, axes, &res));
+    Var xv = x;
+    *out = apply(ctx, "Permute", res, {x}, [ctx, inverse, xv](const Tensor &g, std::vector<Tensor> &gi) -> mcb_status {
+        Tensor t;
+        MCB_TRY(permute_tensor(ctx, g, inverse, &t));
+        return like_input(ctx, t, xv, &gi[0]);
+    });
+    return MCB_OK;
+}
+
+mcb_status f_transpose(const Var &x, Var *out) {
+    if (x->data.shape.size() != 2) return mcb_fail(x->ctx, MCB_INVALID_ARGUMENT, "transpose2d expects a 2-D tensor, got rank %d", (int)x->data.shape.size());
+    mcb_status st = f_permute(x, {1, 0}, out);
+    if (st == MCB_OK && (*out)->node) (*out)->node->name = "Transpose";
+    return st;
+}
+
 mcb_status f_multi_head_attention(const Var &q, const Var &k, const Var &v, int64_t heads, bool causal, Var *out) {
     mcb_ctx *ctx = q->ctx;
     if (q->data.shape.size() != 3) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "attention expects [N, S, D]");
@@ -1200,8 +1240,8 @@ mcb_status AdamOpt::update(const std::vector<Var> &params, const float *inv_scal
         MCB_TRY(arena_wait_comm(a));
         double inv = inv_scale_host * arena_grad_divisor(a);
         int32_t t = a->step[0] + 1;
-        MCB_TRY(mcb_adam_flat_ex(ctx, (float *)a->p->p, a->g->p, MCB_F32, (float *)a->m->p, (float *)a->v->p, a->shadow->p, a->total, lr, beta1,
-                                 beta2, eps, t, inv, inv_scale_dev, skip, step_dev));
+        MCB_TRY(mcb_opt_flat(ctx, kind, (float *)a->p->p, a->g->p, MCB_F32, (float *)a->m->p, (float *)a->v->p, a->shadow->p, a->total, lr, beta1,
+                             beta2, eps, weight_decay, t, inv, inv_scale_dev, skip, step_dev));
         // the step counter advances on the host even if the device skips: a skipped step must not
         // count, so callers that pass `skip` roll it back through rollback_step() once they know
         for (auto &s : a->step) s = t;
@@ -1216,9 +1256,9 @@ mcb_status AdamOpt::update(const std::vector<Var> &params, const float *inv_scal
             int i = p->arena_idx;
             int32_t t = ++pa->step[i];
             int64_t off = pa->off[i];
-            MCB_TRY(mcb_adam_flat_ex(ctx, (float *)pa->p->p + off, (float *)pa->g->p + off, MCB_F32, (float *)pa->m->p + off, (float *)pa->v->p + off,
-                                     (__nv_bfloat16 *)pa->shadow->p + off, pa->size[i], lr, beta1, beta2, eps, t, inv_scale_host * arena_grad_divisor(pa),
-                                     inv_scale_dev, skip, step_dev));
+            MCB_TRY(mcb_opt_flat(ctx, kind, (float *)pa->p->p + off, (float *)pa->g->p + off, MCB_F32, (float *)pa->m->p + off, (float *)pa->v->p + off,
+                                 (__nv_bfloat16 *)pa->shadow->p + off, pa->size[i], lr, beta1, beta2, eps, weight_decay, t,
+                                 inv_scale_host * arena_grad_divisor(pa), inv_scale_dev, skip, step_dev));
             continue;
         }
         AdamState &st = state[p.get()];
@@ -1231,8 +1271,8 @@ mcb_status AdamOpt::update(const std::vector<Var> &params, const float *inv_scal
         st.t += 1;
         Tensor gf;
         MCB_TRY(to_dtype(ctx, p->grad, MCB_F32, &gf));
-        MCB_TRY(mcb_adam_flat_ex(ctx, (float *)p->data.ptr, gf.ptr, MCB_F32, (float *)st.m.ptr, (float *)st.v.ptr, nullptr, p->data.numel(), lr, beta1, beta2,
-                                 eps, st.t, inv_scale_host, inv_scale_dev, skip, step_dev));
+        MCB_TRY(mcb_opt_flat(ctx, kind, (float *)p->data.ptr, gf.ptr, MCB_F32, (float *)st.m.ptr, (float *)st.v.ptr, nullptr, p->data.numel(), lr, beta1,
+                             beta2, eps, weight_decay, st.t, inv_scale_host, inv_scale_dev, skip, step_dev));
     }
     return MCB_OK;
 }

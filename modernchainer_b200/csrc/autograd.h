@@ -97,6 +97,8 @@ mcb_status f_softmax_cross_entropy(const Var &logits, const Var &target, Var *ou
 mcb_status f_sce_consuming(const Var &logits, const Var &target, Var *out);
 mcb_status f_embedding(const Var &ids, const Var &weight, Var *out);
 mcb_status f_reshape(const Var &x, const std::vector<int64_t> &shape, Var *out);
+mcb_status f_permute(const Var &x, const std::vector<int32_t> &axes, Var *out);
+mcb_status f_transpose(const Var &x, Var *out);
 mcb_status f_multi_head_attention(const Var &q, const Var &k, const Var &v, int64_t heads, bool causal, Var *out);
 mcb_status f_conv2d(const Var &x, const Var &w, const Var &b, int64_t stride, int64_t pad, Var *out);
 mcb_status f_max_pool2d(const Var &x, int64_t kernel, int64_t stride, int64_t pad, Var *out);
@@ -119,6 +121,8 @@ struct AdamState {
 struct AdamOpt {
     mcb_ctx *ctx = nullptr;
     double lr = 1e-3, beta1 = 0.9, beta2 = 0.999, eps = 1e-8;
+    int kind = MCB_OPT_ADAM;      // MCB_OPT_*: Adam, AdamW, SGD, MomentumSGD (beta1 = momentum) on the same flat pass
+    double weight_decay = 0.0;    // AdamW only
     std::unordered_map<VarImpl *, AdamState> state;
     mcb_status update(const std::vector<Var> &params, const float *inv_scale_dev = nullptr, double inv_scale_host = 1.0,
                       const int32_t *skip = nullptr, const int32_t *step_dev = nullptr);

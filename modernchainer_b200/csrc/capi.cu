@@ -200,6 +200,15 @@ mcb_status mcb_f_reshape(mcb_var *x, const int64_t *dims, int32_t rank, mcb_var 
     Var r;
     return wrap(f_reshape(x->v, std::vector<int64_t>(dims, dims + rank), &r), r, out);
 }
+mcb_status mcb_f_transpose(mcb_var *x, mcb_var **out) {
+    Var r;
+    return wrap(f_transpose(x->v, &r), r, out);
+}
+mcb_status mcb_f_permute(mcb_var *x, const int32_t *axes, int32_t rank, mcb_var **out) {
+    Var r;
+    if (rank < 0 || (rank > 0 && !axes)) return MCB_INVALID_ARGUMENT;
+    return wrap(f_permute(x->v, std::vector<int32_t>(axes, axes + rank), &r), r, out);
+}
 mcb_status mcb_f_multi_head_attention(mcb_var *q, mcb_var *k, mcb_var *v, int64_t heads, int32_t causal, mcb_var **out) {
     Var r;
     return wrap(f_multi_head_attention(q->v, k->v, v->v, heads, causal != 0, &r), r, out);
@@ -248,6 +257,126 @@ mcb_status mcb_adam_create(mcb_ctx *ctx, double lr, double beta1, double beta2, 
 }
 void mcb_adam_release(mcb_adam *opt) { delete opt; }
 mcb_status mcb_adam_step(mcb_adam *opt, mcb_var **params, int32_t n) { return opt->opt.update(collect(params, n)); }
+
+mcb_status mcb_opt_create(mcb_ctx *ctx, int32_t kind, double lr, double beta1, double beta2, double eps, double weight_decay,
+                          mcb_adam **out) {
+    MCB_CHECK_CTX(ctx);
+    if (kind < MCB_OPT_ADAM || kind > MCB_OPT_MOMENTUM_SGD) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "unknown optimizer kind %d", kind);
+    mcb_adam *o = new mcb_adam();
+    o->opt.ctx = ctx;
+    o->opt.kind = kind;
+    o->opt.lr = lr;
+    o->opt.beta1 = beta1;
+    o->opt.beta2 = beta2;
+    o->opt.eps = eps;
+    o->opt.weight_decay = kind == MCB_OPT_ADAMW ? weight_decay : 0.0;
+    *out = o;
+    return MCB_OK;
+}
+mcb_status mcb_opt_set_lr(mcb_adam *opt, double lr) {
+    if (!opt) return MCB_INVALID_ARGUMENT;
+    opt->opt.lr = lr;
+    return MCB_OK;
+}
+mcb_status mcb_opt_get_lr(mcb_adam *opt, double *lr_out) {
+    if (!opt || !lr_out) return MCB_INVALID_ARGUMENT;
+    *lr_out = opt->opt.lr;
+    return MCB_OK;
+}
+
+mcb_status mcb_clip_grad_norm(mcb_var **params, int32_t n, double max_norm, double *norm_out) {
+    std::vector<Var> ps = collect(params, n);
+    mcb_ctx *ctx = nullptr;
+    for (auto &p : ps)
+        if (p) ctx = p->ctx;
+    if (!ctx) {
+        if (norm_out) *norm_out = 0.0;
+        return max_norm > 0.0 ? MCB_OK : MCB_INVALID_ARGUMENT;
+    }
+    if (!(max_norm > 0.0)) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "max_norm must be positive");
+    // gradient ranges: the whole flat arena in one piece when every parameter of it is listed and has a gradient
+    struct Range {
+        float *g;
+        int64_t n;
+    };
+    std::vector<Range> ranges;
+    Arena *a = ps[0]->arena;
+    bool flat = a && ps.size() == a->vars.size();
+    for (size_t i = 0; i < ps.size() && flat; ++i) flat = ps[i]->arena == a && ps[i]->arena_idx == (int)i && ps[i]->has_grad;
+    std::vector<Tensor> keep;
+    if (flat) {
+        MCB_TRY(arena_wait_comm(a));
+        ranges.push_back({(float *)a->g->p, a->total}); // padding between slots is zero
+    } else {
+        for (auto &p : ps) {
+            if (!p->has_grad) continue;
+            if (p->arena) MCB_TRY(arena_wait_comm(p->arena));
+            if (p->grad.dt != MCB_F32) { // clip in f32, as the reference's gradients are
+                Tensor gf;
+                MCB_TRY(to_dtype(ctx, p->grad, MCB_F32, &gf));
+                p->grad = gf;
+            }
+            ranges.push_back({(float *)p->grad.ptr, p->grad.numel()});
+        }
+    }
+    int total_blocks = 0;
+    std::vector<int> blocks(ranges.size());
+    for (size_t i = 0; i < ranges.size(); ++i) {
+        blocks[i] = mcb_sumsq_blocks(ctx, ranges[i].n);
+        if (!flat && blocks[i] > 64) blocks[i] = 64;
+        total_blocks += blocks[i];
+    }
+    void *scratch;
+    MCB_TRY(mcb_scratch(ctx, sizeof(double) * (size_t)(total_blocks + 2), &scratch));
+    double *partial = (double *)scratch, *clip = partial + total_blocks;
+    int at = 0;
+    for (size_t i = 0; i < ranges.size(); ++i) {
+        MCB_TRY(mcb_sumsq_partial(ctx, ranges[i].g, ranges[i].n, partial + at, blocks[i]));
+        at += blocks[i];
+    }
+    MCB_TRY(mcb_clip_finalize(ctx, partial, total_blocks, max_norm, clip));
+    for (auto &r : ranges) MCB_TRY(mcb_scale_by_clip(ctx, r.g, r.n, clip));
+    if (norm_out) MCB_TRY(mcb_memcpy_d2h(ctx, norm_out, clip, sizeof(double)));
+    return MCB_OK;
+}
+
+namespace {
+// f64::powi as compiler-rt computes it (binary exponentiation), so StepLR matches gamma.powi(e) bit for bit
+double powi_f64(double a, int32_t b) {
+    const bool recip = b < 0;
+    double r = 1.0;
+    for (;;) {
+        if (b & 1) r *= a;
+        b /= 2;
+        if (b == 0) break;
+        a *= a;
+    }
+    return recip ? 1.0 / r : r;
+}
+} // namespace
+
+double mcb_lr_linear_warmup_cosine(uint64_t step, uint64_t warmup_steps, uint64_t total_steps, double base_lr, double min_lr) {
+    if (step < warmup_steps) {
+        if (warmup_steps == 0) return base_lr;
+        return base_lr * (double)step / (double)warmup_steps;
+    }
+    if (step >= total_steps) return min_lr;
+    uint64_t span = total_steps - warmup_steps;
+    double denom = (double)(span < 1 ? 1 : span);
+    double progress = (double)(step - warmup_steps) / denom;
+    double c = cos(3.14159265358979323846 * progress) * 0.5 + 0.5;
+    return min_lr + (base_lr - min_lr) * c;
+}
+double mcb_lr_step(uint64_t step, double base_lr, uint64_t step_size, double gamma) {
+    uint64_t ss = step_size < 1 ? 1 : step_size;
+    return base_lr * powi_f64(gamma, (int32_t)(step / ss));
+}
+double mcb_lr_polynomial(uint64_t step, double base_lr, uint64_t total_steps, double power, double min_lr) {
+    if (step == 0) return base_lr;
+    double progress = (double)step / (double)(total_steps < 1 ? 1 : total_steps);
+    progress = progress < 0.0 ? 0.0 : (progress > 1.0 ? 1.0 : progress);
+    return min_lr + (base_lr - min_lr) * pow(1.0 - progress, power);
+}
 
 mcb_status mcb_scaler_create(mcb_ctx *ctx, double init_scale, double growth_factor, double backoff_factor,
                              int32_t growth_interval, mcb_scaler **out) {

@@ -81,5 +81,14 @@ mcb_status mcb_partial_sum_final(mcb_ctx *ctx, const float *partial, int parts, 
 mcb_status mcb_adam_flat_ex(mcb_ctx *ctx, float *p, const void *g, int32_t g_dt, float *m, float *v, void *p_bf16,
                             int64_t n, double lr, double beta1, double beta2, double eps, int32_t step,
                             double inv_scale, const float *inv_scale_dev, const int32_t *skip_flag, const int32_t *step_dev);
+// any optimizer of the family (MCB_OPT_*) as one fused in-place pass; see optim.cu
+mcb_status mcb_opt_flat(mcb_ctx *ctx, int32_t kind, float *p, const void *g, int32_t g_dt, float *m, float *v, void *p_bf16, int64_t n,
+                        double lr, double beta1, double beta2, double eps, double weight_decay, int32_t step, double inv_scale,
+                        const float *inv_scale_dev, const int32_t *skip_flag, const int32_t *step_dev);
+// global-norm clipping in three launches: per-block sums of squares (f64), {norm, factor}, conditional scale
+int mcb_sumsq_blocks(mcb_ctx *ctx, int64_t n);
+mcb_status mcb_sumsq_partial(mcb_ctx *ctx, const float *g, int64_t n, double *partial, int blocks);
+mcb_status mcb_clip_finalize(mcb_ctx *ctx, const double *partial, int count, double max_norm, double *out2);
+mcb_status mcb_scale_by_clip(mcb_ctx *ctx, float *g, int64_t n, const double *clip2);
 // scaler state on the device: {scale, inv_scale} floats then {growth_tracker, found_inf, last_found_inf, applied_steps} ints
 mcb_status mcb_scaler_update(mcb_ctx *ctx, float *state_f, int *state_i, float growth, float backoff, int interval);

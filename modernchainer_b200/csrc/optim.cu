@@ -10,6 +10,11 @@ constexpr int kThreads = 256;
 
 struct AdamK {
     float b1, b2, omb1, omb2, bc1, bc2, lr, eps, inv_scale;
+    // the rest of the optimizer family on the same flat pass (optim/src/lib.rs:23-51, 122-233)
+    float wd = 0.0f;   // AdamW: (f32)(weight_decay * lr), applied to the parameter value before the step
+    float nlr = 0.0f;  // SGD forms: (f32)(-lr)
+    float mom = 0.0f;  // MomentumSGD: (f32)momentum
+    int first = 0;     // MomentumSGD: no velocity yet, so velocity = gradient
 };
 
 // Rust f32::powi: repeated squaring in f32 (the reference computes 1 - beta^t this way,
@@ -66,7 +71,58 @@ __global__ void adam_update_kernel(const float *__restrict__ p, const float *__r
     }
 }
 
-template <typename GT>
+// One element of the other update rules, in the reference's operation order and without FMA:
+//   AdamW        : next = adam(p, ...); p' = next - p * (f32)(wd * lr)          (lib.rs:196-211)
+//   SGD          : p' = p + g * (f32)(-lr)                                      (lib.rs:38-41)
+//   MomentumSGD  : vel' = vel * (f32)mom + g (vel' = g on the first step); p' = p + vel' * (f32)(-lr)  (lib.rs:141-150)
+template <int KIND> __device__ __forceinline__ void opt_one(const AdamK &k, float g, float &p, float &m, float &v) {
+    if (KIND == MCB_OPT_ADAM) {
+        adam_one(k, g, p, m, v);
+    } else if (KIND == MCB_OPT_ADAMW) {
+        float decay = __fmul_rn(p, k.wd);
+        adam_one(k, g, p, m, v);
+        p = __fsub_rn(p, decay);
+    } else if (KIND == MCB_OPT_SGD) {
+        p = __fadd_rn(p, __fmul_rn(g, k.nlr));
+    } else {
+        float vel = k.first ? g : __fadd_rn(__fmul_rn(m, k.mom), g);
+        m = vel;
+        p = __fadd_rn(p, __fmul_rn(vel, k.nlr));
+    }
+}
+
+// SGD touches only p and g, MomentumSGD p, g and the velocity (kept where Adam keeps m)
+template <typename GT, int KIND>
+__global__ void __launch_bounds__(kThreads)
+sgd_flat_kernel(float *__restrict__ p, const GT *__restrict__ g, float *__restrict__ m, __nv_bfloat16 *__restrict__ shadow, long long n,
+                AdamK k, const float *__restrict__ inv_scale_dev, const int *__restrict__ skip, int vec) {
+    if (skip && *skip) return;
+    if (inv_scale_dev) k.inv_scale *= inv_scale_dev[0];
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    long long stride = (long long)gridDim.x * blockDim.x;
+    long long n4 = vec ? (n >> 2) : 0;
+    float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (long long j = i; j < n4; j += stride) {
+        float4 pp = reinterpret_cast<float4 *>(p)[j], gg = Elem<GT>::ld4(g, j);
+        float4 mm = KIND == MCB_OPT_MOMENTUM_SGD ? reinterpret_cast<float4 *>(m)[j] : zero, vv = zero;
+        opt_one<KIND>(k, gg.x * k.inv_scale, pp.x, mm.x, vv.x);
+        opt_one<KIND>(k, gg.y * k.inv_scale, pp.y, mm.y, vv.y);
+        opt_one<KIND>(k, gg.z * k.inv_scale, pp.z, mm.z, vv.z);
+        opt_one<KIND>(k, gg.w * k.inv_scale, pp.w, mm.w, vv.w);
+        reinterpret_cast<float4 *>(p)[j] = pp;
+        if (KIND == MCB_OPT_MOMENTUM_SGD) reinterpret_cast<float4 *>(m)[j] = mm;
+        if (shadow) Elem<__nv_bfloat16>::st4(shadow, j, pp);
+    }
+    for (long long j = (n4 << 2) + i; j < n; j += stride) {
+        float pp = p[j], mm = KIND == MCB_OPT_MOMENTUM_SGD ? m[j] : 0.0f, vv = 0.0f;
+        opt_one<KIND>(k, Elem<GT>::ld(g, j) * k.inv_scale, pp, mm, vv);
+        p[j] = pp;
+        if (KIND == MCB_OPT_MOMENTUM_SGD) m[j] = mm;
+        if (shadow) shadow[j] = __float2bfloat16_rn(pp);
+    }
+}
+
+template <typename GT, int KIND = MCB_OPT_ADAM>
 __global__ void __launch_bounds__(kThreads)
 adam_flat_kernel(float *__restrict__ p, const GT *__restrict__ g, float *__restrict__ m, float *__restrict__ v,
                  __nv_bfloat16 *__restrict__ shadow, long long n, AdamK k, const float *__restrict__ inv_scale_dev,
@@ -95,10 +151,10 @@ adam_flat_kernel(float *__restrict__ p, const GT *__restrict__ g, float *__restr
     for (long long j = i; j < n4; j += stride) {
         float4 pp = reinterpret_cast<float4 *>(p)[j], mm = reinterpret_cast<float4 *>(m)[j];
         float4 vv = reinterpret_cast<float4 *>(v)[j], gg = Elem<GT>::ld4(g, j);
-        adam_one(k, gg.x * k.inv_scale, pp.x, mm.x, vv.x);
-        adam_one(k, gg.y * k.inv_scale, pp.y, mm.y, vv.y);
-        adam_one(k, gg.z * k.inv_scale, pp.z, mm.z, vv.z);
-        adam_one(k, gg.w * k.inv_scale, pp.w, mm.w, vv.w);
+        opt_one<KIND>(k, gg.x * k.inv_scale, pp.x, mm.x, vv.x);
+        opt_one<KIND>(k, gg.y * k.inv_scale, pp.y, mm.y, vv.y);
+        opt_one<KIND>(k, gg.z * k.inv_scale, pp.z, mm.z, vv.z);
+        opt_one<KIND>(k, gg.w * k.inv_scale, pp.w, mm.w, vv.w);
         reinterpret_cast<float4 *>(p)[j] = pp;
         reinterpret_cast<float4 *>(m)[j] = mm;
         reinterpret_cast<float4 *>(v)[j] = vv;
@@ -106,7 +162,7 @@ adam_flat_kernel(float *__restrict__ p, const GT *__restrict__ g, float *__restr
     }
     for (long long j = (n4 << 2) + i; j < n; j += stride) {
         float pp = p[j], mm = m[j], vv = v[j];
-        adam_one(k, Elem<GT>::ld(g, j) * k.inv_scale, pp, mm, vv);
+        opt_one<KIND>(k, Elem<GT>::ld(g, j) * k.inv_scale, pp, mm, vv);
         p[j] = pp;
         m[j] = mm;
         v[j] = vv;
@@ -188,19 +244,106 @@ mcb_status mcb_check_finite(mcb_ctx *ctx, const void *g, int32_t g_dt, int64_t n
 mcb_status mcb_adam_flat_ex(mcb_ctx *ctx, float *p, const void *g, int32_t g_dt, float *m, float *v, void *p_bf16,
                             int64_t n, double lr, double beta1, double beta2, double eps, int32_t step,
                             double inv_scale, const float *inv_scale_dev, const int32_t *skip_flag, const int32_t *step_dev) {
-    if (step < 1) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "adam step must be >= 1");
+    return mcb_opt_flat(ctx, MCB_OPT_ADAM, p, g, g_dt, m, v, p_bf16, n, lr, beta1, beta2, eps, 0.0, step, inv_scale, inv_scale_dev, skip_flag,
+                        step_dev);
+}
+
+namespace {
+template <typename GT>
+void launch_opt(mcb_ctx *ctx, int kind, int grid, float *p, const GT *g, float *m, float *v, __nv_bfloat16 *sh, long long n, const AdamK &k,
+                const float *inv_scale_dev, const int32_t *skip, const int32_t *step_dev, int vec) {
+    cudaStream_t s = ctx->stream;
+    if (kind == MCB_OPT_ADAM) adam_flat_kernel<GT, MCB_OPT_ADAM><<<grid, kThreads, 0, s>>>(p, g, m, v, sh, n, k, inv_scale_dev, skip, step_dev, vec);
+    else if (kind == MCB_OPT_ADAMW) adam_flat_kernel<GT, MCB_OPT_ADAMW><<<grid, kThreads, 0, s>>>(p, g, m, v, sh, n, k, inv_scale_dev, skip, step_dev, vec);
+    else if (kind == MCB_OPT_SGD) sgd_flat_kernel<GT, MCB_OPT_SGD><<<grid, kThreads, 0, s>>>(p, g, m, sh, n, k, inv_scale_dev, skip, vec);
+    else sgd_flat_kernel<GT, MCB_OPT_MOMENTUM_SGD><<<grid, kThreads, 0, s>>>(p, g, m, sh, n, k, inv_scale_dev, skip, vec);
+}
+} // namespace
+
+// One fused in-place pass of any optimizer of the family over a flat range.  For the SGD forms
+// `beta1` carries the momentum, `v` is unused and `m` holds the velocity; `step` is the 1-based
+// count of this update (bias correction for Adam/AdamW, "no velocity yet" when 1 for MomentumSGD).
+mcb_status mcb_opt_flat(mcb_ctx *ctx, int32_t kind, float *p, const void *g, int32_t g_dt, float *m, float *v, void *p_bf16, int64_t n,
+                        double lr, double beta1, double beta2, double eps, double weight_decay, int32_t step, double inv_scale,
+                        const float *inv_scale_dev, const int32_t *skip_flag, const int32_t *step_dev) {
+    if (kind < MCB_OPT_ADAM || kind > MCB_OPT_MOMENTUM_SGD) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "unknown optimizer kind %d", kind);
+    if (step < 1) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "optimizer step must be >= 1");
     if (n == 0) return MCB_OK;
-    AdamK k = make_k(lr, beta1, beta2, eps, step, inv_scale);
-    int vec = mcb_aligned16(p) && mcb_aligned16(g) && mcb_aligned16(m) && mcb_aligned16(v) && (!p_bf16 || mcb_aligned16(p_bf16));
+    const bool adam = kind == MCB_OPT_ADAM || kind == MCB_OPT_ADAMW;
+    AdamK k = make_k(lr, adam ? beta1 : 0.9, adam ? beta2 : 0.999, eps, step, inv_scale);
+    k.wd = (float)(weight_decay * lr);
+    k.nlr = (float)(-lr);
+    k.mom = (float)beta1;
+    k.first = step == 1;
+    int vec = mcb_aligned16(p) && mcb_aligned16(g) && (!m || mcb_aligned16(m)) && (!v || mcb_aligned16(v)) && (!p_bf16 || mcb_aligned16(p_bf16));
     int grid = mcb_grid_for(ctx, (n + 3) / 4, kThreads, 8);
-    // algorithmic bytes per parameter: read p, m, v, g; write p, m, v (+ the bf16 shadow)
-    ProfScope prof(ctx, MCB_PROF_OPTIMIZER, 0.0, (double)n * (24.0 + (g_dt == MCB_BF16 ? 2.0 : 4.0) + (p_bf16 ? 2.0 : 0.0)));
-    if (g_dt == MCB_F32)
-        adam_flat_kernel<float><<<grid, kThreads, 0, ctx->stream>>>(p, (const float *)g, m, v, (__nv_bfloat16 *)p_bf16, n, k, inv_scale_dev, skip_flag, step_dev, vec);
+    // algorithmic bytes per parameter: read and write p plus the state the rule keeps, read g (+ the bf16 shadow)
+    double state_bytes = adam ? 16.0 : (kind == MCB_OPT_MOMENTUM_SGD ? 8.0 : 0.0);
+    ProfScope prof(ctx, MCB_PROF_OPTIMIZER, 0.0, (double)n * (8.0 + state_bytes + (g_dt == MCB_BF16 ? 2.0 : 4.0) + (p_bf16 ? 2.0 : 0.0)));
+    if (g_dt == MCB_F32) launch_opt<float>(ctx, kind, grid, p, (const float *)g, m, v, (__nv_bfloat16 *)p_bf16, n, k, inv_scale_dev, skip_flag, step_dev, vec);
     else if (g_dt == MCB_BF16)
-        adam_flat_kernel<__nv_bfloat16><<<grid, kThreads, 0, ctx->stream>>>(p, (const __nv_bfloat16 *)g, m, v, (__nv_bfloat16 *)p_bf16, n, k, inv_scale_dev, skip_flag, step_dev, vec);
-    else
-        return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "adam grads must be f32 or bf16");
+        launch_opt<__nv_bfloat16>(ctx, kind, grid, p, (const __nv_bfloat16 *)g, m, v, (__nv_bfloat16 *)p_bf16, n, k, inv_scale_dev, skip_flag, step_dev, vec);
+    else return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "optimizer grads must be f32 or bf16");
+    MCB_LAUNCHED(ctx);
+    return MCB_OK;
+}
+
+// ------------------------------------------------------------------ clip_grad_norm (optim/src/lib.rs:216-243)
+namespace {
+// per-block sum of g^2: the square in f32 (as ops.mul does), the sum in f64
+__global__ void sumsq_partial_kernel(const float *__restrict__ g, long long n, double *__restrict__ partial) {
+    __shared__ double red[kThreads / 32];
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    long long stride = (long long)gridDim.x * blockDim.x;
+    double acc = 0.0;
+    for (; i < n; i += stride) {
+        float x = g[i];
+        acc += (double)__fmul_rn(x, x);
+    }
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double t = 0.0;
+        for (int w = 0; w < kThreads / 32; ++w) t += red[w];
+        partial[blockIdx.x] = t;
+    }
+}
+// out[0] = norm, out[1] = factor (max_norm / norm when the norm exceeds max_norm and is positive, else 1)
+__global__ void clip_final_kernel(const double *__restrict__ partial, int count, double max_norm, double *__restrict__ out) {
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    double t = 0.0;
+    for (int i = 0; i < count; ++i) t += partial[i];
+    double norm = sqrt(t);
+    out[0] = norm;
+    out[1] = (norm > max_norm && norm > 0.0) ? max_norm / norm : 1.0;
+}
+__global__ void scale_by_clip_kernel(float *__restrict__ g, long long n, const double *__restrict__ clip) {
+    double f = clip[1];
+    if (f == 1.0) return; // within the limit: gradients stay untouched (no pass over memory)
+    float ff = (float)f;  // Ops::scale narrows the factor to f32 first
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    long long stride = (long long)gridDim.x * blockDim.x;
+    for (; i < n; i += stride) g[i] = __fmul_rn(g[i], ff);
+}
+} // namespace
+
+int mcb_sumsq_blocks(mcb_ctx *ctx, int64_t n) { return mcb_grid_for(ctx, n > 0 ? n : 1, kThreads, 4); }
+mcb_status mcb_sumsq_partial(mcb_ctx *ctx, const float *g, int64_t n, double *partial, int blocks) {
+    ProfScope prof(ctx, MCB_PROF_OPTIMIZER, 0.0, 4.0 * (double)n);
+    sumsq_partial_kernel<<<blocks, kThreads, 0, ctx->stream>>>(g, n, partial);
+    MCB_LAUNCHED(ctx);
+    return MCB_OK;
+}
+mcb_status mcb_clip_finalize(mcb_ctx *ctx, const double *partial, int count, double max_norm, double *out2) {
+    clip_final_kernel<<<1, 32, 0, ctx->stream>>>(partial, count, max_norm, out2);
+    MCB_LAUNCHED(ctx);
+    return MCB_OK;
+}
+mcb_status mcb_scale_by_clip(mcb_ctx *ctx, float *g, int64_t n, const double *clip2) {
+    if (n == 0) return MCB_OK;
+    ProfScope prof(ctx, MCB_PROF_OPTIMIZER, 0.0, 8.0 * (double)n);
+    scale_by_clip_kernel<<<mcb_grid_for(ctx, n, kThreads, 8), kThreads, 0, ctx->stream>>>(g, n, clip2);
     MCB_LAUNCHED(ctx);
     return MCB_OK;
 }

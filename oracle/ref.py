@@ -597,6 +597,29 @@ class F:
         return _apply(x.data.reshape(shape), [x], lambda g: [g.reshape(x.data.shape)])
 
     @staticmethod
+    def transpose(x):
+        """Transpose2d (autograd/src/ops.rs:235-255, cpu/src/kernels.rs:306-330): 2-D only; the
+        gradient is the transposed upstream gradient.  Pure data movement, so numpy is exact."""
+        if x.data.ndim != 2:
+            raise ValueError("transpose2d expects a 2-D tensor, got rank %d" % x.data.ndim)
+        return _apply(np.ascontiguousarray(x.data.T), [x], lambda g: [np.ascontiguousarray(g.T)])
+
+    @staticmethod
+    def permute(x, axes):
+        """PermuteOp (autograd/src/host_ops.rs:690-777): output dim d takes source axis axes[d];
+        backward applies the inverse permutation.  Errors follow permute_data (703-715)."""
+        axes = [int(a) for a in axes]
+        if len(axes) != x.data.ndim:
+            raise ValueError("permute rank mismatch")
+        if sorted(axes) != list(range(len(axes))):
+            raise ValueError("invalid permute axes")
+        inverse = [0] * len(axes)
+        for i, a in enumerate(axes):
+            inverse[a] = i
+        return _apply(np.ascontiguousarray(np.transpose(x.data, axes)), [x],
+                      lambda g: [np.ascontiguousarray(np.transpose(g, inverse))])
+
+    @staticmethod
     def conv2d(x, w, b, stride, pad):
         def bwd(g):
             dx, dw, db = conv2d_backward(x.data, w.data, g, stride, pad, b is not None)
@@ -648,6 +671,124 @@ class Adam:
             st["t"] += 1
             p.data, st["m"], st["v"] = adam_update(p.data, p.grad, st["m"], st["v"], self.lr, self.beta1, self.beta2,
                                                    self.eps, st["t"])
+
+
+class MomentumSGD:
+    """optim/src/lib.rs:122-160: velocity = previous*momentum + grad (the gradient itself on the first
+    update of a parameter), p += velocity * (-lr); every product narrows its factor to f32 first."""
+
+    def __init__(self, lr, momentum):
+        self.lr, self.momentum = lr, momentum
+        self.velocity = {}
+
+    def update(self, params):
+        for p in params:
+            if p.grad is None:
+                continue
+            prev = self.velocity.get(id(p))
+            vel = p.grad.copy() if prev is None else add(scale(prev, self.momentum), p.grad)
+            self.velocity[id(p)] = vel
+            p.data = add(p.data, scale(vel, -self.lr))
+
+
+class AdamW:
+    """optim/src/lib.rs:162-214: the Adam step, then next - scale(p_old, weight_decay*lr)."""
+
+    def __init__(self, lr, weight_decay, beta1=0.9, beta2=0.999, eps=1e-8):
+        self.lr, self.weight_decay, self.beta1, self.beta2, self.eps = lr, weight_decay, beta1, beta2, eps
+        self.state = {}
+
+    def update(self, params):
+        for p in params:
+            if p.grad is None:
+                continue
+            st = self.state.setdefault(id(p), {"m": np.zeros_like(p.data), "v": np.zeros_like(p.data), "t": 0})
+            st["t"] += 1
+            nxt, st["m"], st["v"] = adam_update(p.data, p.grad, st["m"], st["v"], self.lr, self.beta1, self.beta2, self.eps, st["t"])
+            p.data = sub(nxt, scale(p.data, self.weight_decay * self.lr))
+
+
+def clip_grad_norm(params, max_norm):
+    """optim/src/lib.rs:216-243: per parameter sum_all(g*g) (an f32 scalar), added up in f64; sqrt in f64;
+    if norm > max_norm the gradients are scaled by max_norm/norm (narrowed to f32).  Returns the pre-clip norm."""
+    if max_norm <= 0.0:
+        raise ValueError("max_norm must be positive")
+    total = 0.0
+    for p in params:
+        if p.grad is not None:
+            total += float(sum_all(mul(p.grad, p.grad)))
+    norm = float(np.sqrt(np.float64(total)))
+    if norm > max_norm and norm > 0.0:
+        f = max_norm / norm
+        for p in params:
+            if p.grad is not None:
+                p.grad = scale(p.grad, f)
+    return norm
+
+
+def _powi_f64(a, b):
+    """f64::powi (binary exponentiation, as compiler-rt's __powidf2)."""
+    recip, r = b < 0, 1.0
+    b = abs(int(b))
+    while True:
+        if b & 1:
+            r *= a
+        b //= 2
+        if b == 0:
+            break
+        a *= a
+    return 1.0 / r if recip else r
+
+
+class LinearWarmupCosineLR:
+    """optim/src/lib.rs:247-270."""
+
+    def __init__(self, warmup_steps, total_steps, base_lr, min_lr):
+        self.warmup_steps, self.total_steps, self.base_lr, self.min_lr = warmup_steps, total_steps, base_lr, min_lr
+
+    def get_lr(self, step):
+        import math
+        if step < self.warmup_steps:
+            if self.warmup_steps == 0:
+                return self.base_lr
+            return self.base_lr * float(step) / float(self.warmup_steps)
+        if step >= self.total_steps:
+            return self.min_lr
+        denom = float(max(self.total_steps - self.warmup_steps, 1))
+        progress = float(step - self.warmup_steps) / denom
+        c = math.cos(math.pi * progress) * 0.5 + 0.5
+        return self.min_lr + (self.base_lr - self.min_lr) * c
+
+
+class StepLR:
+    """optim/src/lib.rs:272-284."""
+
+    def __init__(self, base_lr, step_size, gamma):
+        self.base_lr, self.step_size, self.gamma = base_lr, step_size, gamma
+
+    def get_lr(self, step):
+        return self.base_lr * _powi_f64(self.gamma, step // max(self.step_size, 1))
+
+
+class ConstantLR:
+    def __init__(self, lr):
+        self.lr = lr
+
+    def get_lr(self, step):
+        return self.lr
+
+
+class PolynomialLR:
+    """optim/src/lib.rs:297-311."""
+
+    def __init__(self, base_lr, total_steps, power, min_lr):
+        self.base_lr, self.total_steps, self.power, self.min_lr = base_lr, total_steps, power, min_lr
+
+    def get_lr(self, step):
+        if step == 0:
+            return self.base_lr
+        progress = min(max(float(step) / float(max(self.total_steps, 1)), 0.0), 1.0)
+        return self.min_lr + (self.base_lr - self.min_lr) * (1.0 - progress) ** self.power
 
 
 class GradScaler:

@@ -73,3 +73,26 @@ def test_host_bf16_helpers_match_oracle(oracle):
     x = np.random.default_rng(0).standard_normal(4096).astype(np.float32) * 3
     assert np.array_equal(mc.f32_to_bf16_bits(x), oracle.f32_to_bf16_bits(x))
     assert np.array_equal(mc.bf16_bits_to_f32(mc.f32_to_bf16_bits(x)), oracle.round_bf16(x))
+
+
+def test_lr_schedules_match_the_oracle_restatement():
+    """The schedules are host functions of the step (optim/src/lib.rs:245-326): the library's C entry
+    points against the oracle's restatement, bit for bit, including the edge cases the formulas carry
+    (zero warm-up, step past the end, step_size 0, total_steps 0)."""
+    import modernchainer_b200 as mc
+    from oracle import ref as oracle
+    steps = [0, 1, 2, 9, 10, 11, 99, 100, 101, 5000]
+    for args in [(10, 100, 1e-3, 1e-5), (0, 100, 3e-4, 0.0), (10, 10, 1e-3, 1e-4)]:
+        a, b = mc.LinearWarmupCosineLR(*args), oracle.LinearWarmupCosineLR(*args)
+        for s in steps:
+            assert a.get_lr(s) == b.get_lr(s), (args, s)
+    for args in [(0.1, 30, 0.5), (0.1, 0, 0.9), (1.0, 1, 1.1)]:
+        a, b = mc.StepLR(*args), oracle.StepLR(*args)
+        for s in steps:
+            assert a.get_lr(s) == b.get_lr(s), (args, s)
+    for args in [(1e-3, 100, 2.0, 1e-5), (1e-3, 0, 0.5, 0.0), (1e-3, 100, 1.0, 1e-4)]:
+        a, b = mc.PolynomialLR(*args), oracle.PolynomialLR(*args)
+        for s in steps:
+            ga, gb = a.get_lr(s), b.get_lr(s)
+            assert ga == gb or abs(ga - gb) <= 1e-15 * abs(gb), (args, s)  # pow() of two C libraries: last-bit room
+    assert mc.ConstantLR(0.3).get_lr(17) == 0.3

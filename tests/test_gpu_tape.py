@@ -47,6 +47,11 @@ CASES = {
     "div": (lambda F, xs: F.sum(F.div(xs[0], xs[1])), [([0.5, 1.2, -0.7, 0.3], (2, 2)), ([0.4, -0.9, 0.8, 1.1], (2, 2))]),
     "matmul": (lambda F, xs: F.sum(F.matmul(xs[0], xs[1])), [([0.2, -0.1, 0.4, 0.3, 0.2, -0.5], (2, 3)), ([0.1, 0.2, -0.3, 0.4, 0.5, -0.2], (3, 2))]),
     "relu": (lambda F, xs: F.sum(F.relu(xs[0])), [([-0.5, 0.2, 0.7, -1.2], (2, 2))]),
+    # attention scores as the reference's example composes them (facade/examples/transformer.rs:96-99)
+    "matmul_transpose_softmax": (lambda F, xs: F.sum(F.mul(F.matmul(F.softmax(F.matmul(xs[0], F.transpose(xs[1]))), xs[1]), xs[0])),
+                                 [([0.2, -0.1, 0.4, 0.3, 0.2, -0.5], (2, 3)), ([0.1, 0.2, -0.3, 0.4, 0.5, -0.2], (2, 3))]),
+    "permute_3d": (lambda F, xs: F.sum(F.mul(F.permute(xs[0], (2, 0, 1)), xs[1])),
+                   [([0.1 * i - 0.5 for i in range(24)], (2, 3, 4)), ([0.05 * i * (-1) ** i for i in range(24)], (4, 2, 3))]),
     "sqrt": (lambda F, xs: F.sum(F.sqrt(xs[0])), [([0.25, 0.5, 1.0, 2.0], (4,))]),
     "matmul_relu_chain": (lambda F, xs: F.sum(F.relu(F.add(F.matmul(xs[0], xs[1]), xs[2]))),
                           [([0.2, -0.3, 0.5, 0.1, 0.7, -0.2], (2, 3)), ([0.1, -0.2, 0.3, 0.4, 0.5, -0.6], (3, 2)), ([0.1, -0.1], (2,))]),
@@ -85,6 +90,41 @@ def test_reference_gradcheck_programs(mc, ctx, oracle, name):
     for a, b in zip(gv, ov):
         assert (a.grad is None) == (b.grad is None)
         close(a.grad, b.grad, 2e-5)
+
+
+def test_transpose_and_permute_layouts_and_errors(mc, ctx, oracle):
+    """Layout ops against the oracle (pure data movement: bit-exact), at sizes that cross the
+    32x32 transpose tile and with every axis order of a rank-4 tensor; error cases of
+    permute_data (autograd/src/host_ops.rs:703-715) and transpose2d (cpu/src/kernels.rs:306-312)."""
+    import itertools
+    rng = np.random.default_rng(5)
+    ops = mc.ops(ctx)
+    for r, c in [(1, 1), (3, 70), (65, 33), (128, 257)]:
+        a = rng.standard_normal((r, c)).astype(np.float32)
+        assert np.array_equal(ops.transpose2d(a), a.T)
+    a = rng.standard_normal((3, 4, 5, 6)).astype(np.float32)
+    for axes in itertools.permutations(range(4)):
+        assert np.array_equal(ops.permute(a, axes), np.transpose(a, axes)), axes
+    assert ops.permute(np.zeros((0, 3), np.float32), (1, 0)).shape == (3, 0)
+    for bad in [(0, 0, 1, 2), (0, 1, 2, 4), (0, 1, 2, -1)]:
+        with pytest.raises(mc.McbError) as e:
+            ops.permute(a, bad)
+        assert e.value.status == 5
+        with pytest.raises(ValueError):
+            oracle.F.permute(oracle.Variable(a), bad)
+    with pytest.raises(mc.McbError):
+        ops.permute(a, (0, 1, 2))
+    x3 = mc.Variable(ctx, a[0])
+    with pytest.raises(mc.McbError) as e:
+        mc.F.transpose(x3)
+    assert e.value.status == 5
+    # tape: gradient of a permuted tensor is the inverse permutation of the upstream gradient
+    gx, ox = mc.Variable(ctx, a[0]), oracle.Variable(a[0])  # [4, 5, 6] -> (1, 2, 0) -> [5, 6, 4]
+    up =rng.standard_normal((5, 6, 4)).astype(np.float32)
+    mc.F.sum(mc.F.mul(mc.F.permute(gx, (1, 2, 0)), mc.Variable.constant(ctx, up))).backward()
+    oracle.F.sum(oracle.F.mul(oracle.F.permute(ox, (1, 2, 0)), oracle.Variable.constant(up))).backward()
+    assert np.array_equal(gx.grad, ox.grad)
+    assert np.array_equal(gx.grad, np.transpose(up, (2, 0, 1)))
 
 
 def test_sce_and_embedding_programs(mc, ctx, oracle):
@@ -406,3 +446,66 @@ def test_fused_backward_passes_match_separate_kernels(mc, ctx, cfg):
     # gradients' split-K partial tiles are added in whatever order the CTAs finish: 1e-5 of the peak
     for i, (a, r) in enumerate(zip(gf, gu)):
         assert np.abs(a - r).max() <= 1e-5 * max(float(np.abs(r).max()), 1e-30), (i, shapes[i])
+
+
+@pytest.mark.parametrize("arena", [False, True])
+@pytest.mark.parametrize("which", ["sgd", "momentum", "adamw"])
+def test_optimizer_family_bit_exact_and_clip(mc, ctx, oracle, which, arena):
+    """SGD, MomentumSGD and AdamW (optim/src/lib.rs:23-51, 122-214) on the fused flat pass against
+    the oracle, which is given the gradients the GPU produced: parameters bit-identical after each of
+    four steps, through the arena and per tensor.  clip_grad_norm (216-243) before each update:
+    the returned norm within 1e-6 (f64 sums grouped differently), clipped gradients bit-identical
+    whenever both sides narrow the same factor to f32 (asserted through the parameters)."""
+    rng = np.random.default_rng(77)
+    x = rng.standard_normal((64, 40)).astype(np.float32)
+    y = rng.integers(0, 7, 64).astype(np.int64)
+    gm, om = mc.Model(ctx, "mlp", [40, 24, 7]), oracle.MLP((40, 24, 7))
+    gp, op = gm.parameters(), om.parameters()
+    if arena:
+        keep = mc.Arena(ctx, gp)
+    if which == "sgd":
+        go, oo = mc.SGD(ctx, 0.05), oracle.SGD(0.05)
+    elif which == "momentum":
+        go, oo = mc.MomentumSGD(ctx, 0.02, 0.9), oracle.MomentumSGD(0.02, 0.9)
+    else:
+        go, oo = mc.AdamW(ctx, 0.01, 0.1), oracle.AdamW(0.01, 0.1)
+    gx, gy = mc.Variable.constant(ctx, x), mc.Variable.constant(ctx, y)
+    for step in range(4):
+        mc.zero_grad(gp)
+        gm.loss(gx, gy).backward()
+        for a, b in zip(gp, op):
+            b.grad = a.grad.copy()
+        max_norm = 0.05 if step % 2 == 0 else 1e6  # clipped on even steps, left alone on odd ones
+        gn, on = mc.clip_grad_norm(gp, max_norm), oracle.clip_grad_norm(op, max_norm)
+        assert abs(gn - on) <= 1e-6 * on, (gn, on)
+        for i, (a, b) in enumerate(zip(gp, op)):
+            close(a.grad, b.grad, 1e-6)
+            b.grad = a.grad.copy()
+        go.update(gp)
+        oo.update(op)
+        for i, (a, b) in enumerate(zip(gp, op)):
+            assert np.array_equal(a.data, b.data), (which, step, i)
+    with pytest.raises(mc.McbError) as e:
+        mc.clip_grad_norm(gp, 0.0)
+    assert e.value.status == 5
+    go.lr = 0.5
+    assert go.lr == 0.5
+
+
+def test_sgd_and_momentum_fit_linear_regression(mc, ctx):
+    """crates/modern-chainer-optim/tests/optimizer.rs:40-56 on the GPU tape: same data, learning rates,
+    step counts and loss bounds."""
+    F = mc.F
+    for make, steps, bound in [(lambda: mc.SGD(ctx, 0.05), 200, 1e-3), (lambda: mc.MomentumSGD(ctx, 0.02, 0.9), 500, 1e-2)]:
+        w, b = mc.Variable(ctx, np.array([[0.3]], np.float32)), mc.Variable(ctx, np.zeros(1, np.float32))
+        opt = make()
+        x = mc.Variable(ctx, np.array([[1.0], [2.0], [3.0], [4.0]], np.float32))
+        t = mc.Variable.constant(ctx, np.array([[2.0], [4.0], [6.0], [8.0]], np.float32))
+        for i in range(steps):
+            d = F.sub(F.linear(x, w, b), t)
+            loss = F.mean(F.mul(d, d))
+            mc.zero_grad([w, b])
+            loss.backward()
+            opt.update([w, b])
+        d = F.sub(F.linear(x, w, b), t)
+        assert float(F.mean(F.mul(d, d)).data) < bound

@@ -254,3 +254,36 @@ def test_adam_fits_linear_regression(oracle):
         if float(loss.data.reshape(-1)[0]) < 1e-4:
             break
     assert float(loss.data.reshape(-1)[0]) < 1e-2
+
+
+def test_oracle_transpose_and_permute_follow_the_reference_index_rule():
+    """permute_data (autograd/src/host_ops.rs:703-735) restated as a scalar loop on a small tensor:
+    the value at source coordinates c lands at output coordinates (c[axes[0]], c[axes[1]], ...);
+    the oracle's numpy form must place every element identically, forward and backward."""
+    import itertools
+    from oracle import ref as oracle
+    dims = (2, 3, 4)
+    x = np.arange(24, dtype=np.float32).reshape(dims)
+    for axes in itertools.permutations(range(3)):
+        out_dims = [dims[a] for a in axes]
+        want = np.zeros(out_dims, np.float32)
+        for c in itertools.product(*[range(d) for d in dims]):
+            want[tuple(c[a] for a in axes)] = x[c]
+        v = oracle.Variable(x)
+        y = oracle.F.permute(v, axes)
+        assert np.array_equal(y.data, want)
+        up = np.arange(24, dtype=np.float32).reshape(out_dims) * 0.5
+        oracle.F.sum(oracle.F.mul(y, oracle.Variable.constant(up))).backward()
+        back = np.zeros(dims, np.float32)
+        for c in itertools.product(*[range(d) for d in dims]):
+            back[c] = up[tuple(c[a] for a in axes)]
+        assert np.array_equal(v.grad, back)
+    m = oracle.Variable(np.arange(6, dtype=np.float32).reshape(2, 3))
+    t = oracle.F.transpose(m)
+    assert np.array_equal(t.data, m.data.T) and t.data.flags["C_CONTIGUOUS"]
+    with pytest.raises(ValueError):
+        oracle.F.transpose(oracle.Variable(x))
+    with pytest.raises(ValueError):
+        oracle.F.permute(oracle.Variable(x), (0, 1))
+    with pytest.raises(ValueError):
+        oracle.F.permute(oracle.Variable(x), (0, 0, 1))
