@@ -360,6 +360,18 @@ double mcb_lr_linear_warmup_cosine(uint64_t step, uint64_t warmup_steps, uint64_
 double mcb_lr_step(uint64_t step, double base_lr, uint64_t step_size, double gamma);
 double mcb_lr_polynomial(uint64_t step, double base_lr, uint64_t total_steps, double power, double min_lr);
 
+/* Training checkpoint in the reference's `.mcn` container (crates/modern-chainer-serial/src/lib.rs:12-115:
+ * "MCHN0001", u32 count, per entry name / dtype tag / rank / u64 dims / u64 byte length / bytes, little-endian).
+ * Entries: `name` (f32 value) for every listed parameter; with `opt`: `name.opt_m`, `name.opt_v` (f32) and
+ * `name.opt_t` (i64 [1]); with `scaler`: `grad_scaler.state` (f32 {scale, inv_scale}) and `grad_scaler.counters`
+ * (i32 {growth_tracker, found_inf, last_found_inf, applied_steps}).  Both calls synchronise.  Load checks every
+ * entry (presence, dtype, shape) before it changes anything; a file that is not .mcn is InvalidArgument
+ * ("not a Modern Chainer .mcn file", lib.rs:41), an unreadable one Io. */
+mcb_status mcb_checkpoint_save(mcb_ctx *ctx, const char *path, const char *const *names, mcb_var **params, int32_t n,
+                               mcb_adam *opt_or_null, mcb_scaler *scaler_or_null);
+mcb_status mcb_checkpoint_load(mcb_ctx *ctx, const char *path, const char *const *names, mcb_var **params, int32_t n,
+                               mcb_adam *opt_or_null, mcb_scaler *scaler_or_null);
+
 /* The benchmark models, built from the nn initialisers (nn/src/lib.rs:38-73,141-147,185-191,
  * 246-271) and, for the decoder, the layout of llm/src/decoder.rs:98-140.
  *   kind 0: MLP  cfg = {in, hidden, out}

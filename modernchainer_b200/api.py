@@ -1,6 +1,7 @@
 """Python classes over the C ABI (include/mcb.h).  Host data are numpy arrays; bf16 host
 data are uint16 bit patterns.  Nothing here computes: every method forwards to libmcb.so."""
 import ctypes as C
+import os
 
 import numpy as np
 
@@ -748,6 +749,29 @@ def clip_grad_norm(params, max_norm):
     out = C.c_double()
     ctx.check(ctx.lib.mcb_clip_grad_norm(arr, n, float(max_norm), C.byref(out)))
     return out.value
+
+
+def _named(named_params):
+    names = [str(k).encode("utf-8") for k, _ in named_params]
+    arr, n = _handles([v for _, v in named_params])
+    cn = (C.c_char_p * max(1, n))(*names)
+    return cn, arr, n
+
+
+def save_checkpoint(path, named_params, optimizer=None, scaler=None):
+    """Parameters (and optimizer / GradScaler state) into one `.mcn` file, the reference's container
+    (crates/modern-chainer-serial/src/lib.rs:12-62).  named_params: [(name, Variable), ...]."""
+    cn, arr, n = _named(named_params)
+    ctx = named_params[0][1].ctx
+    ctx.check(ctx.lib.mcb_checkpoint_save(ctx.h, os.fsencode(path), cn, arr, n, optimizer.h if optimizer else None,
+                                          scaler.h if scaler else None))
+
+
+def load_checkpoint(path, named_params, optimizer=None, scaler=None):
+    cn, arr, n = _named(named_params)
+    ctx = named_params[0][1].ctx
+    ctx.check(ctx.lib.mcb_checkpoint_load(ctx.h, os.fsencode(path), cn, arr, n, optimizer.h if optimizer else None,
+                                          scaler.h if scaler else None))
 
 
 class LinearWarmupCosineLR:

@@ -673,6 +673,56 @@ class Adam:
                                                    self.eps, st["t"])
 
 
+_MCN_TAGS = {np.dtype(np.float32): 0, np.dtype(np.float64): 1, np.dtype(np.float16): 2, np.dtype(np.int32): 4,
+             np.dtype(np.int64): 5, np.dtype(np.uint8): 6, np.dtype(np.bool_): 7}
+
+
+def mcn_save(path, entries):
+    """serial/src/lib.rs:14-33: "MCHN0001", u32 count, then per (name, array): u32 name length, name,
+    u8 dtype tag, u32 rank, u64 dims, u64 byte length, bytes; all little-endian."""
+    import struct
+    with open(path, "wb") as f:
+        f.write(b"MCHN0001")
+        f.write(struct.pack("<I", len(entries)))
+        for name, arr in entries:
+            arr = np.ascontiguousarray(arr)
+            nb = name.encode("utf-8")
+            f.write(struct.pack("<I", len(nb)) + nb)
+            f.write(bytes([_MCN_TAGS[arr.dtype]]))
+            f.write(struct.pack("<I", arr.ndim))
+            for d in arr.shape:
+                f.write(struct.pack("<Q", d))
+            raw = arr.astype(arr.dtype.newbyteorder("<"), copy=False).tobytes()
+            f.write(struct.pack("<Q", len(raw)))
+            f.write(raw)
+
+
+def mcn_load(path):
+    """serial/src/lib.rs:35-62; returns [(name, array)] in file order."""
+    import struct
+    inv = {v: k for k, v in _MCN_TAGS.items()}
+    out = []
+    with open(path, "rb") as f:
+        if f.read(8) != b"MCHN0001":
+            raise ValueError("not a Modern Chainer .mcn file")
+        (count,) = struct.unpack("<I", f.read(4))
+        for _ in range(count):
+            (nl,) = struct.unpack("<I", f.read(4))
+            name = f.read(nl).decode("utf-8")
+            tag = f.read(1)[0]
+            if tag == 3:
+                dt = np.dtype(np.uint16)  # bf16 bit patterns
+            elif tag in inv:
+                dt = inv[tag]
+            else:
+                raise ValueError("unknown dtype tag %d" % tag)
+            (rank,) = struct.unpack("<I", f.read(4))
+            dims = [struct.unpack("<Q", f.read(8))[0] for _ in range(rank)]
+            (nbytes,) = struct.unpack("<Q", f.read(8))
+            out.append((name, np.frombuffer(f.read(nbytes), dt.newbyteorder("<")).astype(dt).reshape(dims)))
+    return out
+
+
 class MomentumSGD:
     """optim/src/lib.rs:122-160: velocity = previous*momentum + grad (the gradient itself on the first
     update of a parameter), p += velocity * (-lr); every product narrows its factor to f32 first."""

@@ -509,3 +509,65 @@ def test_sgd_and_momentum_fit_linear_regression(mc, ctx):
             opt.update([w, b])
         d = F.sub(F.linear(x, w, b), t)
         assert float(F.mean(F.mul(d, d)).data) < bound
+
+
+@pytest.mark.parametrize("arena", [False, True])
+def test_checkpoint_mcn_resume_is_bit_exact(mc, ctx, oracle, arena, tmp_path):
+    """Checkpoint in the reference's .mcn container: the file the library writes is read by the oracle's
+    restatement of serial/src/lib.rs (names, shapes, values, optimizer state, scaler state), a file the
+    oracle writes loads into the library, and training that resumes from the checkpoint continues bit for
+    bit like the run that never stopped (AMP encoder block, Adam, GradScaler with a non-default state)."""
+    rng = np.random.default_rng(11)
+    d, heads, ff = 64, 2, 128
+    x = rng.standard_normal((2, 32, d)).astype(np.float32)
+    t = rng.standard_normal((2, 32, d)).astype(np.float32)
+
+    def fresh():
+        m = mc.Model(ctx, "encoder", [d, heads, ff, 0])
+        ps = m.parameters()
+        keep = mc.Arena(ctx, ps) if arena else None
+        return m, ps, keep, mc.Adam(ctx, 1e-3), mc.GradScaler(ctx, 1024.0, 2.0, 0.5, 3)
+
+    def steps(m, ps, opt, sc, n):
+        gx, gt = mc.Variable.constant(ctx, x), mc.Variable.constant(ctx, t)
+        for _ in range(n):
+            mc.zero_grad(ps)
+            with mc.autocast(mc.BF16):
+                loss = m.loss(gx, gt)
+            sc.scale_loss(loss).backward()
+            sc.step(opt, ps)
+
+    m1, p1, k1, o1, s1 = fresh()
+    steps(m1, p1, o1, s1, 4)  # growth_interval 3: the scale has doubled once by now
+    path = str(tmp_path / "ckpt.mcn")
+    names = ["p%d" % i for i in range(len(p1))]
+    mc.save_checkpoint(path, list(zip(names, p1)), o1, s1)
+    entries = dict(oracle.mcn_load(path))
+    for n_, p in zip(names, p1):
+        assert np.array_equal(entries[n_], p.data) and entries[n_].dtype == np.float32
+        assert entries[n_ + ".opt_m"].shape == p.data.shape and entries[n_ + ".opt_t"].tolist() == [4]
+    assert entries["grad_scaler.state"][0] == 2048.0 and entries["grad_scaler.counters"].dtype == np.int32
+    steps(m1, p1, o1, s1, 3)
+
+    m2, p2, k2, o2, s2 = fresh()
+    mc.load_checkpoint(path, list(zip(names, p2)), o2, s2)
+    assert s2.scale == 2048.0
+    steps(m2, p2, o2, s2, 3)
+    for a, b in zip(p1, p2):
+        assert np.array_equal(a.data, b.data)
+    assert s1.scale == s2.scale and s1.growth_tracker == s2.growth_tracker
+
+    # a file written by the oracle loads (parameters only), a foreign file and a shape mismatch are refused
+    path2 = str(tmp_path / "oracle.mcn")
+    oracle.mcn_save(path2, [(n_, np.full(p.data.shape, 0.25, np.float32)) for n_, p in zip(names, p2)])
+    mc.load_checkpoint(path2, list(zip(names, p2)))
+    assert all(np.all(p.data == 0.25) for p in p2)
+    open(path2, "wb").write(b"garbage-not-mcn")
+    with pytest.raises(mc.McbError) as e:
+        mc.load_checkpoint(path2, list(zip(names, p2)))
+    assert e.value.status == 5
+    oracle.mcn_save(path2, [(n_, np.zeros((3,), np.float32)) for n_ in names])
+    with pytest.raises(mc.McbError) as e:
+        mc.load_checkpoint(path2, list(zip(names, p2)))
+    assert e.value.status == 1
+    assert all(np.all(p.data == 0.25) for p in p2)  # a refused file changes nothing

@@ -287,3 +287,24 @@ def test_oracle_transpose_and_permute_follow_the_reference_index_rule():
         oracle.F.permute(oracle.Variable(x), (0, 1))
     with pytest.raises(ValueError):
         oracle.F.permute(oracle.Variable(x), (0, 0, 1))
+
+
+def test_oracle_mcn_container_roundtrip_and_byte_layout(tmp_path):
+    """crates/modern-chainer-serial/tests/roundtrip.rs with the same two tensors, plus the byte layout
+    of serial/src/lib.rs:14-33 spelled out for the first entry."""
+    import struct
+    from oracle import ref as oracle
+    w = np.array([0.1, 0.2, 0.3, 0.4, 0.5, 0.6], np.float32).reshape(2, 3)
+    b = np.array([1.0, 2.0], np.float32)
+    path = str(tmp_path / "t.mcn")
+    oracle.mcn_save(path, [("W", w), ("b", b)])
+    loaded = oracle.mcn_load(path)
+    assert len(loaded) == 2 and loaded[0][0] == "W" and loaded[0][1].shape == (2, 3) and loaded[0][1].dtype == np.float32
+    assert np.array_equal(loaded[0][1], w) and np.array_equal(loaded[1][1], b)
+    raw = open(path, "rb").read()
+    want = b"MCHN0001" + struct.pack("<I", 2) + struct.pack("<I", 1) + b"W" + bytes([0]) + struct.pack("<I", 2) + \
+        struct.pack("<QQ", 2, 3) + struct.pack("<Q", 24) + w.tobytes()
+    assert raw[:len(want)] == want
+    open(path, "wb").write(b"NOTMCHN1" + raw[8:])
+    with pytest.raises(ValueError):
+        oracle.mcn_load(path)
