@@ -284,6 +284,28 @@ def run_ours(args, dist):
             prof[cname] = dict(launches=n.value, ms=ms.value, flops=fl.value, bytes=by.value)
     ctx.check(lib.mcb_prof_enable(ctx.h, 0))
 
+    # the same step captured as one CUDA Graph and replayed (single GPU): resident and end-to-end timings
+    graph = None
+    if args.graph and dist.world == 1:
+        step = mc.StaticStep(model, opt, x_np, y_np, scaler=scaler, autocast_dtype=mc.BF16 if cfg["amp"] else None)
+        for _ in range(args.warmup):
+            ctx.check(lib.mcb_static_step_run(step.h, None, None))
+        ctx.sync()
+        ctx.record(e0)
+        for _ in range(args.steps):
+            ctx.check(lib.mcb_static_step_run(step.h, None, None))
+        ctx.record(e1)
+        g_res = ctx.elapsed_ms(e0, e1) / args.steps
+        ctx.sync()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            ctx.check(lib.mcb_static_step_run(step.h, hx, hy))  # pinned host inputs copied every step
+            g_loss = step.loss()                                   # loss read back every step
+        g_e2e = (time.perf_counter() - t0) * 1e3 / args.steps
+        graph = {"ms_per_step": g_res, "samples_per_s": cfg["batch"] / (g_res / 1e3), "e2e_ms_per_step": g_e2e,
+                 "e2e_samples_per_s": cfg["batch"] / (g_e2e / 1e3), "kernels_per_step": step.kernels_per_step, "loss_last": g_loss}
+        step.close()
+
     ms_step = dist.max(ms_resident / args.steps)
     ms_step_e2e = dist.max(max(ms_e2e_dev, wall_e2e) / args.steps)
     global_batch = cfg["batch"] * dist.world
@@ -324,7 +346,7 @@ def run_ours(args, dist):
                     "d2h_bytes_per_step": 4, "ms_per_step": ms_step_e2e},
             "gpu_launches": int(launches), "clocks": clocks, "roofline": roof, "kernels": kernels,
             "model_tflops": step_flops(cfg) / (ms_step / 1e3) / 1e12, "loss_first": first_loss, "loss_last": last_loss,
-            "replicas_in_sync": in_sync,
+            "replicas_in_sync": in_sync, "cuda_graph_step": graph,
         }
     if dist.world > 1:
         ctx.check(lib.mcb_dp_shutdown(ctx.h))
@@ -539,6 +561,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--n-params", type=int, default=0, help="c5 only: number of parameters (default 125M)")
     ap.add_argument("--gemm", default="8192,3072,768", help="gemm workload: m,n,k[,a_mn,b_mn]")
+    ap.add_argument("--graph", action="store_true", help="also time the step captured as one CUDA Graph (single GPU)")
     ap.add_argument("--layers", type=int, default=0, help="c4 only: override the layer count (small cases for ncu captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup

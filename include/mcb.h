@@ -372,6 +372,13 @@ mcb_status mcb_checkpoint_save(mcb_ctx *ctx, const char *path, const char *const
 mcb_status mcb_checkpoint_load(mcb_ctx *ctx, const char *path, const char *const *names, mcb_var **params, int32_t n,
                                mcb_adam *opt_or_null, mcb_scaler *scaler_or_null);
 
+/* Whole-step CUDA Graph (cuda/src/graph.rs:261-603 GraphLinearTrainer, cuda/src/static_run.rs:1875-2096
+ * CudaStaticStep / LinearMseAdamStep): zero_grad + model loss (+ GradScaler scaling) + backward + optimizer update
+ * recorded once from the tape and replayed with a single launch.  Inputs live in fixed device buffers; _run copies
+ * host_x / host_y into them first (either may be NULL when the caller filled the buffers returned by _inputs).
+ * autocast_dt is -1 (f32) or MCB_BF16.  Declared after mcb_model below. */
+typedef struct mcb_static_step mcb_static_step;
+
 /* The benchmark models, built from the nn initialisers (nn/src/lib.rs:38-73,141-147,185-191,
  * 246-271) and, for the decoder, the layout of llm/src/decoder.rs:98-140.
  *   kind 0: MLP  cfg = {in, hidden, out}
@@ -384,6 +391,17 @@ mcb_status mcb_model_num_params(mcb_model *m, int32_t *out);
 mcb_status mcb_model_param(mcb_model *m, int32_t index, mcb_var **out); /* a new reference; release it */
 /* forward to the scalar loss: (x f32, labels int) for kinds 0,2; (x, target f32) for 1; (ids, targets int) for 3 */
 mcb_status mcb_model_loss(mcb_model *m, mcb_var *input, mcb_var *target, mcb_var **loss_out);
+
+/* static (graph-captured) training step; see the note at the typedef above.  Creating one changes no parameter
+ * (capture records, it does not execute).  Data-parallel arenas are Unsupported; per-kernel timing must be off. */
+mcb_status mcb_static_step_create(mcb_model *model, mcb_adam *opt, mcb_scaler *scaler_or_null, int32_t autocast_dt,
+                                  const int64_t *x_dims, int32_t x_rank, int32_t x_dt, const int64_t *y_dims, int32_t y_rank,
+                                  int32_t y_dt, mcb_static_step **out);
+mcb_status mcb_static_step_inputs(mcb_static_step *s, void **x_dev_out, void **y_dev_out);
+mcb_status mcb_static_step_run(mcb_static_step *s, const void *host_x_or_null, const void *host_y_or_null);
+mcb_status mcb_static_step_loss(mcb_static_step *s, float *loss_out); /* synchronises; the unscaled loss of the last run */
+mcb_status mcb_static_step_launches(mcb_static_step *s, int64_t *kernels_per_step_out);
+void mcb_static_step_release(mcb_static_step *s);
 
 /* ------------------------------------------------------------------ data parallel */
 /* No counterpart in the reference (it has no distributed training).  One process per GPU.

@@ -869,3 +869,57 @@ class Model:
     def loss(self, x, target):
         h = C.c_void_p()
         return _out(self.ctx, self.ctx.lib.mcb_model_loss(self.h, x.h, target.h, C.byref(h)), h)
+
+
+class StaticStep:
+    """One whole training step (zero_grad, loss, backward, optimizer update) captured as a CUDA Graph and
+    replayed with a single launch (the reference's CudaStaticStep, cuda/src/static_run.rs:1875-2096).
+    x_like / y_like give the shape and dtype of the fixed input buffers."""
+
+    def __init__(self, model, optimizer, x_like, y_like, scaler=None, autocast_dtype=None):
+        self.ctx = model.ctx
+        x_like, y_like = np.asarray(x_like), np.asarray(y_like)
+        self._xs, self._ys = (x_like.shape, x_like.dtype), (y_like.shape, y_like.dtype)
+        h = C.c_void_p()
+        self.ctx.check(self.ctx.lib.mcb_static_step_create(
+            model.h, optimizer.h, scaler.h if scaler else None, -1 if autocast_dtype is None else autocast_dtype,
+            _dims(x_like.shape), x_like.ndim, _DT_OF[x_like.dtype], _dims(y_like.shape), y_like.ndim, _DT_OF[y_like.dtype], C.byref(h)))
+        self.h = h
+        self._keep = (model, optimizer, scaler)
+
+    def _host(self, a, spec):
+        a = np.ascontiguousarray(a, spec[1])
+        if a.shape != tuple(spec[0]):
+            raise McbError(1, "static step input has shape %s, captured %s" % (a.shape, tuple(spec[0])))
+        return a
+
+    def run(self, x=None, y=None):
+        """Copies x / y (host arrays; None keeps the buffer's contents) and launches the graph; asynchronous,
+        but the host arrays may be reused as soon as this returns only if they are pageable (pinned: sync first)."""
+        hx = self._host(x, self._xs) if x is not None else None
+        hy = self._host(y, self._ys) if y is not None else None
+        self.ctx.check(self.ctx.lib.mcb_static_step_run(self.h, hx.ctypes.data if hx is not None else None,
+                                                        hy.ctypes.data if hy is not None else None))
+        self._last = (hx, hy)
+
+    def loss(self):
+        v = C.c_float()
+        self.ctx.check(self.ctx.lib.mcb_static_step_loss(self.h, C.byref(v)))
+        return v.value
+
+    @property
+    def kernels_per_step(self):
+        v = C.c_int64()
+        self.ctx.check(self.ctx.lib.mcb_static_step_launches(self.h, C.byref(v)))
+        return v.value
+
+    def close(self):
+        if self.h and self.ctx.h:  # a closed context has already freed everything the step owned
+            self.ctx.lib.mcb_static_step_release(self.h)
+        self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

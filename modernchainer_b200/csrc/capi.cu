@@ -1,25 +1,9 @@
 // extern "C" surface of the tape / optimizer / model handles (declared in include/mcb.h).
 #include <cstring>
 
-#include "autograd.h"
+#include "handles.h"
 
 using namespace mcbag;
-
-struct mcb_var {
-    Var v;
-};
-struct mcb_adam {
-    AdamOpt opt;
-};
-struct mcb_scaler {
-    Scaler *s;
-};
-struct mcb_arena {
-    Arena *a;
-};
-struct mcb_model {
-    Model *m;
-};
 
 static mcb_status wrap(mcb_status st, const Var &v, mcb_var **out) {
     if (st != MCB_OK) return st;

@@ -12,19 +12,9 @@
 #include <map>
 #include <string>
 
-#include "autograd.h"
+#include "handles.h"
 
 using namespace mcbag;
-
-struct mcb_var {
-    Var v;
-};
-struct mcb_adam {
-    AdamOpt opt;
-};
-struct mcb_scaler {
-    Scaler *s;
-};
 
 namespace {
 

@@ -46,6 +46,16 @@ struct mcb_ctx {
     };
     std::vector<ProfRec> prof;
     std::vector<cudaEvent_t> ev_pool;
+    // Stream capture of a static training step (static_step.cu).  While capture_id != 0 every block
+    // that is allocated or freed becomes the property of that step: the recorded kernels hold its
+    // address, so it may be reused inside the same step's captures but never handed to anyone else
+    // until the step is released.
+    int capture_id = 0;
+    int next_capture_id = 1;
+    int static_steps = 0; // live static steps: while > 0 an outgrown scratch buffer is parked, not freed
+    std::unordered_map<void *, int> graph_owner;
+    std::unordered_map<int, std::multimap<size_t, void *>> graph_free;
+    std::vector<void *> retired_scratch;
     // SM clock trace (mcb_clock_trace_*): a one-thread sampler kernel on its own stream
     cudaStream_t trace_stream = nullptr;
     unsigned long long *trace_buf = nullptr; // [0] = samples written, then (globaltimer ns, clock64) pairs

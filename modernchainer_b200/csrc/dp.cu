@@ -9,7 +9,7 @@
 #include <dlfcn.h>
 #include <nccl.h>
 
-#include "autograd.h"
+#include "handles.h"
 
 using namespace mcbag;
 
@@ -104,10 +104,6 @@ double arena_grad_divisor(Arena *a) {
 }
 
 } // namespace mcbag
-
-struct mcb_arena {
-    Arena *a;
-};
 
 extern "C" {
 

@@ -85,6 +85,10 @@ mcb_status mcb_adam_flat_ex(mcb_ctx *ctx, float *p, const void *g, int32_t g_dt,
 mcb_status mcb_opt_flat(mcb_ctx *ctx, int32_t kind, float *p, const void *g, int32_t g_dt, float *m, float *v, void *p_bf16, int64_t n,
                         double lr, double beta1, double beta2, double eps, double weight_decay, int32_t step, double inv_scale,
                         const float *inv_scale_dev, const int32_t *skip_flag, const int32_t *step_dev);
+// *counter += 1 on the stream (device-resident step count of a replayed graph without a GradScaler)
+mcb_status mcb_increment_i32(mcb_ctx *ctx, int32_t *counter);
+// runtime.cu: blocks owned by a released static step go back to the general pool
+extern "C" void mcb_release_capture_blocks(mcb_ctx *ctx, int capture_id);
 // global-norm clipping in three launches: per-block sums of squares (f64), {norm, factor}, conditional scale
 int mcb_sumsq_blocks(mcb_ctx *ctx, int64_t n);
 mcb_status mcb_sumsq_partial(mcb_ctx *ctx, const float *g, int64_t n, double *partial, int blocks);

@@ -95,9 +95,10 @@ template <int KIND> __device__ __forceinline__ void opt_one(const AdamK &k, floa
 template <typename GT, int KIND>
 __global__ void __launch_bounds__(kThreads)
 sgd_flat_kernel(float *__restrict__ p, const GT *__restrict__ g, float *__restrict__ m, __nv_bfloat16 *__restrict__ shadow, long long n,
-                AdamK k, const float *__restrict__ inv_scale_dev, const int *__restrict__ skip, int vec) {
+                AdamK k, const float *__restrict__ inv_scale_dev, const int *__restrict__ skip, const int *__restrict__ step_dev, int vec) {
     if (skip && *skip) return;
     if (inv_scale_dev) k.inv_scale *= inv_scale_dev[0];
+    if (step_dev) k.first = step_dev[0] == 0; // device-resident count of applied steps (replayed graphs)
     long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     long long stride = (long long)gridDim.x * blockDim.x;
     long long n4 = vec ? (n >> 2) : 0;
@@ -255,10 +256,19 @@ void launch_opt(mcb_ctx *ctx, int kind, int grid, float *p, const GT *g, float *
     cudaStream_t s = ctx->stream;
     if (kind == MCB_OPT_ADAM) adam_flat_kernel<GT, MCB_OPT_ADAM><<<grid, kThreads, 0, s>>>(p, g, m, v, sh, n, k, inv_scale_dev, skip, step_dev, vec);
     else if (kind == MCB_OPT_ADAMW) adam_flat_kernel<GT, MCB_OPT_ADAMW><<<grid, kThreads, 0, s>>>(p, g, m, v, sh, n, k, inv_scale_dev, skip, step_dev, vec);
-    else if (kind == MCB_OPT_SGD) sgd_flat_kernel<GT, MCB_OPT_SGD><<<grid, kThreads, 0, s>>>(p, g, m, sh, n, k, inv_scale_dev, skip, vec);
-    else sgd_flat_kernel<GT, MCB_OPT_MOMENTUM_SGD><<<grid, kThreads, 0, s>>>(p, g, m, sh, n, k, inv_scale_dev, skip, vec);
+    else if (kind == MCB_OPT_SGD) sgd_flat_kernel<GT, MCB_OPT_SGD><<<grid, kThreads, 0, s>>>(p, g, m, sh, n, k, inv_scale_dev, skip, step_dev, vec);
+    else sgd_flat_kernel<GT, MCB_OPT_MOMENTUM_SGD><<<grid, kThreads, 0, s>>>(p, g, m, sh, n, k, inv_scale_dev, skip, step_dev, vec);
+}
+__global__ void increment_i32_kernel(int *p) {
+    if (threadIdx.x == 0 && blockIdx.x == 0) p[0] += 1;
 }
 } // namespace
+
+mcb_status mcb_increment_i32(mcb_ctx *ctx, int32_t *counter) {
+    increment_i32_kernel<<<1, 32, 0, ctx->stream>>>(counter);
+    MCB_LAUNCHED(ctx);
+    return MCB_OK;
+}
 
 // One fused in-place pass of any optimizer of the family over a flat range.  For the SGD forms
 // `beta1` carries the momentum, `v` is unused and `m` holds the velocity; `step` is the 1-based

@@ -96,6 +96,9 @@ void mcb_ctx_destroy(mcb_ctx *ctx) {
     for (auto &kv : ctx->free_blocks) cudaFree(kv.second);
     for (auto &kv : ctx->live) cudaFree(kv.first);
     if (ctx->scratch) cudaFree(ctx->scratch);
+    for (void *p : ctx->retired_scratch) cudaFree(p);
+    for (auto &kv : ctx->graph_free)
+        for (auto &b : kv.second) cudaFree(b.second);
     if (ctx->trace_stream) {
         cudaStreamSynchronize(ctx->trace_stream);
         cudaStreamDestroy(ctx->trace_stream);
@@ -113,14 +116,27 @@ mcb_status mcb_alloc(mcb_ctx *ctx, size_t bytes, void **out) {
     if (!out) return MCB_INVALID_ARGUMENT;
     size_t sz = round_size(bytes);
     std::lock_guard<std::mutex> lk(ctx->mu);
-    auto it = ctx->free_blocks.find(sz);
     void *p = nullptr;
+    if (ctx->capture_id) {
+        // blocks this step already owns first (a second capture of the same step finds the first one's blocks)
+        auto &own = ctx->graph_free[ctx->capture_id];
+        auto g = own.find(sz);
+        if (g != own.end()) {
+            p = g->second;
+            own.erase(g);
+            ctx->live[p] = sz;
+            *out = p;
+            return MCB_OK;
+        }
+    }
+    auto it = ctx->free_blocks.find(sz);
     if (it != ctx->free_blocks.end()) {
         p = it->second;
         ctx->free_blocks.erase(it);
     } else {
         cudaSetDevice(ctx->device);
         cudaError_t e = cudaMalloc(&p, sz);
+        if (e != cudaSuccess && ctx->capture_id) return mcb_cuda_check(ctx, e, "alloc during stream capture");
         if (e != cudaSuccess) {
             // release cached blocks once and retry before giving up
             cudaGetLastError();
@@ -132,6 +148,7 @@ mcb_status mcb_alloc(mcb_ctx *ctx, size_t bytes, void **out) {
         }
         ctx->allocated_bytes += (int64_t)sz;
     }
+    if (ctx->capture_id) ctx->graph_owner[p] = ctx->capture_id;
     ctx->live[p] = sz;
     *out = p;
     return MCB_OK;
@@ -144,9 +161,26 @@ mcb_status mcb_free(mcb_ctx *ctx, void *ptr) {
     auto it = ctx->live.find(ptr);
     if (it == ctx->live.end()) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "free of a pointer this context did not allocate");
     // single stream: work already enqueued on the block finishes before any later user starts
-    ctx->free_blocks.emplace(it->second, ptr);
+    auto own = ctx->graph_owner.find(ptr);
+    if (own == ctx->graph_owner.end() && ctx->capture_id) own = ctx->graph_owner.emplace(ptr, ctx->capture_id).first;
+    if (own != ctx->graph_owner.end()) ctx->graph_free[own->second].emplace(it->second, ptr); // recorded kernels know this address
+    else ctx->free_blocks.emplace(it->second, ptr);
     ctx->live.erase(it);
     return MCB_OK;
+}
+
+// A static step is gone: its parked blocks return to the general pool, live ones become ordinary blocks.
+void mcb_release_capture_blocks(mcb_ctx *ctx, int capture_id) {
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    auto f = ctx->graph_free.find(capture_id);
+    if (f != ctx->graph_free.end()) {
+        for (auto &kv : f->second) ctx->free_blocks.emplace(kv.first, kv.second);
+        ctx->graph_free.erase(f);
+    }
+    for (auto it = ctx->graph_owner.begin(); it != ctx->graph_owner.end();) {
+        if (it->second == capture_id) it = ctx->graph_owner.erase(it);
+        else ++it;
+    }
 }
 
 mcb_status mcb_host_alloc(size_t bytes, void **host_out) {
@@ -325,7 +359,9 @@ mcb_status mcb_scratch(mcb_ctx *ctx, size_t bytes, void **out) {
         MCB_CUDA(ctx, cudaMalloc(&p, want));
         if (ctx->scratch) {
             std::lock_guard<std::mutex> lk(ctx->mu);
-            ctx->free_blocks.emplace(round_size(ctx->scratch_bytes), ctx->scratch);
+            // a captured step may have recorded the old address: park it instead of recycling it
+            if (ctx->static_steps > 0 || ctx->capture_id) ctx->retired_scratch.push_back(ctx->scratch);
+            else ctx->free_blocks.emplace(round_size(ctx->scratch_bytes), ctx->scratch);
         }
         ctx->scratch = p;
         ctx->scratch_bytes = want;

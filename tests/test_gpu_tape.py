@@ -571,3 +571,85 @@ def test_checkpoint_mcn_resume_is_bit_exact(mc, ctx, oracle, arena, tmp_path):
         mc.load_checkpoint(path2, list(zip(names, p2)))
     assert e.value.status == 1
     assert all(np.all(p.data == 0.25) for p in p2)  # a refused file changes nothing
+
+
+@pytest.mark.parametrize("case", ["mlp_f32_sgdm", "mlp_f32_adam_noarena", "decoder_amp_adam_scaler"])
+def test_static_step_graph_replay_equals_the_tape_step(mc, ctx, case):
+    """A captured step replayed N times against N ordinary tape steps from the same start: same
+    kernels, same order, same buffers' contents, so parameters, loss and GradScaler state must be
+    bit-identical after every step (weight gradients of the bf16 case use split-K adds whose order
+    may differ between any two runs: those parameters agree to 1e-6).  Creating the step must not
+    change a parameter, and eager ops between replays must not disturb it."""
+    rng = np.random.default_rng(3)
+    amp = case.startswith("decoder")
+    if amp:
+        kind, cfg = "decoder", [512, 128, 2, 256, 2, 0]
+        xs = [rng.integers(0, 512, (2, 64)).astype(np.int64) for _ in range(4)]
+        ys = [rng.integers(0, 512, (2, 64)).astype(np.int64) for _ in range(4)]
+    else:
+        kind, cfg = "mlp", [64, 32, 10]
+        xs = [rng.standard_normal((16, 64)).astype(np.float32) for _ in range(4)]
+        ys = [rng.integers(0, 10, 16).astype(np.int64) for _ in range(4)]
+
+    def make():
+        m = mc.Model(ctx, kind, cfg)
+        ps = m.parameters()
+        keep = None if case.endswith("noarena") else mc.Arena(ctx, ps)
+        opt = mc.MomentumSGD(ctx, 0.05, 0.9) if case.endswith("sgdm") else mc.Adam(ctx, 1e-3)
+        sc = mc.GradScaler(ctx, 4096.0, 2.0, 0.5, 2) if amp else None
+        return m, ps, keep, opt, sc
+
+    # tape run
+    m, ps, keep, opt, sc = make()
+    tape_losses, tape_params = [], []
+    for x, y in zip(xs, ys):
+        mc.zero_grad(ps)
+        gx, gy = mc.Variable.constant(ctx, x), mc.Variable.constant(ctx, y)
+        if amp:
+            with mc.autocast(mc.BF16):
+                loss = m.loss(gx, gy)
+            sc.scale_loss(loss).backward()
+            sc.step_async(opt, ps)
+        else:
+            loss = m.loss(gx, gy)
+            loss.backward()
+            opt.update(ps)
+        tape_losses.append(float(loss.data.reshape(-1)[0]))
+        tape_params.append([p.data.copy() for p in ps])
+    tape_scale = sc.scale if amp else None
+
+    # graph run
+    m2, ps2, keep2, opt2, sc2 = make()
+    before = [p.data.copy() for p in ps2]
+    step = mc.StaticStep(m2, opt2, xs[0], ys[0], scaler=sc2, autocast_dtype=mc.BF16 if amp else None)
+    assert all(np.array_equal(a, p.data) for a, p in zip(before, ps2))
+    assert step.kernels_per_step > 5
+    ops = mc.ops(ctx)
+    for i, (x, y) in enumerate(zip(xs, ys)):
+        step.run(x, y)
+        assert step.loss() == tape_losses[i], (i, step.loss(), tape_losses[i])
+        ops.binary(0, np.ones((1000,), np.float32), np.ones((1000,), np.float32))  # eager work (an add) between replays
+        for j, (p, want) in enumerate(zip(ps2, tape_params[i])):
+            if amp and p.data.ndim == 2:
+                assert np.abs(p.data - want).max() <= 1e-6 * max(float(np.abs(want).max()), 1e-30), (i, j)
+            else:
+                assert np.array_equal(p.data, want), (i, j)
+    if amp:
+        assert sc2.scale == tape_scale
+    # the tape can take over after the graph: optimizer step counters were advanced by the replays
+    mc.zero_grad(ps2)
+    mc.zero_grad(ps)
+    for mm, pp, oo, ss in [(m, ps, opt, sc), (m2, ps2, opt2, sc2)]:
+        gx, gy = mc.Variable.constant(ctx, xs[0]), mc.Variable.constant(ctx, ys[0])
+        if amp:
+            with mc.autocast(mc.BF16):
+                l = mm.loss(gx, gy)
+            ss.scale_loss(l).backward()
+            ss.step(oo, pp)
+        else:
+            mm.loss(gx, gy).backward()
+            oo.update(pp)
+    for j, (a, b) in enumerate(zip(ps, ps2)):
+        tol = 2e-6 if amp else 0.0
+        assert np.abs(a.data - b.data).max() <= tol * max(float(np.abs(a.data).max()), 1e-30), j
+    step.close()
