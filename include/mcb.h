@@ -393,7 +393,8 @@ mcb_status mcb_model_param(mcb_model *m, int32_t index, mcb_var **out); /* a new
 mcb_status mcb_model_loss(mcb_model *m, mcb_var *input, mcb_var *target, mcb_var **loss_out);
 
 /* static (graph-captured) training step; see the note at the typedef above.  Creating one changes no parameter
- * (capture records, it does not execute).  Data-parallel arenas are Unsupported; per-kernel timing must be off. */
+ * (capture records, it does not execute).  Per-kernel timing must be off.  With a data-parallel arena the bucket
+ * all-reduces are part of the graph; run at least one ordinary step first so that NCCL has set up its connections. */
 mcb_status mcb_static_step_create(mcb_model *model, mcb_adam *opt, mcb_scaler *scaler_or_null, int32_t autocast_dt,
                                   const int64_t *x_dims, int32_t x_rank, int32_t x_dt, const int64_t *y_dims, int32_t y_rank,
                                   int32_t y_dt, mcb_static_step **out);

@@ -126,9 +126,10 @@ mcb_status mcb_static_step_create(mcb_model *model, mcb_adam *opt, mcb_scaler *s
     if (ctx->capture_id) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "static step: another capture is in progress");
     if (dt_size(x_dt) == 0 || dt_size(y_dt) == 0 || x_rank < 0 || y_rank < 0) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "static step: bad input description");
     if (autocast_dt != -1 && autocast_dt != MCB_BF16) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "static step: autocast must be -1 (off) or bf16");
-    for (auto &p : model->m->params)
-        if (p->arena && p->arena->dp_attached)
-            return mcb_fail(ctx, MCB_UNSUPPORTED, "static step: data-parallel arenas are not captured; run the tape step instead");
+    // Data-parallel arenas are captured too: the bucket all-reduces are enqueued on the communication stream
+    // behind an event of the capturing stream, which pulls that stream into the capture, and the optimizer's
+    // wait on the communication stream joins it back.  NCCL must have run one eager step first (its lazy
+    // connection set-up is not capturable), which any warm-up step provides.
     auto s = std::make_unique<mcb_static_step>();
     s->ctx = ctx;
     s->model = model->m;
