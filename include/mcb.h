@@ -360,6 +360,11 @@ double mcb_lr_linear_warmup_cosine(uint64_t step, uint64_t warmup_steps, uint64_
 double mcb_lr_step(uint64_t step, double base_lr, uint64_t step_size, double gamma);
 double mcb_lr_polynomial(uint64_t step, double base_lr, uint64_t total_steps, double power, double min_lr);
 
+/* he_normal, core/src/init.rs:6-11 over Rng (core/src/rng.rs:14-56): the values nn::Linear / Conv2d / Embedding
+ * start from for a given seed, so that a link built above this library is bit-identical to the reference's.
+ * Host function (no context, no device). */
+mcb_status mcb_he_normal(float *host_out, int64_t n, int64_t fan_in, uint64_t seed);
+
 /* Training checkpoint in the reference's `.mcn` container (crates/modern-chainer-serial/src/lib.rs:12-115:
  * "MCHN0001", u32 count, per entry name / dtype tag / rank / u64 dims / u64 byte length / bytes, little-endian).
  * Entries: `name` (f32 value) for every listed parameter; with `opt`: `name.opt_m`, `name.opt_v` (f32) and

@@ -1593,3 +1593,14 @@ mcb_status Model::loss(const Var &input, const Var &target, Var *out) {
 }
 
 } // namespace mcbag
+
+// He-normal values exactly as the reference's links draw them (core/src/init.rs:6-11 over the
+// xorshift64* / polar Box-Muller generator of core/src/rng.rs:14-56); a host function.
+extern "C" mcb_status mcb_he_normal(float *host_out, int64_t n, int64_t fan_in, uint64_t seed) {
+    if (n < 0 || (n > 0 && !host_out)) return MCB_INVALID_ARGUMENT;
+    std::vector<float> h((size_t)n);
+    mcbag::Rng r(seed);
+    r.fill(h, 0.0, std::sqrt(2.0 / (double)(fan_in > 1 ? fan_in : 1)));
+    if (n) memcpy(host_out, h.data(), sizeof(float) * (size_t)n);
+    return MCB_OK;
+}

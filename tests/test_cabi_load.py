@@ -96,3 +96,26 @@ def test_lr_schedules_match_the_oracle_restatement():
             ga, gb = a.get_lr(s), b.get_lr(s)
             assert ga == gb or abs(ga - gb) <= 1e-15 * abs(gb), (args, s)  # pow() of two C libraries: last-bit room
     assert mc.ConstantLR(0.3).get_lr(17) == 0.3
+
+
+def test_chainer_facade_imports_without_a_gpu_and_refuses_to_compute():
+    """The facade package loads on a host without a GPU (host-side Tensor and initialiser work), but the
+    first Variable needs the device context and fails loudly: there is no CPU execution path."""
+    import ctypes as C
+    import modernchainer_b200.chainer as chainer
+    import modernchainer_b200.chainer.functions as F
+    import modernchainer_b200.chainer.links as L
+    import modernchainer_b200.chainer.optimizers as O
+    from oracle import ref as oracle
+    assert chainer.__version__ and chainer.vulkan_available() is False
+    t = chainer.Tensor.from_list([1.0, 2.0, 3.0, 4.0], [2, 2])
+    assert t.shape == [2, 2] and t.dtype == "f32" and t.device == "cpu" and t.astype("i64").dtype == "i64"
+    assert set(F.__all__) >= {"linear", "softmax_cross_entropy", "permute", "transpose"} and "Linear" in L.__all__ and "AdamW" in O.__all__
+    # the initialiser behind the links is the reference's generator: bit-identical to the oracle's restatement
+    for shape, fan_in, seed in [((3, 5), 5, 0), ((100, 784), 784, 0), ((64, 3, 3, 3), 27, 7), ((7,), 1, 123456789)]:
+        out = np.empty(int(np.prod(shape)), np.float32)
+        assert chainer._api._lib.load().mcb_he_normal(out.ctypes.data_as(C.c_void_p), out.size, fan_in, seed) == 0
+        assert np.array_equal(out.reshape(shape), oracle.he_normal(shape, fan_in, seed))
+    if not chainer.cuda_available():
+        with pytest.raises(Exception):
+            chainer.Variable(t)
