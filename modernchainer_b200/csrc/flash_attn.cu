@@ -409,6 +409,11 @@ mcb_status mcb_flash_forward(mcb_ctx *ctx, const void *q, const void *k, const v
     if (!mcb_aligned16(q) || !mcb_aligned16(k) || !mcb_aligned16(v) || !mcb_aligned16(out) || (dim % 8))
         return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "fused attention needs 16-byte aligned tensors");
     if (n * heads > 65535) return mcb_fail(ctx, MCB_UNSUPPORTED, "fused attention: n * heads > 65535");
+    // the tcgen05 / TMEM forward first; MCB_FLASH_LEGACY (test knob) keeps the mma.sync kernel
+    if (!getenv("MCB_FLASH_LEGACY")) {
+        mcb_status tc = mcb_flash_tc_forward(ctx, q, k, v, out, lse, n, seq, dim, heads, causal, ldi, ldo);
+        if (tc != MCB_UNSUPPORTED) return tc;
+    }
     float scale_log2 = (1.0f / sqrtf((float)HD)) * 1.4426950408889634f;
     dim3 grid((unsigned)((seq + TILE - 1) / TILE), (unsigned)(n * heads));
     if (causal)
