@@ -436,6 +436,14 @@ mcb_status mcb_flash_backward(mcb_ctx *ctx, const void *q, const void *k, const 
     MCB_TRY(mcb_alloc(ctx, sizeof(float) * rows, &delta));
     flash_delta_kernel<<<(unsigned)((rows * 32 + 255) / 256), 256, 0, ctx->stream>>>((const bf16 *)out, (const bf16 *)gout, (float *)delta, (int)seq, (int)ldo, (int)heads, rows);
     ctx->launches++;
+    // the tcgen05 / TMEM kernels first; MCB_FLASH_LEGACY (test knob) keeps the mma.sync pair
+    if (!getenv("MCB_FLASH_LEGACY") && !getenv("MCB_FLASH_LEGACY_BWD")) {
+        mcb_status tc = mcb_flash_tc_backward(ctx, q, k, v, gout, lse, (const float *)delta, dq, dk, dv, n, seq, dim, heads, causal, ldi, ldo, ldg);
+        if (tc != MCB_UNSUPPORTED) {
+            mcb_free(ctx, delta); // stream-ordered reuse
+            return tc;
+        }
+    }
     dim3 grid((unsigned)((seq + TILE - 1) / TILE), (unsigned)(n * heads));
     if (causal) {
         flash_dkv_kernel<true><<<grid, kThreads, 0, ctx->stream>>>((const bf16 *)q, (const bf16 *)k, (const bf16 *)v, (const bf16 *)gout, lse, (const float *)delta, (bf16 *)dk, (bf16 *)dv, (int)seq, (int)ldi, (int)ldo, (int)ldg, (int)heads, scale, scale_log2);

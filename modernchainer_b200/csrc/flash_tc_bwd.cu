@@ -1,0 +1,382 @@
+// Fused attention backward on the tcgen05 tensor cores (bf16, head_dim 64), two kernels from one template:
+//   MODE 0 (dK, dV): one CTA per 128-key tile; K_j, V_j stay in shared memory, the query tiles stream through.
+//   MODE 1 (dQ)    : one CTA per 128-query tile; Q_i, dO_i stay, the key tiles stream through.
+// Per (query tile, key tile) pair, with rows = queries (TMEM lanes) and columns = keys:
+//   S  = Q K^T, dP = dO V^T         tcgen05.mma M=128 N=128 K=64 each, both into TMEM
+//   P  = exp2(S * scale*log2e - lse*log2e),  dS = P * (dP - delta)     (masked pairs give 0)
+//        eight warps, two per TMEM lane quarter, each thread takes 64 keys of its query row: one TMEM round
+//        trip for S and dP, independent arithmetic per element, results packed to bf16 into shared memory as
+//        [key block][query block][64 queries][64 keys] atoms of 8 KB with the 128-byte swizzle.  That one
+//        layout serves as the K-major operand dS (for dQ) and as the MN-major operands P^T, dS^T (for dV, dK).
+//   MODE 0: dV += P^T dO, dK += dS^T Q   M=128 (keys) N=64 K=128 (queries), accumulators in TMEM for the whole walk
+//   MODE 1: dQ += dS K                   M=128 (queries) N=64 K=128 (keys)
+// The next pair's S / dP are issued as soon as the rows have read the current ones, so they run under the
+// exponentials; the 1/sqrt(hd) factor is applied once, to dK and dQ, in the epilogue.
+// delta = rowsum(O * dO) and the log-sum-exp come from the forward pass / a small pre-kernel.
+// Roles (320 threads): warp 0 TMA, warp 1 MMA + TMEM, warps 2..9 the pair arithmetic and the epilogue.
+// Every mbarrier wait is bounded; on expiry the CTA raises the device error word and drains.
+#include "internal.h"
+#include "tc_ptx.cuh"
+
+using namespace tcptx;
+
+namespace {
+
+constexpr int HD = 64;
+constexpr int BT = 128;  // tile edge: queries and keys per tile
+constexpr int kThreads = 320;
+constexpr int kTileBytes = BT * HD * 2;  // 16 KB
+// shared memory: X0 X1 (resident pair) | Y0 Y1 x 2 stages (streamed pair) | P | dS | barriers
+constexpr int kSmemX = 0, kSmemY = 2 * kTileBytes, kSmemP = kSmemY + 4 * kTileBytes, kSmemDS = kSmemP + 2 * kTileBytes,
+              kSmemBar = kSmemDS + 2 * kTileBytes;
+constexpr int kSmemBytes = kSmemBar + 128 + 1024;
+constexpr unsigned kTmemCols = 512;
+constexpr unsigned kColS = 0, kColDP = 128, kColAcc0 = 256, kColAcc1 = 320;
+
+struct BwdArgs {
+    const float *lse, *delta;  // [n, heads, seq]
+    int seq, heads, causal;
+    float scale, scale_log2;
+    unsigned int *err;
+};
+
+template <int MODE>
+__global__ void __launch_bounds__(kThreads, 1)
+flash_tc_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                    const __grid_constant__ CUtensorMap map_do, const __grid_constant__ CUtensorMap map_out0,
+                    const __grid_constant__ CUtensorMap map_out1, BwdArgs args) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char *smem = (unsigned char *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    unsigned char *sX0 = smem + kSmemX, *sX1 = sX0 + kTileBytes, *sP = smem + kSmemP, *sDS = smem + kSmemDS;
+    unsigned long long *bars = (unsigned long long *)(smem + kSmemBar);
+    unsigned long long *x_full = bars, *y_full = bars + 1, *y_empty = bars + 3, *sd_full = bars + 5, *sd_free = bars + 6, *pds_full = bars + 7,
+                       *mma_done = bars + 8;
+    unsigned *tmem_slot = (unsigned *)(bars + 9);
+    volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n = blockIdx.y / args.heads, h = blockIdx.y % args.heads;
+    const int tiles = (args.seq + BT - 1) / BT;
+    // MODE 0: this CTA owns key tile `own`; query tiles own..tiles-1 (causal) or all stream through.
+    // MODE 1: this CTA owns query tile `own` (late tiles first when causal: they walk the most key tiles);
+    //         key tiles 0..own (causal) or all stream through.
+    const int own = (MODE == 1 && args.causal) ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;
+    const int t_first = (MODE == 0 && args.causal) ? own : 0;
+    const int nt = (MODE == 0) ? tiles - t_first : (args.causal ? own + 1 : tiles);
+    const int o0 = own * BT;
+
+    if (threadIdx.x == 0) {
+        mbar_init(x_full, 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&y_full[s], 1);
+            mbar_init(&y_empty[s], 1);
+        }
+        mbar_init(sd_full, 1);
+        mbar_init(sd_free, 8);
+        mbar_init(pds_full, 8);
+        mbar_init(mma_done, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const unsigned tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            mbar_expect_tx(x_full, 2 * kTileBytes);
+            if (MODE == 0) {
+                tma_load_3d(sX0, &map_k, x_full, h * HD, o0, n);
+                tma_load_3d(sX1, &map_v, x_full, h * HD, o0, n);
+            } else {
+                tma_load_3d(sX0, &map_q, x_full, h * HD, o0, n);
+                tma_load_3d(sX1, &map_do, x_full, h * HD, o0, n);
+            }
+            bool ok = true;
+            for (int t = 0; t < nt && ok; ++t) {
+                const int st = t & 1;
+                ok = mbar_wait(&y_empty[st], ((t >> 1) & 1) ^ 1u, abort_flag, args.err);
+                if (!ok) break;
+                unsigned char *y0 = smem + kSmemY + st * 2 * kTileBytes, *y1 = y0 + kTileBytes;
+                const int r0 = (t_first + t) * BT;
+                mbar_expect_tx(&y_full[st], 2 * kTileBytes);
+                if (MODE == 0) {
+                    tma_load_3d(y0, &map_q, &y_full[st], h * HD, r0, n);
+                    tma_load_3d(y1, &map_do, &y_full[st], h * HD, r0, n);
+                } else {
+                    tma_load_3d(y0, &map_k, &y_full[st], h * HD, r0, n);
+                    tma_load_3d(y1, &map_v, &y_full[st], h * HD, r0, n);
+                }
+            }
+            for (int st = 0; st < 2 && ok; ++st) { // drain
+                int fills = (nt > st) ? ((nt - 1 - st) / 2 + 1) : 0;
+                if (fills) ok = mbar_wait(&y_empty[st], (unsigned)(fills - 1) & 1u, abort_flag, args.err);
+            }
+            if (*abort_flag) {
+                unsigned long long t0 = global_ns();
+                while (global_ns() - t0 < 200000ull) {
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr unsigned idesc_sd = make_idesc(BT, BT, 0, 0);                       // S, dP: both operands K-major
+            constexpr unsigned idesc_acc = make_idesc(BT, HD, MODE == 0 ? 1 : 0, 1);      // MODE 0: A = P^T / dS^T (MN-major); MODE 1: A = dS (K-major)
+            const unsigned x0 = smem_u32(sX0), x1 = smem_u32(sX1), p_addr = smem_u32(sP), ds_addr = smem_u32(sDS);
+            bool ok = mbar_wait(x_full, 0, abort_flag, args.err);
+            auto issue_sd = [&](int t) {
+                const unsigned y0 = smem_u32(smem + kSmemY + (t & 1) * 2 * kTileBytes), y1 = y0 + kTileBytes;
+                // S = Q K^T and dP = dO V^T: MODE 0 streams (Q, dO) against resident (K, V); MODE 1 the other way round
+                const unsigned a_s = MODE == 0 ? y0 : x0, b_s = MODE == 0 ? x0 : y0, a_p = MODE == 0 ? y1 : x1, b_p = MODE == 0 ? x1 : y1;
+#pragma unroll
+                for (int ks = 0; ks < HD / 16; ++ks)
+                    tc_mma(tmem_base + kColS, make_desc(a_s + ks * 32, 16, 1024), make_desc(b_s + ks * 32, 16, 1024), idesc_sd, ks > 0 ? 1u : 0u);
+#pragma unroll
+                for (int ks = 0; ks < HD / 16; ++ks)
+                    tc_mma(tmem_base + kColDP, make_desc(a_p + ks * 32, 16, 1024), make_desc(b_p + ks * 32, 16, 1024), idesc_sd, ks > 0 ? 1u : 0u);
+                tc_commit(sd_full);
+            };
+            if (ok) ok = mbar_wait(&y_full[0], 0, abort_flag, args.err);
+            if (ok) {
+                tc_fence_after();
+                issue_sd(0);
+            }
+            for (int t = 0; t < nt && ok; ++t) {
+                const int st = t & 1;
+                if (t + 1 < nt) {
+                    ok = mbar_wait(&y_full[(t + 1) & 1], ((t + 1) >> 1) & 1u, abort_flag, args.err);
+                    if (ok) ok = mbar_wait(sd_free, (unsigned)t & 1u, abort_flag, args.err);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_sd(t + 1);
+                }
+                ok = mbar_wait(pds_full, (unsigned)t & 1u, abort_flag, args.err);
+                if (!ok) break;
+                tc_fence_after();
+                const unsigned y0 = smem_u32(smem + kSmemY + st * 2 * kTileBytes), y1 = y0 + kTileBytes;
+                const unsigned acc = (t > 0) ? 1u : 0u;
+                if (MODE == 0) {
+                    // dV += P^T dO, dK += dS^T Q: A is MN-major over [key block (16 KB)][query block (8 KB)] atoms,
+                    // 16 queries per step = 2048 bytes inside a query block; B = dO / Q as loaded ([queries, hd]: MN-major)
+#pragma unroll
+                    for (int ks = 0; ks < BT / 16; ++ks) {
+                        const unsigned a_off = (ks >> 2) * 8192 + (ks & 3) * 2048;
+                        tc_mma(tmem_base + kColAcc0, make_desc(p_addr + a_off, 16384, 1024), make_desc(y1 + ks * 2048, 8192, 1024), idesc_acc,
+                               (ks > 0) ? 1u : acc);
+                    }
+#pragma unroll
+                    for (int ks = 0; ks < BT / 16; ++ks) {
+                        const unsigned a_off = (ks >> 2) * 8192 + (ks & 3) * 2048;
+                        tc_mma(tmem_base + kColAcc1, make_desc(ds_addr + a_off, 16384, 1024), make_desc(y0 + ks * 2048, 8192, 1024), idesc_acc,
+                               (ks > 0) ? 1u : acc);
+                    }
+                } else {
+                    // dQ += dS K: A = dS K-major ([key block][128 queries][64 keys]), 16 keys per step = 32 bytes;
+                    // B = K as loaded ([keys, hd]: MN-major), 16 keys = 2048 bytes
+#pragma unroll
+                    for (int ks = 0; ks < BT / 16; ++ks)
+                        tc_mma(tmem_base + kColAcc0, make_desc(ds_addr + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024),
+                               make_desc(y0 + ks * 2048, 8192, 1024), idesc_acc, (ks > 0) ? 1u : acc);
+                }
+                tc_commit(mma_done);
+                tc_commit(&y_empty[st]);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ pair arithmetic and epilogue (warps 2..9)
+        const int wq = warp & 3;                 // TMEM lane quarter
+        const int hh = (warp - 2) >> 2;          // which 64 keys of the row this thread takes
+        const int row_local = wq * 32 + lane;    // query inside the tile = TMEM lane
+        const unsigned lane_addr = ((unsigned)(wq * 32) << 16);
+        const long long stat_base = ((long long)n * args.heads + h) * args.seq;
+        float lse2 = INFINITY, dl = 0.0f;
+        if (MODE == 1) {
+            const int qrow = o0 + row_local;
+            if (qrow < args.seq) {
+                lse2 = args.lse[stat_base + qrow] * 1.4426950408889634f;
+                dl = args.delta[stat_base + qrow];
+            }
+        }
+        bool ok = true;
+        for (int t = 0; t < nt && ok; ++t) {
+            const int q0 = (MODE == 0) ? (t_first + t) * BT : o0;  // first query of this pair
+            const int k0 = (MODE == 0) ? o0 : t * BT;              // first key of this pair
+            const int qrow = q0 + row_local;
+            if (MODE == 0) {
+                lse2 = INFINITY;
+                dl = 0.0f;
+                if (qrow < args.seq) {
+                    lse2 = args.lse[stat_base + qrow] * 1.4426950408889634f;
+                    dl = args.delta[stat_base + qrow];
+                }
+            }
+            ok = mbar_wait(sd_full, (unsigned)t & 1u, abort_flag, args.err);
+            if (!ok) break;
+            tc_fence_after();
+            unsigned s[64], d[64];
+            tmem_ld32(tmem_base + lane_addr + kColS + hh * 64, *reinterpret_cast<unsigned(*)[32]>(&s[0]));
+            tmem_ld32(tmem_base + lane_addr + kColS + hh * 64 + 32, *reinterpret_cast<unsigned(*)[32]>(&s[32]));
+            tmem_ld32(tmem_base + lane_addr + kColDP + hh * 64, *reinterpret_cast<unsigned(*)[32]>(&d[0]));
+            tmem_ld32(tmem_base + lane_addr + kColDP + hh * 64 + 32, *reinterpret_cast<unsigned(*)[32]>(&d[32]));
+            tmem_ld_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(sd_free);
+            const bool masked = (args.causal && (k0 + BT - 1 > q0)) || (k0 + BT > args.seq);
+            if (masked) {
+#pragma unroll
+                for (int e = 0; e < 64; ++e) {
+                    int col = k0 + hh * 64 + e;
+                    if (col >= args.seq || (args.causal && col > qrow)) s[e] = 0xff800000u; // exp2(-inf) = 0
+                }
+            }
+            const float neg_l = -lse2; // +inf for rows past the end: p = 0 there
+#pragma unroll
+            for (int e = 0; e < 64; e += 2) {
+                float p0 = fast_exp2(fmaf(__uint_as_float(s[e]), args.scale_log2, neg_l));
+                float p1 = fast_exp2(fmaf(__uint_as_float(s[e + 1]), args.scale_log2, neg_l));
+                float g0 = p0 * (__uint_as_float(d[e]) - dl), g1 = p1 * (__uint_as_float(d[e + 1]) - dl);
+                s[e >> 1] = pack_bf16(p0, p1);   // packed pairs fill the front of the same registers
+                d[e >> 1] = pack_bf16(g0, g1);
+            }
+            if (t > 0) { // the previous pair's MMAs may still be reading P / dS
+                ok = mbar_wait(mma_done, (unsigned)(t - 1) & 1u, abort_flag, args.err);
+                if (!ok) break;
+                tc_fence_after();
+            }
+            // atom [key block hh][query block row>>6]: row (row & 63) of 128 bytes, 16-byte chunk c at (c ^ (row & 7))
+            const unsigned atom = (unsigned)hh * 16384u + (unsigned)(row_local >> 6) * 8192u + (unsigned)(row_local & 63) * 128u;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                const unsigned off = atom + (unsigned)((c ^ (row_local & 7)) << 4);
+                if (MODE == 0) *(uint4 *)(sP + off) = make_uint4(s[c * 4], s[c * 4 + 1], s[c * 4 + 2], s[c * 4 + 3]);
+                *(uint4 *)(sDS + off) = make_uint4(d[c * 4], d[c * 4 + 1], d[c * 4 + 2], d[c * 4 + 3]);
+            }
+            fence_async_smem();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(pds_full);
+        }
+        // ---- epilogue: accumulators as bf16 through shared memory and TMA
+        if (ok && nt > 0) ok = mbar_wait(mma_done, (unsigned)(nt - 1) & 1u, abort_flag, args.err);
+        if (ok && (MODE == 0 || hh == 0)) {
+            tc_fence_after();
+            // MODE 0: warps with hh = 0 write dV (acc0), hh = 1 write dK (acc1, times 1/sqrt(hd)); MODE 1: dQ (acc0, scaled)
+            const unsigned col = (MODE == 0 && hh == 1) ? kColAcc1 : kColAcc0;
+            const float f = (MODE == 0 && hh == 0) ? 1.0f : args.scale;
+            const CUtensorMap *om = (MODE == 0 && hh == 1) ? &map_out1 : &map_out0;
+            unsigned char *stage = sP + (warp - 2) * 4096; // this warp's [32 rows x 128 bytes] box (P is no longer read)
+#pragma unroll 1
+            for (int c = 0; c < HD / 32; ++c) {
+                unsigned o[32];
+                if (nt > 0) {
+                    tmem_ld32(tmem_base + lane_addr + col + c * 32, o);
+                    tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) o[e] = 0u;
+                }
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    uint4 piece;
+                    piece.x = pack_bf16(__uint_as_float(o[q * 8]) * f, __uint_as_float(o[q * 8 + 1]) * f);
+                    piece.y = pack_bf16(__uint_as_float(o[q * 8 + 2]) * f, __uint_as_float(o[q * 8 + 3]) * f);
+                    piece.z = pack_bf16(__uint_as_float(o[q * 8 + 4]) * f, __uint_as_float(o[q * 8 + 5]) * f);
+                    piece.w = pack_bf16(__uint_as_float(o[q * 8 + 6]) * f, __uint_as_float(o[q * 8 + 7]) * f);
+                    int chunk = c * 4 + q;
+                    *(uint4 *)(stage + lane * 128 + ((chunk ^ (lane & 7)) << 4)) = piece;
+                }
+            }
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0 && o0 + wq * 32 < args.seq) {
+                tma_store_3d(om, stage, h * HD, o0 + wq * 32, n);
+                bulk_commit();
+                bulk_wait_all();
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+EncodeTiledFn get_encode() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess && qres == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// [n][seq][cols] bf16 view with row pitch `ld` elements; boxes of {64 columns, box_rows rows, 1 sample}
+mcb_status make_map3(mcb_ctx *ctx, CUtensorMap *map, const void *base, long long cols, long long seq, long long n, long long ld, int box_rows) {
+    EncodeTiledFn enc = get_encode();
+    if (!enc) return mcb_fail(ctx, MCB_BACKEND, "cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)seq, (cuuint64_t)n};
+    cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)ld * 2 * (cuuint64_t)seq};
+    cuuint32_t box[3] = {64u, (cuuint32_t)box_rows, 1u};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return mcb_fail(ctx, MCB_BACKEND, "cuTensorMapEncodeTiled (attention backward) failed with %d", (int)r);
+    return MCB_OK;
+}
+
+} // namespace
+
+// dq, dk, dv from q, k, v, dO and the forward's log-sum-exp; `delta` = rowsum(O * dO) per (sample, head, row).
+// MCB_UNSUPPORTED (nothing launched) outside the kernel's range.
+mcb_status mcb_flash_tc_backward(mcb_ctx *ctx, const void *q, const void *k, const void *v, const void *gout, const float *lse, const float *delta,
+                                 void *dq, void *dk, void *dv, int64_t n, int64_t seq, int64_t dim, int64_t heads, int32_t causal, int64_t ldi,
+                                 int64_t ldo, int64_t ldg) {
+    if (heads <= 0 || dim != heads * HD || ldi % 8 || ldo % 8 || ldg % 8 || n * heads > 65535) return MCB_UNSUPPORTED;
+    if (!mcb_aligned16(q) || !mcb_aligned16(k) || !mcb_aligned16(v) || !mcb_aligned16(gout) || !mcb_aligned16(dq) || !mcb_aligned16(dk) ||
+        !mcb_aligned16(dv))
+        return MCB_UNSUPPORTED;
+    if (n == 0 || seq == 0) return MCB_OK;
+    CUtensorMap mq, mk, mv, mdo, mdq, mdk, mdv;
+    MCB_TRY(make_map3(ctx, &mq, q, dim, seq, n, ldi, BT));
+    MCB_TRY(make_map3(ctx, &mk, k, dim, seq, n, ldi, BT));
+    MCB_TRY(make_map3(ctx, &mv, v, dim, seq, n, ldi, BT));
+    MCB_TRY(make_map3(ctx, &mdo, gout, dim, seq, n, ldo, BT));
+    MCB_TRY(make_map3(ctx, &mdq, dq, dim, seq, n, ldg, 32));
+    MCB_TRY(make_map3(ctx, &mdk, dk, dim, seq, n, ldg, 32));
+    MCB_TRY(make_map3(ctx, &mdv, dv, dim, seq, n, ldg, 32));
+    BwdArgs a;
+    a.lse = lse;
+    a.delta = delta;
+    a.seq = (int)seq;
+    a.heads = (int)heads;
+    a.causal = causal;
+    a.scale = 1.0f / sqrtf((float)HD);
+    a.scale_log2 = a.scale * 1.4426950408889634f;
+    a.err = ctx->d_err;
+    static bool attr_set = false;
+    if (!attr_set) {
+        MCB_CUDA(ctx, cudaFuncSetAttribute(flash_tc_bwd_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+        MCB_CUDA(ctx, cudaFuncSetAttribute(flash_tc_bwd_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+        attr_set = true;
+    }
+    dim3 grid((unsigned)((seq + BT - 1) / BT), (unsigned)(n * heads));
+    flash_tc_bwd_kernel<0><<<grid, kThreads, kSmemBytes, ctx->stream>>>(mq, mk, mv, mdo, mdv, mdk, a);
+    MCB_LAUNCHED(ctx);
+    flash_tc_bwd_kernel<1><<<grid, kThreads, kSmemBytes, ctx->stream>>>(mq, mk, mv, mdo, mdq, mdq, a);
+    MCB_LAUNCHED(ctx);
+    return MCB_OK;
+}
