@@ -4,9 +4,9 @@
 // tile may see (all of them, or up to the diagonal when causal):
 //   S = Q K^T      tcgen05.mma  M=128 N=128 K=64, A = Q tile, B = K tile (both K-major in smem), D in TMEM
 //   P = softmax    one thread per query row reads its row of S from TMEM (tcgen05.ld), keeps a
-//                  running maximum m and sum l in the log2 domain, writes P as bf16 into shared
-//                  memory in the K-major operand layout
-//   O += P V       tcgen05.mma  M=128 N=64 K=128, A = P (smem), B = V tile as loaded ([keys, 64]: MN-major)
+//                  running maximum m and sum l in the log2 domain, writes P as packed bf16 back into
+//                  TMEM (tcgen05.st)
+//   O += P V       tcgen05.mma  M=128 N=64 K=128, A = P from TMEM, B = V tile as loaded ([keys, 64]: MN-major)
 // O stays in TMEM for the whole walk.  When a row's maximum grows it is NOT followed at once: the
 // reference maximum is only moved (and O, l rescaled) when it lags by more than 8 in the log2 domain,
 // so the probabilities stay below 2^8 and the rescale of O, a TMEM round trip, is rare.
@@ -14,7 +14,7 @@
 // allocates TMEM and issues the MMAs, warps 2..5 are the softmax rows and the epilogue (O / l as
 // bf16 through shared memory and TMA, log-sum-exp per row for the backward pass).  The next S = Q K^T
 // is issued as soon as the softmax rows have read the previous S, so it overlaps the exponentials.
-// Two CTAs fit on an SM (about 112 KB of shared memory and 256 TMEM columns each).
+// Two CTAs fit on an SM (about 97 KB of shared memory and 256 TMEM columns each).
 // Every mbarrier wait is bounded; on expiry the CTA raises the device error word and drains.
 #include "internal.h"
 #include "tc_ptx.cuh"
@@ -29,14 +29,15 @@ constexpr int BN = 128;   // keys per tile
 constexpr int kThreads = 192;
 constexpr int kTileBytes = 128 * 64 * 2; // a [128 x 64] bf16 tile: 16 KB
 constexpr int kStages = 2;
-// shared memory: Q | K0 V0 | K1 V1 | P (two 16 KB key blocks; reused as the output staging) | barriers
-constexpr int kSmemQ = 0, kSmemKV = kTileBytes, kSmemP = kSmemKV + kStages * 2 * kTileBytes, kSmemBar = kSmemP + 2 * kTileBytes;
+// shared memory: Q | K0 V0 | K1 V1 | output staging (16 KB) | barriers.  P never touches shared memory: it goes from
+// the softmax registers into TMEM and is the A operand of P V from there.
+constexpr int kSmemQ = 0, kSmemKV = kTileBytes, kSmemP = kSmemKV + kStages * 2 * kTileBytes, kSmemBar = kSmemP + kTileBytes;
 // Two CTAs must fit in the SM's 228 KB (each also pays 1 KB of system reservation): 115,712 bytes at most.
 // The alignment slack is therefore 768 bytes, not 1024; the kernel checks that the aligned carve-up fits.
 constexpr int kSmemBytes = kSmemBar + 128 + 768;
 static_assert(2 * (kSmemBytes + 1024) <= 228 * 1024, "two CTAs per SM");
-constexpr unsigned kTmemCols = 256; // S: columns [0,128), O: [128,192)
-constexpr unsigned kColS = 0, kColO = 128;
+constexpr unsigned kTmemCols = 256; // S: columns [0,128), O: [128,192), P as packed bf16 pairs: [192,256)
+constexpr unsigned kColS = 0, kColO = 128, kColP = 192;
 
 struct FwdArgs {
     float *lse;        // [n, heads, seq]
@@ -132,7 +133,7 @@ flash_tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             constexpr unsigned idesc_s = make_idesc(BM, BN, 0, 0);   // S = Q K^T: both operands K-major
             constexpr unsigned idesc_o = make_idesc(BM, HD, 0, 1);   // O += P V: V is [keys, hd] = MN-major B
             const unsigned tmem_s = tmem_base + kColS, tmem_o = tmem_base + kColO;
-            const unsigned a_q = smem_u32(sQ), a_p = smem_u32(sP);
+            const unsigned a_q = smem_u32(sQ);
             bool ok = mbar_wait(q_full, 0, abort_flag, args.err);
             auto issue_s = [&](int j) {
                 const unsigned b_k = smem_u32(smem + kSmemKV + (j & 1) * 2 * kTileBytes);
@@ -164,10 +165,9 @@ flash_tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 const unsigned b_v = smem_u32(smem + kSmemKV + st * 2 * kTileBytes + kTileBytes);
 #pragma unroll
                 for (int ks = 0; ks < BN / 16; ++ks) {
-                    // P: two 16 KB key blocks of [128 rows x 64 keys]; V: 16 keys = 2048 bytes per step
-                    unsigned long long ad = make_desc(a_p + (ks >> 2) * kTileBytes + (ks & 3) * 32, 16, 1024);
+                    // P from TMEM: 16 keys = 8 columns of packed pairs per step; V: 16 keys = 2048 bytes per step
                     unsigned long long bd = make_desc(b_v + ks * 2048, 8192, 1024);
-                    tc_mma(tmem_o, ad, bd, idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
+                    tc_mma_ta(tmem_o, tmem_base + kColP + ks * 8, bd, idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
                 }
                 tc_commit(pv_done);
                 tc_commit(&v_empty[st]);
@@ -258,15 +258,10 @@ flash_tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 }
                 tmem_st_wait();
             }
-            // P into shared memory, K-major operand layout: key block kb, row r, 16-byte chunk c at (c ^ (r & 7))
-#pragma unroll
-            for (int kb = 0; kb < 2; ++kb)
-#pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    uint4 piece = make_uint4(r[kb * 32 + c * 4], r[kb * 32 + c * 4 + 1], r[kb * 32 + c * 4 + 2], r[kb * 32 + c * 4 + 3]);
-                    *(uint4 *)(sP + kb * kTileBytes + row_local * 128 + ((c ^ (row_local & 7)) << 4)) = piece;
-                }
-            fence_async_smem();
+            // P into TMEM (this row's lane, 64 columns of packed bf16 pairs): the A operand of P V
+            tmem_st32(tmem_base + lane_addr + kColP, *reinterpret_cast<unsigned(*)[32]>(&r[0]));
+            tmem_st32(tmem_base + lane_addr + kColP + 32, *reinterpret_cast<unsigned(*)[32]>(&r[32]));
+            tmem_st_wait();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(p_full);

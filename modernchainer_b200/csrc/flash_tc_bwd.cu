@@ -32,6 +32,7 @@ constexpr int kSmemX = 0, kSmemY = 2 * kTileBytes, kSmemP = kSmemY + 4 * kTileBy
 constexpr int kSmemBytes = kSmemBar + 128 + 1024;
 constexpr unsigned kTmemCols = 512;
 constexpr unsigned kColS = 0, kColDP = 128, kColAcc0 = 256, kColAcc1 = 320;
+constexpr unsigned kColDSt = 320; // MODE 1: dS as packed bf16 pairs (64 columns), the A operand of dQ += dS K, read from TMEM
 
 struct BwdArgs {
     const float *lse, *delta;  // [n, heads, seq]
@@ -178,12 +179,12 @@ flash_tc_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                                (ks > 0) ? 1u : acc);
                     }
                 } else {
-                    // dQ += dS K: A = dS K-major ([key block][128 queries][64 keys]), 16 keys per step = 32 bytes;
+                    // dQ += dS K: A = dS straight from TMEM (16 keys = 8 columns of packed pairs per step);
                     // B = K as loaded ([keys, hd]: MN-major), 16 keys = 2048 bytes
 #pragma unroll
                     for (int ks = 0; ks < BT / 16; ++ks)
-                        tc_mma(tmem_base + kColAcc0, make_desc(ds_addr + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024),
-                               make_desc(y0 + ks * 2048, 8192, 1024), idesc_acc, (ks > 0) ? 1u : acc);
+                        tc_mma_ta(tmem_base + kColAcc0, tmem_base + kColDSt + ks * 8, make_desc(y0 + ks * 2048, 8192, 1024), idesc_acc,
+                                  (ks > 0) ? 1u : acc);
                 }
                 tc_commit(mma_done);
                 tc_commit(&y_empty[st]);
@@ -250,6 +251,15 @@ flash_tc_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 ok = mbar_wait(mma_done, (unsigned)(t - 1) & 1u, abort_flag, args.err);
                 if (!ok) break;
                 tc_fence_after();
+            }
+            if (MODE == 1) {
+                // dS into TMEM: this row's lane, columns of this thread's 64 keys
+                tmem_st32(tmem_base + lane_addr + kColDSt + hh * 32, *reinterpret_cast<unsigned(*)[32]>(&d[0]));
+                tmem_st_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(pds_full);
+                continue;
             }
             // atom [key block hh][query block row>>6]: row (row & 63) of 128 bytes, 16-byte chunk c at (c ^ (row & 7))
             const unsigned atom = (unsigned)hh * 16384u + (unsigned)(row_local >> 6) * 8192u + (unsigned)(row_local & 63) * 128u;
