@@ -229,19 +229,32 @@ __global__ void __launch_bounds__(kThreads) flash_fwd_kernel(const bf16 *__restr
 }
 
 // ------------------------------------------------------------------ backward: delta
-__global__ void flash_delta_kernel(const bf16 *__restrict__ O, const bf16 *__restrict__ dO, float *__restrict__ delta, int S, int D, int H,
-                                   long long total_rows) {
-    long long w = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5; // one warp per (n, h, row)
-    int lane = threadIdx.x & 31;
-    if (w >= total_rows) return;
-    long long row = w % S, nh = w / S;
-    long long n = nh / H, h = nh % H;
-    long long off = (n * S + row) * D + h * HD + lane * 2;
-    float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(O + off));
-    float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(dO + off));
-    float v = a.x * b.x + a.y * b.y;
-    v = warp_sum(v);
-    if (lane == 0) delta[w] = v;
+__global__ void flash_delta_kernel(const bf16 *__restrict__ O, const bf16 *__restrict__ dO, float *__restrict__ delta, int S, int DO, int DG, int H,
+                                   long long total_chunks) {
+    // eight lanes per (sample, row, head): 16 bytes of O and of dO each, so a warp reads 512 contiguous bytes of a row
+    long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const bool live = t < total_chunks;
+    if (!live) t = total_chunks - 1;
+    const int per_row = H * (HD / 8);
+    const long long srow = t / per_row; // n * S + row
+    const int chunk = (int)(t - srow * per_row);
+    const int h = chunk >> 3;
+    const uint4 a = *reinterpret_cast<const uint4 *>(O + srow * DO + chunk * 8);
+    const uint4 b = *reinterpret_cast<const uint4 *>(dO + srow * DG + chunk * 8);
+    const __nv_bfloat162 *pa = reinterpret_cast<const __nv_bfloat162 *>(&a), *pb = reinterpret_cast<const __nv_bfloat162 *>(&b);
+    float v = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 x = __bfloat1622float2(pa[i]), y = __bfloat1622float2(pb[i]);
+        v = fmaf(x.x, y.x, fmaf(x.y, y.y, v));
+    }
+    v += __shfl_xor_sync(0xffffffffu, v, 1);
+    v += __shfl_xor_sync(0xffffffffu, v, 2);
+    v += __shfl_xor_sync(0xffffffffu, v, 4);
+    if (live && (threadIdx.x & 7) == 0) {
+        const long long n = srow / S, row = srow - n * S;
+        delta[(n * H + h) * S + row] = v;
+    }
 }
 
 // ------------------------------------------------------------------ backward: dQ
@@ -430,11 +443,15 @@ mcb_status mcb_flash_backward(mcb_ctx *ctx, const void *q, const void *k, const 
     (void)dim;
     if (ldi % 8 || ldo % 8 || ldg % 8) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "fused attention needs row pitches that are multiples of 8");
     if (n * heads > 65535) return mcb_fail(ctx, MCB_UNSUPPORTED, "fused attention: n * heads > 65535");
+    if ((((uintptr_t)out) | ((uintptr_t)gout)) & 15) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "fused attention needs 16-byte aligned tensors");
     float scale = 1.0f / sqrtf((float)HD), scale_log2 = scale * 1.4426950408889634f;
     long long rows = n * heads * seq;
     void *delta = nullptr;
     MCB_TRY(mcb_alloc(ctx, sizeof(float) * rows, &delta));
-    flash_delta_kernel<<<(unsigned)((rows * 32 + 255) / 256), 256, 0, ctx->stream>>>((const bf16 *)out, (const bf16 *)gout, (float *)delta, (int)seq, (int)ldo, (int)heads, rows);
+    {
+        const long long chunks = rows * (HD / 8);
+        flash_delta_kernel<<<(unsigned)((chunks + 255) / 256), 256, 0, ctx->stream>>>((const bf16 *)out, (const bf16 *)gout, (float *)delta, (int)seq, (int)ldo, (int)ldo, (int)heads, chunks); // gout has the pitch of out; ldg is the pitch of dq / dk / dv
+    }
     ctx->launches++;
     // the tcgen05 / TMEM kernels first; MCB_FLASH_LEGACY (test knob) keeps the mma.sync pair
     if (!getenv("MCB_FLASH_LEGACY") && !getenv("MCB_FLASH_LEGACY_BWD")) {
