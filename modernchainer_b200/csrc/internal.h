@@ -60,6 +60,12 @@ mcb_status mcb_ln_fast_forward(mcb_ctx *ctx, const float *x, const float *gamma,
                                float *mean, float *rstd, int64_t rows, int64_t dim);
 mcb_status mcb_ln_fast_backward(mcb_ctx *ctx, const float *x, const float *gamma, const void *g, int32_t g_dt, double eps, const float *mean,
                                 const float *rstd, const float *addend, float *dx, float *dgamma, float *dbeta, int64_t rows, int64_t dim);
+// layer_norm_bulk.cu: the same two passes as a persistent bulk-copy pipeline through shared memory, for
+// problems with enough rows to fill every SM; MCB_UNSUPPORTED (nothing launched) otherwise
+mcb_status mcb_ln_bulk_forward(mcb_ctx *ctx, const float *x, const float *gamma, const float *beta, double eps, void *out, int32_t out_dt,
+                               float *mean, float *rstd, int64_t rows, int64_t dim);
+mcb_status mcb_ln_bulk_backward(mcb_ctx *ctx, const float *x, const float *gamma, const void *g, int32_t g_dt, double eps, const float *mean,
+                                const float *rstd, const float *addend, float *dx, float *dgamma, float *dbeta, int64_t rows, int64_t dim);
 // reduce.cu: LayerNorm backward that writes dx as addend + dx when `addend` is given (may alias dx);
 // MCB_UNSUPPORTED (nothing launched) where only the plain form exists
 mcb_status mcb_layer_norm_backward_ex(mcb_ctx *ctx, const float *x, const float *gamma, const void *g, int32_t g_dt, double eps,

@@ -631,6 +631,8 @@ mcb_status mcb_layer_norm(mcb_ctx *ctx, const float *x, const float *gamma, cons
     int vec = (dim % 4 == 0) && mcb_aligned16(x) && mcb_aligned16(out) && mcb_aligned16(gamma) && mcb_aligned16(beta);
     ProfScope prof(ctx, MCB_PROF_NORM, 0.0, (double)rows * dim * (4.0 + (out_dt == MCB_BF16 ? 2.0 : 4.0)) + 8.0 * rows);
     if (out_dt == MCB_F32 || out_dt == MCB_BF16) {
+        mcb_status bulk = mcb_ln_bulk_forward(ctx, x, gamma, beta, eps, out, out_dt, mean, rstd, rows, dim);
+        if (bulk != MCB_UNSUPPORTED) return bulk; // enough rows to fill every SM: shared-memory pipeline
         mcb_status fast = mcb_ln_fast_forward(ctx, x, gamma, beta, eps, out, out_dt, mean, rstd, rows, dim);
         if (fast != MCB_UNSUPPORTED) return fast; // rows of up to 1024 aligned elements stay in registers
     }
@@ -668,6 +670,8 @@ mcb_status mcb_layer_norm_backward_ex(mcb_ctx *ctx, const float *x, const float 
     ProfScope prof(ctx, MCB_PROF_NORM, 0.0,
                    (double)rows * dim * (8.0 + (g_dt == MCB_BF16 ? 2.0 : 4.0) + (addend ? 4.0 : 0.0)) + 8.0 * rows + 8.0 * dim);
     if (g_dt == MCB_F32 || g_dt == MCB_BF16) {
+        mcb_status bulk = mcb_ln_bulk_backward(ctx, x, gamma, g, g_dt, eps, mean, rstd, addend, dx, dgamma, dbeta, rows, dim);
+        if (bulk != MCB_UNSUPPORTED) return bulk;
         mcb_status fast = mcb_ln_fast_backward(ctx, x, gamma, g, g_dt, eps, mean, rstd, addend, dx, dgamma, dbeta, rows, dim);
         if (fast != MCB_UNSUPPORTED) return fast;
     }

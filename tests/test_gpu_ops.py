@@ -183,6 +183,26 @@ def test_layer_norm_forward_backward(ops, oracle, rows, dim):
         close(a, b, 2e-5)
 
 
+@pytest.mark.parametrize("rows,dim", [(1500, 128), (1189, 768), (2051, 1000), (1300, 1024)])
+def test_layer_norm_pipeline_kernels(ops, oracle, rows, dim):
+    """From 8 x 148 rows on (dim % 8 == 0, dim <= 1024) LayerNorm is a persistent bulk-copy pipeline:
+    ragged last row block, f32 and bf16 in/out, statistics given or recomputed."""
+    x, g = randn(rows, dim) * 2 + 0.5, randn(rows, dim)
+    gam, bet = randn(dim) * 0.2 + 1, randn(dim) * 0.1
+    y, mean, rstd = ops.layer_norm(x, gam, bet, 1e-5, with_stats=True)
+    want = oracle.layer_norm(x, gam, bet, 1e-5)
+    close(y, want)
+    bf16_close(ops.layer_norm(x, gam, bet, 1e-5, out_dt=5), want)
+    ref = oracle.layer_norm_backward(x, gam, g, 1e-5)
+    for a, b in zip(ops.layer_norm_backward(x, gam, g, 1e-5), ref):
+        close(a, b, 2e-5)
+    for a, b in zip(ops.layer_norm_backward(x, gam, g, 1e-5, stats=(mean, rstd)), ref):
+        close(a, b, 2e-5)
+    gb = oracle.round_bf16(g)
+    for a, b in zip(ops.layer_norm_backward(x, gam, gb, 1e-5, g_dt=5, stats=(mean, rstd)), oracle.layer_norm_backward(x, gam, gb, 1e-5)):
+        close(a, b, 2e-5)
+
+
 def test_layer_norm_bf16_io(ops, oracle):
     x, g = randn(64, 768), oracle.round_bf16(randn(64, 768))
     gam, bet = np.ones(768, np.float32), np.zeros(768, np.float32)
