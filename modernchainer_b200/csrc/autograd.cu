@@ -315,6 +315,8 @@ static mcb_status like_input_lazy(mcb_ctx *ctx, const Tensor &g, const Var &in, 
     return like_input(ctx, g, in, out);
 }
 
+void binary_node(mcb_ctx *ctx, int op, const Var &a, const Var &b, const Tensor &res, Var *out);
+
 mcb_status f_binary(int op, const Var &a, const Var &b, Var *out) {
     MCB_TRY(check_same_ctx(a, b));
     mcb_ctx *ctx = a->ctx;
@@ -332,6 +334,12 @@ mcb_status f_binary(int op, const Var &a, const Var &b, Var *out) {
         MCB_TRY(f32_of(b, &bf));
         MCB_TRY(bin(ctx, op, af, bf, &res));
     }
+    binary_node(ctx, op, a, b, res, out);
+    return MCB_OK;
+}
+
+// the tape node of a + b, a - b, a * b, a / b over an already computed result
+void binary_node(mcb_ctx *ctx, int op, const Var &a, const Var &b, const Tensor &res, Var *out) {
     Var av = a, bv = b;
     *out = apply(ctx, "Binary", res, {a, b}, [ctx, op, av, bv](const Tensor &g, std::vector<Tensor> &gi) -> mcb_status {
         const std::vector<int64_t> &as = av->data.shape, &bs = bv->data.shape;
@@ -390,7 +398,6 @@ mcb_status f_binary(int op, const Var &a, const Var &b, Var *out) {
         }
         return MCB_OK;
     });
-    return MCB_OK;
 }
 
 mcb_status f_scale(const Var &x, double factor, Var *out) {
@@ -757,6 +764,9 @@ mcb_status f_softmax(const Var &x, Var *out) {
     return MCB_OK;
 }
 
+void layer_norm_node(mcb_ctx *ctx, const Var &x, const Var &gamma, const Var &beta, double eps, const Tensor &xf, const Tensor &res,
+                     const Tensor &mean, const Tensor &rstd, Var *out);
+
 mcb_status f_layer_norm(const Var &x, const Var &gamma, const Var &beta, double eps, Var *out) {
     mcb_ctx *ctx = x->ctx;
     if (x->data.shape.size() < 2) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "layer_norm expects rank >= 2");
@@ -771,6 +781,15 @@ mcb_status f_layer_norm(const Var &x, const Var &gamma, const Var &beta, double 
     MCB_TRY(new_tensor(ctx, MCB_F32, {rows}, &rstd));
     MCB_TRY(mcb_layer_norm(ctx, (const float *)xf.ptr, (const float *)gamma->data.ptr, (const float *)beta->data.ptr, eps, res.ptr, odt,
                            (float *)mean.ptr, (float *)rstd.ptr, rows, dim));
+    layer_norm_node(ctx, x, gamma, beta, eps, xf, res, mean, rstd, out);
+    return MCB_OK;
+}
+
+// the tape node of LayerNorm over an already computed result (xf: x as f32; mean, rstd: the row statistics)
+void layer_norm_node(mcb_ctx *ctx, const Var &x, const Var &gamma, const Var &beta, double eps, const Tensor &xf, const Tensor &res,
+                     const Tensor &mean, const Tensor &rstd, Var *out) {
+    const int64_t dim = x->data.shape.back();
+    const int64_t rows = dim ? x->data.numel() / dim : 0;
     Var xv = x, gv = gamma, bv = beta;
     *out = apply(ctx, "LayerNorm", res, {x, gamma, beta}, [ctx, xf, mean, rstd, xv, gv, bv, eps, rows, dim](const Tensor &g, std::vector<Tensor> &gi) -> mcb_status {
         Tensor dx, dg, db;
@@ -799,7 +818,40 @@ mcb_status f_layer_norm(const Var &x, const Var &gamma, const Var &beta, double 
         gi[2] = db;
         return MCB_OK;
     });
-    return MCB_OK;
+}
+
+// sum = a + b and out = LayerNorm(sum): the residual add of a pre-norm block and the LayerNorm that reads it.
+// Two tape nodes, exactly those of f_binary(MCB_ADD) and f_layer_norm; when a is an f32 residual stream and the
+// shapes suit the pipeline kernel, one kernel produces both results (same arithmetic, one pass over the rows).
+mcb_status f_add_layer_norm(const Var &a, const Var &b, const Var &gamma, const Var &beta, double eps, Var *sum, Var *out) {
+    MCB_TRY(check_same_ctx(a, b));
+    mcb_ctx *ctx = a->ctx;
+    const std::vector<int64_t> &sh = a->data.shape;
+    if (!getenv("MCB_UNFUSED_ADD_LN") && sh.size() >= 2 && sh == b->data.shape && a->data.dt == MCB_F32 &&
+        (b->data.dt == MCB_F32 || b->data.dt == MCB_BF16) && gamma->data.numel() == sh.back() && beta->data.numel() == sh.back() &&
+        gamma->data.dt == MCB_F32 && beta->data.dt == MCB_F32) {
+        const int64_t dim = sh.back(), rows = dim ? a->data.numel() / dim : 0;
+        const int odt = (g_autocast == MCB_BF16) ? MCB_BF16 : MCB_F32;
+        Tensor st, res, mean, rstd;
+        MCB_TRY(new_tensor(ctx, MCB_F32, sh, &st));
+        MCB_TRY(new_tensor(ctx, odt, sh, &res));
+        MCB_TRY(new_tensor(ctx, MCB_F32, {rows}, &mean));
+        MCB_TRY(new_tensor(ctx, MCB_F32, {rows}, &rstd));
+        mcb_status fused;
+        {
+            ProfScope prof(ctx, MCB_PROF_NORM, 0.0, (double)rows * dim * (8.0 + (b->data.dt == MCB_BF16 ? 2.0 : 4.0) + (odt == MCB_BF16 ? 2.0 : 4.0)) + 8.0 * rows);
+            fused = mcb_ln_bulk_add_forward(ctx, (const float *)a->data.ptr, b->data.ptr, b->data.dt, (const float *)gamma->data.ptr,
+                                            (const float *)beta->data.ptr, eps, (float *)st.ptr, res.ptr, odt, (float *)mean.ptr, (float *)rstd.ptr, rows, dim);
+        }
+        if (fused != MCB_UNSUPPORTED) {
+            MCB_TRY(fused);
+            binary_node(ctx, MCB_ADD, a, b, st, sum);
+            layer_norm_node(ctx, *sum, gamma, beta, eps, st, res, mean, rstd, out);
+            return MCB_OK;
+        }
+    }
+    MCB_TRY(f_binary(MCB_ADD, a, b, sum));
+    return f_layer_norm(*sum, gamma, beta, eps, out);
 }
 
 mcb_status f_softmax_cross_entropy(const Var &logits, const Var &target, Var *out) {
@@ -1562,9 +1614,12 @@ mcb_status Model::loss(const Var &input, const Var &target, Var *out) {
     MCB_TRY(f_reshape(target, {b * s}, &tgt));
     MCB_TRY(f_embedding(ids, P[0], &x));
     size_t pi = 1;
+    // every residual add is followed by the LayerNorm of the next sub-block (or the final one), so the two are
+    // issued together (f_add_layer_norm); n1 carries the normalised input of the coming attention sub-block
+    Var n1;
+    if (layers > 0) MCB_TRY(f_layer_norm(x, P[pi + 0], P[pi + 1], eps, &n1));
     for (int64_t l = 0; l < layers; ++l, pi += 16) {
-        Var n1, q, k, v, q3, k3, v3, att, att2, o, x1, n2, h, f2, x2;
-        MCB_TRY(f_layer_norm(x, P[pi + 0], P[pi + 1], eps, &n1));
+        Var q, k, v, q3, k3, v3, att, att2, o, x1, n2, h, f2, x2;
         mcb_status fused = f_qkv_attention(n1, P[pi + 2], P[pi + 3], P[pi + 4], P[pi + 5], P[pi + 6], P[pi + 7], b, s, heads, true, &att2);
         if (fused == MCB_UNSUPPORTED) {
             MCB_TRY(f_linear(n1, P[pi + 2], P[pi + 3], &q));
@@ -1579,15 +1634,15 @@ mcb_status Model::loss(const Var &input, const Var &target, Var *out) {
             MCB_TRY(fused);
         }
         MCB_TRY(f_linear(att2, P[pi + 8], P[pi + 9], &o));
-        MCB_TRY(f_binary(MCB_ADD, x, o, &x1));
-        MCB_TRY(f_layer_norm(x1, P[pi + 10], P[pi + 11], eps, &n2));
+        MCB_TRY(f_add_layer_norm(x, o, P[pi + 10], P[pi + 11], eps, &x1, &n2));
         MCB_TRY(f_linear_activation(n2, P[pi + 12], P[pi + 13], MCB_ACT_GELU, &h));
         MCB_TRY(f_linear(h, P[pi + 14], P[pi + 15], &f2));
-        MCB_TRY(f_binary(MCB_ADD, x1, f2, &x2));
+        // the LayerNorm that reads x2: the next layer's first one, or the final one (same slots of the next group)
+        MCB_TRY(f_add_layer_norm(x1, f2, P[pi + 16], P[pi + 17], eps, &x2, &n1));
         x = x2;
     }
-    Var nf, logits;
-    MCB_TRY(f_layer_norm(x, P[pi + 0], P[pi + 1], eps, &nf));
+    Var nf = n1, logits;
+    if (layers == 0) MCB_TRY(f_layer_norm(x, P[pi + 0], P[pi + 1], eps, &nf));
     MCB_TRY(f_linear(nf, P[pi + 2], nullptr, &logits));
     return f_sce_consuming(logits, tgt, out);
 }

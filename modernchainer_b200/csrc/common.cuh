@@ -60,6 +60,9 @@ struct mcb_ctx {
     cudaStream_t trace_stream = nullptr;
     unsigned long long *trace_buf = nullptr; // [0] = samples written, then (globaltimer ns, clock64) pairs
     int trace_cap = 0;
+    // Programmatic dependent launch: kernels launched through mcb_launch_dep may be scheduled while the
+    // previous kernel of the stream drains; they call dep_wait() before touching global memory.
+    bool dep_launch = true;
 };
 
 // RAII timing scope: when profiling is on, brackets the launches made inside it with events
@@ -119,6 +122,33 @@ static inline int mcb_grid_for(mcb_ctx *ctx, int64_t work_items, int per_block, 
 }
 
 #ifdef __CUDACC__
+// ------------------------------------------------------------------ programmatic dependent launch
+// A kernel launched with mcb_launch_dep may become resident while the preceding kernel of the stream is
+// still running its last CTAs (that kernel must have passed dep_trigger() in every CTA, or finished).
+// Contract for such a kernel: EVERY thread calls dep_wait() before its first access to global memory
+// (reads and writes: the predecessor may still be reading what this kernel overwrites); only index
+// arithmetic, barrier initialisation and shared/tensor-memory set-up may come before.  dep_wait() returns
+// once all preceding kernels have completed and their writes are visible, so the stream stays in order;
+// what overlaps is launch latency, the prologue and the tail of the previous grid.  Both calls are no-ops
+// in a kernel launched the ordinary way.
+__device__ __forceinline__ void dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void dep_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t mcb_launch_dep(mcb_ctx *ctx, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, Args &&...args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = ctx->dep_launch ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // ------------------------------------------------------------------ device helpers
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

@@ -261,6 +261,8 @@ __global__ void __launch_bounds__(256) map_colsum_kernel(const void *__restrict_
     float acc[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
+    dep_wait();
+    dep_trigger();
     if (col < cols) {
 #pragma unroll 2
         for (long long r = r0 + w; r < r1; r += 8) {
@@ -478,6 +480,8 @@ __global__ void add_typed_kernel(const A *__restrict__ a, const B *__restrict__ 
     long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     long long stride = (long long)gridDim.x * blockDim.x;
     long long n4 = vec ? (n >> 2) : 0;
+    dep_wait();
+    dep_trigger();
     for (long long j = i; j < n4; j += stride) {
         float4 x = Elem<A>::ld4(a, j), y = Elem<B>::ld4(b, j);
         Elem<O>::st4(out, j, make_float4(x.x + y.x, x.y + y.y, x.z + y.z, x.w + y.w));
@@ -487,7 +491,8 @@ __global__ void add_typed_kernel(const A *__restrict__ a, const B *__restrict__ 
 template <typename A, typename B, typename O>
 void launch_add_typed(mcb_ctx *ctx, const void *a, const void *b, void *out, long long n) {
     int vec = mcb_aligned16(a) && mcb_aligned16(b) && mcb_aligned16(out);
-    add_typed_kernel<A, B, O><<<mcb_grid_for(ctx, (n + 3) / 4, kThreads), kThreads, 0, ctx->stream>>>((const A *)a, (const B *)b, (O *)out, n, vec);
+    (void)mcb_launch_dep(ctx, add_typed_kernel<A, B, O>, dim3(mcb_grid_for(ctx, (n + 3) / 4, kThreads)), dim3(kThreads), 0, (const A *)a, (const B *)b,
+                         (O *)out, n, vec); // a launch error is picked up by the caller's MCB_LAUNCHED
 }
 } // namespace
 
@@ -542,9 +547,9 @@ mcb_status mcb_map_colsum(mcb_ctx *ctx, int mode, const void *a, const void *b, 
     MCB_TRY(mcb_scratch(ctx, sizeof(float) * (size_t)splits * cols, &scratch));
     dim3 grid(chunks, splits);
     __nv_bfloat16 *o = (__nv_bfloat16 *)out_bf16;
-    if (mode == 0) map_colsum_kernel<0><<<grid, 256, 0, ctx->stream>>>(a, b, o, rows, cols, (float *)scratch);
-    else if (mode == 1) map_colsum_kernel<1><<<grid, 256, 0, ctx->stream>>>(a, b, o, rows, cols, (float *)scratch);
-    else if (mode == 2) map_colsum_kernel<2><<<grid, 256, 0, ctx->stream>>>(a, b, o, rows, cols, (float *)scratch);
+    if (mode == 0) MCB_CUDA(ctx, mcb_launch_dep(ctx, map_colsum_kernel<0>, grid, dim3(256), 0, a, b, o, (long long)rows, (long long)cols, (float *)scratch));
+    else if (mode == 1) MCB_CUDA(ctx, mcb_launch_dep(ctx, map_colsum_kernel<1>, grid, dim3(256), 0, a, b, o, (long long)rows, (long long)cols, (float *)scratch));
+    else if (mode == 2) MCB_CUDA(ctx, mcb_launch_dep(ctx, map_colsum_kernel<2>, grid, dim3(256), 0, a, b, o, (long long)rows, (long long)cols, (float *)scratch));
     else return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "map_colsum: unknown mode %d", mode);
     MCB_LAUNCHED(ctx);
     return mcb_partial_sum_final(ctx, (const float *)scratch, splits, cols, colsum_out);

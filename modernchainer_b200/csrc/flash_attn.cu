@@ -232,6 +232,8 @@ __global__ void __launch_bounds__(kThreads) flash_fwd_kernel(const bf16 *__restr
 __global__ void flash_delta_kernel(const bf16 *__restrict__ O, const bf16 *__restrict__ dO, float *__restrict__ delta, int S, int DO, int DG, int H,
                                    long long total_chunks) {
     // eight lanes per (sample, row, head): 16 bytes of O and of dO each, so a warp reads 512 contiguous bytes of a row
+    dep_wait();
+    dep_trigger();
     long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const bool live = t < total_chunks;
     if (!live) t = total_chunks - 1;
@@ -450,7 +452,7 @@ mcb_status mcb_flash_backward(mcb_ctx *ctx, const void *q, const void *k, const 
     MCB_TRY(mcb_alloc(ctx, sizeof(float) * rows, &delta));
     {
         const long long chunks = rows * (HD / 8);
-        flash_delta_kernel<<<(unsigned)((chunks + 255) / 256), 256, 0, ctx->stream>>>((const bf16 *)out, (const bf16 *)gout, (float *)delta, (int)seq, (int)ldo, (int)ldo, (int)heads, chunks); // gout has the pitch of out; ldg is the pitch of dq / dk / dv
+        MCB_CUDA(ctx, mcb_launch_dep(ctx, flash_delta_kernel, dim3((unsigned)((chunks + 255) / 256)), dim3(256), 0, (const bf16 *)out, (const bf16 *)gout, (float *)delta, (int)seq, (int)ldo, (int)ldo, (int)heads, chunks)); // gout has the pitch of out; ldg is the pitch of dq / dk / dv
     }
     ctx->launches++;
     // the tcgen05 / TMEM kernels first; MCB_FLASH_LEGACY (test knob) keeps the mma.sync pair

@@ -95,6 +95,9 @@ flash_tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     __syncthreads();
     tc_fence_after();
     const unsigned tmem_base = *tmem_slot;
+    // only shared and tensor memory so far: this much may overlap the previous kernel of the stream
+    dep_wait();
+    dep_trigger();
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
@@ -365,7 +368,7 @@ mcb_status mcb_flash_tc_forward(mcb_ctx *ctx, const void *q, const void *k, cons
         attr_set = true;
     }
     dim3 grid((unsigned)((seq + BM - 1) / BM), (unsigned)(n * heads));
-    flash_tc_fwd_kernel<<<grid, kThreads, kSmemBytes, ctx->stream>>>(mq, mk, mv, mo, a);
+    MCB_CUDA(ctx, mcb_launch_dep(ctx, flash_tc_fwd_kernel, grid, dim3(kThreads), kSmemBytes, mq, mk, mv, mo, a));
     MCB_LAUNCHED(ctx);
     return MCB_OK;
 }

@@ -87,6 +87,13 @@ flash_tc_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     __syncthreads();
     tc_fence_after();
     const unsigned tmem_base = *tmem_slot;
+    // Only shared and tensor memory so far: this much may overlap the previous kernel of the stream.  The dK/dV
+    // kernel (MODE 0) waits here for everything before it.  The dQ kernel (MODE 1) is launched right behind it, reads
+    // the same inputs and writes other bytes, so it needs nothing from MODE 0: it starts on the SMs that MODE 0's tail
+    // leaves idle (MODE 0 raised its trigger after its own wait, so all earlier kernels are complete by then) and waits
+    // for MODE 0 only before it exits, which keeps the stream in order for whatever follows.
+    if (MODE == 0) dep_wait();
+    dep_trigger();
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
@@ -316,6 +323,7 @@ flash_tc_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     tc_fence_before();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+    if (MODE == 1) dep_wait();
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
@@ -384,9 +392,9 @@ mcb_status mcb_flash_tc_backward(mcb_ctx *ctx, const void *q, const void *k, con
         attr_set = true;
     }
     dim3 grid((unsigned)((seq + BT - 1) / BT), (unsigned)(n * heads));
-    flash_tc_bwd_kernel<0><<<grid, kThreads, kSmemBytes, ctx->stream>>>(mq, mk, mv, mdo, mdv, mdk, a);
+    MCB_CUDA(ctx, mcb_launch_dep(ctx, flash_tc_bwd_kernel<0>, grid, dim3(kThreads), kSmemBytes, mq, mk, mv, mdo, mdv, mdk, a));
     MCB_LAUNCHED(ctx);
-    flash_tc_bwd_kernel<1><<<grid, kThreads, kSmemBytes, ctx->stream>>>(mq, mk, mv, mdo, mdq, mdq, a);
+    MCB_CUDA(ctx, mcb_launch_dep(ctx, flash_tc_bwd_kernel<1>, grid, dim3(kThreads), kSmemBytes, mq, mk, mv, mdo, mdq, mdq, a));
     MCB_LAUNCHED(ctx);
     return MCB_OK;
 }

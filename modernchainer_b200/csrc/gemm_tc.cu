@@ -357,6 +357,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (PAIR) cluster_sync_all(); // the peer's barriers exist before anything signals them
     tc_fence_after();
     unsigned tmem_base = *tmem_slot;
+    // everything above touched only shared and tensor memory, so it may run while the previous kernel of the
+    // stream drains; from here on global memory is read and written
+    dep_wait();
+    dep_trigger();
 
     const unsigned tiles_mn = (unsigned)args.m_tiles * (unsigned)args.n_tiles;
     const unsigned work_total = tiles_mn * (unsigned)args.split_k;
@@ -843,7 +847,7 @@ template <int BN, bool PAIR> mcb_status launch(mcb_ctx *ctx, const TcGemmParams 
     }
     if (!PAIR) {
         int grid = (int)(work < ctx->sm_count ? work : ctx->sm_count);
-        tc_gemm_kernel<BN, false><<<grid, kThreads, C::kSmemBytes, ctx->stream>>>(map_a, map_b, map_d, map_pre, a);
+        MCB_CUDA(ctx, mcb_launch_dep(ctx, tc_gemm_kernel<BN, false>, dim3(grid), dim3(kThreads), C::kSmemBytes, map_a, map_b, map_d, map_pre, a));
     } else {
         int pairs = (int)(work < max_pairs ? work : max_pairs);
         cudaLaunchConfig_t cfg = {};
@@ -851,13 +855,15 @@ template <int BN, bool PAIR> mcb_status launch(mcb_ctx *ctx, const TcGemmParams 
         cfg.blockDim = dim3(kThreads);
         cfg.dynamicSmemBytes = C::kSmemBytes;
         cfg.stream = ctx->stream;
-        cudaLaunchAttribute at[1];
+        cudaLaunchAttribute at[2];
         at[0].id = cudaLaunchAttributeClusterDimension;
         at[0].val.clusterDim.x = 2;
         at[0].val.clusterDim.y = 1;
         at[0].val.clusterDim.z = 1;
+        at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization; // see dep_wait() in the kernel
+        at[1].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = at;
-        cfg.numAttrs = 1;
+        cfg.numAttrs = ctx->dep_launch ? 2 : 1;
         MCB_CUDA(ctx, cudaLaunchKernelEx(&cfg, tc_gemm_kernel<BN, true>, map_a, map_b, map_d, map_pre, a));
     }
     MCB_LAUNCHED(ctx);

@@ -64,6 +64,9 @@ mcb_status mcb_ln_fast_backward(mcb_ctx *ctx, const float *x, const float *gamma
 // problems with enough rows to fill every SM; MCB_UNSUPPORTED (nothing launched) otherwise
 mcb_status mcb_ln_bulk_forward(mcb_ctx *ctx, const float *x, const float *gamma, const float *beta, double eps, void *out, int32_t out_dt,
                                float *mean, float *rstd, int64_t rows, int64_t dim);
+// sum = x + res (res f32 or bf16) and out = LayerNorm(sum) in one pass
+mcb_status mcb_ln_bulk_add_forward(mcb_ctx *ctx, const float *x, const void *res, int32_t res_dt, const float *gamma, const float *beta, double eps,
+                                   float *sum, void *out, int32_t out_dt, float *mean, float *rstd, int64_t rows, int64_t dim);
 mcb_status mcb_ln_bulk_backward(mcb_ctx *ctx, const float *x, const float *gamma, const void *g, int32_t g_dt, double eps, const float *mean,
                                 const float *rstd, const float *addend, float *dx, float *dgamma, float *dbeta, int64_t rows, int64_t dim);
 // reduce.cu: LayerNorm backward that writes dx as addend + dx when `addend` is given (may alias dx);

@@ -9,6 +9,8 @@
 // (layer_norm_fast.cu: 255 registers, one block per SM, 3.4 TB/s).  Every mbarrier wait is bounded.
 // dgamma / dbeta: per-lane register sums over the rows a warp handles, folded through shared memory in
 // a fixed warp order, finished by ln_bulk_params_final over the per-CTA partials (no float atomics).
+#include <type_traits>
+
 #include "common.cuh"
 #include "internal.h"
 #include "tc_ptx.cuh"
@@ -30,6 +32,7 @@ struct LnBulkArgs {
     void *out;           // forward: y (f32 or bf16); backward: dx (f32)
     float *mean_out, *rstd_out;
     float *partial;      // backward: [grid][2][dim]
+    float *sum_out;      // forward with a residual operand (g): x + g, written beside the normalised rows
     long long rows;
     int dim;
     int stages;
@@ -95,10 +98,16 @@ __device__ __forceinline__ void ring_init(const LnBulkArgs &a, unsigned long lon
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
+    dep_wait(); // global memory is touched only from here on
+    dep_trigger();
 }
 
-template <typename OutT, int NV>
+// ResT = void: y = LN(x).  Otherwise the residual add of a pre-norm block rides along: s = x + g (g of type
+// ResT) is written to sum_out and y = LN(s), in the arithmetic of the separate add and LayerNorm kernels.
+template <typename OutT, int NV, typename ResT>
 __global__ void __launch_bounds__(kThreads, 1) ln_fwd_bulk_kernel(const LnBulkArgs a) {
+    constexpr bool kRes = !std::is_same<ResT, void>::value;
+    typedef typename std::conditional<kRes, ResT, float>::type RT;
     extern __shared__ __align__(128) unsigned char smem[];
     unsigned long long *full = (unsigned long long *)(smem + (size_t)a.stages * a.stage_bytes), *empty = full + kMaxStages;
     volatile int *abort_flag = (volatile int *)(empty + kMaxStages);
@@ -106,9 +115,9 @@ __global__ void __launch_bounds__(kThreads, 1) ln_fwd_bulk_kernel(const LnBulkAr
     ring_init(a, full, empty, abort_flag);
     if (warp == kRows) {
         if (lane == 0) {
-            const void *const src[3] = {a.x, nullptr, nullptr};
-            const unsigned elem[3] = {4u, 0u, 0u}, off[3] = {0u, 0u, 0u};
-            produce<1>(a, smem, full, empty, abort_flag, src, elem, off);
+            const void *const src[3] = {a.x, kRes ? a.g : nullptr, nullptr};
+            const unsigned elem[3] = {4u, (unsigned)sizeof(RT), 0u}, off[3] = {0u, a.off_g, 0u};
+            produce<2>(a, smem, full, empty, abort_flag, src, elem, off);
         }
         return;
     }
@@ -136,6 +145,13 @@ __global__ void __launch_bounds__(kThreads, 1) ln_fwd_bulk_kernel(const LnBulkAr
             for (int j = 0; j < NV; ++j) {
                 const int idx = lane + 32 * j;
                 v[j] = idx < dim4 ? sx[idx] : make_float4(0.f, 0.f, 0.f, 0.f);
+                if (kRes && idx < dim4) {
+                    const typename Raw4<RT>::type *sg =
+                        reinterpret_cast<const typename Raw4<RT>::type *>(smem + (size_t)s * a.stage_bytes + a.off_g + (size_t)warp * a.dim * sizeof(RT));
+                    const float4 t = unpack4(sg[idx]);
+                    v[j] = make_float4(v[j].x + t.x, v[j].y + t.y, v[j].z + t.z, v[j].w + t.w);
+                    reinterpret_cast<float4 *>(a.sum_out + r * a.dim)[idx] = v[j];
+                }
                 sum += (v[j].x + v[j].y) + (v[j].z + v[j].w);
             }
             const float mean = warp_sum(sum) * inv_dim;
@@ -314,6 +330,8 @@ __global__ void ln_bulk_params_final(const float *__restrict__ partial, int bloc
     // block (32, 32): 32 of the 2*dim columns, 32 interleaved groups of per-CTA partials, fixed order
     __shared__ float red[32][33];
     const int j = blockIdx.x * 32 + threadIdx.x;
+    dep_wait();
+    dep_trigger();
     float t = 0.0f;
     if (j < 2 * dim) {
 #pragma unroll 4
@@ -350,20 +368,20 @@ int plan_stages(unsigned stage_bytes) {
 template <typename K> mcb_status launch(mcb_ctx *ctx, K kernel, const LnBulkArgs &a, int grid, const char *what) {
     const size_t smem = (size_t)a.stages * a.stage_bytes + 2 * kMaxStages * sizeof(unsigned long long) + 16;
     MCB_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kernel<<<grid, kThreads, smem, ctx->stream>>>(a);
+    MCB_CUDA(ctx, mcb_launch_dep(ctx, kernel, dim3(grid), dim3(kThreads), smem, a));
     MCB_LAUNCHED(ctx);
     (void)what;
     return MCB_OK;
 }
 
-template <typename OutT> mcb_status launch_fwd(mcb_ctx *ctx, int nv, const LnBulkArgs &a, int grid) {
+template <typename OutT, typename ResT> mcb_status launch_fwd(mcb_ctx *ctx, int nv, const LnBulkArgs &a, int grid) {
     switch (nv) {
-    case 1: return launch(ctx, ln_fwd_bulk_kernel<OutT, 1>, a, grid, "fwd");
-    case 2: return launch(ctx, ln_fwd_bulk_kernel<OutT, 2>, a, grid, "fwd");
-    case 3: return launch(ctx, ln_fwd_bulk_kernel<OutT, 3>, a, grid, "fwd");
-    case 4: return launch(ctx, ln_fwd_bulk_kernel<OutT, 4>, a, grid, "fwd");
-    case 6: return launch(ctx, ln_fwd_bulk_kernel<OutT, 6>, a, grid, "fwd");
-    default: return launch(ctx, ln_fwd_bulk_kernel<OutT, 8>, a, grid, "fwd");
+    case 1: return launch(ctx, ln_fwd_bulk_kernel<OutT, 1, ResT>, a, grid, "fwd");
+    case 2: return launch(ctx, ln_fwd_bulk_kernel<OutT, 2, ResT>, a, grid, "fwd");
+    case 3: return launch(ctx, ln_fwd_bulk_kernel<OutT, 3, ResT>, a, grid, "fwd");
+    case 4: return launch(ctx, ln_fwd_bulk_kernel<OutT, 4, ResT>, a, grid, "fwd");
+    case 6: return launch(ctx, ln_fwd_bulk_kernel<OutT, 6, ResT>, a, grid, "fwd");
+    default: return launch(ctx, ln_fwd_bulk_kernel<OutT, 8, ResT>, a, grid, "fwd");
     }
 }
 template <typename GT> mcb_status launch_bwd(mcb_ctx *ctx, int nv, const LnBulkArgs &a, int grid) {
@@ -398,8 +416,32 @@ mcb_status mcb_ln_bulk_forward(mcb_ctx *ctx, const float *x, const float *gamma,
     const int64_t nblk = (rows + kRows - 1) / kRows;
     const int grid = (int)(nblk < ctx->sm_count ? nblk : ctx->sm_count);
     const int nv = pick_nv(dim);
-    if (out_dt == MCB_F32) return launch_fwd<float>(ctx, nv, a, grid);
-    return launch_fwd<__nv_bfloat16>(ctx, nv, a, grid);
+    if (out_dt == MCB_F32) return launch_fwd<float, void>(ctx, nv, a, grid);
+    return launch_fwd<__nv_bfloat16, void>(ctx, nv, a, grid);
+}
+
+// sum = x + res (res f32 or bf16), out = LayerNorm(sum): the residual add and the LayerNorm that follows it in a
+// pre-norm block, in one pass over the rows.  Same arithmetic as mcb_add_typed followed by mcb_layer_norm.
+mcb_status mcb_ln_bulk_add_forward(mcb_ctx *ctx, const float *x, const void *res, int32_t res_dt, const float *gamma, const float *beta, double eps,
+                                   float *sum, void *out, int32_t out_dt, float *mean, float *rstd, int64_t rows, int64_t dim) {
+    if (!eligible(rows, dim, x, gamma, beta, out) || !mcb_aligned16(res) || !mcb_aligned16(sum) || getenv("MCB_LN_NO_BULK")) return MCB_UNSUPPORTED;
+    if ((res_dt != MCB_F32 && res_dt != MCB_BF16) || (out_dt != MCB_F32 && out_dt != MCB_BF16)) return MCB_UNSUPPORTED;
+    LnBulkArgs a = {};
+    a.x = x; a.g = res; a.gamma = gamma; a.beta = beta; a.out = out; a.sum_out = sum; a.mean_out = mean; a.rstd_out = rstd;
+    a.rows = rows; a.dim = (int)dim; a.eps = (float)eps; a.err = ctx->d_err;
+    a.off_g = round128((size_t)kRows * dim * 4);
+    a.stage_bytes = a.off_g + round128((size_t)kRows * dim * (res_dt == MCB_BF16 ? 2 : 4));
+    a.stages = plan_stages(a.stage_bytes);
+    if (!a.stages) return MCB_UNSUPPORTED;
+    const int64_t nblk = (rows + kRows - 1) / kRows;
+    const int grid = (int)(nblk < ctx->sm_count ? nblk : ctx->sm_count);
+    const int nv = pick_nv(dim);
+    if (out_dt == MCB_F32) {
+        if (res_dt == MCB_F32) return launch_fwd<float, float>(ctx, nv, a, grid);
+        return launch_fwd<float, __nv_bfloat16>(ctx, nv, a, grid);
+    }
+    if (res_dt == MCB_F32) return launch_fwd<__nv_bfloat16, float>(ctx, nv, a, grid);
+    return launch_fwd<__nv_bfloat16, __nv_bfloat16>(ctx, nv, a, grid);
 }
 
 mcb_status mcb_ln_bulk_backward(mcb_ctx *ctx, const float *x, const float *gamma, const void *g, int32_t g_dt, double eps, const float *mean,
@@ -422,7 +464,7 @@ mcb_status mcb_ln_bulk_backward(mcb_ctx *ctx, const float *x, const float *gamma
     const int nv = pick_nv(dim);
     if (g_dt == MCB_F32) MCB_TRY(launch_bwd<float>(ctx, nv, a, grid));
     else MCB_TRY(launch_bwd<__nv_bfloat16>(ctx, nv, a, grid));
-    ln_bulk_params_final<<<(int)((2 * dim + 31) / 32), dim3(32, 32), 0, ctx->stream>>>((const float *)scratch, grid, (int)dim, dgamma, dbeta);
+    MCB_CUDA(ctx, mcb_launch_dep(ctx, ln_bulk_params_final, dim3((unsigned)((2 * dim + 31) / 32)), dim3(32, 32), 0, (const float *)scratch, grid, (int)dim, dgamma, dbeta));
     MCB_LAUNCHED(ctx);
     return MCB_OK;
 }

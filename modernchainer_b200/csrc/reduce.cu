@@ -77,6 +77,8 @@ __global__ void __launch_bounds__(256) col_sum_vec_kernel(const T *__restrict__ 
     long long rows_per = (rows + gridDim.y - 1) / gridDim.y;
     long long r0 = (long long)blockIdx.y * rows_per, r1 = r0 + rows_per < rows ? r0 + rows_per : rows;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    dep_wait();
+    dep_trigger();
     if (col < cols) {
         long long c4 = col >> 2, ld4 = cols >> 2;
 #pragma unroll 4
@@ -109,6 +111,8 @@ __global__ void partial_sum_final_kernel(const float *__restrict__ partial, int 
     long long col = (long long)blockIdx.x * 32 + threadIdx.x;
     const int groups = blockDim.y; // 8 or 32 interleaved groups of partial rows
     float t = 0.0f;
+    dep_wait();
+    dep_trigger();
     if (col < cols) {
 #pragma unroll 4
         for (int s = threadIdx.y; s < parts; s += groups) t += partial[(long long)s * cols + col];
@@ -539,10 +543,14 @@ mcb_status mcb_col_sum(mcb_ctx *ctx, const void *a, int32_t dt, int64_t rows, in
         void *scratch;
         MCB_TRY(mcb_scratch(ctx, sizeof(float) * splits * cols, &scratch));
         dim3 grid(chunks, splits);
-        if (dt == MCB_F32) col_sum_vec_kernel<float><<<grid, 256, 0, ctx->stream>>>((const float *)a, rows, cols, (float *)scratch);
-        else col_sum_vec_kernel<__nv_bfloat16><<<grid, 256, 0, ctx->stream>>>((const __nv_bfloat16 *)a, rows, cols, (float *)scratch);
+        if (dt == MCB_F32)
+            MCB_CUDA(ctx, mcb_launch_dep(ctx, col_sum_vec_kernel<float>, grid, dim3(256), 0, (const float *)a, (long long)rows, (long long)cols, (float *)scratch));
+        else
+            MCB_CUDA(ctx, mcb_launch_dep(ctx, col_sum_vec_kernel<__nv_bfloat16>, grid, dim3(256), 0, (const __nv_bfloat16 *)a, (long long)rows,
+                                         (long long)cols, (float *)scratch));
         MCB_LAUNCHED(ctx);
-        partial_sum_final_kernel<<<(int)((cols + 31) / 32), dim3(32, 32), 0, ctx->stream>>>((const float *)scratch, splits, cols, out);
+        MCB_CUDA(ctx, mcb_launch_dep(ctx, partial_sum_final_kernel, dim3((unsigned)((cols + 31) / 32)), dim3(32, 32), 0, (const float *)scratch, splits,
+                                     (long long)cols, out));
         MCB_LAUNCHED(ctx);
         return MCB_OK;
     }
@@ -799,7 +807,7 @@ mcb_status mcb_sum_scaled(mcb_ctx *ctx, const float *x, int64_t n, double scale,
 // out[col] = sum of `parts` rows of partial[parts, cols], in a fixed order (used by fused kernels
 // in other files that leave per-block column sums in the context's scratch buffer)
 mcb_status mcb_partial_sum_final(mcb_ctx *ctx, const float *partial, int parts, int64_t cols, float *out) {
-    partial_sum_final_kernel<<<(int)((cols + 31) / 32), dim3(32, 32), 0, ctx->stream>>>(partial, parts, cols, out);
+    MCB_CUDA(ctx, mcb_launch_dep(ctx, partial_sum_final_kernel, dim3((unsigned)((cols + 31) / 32)), dim3(32, 32), 0, partial, parts, (long long)cols, out));
     MCB_LAUNCHED(ctx);
     return MCB_OK;
 }

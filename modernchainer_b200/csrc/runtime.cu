@@ -85,6 +85,7 @@ mcb_status mcb_ctx_create(int32_t ordinal, mcb_ctx **out) {
         return MCB_BACKEND;
     }
     ctx->sm_count = prop.multiProcessorCount;
+    ctx->dep_launch = getenv("MCB_NO_DEP_LAUNCH") == nullptr; // test knob: plain stream-ordered launches
     *out = ctx;
     return MCB_OK;
 }

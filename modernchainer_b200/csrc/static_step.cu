@@ -203,6 +203,17 @@ mcb_status mcb_static_step_create(mcb_model *model, mcb_adam *opt, mcb_scaler *s
             graph = g;
         }
     }
+    if (st == MCB_OK && getenv("MCB_GRAPH_INFO")) { // diagnostic: how many recorded edges are programmatic (dependent launch)
+        size_t ne = 0, prog = 0;
+        if (cudaGraphGetEdges_v2(graph, nullptr, nullptr, nullptr, &ne) == cudaSuccess && ne) {
+            std::vector<cudaGraphNode_t> from(ne), to(ne);
+            std::vector<cudaGraphEdgeData> ed(ne);
+            if (cudaGraphGetEdges_v2(graph, from.data(), to.data(), ed.data(), &ne) == cudaSuccess)
+                for (size_t i = 0; i < ne; ++i) prog += ed[i].type == cudaGraphDependencyTypeProgrammatic;
+        }
+        fprintf(stderr, "static step graph: %zu edges, %zu programmatic\n", ne, prog);
+        (void)cudaGetLastError();
+    }
     if (st == MCB_OK) {
         cudaError_t e = cudaGraphInstantiate(&s->exec, graph, 0);
         if (e != cudaSuccess) st = mcb_cuda_check(ctx, e, "graph instantiate");

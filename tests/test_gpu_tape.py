@@ -448,12 +448,14 @@ def test_fused_backward_passes_match_separate_kernels(mc, ctx, cfg):
         assert np.abs(a - r).max() <= 1e-5 * max(float(np.abs(r).max()), 1e-30), (i, shapes[i])
 
 
+@pytest.mark.parametrize("knob", ["MCB_LN_NO_BULK", "MCB_UNFUSED_ADD_LN"])
 @pytest.mark.parametrize("cfg", [(1000, 256, 4, 512, 2, 200, 8), (2048, 768, 12, 3072, 1, 1024, 2)])
-def test_layer_norm_pipeline_kernels_match_register_kernels_on_the_tape(mc, ctx, cfg):
+def test_layer_norm_pipeline_kernels_match_register_kernels_on_the_tape(mc, ctx, cfg, knob):
     """With at least 8 x 148 rows LayerNorm runs as the bulk-copy shared-memory pipeline, forward and
-    backward (with the in-place add into the pending residual gradient).  The same tape with those
-    kernels switched off (MCB_LN_NO_BULK: one row per warp held in registers) must give the same loss
-    and gradients up to the grouping of the f32 column sums."""
+    backward (with the in-place add into the pending residual gradient), and the residual add in front
+    of a LayerNorm is computed by the same kernel.  The same tape with those kernels switched off
+    (MCB_LN_NO_BULK: one row per warp held in registers; MCB_UNFUSED_ADD_LN: separate add and
+    LayerNorm kernels) must give the same loss and gradients up to the grouping of the f32 column sums."""
     import os
     rng = np.random.default_rng(123)
     vocab, d, heads, ff, layers, s, b = cfg
@@ -462,9 +464,9 @@ def test_layer_norm_pipeline_kernels_match_register_kernels_on_the_tape(mc, ctx,
 
     def run(no_bulk):
         if no_bulk:
-            os.environ["MCB_LN_NO_BULK"] = "1"
+            os.environ[knob] = "1"
         else:
-            os.environ.pop("MCB_LN_NO_BULK", None)
+            os.environ.pop(knob, None)
         try:
             m = mc.Model(ctx, "decoder", [vocab, d, heads, ff, layers, 0])
             ps = m.parameters()
@@ -474,7 +476,7 @@ def test_layer_norm_pipeline_kernels_match_register_kernels_on_the_tape(mc, ctx,
             loss.backward()
             return float(loss.data.reshape(-1)[0]), [p.grad for p in ps], [p.data.shape for p in ps]
         finally:
-            os.environ.pop("MCB_LN_NO_BULK", None)
+            os.environ.pop(knob, None)
 
     lp, gp, shapes = run(False)
     lr, gr, _ = run(True)
