@@ -170,6 +170,10 @@ mcb_status backward(const Var &root) {
     std::vector<Var> order;
     std::unordered_set<VarImpl *> seen;
     std::vector<std::pair<Var, bool>> stack;
+    // How many node inputs each leaf feeds.  The visiting order puts the leaves last, but a leaf's gradient is
+    // final as soon as its last consumer has run: it is stored then (same value, same order of additions), so a
+    // data-parallel bucket can start its all-reduce while the rest of backward still runs.
+    std::unordered_map<VarImpl *, int> leaf_uses;
     stack.emplace_back(root, false);
     while (!stack.empty()) {
         auto top = stack.back();
@@ -181,7 +185,10 @@ mcb_status backward(const Var &root) {
         if (!seen.insert(top.first.get()).second) continue;
         stack.emplace_back(top.first, true);
         if (top.first->node)
-            for (auto &in : top.first->node->inputs) stack.emplace_back(in, false);
+            for (auto &in : top.first->node->inputs) {
+                stack.emplace_back(in, false);
+                if (!in->node && in->requires_grad) ++leaf_uses[in.get()];
+            }
     }
     std::unordered_map<VarImpl *, Tensor> grads;
     {
@@ -197,15 +204,35 @@ mcb_status backward(const Var &root) {
     }
     std::vector<Arena *> touched;
     mcb_status st = MCB_OK;
+    auto store_leaf = [&](const Var &leaf, const Tensor &g) -> mcb_status {
+        if (leaf->arena && std::find(touched.begin(), touched.end(), leaf->arena) == touched.end()) touched.push_back(leaf->arena);
+        return accumulate_leaf(leaf, g);
+    };
+    // a node is done with (it ran, or no gradient reached it): leaves it was the last consumer of are stored now
+    auto release_inputs = [&](const Var &v) -> mcb_status {
+        for (const Var &in : v->node->inputs) {
+            if (in->node || !in->requires_grad) continue;
+            auto u = leaf_uses.find(in.get());
+            if (u == leaf_uses.end() || --u->second > 0) continue;
+            auto e = grads.find(in.get());
+            if (e == grads.end()) continue;
+            Tensor g = e->second;
+            grads.erase(e);
+            MCB_TRY(store_leaf(in, g));
+        }
+        return MCB_OK;
+    };
     for (auto it = order.rbegin(); it != order.rend() && st == MCB_OK; ++it) {
         const Var &v = *it;
         auto f = grads.find(v.get());
-        if (f == grads.end()) continue;
+        if (f == grads.end()) {
+            if (v->node) st = release_inputs(v);
+            continue;
+        }
         Tensor g = f->second;
         grads.erase(f);
         if (!v->node) {
-            if (v->arena && std::find(touched.begin(), touched.end(), v->arena) == touched.end()) touched.push_back(v->arena);
-            st = accumulate_leaf(v, g);
+            st = store_leaf(v, g);
             continue;
         }
         std::vector<Tensor> in_grads(v->node->inputs.size());
@@ -252,6 +279,7 @@ mcb_status backward(const Var &root) {
             }
             if (st != MCB_OK) break;
         }
+        if (st == MCB_OK) st = release_inputs(v);
     }
     for (Arena *a : touched) {
         for (VarImpl *c : a->claimed) c->slot_claimed = false;

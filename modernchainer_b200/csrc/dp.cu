@@ -49,6 +49,10 @@ struct DpState {
     cudaEvent_t ready = nullptr, done = nullptr;
     std::vector<char> launched; // per bucket, this round
     bool round_active = false;
+    // MCB_DP_TRACE (diagnostic, tape path only): per bucket, when it became ready and when its all-reduce ended
+    bool trace = false;
+    std::vector<cudaEvent_t> t_ready, t_end;
+    std::vector<int> t_bucket;
 };
 
 mcb_status nccl_check(mcb_ctx *ctx, ncclResult_t r, const char *what) {
@@ -66,7 +70,19 @@ mcb_status launch_bucket(Arena *a, int b) {
     MCB_CUDA(ctx, cudaStreamWaitEvent(dp->comm_stream, dp->ready, 0));
     float *g = (float *)a->g->p + a->bucket_begin[b];
     size_t count = (size_t)(a->bucket_end[b] - a->bucket_begin[b]);
-    return nccl_check(ctx, api().AllReduce(g, g, count, ncclFloat, ncclSum, dp->comm, dp->comm_stream), "all-reduce");
+    const bool trace = dp->trace && ctx->capture_id == 0;
+    if (trace) {
+        cudaEvent_t e0, e1;
+        cudaEventCreate(&e0);
+        cudaEventCreate(&e1);
+        cudaEventRecord(e0, dp->comm_stream);
+        dp->t_ready.push_back(e0);
+        dp->t_end.push_back(e1);
+        dp->t_bucket.push_back(b);
+    }
+    mcb_status st = nccl_check(ctx, api().AllReduce(g, g, count, ncclFloat, ncclSum, dp->comm, dp->comm_stream), "all-reduce");
+    if (trace) cudaEventRecord(dp->t_end.back(), dp->comm_stream);
+    return st;
 }
 
 } // namespace
@@ -90,8 +106,35 @@ mcb_status arena_wait_comm(Arena *a) {
     // buckets whose parameters did not all receive a gradient still have to take part,
     // or the ranks' collectives would not match
     for (size_t b = 0; b < a->bucket_begin.size(); ++b) MCB_TRY(launch_bucket(a, (int)b));
+    cudaEvent_t tail = nullptr;
+    if (dp->trace && !dp->t_ready.empty()) { // where the compute stream's own backward work ends
+        cudaEventCreate(&tail);
+        cudaEventRecord(tail, ctx->stream);
+    }
     MCB_CUDA(ctx, cudaEventRecord(dp->done, dp->comm_stream));
     MCB_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, dp->done, 0));
+    if (tail) {
+        cudaStreamSynchronize(dp->comm_stream);
+        cudaStreamSynchronize(ctx->stream);
+        if (dp->rank == 0) {
+            for (size_t i = 0; i < dp->t_ready.size(); ++i) {
+                float r = 0, e = 0;
+                cudaEventElapsedTime(&r, dp->t_ready[0], dp->t_ready[i]);
+                cudaEventElapsedTime(&e, dp->t_ready[0], dp->t_end[i]);
+                fprintf(stderr, "dp trace: bucket %d (%.1f MB) ready %.3f ms, reduced %.3f ms\n", dp->t_bucket[i],
+                        (a->bucket_end[dp->t_bucket[i]] - a->bucket_begin[dp->t_bucket[i]]) * 4e-6, r, e);
+            }
+            float t = 0;
+            cudaEventElapsedTime(&t, dp->t_ready[0], tail);
+            fprintf(stderr, "dp trace: compute stream reaches the optimizer at %.3f ms\n", t);
+        }
+        for (cudaEvent_t e : dp->t_ready) cudaEventDestroy(e);
+        for (cudaEvent_t e : dp->t_end) cudaEventDestroy(e);
+        cudaEventDestroy(tail);
+        dp->t_ready.clear();
+        dp->t_end.clear();
+        dp->t_bucket.clear();
+    }
     dp->round_active = false;
     std::fill(dp->launched.begin(), dp->launched.end(), 0);
     a->bucket_pending = a->bucket_size;
@@ -154,6 +197,7 @@ mcb_status mcb_dp_init(mcb_ctx *ctx, int32_t rank, int32_t world, const void *ho
     MCB_CUDA(ctx, cudaStreamCreateWithPriority(&dp->comm_stream, cudaStreamNonBlocking, hi));
     MCB_CUDA(ctx, cudaEventCreateWithFlags(&dp->ready, cudaEventDisableTiming));
     MCB_CUDA(ctx, cudaEventCreateWithFlags(&dp->done, cudaEventDisableTiming));
+    dp->trace = getenv("MCB_DP_TRACE") != nullptr;
     ctx->dp = dp;
     return MCB_OK;
 }

@@ -85,6 +85,11 @@ mcb_status mcb_ctx_create(int32_t ordinal, mcb_ctx **out) {
         return MCB_BACKEND;
     }
     ctx->sm_count = prop.multiProcessorCount;
+    // MCB_SM_LIMIT: size persistent grids for fewer SMs (leaves room for communication kernels that run beside the step)
+    if (const char *lim = getenv("MCB_SM_LIMIT")) {
+        int v = atoi(lim);
+        if (v >= 8 && v < ctx->sm_count) ctx->sm_count = v;
+    }
     ctx->dep_launch = getenv("MCB_NO_DEP_LAUNCH") == nullptr; // test knob: plain stream-ordered launches
     *out = ctx;
     return MCB_OK;
