@@ -920,12 +920,13 @@ mcb_status f_sce_consuming(const Var &logits, const Var &target, Var *out) {
     if (target->data.numel() != n) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "expected %lld targets", (long long)n);
     Tensor res;
     MCB_TRY(new_tensor(ctx, MCB_F32, {}, &res));
-    Tensor x = logits->data, lab = target->data;
-    MCB_TRY(mcb_sce_grad(ctx, x.ptr, nullptr, x.dt, lab.ptr, ldt, n, c, (float *)res.ptr, nullptr)); // loss only
-    *out = apply(ctx, "SoftmaxCrossEntropy", res, {logits, target}, [ctx, x, lab, ldt, n, c](const Tensor &g, std::vector<Tensor> &gi) -> mcb_status {
+    Tensor x = logits->data, lab = target->data, stats;
+    MCB_TRY(new_tensor(ctx, MCB_F32, {n, 2}, &stats)); // row maximum and sum of exp: the gradient pass streams the rows without reducing them again
+    MCB_TRY(mcb_sce_grad(ctx, x.ptr, nullptr, x.dt, lab.ptr, ldt, n, c, (float *)res.ptr, nullptr, (float *)stats.ptr, nullptr)); // loss only
+    *out = apply(ctx, "SoftmaxCrossEntropy", res, {logits, target}, [ctx, x, lab, stats, ldt, n, c](const Tensor &g, std::vector<Tensor> &gi) -> mcb_status {
         Tensor gf;
         MCB_TRY(to_dtype(ctx, g, MCB_F32, &gf));
-        MCB_TRY(mcb_sce_grad(ctx, x.ptr, x.ptr, x.dt, lab.ptr, ldt, n, c, nullptr, (const float *)gf.ptr));
+        MCB_TRY(mcb_sce_grad(ctx, x.ptr, x.ptr, x.dt, lab.ptr, ldt, n, c, nullptr, (const float *)gf.ptr, nullptr, (const float *)stats.ptr));
         gi[0] = x;
         return MCB_OK;
     });

@@ -76,7 +76,8 @@ mcb_status mcb_layer_norm_backward_ex(mcb_ctx *ctx, const float *x, const float 
                                       float *dbeta, int64_t rows, int64_t dim);
 // reduce.cu
 mcb_status mcb_sce_grad(mcb_ctx *ctx, const void *logits, void *out, int32_t dt, const void *labels, int32_t label_dt,
-                        int64_t n, int64_t c, float *loss_out, const float *upstream);
+                        int64_t n, int64_t c, float *loss_out, const float *upstream, float *stats_out = nullptr,
+                        const float *stats_in = nullptr); // stats: [n][2] row maximum and sum of exp, passed from the loss pass to the gradient pass
 mcb_status mcb_sum_scaled(mcb_ctx *ctx, const float *x, int64_t n, double scale, float *out);
 // elementwise.cu
 // out[i] = (*scalar) * factor for all i (broadcast of a device scalar)

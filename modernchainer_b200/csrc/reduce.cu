@@ -345,6 +345,7 @@ __device__ __forceinline__ void row_max_sumexp(const T *__restrict__ row, long l
     if (vec8) {
         // bf16 rows: 16-byte loads, 8 logits per thread per step
         const uint4 *r8 = reinterpret_cast<const uint4 *>(row);
+#pragma unroll 4
         for (long long j = threadIdx.x; j < (c >> 3); j += blockDim.x) {
             uint4 raw = r8[j];
             float f[8];
@@ -420,10 +421,12 @@ __global__ void sce_final_kernel(const float *__restrict__ row_loss, long long n
 }
 // fused: row loss + in-place gradient, one DRAM read and one DRAM write of the logits
 // `out` may alias `x` (each block reads its whole row before it writes any of it).
+// `stats_out` / `stats_in` ([n][2]: row maximum, sum of exp): the loss pass of a training step leaves them for the
+// gradient pass, which then needs no reduction over the row and streams it once.
 template <typename T>
 __global__ void sce_fused_kernel(const T *x, T *out, const void *__restrict__ labels, int label_dt, long long n,
                                  long long c, float *__restrict__ row_loss, const float *__restrict__ upstream,
-                                 unsigned int *err) {
+                                 unsigned int *err, float *__restrict__ stats_out, const float *__restrict__ stats_in) {
     __shared__ float red[32];
     long long i = blockIdx.x;
     long long lab = load_index(labels, label_dt, i);
@@ -439,15 +442,55 @@ __global__ void sce_fused_kernel(const T *x, T *out, const void *__restrict__ la
         return;
     }
     float mx, sum;
-    row_max_sumexp<T>(row, c, red, mx, sum);
-    float at_label = Elem<T>::ld(row, lab);
-    __syncthreads(); // every thread has read row[lab] before anyone overwrites it
-    if (threadIdx.x == 0 && row_loss) row_loss[i] = (mx + logf(sum)) - at_label;
+    if (stats_in) {
+        mx = stats_in[2 * i];
+        sum = stats_in[2 * i + 1];
+    } else {
+        row_max_sumexp<T>(row, c, red, mx, sum);
+    }
+    if (row_loss) { // the label's logit is read before anyone overwrites it
+        float at_label = Elem<T>::ld(row, lab);
+        __syncthreads();
+        if (threadIdx.x == 0) row_loss[i] = (mx + logf(sum)) - at_label;
+    }
+    if (threadIdx.x == 0 && stats_out) {
+        stats_out[2 * i] = mx;
+        stats_out[2 * i + 1] = sum;
+    }
     if (!out) return; // loss only
     float up = upstream ? upstream[0] : 1.0f;
     float inv_sum = 1.0f / sum, k = up / (float)n;
     bool vec = ((c & 3) == 0) && (((reinterpret_cast<uintptr_t>(row) | reinterpret_cast<uintptr_t>(orow)) & (4 * sizeof(T) - 1)) == 0);
-    if (vec) {
+    const bool vec8 = sizeof(T) == 2 && ((c & 7) == 0) && (((reinterpret_cast<uintptr_t>(row) | reinterpret_cast<uintptr_t>(orow)) & 15) == 0);
+    if (vec8) {
+        // bf16 rows: 16-byte loads and stores, 8 logits per thread per step, several steps in flight
+        const uint4 *r8 = reinterpret_cast<const uint4 *>(row);
+        uint4 *o8 = reinterpret_cast<uint4 *>(orow);
+#pragma unroll 4
+        for (long long j = threadIdx.x; j < (c >> 3); j += blockDim.x) {
+            const uint4 raw = r8[j];
+            const unsigned wds[4] = {raw.x, raw.y, raw.z, raw.w};
+            float p[8];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                p[2 * q] = row_exp<T>(__uint_as_float(wds[q] << 16) - mx) * inv_sum;
+                p[2 * q + 1] = row_exp<T>(__uint_as_float(wds[q] & 0xFFFF0000u) - mx) * inv_sum;
+            }
+            const long long b = j << 3;
+            if (lab >= b && lab < b + 8) {
+#pragma unroll
+                for (int q = 0; q < 8; ++q)
+                    if (lab - b == q) p[q] -= 1.0f;
+            }
+            unsigned ow[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                __nv_bfloat162 h = __floats2bfloat162_rn(p[2 * q] * k, p[2 * q + 1] * k);
+                ow[q] = *reinterpret_cast<unsigned *>(&h);
+            }
+            o8[j] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+        }
+    } else if (vec) {
         for (long long j = threadIdx.x; j < (c >> 2); j += blockDim.x) {
             float4 v = Elem<T>::ld4(row, j);
             long long b = j << 2;
@@ -663,8 +706,8 @@ mcb_status mcb_layer_norm_backward(mcb_ctx *ctx, const float *x, const float *ga
 
 } // extern "C"
 
-// With `addend` (may alias dx) the input gradient is written as addend + dx; only the register-resident
-// kernel does that, so other shapes return MCB_UNSUPPORTED before anything is launched.
+// With `addend` (may alias dx) the input gradient is written as addend + dx; only the pipeline and the
+// register-resident kernels do that, so other shapes return MCB_UNSUPPORTED before anything is launched.
 mcb_status mcb_layer_norm_backward_ex(mcb_ctx *ctx, const float *x, const float *gamma, const void *g, int32_t g_dt, double eps,
                                       const float *mean, const float *rstd, const float *addend, float *dx, float *dgamma,
                                       float *dbeta, int64_t rows, int64_t dim) {
@@ -727,13 +770,13 @@ mcb_status mcb_softmax_cross_entropy(mcb_ctx *ctx, const float *logits, const vo
 mcb_status mcb_softmax_cross_entropy_backward(mcb_ctx *ctx, const float *logits, const void *labels,
                                               int32_t label_dt, int64_t n, int64_t c, float *out) {
     MCB_CHECK_CTX(ctx);
-    return mcb_sce_grad(ctx, logits, out, MCB_F32, labels, label_dt, n, c, nullptr, nullptr);
+    return mcb_sce_grad(ctx, logits, out, MCB_F32, labels, label_dt, n, c, nullptr, nullptr, nullptr, nullptr);
 }
 
 mcb_status mcb_softmax_ce_fused(mcb_ctx *ctx, void *logits, int32_t logits_dt, const void *labels, int32_t label_dt,
                                 int64_t n, int64_t c, float *loss_out, const float *upstream) {
     MCB_CHECK_CTX(ctx);
-    return mcb_sce_grad(ctx, logits, logits, logits_dt, labels, label_dt, n, c, loss_out, upstream);
+    return mcb_sce_grad(ctx, logits, logits, logits_dt, labels, label_dt, n, c, loss_out, upstream, nullptr, nullptr);
 }
 
 mcb_status mcb_embedding(mcb_ctx *ctx, const void *ids, int32_t id_dt, int64_t n, const float *weight, int64_t vocab,
@@ -769,7 +812,7 @@ mcb_status mcb_embedding_backward(mcb_ctx *ctx, const void *ids, int32_t id_dt, 
 
 // gradient of the mean cross entropy (times *upstream), optionally with the loss, in one pass
 mcb_status mcb_sce_grad(mcb_ctx *ctx, const void *logits, void *out, int32_t dt, const void *labels, int32_t label_dt,
-                        int64_t n, int64_t c, float *loss_out, const float *upstream) {
+                        int64_t n, int64_t c, float *loss_out, const float *upstream, float *stats_out, const float *stats_in) {
     if (!index_dtype_ok(label_dt)) return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "labels must be i64, i32 or u8");
     if (n == 0) return loss_out ? mcb_memset(ctx, loss_out, 0, sizeof(float)) : MCB_OK;
     if (c == 0) return MCB_OK;
@@ -779,9 +822,9 @@ mcb_status mcb_sce_grad(mcb_ctx *ctx, const void *logits, void *out, int32_t dt,
     // algorithmic bytes: one read of the logits, one write of the gradient when requested
     ProfScope prof(ctx, MCB_PROF_LOSS, 0.0, (double)n * c * (dt == MCB_BF16 ? 2.0 : 4.0) * (out ? 2.0 : 1.0) + 8.0 * n);
     if (dt == MCB_F32)
-        sce_fused_kernel<float><<<(unsigned)n, threads, 0, ctx->stream>>>((const float *)logits, (float *)out, labels, label_dt, n, c, (float *)scratch, upstream, ctx->d_err);
+        sce_fused_kernel<float><<<(unsigned)n, threads, 0, ctx->stream>>>((const float *)logits, (float *)out, labels, label_dt, n, c, (float *)scratch, upstream, ctx->d_err, stats_out, stats_in);
     else if (dt == MCB_BF16)
-        sce_fused_kernel<__nv_bfloat16><<<(unsigned)n, threads, 0, ctx->stream>>>((const __nv_bfloat16 *)logits, (__nv_bfloat16 *)out, labels, label_dt, n, c, (float *)scratch, upstream, ctx->d_err);
+        sce_fused_kernel<__nv_bfloat16><<<(unsigned)n, threads, 0, ctx->stream>>>((const __nv_bfloat16 *)logits, (__nv_bfloat16 *)out, labels, label_dt, n, c, (float *)scratch, upstream, ctx->d_err, stats_out, stats_in);
     else
         return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "logits must be f32 or bf16");
     MCB_LAUNCHED(ctx);
