@@ -46,8 +46,45 @@ struct TcArgs {
     unsigned idesc;
     int m_tiles, n_tiles, kb_total, kb_per_split;
     int stages; // depth of the operand ring actually used (tuning knob; at most the compiled depth)
+    // Split tail (sk_splits > 1): work items [0, sk_full) are whole tiles; the sk_rem tiles that would form a
+    // mostly empty last wave are each cut into sk_splits slices of sk_kb k-blocks, whose f32 partial sums are
+    // added into a workspace (map_pre) that a finishing kernel converts into the output.
+    int sk_full, sk_rem, sk_splits, sk_kb;
     unsigned int *err;
 };
+
+struct WorkItem {
+    unsigned t;   // tile index (tn-major: t = tn * m_tiles + tm)
+    int kb0, kb1; // k-block range
+    int split;    // index of the slice along K (0 for whole tiles)
+    bool partial; // slice of a split-tail tile: f32 partial sum into the workspace
+};
+__device__ __forceinline__ WorkItem decode_work(const TcArgs &args, unsigned w, unsigned tiles_mn, bool one_split) {
+    WorkItem it;
+    if (args.sk_splits > 1) {
+        if (w < (unsigned)args.sk_full) {
+            it.t = w;
+            it.kb0 = 0;
+            it.kb1 = args.kb_total;
+            it.split = 0;
+            it.partial = false;
+        } else {
+            const unsigned idx = w - (unsigned)args.sk_full, q = idx / (unsigned)args.sk_splits;
+            it.split = (int)(idx - q * (unsigned)args.sk_splits);
+            it.t = (unsigned)args.sk_full + q;
+            it.kb0 = it.split * args.sk_kb;
+            it.kb1 = min(it.kb0 + args.sk_kb, args.kb_total);
+            it.partial = true;
+        }
+        return it;
+    }
+    it.split = one_split ? 0 : (int)(w / tiles_mn);
+    it.t = w - (unsigned)it.split * tiles_mn;
+    it.kb0 = it.split * args.kb_per_split;
+    it.kb1 = min(it.kb0 + args.kb_per_split, args.kb_total);
+    it.partial = false;
+    return it;
+}
 
 // ------------------------------------------------------------------ PTX wrappers
 __device__ __forceinline__ unsigned smem_u32(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -363,7 +400,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     dep_trigger();
 
     const unsigned tiles_mn = (unsigned)args.m_tiles * (unsigned)args.n_tiles;
-    const unsigned work_total = tiles_mn * (unsigned)args.split_k;
+    const unsigned work_total =
+        args.sk_splits > 1 ? (unsigned)args.sk_full + (unsigned)args.sk_rem * (unsigned)args.sk_splits : tiles_mn * (unsigned)args.split_k;
     const unsigned m_tiles = (unsigned)args.m_tiles;
     const bool one_split = args.split_k == 1;
 
@@ -384,12 +422,11 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             unsigned ph = 0;
             bool ok = true;
             for (unsigned w = w_first; w < work_total && ok; w += w_stride) {
-                int split = one_split ? 0 : (int)(w / tiles_mn);
-                unsigned t = w - (unsigned)split * tiles_mn;
+                const WorkItem wi = decode_work(args, w, tiles_mn, one_split);
+                const unsigned t = wi.t;
                 const unsigned tn = t / m_tiles, tm = t - tn * m_tiles;
                 int r0 = is_a ? (int)tm * kTileM + (int)crank * BM : (int)tn * BN + (int)crank * (PAIR ? BN / 2 : 0);
-                int kb0 = split * args.kb_per_split;
-                int kb1 = min(kb0 + args.kb_per_split, args.kb_total);
+                const int kb0 = wi.kb0, kb1 = wi.kb1;
                 for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     ok = mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag, args.err);
                     if (!ok) break;
@@ -452,9 +489,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             unsigned s = 0, soff = 0, ph = 0;
             bool ok = true;
             for (unsigned w = w_first; w < work_total && ok; w += w_stride, ++tile_it) {
-                int split = one_split ? 0 : (int)(w / tiles_mn);
-                int kb0 = split * args.kb_per_split;
-                int nkb = min(kb0 + args.kb_per_split, args.kb_total) - kb0;
+                const WorkItem wi = decode_work(args, w, tiles_mn, one_split);
+                const int nkb = wi.kb1 - wi.kb0;
                 int acc = tile_it & 1;
                 unsigned acc_ph = (tile_it >> 1) & 1u;
                 if (!mbar_wait(&acc_empty[acc], acc_ph ^ 1u, abort_flag, args.err)) break;
@@ -496,10 +532,11 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         rg.base = out_stage + q * 8192;
         rg.issued = 0;
         for (unsigned w = w_first; w < work_total; w += w_stride, ++tile_it) {
-            int split = one_split ? 0 : (int)(w / tiles_mn);
-            unsigned t = w - (unsigned)split * tiles_mn;
-            int kb0 = split * args.kb_per_split;
-            bool has_k = kb0 < args.kb_total;
+            const WorkItem wi = decode_work(args, w, tiles_mn, one_split);
+            const int split = wi.split;
+            const unsigned t = wi.t;
+            const bool part = wi.partial; // slice of a split-tail tile: plain f32 partial sum, added into the workspace
+            bool has_k = wi.kb0 < args.kb_total;
             // a pair's CTA holds its own 128 rows of the 256-row tile in its TMEM lanes, all BN columns
             const unsigned tn = t / m_tiles, tm = t - tn * m_tiles;
             long long m0 = (long long)tm * kTileM + (long long)crank * BM, n0 = (long long)tn * BN;
@@ -508,12 +545,12 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (!mbar_wait(&acc_full[acc], acc_ph, abort_flag, args.err, 100u)) break;
             tc_fence_after();
             long long row = m0 + q * 32 + lane;
-            bool add_bias = args.bias != nullptr && split == 0;
+            bool add_bias = args.bias != nullptr && split == 0 && !part;
             if (args.tma_out) {
                 // ---- staged output: rows of this warp's 32-row slab go out as 128-byte swizzled boxes
                 const int y0 = (int)(m0 + q * 32);
                 const bool live = has_k && (long long)y0 < args.m;
-                if (args.out_bf16) {
+                if (args.out_bf16 && !part) {
 #pragma unroll 1
                     for (int c0 = 0; c0 < BN; c0 += 64) {
                         unsigned r0[32], r1[32];
@@ -584,7 +621,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                             for (int j = 0; j < 32; ++j)
                                 if (col0 + j < args.n) v[j] += args.bias[col0 + j];
                         }
-                        if (!args.accumulate) {
+                        if (!args.accumulate && !part) {
                             if (args.act == MCB_ACT_GELU) {
 #pragma unroll
                                 for (int j = 0; j < 32; ++j) v[j] = gelu_f(v[j]);
@@ -599,7 +636,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                             ring_put(box, lane, j,
                                      make_uint4(__float_as_uint(v[4 * j]), __float_as_uint(v[4 * j + 1]), __float_as_uint(v[4 * j + 2]),
                                                 __float_as_uint(v[4 * j + 3])));
-                        ring_submit(rg, box, &map_d, (int)col0, y0, args.accumulate != 0, lane);
+                        ring_submit(rg, box, part ? &map_pre : &map_d, (int)col0, y0, args.accumulate != 0 || part, lane);
                     }
                 }
                 tc_fence_before();
@@ -771,6 +808,32 @@ mcb_status make_out_map(mcb_ctx *ctx, CUtensorMap *map, const void *base, bool b
     return MCB_OK;
 }
 
+// Finishes the tiles of a split tail: out[r][c] = act(ws[r][c] + bias[c]) over rows [row0, m) and columns
+// [col0, col1) (col0, col1, ld multiples of 4), four columns per thread.
+template <typename OutT>
+__global__ void tc_split_tail_finish_kernel(const float *__restrict__ ws, OutT *__restrict__ out, const float *__restrict__ bias, int act,
+                                            long long row0, long long m, long long col0, long long col1, long long ld) {
+    const long long w4 = (col1 - col0) >> 2, total = (m - row0) * w4;
+    dep_wait();
+    dep_trigger();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long r = row0 + i / w4, c = col0 + ((i % w4) << 2);
+        float4 v = *reinterpret_cast<const float4 *>(ws + r * ld + c);
+        if (bias) {
+            v.x += bias[c];
+            v.y += bias[c + 1];
+            v.z += bias[c + 2];
+            v.w += bias[c + 3];
+        }
+        if (act == MCB_ACT_GELU) {
+            v.x = gelu_f(v.x); v.y = gelu_f(v.y); v.z = gelu_f(v.z); v.w = gelu_f(v.w);
+        } else if (act == MCB_ACT_RELU) {
+            v.x = fmaxf(v.x, 0.0f); v.y = fmaxf(v.y, 0.0f); v.z = fmaxf(v.z, 0.0f); v.w = fmaxf(v.w, 0.0f);
+        }
+        Elem<OutT>::st4(out + r * ld, c >> 2, v);
+    }
+}
+
 template <int BN, bool PAIR> mcb_status launch(mcb_ctx *ctx, const TcGemmParams &p) {
     using C = Cfg<BN, PAIR>;
     constexpr int kTileM = PAIR ? 2 * BM : BM;
@@ -845,6 +908,52 @@ template <int BN, bool PAIR> mcb_status launch(mcb_ctx *ctx, const TcGemmParams 
         }
         attr_set = true;
     }
+    // Split tail: when the tiles do not fill the last wave, the tiles of that wave are cut along K so that every
+    // worker gets one slice; their f32 partial sums meet in a workspace and a small kernel finishes those tiles.
+    struct Region {
+        long long row0, col0, col1;
+    };
+    Region regions[4];
+    int n_regions = 0;
+    void *ws = nullptr;
+    a.sk_full = a.sk_rem = a.sk_kb = 0;
+    a.sk_splits = 1;
+    const int workers = PAIR ? max_pairs : ctx->sm_count;
+    const long long tiles = (long long)a.m_tiles * a.n_tiles;
+    if (p.split_tail && a.tma_out && !p.accumulate && split == 1 && !p.d_pre && tiles > workers && p.ldd % 4 == 0 && p.n % 4 == 0) {
+        const long long rem = tiles % workers, full = tiles - rem;
+        int s = rem > 0 ? (int)(workers / rem) : 1;
+        if (s > 8) s = 8;
+        if (s > a.kb_total / 4) s = a.kb_total / 4;
+        const long long tn0 = full / a.m_tiles;
+        if (s >= 2 && a.n_tiles - tn0 <= 4) {
+            const int kb = (a.kb_total + s - 1) / s;
+            s = (a.kb_total + kb - 1) / kb;
+            if (s >= 2) {
+                MCB_TRY(mcb_alloc(ctx, sizeof(float) * (size_t)p.m * (size_t)p.ldd, &ws));
+                mcb_status st = make_out_map(ctx, &map_pre, ws, false, p.n, p.m, p.ldd);
+                for (long long tn = tn0; tn < a.n_tiles && st == MCB_OK; ++tn) {
+                    Region r;
+                    r.row0 = (tn == tn0 ? full % a.m_tiles : 0) * (long long)kTileM;
+                    r.col0 = tn * BN;
+                    r.col1 = (tn + 1) * (long long)BN < p.n ? (tn + 1) * (long long)BN : p.n;
+                    regions[n_regions++] = r;
+                    cudaError_t e = cudaMemset2DAsync((float *)ws + r.row0 * p.ldd + r.col0, (size_t)p.ldd * 4, 0, (size_t)(r.col1 - r.col0) * 4,
+                                                      (size_t)(p.m - r.row0), ctx->stream);
+                    if (e != cudaSuccess) st = mcb_cuda_check(ctx, e, "split tail: workspace memset");
+                }
+                if (st != MCB_OK) {
+                    mcb_free(ctx, ws);
+                    return st;
+                }
+                a.sk_full = (int)full;
+                a.sk_rem = (int)rem;
+                a.sk_splits = s;
+                a.sk_kb = kb;
+                work = full + rem * s;
+            }
+        }
+    }
     if (!PAIR) {
         int grid = (int)(work < ctx->sm_count ? work : ctx->sm_count);
         MCB_CUDA(ctx, mcb_launch_dep(ctx, tc_gemm_kernel<BN, false>, dim3(grid), dim3(kThreads), C::kSmemBytes, map_a, map_b, map_d, map_pre, a));
@@ -867,6 +976,24 @@ template <int BN, bool PAIR> mcb_status launch(mcb_ctx *ctx, const TcGemmParams 
         MCB_CUDA(ctx, cudaLaunchKernelEx(&cfg, tc_gemm_kernel<BN, true>, map_a, map_b, map_d, map_pre, a));
     }
     MCB_LAUNCHED(ctx);
+    for (int i = 0; i < n_regions; ++i) {
+        const Region &r = regions[i];
+        const long long total4 = (p.m - r.row0) * ((r.col1 - r.col0) >> 2);
+        const dim3 grid((unsigned)mcb_grid_for(ctx, total4, 256, 4)), block(256);
+        cudaError_t e;
+        if (a.out_bf16)
+            e = mcb_launch_dep(ctx, tc_split_tail_finish_kernel<__nv_bfloat16>, grid, block, 0, (const float *)ws, (__nv_bfloat16 *)p.d, p.bias, p.act,
+                               r.row0, (long long)p.m, r.col0, r.col1, (long long)p.ldd);
+        else
+            e = mcb_launch_dep(ctx, tc_split_tail_finish_kernel<float>, grid, block, 0, (const float *)ws, (float *)p.d, p.bias, p.act, r.row0,
+                               (long long)p.m, r.col0, r.col1, (long long)p.ldd);
+        if (e != cudaSuccess) {
+            mcb_free(ctx, ws);
+            return mcb_cuda_check(ctx, e, "split tail: finishing kernel");
+        }
+        ctx->launches++;
+    }
+    if (ws) mcb_free(ctx, ws); // stream-ordered reuse: later users are enqueued behind the finishing kernels
     return MCB_OK;
 }
 
@@ -900,6 +1027,35 @@ mcb_status mcb_tc_gemm(mcb_ctx *ctx, const TcGemmParams &p) {
     if (const char *force = getenv("MCB_TC_PAIR")) pair = atoi(force); // tuning knob: 0 single CTA, 1 CTA pair
     if (pair < 0) pair = (bn != 192 && p.m > 128) ? 1 : 0;
     if (bn == 192) pair = 0; // half of 192 columns is not a whole number of 64-column boxes
+    // Split tail on 256 x 256 pair tiles against the planned form, by the same cycle estimate as mcb_tc_plan
+    // plus 14000 cycles for the workspace memset, the finishing kernel and the f32 epilogue of the slices (measured at
+    // 8192 x 768: K = 3072 loses 1-5 us with the split tail, K = 32000 gains 90 us)
+    int tail = p.split_tail;
+    if (const char *force = getenv("MCB_TC_SPLIT_TAIL")) tail = atoi(force); // tuning knob: 0 never, 1 whenever it applies
+    const bool tail_ok = !p.accumulate && split == 1 && !p.d_pre && p.m > 128 && p.ldd % 4 == 0 && p.n % 4 == 0 && !getenv("MCB_TC_BN");
+    if (tail < 0 && tail_ok) {
+        const long long kb = (p.k + BK - 1) / BK, workers = ctx->sm_count / 2;
+        const long long tiles = ((p.m + 255) / 256) * ((p.n + 255) / 256), rem = tiles % workers;
+        long long s = rem > 0 ? workers / rem : 1;
+        if (s > 8) s = 8;
+        if (s > kb / 4) s = kb / 4;
+        tail = 0;
+        if (tiles > workers && s >= 2) {
+            const double per_tail = 4.0 * 128.0 + 60.0;
+            const double cost_tail = (double)((tiles / workers) * kb + (kb + s - 1) / s) * per_tail + 12.0 * 256 + 14000.0;
+            const long long w_now = pair ? ctx->sm_count / 2 : ctx->sm_count;
+            const long long t_now = ((p.m + (pair ? 255 : 127)) / (pair ? 256 : 128)) * ((p.n + bn - 1) / bn);
+            const double mma = bn / 2.0 > 125.0 ? bn / 2.0 : 125.0;
+            const double cost_now = (double)((t_now + w_now - 1) / w_now) * (double)kb * (4.0 * mma + 60.0) + 5.0 * bn;
+            if (cost_tail < 0.9 * cost_now) tail = 1;
+        }
+    }
+    if (!tail_ok || tail < 0) tail = 0;
+    q.split_tail = tail;
+    if (tail) {
+        bn = 256;
+        pair = 1;
+    }
     if (pair) {
         if (bn == 256) return launch<256, true>(ctx, q);
         return launch<128, true>(ctx, q);

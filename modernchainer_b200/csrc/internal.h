@@ -35,6 +35,7 @@ struct TcGemmParams {
     int pair = -1; // 1 = two CTAs share a 256-row tile (cta_group::2), 0 = one CTA per 128-row tile, -1 = choose
     int act = MCB_ACT_NONE;
     void *d_pre = nullptr; // optional second output: value before the activation (same dtype/ld as d)
+    int split_tail = -1;   // 1 = cut the tiles of a mostly empty last wave along K (f32 workspace + finishing kernel), 0 = never, -1 = choose
 };
 mcb_status mcb_tc_gemm(mcb_ctx *ctx, const TcGemmParams &p);
 // tile width and reduction split for an [m, n] output reduced over k (see gemm_tc.cu)

@@ -310,6 +310,30 @@ def test_tc_gemm_layouts(ops, oracle, m, n, k, a_mn, b_mn):
     assert np.abs(out16 - ref).max() <= np.abs(ref).max() * 2.0 ** -8
 
 
+@pytest.mark.parametrize("m,n,k,a_mn,b_mn", [(8192, 768, 1024, 0, 0), (8100, 760, 1000, 0, 1), (8192, 768, 640, 1, 1)])
+def test_tc_gemm_split_tail(ops, oracle, m, n, k, a_mn, b_mn):
+    """96 tiles of 256 x 256 on 74 CTA pairs: the 22 tiles of the second wave are cut into K slices whose
+    f32 partial sums meet in a workspace, and a finishing kernel adds the bias and writes the output
+    (MCB_TC_SPLIT_TAIL=1 forces that form, =0 forbids it).  Both forms against the f64 product."""
+    import os
+    a = randn(k, m) if a_mn else randn(m, k)
+    b = randn(k, n) if b_mn else randn(n, k)
+    bias = randn(n)
+    ref = gemm_ref(oracle, a, a_mn, b, b_mn) + bias
+    outs = {}
+    try:
+        for knob in ("1", "0"):
+            os.environ["MCB_TC_SPLIT_TAIL"] = knob
+            out = ops.gemm_bf16(a, a_mn, b, b_mn, m, n, k, out_dt=0, bias=bias)
+            close(out, ref, 2e-5)
+            out16 = ops.gemm_bf16(a, a_mn, b, b_mn, m, n, k, out_dt=5, bias=bias)
+            assert np.abs(out16 - ref).max() <= np.abs(ref).max() * 2.0 ** -8
+            outs[knob] = (out, out16)
+    finally:
+        os.environ.pop("MCB_TC_SPLIT_TAIL", None)
+    close(outs["1"][0], outs["0"][0], 2e-6)  # same products, another grouping of the f32 sums
+
+
 def test_tc_gemm_bias_accumulate_splitk(ops, oracle):
     m, n, k = 768, 768, 4096
     a, b, bias = randn(k, m), randn(k, n), randn(n)  # weight-gradient shape: both operands MN-major

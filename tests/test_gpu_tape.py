@@ -485,6 +485,47 @@ def test_layer_norm_pipeline_kernels_match_register_kernels_on_the_tape(mc, ctx,
         assert np.abs(a - r).max() <= 1e-5 * max(float(np.abs(r).max()), 1e-30), (i, shapes[i])
 
 
+def test_dependent_launch_keeps_stream_order(mc):
+    """Kernels launched as programmatic dependents start while their predecessor drains but touch
+    global memory only after it has completed (and the dQ attention kernel runs beside the dK/dV
+    kernel).  A context created with MCB_NO_DEP_LAUNCH uses plain stream-ordered launches: same loss,
+    same gradients (weight gradients up to the order of their split-K partial sums), five times over
+    to give a race a chance to show."""
+    import os
+    rng = np.random.default_rng(321)
+    vocab, d, heads, ff, layers, s, b = 1000, 256, 4, 1024, 2, 256, 8
+    ids = rng.integers(0, vocab, (b, s)).astype(np.int64)
+    tgt = np.concatenate([ids[:, 1:], rng.integers(0, vocab, (b, 1))], 1).astype(np.int64)
+
+    def run(plain):
+        if plain:
+            os.environ["MCB_NO_DEP_LAUNCH"] = "1"
+        try:
+            c = mc.Context(0)
+        finally:
+            os.environ.pop("MCB_NO_DEP_LAUNCH", None)
+        try:
+            m = mc.Model(c, "decoder", [vocab, d, heads, ff, layers, 0])
+            ps = m.parameters()
+            keep = mc.Arena(c, ps)
+            out = []
+            for _ in range(5 if not plain else 1):
+                mc.zero_grad(ps)
+                with mc.autocast(mc.BF16):
+                    loss = m.loss(mc.Variable.constant(c, ids), mc.Variable.constant(c, tgt))
+                loss.backward()
+                out.append((float(loss.data.reshape(-1)[0]), [p.grad for p in ps]))
+            return out
+        finally:
+            c.close()
+
+    ref_loss, ref_grads = run(True)[0]
+    for loss, grads in run(False):
+        assert loss == ref_loss
+        for i, (a, r) in enumerate(zip(grads, ref_grads)):
+            assert np.abs(a - r).max() <= 1e-5 * max(float(np.abs(r).max()), 1e-30), i
+
+
 @pytest.mark.parametrize("arena", [False, True])
 @pytest.mark.parametrize("which", ["sgd", "momentum", "adamw"])
 def test_optimizer_family_bit_exact_and_clip(mc, ctx, oracle, which, arena):
