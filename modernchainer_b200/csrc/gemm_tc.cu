@@ -920,7 +920,25 @@ template <int BN, bool PAIR> mcb_status launch(mcb_ctx *ctx, const TcGemmParams 
     a.sk_splits = 1;
     const int workers = PAIR ? max_pairs : ctx->sm_count;
     const long long tiles = (long long)a.m_tiles * a.n_tiles;
-    if (p.split_tail && a.tma_out && !p.accumulate && split == 1 && !p.d_pre && tiles > workers && p.ldd % 4 == 0 && p.n % 4 == 0) {
+    if (p.split_tail && a.tma_out && p.accumulate && !p.bias && split == 1 && tiles > workers) {
+        // accumulating f32 output: the slices add straight into it (no workspace, nothing to finish)
+        const long long rem = tiles % workers, full = tiles - rem;
+        int s = rem > 0 ? (int)(workers / rem) : 1;
+        if (s > 8) s = 8;
+        if (s > a.kb_total / 4) s = a.kb_total / 4;
+        if (s >= 2) {
+            const int kb = (a.kb_total + s - 1) / s;
+            s = (a.kb_total + kb - 1) / kb;
+            if (s >= 2) {
+                map_pre = map_d;
+                a.sk_full = (int)full;
+                a.sk_rem = (int)rem;
+                a.sk_splits = s;
+                a.sk_kb = kb;
+                work = full + rem * s;
+            }
+        }
+    } else if (p.split_tail && a.tma_out && !p.accumulate && split == 1 && !p.d_pre && tiles > workers && p.ldd % 4 == 0 && p.n % 4 == 0) {
         const long long rem = tiles % workers, full = tiles - rem;
         int s = rem > 0 ? (int)(workers / rem) : 1;
         if (s > 8) s = 8;
@@ -1032,7 +1050,8 @@ mcb_status mcb_tc_gemm(mcb_ctx *ctx, const TcGemmParams &p) {
     // 8192 x 768: K = 3072 loses 1-5 us with the split tail, K = 32000 gains 90 us)
     int tail = p.split_tail;
     if (const char *force = getenv("MCB_TC_SPLIT_TAIL")) tail = atoi(force); // tuning knob: 0 never, 1 whenever it applies
-    const bool tail_ok = !p.accumulate && split == 1 && !p.d_pre && p.m > 128 && p.ldd % 4 == 0 && p.n % 4 == 0 && !getenv("MCB_TC_BN");
+    const bool tail_ok = (p.accumulate ? (p.bias == nullptr) : (split == 1 && !p.d_pre && p.ldd % 4 == 0 && p.n % 4 == 0)) && p.m > 128 &&
+                         !getenv("MCB_TC_BN");
     if (tail < 0 && tail_ok) {
         const long long kb = (p.k + BK - 1) / BK, workers = ctx->sm_count / 2;
         const long long tiles = ((p.m + 255) / 256) * ((p.n + 255) / 256), rem = tiles % workers;
@@ -1042,11 +1061,15 @@ mcb_status mcb_tc_gemm(mcb_ctx *ctx, const TcGemmParams &p) {
         tail = 0;
         if (tiles > workers && s >= 2) {
             const double per_tail = 4.0 * 128.0 + 60.0;
-            const double cost_tail = (double)((tiles / workers) * kb + (kb + s - 1) / s) * per_tail + 12.0 * 256 + 14000.0;
+            // an accumulating output takes the slices directly; otherwise workspace memset + finishing kernel
+            const double cost_tail = (double)((tiles / workers) * kb + (kb + s - 1) / s) * per_tail + 12.0 * 256 + (p.accumulate ? 1000.0 : 14000.0);
+            // the planned form: `split` slices of every tile
             const long long w_now = pair ? ctx->sm_count / 2 : ctx->sm_count;
             const long long t_now = ((p.m + (pair ? 255 : 127)) / (pair ? 256 : 128)) * ((p.n + bn - 1) / bn);
+            const long long kb_item = (kb + split - 1) / split, items = t_now * ((kb + kb_item - 1) / kb_item);
             const double mma = bn / 2.0 > 125.0 ? bn / 2.0 : 125.0;
-            const double cost_now = (double)((t_now + w_now - 1) / w_now) * (double)kb * (4.0 * mma + 60.0) + 5.0 * bn;
+            const double cost_now = (double)((items + w_now - 1) / w_now) * (double)kb_item * (4.0 * mma + 60.0) + (p.accumulate ? 12.0 : 5.0) * bn +
+                                    (split > 1 ? 300.0 * split + (double)(split - 1) * (double)p.m * (double)p.n * 1.0e-3 : 0.0);
             if (cost_tail < 0.9 * cost_now) tail = 1;
         }
     }
@@ -1055,6 +1078,7 @@ mcb_status mcb_tc_gemm(mcb_ctx *ctx, const TcGemmParams &p) {
     if (tail) {
         bn = 256;
         pair = 1;
+        q.split_k = 1; // the tail is the only part that is cut along K
     }
     if (pair) {
         if (bn == 256) return launch<256, true>(ctx, q);
@@ -1091,7 +1115,22 @@ void mcb_tc_plan(mcb_ctx *ctx, int64_t m, int64_t n, int64_t k, bool allow_split
             // one K=16 MMA at M=128 takes bn/2 cycles but never less than ~125 (the A operand's 4 KB
             // leave shared memory at 32 B/clk), so narrow tiles run the tensor pipe below its rate
             double mma = bn / 2.0 > 125.0 ? bn / 2.0 : 125.0;
-            double cost = (double)waves * (double)kb * (4.0 * mma + 60.0) + epi + (sp > 1 ? 300.0 * sp : 0.0);
+            // every additional slice adds the whole f32 output once more into L2 (measured: 13 us per slice on a
+            // 32000 x 768 output, i.e. about 1e-3 cycles per output element and slice)
+            double cost = (double)waves * (double)kb * (4.0 * mma + 60.0) + epi +
+                          (sp > 1 ? 300.0 * sp + (double)(sp - 1) * (double)m * (double)n * 1.0e-3 : 0.0);
+            if (bn == 256 && sp == 1 && m > 128) {
+                // unsplit 256-wide tiles may run with a split tail (see mcb_tc_gemm): same estimate as there
+                const long long workers = ctx->sm_count / 2, t256 = ((m + 255) / 256) * ((n + 255) / 256), rem = t256 % workers;
+                long long st = rem > 0 ? workers / rem : 1;
+                if (st > 8) st = 8;
+                if (st > kb_total / 4) st = kb_total / 4;
+                if (t256 > workers && st >= 2) {
+                    const double tail = (double)((t256 / workers) * kb_total + (kb_total + st - 1) / st) * (4.0 * 128.0 + 60.0) + 12.0 * 256 +
+                                        (atomic_out ? 1000.0 : 14000.0);
+                    if (tail < 0.9 * cost) cost = tail;
+                }
+            }
             if (cost < best - 1e-9) {
                 best = cost;
                 best_bn = bn;

@@ -329,6 +329,9 @@ def test_tc_gemm_split_tail(ops, oracle, m, n, k, a_mn, b_mn):
             out16 = ops.gemm_bf16(a, a_mn, b, b_mn, m, n, k, out_dt=5, bias=bias)
             assert np.abs(out16 - ref).max() <= np.abs(ref).max() * 2.0 ** -8
             outs[knob] = (out, out16)
+            # accumulating f32 output (weight-gradient form): the slices add straight into it
+            init = randn(m, n)
+            close(ops.gemm_bf16(a, a_mn, b, b_mn, m, n, k, out_dt=0, accumulate=True, split_k=1, init=init), ref - bias + init, 2e-5)
     finally:
         os.environ.pop("MCB_TC_SPLIT_TAIL", None)
     close(outs["1"][0], outs["0"][0], 2e-6)  # same products, another grouping of the f32 sums
