@@ -360,8 +360,16 @@ __device__ __forceinline__ void row_max_sumexp(const T *__restrict__ row, long l
                 s *= row_exp<T>(m - gm);
                 m = gm;
             }
+            // exp(f - m) as one FMA and one ex2 per logit (this loop is bound by instruction issue, not by HBM)
+            const float nml = -m * 1.4426950408889634f;
+            float part = 0.0f;
 #pragma unroll
-            for (int q = 0; q < 8; ++q) s += row_exp<T>(f[q] - m);
+            for (int q = 0; q < 8; ++q) {
+                float e;
+                asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(fmaf(f[q], 1.4426950408889634f, nml)));
+                part += e;
+            }
+            s += part;
         }
     } else if (vec) {
         for (long long j = threadIdx.x; j < (c >> 2); j += blockDim.x) {
@@ -511,6 +519,58 @@ __global__ void sce_fused_kernel(const T *x, T *out, const void *__restrict__ la
             if (j == lab) p -= 1.0f;
             Elem<T>::st(orow, j, p * k);
         }
+    }
+}
+
+// Gradient pass over bf16 logits whose row statistics are known: nothing is reduced, so the rows are cut into
+// segments of 1024 16-byte chunks and every thread streams four of them (all loads issued before the first
+// use).  g = (softmax - onehot) * up / n with the softmax as one FMA and one ex2 per logit:
+// p = 2^(v * log2e - (mx * log2e + log2(sum))).  `out` may alias `x`: a chunk is written by the thread that read it.
+__global__ void __launch_bounds__(256) sce_grad_stream_kernel(const uint4 *x, uint4 *out, const void *__restrict__ labels, int label_dt,
+                                                              long long n, long long c8, const float *__restrict__ stats,
+                                                              const float *__restrict__ upstream, unsigned int *err) {
+    const long long row = blockIdx.y;
+    const long long j0 = (long long)blockIdx.x * 1024 + threadIdx.x;
+    const uint4 *r8 = x + row * c8;
+    uint4 *o8 = out + row * c8;
+    uint4 raw[4];
+    dep_wait();
+    dep_trigger();
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        const long long j = j0 + u * 256;
+        raw[u] = j < c8 ? r8[j] : make_uint4(0u, 0u, 0u, 0u);
+    }
+    const long long lab = load_index(labels, label_dt, row);
+    const bool bad = lab < 0 || lab >= c8 * 8;
+    if (bad && blockIdx.x == 0 && threadIdx.x == 0) atomicOr(err, MCB_DEVERR_LABEL);
+    const float mx = stats[2 * row], sum = stats[2 * row + 1];
+    const float k = (upstream ? upstream[0] : 1.0f) / (float)n;
+    const float c1 = -(mx * 1.4426950408889634f + log2f(sum));
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        const long long j = j0 + u * 256;
+        if (j >= c8) continue;
+        const unsigned wds[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
+        float p[8];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p[2 * q]) : "f"(fmaf(__uint_as_float(wds[q] << 16), 1.4426950408889634f, c1)));
+            asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p[2 * q + 1]) : "f"(fmaf(__uint_as_float(wds[q] & 0xFFFF0000u), 1.4426950408889634f, c1)));
+        }
+        const long long b = j << 3;
+        if (lab >= b && lab < b + 8) {
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+                if (lab - b == q) p[q] -= 1.0f;
+        }
+        unsigned ow[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(p[2 * q] * k, p[2 * q + 1] * k);
+            ow[q] = bad ? 0u : *reinterpret_cast<unsigned *>(&h);
+        }
+        o8[j] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
     }
 }
 
@@ -821,6 +881,16 @@ mcb_status mcb_sce_grad(mcb_ctx *ctx, const void *logits, void *out, int32_t dt,
     int threads = c >= 4096 ? 512 : (c >= 256 ? 128 : 32);
     // algorithmic bytes: one read of the logits, one write of the gradient when requested
     ProfScope prof(ctx, MCB_PROF_LOSS, 0.0, (double)n * c * (dt == MCB_BF16 ? 2.0 : 4.0) * (out ? 2.0 : 1.0) + 8.0 * n);
+    if (dt == MCB_BF16 && out && stats_in && !loss_out && !stats_out && (c % 8) == 0 && n <= 65535 && mcb_aligned16(logits) && mcb_aligned16(out) &&
+        !getenv("MCB_SCE_NO_STREAM")) {
+        // gradient pass with known row statistics: pure streaming
+        const long long c8 = c / 8;
+        dim3 grid((unsigned)((c8 + 1023) / 1024), (unsigned)n);
+        MCB_CUDA(ctx, mcb_launch_dep(ctx, sce_grad_stream_kernel, grid, dim3(256), 0, (const uint4 *)logits, (uint4 *)out, labels, (int)label_dt, (long long)n,
+                                     c8, stats_in, upstream, ctx->d_err));
+        MCB_LAUNCHED(ctx);
+        return MCB_OK;
+    }
     if (dt == MCB_F32)
         sce_fused_kernel<float><<<(unsigned)n, threads, 0, ctx->stream>>>((const float *)logits, (float *)out, labels, label_dt, n, c, (float *)scratch, upstream, ctx->d_err, stats_out, stats_in);
     else if (dt == MCB_BF16)

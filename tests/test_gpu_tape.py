@@ -485,6 +485,38 @@ def test_layer_norm_pipeline_kernels_match_register_kernels_on_the_tape(mc, ctx,
         assert np.abs(a - r).max() <= 1e-5 * max(float(np.abs(r).max()), 1e-30), (i, shapes[i])
 
 
+def test_streaming_loss_gradient_matches_row_kernel(mc, ctx):
+    """The decoder's loss head leaves the row statistics of the loss pass for the gradient pass, which
+    then streams the bf16 logits (one FMA and one ex2 per logit).  Against the row kernel that reduces
+    every row again (MCB_SCE_NO_STREAM): same loss; logit gradients differ by a bf16 rounding here and
+    there, so parameter gradients agree to a few bf16 ulps of their peak."""
+    import os
+    rng = np.random.default_rng(77)
+    vocab, d, heads, ff, layers, s, b = 4096, 256, 4, 512, 1, 128, 8
+    ids = rng.integers(0, vocab, (b, s)).astype(np.int64)
+    tgt = np.concatenate([ids[:, 1:], rng.integers(0, vocab, (b, 1))], 1).astype(np.int64)
+
+    def run(row_kernel):
+        if row_kernel:
+            os.environ["MCB_SCE_NO_STREAM"] = "1"
+        try:
+            m = mc.Model(ctx, "decoder", [vocab, d, heads, ff, layers, 0])
+            ps = m.parameters()
+            keep = mc.Arena(ctx, ps)
+            with mc.autocast(mc.BF16):
+                loss = m.loss(mc.Variable.constant(ctx, ids), mc.Variable.constant(ctx, tgt))
+            loss.backward()
+            return float(loss.data.reshape(-1)[0]), [p.grad for p in ps]
+        finally:
+            os.environ.pop("MCB_SCE_NO_STREAM", None)
+
+    ls, gs = run(False)
+    lr, gr = run(True)
+    assert ls == lr
+    for i, (a, r) in enumerate(zip(gs, gr)):
+        assert np.abs(a - r).max() <= 2.0 ** -7 * max(float(np.abs(r).max()), 1e-30), i
+
+
 def test_dependent_launch_keeps_stream_order(mc):
     """Kernels launched as programmatic dependents start while their predecessor drains but touch
     global memory only after it has completed (and the dQ attention kernel runs beside the dK/dV
