@@ -314,8 +314,24 @@ def run_ours(args, dist):
             g_loss = step.loss()                                   # loss read back every step
         g_e2e = dist.max((time.perf_counter() - t0) * 1e3 / args.steps)
         gb = cfg["batch"] * dist.world
+        # the same replays once more beside the device-side clock sampler (a one-thread kernel reading %globaltimer and
+        # clock64): the SM clock the step really runs at, which nvidia-smi's 200 ms samples cannot resolve
+        sm_trace = None
+        if dist.world == 1:  # with several ranks the replay holds collectives: no rank may run it alone
+            dur_us = int(g_res * 1e3 * args.steps * 1.2) + 300
+            ctx.check(lib.mcb_clock_trace_start(ctx.h, dur_us, max(10, dur_us // 200)))
+            for _ in range(args.steps):
+                ctx.check(lib.mcb_static_step_run(step.h, None, None))
+            ctx.sync()
+            mhz = (C.c_double * 256)()
+            cnt = C.c_int32(0)
+            ctx.check(lib.mcb_clock_trace_read(ctx.h, mhz, 256, C.byref(cnt)))
+            tr = sorted(mhz[i] for i in range(cnt.value))
+            if tr:
+                sm_trace = {"median": tr[len(tr) // 2], "min": tr[0], "max": tr[-1], "samples": len(tr)}
         graph = {"ms_per_step": g_res, "samples_per_s": gb / (g_res / 1e3), "e2e_ms_per_step": g_e2e,
-                 "e2e_samples_per_s": gb / (g_e2e / 1e3), "kernels_per_step": step.kernels_per_step, "loss_last": g_loss}
+                 "e2e_samples_per_s": gb / (g_e2e / 1e3), "kernels_per_step": step.kernels_per_step, "loss_last": g_loss,
+                 "sm_mhz_trace": sm_trace}
         step.close()
 
     ms_step = dist.max(ms_resident / args.steps)

@@ -513,8 +513,11 @@ def test_streaming_loss_gradient_matches_row_kernel(mc, ctx):
     ls, gs = run(False)
     lr, gr = run(True)
     assert ls == lr
+    # the key-bias gradient is zero in exact arithmetic (softmax is shift-invariant): rounding noise only, so
+    # tensors are measured against their own peak or 5e-2 of the largest gradient, whichever is larger
+    floor = 5e-2 * max(float(np.abs(g).max()) for g in gr)
     for i, (a, r) in enumerate(zip(gs, gr)):
-        assert np.abs(a - r).max() <= 2.0 ** -7 * max(float(np.abs(r).max()), 1e-30), i
+        assert np.abs(a - r).max() <= 2.0 ** -7 * max(float(np.abs(r).max()), floor), i
 
 
 def test_dependent_launch_keeps_stream_order(mc):
