@@ -73,6 +73,10 @@ flash_tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         return;
     }
     if (threadIdx.x == 0) {
+        prefetch_map(&map_q);
+        prefetch_map(&map_k);
+        prefetch_map(&map_v);
+        prefetch_map(&map_o);
         mbar_init(q_full, 1);
         for (int s = 0; s < kStages; ++s) {
             mbar_init(&k_full[s], 1);
@@ -296,7 +300,7 @@ flash_tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             if (lane == 0 && q0 + wq * 32 < args.seq) {
                 tma_store_3d(&map_o, stage, h * HD, q0 + wq * 32, n);
                 bulk_commit();
-                bulk_wait_all();
+                bulk_wait_read0(); // the staging tile has been read; the write itself completes before the grid does
             }
             if (row < args.seq)
                 args.lse[((long long)n * args.heads + h) * args.seq + row] = (l > 0.0f) ? m_ref * 0.6931471805599453f + logf(l) : -INFINITY;

@@ -67,6 +67,12 @@ flash_tc_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     const int o0 = own * BT;
 
     if (threadIdx.x == 0) {
+        prefetch_map(&map_q);
+        prefetch_map(&map_k);
+        prefetch_map(&map_v);
+        prefetch_map(&map_do);
+        prefetch_map(&map_out0);
+        prefetch_map(&map_out1);
         mbar_init(x_full, 1);
         for (int s = 0; s < 2; ++s) {
             mbar_init(&y_full[s], 1);
@@ -316,7 +322,7 @@ flash_tc_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             if (lane == 0 && o0 + wq * 32 < args.seq) {
                 tma_store_3d(om, stage, h * HD, o0 + wq * 32, n);
                 bulk_commit();
-                bulk_wait_all();
+                bulk_wait_read0(); // the staging tile has been read; the write itself completes before the grid does
             }
         }
     }

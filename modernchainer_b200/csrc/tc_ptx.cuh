@@ -69,6 +69,10 @@ __device__ __forceinline__ void tma_reduce_add_3d(const CUtensorMap *map, const 
                  : "l"((unsigned long long)map), "r"(smem_u32(smem_src)), "r"(x), "r"(y), "r"(z)
                  : "memory");
 }
+// fetches a tensor map (a kernel parameter) into the descriptor cache ahead of the first copy that uses it
+__device__ __forceinline__ void prefetch_map(const CUtensorMap *map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)map) : "memory");
+}
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
