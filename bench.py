@@ -596,7 +596,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--workload", default="c4", choices=list(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--bucket-mb", type=int, default=32)
+    ap.add_argument("--bucket-mb", type=int, default=64, help="gradient all-reduce bucket (measured at N=8: 64 MB 11.5 ms, 32 MB 11.8 ms per step)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--n-params", type=int, default=0, help="c5 only: number of parameters (default 125M)")
     ap.add_argument("--gemm", default="8192,3072,768", help="gemm workload: m,n,k[,a_mn,b_mn]")
