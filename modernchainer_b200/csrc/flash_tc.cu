@@ -62,8 +62,11 @@ flash_tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // causal: late query tiles walk the most key tiles, so they are scheduled first
-    const int qt = args.causal ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;
-    const int n = blockIdx.y / args.heads, h = blockIdx.y % args.heads;
+    // (CTAs are dispatched in the order of their linear index, read here as (weight rank, sample*head): all the longest
+    // jobs of the grid start first and the shortest fill the tail)
+    const int lin = (int)(blockIdx.y * gridDim.x + blockIdx.x), rank = lin / (int)gridDim.y, nh = lin - rank * (int)gridDim.y;
+    const int qt = args.causal ? (int)gridDim.x - 1 - rank : rank;
+    const int n = nh / args.heads, h = nh % args.heads;
     const int q0 = qt * BM;
     const int kt_all = (args.seq + BN - 1) / BN;
     const int nt = args.causal ? min(qt + 1, kt_all) : kt_all;

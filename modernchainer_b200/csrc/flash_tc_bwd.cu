@@ -56,12 +56,15 @@ flash_tc_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n = blockIdx.y / args.heads, h = blockIdx.y % args.heads;
+    // CTAs are dispatched in the order of their linear index; that index is read as (weight rank, sample*head) so that,
+    // under a causal mask, ALL the longest jobs start first and the shortest fill the tail (longest-first list scheduling)
+    const int lin = (int)(blockIdx.y * gridDim.x + blockIdx.x), rank = lin / (int)gridDim.y, nh = lin - rank * (int)gridDim.y;
+    const int n = nh / args.heads, h = nh % args.heads;
     const int tiles = (args.seq + BT - 1) / BT;
     // MODE 0: this CTA owns key tile `own`; query tiles own..tiles-1 (causal) or all stream through.
     // MODE 1: this CTA owns query tile `own` (late tiles first when causal: they walk the most key tiles);
     //         key tiles 0..own (causal) or all stream through.
-    const int own = (MODE == 1 && args.causal) ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;
+    const int own = (MODE == 1 && args.causal) ? (int)gridDim.x - 1 - rank : rank;
     const int t_first = (MODE == 0 && args.causal) ? own : 0;
     const int nt = (MODE == 0) ? tiles - t_first : (args.causal ? own + 1 : tiles);
     const int o0 = own * BT;
