@@ -46,6 +46,7 @@ struct TcArgs {
     unsigned idesc;
     int m_tiles, n_tiles, kb_total, kb_per_split;
     int stages; // depth of the operand ring actually used (tuning knob; at most the compiled depth)
+    int ring;   // output boxes per epilogue warp: 2, or 4 when one operand stage is given up for them
     // Split tail (sk_splits > 1): work items [0, sk_full) are whole tiles; the sk_rem tiles that would form a
     // mostly empty last wave are each cut into sk_splits slices of sk_kb k-blocks, whose f32 partial sums are
     // added into a workspace (map_pre) that a finishing kernel converts into the output.
@@ -281,16 +282,19 @@ __device__ __forceinline__ unsigned pack_bf16(float a, float b) {
     return *(unsigned *)&p;
 }
 
-// Per-warp staging ring of two 4 KB boxes.  `issued` counts the boxes handed to TMA so far.
+// Per-warp staging ring of two (or four) 4 KB boxes.  `issued` counts the boxes handed to TMA so far.
 struct StageRing {
     unsigned char *base;
     unsigned issued;
 };
 // Wait until the box about to be overwritten has been read, and return it.
-__device__ __forceinline__ unsigned char *ring_acquire(StageRing &rg, int lane) {
-    if (lane == 0) bulk_wait_read1();
+__device__ __forceinline__ unsigned char *ring_acquire(StageRing &rg, int lane, int ring) {
+    if (lane == 0) {
+        if (ring == 4) asm volatile("cp.async.bulk.wait_group.read 3;" ::: "memory");
+        else bulk_wait_read1();
+    }
     __syncwarp();
-    return rg.base + (rg.issued & 1u) * 4096u;
+    return rg.base + (rg.issued & (unsigned)(ring - 1)) * 4096u;
 }
 // 16-byte piece `j` (0..7) of this lane's 128-byte row, at its swizzled position
 __device__ __forceinline__ void ring_put(unsigned char *box, int lane, int j, uint4 piece) {
@@ -351,8 +355,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     extern __shared__ unsigned char smem_raw[];
     // operand tiles need 1024-byte alignment for the 128-byte swizzle pattern
     unsigned char *tiles = (unsigned char *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    unsigned char *out_stage = tiles + kStages * C::kStageBytes; // 1024-aligned: stage sizes are multiples of 8 KB
-    unsigned long long *bars = (unsigned long long *)(out_stage + C::kOutStageBytes);
+    // the output boxes follow the operand stages in use: a launch may run one stage less and give that room to a
+    // deeper ring of output boxes (args.ring = 4); the barriers sit behind the compiled maximum of both
+    unsigned char *out_stage = tiles + (unsigned)args.stages * C::kStageBytes; // 1024-aligned: stage sizes are multiples of 8 KB
+    unsigned long long *bars = (unsigned long long *)(tiles + kStages * C::kStageBytes + C::kOutStageBytes);
     unsigned long long *full_bar = bars, *empty_bar = bars + kStages;
     unsigned long long *acc_full = bars + 2 * kStages, *acc_empty = acc_full + 2;
     unsigned *tmem_slot = (unsigned *)(acc_empty + 2);
@@ -529,7 +535,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         int q = warp & 3; // TMEM lane quarter this warp may access
         unsigned tile_it = 0;
         StageRing rg;
-        rg.base = out_stage + q * 8192;
+        rg.base = out_stage + q * (args.ring * 4096);
         rg.issued = 0;
         for (unsigned w = w_first; w < work_total; w += w_stride, ++tile_it) {
             const WorkItem wi = decode_work(args, w, tiles_mn, one_split);
@@ -581,7 +587,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                             }
                         }
                         if (args.d_pre) {
-                            unsigned char *box = ring_acquire(rg, lane);
+                            unsigned char *box = ring_acquire(rg, lane, args.ring);
 #pragma unroll
                             for (int j = 0; j < 8; ++j)
                                 ring_put(box, lane, j,
@@ -596,7 +602,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
                             for (int j = 0; j < 64; ++j) v[j] = v[j] > 0.0f ? v[j] : 0.0f;
                         }
-                        unsigned char *box = ring_acquire(rg, lane);
+                        unsigned char *box = ring_acquire(rg, lane, args.ring);
 #pragma unroll
                         for (int j = 0; j < 8; ++j)
                             ring_put(box, lane, j,
@@ -630,7 +636,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                                 for (int j = 0; j < 32; ++j) v[j] = v[j] > 0.0f ? v[j] : 0.0f;
                             }
                         }
-                        unsigned char *box = ring_acquire(rg, lane);
+                        unsigned char *box = ring_acquire(rg, lane, args.ring);
 #pragma unroll
                         for (int j = 0; j < 8; ++j)
                             ring_put(box, lane, j,
@@ -868,6 +874,14 @@ template <int BN, bool PAIR> mcb_status launch(mcb_ctx *ctx, const TcGemmParams 
         return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "tensor-core GEMM: dimensions beyond 2^31 are not supported");
     a.bias_vec = p.bias && mcb_aligned16(p.bias);
     a.stages = C::kStages;
+    a.ring = 2;
+    // Short reductions on 256-wide pair tiles are bound by the latency of the output stores (eight 4 KB boxes per
+    // tile and warp, sixteen with a second output), not by the operand ring: one stage less, four boxes in flight.
+    // (8192x3072x768: 34.8 -> 32.6 us; with K = 8192 or more the sixth stage is worth more: 323 -> 347 us.)
+    if (PAIR && BN == 256 && a.kb_per_split <= 16 && C::kStageBytes * 1 >= 4 * 2 * 4096 && !getenv("MCB_TC_STAGES")) {
+        a.stages = C::kStages - 1;
+        a.ring = 4;
+    }
     if (const char *st = getenv("MCB_TC_STAGES")) {
         int v = atoi(st);
         if (v >= 2 && v < C::kStages) a.stages = v;
