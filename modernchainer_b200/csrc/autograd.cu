@@ -260,6 +260,7 @@ mcb_status backward(const Var &root) {
             }
             Tensor &cur = e->second;
             if (in_grads[i].ptr == cur.ptr && in_grads[i].buf == cur.buf) { // the op already added into the pending tensor
+                cur.aux = in_grads[i].aux; // by-products of the kernel that wrote the new values (or none)
                 in_grads[i] = Tensor();
                 continue;
             }
@@ -267,9 +268,11 @@ mcb_status backward(const Var &root) {
             in_grads[i] = Tensor();
             if (cur.buf && cur.buf.use_count() == 1 && cur.dt == add.dt) {
                 st = mcb_add_inplace(ctx, cur.ptr, add.ptr, cur.numel(), cur.dt);
+                cur.aux.reset(); // the values changed
             } else if (add.buf && add.buf.use_count() == 1 && cur.dt == add.dt) {
                 st = mcb_add_inplace(ctx, add.ptr, cur.ptr, cur.numel(), cur.dt);
                 cur = add;
+                cur.aux.reset();
             } else {
                 Tensor sum;
                 int dt = (cur.dt == MCB_F32 || add.dt == MCB_F32) ? MCB_F32 : MCB_BF16;
@@ -600,7 +603,17 @@ static mcb_status linear_backward_impl(mcb_ctx *ctx, const Tensor &g_in, const L
     const bool fuse = getenv("MCB_UNFUSED_BWD") == nullptr; // test knob: separate cast / activation-backward / column-sum kernels
     const bool want_db = b && b->requires_grad;
     bool db_done = false;
-    if (fuse && sv.bf16 && want_db && sv.act == MCB_ACT_NONE && g_in.dt == MCB_F32 && mcb_map_colsum_supported(g_in.ptr, nullptr, g_in.ptr, n)) {
+    if (fuse && sv.bf16 && sv.act == MCB_ACT_NONE && g_in.dt == MCB_F32 && g_in.aux && g_in.aux->bf16.numel() == g_in.numel() &&
+        g_in.aux->colsum.numel() == n && !g_in.shape.empty() && g_in.shape.back() == n) {
+        // the kernel that wrote this f32 gradient (LayerNorm backward on the residual stream) already left it rounded to
+        // bf16 together with the column sums of the rounded values: nothing to read again
+        g = g_in.aux->bf16;
+        g.shape = g_in.shape;
+        if (want_db) {
+            gi[2] = g_in.aux->colsum;
+            db_done = true;
+        }
+    } else if (fuse && sv.bf16 && want_db && sv.act == MCB_ACT_NONE && g_in.dt == MCB_F32 && mcb_map_colsum_supported(g_in.ptr, nullptr, g_in.ptr, n)) {
         bool direct;
         MCB_TRY(grad_dst(b, &gi[2], &direct));
         MCB_TRY(new_tensor(ctx, MCB_BF16, g_in.shape, &g));
@@ -819,29 +832,57 @@ void layer_norm_node(mcb_ctx *ctx, const Var &x, const Var &gamma, const Var &be
     const int64_t dim = x->data.shape.back();
     const int64_t rows = dim ? x->data.numel() / dim : 0;
     Var xv = x, gv = gamma, bv = beta;
-    *out = apply(ctx, "LayerNorm", res, {x, gamma, beta}, [ctx, xf, mean, rstd, xv, gv, bv, eps, rows, dim](const Tensor &g, std::vector<Tensor> &gi) -> mcb_status {
+    // A bf16 result means the model runs under autocast: the gradient of the f32 residual stream that this backward
+    // writes is then read next by the backward of a bf16 Linear, which wants it rounded to bf16 and its column sums (the
+    // bias gradient).  The pipeline kernel leaves both as by-products (GradAux) and saves that Linear a pass over dx.
+    const bool lowp = res.dt == MCB_BF16;
+    *out = apply(ctx, "LayerNorm", res, {x, gamma, beta}, [ctx, xf, mean, rstd, xv, gv, bv, eps, rows, dim, lowp](const Tensor &g, std::vector<Tensor> &gi) -> mcb_status {
         Tensor dx, dg, db;
         bool d1, d2;
         MCB_TRY(grad_dst(gv, &dg, &d1));
         MCB_TRY(grad_dst(bv, &db, &d2));
+        const bool fuse = getenv("MCB_UNFUSED_BWD") == nullptr; // test knob: separate fan-in add, cast and column sums
+        const bool want_aux = fuse && lowp && xv->data.dt == MCB_F32 && (g.dt == MCB_F32 || g.dt == MCB_BF16) && !getenv("MCB_LN_NO_AUX");
+        // the pipeline kernel with the by-products; MCB_UNSUPPORTED (nothing launched) where it does not apply
+        auto with_aux = [&](const float *addend, float *dst, std::shared_ptr<GradAux> *aux_out) -> mcb_status {
+            if (!want_aux) return MCB_UNSUPPORTED;
+            auto aux = std::make_shared<GradAux>();
+            MCB_TRY(new_tensor(ctx, MCB_BF16, xf.shape, &aux->bf16));
+            MCB_TRY(new_tensor(ctx, MCB_F32, {dim}, &aux->colsum));
+            ProfScope prof(ctx, MCB_PROF_NORM, 0.0, (double)rows * dim * (10.0 + (g.dt == MCB_BF16 ? 2.0 : 4.0) + (addend ? 4.0 : 0.0)) + 8.0 * rows + 12.0 * dim);
+            mcb_status st = mcb_ln_bulk_backward(ctx, (const float *)xf.ptr, (const float *)gv->data.ptr, g.ptr, g.dt, eps, (const float *)mean.ptr,
+                                                 (const float *)rstd.ptr, addend, dst, (float *)dg.ptr, (float *)db.ptr, rows, dim, aux->bf16.ptr,
+                                                 (float *)aux->colsum.ptr);
+            if (st == MCB_OK) *aux_out = aux;
+            return st;
+        };
         // A gradient already waiting for x (the residual branch of a pre-norm block) takes dx in place
-        const Tensor *pend = getenv("MCB_UNFUSED_BWD") ? nullptr : pending_grad(0); // test knob: separate fan-in add
+        const Tensor *pend = fuse ? pending_grad(0) : nullptr;
         if (pend && pend->dt == MCB_F32 && xv->data.dt == MCB_F32 && pend->numel() == xf.numel()) {
-            mcb_status st = mcb_layer_norm_backward_ex(ctx, (const float *)xf.ptr, (const float *)gv->data.ptr, g.ptr, g.dt, eps,
-                                                       (const float *)mean.ptr, (const float *)rstd.ptr, (const float *)pend->ptr,
-                                                       (float *)pend->ptr, (float *)dg.ptr, (float *)db.ptr, rows, dim);
+            std::shared_ptr<GradAux> aux;
+            mcb_status st = with_aux((const float *)pend->ptr, (float *)pend->ptr, &aux);
+            if (st == MCB_UNSUPPORTED)
+                st = mcb_layer_norm_backward_ex(ctx, (const float *)xf.ptr, (const float *)gv->data.ptr, g.ptr, g.dt, eps, (const float *)mean.ptr,
+                                                (const float *)rstd.ptr, (const float *)pend->ptr, (float *)pend->ptr, (float *)dg.ptr,
+                                                (float *)db.ptr, rows, dim);
             if (st != MCB_UNSUPPORTED) {
                 MCB_TRY(st);
                 gi[0] = *pend; // same storage: the walker sees that the sum is already in place
+                gi[0].aux = aux; // by-products of the new values, or none
                 gi[1] = dg;
                 gi[2] = db;
                 return MCB_OK;
             }
         }
         MCB_TRY(new_tensor(ctx, MCB_F32, xf.shape, &dx));
-        MCB_TRY(mcb_layer_norm_backward(ctx, (const float *)xf.ptr, (const float *)gv->data.ptr, g.ptr, g.dt, eps, (const float *)mean.ptr,
-                                        (const float *)rstd.ptr, (float *)dx.ptr, (float *)dg.ptr, (float *)db.ptr, rows, dim));
+        std::shared_ptr<GradAux> aux;
+        mcb_status st = with_aux(nullptr, (float *)dx.ptr, &aux);
+        if (st == MCB_UNSUPPORTED)
+            st = mcb_layer_norm_backward(ctx, (const float *)xf.ptr, (const float *)gv->data.ptr, g.ptr, g.dt, eps, (const float *)mean.ptr,
+                                         (const float *)rstd.ptr, (float *)dx.ptr, (float *)dg.ptr, (float *)db.ptr, rows, dim);
+        MCB_TRY(st);
         MCB_TRY(like_input(ctx, dx, xv, &gi[0]));
+        if (gi[0].ptr == dx.ptr) gi[0].aux = aux;
         gi[1] = dg;
         gi[2] = db;
         return MCB_OK;

@@ -21,13 +21,23 @@ struct Buf {
     Buf &operator=(const Buf &) = delete;
 };
 
+struct GradAux;
+
 struct Tensor {
     std::shared_ptr<Buf> buf;
     void *ptr = nullptr;
     int dt = MCB_F32;
     std::vector<int64_t> shape;
     bool defined = false;
+    // Optional by-products of the kernel that wrote an f32 gradient: the same values rounded to bf16 and their
+    // column sums.  Valid only while the values are unchanged: whoever modifies the tensor in place drops it.
+    std::shared_ptr<GradAux> aux;
     int64_t numel() const;
+};
+
+struct GradAux {
+    Tensor bf16;   // same shape, bf16
+    Tensor colsum; // [last dim], f32: column sums of the bf16 values
 };
 
 struct Node;

@@ -68,8 +68,10 @@ mcb_status mcb_ln_bulk_forward(mcb_ctx *ctx, const float *x, const float *gamma,
 // sum = x + res (res f32 or bf16) and out = LayerNorm(sum) in one pass
 mcb_status mcb_ln_bulk_add_forward(mcb_ctx *ctx, const float *x, const void *res, int32_t res_dt, const float *gamma, const float *beta, double eps,
                                    float *sum, void *out, int32_t out_dt, float *mean, float *rstd, int64_t rows, int64_t dim);
+// dx_bf16 / dx_colsum (both or neither): also leaves dx rounded to bf16 and the column sums of those rounded values
 mcb_status mcb_ln_bulk_backward(mcb_ctx *ctx, const float *x, const float *gamma, const void *g, int32_t g_dt, double eps, const float *mean,
-                                const float *rstd, const float *addend, float *dx, float *dgamma, float *dbeta, int64_t rows, int64_t dim);
+                                const float *rstd, const float *addend, float *dx, float *dgamma, float *dbeta, int64_t rows, int64_t dim,
+                                void *dx_bf16 = nullptr, float *dx_colsum = nullptr);
 // reduce.cu: LayerNorm backward that writes dx as addend + dx when `addend` is given (may alias dx);
 // MCB_UNSUPPORTED (nothing launched) where only the plain form exists
 mcb_status mcb_layer_norm_backward_ex(mcb_ctx *ctx, const float *x, const float *gamma, const void *g, int32_t g_dt, double eps,

@@ -1,9 +1,9 @@
 // LayerNorm forward / backward as a bulk-copy pipeline (rows of up to 1024 elements, dim % 8 == 0).
 //
-// One persistent CTA per SM: a producer thread streams blocks of eight consecutive rows (x, and for
+// One persistent CTA per SM: a producer thread streams blocks of seven consecutive rows (x, and for
 // backward g and the pending gradient) from HBM into a ring of shared-memory stages with
 // cp.async.bulk (rows are contiguous, so each operand of a block is ONE copy and no tensor map is
-// needed); eight compute warps take one row each from the stage, reduce it with warp shuffles and
+// needed); seven compute warps take one row each from the stage, reduce it with warp shuffles and
 // write the result straight from registers.  The ring keeps 100-180 KB of loads in flight per SM
 // without holding them in registers, which is what bounded the register-resident kernels
 // (layer_norm_fast.cu: 255 registers, one block per SM, 3.4 TB/s).  Every mbarrier wait is bounded.
@@ -19,8 +19,13 @@ namespace {
 
 using namespace tcptx;
 
-constexpr int kRows = 8;                     // rows per stage = compute warps
-constexpr int kThreads = (kRows + 1) * 32;   // + the producer warp
+// rows per stage = compute warps.  Seven, so that the block is eight warps with the producer: registers are granted to
+// warps in groups of four, and a ninth warp would cap every thread at 168 registers, which the backward kernel with
+// by-products exceeds
+constexpr int kRowsBwd = 7;
+constexpr int kRowsFwd = 8;                  // the forward kernel needs 112 registers: nine warps are fine
+constexpr int kThreadsBwd = (kRowsBwd + 1) * 32; // + the producer warp
+constexpr int kThreadsFwd = (kRowsFwd + 1) * 32;
 constexpr int kMaxStages = 6;
 constexpr unsigned kSmemBudget = 200u * 1024u;
 
@@ -31,7 +36,9 @@ struct LnBulkArgs {
     const float *addend; // backward: gradient already pending for x (may alias dx), or null
     void *out;           // forward: y (f32 or bf16); backward: dx (f32)
     float *mean_out, *rstd_out;
-    float *partial;      // backward: [grid][2][dim]
+    float *partial;      // backward: [grid][2][dim], or [grid][3][dim] with dx_bf16
+    __nv_bfloat16 *dx_bf16; // backward, optional: dx rounded to bf16 (what the backward GEMMs of the Linear feeding this
+                            // residual stream read); the third partial row then holds the column sums of those rounded values
     float *sum_out;      // forward with a residual operand (g): x + g, written beside the normalised rows
     long long rows;
     int dim;
@@ -63,7 +70,7 @@ __device__ __forceinline__ void store4(__nv_bfloat16 *p, int idx, float4 v) {
 }
 
 // The producer: one thread walks this CTA's row blocks and fills the ring.  NOPS operands per stage.
-template <int NOPS>
+template <int NOPS, int kRows>
 __device__ __forceinline__ void produce(const LnBulkArgs &a, unsigned char *smem, unsigned long long *full, unsigned long long *empty,
                                         volatile int *abort_flag, const void *const (&src)[3], const unsigned (&elem)[3],
                                         const unsigned (&off)[3]) {
@@ -88,7 +95,7 @@ __device__ __forceinline__ void produce(const LnBulkArgs &a, unsigned char *smem
     }
 }
 
-__device__ __forceinline__ void ring_init(const LnBulkArgs &a, unsigned long long *full, unsigned long long *empty, volatile int *abort_flag) {
+template <int kRows> __device__ __forceinline__ void ring_init(const LnBulkArgs &a, unsigned long long *full, unsigned long long *empty, volatile int *abort_flag) {
     if (threadIdx.x == 0) {
         for (int s = 0; s < a.stages; ++s) {
             mbar_init(&full[s], 1);
@@ -105,19 +112,20 @@ __device__ __forceinline__ void ring_init(const LnBulkArgs &a, unsigned long lon
 // ResT = void: y = LN(x).  Otherwise the residual add of a pre-norm block rides along: s = x + g (g of type
 // ResT) is written to sum_out and y = LN(s), in the arithmetic of the separate add and LayerNorm kernels.
 template <typename OutT, int NV, typename ResT>
-__global__ void __launch_bounds__(kThreads, 1) ln_fwd_bulk_kernel(const LnBulkArgs a) {
+__global__ void __launch_bounds__(kThreadsFwd, 1) ln_fwd_bulk_kernel(const LnBulkArgs a) {
+    constexpr int kRows = kRowsFwd;
     constexpr bool kRes = !std::is_same<ResT, void>::value;
     typedef typename std::conditional<kRes, ResT, float>::type RT;
     extern __shared__ __align__(128) unsigned char smem[];
     unsigned long long *full = (unsigned long long *)(smem + (size_t)a.stages * a.stage_bytes), *empty = full + kMaxStages;
     volatile int *abort_flag = (volatile int *)(empty + kMaxStages);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    ring_init(a, full, empty, abort_flag);
+    ring_init<kRows>(a, full, empty, abort_flag);
     if (warp == kRows) {
         if (lane == 0) {
             const void *const src[3] = {a.x, kRes ? a.g : nullptr, nullptr};
             const unsigned elem[3] = {4u, (unsigned)sizeof(RT), 0u}, off[3] = {0u, a.off_g, 0u};
-            produce<2>(a, smem, full, empty, abort_flag, src, elem, off);
+            produce<2, kRows>(a, smem, full, empty, abort_flag, src, elem, off);
         }
         return;
     }
@@ -181,26 +189,30 @@ __global__ void __launch_bounds__(kThreads, 1) ln_fwd_bulk_kernel(const LnBulkAr
     }
 }
 
-template <typename GT, int NV>
-__global__ void __launch_bounds__(kThreads, 1) ln_bwd_bulk_kernel(const LnBulkArgs a) {
+// (256 threads: the variant with by-products needs about 200 registers)
+template <typename GT, int NV, bool AUX>
+__global__ void __maxnreg__(216) ln_bwd_bulk_kernel(const LnBulkArgs a) {
+    constexpr int kRows = kRowsBwd;
+    constexpr int kVec = AUX ? 3 : 2; // dgamma, dbeta (, column sums of the bf16 copy of dx)
     extern __shared__ __align__(128) unsigned char smem[];
-    __shared__ float acc[2 * 32 * NV * 4];
+    __shared__ float acc[kVec * 32 * NV * 4];
     unsigned long long *full = (unsigned long long *)(smem + (size_t)a.stages * a.stage_bytes), *empty = full + kMaxStages;
     volatile int *abort_flag = (volatile int *)(empty + kMaxStages);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    ring_init(a, full, empty, abort_flag);
+    ring_init<kRows>(a, full, empty, abort_flag);
     const int dim4 = a.dim >> 2;
-    float4 dga[NV], dbe[NV];
+    float4 dga[NV], dbe[NV], dcs[AUX ? NV : 1];
 #pragma unroll
     for (int j = 0; j < NV; ++j) {
         dga[j] = make_float4(0.f, 0.f, 0.f, 0.f);
         dbe[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (AUX) dcs[AUX ? j : 0] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
     if (warp == kRows) {
         if (lane == 0) {
             const void *const src[3] = {a.x, a.g, a.addend};
             const unsigned elem[3] = {4u, (unsigned)sizeof(GT), 4u}, off[3] = {0u, a.off_g, a.off_ad};
-            produce<3>(a, smem, full, empty, abort_flag, src, elem, off);
+            produce<3, kRows>(a, smem, full, empty, abort_flag, src, elem, off);
         }
     } else {
         const float fdim = (float)a.dim, inv_dim = 1.0f / fdim;
@@ -294,6 +306,16 @@ __global__ void __launch_bounds__(kThreads, 1) ln_bwd_bulk_kernel(const LnBulkAr
                             o.w += ad.w;
                         }
                         reinterpret_cast<float4 *>(d)[lane + 32 * j] = o;
+                        if (AUX) { // the bf16 copy the next Linear's backward GEMMs read, and the column sums of exactly those values
+                            const uint2 h = make_uint2(pack_bf16(o.x, o.y), pack_bf16(o.z, o.w));
+                            reinterpret_cast<uint2 *>(a.dx_bf16 + r * a.dim)[lane + 32 * j] = h;
+                            const float4 back = unpack4(h);
+                            float4 &cs = dcs[AUX ? j : 0];
+                            cs.x += back.x;
+                            cs.y += back.y;
+                            cs.z += back.z;
+                            cs.w += back.w;
+                        }
                     }
             }
             __syncwarp();
@@ -310,41 +332,50 @@ __global__ void __launch_bounds__(kThreads, 1) ln_bwd_bulk_kernel(const LnBulkAr
                 if (turn == 0) {
                     acc_g[idx] = dga[j];
                     acc_b[idx] = dbe[j];
+                    if (AUX) acc_b[32 * NV + idx] = dcs[AUX ? j : 0];
                 } else {
                     const float4 p = acc_g[idx], q = acc_b[idx];
                     acc_g[idx] = make_float4(p.x + dga[j].x, p.y + dga[j].y, p.z + dga[j].z, p.w + dga[j].w);
                     acc_b[idx] = make_float4(q.x + dbe[j].x, q.y + dbe[j].y, q.z + dbe[j].z, q.w + dbe[j].w);
+                    if (AUX) {
+                        const float4 t = acc_b[32 * NV + idx], u = dcs[AUX ? j : 0];
+                        acc_b[32 * NV + idx] = make_float4(t.x + u.x, t.y + u.y, t.z + u.z, t.w + u.w);
+                    }
                 }
             }
         }
         __syncthreads();
     }
-    float *dst = a.partial + (size_t)blockIdx.x * 2 * a.dim;
+    float *dst = a.partial + (size_t)blockIdx.x * kVec * a.dim;
     for (int c = threadIdx.x; c < a.dim; c += blockDim.x) {
         dst[c] = acc[c];
         dst[a.dim + c] = acc[32 * NV * 4 + c];
+        if (AUX) dst[2 * a.dim + c] = acc[2 * 32 * NV * 4 + c];
     }
 }
 
-__global__ void ln_bulk_params_final(const float *__restrict__ partial, int blocks, int dim, float *__restrict__ dgamma, float *__restrict__ dbeta) {
-    // block (32, 32): 32 of the 2*dim columns, 32 interleaved groups of per-CTA partials, fixed order
+__global__ void ln_bulk_params_final(const float *__restrict__ partial, int blocks, int dim, float *__restrict__ dgamma, float *__restrict__ dbeta,
+                                     float *__restrict__ colsum) {
+    // block (32, 32): 32 of the nvec*dim columns (nvec = 3 with `colsum`), 32 interleaved groups of per-CTA partials, fixed order
+    const int nvec = colsum ? 3 : 2;
     __shared__ float red[32][33];
     const int j = blockIdx.x * 32 + threadIdx.x;
     dep_wait();
     dep_trigger();
     float t = 0.0f;
-    if (j < 2 * dim) {
+    if (j < nvec * dim) {
 #pragma unroll 4
-        for (int b = threadIdx.y; b < blocks; b += 32) t += partial[(size_t)b * 2 * dim + j];
+        for (int b = threadIdx.y; b < blocks; b += 32) t += partial[(size_t)b * nvec * dim + j];
     }
     red[threadIdx.y][threadIdx.x] = t;
     __syncthreads();
-    if (threadIdx.y == 0 && j < 2 * dim) {
+    if (threadIdx.y == 0 && j < nvec * dim) {
         float u = 0.0f;
 #pragma unroll
         for (int y = 0; y < 32; ++y) u += red[y][threadIdx.x];
         if (j < dim) dgamma[j] = u;
-        else dbeta[j - dim] = u;
+        else if (j < 2 * dim) dbeta[j - dim] = u;
+        else colsum[j - 2 * dim] = u;
     }
 }
 
@@ -366,6 +397,7 @@ int plan_stages(unsigned stage_bytes) {
 }
 
 template <typename K> mcb_status launch(mcb_ctx *ctx, K kernel, const LnBulkArgs &a, int grid, const char *what) {
+    const int kThreads = what[0] == 'f' ? kThreadsFwd : kThreadsBwd;
     const size_t smem = (size_t)a.stages * a.stage_bytes + 2 * kMaxStages * sizeof(unsigned long long) + 16;
     MCB_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     MCB_CUDA(ctx, mcb_launch_dep(ctx, kernel, dim3(grid), dim3(kThreads), smem, a));
@@ -384,15 +416,18 @@ template <typename OutT, typename ResT> mcb_status launch_fwd(mcb_ctx *ctx, int 
     default: return launch(ctx, ln_fwd_bulk_kernel<OutT, 8, ResT>, a, grid, "fwd");
     }
 }
-template <typename GT> mcb_status launch_bwd(mcb_ctx *ctx, int nv, const LnBulkArgs &a, int grid) {
+template <typename GT, bool AUX> mcb_status launch_bwd_aux(mcb_ctx *ctx, int nv, const LnBulkArgs &a, int grid) {
     switch (nv) {
-    case 1: return launch(ctx, ln_bwd_bulk_kernel<GT, 1>, a, grid, "bwd");
-    case 2: return launch(ctx, ln_bwd_bulk_kernel<GT, 2>, a, grid, "bwd");
-    case 3: return launch(ctx, ln_bwd_bulk_kernel<GT, 3>, a, grid, "bwd");
-    case 4: return launch(ctx, ln_bwd_bulk_kernel<GT, 4>, a, grid, "bwd");
-    case 6: return launch(ctx, ln_bwd_bulk_kernel<GT, 6>, a, grid, "bwd");
-    default: return launch(ctx, ln_bwd_bulk_kernel<GT, 8>, a, grid, "bwd");
+    case 1: return launch(ctx, ln_bwd_bulk_kernel<GT, 1, AUX>, a, grid, "bwd");
+    case 2: return launch(ctx, ln_bwd_bulk_kernel<GT, 2, AUX>, a, grid, "bwd");
+    case 3: return launch(ctx, ln_bwd_bulk_kernel<GT, 3, AUX>, a, grid, "bwd");
+    case 4: return launch(ctx, ln_bwd_bulk_kernel<GT, 4, AUX>, a, grid, "bwd");
+    case 6: return launch(ctx, ln_bwd_bulk_kernel<GT, 6, AUX>, a, grid, "bwd");
+    default: return launch(ctx, ln_bwd_bulk_kernel<GT, 8, AUX>, a, grid, "bwd");
     }
+}
+template <typename GT> mcb_status launch_bwd(mcb_ctx *ctx, int nv, const LnBulkArgs &a, int grid) {
+    return a.dx_bf16 ? launch_bwd_aux<GT, true>(ctx, nv, a, grid) : launch_bwd_aux<GT, false>(ctx, nv, a, grid);
 }
 
 bool eligible(int64_t rows, int64_t dim, const void *p0, const void *p1, const void *p2, const void *p3) {
@@ -410,10 +445,10 @@ mcb_status mcb_ln_bulk_forward(mcb_ctx *ctx, const float *x, const float *gamma,
     LnBulkArgs a = {};
     a.x = x; a.gamma = gamma; a.beta = beta; a.out = out; a.mean_out = mean; a.rstd_out = rstd;
     a.rows = rows; a.dim = (int)dim; a.eps = (float)eps; a.err = ctx->d_err;
-    a.stage_bytes = round128((size_t)kRows * dim * 4);
+    a.stage_bytes = round128((size_t)kRowsFwd * dim * 4);
     a.stages = plan_stages(a.stage_bytes);
     if (!a.stages) return MCB_UNSUPPORTED;
-    const int64_t nblk = (rows + kRows - 1) / kRows;
+    const int64_t nblk = (rows + kRowsFwd - 1) / kRowsFwd;
     const int grid = (int)(nblk < ctx->sm_count ? nblk : ctx->sm_count);
     const int nv = pick_nv(dim);
     if (out_dt == MCB_F32) return launch_fwd<float, void>(ctx, nv, a, grid);
@@ -429,11 +464,11 @@ mcb_status mcb_ln_bulk_add_forward(mcb_ctx *ctx, const float *x, const void *res
     LnBulkArgs a = {};
     a.x = x; a.g = res; a.gamma = gamma; a.beta = beta; a.out = out; a.sum_out = sum; a.mean_out = mean; a.rstd_out = rstd;
     a.rows = rows; a.dim = (int)dim; a.eps = (float)eps; a.err = ctx->d_err;
-    a.off_g = round128((size_t)kRows * dim * 4);
-    a.stage_bytes = a.off_g + round128((size_t)kRows * dim * (res_dt == MCB_BF16 ? 2 : 4));
+    a.off_g = round128((size_t)kRowsFwd * dim * 4);
+    a.stage_bytes = a.off_g + round128((size_t)kRowsFwd * dim * (res_dt == MCB_BF16 ? 2 : 4));
     a.stages = plan_stages(a.stage_bytes);
     if (!a.stages) return MCB_UNSUPPORTED;
-    const int64_t nblk = (rows + kRows - 1) / kRows;
+    const int64_t nblk = (rows + kRowsFwd - 1) / kRowsFwd;
     const int grid = (int)(nblk < ctx->sm_count ? nblk : ctx->sm_count);
     const int nv = pick_nv(dim);
     if (out_dt == MCB_F32) {
@@ -445,26 +480,30 @@ mcb_status mcb_ln_bulk_add_forward(mcb_ctx *ctx, const float *x, const void *res
 }
 
 mcb_status mcb_ln_bulk_backward(mcb_ctx *ctx, const float *x, const float *gamma, const void *g, int32_t g_dt, double eps, const float *mean,
-                                const float *rstd, const float *addend, float *dx, float *dgamma, float *dbeta, int64_t rows, int64_t dim) {
+                                const float *rstd, const float *addend, float *dx, float *dgamma, float *dbeta, int64_t rows, int64_t dim,
+                                void *dx_bf16, float *dx_colsum) {
     if (!eligible(rows, dim, x, gamma, g, dx) || (addend && !mcb_aligned16(addend)) || getenv("MCB_LN_NO_BULK")) return MCB_UNSUPPORTED;
+    if ((dx_bf16 != nullptr) != (dx_colsum != nullptr) || (dx_bf16 && !mcb_aligned16(dx_bf16))) return MCB_UNSUPPORTED;
     LnBulkArgs a = {};
     a.x = x; a.gamma = gamma; a.g = g; a.mean_in = mean; a.rstd_in = rstd; a.addend = addend; a.out = dx;
+    a.dx_bf16 = (__nv_bfloat16 *)dx_bf16;
     a.rows = rows; a.dim = (int)dim; a.eps = (float)eps; a.err = ctx->d_err;
     const size_t gsz = g_dt == MCB_BF16 ? 2 : 4;
-    a.off_g = round128((size_t)kRows * dim * 4);
-    a.off_ad = a.off_g + round128((size_t)kRows * dim * gsz);
-    a.stage_bytes = a.off_ad + (addend ? round128((size_t)kRows * dim * 4) : 0u);
+    a.off_g = round128((size_t)kRowsBwd * dim * 4);
+    a.off_ad = a.off_g + round128((size_t)kRowsBwd * dim * gsz);
+    a.stage_bytes = a.off_ad + (addend ? round128((size_t)kRowsBwd * dim * 4) : 0u);
     a.stages = plan_stages(a.stage_bytes);
     if (!a.stages) return MCB_UNSUPPORTED;
-    const int64_t nblk = (rows + kRows - 1) / kRows;
+    const int64_t nblk = (rows + kRowsBwd - 1) / kRowsBwd;
     const int grid = (int)(nblk < ctx->sm_count ? nblk : ctx->sm_count);
     void *scratch;
-    MCB_TRY(mcb_scratch(ctx, sizeof(float) * (size_t)grid * 2 * dim, &scratch));
+    MCB_TRY(mcb_scratch(ctx, sizeof(float) * (size_t)grid * (dx_bf16 ? 3 : 2) * dim, &scratch));
     a.partial = (float *)scratch;
     const int nv = pick_nv(dim);
     if (g_dt == MCB_F32) MCB_TRY(launch_bwd<float>(ctx, nv, a, grid));
     else MCB_TRY(launch_bwd<__nv_bfloat16>(ctx, nv, a, grid));
-    MCB_CUDA(ctx, mcb_launch_dep(ctx, ln_bulk_params_final, dim3((unsigned)((2 * dim + 31) / 32)), dim3(32, 32), 0, (const float *)scratch, grid, (int)dim, dgamma, dbeta));
+    MCB_CUDA(ctx, mcb_launch_dep(ctx, ln_bulk_params_final, dim3((unsigned)(((dx_bf16 ? 3 : 2) * dim + 31) / 32)), dim3(32, 32), 0, (const float *)scratch, grid,
+                                 (int)dim, dgamma, dbeta, dx_colsum));
     MCB_LAUNCHED(ctx);
     return MCB_OK;
 }
