@@ -1136,15 +1136,20 @@ mcb_status f_qkv_attention(const Var &x, const Var &wq, const Var &bq, const Var
     Var xv = x, wqv = wq, wkv = wk, wvv = wv, bqv = bq, bkv = bk, bvv = bv;
     *out = apply(ctx, "QkvAttention", o, {x, wq, bq, wk, bk, wv, bv},
                  [=](const Tensor &g_in, std::vector<Tensor> &gi) -> mcb_status {
-        Tensor g, dqkv;
+        Tensor g, dqkv, bias_part;
+        int bias_done = 0;
         MCB_TRY(to_dtype(ctx, g_in, MCB_BF16, &g));
         MCB_TRY(new_tensor(ctx, MCB_BF16, {m, 3 * d}, &dqkv));
         __nv_bfloat16 *dp = (__nv_bfloat16 *)dqkv.ptr;
         const __nv_bfloat16 *qp = (const __nv_bfloat16 *)qkv.ptr; // the closure owns qkv, o and lse until backward has run
         {
             ProfScope prof(ctx, MCB_PROF_ATTENTION, 10.0 * (double)n * heads * s * s * 64 * (causal ? 0.5 : 1.0), 16.0 * (double)m * d);
+            // the attention backward kernels can leave per-warp column sums of dq | dk | dv (the rounded values they write): the bias
+            // gradients then need only the final reduction over those rows instead of another pass over dqkv
+            const int64_t brows = getenv("MCB_UNFUSED_BWD") ? 0 : mcb_flash_bias_rows(n, s);
+            if (brows > 0) MCB_TRY(new_tensor(ctx, MCB_F32, {brows, 3 * d}, &bias_part));
             MCB_TRY(mcb_flash_backward(ctx, qp, qp + d, qp + 2 * d, o.ptr, g.ptr, (const float *)lse.ptr, dp, dp + d, dp + 2 * d, n, s, d, heads,
-                                       causal, 3 * d, d, 3 * d));
+                                       causal, 3 * d, d, 3 * d, brows > 0 ? (float *)bias_part.ptr : nullptr, 3 * d, &bias_done));
         }
         if (xv->requires_grad) {
             int xdt = is_float(xv->data.dt) ? xv->data.dt : MCB_F32;
@@ -1197,7 +1202,8 @@ mcb_status f_qkv_attention(const Var &x, const Var &wq, const Var &bq, const Var
             }
             MCB_TRY(mcb_tc_gemm(ctx, p));
         }
-        MCB_TRY(mcb_col_sum(ctx, dqkv.ptr, MCB_BF16, m, 3 * d, (float *)db.ptr));
+        if (bias_done) MCB_TRY(mcb_partial_sum_final(ctx, (const float *)bias_part.ptr, (int)bias_part.shape[0], 3 * d, (float *)db.ptr));
+        else MCB_TRY(mcb_col_sum(ctx, dqkv.ptr, MCB_BF16, m, 3 * d, (float *)db.ptr));
         gi[1] = tw[0]; gi[3] = tw[1]; gi[5] = tw[2];
         gi[2] = tb[0]; gi[4] = tb[1]; gi[6] = tb[2];
         return MCB_OK;

@@ -441,8 +441,9 @@ mcb_status mcb_flash_forward(mcb_ctx *ctx, const void *q, const void *k, const v
 
 mcb_status mcb_flash_backward(mcb_ctx *ctx, const void *q, const void *k, const void *v, const void *out, const void *gout, const float *lse,
                               void *dq, void *dk, void *dv, int64_t n, int64_t seq, int64_t dim, int64_t heads, int32_t causal,
-                              int64_t ldi, int64_t ldo, int64_t ldg) {
+                              int64_t ldi, int64_t ldo, int64_t ldg, float *bias_partial, int64_t bias_ld, int *bias_done) {
     (void)dim;
+    if (bias_done) *bias_done = 0;
     if (ldi % 8 || ldo % 8 || ldg % 8) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "fused attention needs row pitches that are multiples of 8");
     if (n * heads > 65535) return mcb_fail(ctx, MCB_UNSUPPORTED, "fused attention: n * heads > 65535");
     if ((((uintptr_t)out) | ((uintptr_t)gout)) & 15) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "fused attention needs 16-byte aligned tensors");
@@ -457,8 +458,10 @@ mcb_status mcb_flash_backward(mcb_ctx *ctx, const void *q, const void *k, const 
     ctx->launches++;
     // the tcgen05 / TMEM kernels first; MCB_FLASH_LEGACY (test knob) keeps the mma.sync pair
     if (!getenv("MCB_FLASH_LEGACY") && !getenv("MCB_FLASH_LEGACY_BWD")) {
-        mcb_status tc = mcb_flash_tc_backward(ctx, q, k, v, gout, lse, (const float *)delta, dq, dk, dv, n, seq, dim, heads, causal, ldi, ldo, ldg);
+        mcb_status tc = mcb_flash_tc_backward(ctx, q, k, v, gout, lse, (const float *)delta, dq, dk, dv, n, seq, dim, heads, causal, ldi, ldo, ldg,
+                                              bias_partial, bias_ld);
         if (tc != MCB_UNSUPPORTED) {
+            if (bias_done && bias_partial && tc == MCB_OK) *bias_done = 1;
             mcb_free(ctx, delta); // stream-ordered reuse
             return tc;
         }

@@ -39,6 +39,10 @@ struct BwdArgs {
     int seq, heads, causal;
     float scale, scale_log2;
     unsigned int *err;
+    // optional by-product: column sums of the bf16 values each epilogue warp writes (the q / k / v bias gradients before
+    // their final reduction): row (sample * tiles + tile) * 4 + lane quarter of [.., bias_ld], columns which * dim + head * 64
+    float *bias_partial;
+    int bias_ld, dim;
 };
 
 template <int MODE>
@@ -322,6 +326,19 @@ flash_tc_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             }
             fence_async_smem();
             __syncwarp();
+            if (args.bias_partial) {
+                // lane l sums columns 2l, 2l+1 of this warp's 32 staged rows (the rounded values; rows past the sequence end excluded)
+                float c0 = 0.0f, c1 = 0.0f;
+                const int rows_live = min(32, args.seq - (o0 + wq * 32));
+                for (int rr = 0; rr < rows_live; ++rr) {
+                    const unsigned w2 = *(const unsigned *)(stage + rr * 128 + (((lane >> 2) ^ (rr & 7)) << 4) + (lane & 3) * 4);
+                    c0 += __uint_as_float(w2 << 16);
+                    c1 += __uint_as_float(w2 & 0xFFFF0000u);
+                }
+                const int which = MODE == 1 ? 0 : (hh == 1 ? 1 : 2); // dq, dk, dv column block of the packed gradient
+                float *dst = args.bias_partial + ((size_t)(n * tiles + own) * 4 + wq) * args.bias_ld + which * args.dim + h * HD + 2 * lane;
+                *(float2 *)dst = make_float2(c0, c1);
+            }
             if (lane == 0 && o0 + wq * 32 < args.seq) {
                 tma_store_3d(om, stage, h * HD, o0 + wq * 32, n);
                 bulk_commit();
@@ -371,7 +388,7 @@ mcb_status make_map3(mcb_ctx *ctx, CUtensorMap *map, const void *base, long long
 // MCB_UNSUPPORTED (nothing launched) outside the kernel's range.
 mcb_status mcb_flash_tc_backward(mcb_ctx *ctx, const void *q, const void *k, const void *v, const void *gout, const float *lse, const float *delta,
                                  void *dq, void *dk, void *dv, int64_t n, int64_t seq, int64_t dim, int64_t heads, int32_t causal, int64_t ldi,
-                                 int64_t ldo, int64_t ldg) {
+                                 int64_t ldo, int64_t ldg, float *bias_partial, int64_t bias_ld) {
     if (heads <= 0 || dim != heads * HD || ldi % 8 || ldo % 8 || ldg % 8 || n * heads > 65535) return MCB_UNSUPPORTED;
     if (!mcb_aligned16(q) || !mcb_aligned16(k) || !mcb_aligned16(v) || !mcb_aligned16(gout) || !mcb_aligned16(dq) || !mcb_aligned16(dk) ||
         !mcb_aligned16(dv))
@@ -394,6 +411,9 @@ mcb_status mcb_flash_tc_backward(mcb_ctx *ctx, const void *q, const void *k, con
     a.scale = 1.0f / sqrtf((float)HD);
     a.scale_log2 = a.scale * 1.4426950408889634f;
     a.err = ctx->d_err;
+    a.bias_partial = bias_partial;
+    a.bias_ld = (int)bias_ld;
+    a.dim = (int)dim;
     static bool attr_set = false;
     if (!attr_set) {
         MCB_CUDA(ctx, cudaFuncSetAttribute(flash_tc_bwd_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
@@ -407,3 +427,5 @@ mcb_status mcb_flash_tc_backward(mcb_ctx *ctx, const void *q, const void *k, con
     MCB_LAUNCHED(ctx);
     return MCB_OK;
 }
+
+int64_t mcb_flash_bias_rows(int64_t n, int64_t seq) { return n * ((seq + BT - 1) / BT) * 4; }

@@ -46,16 +46,20 @@ void mcb_tc_plan(mcb_ctx *ctx, int64_t m, int64_t n, int64_t k, bool allow_split
 bool mcb_flash_supported(int64_t dim, int64_t heads, int32_t dt);
 mcb_status mcb_flash_forward(mcb_ctx *ctx, const void *q, const void *k, const void *v, void *out, float *lse, int64_t n, int64_t seq,
                              int64_t dim, int64_t heads, int32_t causal, int64_t ldi, int64_t ldo);
+// bias_partial (optional): see mcb_flash_tc_backward; *bias_done says whether it was filled
 mcb_status mcb_flash_backward(mcb_ctx *ctx, const void *q, const void *k, const void *v, const void *out, const void *gout, const float *lse,
                               void *dq, void *dk, void *dv, int64_t n, int64_t seq, int64_t dim, int64_t heads, int32_t causal,
-                              int64_t ldi, int64_t ldo, int64_t ldg);
+                              int64_t ldi, int64_t ldo, int64_t ldg, float *bias_partial = nullptr, int64_t bias_ld = 0, int *bias_done = nullptr);
 // flash_tc.cu: the same forward on tcgen05 / TMEM; MCB_UNSUPPORTED (nothing launched) outside its range
 mcb_status mcb_flash_tc_forward(mcb_ctx *ctx, const void *q, const void *k, const void *v, void *out, float *lse, int64_t n, int64_t seq,
                                 int64_t dim, int64_t heads, int32_t causal, int64_t ldi, int64_t ldo);
 // flash_tc_bwd.cu: dq, dk, dv on tcgen05 / TMEM; `delta` = rowsum(O * dO) per (sample, head, row)
 mcb_status mcb_flash_tc_backward(mcb_ctx *ctx, const void *q, const void *k, const void *v, const void *gout, const float *lse, const float *delta,
                                  void *dq, void *dk, void *dv, int64_t n, int64_t seq, int64_t dim, int64_t heads, int32_t causal, int64_t ldi,
-                                 int64_t ldo, int64_t ldg);
+                                 int64_t ldo, int64_t ldg, float *bias_partial = nullptr, int64_t bias_ld = 0);
+// rows of the bias by-product of mcb_flash_tc_backward: [mcb_flash_bias_rows(n, seq)][bias_ld] partial column sums of dq | dk | dv
+// (columns 0, dim, 2 dim); 0 when the tcgen05 kernels would decline the shape
+int64_t mcb_flash_bias_rows(int64_t n, int64_t seq);
 // layer_norm_fast.cu: register-resident rows; MCB_UNSUPPORTED (nothing launched) outside their range
 mcb_status mcb_ln_fast_forward(mcb_ctx *ctx, const float *x, const float *gamma, const float *beta, double eps, void *out, int32_t out_dt,
                                float *mean, float *rstd, int64_t rows, int64_t dim);
