@@ -31,7 +31,7 @@ namespace {
 
 constexpr int BM = 128;
 constexpr int BK = 64; // 64 bf16 = one 128-byte swizzle row
-constexpr int kThreads = 224;
+constexpr int kThreads = 352; // 11 warps: A producer, MMA issuer, epilogue group 0 (warps 2-5), B producer, epilogue group 1 (warps 7-10)
 constexpr unsigned long long kWaitLimitNs = 2000000000ull; // 2 s
 
 struct TcArgs {
@@ -47,6 +47,7 @@ struct TcArgs {
     int m_tiles, n_tiles, kb_total, kb_per_split;
     int stages; // depth of the operand ring actually used (tuning knob; at most the compiled depth)
     int ring;   // output boxes per epilogue warp: 2, or 4 when one operand stage is given up for them
+    int epi_groups; // epilogue groups of four warps in use: 1 or 2
     // Split tail (sk_splits > 1): work items [0, sk_full) are whole tiles; the sk_rem tiles that would form a
     // mostly empty last wave are each cut into sk_splits slices of sk_kb k-blocks, whose f32 partial sums are
     // added into a workspace (map_pre) that a finishing kernel converts into the output.
@@ -340,8 +341,15 @@ template <int BN, bool PAIR> struct Cfg {
     static constexpr int kBRows = PAIR ? BN / 2 : BN; // B rows (output columns) staged per CTA
     static constexpr int kStageBytes = (BM + kBRows) * BK * 2;
     static constexpr int kStages = PAIR ? (BN == 128 ? 8 : 6) : (BN == 128 ? 6 : 4);
-    static constexpr int kOutStageBytes = 4 * 2 * 4096; // four epilogue warps x two 4 KB output boxes
-    static constexpr int kSmemBytes = kStages * kStageBytes + kOutStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+    // Output boxes: 4 KB each, `ring` per epilogue warp.  One epilogue group (four warps, one per TMEM lane quarter) needs
+    // 32 KB with two boxes each.  Tiles whose main loop is short (K of a few hundred) are bound by the epilogue, so where
+    // shared memory allows a second group of four warps takes every other 64-column chunk: 128 x 192 tiles have the room
+    // beside their four stages, 256-wide pair tiles give up one of six stages for it (chosen per launch).
+    static constexpr int kMaxGroups = ((BN == 192 && !PAIR) || (BN == 256 && PAIR)) ? 2 : 1;
+    static constexpr int kOutStageBytes = 4 * 2 * 4096;
+    static constexpr int kTileAndOutBytes = (BN == 256 && PAIR) ? (kStages * kStageBytes + kOutStageBytes) /* = 5 stages + 64 KB */
+                                                                : (kStages * kStageBytes + kMaxGroups * kOutStageBytes);
+    static constexpr int kSmemBytes = kTileAndOutBytes + 1024 /*align*/ + 256 /*barriers*/;
     static_assert(kSmemBytes <= 227 * 1024, "shared memory budget of one CTA");
 };
 
@@ -358,7 +366,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // the output boxes follow the operand stages in use: a launch may run one stage less and give that room to a
     // deeper ring of output boxes (args.ring = 4); the barriers sit behind the compiled maximum of both
     unsigned char *out_stage = tiles + (unsigned)args.stages * C::kStageBytes; // 1024-aligned: stage sizes are multiples of 8 KB
-    unsigned long long *bars = (unsigned long long *)(tiles + kStages * C::kStageBytes + C::kOutStageBytes);
+    unsigned long long *bars = (unsigned long long *)(tiles + C::kTileAndOutBytes);
     unsigned long long *full_bar = bars, *empty_bar = bars + kStages;
     unsigned long long *acc_full = bars + 2 * kStages, *acc_empty = acc_full + 2;
     unsigned *tmem_slot = (unsigned *)(acc_empty + 2);
@@ -381,7 +389,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(&acc_full[a], 1);
-            mbar_init(&acc_empty[a], PAIR ? 8 : 4); // the leader also collects the peer's four epilogue warps
+            mbar_init(&acc_empty[a], (PAIR ? 8u : 4u) * (unsigned)args.epi_groups); // the leader also collects the peer's epilogue warps
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -533,11 +541,13 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     } else {
         // ---------------------------------------------------------------- epilogue (warps 2..5)
         int q = warp & 3; // TMEM lane quarter this warp may access
+        const int ew = warp < 6 ? warp - 2 : warp - 3; // epilogue warp 0..7; group 0 = warps 2-5, group 1 = warps 7-10
+        const int grp = ew >> 2, groups = args.epi_groups; // a group takes every groups-th chunk of a tile
         unsigned tile_it = 0;
         StageRing rg;
-        rg.base = out_stage + q * (args.ring * 4096);
+        rg.base = out_stage + ew * (args.ring * 4096);
         rg.issued = 0;
-        for (unsigned w = w_first; w < work_total; w += w_stride, ++tile_it) {
+        for (unsigned w = w_first; w < work_total && grp < groups; w += w_stride, ++tile_it) {
             const WorkItem wi = decode_work(args, w, tiles_mn, one_split);
             const int split = wi.split;
             const unsigned t = wi.t;
@@ -558,7 +568,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 const bool live = has_k && (long long)y0 < args.m;
                 if (args.out_bf16 && !part) {
 #pragma unroll 1
-                    for (int c0 = 0; c0 < BN; c0 += 64) {
+                    for (int c0 = grp * 64; c0 < BN; c0 += 64 * groups) {
                         unsigned r0[32], r1[32];
                         unsigned taddr = tmem_base + ((unsigned)(q * 32) << 16) + (unsigned)(acc * BN + c0);
                         tmem_ld32(taddr, r0);
@@ -612,7 +622,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     }
                 } else {
 #pragma unroll 1
-                    for (int c0 = 0; c0 < BN; c0 += 32) {
+                    for (int c0 = grp * 32; c0 < BN; c0 += 32 * groups) {
                         unsigned r[32];
                         unsigned taddr = tmem_base + ((unsigned)(q * 32) << 16) + (unsigned)(acc * BN + c0);
                         tmem_ld32(taddr, r);
@@ -654,7 +664,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 continue;
             }
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
+            for (int c0 = grp * 32; c0 < BN; c0 += 32 * groups) {
                 unsigned r[32];
                 unsigned taddr = tmem_base + ((unsigned)(q * 32) << 16) + (unsigned)(acc * BN + c0);
                 tmem_ld32(taddr, r);
@@ -878,10 +888,16 @@ template <int BN, bool PAIR> mcb_status launch(mcb_ctx *ctx, const TcGemmParams 
     // Short reductions on 256-wide pair tiles are bound by the latency of the output stores (eight 4 KB boxes per
     // tile and warp, sixteen with a second output), not by the operand ring: one stage less, four boxes in flight.
     // (8192x3072x768: 34.8 -> 32.6 us; with K = 8192 or more the sixth stage is worth more: 323 -> 347 us.)
+    // The room of that stage goes either to four boxes per warp or to a second group of four epilogue warps (two boxes
+    // each) that takes every other chunk; MCB_TC_EPI=1 keeps the single group (tuning knob).
+    static const bool one_group = getenv("MCB_TC_EPI") && atoi(getenv("MCB_TC_EPI")) == 1;
+    a.epi_groups = 1;
     if (PAIR && BN == 256 && a.kb_per_split <= 16 && C::kStageBytes * 1 >= 4 * 2 * 4096 && !getenv("MCB_TC_STAGES")) {
         a.stages = C::kStages - 1;
-        a.ring = 4;
+        if (one_group) a.ring = 4;
+        else a.epi_groups = 2;
     }
+    if (BN == 192 && !PAIR && !one_group) a.epi_groups = 2; // 128 x 192 tiles: room for both groups beside the four stages
     if (const char *st = getenv("MCB_TC_STAGES")) {
         int v = atoi(st);
         if (v >= 2 && v < C::kStages) a.stages = v;
