@@ -892,7 +892,8 @@ template <int BN, bool PAIR> mcb_status launch(mcb_ctx *ctx, const TcGemmParams 
     // each) that takes every other chunk; MCB_TC_EPI=1 keeps the single group (tuning knob).
     static const bool one_group = getenv("MCB_TC_EPI") && atoi(getenv("MCB_TC_EPI")) == 1;
     a.epi_groups = 1;
-    if (PAIR && BN == 256 && a.kb_per_split <= 16 && C::kStageBytes * 1 >= 4 * 2 * 4096 && !getenv("MCB_TC_STAGES")) {
+    static const int short_kb = getenv("MCB_TC_EPI_KB") ? atoi(getenv("MCB_TC_EPI_KB")) : 16; // tuning knob: k-blocks per item up to which the stage is traded
+    if (PAIR && BN == 256 && a.kb_per_split <= short_kb && C::kStageBytes * 1 >= 4 * 2 * 4096 && !getenv("MCB_TC_STAGES")) {
         a.stages = C::kStages - 1;
         if (one_group) a.ring = 4;
         else a.epi_groups = 2;
