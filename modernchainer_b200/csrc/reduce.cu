@@ -432,7 +432,7 @@ __global__ void sce_final_kernel(const float *__restrict__ row_loss, long long n
 // `stats_out` / `stats_in` ([n][2]: row maximum, sum of exp): the loss pass of a training step leaves them for the
 // gradient pass, which then needs no reduction over the row and streams it once.
 template <typename T>
-__global__ void sce_fused_kernel(const T *x, T *out, const void *__restrict__ labels, int label_dt, long long n,
+__global__ void __launch_bounds__(512, 3) sce_fused_kernel(const T *x, T *out, const void *__restrict__ labels, int label_dt, long long n,
                                  long long c, float *__restrict__ row_loss, const float *__restrict__ upstream,
                                  unsigned int *err, float *__restrict__ stats_out, const float *__restrict__ stats_in) {
     __shared__ float red[32];
