@@ -250,7 +250,7 @@ mcb_status launch_map2(mcb_ctx *ctx, const void *x, const void *g, void *out, in
 // Lane l of a warp owns columns blockIdx.x*256 + 8l .. +7; the 8 warps of a block take rows
 // r0+w, r0+w+8, ...; partial[blockIdx.y][col] receives the block's sum of the ROUNDED outputs.
 template <int MODE>
-__global__ void __launch_bounds__(256) map_colsum_kernel(const void *__restrict__ a, const void *__restrict__ b,
+__global__ void __launch_bounds__(256, 6) map_colsum_kernel(const void *__restrict__ a, const void *__restrict__ b,
                                                          __nv_bfloat16 *__restrict__ out, long long rows, long long cols,
                                                          float *__restrict__ partial) {
     __shared__ float red[8][32][9];
