@@ -9,9 +9,11 @@
 // so fprop (x W^T), dgrad (g W) and wgrad (g^T x) all read the tensors where they lie; no
 // transposed copy is ever made.
 //
-// CTA layout (224 threads): warp 0 issues the TMA copies of A and warp 6 those of B, warp 1
+// CTA layout (352 threads): warp 0 issues the TMA copies of A and warp 6 those of B, warp 1
 // issues MMA and owns the TMEM allocation, warps 2..5 drain the accumulator (one TMEM lane
-// quarter each) and hand D to TMA in 128-byte-row boxes.  Two accumulators (2 x BN columns of
+// quarter each) and hand D to TMA in 128-byte-row boxes; warps 7..10 are a second such group
+// that takes every other 64-column chunk where shared memory has room for its boxes (short-K
+// tiles are bound by the epilogue).  Two accumulators (2 x BN columns of
 // TMEM) let the epilogue of tile i overlap the MMAs of tile i+1.  A 4..8-deep smem ring
 // decouples TMA from MMA.  Each of the single-thread roles is latency-bound on its own
 // instruction stream (a runtime division in the MMA loop alone cost 20% of the tensor rate),
