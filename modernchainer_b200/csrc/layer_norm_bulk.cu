@@ -1,14 +1,15 @@
 // LayerNorm forward / backward as a bulk-copy pipeline (rows of up to 1024 elements, dim % 8 == 0).
 //
-// One persistent CTA per SM: a producer thread streams blocks of seven consecutive rows (x, and for
+// One persistent CTA per SM: a producer thread streams blocks of eight (forward) or seven (backward) consecutive rows (x, and for
 // backward g and the pending gradient) from HBM into a ring of shared-memory stages with
 // cp.async.bulk (rows are contiguous, so each operand of a block is ONE copy and no tensor map is
-// needed); seven compute warps take one row each from the stage, reduce it with warp shuffles and
-// write the result straight from registers.  The ring keeps 100-180 KB of loads in flight per SM
+// needed); one compute warp per row takes its row from the stage, reduces it with warp shuffles and
+// writes the result straight from registers.  The ring keeps 100-180 KB of loads in flight per SM
 // without holding them in registers, which is what bounded the register-resident kernels
 // (layer_norm_fast.cu: 255 registers, one block per SM, 3.4 TB/s).  Every mbarrier wait is bounded.
 // dgamma / dbeta: per-lane register sums over the rows a warp handles, folded through shared memory in
-// a fixed warp order, finished by ln_bulk_params_final over the per-CTA partials (no float atomics).
+// a fixed warp order, finished by ln_bulk_params_final over the per-CTA partials (no float atomics).  Backward can
+// also leave dx rounded to bf16 and the column sums of those values for the Linear backward that reads dx next.
 #include <type_traits>
 
 #include "common.cuh"
@@ -19,9 +20,9 @@ namespace {
 
 using namespace tcptx;
 
-// rows per stage = compute warps.  Seven, so that the block is eight warps with the producer: registers are granted to
-// warps in groups of four, and a ninth warp would cap every thread at 168 registers, which the backward kernel with
-// by-products exceeds
+// rows per stage = compute warps.  Seven for backward, so that the block is eight warps with the producer: a ninth
+// warp puts three warps on one SM sub-partition, whose 16 K registers then cap every thread at 168, which the backward
+// kernel with by-products exceeds
 constexpr int kRowsBwd = 7;
 constexpr int kRowsFwd = 8;                  // the forward kernel needs 112 registers: nine warps are fine
 constexpr int kThreadsBwd = (kRowsBwd + 1) * 32; // + the producer warp
