@@ -359,10 +359,10 @@ def run_ours(args, dist):
             achieved = r["flops"] / (r["ms"] / 1e3) / 1e12
             traffic = traffic_src = None
             if dom == "gemm_tc" and cfg["kind"] == "decoder" and (cfg["vocab"], cfg["d"], cfg["ff"], cfg["seq"], cfg["batch"]) == (32000, 768, 3072, 1024, 8):
-                # ncu dram__bytes_read + dram__bytes_write of every GEMM launch of one step (profiles/c4_gemm_dram_traffic.md):
+                # ncu dram__bytes_read + dram__bytes_write of every GEMM launch of one step (the GEMM traffic summary under profiles/):
                 # 3180.4 MB for the three lm_head launches + 501.6 MB per layer, averaged over the step's GEMM launches
                 traffic = (3180.4e6 + 501.6e6 * cfg["layers"]) / (3 + 12 * cfg["layers"])
-                traffic_src = "ncu, 2-layer capture scaled by the layer count (profiles/c4_gemm_dram_traffic.md); bytes per launch, mean over the step's GEMMs"
+                traffic_src = "ncu capture of every GEMM launch of a 2-layer step, scaled by the layer count; bytes per launch, mean over the step's GEMMs"
             roof = dict(bound="tensor", kernel=dom, achieved=achieved, peak=pk["tf_sustained"], unit="TFLOP/s", frac=achieved / pk["tf_sustained"],
                         traffic=traffic, traffic_source=traffic_src, peak_source=pk["src"] + " (sustained cuBLAS bf16)",
                         avg_launch_ms=r["ms"] / r["launches"])
