@@ -60,9 +60,11 @@ enum {
 enum { MCB_F32 = 0, MCB_I64 = 1, MCB_I32 = 2, MCB_U8 = 3, MCB_F16 = 4, MCB_BF16 = 5 };
 
 /* GEMM arithmetic (ComputeType, crates/modern-chainer-cuda/src/backend.rs:109-136).
- * MCB_COMPUTE_F32: exact-f32 FMA kernel.  MCB_COMPUTE_BF16: tcgen05 tensor-core
- * kernel, bf16 operands rounded to nearest even, f32 accumulate in TMEM. */
-enum { MCB_COMPUTE_F32 = 0, MCB_COMPUTE_BF16 = 1 };
+ * MCB_COMPUTE_F32: exact-f32 FMA kernel.  MCB_COMPUTE_BF16 / MCB_COMPUTE_F16: tcgen05
+ * tensor-core kernel, operands rounded to nearest even to bf16 / IEEE f16, f32 accumulate
+ * in TMEM (the reference's ComputeType::Bf16 / ::F16; its Tf32 default has no counterpart:
+ * MCB_COMPUTE_F32 is exact). */
+enum { MCB_COMPUTE_F32 = 0, MCB_COMPUTE_BF16 = 1, MCB_COMPUTE_F16 = 2 };
 
 enum { MCB_ADD = 0, MCB_SUB = 1, MCB_MUL = 2, MCB_DIV = 3 };
 enum { MCB_EXP = 0, MCB_LOG = 1, MCB_SIGMOID = 2, MCB_SQRT = 3, MCB_SILU = 4, MCB_ABS = 5, MCB_NEG = 6 };
@@ -213,14 +215,18 @@ mcb_status mcb_linear(mcb_ctx *ctx, const float *x, const float *w, const float 
 /* Ops::linear_backward / linear_backward_with_bias, ops.rs:833-843: any of dx, dw, db may be NULL */
 mcb_status mcb_linear_backward(mcb_ctx *ctx, const float *g, const float *x, const float *w, float *dx, float *dw,
                                float *db, int64_t m, int64_t k, int64_t n);
-/* The tensor-core GEMM behind the bf16 compute type (replaces mixed_linear / mixed_matmul,
- * ops.rs:419-597).  D[M,N] (+)= A * B with f32 accumulation in TMEM.
+/* The tensor-core GEMM behind the bf16 / f16 compute types (replaces mixed_linear / mixed_matmul,
+ * ops.rs:419-597).  D[M,N] (+)= A * B with f32 accumulation in TMEM.  mcb_gemm_lowp takes the
+ * operands' 16-bit type (MCB_BF16 or MCB_F16) as in_dt; mcb_gemm_bf16 is the same call with MCB_BF16.
  *   A: bf16, a_mn_major=0 -> stored [M,K] (K contiguous); 1 -> stored [K,M] (M contiguous)
  *   B: bf16, b_mn_major=0 -> stored [N,K] (K contiguous); 1 -> stored [K,N] (N contiguous)
  *   D: [M,N] row-major, out_dt MCB_F32 or MCB_BF16; bias (f32 [N]) may be NULL
  *   accumulate!=0: D += result (f32 only, atomic adds, used with split_k > 1 for weight gradients)
  * M,N,K and the leading dimensions must be multiples of 8. */
 mcb_status mcb_gemm_bf16(mcb_ctx *ctx, const void *a, int32_t a_mn_major, const void *b, int32_t b_mn_major, void *d,
+                         int32_t out_dt, const float *bias, int64_t m, int64_t n, int64_t k, int32_t accumulate,
+                         int32_t split_k);
+mcb_status mcb_gemm_lowp(mcb_ctx *ctx, int32_t in_dt, const void *a, int32_t a_mn_major, const void *b, int32_t b_mn_major, void *d,
                          int32_t out_dt, const float *bias, int64_t m, int64_t n, int64_t k, int32_t accumulate,
                          int32_t split_k);
 
@@ -286,11 +292,14 @@ mcb_status mcb_var_is_leaf(mcb_var *v, int32_t *out);
 mcb_status mcb_var_unchain_backward(mcb_var *v);
 /* Variable::backward, autograd/src/variable.rs:150-207 */
 mcb_status mcb_var_backward(mcb_var *v);
-/* no_grad, autograd/src/lib.rs:20-60 (process-wide here; the binding keeps the thread-local) */
+/* no_grad, autograd/src/lib.rs:20-60: per host thread, like the reference's thread-local cell */
 void mcb_set_grad_enabled(int32_t enabled);
 int32_t mcb_is_grad_enabled(void);
-/* autocast, core/src/autocast.rs:6-44: MCB_BF16 to lower linear/matmul/attention, -1 to disable */
+/* autocast, core/src/autocast.rs:6-44: MCB_BF16 or MCB_F16 lowers linear / matmul / attention of the calling
+ * host thread to that type (operands rounded to nearest even, f32 accumulate); -1 disables.  LayerNorm,
+ * softmax, the loss and every reduction stay in f32. */
 void mcb_set_autocast(int32_t dtype_or_minus1);
+int32_t mcb_get_autocast(void); /* the calling thread's autocast type, or -1 */
 
 /* F::*, autograd/src/ops.rs:356-415,579-612,888-936 and host_ops.rs:594-990 */
 mcb_status mcb_f_binary(int32_t op, mcb_var *a, mcb_var *b, mcb_var **out);
@@ -415,9 +424,25 @@ void mcb_static_step_release(mcb_static_step *s);
  * and shared by the launcher.  After mcb_dp_attach every backward pass over the arena's
  * parameters all-reduces the gradient arena in buckets on a communication stream as soon
  * as the last gradient of a bucket is final, and the optimizer waits for them.  Gradients
- * are summed; the 1/world factor is folded into the optimizer's unscale factor. */
+ * are summed; the 1/world factor is folded into the optimizer's unscale factor (and into
+ * the norm mcb_clip_grad_norm measures), so N ranks at batch B behave like one at batch N*B.
+ *
+ * Rules and failure behaviour:
+ *   - ONE backward pass per optimizer step on an attached arena.  A second mcb_var_backward before
+ *     the optimizer (or mcb_zero_grad) has closed the round returns MCB_UNSUPPORTED and enqueues
+ *     nothing: its gradients would be added into buckets that are already summed over the ranks
+ *     and would never be exchanged themselves.
+ *   - mcb_dp_attach compares a checksum of the bucket plan across ranks and returns
+ *     MCB_INVALID_ARGUMENT when they differ.
+ *   - No call waits without a limit.  mcb_dp_init gives up after the timeout when a rank does not
+ *     join; synchronising calls (mcb_sync, mcb_memcpy_d2h, read-backs) poll instead of blocking
+ *     while collectives may be in flight.  An error reported by NCCL, a failed enqueue or an
+ *     expired timeout ABORTS the communicator (ncclCommAbort), after which every data-parallel
+ *     call on the context returns MCB_BACKEND: the caller leaves its loop, calls mcb_dp_shutdown
+ *     and may rebuild the group.  Default timeout 300 s; MCB_DP_TIMEOUT_MS or mcb_dp_set_timeout_ms. */
 mcb_status mcb_dp_unique_id(void *host_id_out_128);
 mcb_status mcb_dp_init(mcb_ctx *ctx, int32_t rank, int32_t world, const void *host_id_128);
+mcb_status mcb_dp_set_timeout_ms(mcb_ctx *ctx, int64_t timeout_ms);
 mcb_status mcb_dp_attach(mcb_ctx *ctx, mcb_arena *arena, int64_t bucket_bytes);
 mcb_status mcb_dp_allreduce_f32(mcb_ctx *ctx, float *buf, int64_t n, int32_t op_max); /* on the compute stream */
 mcb_status mcb_dp_shutdown(mcb_ctx *ctx);
@@ -425,6 +450,36 @@ mcb_status mcb_dp_shutdown(mcb_ctx *ctx);
  * first, into buckets of at most bucket_elems; bucket_of[i] receives the bucket index of tensor i */
 mcb_status mcb_dp_plan_buckets(const int64_t *sizes, int32_t n, int64_t bucket_elems, int32_t *bucket_of,
                                int32_t *n_buckets_out);
+/* host-only: MCB_OK when the `world` plan checksums (one per rank) agree, else MCB_INVALID_ARGUMENT */
+mcb_status mcb_dp_check_plan_checksums(const uint64_t *checksums, int32_t world);
+
+/* Host-only model of one rank's data-parallel round logic over a recording transport (no device, no NCCL):
+ * the code that decides when a bucket's all-reduce starts, refuses a second backward pass, and turns
+ * transport errors and timeouts into an abort is the code the GPU path runs; only the transport differs.
+ * For tests of the failure paths, which must not be provoked on a GPU.
+ *   _create      `n` parameter slots of the given (padded) sizes, planned into buckets like mcb_dp_attach does
+ *   _backward_begin / _grad_ready(param) / _finish (the optimizer's first act) / _zero_grad / _host_wait
+ *   _inject      what = 0: the enqueue of bucket `value` fails (this rank broke before it could take part);
+ *                what = 1: the transport reports an asynchronous error from its `value`-th poll on (a peer
+ *                          or the network failed); what = 2: value != 0: collectives never complete (a peer
+ *                          never joined)
+ *   _log         buckets in the order their all-reduce was enqueued; returns how many */
+typedef struct mcb_dp_sim mcb_dp_sim;
+mcb_status mcb_dp_sim_create(const int64_t *slot_sizes, int32_t n, int64_t bucket_elems, int32_t world, mcb_dp_sim **out);
+void mcb_dp_sim_release(mcb_dp_sim *s);
+mcb_status mcb_dp_sim_backward_begin(mcb_dp_sim *s);
+mcb_status mcb_dp_sim_grad_ready(mcb_dp_sim *s, int32_t param);
+mcb_status mcb_dp_sim_finish(mcb_dp_sim *s);
+mcb_status mcb_dp_sim_zero_grad(mcb_dp_sim *s);
+mcb_status mcb_dp_sim_host_wait(mcb_dp_sim *s, int32_t timeout_ms);
+void mcb_dp_sim_inject(mcb_dp_sim *s, int32_t what, int32_t value);
+int32_t mcb_dp_sim_log(mcb_dp_sim *s, int32_t *buckets_out, int32_t max);
+int32_t mcb_dp_sim_bucket_of(mcb_dp_sim *s, int32_t param);
+int32_t mcb_dp_sim_buckets(mcb_dp_sim *s);
+int32_t mcb_dp_sim_joins(mcb_dp_sim *s);
+int32_t mcb_dp_sim_aborted(mcb_dp_sim *s);
+uint64_t mcb_dp_sim_plan_checksum(mcb_dp_sim *s);
+const char *mcb_dp_sim_last_error(mcb_dp_sim *s);
 
 #ifdef __cplusplus
 }

@@ -123,6 +123,9 @@ class DeviceArray:
             pass
 
     def upload(self, host):
+        host = np.asarray(host)
+        if self.dtype == F16 and host.dtype == np.uint16:
+            host = host.view(np.float16)  # f16 bit patterns, like the uint16 form of bf16
         host = np.ascontiguousarray(host, _NP_OF[self.dtype])
         assert host.size == self.size
         self.ctx.check(self.ctx.lib.mcb_memcpy_h2d(self.ctx.h, self.ptr, host.ctypes.data_as(C.c_void_p), self.nbytes))
@@ -132,7 +135,9 @@ class DeviceArray:
         """Host copy; bf16 is widened to f32.  Raises if a kernel flagged a bad label or index."""
         out = np.empty(self.shape, _NP_OF[self.dtype])
         self.ctx.check(self.ctx.lib.mcb_memcpy_d2h(self.ctx.h, out.ctypes.data_as(C.c_void_p), self.ptr, self.nbytes))
-        return bf16_bits_to_f32(out).reshape(self.shape) if self.dtype == BF16 else out
+        if self.dtype == BF16:
+            return bf16_bits_to_f32(out).reshape(self.shape)
+        return out.astype(np.float32) if self.dtype == F16 else out
 
 
 class _Ops:
@@ -339,10 +344,14 @@ class _Ops:
 
     def gemm_bf16(self, a, a_mn, b, b_mn, m, n, k, out_dt=F32, bias=None, accumulate=False, split_k=1, init=None):
         """a, b: f32 host arrays in their stored layout (rounded to bf16 on upload)."""
-        da, db = self._a(np.asarray(a, np.float32), BF16), self._a(np.asarray(b, np.float32), BF16)
+        return self.gemm_lowp(BF16, a, a_mn, b, b_mn, m, n, k, out_dt, bias, accumulate, split_k, init)
+
+    def gemm_lowp(self, in_dt, a, a_mn, b, b_mn, m, n, k, out_dt=F32, bias=None, accumulate=False, split_k=1, init=None):
+        """The tensor-core GEMM with bf16 or f16 operands (in_dt); a, b are rounded to in_dt on upload."""
+        da, db = self._a(np.asarray(a, np.float32), in_dt), self._a(np.asarray(b, np.float32), in_dt)
         dbias = self._a(np.asarray(bias, np.float32)) if bias is not None else None
         out = self.ctx.array(np.asarray(init, np.float32)) if init is not None else self.ctx.zeros((m, n), out_dt)
-        self.ctx.check(self.lib.mcb_gemm_bf16(self.ctx.h, da.ptr, int(a_mn), db.ptr, int(b_mn), out.ptr, out_dt,
+        self.ctx.check(self.lib.mcb_gemm_lowp(self.ctx.h, in_dt, da.ptr, int(a_mn), db.ptr, int(b_mn), out.ptr, out_dt,
                                               dbias.ptr if dbias else None, m, n, k, int(accumulate), split_k))
         return out.numpy()
 
@@ -438,16 +447,19 @@ class no_grad:
 
 
 class autocast:
-    """`with autocast(BF16):` lowers linear / attention to bf16 tensor-core kernels."""
+    """`with autocast(BF16):` / `with autocast(F16):` lowers linear / attention of the calling thread to
+    tensor-core kernels with operands of that type (core/src/autocast.rs:10-44); scopes nest."""
 
     def __init__(self, dtype=BF16):
         self.dtype = dtype
 
     def __enter__(self):
-        _lib.load().mcb_set_autocast(self.dtype)
+        lib = _lib.load()
+        self.prev = lib.mcb_get_autocast()
+        lib.mcb_set_autocast(self.dtype)
 
     def __exit__(self, *a):
-        _lib.load().mcb_set_autocast(-1)
+        _lib.load().mcb_set_autocast(self.prev)
 
 
 class Variable:

@@ -106,17 +106,17 @@ mcb_status mcb_attention(mcb_ctx *ctx, const void *q, const void *k, const void 
                          int64_t seq, int64_t dim, int64_t heads, int32_t causal, int32_t dt) {
     MCB_CHECK_CTX(ctx);
     if (heads <= 0 || dim % heads != 0) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "attention dimension must divide heads");
-    if (dt != MCB_F32 && dt != MCB_BF16) return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "attention supports f32 and bf16");
+    if (dt != MCB_F32 && !mcb_is_lp(dt)) return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "attention supports f32, bf16 and f16");
     if (n == 0 || seq == 0 || dim == 0) return MCB_OK;
     long long hd = dim / heads, total = n * seq * dim;
     // algorithmic flops: 4 N H S^2 hd forward, 10 N H S^2 hd backward (halved under a causal mask)
     ProfScope prof(ctx, MCB_PROF_ATTENTION, 4.0 * (double)n * heads * seq * seq * hd * (causal ? 0.5 : 1.0),
-                   (double)total * (dt == MCB_BF16 ? 2.0 : 4.0) * 4.0);
+                   (double)total * (mcb_is_lp(dt) ? 2.0 : 4.0) * 4.0);
     if (mcb_flash_supported(dim, heads, dt)) {
         void *lse_buf = lse;
         Tmp own(ctx);
         if (!lse_buf) MCB_TRY(own.get(sizeof(float) * n * heads * seq, &lse_buf));
-        return mcb_flash_forward(ctx, q, k, v, out, (float *)lse_buf, n, seq, dim, heads, causal, dim, dim);
+        return mcb_flash_forward(ctx, q, k, v, out, (float *)lse_buf, n, seq, dim, heads, causal, dim, dim, dt);
     }
     Tmp tmp(ctx);
     const float *qf, *kf, *vf;
@@ -153,14 +153,14 @@ mcb_status mcb_attention_backward(mcb_ctx *ctx, const void *q, const void *k, co
     (void)out;
     (void)lse;
     if (heads <= 0 || dim % heads != 0) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "attention dimension must divide heads");
-    if (dt != MCB_F32 && dt != MCB_BF16) return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "attention supports f32 and bf16");
+    if (dt != MCB_F32 && !mcb_is_lp(dt)) return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "attention supports f32, bf16 and f16");
     if (n == 0 || seq == 0 || dim == 0) return MCB_OK;
     long long hd = dim / heads, total = n * seq * dim;
     // algorithmic flops: 4 N H S^2 hd forward, 10 N H S^2 hd backward (halved under a causal mask)
     ProfScope prof(ctx, MCB_PROF_ATTENTION, 10.0 * (double)n * heads * seq * seq * hd * (causal ? 0.5 : 1.0),
-                   (double)total * (dt == MCB_BF16 ? 2.0 : 4.0) * 8.0);
+                   (double)total * (mcb_is_lp(dt) ? 2.0 : 4.0) * 8.0);
     if (mcb_flash_supported(dim, heads, dt) && out && lse)
-        return mcb_flash_backward(ctx, q, k, v, out, gout, lse, dq, dk, dv, n, seq, dim, heads, causal, dim, dim, dim);
+        return mcb_flash_backward(ctx, q, k, v, out, gout, lse, dq, dk, dv, n, seq, dim, heads, causal, dim, dim, dim, nullptr, 0, nullptr, dt);
     float scale = 1.0f / sqrtf((float)hd);
     Tmp tmp(ctx);
     const float *qf, *kf, *vf, *gf;

@@ -26,8 +26,11 @@
 
 namespace mcbag {
 
-static bool g_grad_enabled = true;
-static int g_autocast = -1;
+// Grad mode and autocast are per host thread, as in the reference (thread-local cells in
+// crates/modern-chainer-autograd/src/lib.rs:20-22 and crates/modern-chainer-core/src/autocast.rs:6-8):
+// two threads driving two contexts do not see each other's no_grad / autocast scopes.
+static thread_local bool g_grad_enabled = true;
+static thread_local int g_autocast = -1;
 
 bool grad_enabled() { return g_grad_enabled; }
 int autocast() { return g_autocast; }
@@ -66,11 +69,21 @@ mcb_status to_dtype(mcb_ctx *ctx, const Tensor &t, int dt, Tensor *out) {
         *out = t;
         return MCB_OK;
     }
+    if (t.dt != MCB_F32 && dt != MCB_F32) { // bf16 <-> f16: through f32 (every bf16 and f16 value is exact in f32)
+        Tensor f;
+        MCB_TRY(new_tensor(ctx, MCB_F32, t.shape, &f));
+        MCB_TRY(mcb_cast(ctx, t.ptr, t.dt, f.ptr, MCB_F32, t.numel()));
+        MCB_TRY(new_tensor(ctx, dt, t.shape, out));
+        return mcb_cast(ctx, f.ptr, MCB_F32, out->ptr, dt, t.numel());
+    }
     MCB_TRY(new_tensor(ctx, dt, t.shape, out));
     return mcb_cast(ctx, t.ptr, t.dt, out->ptr, dt, t.numel());
 }
 
-static bool is_float(int dt) { return dt == MCB_F32 || dt == MCB_BF16; }
+static bool is_float(int dt) { return dt == MCB_F32 || dt == MCB_BF16 || dt == MCB_F16; }
+static bool is_lp(int dt) { return dt == MCB_BF16 || dt == MCB_F16; }
+// storage type of the sum of two gradients: f32 unless both are the same 16-bit type
+static int sum_dtype(int a, int b) { return (is_lp(a) && a == b) ? a : MCB_F32; }
 
 // ------------------------------------------------------------------ apply
 Var make_var(mcb_ctx *ctx, const Tensor &data, bool requires_grad) {
@@ -125,7 +138,7 @@ static mcb_status grad_dst(const Var &v, Tensor *out, bool *direct) {
 // While a node's backward runs, the walker exposes, per input, the gradient that is already
 // waiting for that input if the walker holds its only reference.  An op that can add into such
 // a tensor in place returns it as the input's gradient and the walker skips its own fan-in add.
-static const std::vector<const Tensor *> *g_pending = nullptr;
+static thread_local const std::vector<const Tensor *> *g_pending = nullptr; // set by the walker of this thread around each node's backward
 static const Tensor *pending_grad(size_t input) {
     if (!g_pending || input >= g_pending->size()) return nullptr;
     return (*g_pending)[input];
@@ -156,7 +169,7 @@ static mcb_status accumulate_leaf(const Var &v, const Tensor &g) {
         return mcb_add_inplace(ctx, v->grad.ptr, g.ptr, g.numel(), g.dt);
     }
     Tensor sum;
-    int dt = (v->grad.dt == MCB_F32 || g.dt == MCB_F32) ? MCB_F32 : MCB_BF16;
+    int dt = sum_dtype(v->grad.dt, g.dt);
     MCB_TRY(new_tensor(ctx, dt, g.shape, &sum));
     MCB_TRY(mcb_add_typed(ctx, v->grad.ptr, v->grad.dt, g.ptr, g.dt, sum.ptr, dt, g.numel()));
     v->grad = sum;
@@ -189,6 +202,16 @@ mcb_status backward(const Var &root) {
                 stack.emplace_back(in, false);
                 if (!in->node && in->requires_grad) ++leaf_uses[in.get()];
             }
+    }
+    // a data-parallel arena takes one backward pass per optimizer step: refused here, before anything is enqueued
+    {
+        std::vector<Arena *> begun;
+        for (auto &lu : leaf_uses) {
+            Arena *a = lu.first->arena;
+            if (!a || std::find(begun.begin(), begun.end(), a) != begun.end()) continue;
+            begun.push_back(a);
+            MCB_TRY(arena_backward_begin(a));
+        }
     }
     std::unordered_map<VarImpl *, Tensor> grads;
     {
@@ -275,7 +298,7 @@ mcb_status backward(const Var &root) {
                 cur.aux.reset();
             } else {
                 Tensor sum;
-                int dt = (cur.dt == MCB_F32 || add.dt == MCB_F32) ? MCB_F32 : MCB_BF16;
+                int dt = sum_dtype(cur.dt, add.dt);
                 st = new_tensor(ctx, dt, cur.shape, &sum);
                 if (st == MCB_OK) st = mcb_add_typed(ctx, cur.ptr, cur.dt, add.ptr, add.dt, sum.ptr, dt, cur.numel());
                 cur = sum;
@@ -338,7 +361,7 @@ static mcb_status like_input(mcb_ctx *ctx, const Tensor &g, const Var &in, Tenso
 // rounds its incoming gradient to bf16 as its first step anyway (same values), and does so in the
 // pass that also produces the bias gradient, so rounding here would only add a kernel.
 static mcb_status like_input_lazy(mcb_ctx *ctx, const Tensor &g, const Var &in, Tensor *out) {
-    if (g.dt == MCB_F32 && in->data.dt == MCB_BF16 && in->node && !getenv("MCB_UNFUSED_BWD") &&
+    if (g.dt == MCB_F32 && is_lp(in->data.dt) && in->node && !getenv("MCB_UNFUSED_BWD") &&
         (!strcmp(in->node->name, "Linear") || !strcmp(in->node->name, "LinearActivation"))) {
         *out = g;
         return MCB_OK;
@@ -356,7 +379,7 @@ mcb_status f_binary(int op, const Var &a, const Var &b, Var *out) {
     bool mixed = (a->data.dt != MCB_F32 || b->data.dt != MCB_F32);
     if (op == MCB_ADD && a->data.shape == b->data.shape && mixed) {
         // residual add with a low-precision operand: one pass, f32 result unless both are bf16
-        int odt = (a->data.dt == MCB_BF16 && b->data.dt == MCB_BF16) ? MCB_BF16 : MCB_F32;
+        int odt = sum_dtype(a->data.dt, b->data.dt);
         MCB_TRY(new_tensor(ctx, odt, a->data.shape, &res));
         MCB_TRY(mcb_add_typed(ctx, a->data.ptr, a->data.dt, b->data.ptr, b->data.dt, res.ptr, odt, res.numel()));
     } else {
@@ -549,28 +572,35 @@ mcb_status f_sum(const Var &x, Var *out) { return f_sum_mean(x, false, out); }
 mcb_status f_mean(const Var &x, Var *out) { return f_sum_mean(x, true, out); }
 
 // ---- GEMM helpers ----------------------------------------------------------------------
-static bool use_bf16(mcb_ctx *ctx) { return g_autocast == MCB_BF16 || ctx->compute == MCB_COMPUTE_BF16; }
+// The 16-bit type linear / matmul / attention are lowered to, or -1: the autocast scope of this thread first
+// (core/src/autocast.rs:10-44), else the context's compute type (cuda/src/backend.rs:109-136).
+static int lowp_dtype(mcb_ctx *ctx) {
+    if (is_lp(g_autocast)) return g_autocast;
+    if (ctx->compute == MCB_COMPUTE_BF16) return MCB_BF16;
+    if (ctx->compute == MCB_COMPUTE_F16) return MCB_F16;
+    return -1;
+}
 static bool tc_shape_ok(int64_t m, int64_t n, int64_t k) { return m > 0 && (n % 8 == 0) && (k % 8 == 0) && n > 0 && k > 0; }
 
-// bf16 operand for `v`: the arena's shadow copy for parameters, the tensor itself when it is
-// already bf16, otherwise a converted copy
-static mcb_status bf16_of(const Var &v, Tensor *out) {
-    if (v->data.dt == MCB_BF16) {
+// 16-bit operand (type lp) for `v`: the arena's shadow copy for parameters, the tensor itself when it
+// already has that type, otherwise a converted copy
+static mcb_status lowp_of(const Var &v, int lp, Tensor *out) {
+    if (v->data.dt == lp) {
         *out = v->data;
         return MCB_OK;
     }
     if (v->arena) {
-        MCB_TRY(arena_refresh_shadow(v->arena));
+        MCB_TRY(arena_refresh_shadow(v->arena, lp));
         Tensor t;
         t.buf = v->arena->shadow;
-        t.ptr = (__nv_bfloat16 *)v->arena->shadow->p + v->arena->off[v->arena_idx];
-        t.dt = MCB_BF16;
+        t.ptr = (uint16_t *)v->arena->shadow->p + v->arena->off[v->arena_idx];
+        t.dt = lp;
         t.shape = v->data.shape;
         t.defined = true;
         *out = t;
         return MCB_OK;
     }
-    return to_dtype(v->ctx, v->data, MCB_BF16, out);
+    return to_dtype(v->ctx, v->data, lp, out);
 }
 
 static int pick_split_k(mcb_ctx *ctx, int64_t m, int64_t n, int64_t k) {
@@ -585,9 +615,11 @@ static int pick_split_k(mcb_ctx *ctx, int64_t m, int64_t n, int64_t k) {
 }
 
 struct LinearSaved {
-    Tensor x;      // activation as used by the forward GEMM (bf16 under autocast, else f32)
+    Tensor x;      // activation as used by the forward GEMM (16-bit under autocast, else f32)
     Tensor pre;    // pre-activation (linear_activation only)
-    bool bf16 = false;
+    bool bf16 = false; // the op ran on the tensor cores with 16-bit operands of type lp
+    int lp = MCB_BF16;
+    bool emulated = false; // operands rounded to lp, product on the exact-f32 kernel (shapes the tensor-core kernel declines)
     int act = MCB_ACT_NONE;
 };
 
@@ -595,7 +627,7 @@ struct LinearSaved {
 static mcb_status linear_backward_impl(mcb_ctx *ctx, const Tensor &g_in, const LinearSaved &sv, const Var &x, const Var &w,
                                        const Var &b, std::vector<Tensor> &gi) {
     int64_t m = sv.x.numel() / sv.x.shape.back(), k = sv.x.shape.back(), n = w->data.shape[0];
-    int gdt = sv.bf16 ? MCB_BF16 : MCB_F32;
+    int gdt = sv.bf16 ? sv.lp : MCB_F32;
     Tensor g;
     // The bias gradient is the column sum of the bf16 gradient the GEMMs below read.  Whenever a
     // pass over that gradient is needed anyway (a cast from f32, the activation's backward), the
@@ -603,7 +635,7 @@ static mcb_status linear_backward_impl(mcb_ctx *ctx, const Tensor &g_in, const L
     const bool fuse = getenv("MCB_UNFUSED_BWD") == nullptr; // test knob: separate cast / activation-backward / column-sum kernels
     const bool want_db = b && b->requires_grad;
     bool db_done = false;
-    if (fuse && sv.bf16 && sv.act == MCB_ACT_NONE && g_in.dt == MCB_F32 && g_in.aux && g_in.aux->bf16.numel() == g_in.numel() &&
+    if (fuse && sv.bf16 && sv.act == MCB_ACT_NONE && g_in.dt == MCB_F32 && g_in.aux && g_in.aux->bf16.numel() == g_in.numel() && g_in.aux->bf16.dt == sv.lp &&
         g_in.aux->colsum.numel() == n && !g_in.shape.empty() && g_in.shape.back() == n) {
         // the kernel that wrote this f32 gradient (LayerNorm backward on the residual stream) already left it rounded to
         // bf16 together with the column sums of the rounded values: nothing to read again
@@ -616,8 +648,8 @@ static mcb_status linear_backward_impl(mcb_ctx *ctx, const Tensor &g_in, const L
     } else if (fuse && sv.bf16 && want_db && sv.act == MCB_ACT_NONE && g_in.dt == MCB_F32 && mcb_map_colsum_supported(g_in.ptr, nullptr, g_in.ptr, n)) {
         bool direct;
         MCB_TRY(grad_dst(b, &gi[2], &direct));
-        MCB_TRY(new_tensor(ctx, MCB_BF16, g_in.shape, &g));
-        MCB_TRY(mcb_map_colsum(ctx, 0, g_in.ptr, nullptr, g.ptr, m, n, (float *)gi[2].ptr));
+        MCB_TRY(new_tensor(ctx, sv.lp, g_in.shape, &g));
+        MCB_TRY(mcb_map_colsum(ctx, 0, g_in.ptr, nullptr, g.ptr, m, n, (float *)gi[2].ptr, sv.lp));
         db_done = true;
     } else {
         MCB_TRY(to_dtype(ctx, g_in, gdt, &g));
@@ -628,7 +660,7 @@ static mcb_status linear_backward_impl(mcb_ctx *ctx, const Tensor &g_in, const L
         if (fuse && sv.bf16 && want_db && mcb_map_colsum_supported(sv.pre.ptr, g.ptr, gp.ptr, n)) {
             bool direct;
             MCB_TRY(grad_dst(b, &gi[2], &direct));
-            MCB_TRY(mcb_map_colsum(ctx, sv.act == MCB_ACT_GELU ? 1 : 2, sv.pre.ptr, g.ptr, gp.ptr, m, n, (float *)gi[2].ptr));
+            MCB_TRY(mcb_map_colsum(ctx, sv.act == MCB_ACT_GELU ? 1 : 2, sv.pre.ptr, g.ptr, gp.ptr, m, n, (float *)gi[2].ptr, sv.lp));
             db_done = true;
         } else {
             MCB_TRY((sv.act == MCB_ACT_GELU ? mcb_gelu_backward : mcb_relu_backward)(ctx, sv.pre.ptr, g.ptr, gp.ptr, g.numel(), gdt));
@@ -638,10 +670,11 @@ static mcb_status linear_backward_impl(mcb_ctx *ctx, const Tensor &g_in, const L
     if (sv.bf16) {
         if (x->requires_grad) {
             Tensor wb;
-            MCB_TRY(bf16_of(w, &wb));
-            int xdt = is_float(x->data.dt) ? x->data.dt : MCB_F32;
+            MCB_TRY(lowp_of(w, sv.lp, &wb));
+            int xdt = x->data.dt == sv.lp ? sv.lp : MCB_F32;
             MCB_TRY(new_tensor(ctx, xdt, x->data.shape, &gi[0]));
             TcGemmParams p; // dx[m,k] = g[m,n] * W[n,k]
+            p.in_dt = sv.lp;
             p.a = g.ptr; p.a_mn_major = 0; p.lda = n;
             p.b = wb.ptr; p.b_mn_major = 1; p.ldb = k;
             p.d = gi[0].ptr; p.out_dt = xdt; p.ldd = k;
@@ -652,6 +685,7 @@ static mcb_status linear_backward_impl(mcb_ctx *ctx, const Tensor &g_in, const L
             bool direct;
             MCB_TRY(grad_dst(w, &gi[1], &direct));
             TcGemmParams p; // dw[n,k] = g^T[n,m] * x[m,k]
+            p.in_dt = sv.lp;
             p.a = g.ptr; p.a_mn_major = 1; p.lda = n;
             p.b = sv.x.ptr; p.b_mn_major = 1; p.ldb = k;
             p.d = gi[1].ptr; p.out_dt = MCB_F32; p.ldd = k;
@@ -674,10 +708,18 @@ static mcb_status linear_backward_impl(mcb_ctx *ctx, const Tensor &g_in, const L
             MCB_TRY(grad_dst(w, &gi[1], &direct));
             dw = (float *)gi[1].ptr;
         }
-        MCB_TRY(mcb_linear_backward(ctx, (const float *)g.ptr, (const float *)sv.x.ptr, (const float *)w->data.ptr, dx, dw, nullptr, m, k, n));
-        if (x->requires_grad && x->data.dt == MCB_BF16) {
+        Tensor wf = w->data;
+        if (sv.emulated) { // same rounding points as the tensor-core path: gradient and weight rounded to the 16-bit type
             Tensor t;
-            MCB_TRY(to_dtype(ctx, gi[0], MCB_BF16, &t));
+            MCB_TRY(to_dtype(ctx, g, sv.lp, &t));
+            MCB_TRY(to_dtype(ctx, t, MCB_F32, &g));
+            MCB_TRY(to_dtype(ctx, w->data, sv.lp, &t));
+            MCB_TRY(to_dtype(ctx, t, MCB_F32, &wf));
+        }
+        MCB_TRY(mcb_linear_backward(ctx, (const float *)g.ptr, (const float *)sv.x.ptr, (const float *)wf.ptr, dx, dw, nullptr, m, k, n));
+        if (x->requires_grad && is_lp(x->data.dt)) {
+            Tensor t;
+            MCB_TRY(to_dtype(ctx, gi[0], x->data.dt, &t));
             gi[0] = t;
         }
     }
@@ -702,35 +744,60 @@ static mcb_status f_linear_impl(const Var &x, const Var &w, const Var &b, int ac
     oshape.back() = n;
     auto sv = std::make_shared<LinearSaved>();
     sv->act = act;
-    sv->bf16 = use_bf16(ctx) && tc_shape_ok(m, n, k);
+    const int lp = lowp_dtype(ctx);
+    sv->bf16 = lp >= 0 && tc_shape_ok(m, n, k);
+    sv->emulated = lp >= 0 && !sv->bf16 && m > 0 && n > 0 && k > 0;
+    if (lp >= 0) sv->lp = lp;
     Tensor res;
     if (sv->bf16) {
         Tensor wb;
-        MCB_TRY(to_dtype(ctx, x->data, MCB_BF16, &sv->x));
-        MCB_TRY(bf16_of(w, &wb));
-        MCB_TRY(new_tensor(ctx, MCB_BF16, oshape, &res));
+        MCB_TRY(to_dtype(ctx, x->data, lp, &sv->x));
+        MCB_TRY(lowp_of(w, lp, &wb));
+        MCB_TRY(new_tensor(ctx, lp, oshape, &res));
         TcGemmParams p; // y[m,n] = x[m,k] * W[n,k]^T + bias
+        p.in_dt = lp;
         p.a = sv->x.ptr; p.lda = k;
         p.b = wb.ptr; p.ldb = k;
-        p.d = res.ptr; p.out_dt = MCB_BF16; p.ldd = n;
+        p.d = res.ptr; p.out_dt = lp; p.ldd = n;
         p.bias = b ? (const float *)b->data.ptr : nullptr;
         p.m = m; p.n = n; p.k = k;
         p.act = act;
         if (act != MCB_ACT_NONE && g_grad_enabled) {
-            MCB_TRY(new_tensor(ctx, MCB_BF16, oshape, &sv->pre));
+            MCB_TRY(new_tensor(ctx, lp, oshape, &sv->pre));
             p.d_pre = sv->pre.ptr;
         }
         MCB_TRY(mcb_tc_gemm(ctx, p));
     } else {
-        MCB_TRY(f32_of(x, &sv->x));
+        // Shapes the tensor-core kernel declines (an extent that is not a multiple of 8) keep the lowering's
+        // numerics under autocast: operands rounded to the 16-bit type, exact f32 products and sums, f32 result
+        // (the reference lowers every linear under autocast, cuda/src/ops.rs:762-781).
+        Tensor wf = w->data;
+        if (sv->emulated) {
+            Tensor t;
+            MCB_TRY(to_dtype(ctx, x->data, lp, &t));
+            MCB_TRY(to_dtype(ctx, t, MCB_F32, &sv->x));
+            MCB_TRY(lowp_of(w, lp, &t));
+            MCB_TRY(to_dtype(ctx, t, MCB_F32, &wf));
+        } else {
+            MCB_TRY(f32_of(x, &sv->x));
+        }
         MCB_TRY(new_tensor(ctx, MCB_F32, oshape, &res));
         const float *bp = b ? (const float *)b->data.ptr : nullptr;
         if (act != MCB_ACT_NONE) {
             MCB_TRY(new_tensor(ctx, MCB_F32, oshape, &sv->pre));
-            MCB_TRY(mcb_linear(ctx, (const float *)sv->x.ptr, (const float *)w->data.ptr, bp, (float *)sv->pre.ptr, m, k, n, MCB_ACT_NONE));
+            MCB_TRY(mcb_linear(ctx, (const float *)sv->x.ptr, (const float *)wf.ptr, bp, (float *)sv->pre.ptr, m, k, n, MCB_ACT_NONE));
             MCB_TRY((act == MCB_ACT_GELU ? mcb_gelu : mcb_relu)(ctx, sv->pre.ptr, res.ptr, res.numel(), MCB_F32));
         } else {
-            MCB_TRY(mcb_linear(ctx, (const float *)sv->x.ptr, (const float *)w->data.ptr, bp, (float *)res.ptr, m, k, n, MCB_ACT_NONE));
+            MCB_TRY(mcb_linear(ctx, (const float *)sv->x.ptr, (const float *)wf.ptr, bp, (float *)res.ptr, m, k, n, MCB_ACT_NONE));
+        }
+        if (sv->emulated) { // stored like the tensor-core path stores it: result in the 16-bit type, pre-activation rounded to it
+            Tensor t;
+            MCB_TRY(to_dtype(ctx, res, lp, &t));
+            res = t;
+            if (sv->pre.defined) {
+                MCB_TRY(to_dtype(ctx, sv->pre, lp, &t));
+                MCB_TRY(to_dtype(ctx, t, MCB_F32, &sv->pre));
+            }
         }
     }
     std::vector<Var> ins = {x, w};
@@ -816,7 +883,7 @@ mcb_status f_layer_norm(const Var &x, const Var &gamma, const Var &beta, double 
     int64_t rows = dim ? x->data.numel() / dim : 0;
     Tensor xf, res, mean, rstd;
     MCB_TRY(f32_of(x, &xf));
-    int odt = (g_autocast == MCB_BF16) ? MCB_BF16 : MCB_F32; // under autocast the result only feeds low-precision GEMMs
+    int odt = is_lp(g_autocast) ? g_autocast : MCB_F32; // under autocast the result only feeds low-precision GEMMs
     MCB_TRY(new_tensor(ctx, odt, xf.shape, &res));
     MCB_TRY(new_tensor(ctx, MCB_F32, {rows}, &mean));
     MCB_TRY(new_tensor(ctx, MCB_F32, {rows}, &rstd));
@@ -835,24 +902,25 @@ void layer_norm_node(mcb_ctx *ctx, const Var &x, const Var &gamma, const Var &be
     // A bf16 result means the model runs under autocast: the gradient of the f32 residual stream that this backward
     // writes is then read next by the backward of a bf16 Linear, which wants it rounded to bf16 and its column sums (the
     // bias gradient).  The pipeline kernel leaves both as by-products (GradAux) and saves that Linear a pass over dx.
-    const bool lowp = res.dt == MCB_BF16;
-    *out = apply(ctx, "LayerNorm", res, {x, gamma, beta}, [ctx, xf, mean, rstd, xv, gv, bv, eps, rows, dim, lowp](const Tensor &g, std::vector<Tensor> &gi) -> mcb_status {
+    const bool lowp = is_lp(res.dt);
+    const int lpdt = res.dt;
+    *out = apply(ctx, "LayerNorm", res, {x, gamma, beta}, [ctx, xf, mean, rstd, xv, gv, bv, eps, rows, dim, lowp, lpdt](const Tensor &g, std::vector<Tensor> &gi) -> mcb_status {
         Tensor dx, dg, db;
         bool d1, d2;
         MCB_TRY(grad_dst(gv, &dg, &d1));
         MCB_TRY(grad_dst(bv, &db, &d2));
         const bool fuse = getenv("MCB_UNFUSED_BWD") == nullptr; // test knob: separate fan-in add, cast and column sums
-        const bool want_aux = fuse && lowp && xv->data.dt == MCB_F32 && (g.dt == MCB_F32 || g.dt == MCB_BF16) && !getenv("MCB_LN_NO_AUX");
+        const bool want_aux = fuse && lowp && xv->data.dt == MCB_F32 && (g.dt == MCB_F32 || g.dt == lpdt) && !getenv("MCB_LN_NO_AUX");
         // the pipeline kernel with the by-products; MCB_UNSUPPORTED (nothing launched) where it does not apply
         auto with_aux = [&](const float *addend, float *dst, std::shared_ptr<GradAux> *aux_out) -> mcb_status {
             if (!want_aux) return MCB_UNSUPPORTED;
             auto aux = std::make_shared<GradAux>();
-            MCB_TRY(new_tensor(ctx, MCB_BF16, xf.shape, &aux->bf16));
+            MCB_TRY(new_tensor(ctx, lpdt, xf.shape, &aux->bf16));
             MCB_TRY(new_tensor(ctx, MCB_F32, {dim}, &aux->colsum));
-            ProfScope prof(ctx, MCB_PROF_NORM, 0.0, (double)rows * dim * (10.0 + (g.dt == MCB_BF16 ? 2.0 : 4.0) + (addend ? 4.0 : 0.0)) + 8.0 * rows + 12.0 * dim);
+            ProfScope prof(ctx, MCB_PROF_NORM, 0.0, (double)rows * dim * (10.0 + (is_lp(g.dt) ? 2.0 : 4.0) + (addend ? 4.0 : 0.0)) + 8.0 * rows + 12.0 * dim);
             mcb_status st = mcb_ln_bulk_backward(ctx, (const float *)xf.ptr, (const float *)gv->data.ptr, g.ptr, g.dt, eps, (const float *)mean.ptr,
                                                  (const float *)rstd.ptr, addend, dst, (float *)dg.ptr, (float *)db.ptr, rows, dim, aux->bf16.ptr,
-                                                 (float *)aux->colsum.ptr);
+                                                 (float *)aux->colsum.ptr, lpdt);
             if (st == MCB_OK) *aux_out = aux;
             return st;
         };
@@ -897,10 +965,10 @@ mcb_status f_add_layer_norm(const Var &a, const Var &b, const Var &gamma, const 
     mcb_ctx *ctx = a->ctx;
     const std::vector<int64_t> &sh = a->data.shape;
     if (!getenv("MCB_UNFUSED_ADD_LN") && sh.size() >= 2 && sh == b->data.shape && a->data.dt == MCB_F32 &&
-        (b->data.dt == MCB_F32 || b->data.dt == MCB_BF16) && gamma->data.numel() == sh.back() && beta->data.numel() == sh.back() &&
+        (b->data.dt == MCB_F32 || is_lp(b->data.dt)) && gamma->data.numel() == sh.back() && beta->data.numel() == sh.back() &&
         gamma->data.dt == MCB_F32 && beta->data.dt == MCB_F32) {
         const int64_t dim = sh.back(), rows = dim ? a->data.numel() / dim : 0;
-        const int odt = (g_autocast == MCB_BF16) ? MCB_BF16 : MCB_F32;
+        const int odt = is_lp(g_autocast) ? g_autocast : MCB_F32;
         Tensor st, res, mean, rstd;
         MCB_TRY(new_tensor(ctx, MCB_F32, sh, &st));
         MCB_TRY(new_tensor(ctx, odt, sh, &res));
@@ -908,7 +976,7 @@ mcb_status f_add_layer_norm(const Var &a, const Var &b, const Var &gamma, const 
         MCB_TRY(new_tensor(ctx, MCB_F32, {rows}, &rstd));
         mcb_status fused;
         {
-            ProfScope prof(ctx, MCB_PROF_NORM, 0.0, (double)rows * dim * (8.0 + (b->data.dt == MCB_BF16 ? 2.0 : 4.0) + (odt == MCB_BF16 ? 2.0 : 4.0)) + 8.0 * rows);
+            ProfScope prof(ctx, MCB_PROF_NORM, 0.0, (double)rows * dim * (8.0 + (is_lp(b->data.dt) ? 2.0 : 4.0) + (is_lp(odt) ? 2.0 : 4.0)) + 8.0 * rows);
             fused = mcb_ln_bulk_add_forward(ctx, (const float *)a->data.ptr, b->data.ptr, b->data.dt, (const float *)gamma->data.ptr,
                                             (const float *)beta->data.ptr, eps, (float *)st.ptr, res.ptr, odt, (float *)mean.ptr, (float *)rstd.ptr, rows, dim);
         }
@@ -1065,7 +1133,7 @@ mcb_status f_multi_head_attention(const Var &q, const Var &k, const Var &v, int6
     if (k->data.shape != q->data.shape || v->data.shape != q->data.shape) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "attention q/k/v shape mismatch");
     int64_t n = q->data.shape[0], s = q->data.shape[1], d = q->data.shape[2];
     if (heads <= 0 || d % heads) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "attention dimension must divide heads");
-    int dt = (q->data.dt == MCB_BF16 && k->data.dt == MCB_BF16 && v->data.dt == MCB_BF16) ? MCB_BF16 : MCB_F32;
+    int dt = (is_lp(q->data.dt) && k->data.dt == q->data.dt && v->data.dt == q->data.dt) ? q->data.dt : MCB_F32;
     Tensor qt, kt, vt, res, lse;
     MCB_TRY(to_dtype(ctx, q->data, dt, &qt));
     MCB_TRY(to_dtype(ctx, k->data, dt, &kt));
@@ -1104,44 +1172,46 @@ static bool adjacent(const Var &a, const Var &b) {
 mcb_status f_qkv_attention(const Var &x, const Var &wq, const Var &bq, const Var &wk, const Var &bk, const Var &wv, const Var &bv,
                            int64_t n, int64_t s, int64_t heads, bool causal, Var *out) {
     mcb_ctx *ctx = x->ctx;
-    if (!use_bf16(ctx) || x->data.shape.size() != 2) return MCB_UNSUPPORTED;
+    const int lp = lowp_dtype(ctx);
+    if (lp < 0 || x->data.shape.size() != 2) return MCB_UNSUPPORTED;
     if (getenv("MCB_UNFUSED_QKV")) return MCB_UNSUPPORTED; // test knob: run the composed ops instead
     int64_t d = x->data.shape[1], m = x->data.shape[0];
-    if (m != n * s || !mcb_flash_supported(d, heads, MCB_BF16) || !tc_shape_ok(m, 3 * d, d)) return MCB_UNSUPPORTED;
+    if (m != n * s || !mcb_flash_supported(d, heads, lp) || !tc_shape_ok(m, 3 * d, d)) return MCB_UNSUPPORTED;
     for (const Var &w : {wq, wk, wv})
         if (w->data.shape != std::vector<int64_t>{d, d}) return MCB_UNSUPPORTED;
     for (const Var &b : {bq, bk, bv})
         if (!b || b->data.shape != std::vector<int64_t>{d}) return MCB_UNSUPPORTED;
     if (!adjacent(wq, wk) || !adjacent(wk, wv) || !adjacent(bq, bk) || !adjacent(bk, bv)) return MCB_UNSUPPORTED;
     Tensor xb, wb, qkv, o, lse;
-    MCB_TRY(to_dtype(ctx, x->data, MCB_BF16, &xb));
-    MCB_TRY(bf16_of(wq, &wb)); // shadow of wq; wk and wv follow it in memory
-    MCB_TRY(new_tensor(ctx, MCB_BF16, {m, 3 * d}, &qkv));
-    MCB_TRY(new_tensor(ctx, MCB_BF16, {m, d}, &o));
+    MCB_TRY(to_dtype(ctx, x->data, lp, &xb));
+    MCB_TRY(lowp_of(wq, lp, &wb)); // shadow of wq; wk and wv follow it in memory
+    MCB_TRY(new_tensor(ctx, lp, {m, 3 * d}, &qkv));
+    MCB_TRY(new_tensor(ctx, lp, {m, d}, &o));
     MCB_TRY(new_tensor(ctx, MCB_F32, {n, heads, s}, &lse));
     {
         TcGemmParams p; // qkv[m, 3d] = x[m, d] * Wqkv[3d, d]^T + bqkv
+        p.in_dt = lp;
         p.a = xb.ptr; p.lda = d;
         p.b = wb.ptr; p.ldb = d;
-        p.d = qkv.ptr; p.out_dt = MCB_BF16; p.ldd = 3 * d;
+        p.d = qkv.ptr; p.out_dt = lp; p.ldd = 3 * d;
         p.bias = (const float *)bq->data.ptr;
         p.m = m; p.n = 3 * d; p.k = d;
         MCB_TRY(mcb_tc_gemm(ctx, p));
     }
-    const __nv_bfloat16 *qp = (const __nv_bfloat16 *)qkv.ptr;
+    const uint16_t *qp = (const uint16_t *)qkv.ptr;
     {
         ProfScope prof(ctx, MCB_PROF_ATTENTION, 4.0 * (double)n * heads * s * s * 64 * (causal ? 0.5 : 1.0), 8.0 * (double)m * d);
-        MCB_TRY(mcb_flash_forward(ctx, qp, qp + d, qp + 2 * d, o.ptr, (float *)lse.ptr, n, s, d, heads, causal, 3 * d, d));
+        MCB_TRY(mcb_flash_forward(ctx, qp, qp + d, qp + 2 * d, o.ptr, (float *)lse.ptr, n, s, d, heads, causal, 3 * d, d, lp));
     }
     Var xv = x, wqv = wq, wkv = wk, wvv = wv, bqv = bq, bkv = bk, bvv = bv;
     *out = apply(ctx, "QkvAttention", o, {x, wq, bq, wk, bk, wv, bv},
                  [=](const Tensor &g_in, std::vector<Tensor> &gi) -> mcb_status {
         Tensor g, dqkv, bias_part;
         int bias_done = 0;
-        MCB_TRY(to_dtype(ctx, g_in, MCB_BF16, &g));
-        MCB_TRY(new_tensor(ctx, MCB_BF16, {m, 3 * d}, &dqkv));
-        __nv_bfloat16 *dp = (__nv_bfloat16 *)dqkv.ptr;
-        const __nv_bfloat16 *qp = (const __nv_bfloat16 *)qkv.ptr; // the closure owns qkv, o and lse until backward has run
+        MCB_TRY(to_dtype(ctx, g_in, lp, &g));
+        MCB_TRY(new_tensor(ctx, lp, {m, 3 * d}, &dqkv));
+        uint16_t *dp = (uint16_t *)dqkv.ptr;
+        const uint16_t *qp = (const uint16_t *)qkv.ptr; // the closure owns qkv, o and lse until backward has run
         {
             ProfScope prof(ctx, MCB_PROF_ATTENTION, 10.0 * (double)n * heads * s * s * 64 * (causal ? 0.5 : 1.0), 16.0 * (double)m * d);
             // the attention backward kernels can leave per-warp column sums of dq | dk | dv (the rounded values they write): the bias
@@ -1149,12 +1219,13 @@ mcb_status f_qkv_attention(const Var &x, const Var &wq, const Var &bq, const Var
             const int64_t brows = getenv("MCB_UNFUSED_BWD") ? 0 : mcb_flash_bias_rows(n, s);
             if (brows > 0) MCB_TRY(new_tensor(ctx, MCB_F32, {brows, 3 * d}, &bias_part));
             MCB_TRY(mcb_flash_backward(ctx, qp, qp + d, qp + 2 * d, o.ptr, g.ptr, (const float *)lse.ptr, dp, dp + d, dp + 2 * d, n, s, d, heads,
-                                       causal, 3 * d, d, 3 * d, brows > 0 ? (float *)bias_part.ptr : nullptr, 3 * d, &bias_done));
+                                       causal, 3 * d, d, 3 * d, brows > 0 ? (float *)bias_part.ptr : nullptr, 3 * d, &bias_done, lp));
         }
         if (xv->requires_grad) {
-            int xdt = is_float(xv->data.dt) ? xv->data.dt : MCB_F32;
+            int xdt = xv->data.dt == lp ? lp : MCB_F32;
             MCB_TRY(new_tensor(ctx, xdt, xv->data.shape, &gi[0]));
             TcGemmParams p; // dx[m, d] = dqkv[m, 3d] * Wqkv[3d, d]
+            p.in_dt = lp;
             p.a = dqkv.ptr; p.lda = 3 * d;
             p.b = wb.ptr; p.b_mn_major = 1; p.ldb = d;
             p.d = gi[0].ptr; p.out_dt = xdt; p.ldd = d;
@@ -1191,6 +1262,7 @@ mcb_status f_qkv_attention(const Var &x, const Var &wq, const Var &bq, const Var
         }
         {
             TcGemmParams p; // dWqkv[3d, d] = dqkv^T[3d, m] * x[m, d]
+            p.in_dt = lp;
             p.a = dqkv.ptr; p.a_mn_major = 1; p.lda = 3 * d;
             p.b = xb.ptr; p.b_mn_major = 1; p.ldb = d;
             p.d = dw.ptr; p.out_dt = MCB_F32; p.ldd = d;
@@ -1203,7 +1275,7 @@ mcb_status f_qkv_attention(const Var &x, const Var &wq, const Var &bq, const Var
             MCB_TRY(mcb_tc_gemm(ctx, p));
         }
         if (bias_done) MCB_TRY(mcb_partial_sum_final(ctx, (const float *)bias_part.ptr, (int)bias_part.shape[0], 3 * d, (float *)db.ptr));
-        else MCB_TRY(mcb_col_sum(ctx, dqkv.ptr, MCB_BF16, m, 3 * d, (float *)db.ptr));
+        else MCB_TRY(mcb_col_sum(ctx, dqkv.ptr, lp, m, 3 * d, (float *)db.ptr));
         gi[1] = tw[0]; gi[3] = tw[1]; gi[5] = tw[2];
         gi[2] = tb[0]; gi[4] = tb[1]; gi[6] = tb[2];
         return MCB_OK;
@@ -1340,19 +1412,31 @@ void arena_release(Arena *a) {
     delete a;
 }
 
-mcb_status arena_refresh_shadow(Arena *a) {
+// The arena's 16-bit copy of the parameters in format `dt` (MCB_BF16 or MCB_F16; -1 keeps the current one):
+// rebuilt when it is stale or held the other format; the fused optimizer pass rewrites it in its current format.
+mcb_status arena_refresh_shadow(Arena *a, int dt) {
+    if (dt >= 0 && dt != a->shadow_dt) {
+        a->shadow_dt = dt;
+        a->shadow_valid = false;
+    }
     if (a->shadow_valid) return MCB_OK;
-    MCB_TRY(mcb_cast(a->ctx, a->p->p, MCB_F32, a->shadow->p, MCB_BF16, a->total));
+    MCB_TRY(mcb_cast(a->ctx, a->p->p, MCB_F32, a->shadow->p, a->shadow_dt, a->total));
     a->shadow_valid = true;
     return MCB_OK;
 }
 
 // ------------------------------------------------------------------ optimizers
-void zero_grad(const std::vector<Var> &params) {
+mcb_status zero_grad(const std::vector<Var> &params) {
+    Arena *last = nullptr;
     for (auto &p : params) {
         p->has_grad = false;
         p->grad = Tensor();
+        if (p->arena && p->arena != last) { // gradients of an open data-parallel round are dropped: wait for their all-reduces, start over
+            last = p->arena;
+            MCB_TRY(arena_abandon_round(last));
+        }
     }
+    return MCB_OK;
 }
 
 mcb_status AdamOpt::update(const std::vector<Var> &params, const float *inv_scale_dev, double inv_scale_host, const int32_t *skip,
@@ -1369,7 +1453,7 @@ mcb_status AdamOpt::update(const std::vector<Var> &params, const float *inv_scal
         double inv = inv_scale_host * arena_grad_divisor(a);
         int32_t t = a->step[0] + 1;
         MCB_TRY(mcb_opt_flat(ctx, kind, (float *)a->p->p, a->g->p, MCB_F32, (float *)a->m->p, (float *)a->v->p, a->shadow->p, a->total, lr, beta1,
-                             beta2, eps, weight_decay, t, inv, inv_scale_dev, skip, step_dev));
+                             beta2, eps, weight_decay, t, inv, inv_scale_dev, skip, step_dev, a->shadow_dt));
         // the step counter advances on the host even if the device skips: a skipped step must not
         // count, so callers that pass `skip` roll it back through rollback_step() once they know
         for (auto &s : a->step) s = t;
@@ -1385,8 +1469,8 @@ mcb_status AdamOpt::update(const std::vector<Var> &params, const float *inv_scal
             int32_t t = ++pa->step[i];
             int64_t off = pa->off[i];
             MCB_TRY(mcb_opt_flat(ctx, kind, (float *)pa->p->p + off, (float *)pa->g->p + off, MCB_F32, (float *)pa->m->p + off, (float *)pa->v->p + off,
-                                 (__nv_bfloat16 *)pa->shadow->p + off, pa->size[i], lr, beta1, beta2, eps, weight_decay, t,
-                                 inv_scale_host * arena_grad_divisor(pa), inv_scale_dev, skip, step_dev));
+                                 (uint16_t *)pa->shadow->p + off, pa->size[i], lr, beta1, beta2, eps, weight_decay, t,
+                                 inv_scale_host * arena_grad_divisor(pa), inv_scale_dev, skip, step_dev, pa->shadow_dt));
             continue;
         }
         AdamState &st = state[p.get()];

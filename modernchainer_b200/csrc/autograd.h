@@ -72,6 +72,7 @@ struct Arena {
     std::vector<int64_t> off, size;
     std::vector<int32_t> step;
     bool shadow_valid = false;
+    int shadow_dt = MCB_BF16; // format of the 16-bit copy: MCB_BF16 or MCB_F16
     std::vector<VarImpl *> claimed;
     // data-parallel bucketing (filled by mcb_dp_attach)
     std::vector<int> bucket_of;            // per parameter
@@ -115,14 +116,16 @@ mcb_status f_max_pool2d(const Var &x, int64_t kernel, int64_t stride, int64_t pa
 
 mcb_status arena_create(mcb_ctx *ctx, const std::vector<Var> &params, Arena **out);
 void arena_release(Arena *a);
-mcb_status arena_refresh_shadow(Arena *a);
+mcb_status arena_refresh_shadow(Arena *a, int dt = -1);
 // data-parallel hooks (dp.cu): a parameter's gradient is final / wait for the buckets in flight /
 // factor that turns the summed gradient into the mean over ranks
 mcb_status arena_grad_ready(Arena *a, int idx);
 mcb_status arena_wait_comm(Arena *a);
+mcb_status arena_backward_begin(Arena *a); // refuses a second backward pass before the optimizer on a data-parallel arena
+mcb_status arena_abandon_round(Arena *a);  // zero_grad while all-reduces of dropped gradients may still run
 double arena_grad_divisor(Arena *a);
 
-void zero_grad(const std::vector<Var> &params);
+mcb_status zero_grad(const std::vector<Var> &params);
 
 struct AdamState {
     Tensor m, v;

@@ -121,7 +121,8 @@ mcb_status mcb_var_backward(mcb_var *v) { return backward(v->v); }
 
 void mcb_set_grad_enabled(int32_t enabled) { set_grad_enabled(enabled != 0); }
 int32_t mcb_is_grad_enabled(void) { return grad_enabled() ? 1 : 0; }
-void mcb_set_autocast(int32_t dt) { set_autocast(dt == MCB_BF16 ? MCB_BF16 : -1); }
+void mcb_set_autocast(int32_t dt) { set_autocast((dt == MCB_BF16 || dt == MCB_F16) ? dt : -1); }
+int32_t mcb_get_autocast(void) { return autocast(); }
 
 mcb_status mcb_f_binary(int32_t op, mcb_var *a, mcb_var *b, mcb_var **out) {
     if (op < MCB_ADD || op > MCB_DIV) return mcb_fail(a->v->ctx, MCB_INVALID_ARGUMENT, "unknown binary op %d", op);
@@ -224,7 +225,7 @@ mcb_status mcb_arena_numel(mcb_arena *a, int64_t *out) {
 }
 
 mcb_status mcb_zero_grad(mcb_var **params, int32_t n) {
-    zero_grad(collect(params, n));
+    MCB_TRY(zero_grad(collect(params, n)));
     return MCB_OK;
 }
 
@@ -288,6 +289,11 @@ mcb_status mcb_clip_grad_norm(mcb_var **params, int32_t n, double max_norm, doub
     bool flat = a && ps.size() == a->vars.size();
     for (size_t i = 0; i < ps.size() && flat; ++i) flat = ps[i]->arena == a && ps[i]->arena_idx == (int)i && ps[i]->has_grad;
     std::vector<Tensor> keep;
+    // Gradients on a data-parallel arena are sums over the ranks until the optimizer folds 1 / world into its
+    // unscale factor; the norm reported and compared here is that of the mean, so N ranks at batch B clip like
+    // one rank at batch N * B.  (A list that mixes arenas with different divisors is not meaningful; the
+    // divisor of the first parameter's arena is used.)
+    const double mean_factor = a ? arena_grad_divisor(a) : 1.0;
     if (flat) {
         MCB_TRY(arena_wait_comm(a));
         ranges.push_back({(float *)a->g->p, a->total}); // padding between slots is zero
@@ -318,7 +324,7 @@ mcb_status mcb_clip_grad_norm(mcb_var **params, int32_t n, double max_norm, doub
         MCB_TRY(mcb_sumsq_partial(ctx, ranges[i].g, ranges[i].n, partial + at, blocks[i]));
         at += blocks[i];
     }
-    MCB_TRY(mcb_clip_finalize(ctx, partial, total_blocks, max_norm, clip));
+    MCB_TRY(mcb_clip_finalize(ctx, partial, total_blocks, max_norm, clip, mean_factor));
     for (auto &r : ranges) MCB_TRY(mcb_scale_by_clip(ctx, r.g, r.n, clip));
     if (norm_out) MCB_TRY(mcb_memcpy_d2h(ctx, norm_out, clip, sizeof(double)));
     return MCB_OK;

@@ -113,6 +113,9 @@ static inline size_t mcb_dtype_size(int dt) {
     }
 }
 
+// the 16-bit storage types a low-precision step can use
+static inline bool mcb_is_lp(int dt) { return dt == MCB_BF16 || dt == MCB_F16; }
+
 static inline int mcb_grid_for(mcb_ctx *ctx, int64_t work_items, int per_block, int max_waves = 8) {
     int64_t blocks = (work_items + per_block - 1) / per_block;
     int64_t cap = (int64_t)ctx->sm_count * max_waves;
@@ -209,6 +212,41 @@ template <> struct Elem<__nv_bfloat16> {
         raw.y = *reinterpret_cast<unsigned int *>(&b);
         reinterpret_cast<uint2 *>(p)[i4] = raw;
     }
+};
+
+template <> struct Elem<__half> {
+    static __device__ __forceinline__ float ld(const __half *p, int64_t i) { return __half2float(p[i]); }
+    static __device__ __forceinline__ void st(__half *p, int64_t i, float v) { p[i] = __float2half_rn(v); }
+    static __device__ __forceinline__ float4 ld4(const __half *p, int64_t i4) {
+        uint2 raw = reinterpret_cast<const uint2 *>(p)[i4];
+        float2 fa = __half22float2(*reinterpret_cast<__half2 *>(&raw.x)), fb = __half22float2(*reinterpret_cast<__half2 *>(&raw.y));
+        return make_float4(fa.x, fa.y, fb.x, fb.y);
+    }
+    static __device__ __forceinline__ void st4(__half *p, int64_t i4, float4 v) {
+        __half2 a = __floats2half2_rn(v.x, v.y), b = __floats2half2_rn(v.z, v.w);
+        uint2 raw;
+        raw.x = *reinterpret_cast<unsigned int *>(&a);
+        raw.y = *reinterpret_cast<unsigned int *>(&b);
+        reinterpret_cast<uint2 *>(p)[i4] = raw;
+    }
+};
+
+// The two 16-bit storage types (bf16, f16) as pairs packed in one 32-bit word, both rounded to
+// nearest even from f32: what the kernels that are written once for both formats use.
+template <typename T> struct Lp;
+template <> struct Lp<__nv_bfloat16> {
+    static __device__ __forceinline__ uint32_t pack2(float a, float b) {
+        __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+        return *reinterpret_cast<uint32_t *>(&v);
+    }
+    static __device__ __forceinline__ float2 unpack2(uint32_t w) { return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162 *>(&w)); }
+};
+template <> struct Lp<__half> {
+    static __device__ __forceinline__ uint32_t pack2(float a, float b) {
+        __half2 v = __floats2half2_rn(a, b);
+        return *reinterpret_cast<uint32_t *>(&v);
+    }
+    static __device__ __forceinline__ float2 unpack2(uint32_t w) { return __half22float2(*reinterpret_cast<__half2 *>(&w)); }
 };
 
 static inline bool mcb_aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }

@@ -199,29 +199,31 @@ template <typename S, typename D> __global__ void cast_kernel(const S *__restric
     long long stride = (long long)gridDim.x * blockDim.x;
     for (; i < n; i += stride) dst[i] = cast_one<S, D>(src[i]);
 }
-__global__ void cast_f32_bf16_vec_kernel(const float *__restrict__ src, __nv_bfloat16 *__restrict__ dst, long long n4) {
+template <typename T> __global__ void cast_f32_lp_vec_kernel(const float *__restrict__ src, T *__restrict__ dst, long long n4) {
     long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     long long stride = (long long)gridDim.x * blockDim.x;
-    for (; i < n4; i += stride) Elem<__nv_bfloat16>::st4(dst, i, reinterpret_cast<const float4 *>(src)[i]);
+    for (; i < n4; i += stride) Elem<T>::st4(dst, i, reinterpret_cast<const float4 *>(src)[i]);
 }
-__global__ void cast_bf16_f32_vec_kernel(const __nv_bfloat16 *__restrict__ src, float *__restrict__ dst, long long n4) {
+template <typename T> __global__ void cast_lp_f32_vec_kernel(const T *__restrict__ src, float *__restrict__ dst, long long n4) {
     long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     long long stride = (long long)gridDim.x * blockDim.x;
-    for (; i < n4; i += stride) reinterpret_cast<float4 *>(dst)[i] = Elem<__nv_bfloat16>::ld4(src, i);
+    for (; i < n4; i += stride) reinterpret_cast<float4 *>(dst)[i] = Elem<T>::ld4(src, i);
 }
 
 template <typename Fn>
 mcb_status launch_map1(mcb_ctx *ctx, const void *x, void *out, int64_t n, int32_t dt) {
     if (n == 0) return MCB_OK;
     int vec = mcb_aligned16(x) && mcb_aligned16(out);
-    ProfScope prof(ctx, MCB_PROF_ELEMENTWISE, 0.0, (double)n * 2.0 * (dt == MCB_BF16 ? 2.0 : 4.0));
+    ProfScope prof(ctx, MCB_PROF_ELEMENTWISE, 0.0, (double)n * 2.0 * (mcb_is_lp(dt) ? 2.0 : 4.0));
     int grid = mcb_grid_for(ctx, (n + 3) / 4, kThreads);
     if (dt == MCB_F32)
         map1_kernel<float, Fn><<<grid, kThreads, 0, ctx->stream>>>((const float *)x, (float *)out, n, vec);
     else if (dt == MCB_BF16)
         map1_kernel<__nv_bfloat16, Fn><<<grid, kThreads, 0, ctx->stream>>>((const __nv_bfloat16 *)x, (__nv_bfloat16 *)out, n, vec);
+    else if (dt == MCB_F16)
+        map1_kernel<__half, Fn><<<grid, kThreads, 0, ctx->stream>>>((const __half *)x, (__half *)out, n, vec);
     else
-        return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "activation supports f32 and bf16 storage");
+        return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "activation supports f32, bf16 and f16 storage");
     MCB_LAUNCHED(ctx);
     return MCB_OK;
 }
@@ -229,29 +231,31 @@ template <typename Fn>
 mcb_status launch_map2(mcb_ctx *ctx, const void *x, const void *g, void *out, int64_t n, int32_t dt) {
     if (n == 0) return MCB_OK;
     int vec = mcb_aligned16(x) && mcb_aligned16(g) && mcb_aligned16(out);
-    ProfScope prof(ctx, MCB_PROF_ELEMENTWISE, 0.0, (double)n * 3.0 * (dt == MCB_BF16 ? 2.0 : 4.0));
+    ProfScope prof(ctx, MCB_PROF_ELEMENTWISE, 0.0, (double)n * 3.0 * (mcb_is_lp(dt) ? 2.0 : 4.0));
     int grid = mcb_grid_for(ctx, (n + 3) / 4, kThreads);
     if (dt == MCB_F32)
         map2_kernel<float, Fn><<<grid, kThreads, 0, ctx->stream>>>((const float *)x, (const float *)g, (float *)out, n, vec);
     else if (dt == MCB_BF16)
         map2_kernel<__nv_bfloat16, Fn><<<grid, kThreads, 0, ctx->stream>>>((const __nv_bfloat16 *)x, (const __nv_bfloat16 *)g,
                                                                            (__nv_bfloat16 *)out, n, vec);
+    else if (dt == MCB_F16)
+        map2_kernel<__half, Fn><<<grid, kThreads, 0, ctx->stream>>>((const __half *)x, (const __half *)g, (__half *)out, n, vec);
     else
-        return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "activation backward supports f32 and bf16 storage");
+        return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "activation backward supports f32, bf16 and f16 storage");
     MCB_LAUNCHED(ctx);
     return MCB_OK;
 }
 
 // ---- a bf16 [rows, cols] result and its column sums in one pass (the bias gradient of a Linear
 // is the column sum of exactly the bf16 gradient its GEMMs read, so both come from one read).
-//   MODE 0: out = bf16(a)            a f32            (cast of an f32 gradient)
-//   MODE 1: out = gelu'(a) * b       a = pre-activation, b = upstream gradient, both bf16
+//   MODE 0: out = T(a)               a f32            (cast of an f32 gradient)
+//   MODE 1: out = gelu'(a) * b       a = pre-activation, b = upstream gradient, both of type T (bf16 or f16)
 //   MODE 2: out = relu'(a) * b
 // Lane l of a warp owns columns blockIdx.x*256 + 8l .. +7; the 8 warps of a block take rows
 // r0+w, r0+w+8, ...; partial[blockIdx.y][col] receives the block's sum of the ROUNDED outputs.
-template <int MODE>
+template <int MODE, typename T>
 __global__ void __launch_bounds__(256, 6) map_colsum_kernel(const void *__restrict__ a, const void *__restrict__ b,
-                                                         __nv_bfloat16 *__restrict__ out, long long rows, long long cols,
+                                                         T *__restrict__ out, long long rows, long long cols,
                                                          float *__restrict__ partial) {
     __shared__ float red[8][32][9];
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
@@ -274,23 +278,23 @@ __global__ void __launch_bounds__(256, 6) map_colsum_kernel(const void *__restri
                 v[0] = lo.x; v[1] = lo.y; v[2] = lo.z; v[3] = lo.w;
                 v[4] = hi.x; v[5] = hi.y; v[6] = hi.z; v[7] = hi.w;
             } else {
-                uint4 xa = *reinterpret_cast<const uint4 *>((const __nv_bfloat16 *)a + e);
-                uint4 xb = *reinterpret_cast<const uint4 *>((const __nv_bfloat16 *)b + e);
-                const __nv_bfloat162 *pa = reinterpret_cast<const __nv_bfloat162 *>(&xa);
-                const __nv_bfloat162 *pb = reinterpret_cast<const __nv_bfloat162 *>(&xb);
+                uint4 xa = *reinterpret_cast<const uint4 *>((const T *)a + e);
+                uint4 xb = *reinterpret_cast<const uint4 *>((const T *)b + e);
+                const uint32_t *pa = reinterpret_cast<const uint32_t *>(&xa);
+                const uint32_t *pb = reinterpret_cast<const uint32_t *>(&xb);
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    float2 fa = __bfloat1622float2(pa[j]), fb = __bfloat1622float2(pb[j]);
+                    float2 fa = Lp<T>::unpack2(pa[j]), fb = Lp<T>::unpack2(pb[j]);
                     v[2 * j] = MODE == 1 ? GeluBLowp::f(fa.x, fb.x) : ReluB::f(fa.x, fb.x);
                     v[2 * j + 1] = MODE == 1 ? GeluBLowp::f(fa.y, fb.y) : ReluB::f(fa.y, fb.y);
                 }
             }
             uint4 o;
-            __nv_bfloat162 *po = reinterpret_cast<__nv_bfloat162 *>(&o);
+            uint32_t *po = reinterpret_cast<uint32_t *>(&o);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                po[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
-                float2 back = __bfloat1622float2(po[j]);
+                po[j] = Lp<T>::pack2(v[2 * j], v[2 * j + 1]);
+                float2 back = Lp<T>::unpack2(po[j]);
                 acc[2 * j] += back.x;
                 acc[2 * j + 1] += back.y;
             }
@@ -375,14 +379,16 @@ mcb_status mcb_add_inplace(mcb_ctx *ctx, void *dst, const void *src, int64_t n, 
     MCB_CHECK_CTX(ctx);
     if (n == 0) return MCB_OK;
     int vec = mcb_aligned16(dst) && mcb_aligned16(src);
-    ProfScope prof(ctx, MCB_PROF_ELEMENTWISE, 0.0, (double)n * 3.0 * (dt == MCB_BF16 ? 2.0 : 4.0));
+    ProfScope prof(ctx, MCB_PROF_ELEMENTWISE, 0.0, (double)n * 3.0 * (mcb_is_lp(dt) ? 2.0 : 4.0));
     int grid = mcb_grid_for(ctx, (n + 3) / 4, kThreads);
     if (dt == MCB_F32)
         add_inplace_kernel<float><<<grid, kThreads, 0, ctx->stream>>>((float *)dst, (const float *)src, n, vec);
     else if (dt == MCB_BF16)
         add_inplace_kernel<__nv_bfloat16><<<grid, kThreads, 0, ctx->stream>>>((__nv_bfloat16 *)dst, (const __nv_bfloat16 *)src, n, vec);
+    else if (dt == MCB_F16)
+        add_inplace_kernel<__half><<<grid, kThreads, 0, ctx->stream>>>((__half *)dst, (const __half *)src, n, vec);
     else
-        return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "add_inplace supports f32 and bf16");
+        return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "add_inplace supports f32, bf16 and f16");
     MCB_LAUNCHED(ctx);
     return MCB_OK;
 }
@@ -426,7 +432,7 @@ mcb_status mcb_gelu(mcb_ctx *ctx, const void *x, void *out, int64_t n, int32_t d
 }
 mcb_status mcb_gelu_backward(mcb_ctx *ctx, const void *x, const void *g, void *out, int64_t n, int32_t dt) {
     MCB_CHECK_CTX(ctx);
-    if (dt == MCB_BF16) return launch_map2<GeluBLowp>(ctx, x, g, out, n, dt);
+    if (mcb_is_lp(dt)) return launch_map2<GeluBLowp>(ctx, x, g, out, n, dt);
     return launch_map2<GeluB>(ctx, x, g, out, n, dt);
 }
 
@@ -437,18 +443,24 @@ mcb_status mcb_cast(mcb_ctx *ctx, const void *src, int32_t src_dt, void *dst, in
     bool vec = (n & 3) == 0 && mcb_aligned16(src) && mcb_aligned16(dst);
     if (src_dt == MCB_F32 && dst_dt == MCB_BF16) {
         if (vec)
-            cast_f32_bf16_vec_kernel<<<mcb_grid_for(ctx, n / 4, kThreads), kThreads, 0, ctx->stream>>>((const float *)src, (__nv_bfloat16 *)dst, n / 4);
+            cast_f32_lp_vec_kernel<__nv_bfloat16><<<mcb_grid_for(ctx, n / 4, kThreads), kThreads, 0, ctx->stream>>>((const float *)src, (__nv_bfloat16 *)dst, n / 4);
         else
             cast_kernel<float, __nv_bfloat16><<<grid, kThreads, 0, ctx->stream>>>((const float *)src, (__nv_bfloat16 *)dst, n);
     } else if (src_dt == MCB_BF16 && dst_dt == MCB_F32) {
         if (vec)
-            cast_bf16_f32_vec_kernel<<<mcb_grid_for(ctx, n / 4, kThreads), kThreads, 0, ctx->stream>>>((const __nv_bfloat16 *)src, (float *)dst, n / 4);
+            cast_lp_f32_vec_kernel<__nv_bfloat16><<<mcb_grid_for(ctx, n / 4, kThreads), kThreads, 0, ctx->stream>>>((const __nv_bfloat16 *)src, (float *)dst, n / 4);
         else
             cast_kernel<__nv_bfloat16, float><<<grid, kThreads, 0, ctx->stream>>>((const __nv_bfloat16 *)src, (float *)dst, n);
     } else if (src_dt == MCB_F32 && dst_dt == MCB_F16) {
-        cast_kernel<float, __half><<<grid, kThreads, 0, ctx->stream>>>((const float *)src, (__half *)dst, n);
+        if (vec)
+            cast_f32_lp_vec_kernel<__half><<<mcb_grid_for(ctx, n / 4, kThreads), kThreads, 0, ctx->stream>>>((const float *)src, (__half *)dst, n / 4);
+        else
+            cast_kernel<float, __half><<<grid, kThreads, 0, ctx->stream>>>((const float *)src, (__half *)dst, n);
     } else if (src_dt == MCB_F16 && dst_dt == MCB_F32) {
-        cast_kernel<__half, float><<<grid, kThreads, 0, ctx->stream>>>((const __half *)src, (float *)dst, n);
+        if (vec)
+            cast_lp_f32_vec_kernel<__half><<<mcb_grid_for(ctx, n / 4, kThreads), kThreads, 0, ctx->stream>>>((const __half *)src, (float *)dst, n / 4);
+        else
+            cast_kernel<__half, float><<<grid, kThreads, 0, ctx->stream>>>((const __half *)src, (float *)dst, n);
     } else if (src_dt == MCB_F32 && dst_dt == MCB_F32) {
         cast_kernel<float, float><<<grid, kThreads, 0, ctx->stream>>>((const float *)src, (float *)dst, n);
     } else {
@@ -510,8 +522,10 @@ mcb_status mcb_mul_scalar_ptr(mcb_ctx *ctx, const void *x, const float *scalar, 
         mul_scalar_ptr_kernel<float><<<grid, kThreads, 0, ctx->stream>>>((const float *)x, scalar, (float *)out, n);
     else if (dt == MCB_BF16)
         mul_scalar_ptr_kernel<__nv_bfloat16><<<grid, kThreads, 0, ctx->stream>>>((const __nv_bfloat16 *)x, scalar, (__nv_bfloat16 *)out, n);
+    else if (dt == MCB_F16)
+        mul_scalar_ptr_kernel<__half><<<grid, kThreads, 0, ctx->stream>>>((const __half *)x, scalar, (__half *)out, n);
     else
-        return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "scalar multiply supports f32 and bf16");
+        return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "scalar multiply supports f32, bf16 and f16");
     MCB_LAUNCHED(ctx);
     return MCB_OK;
 }
@@ -524,6 +538,10 @@ mcb_status mcb_add_typed(mcb_ctx *ctx, const void *a, int32_t a_dt, const void *
     else if (a_dt == MCB_BF16 && b_dt == MCB_F32 && out_dt == MCB_F32) launch_add_typed<bf, float, float>(ctx, a, b, out, n);
     else if (a_dt == MCB_BF16 && b_dt == MCB_BF16 && out_dt == MCB_BF16) launch_add_typed<bf, bf, bf>(ctx, a, b, out, n);
     else if (a_dt == MCB_BF16 && b_dt == MCB_BF16 && out_dt == MCB_F32) launch_add_typed<bf, bf, float>(ctx, a, b, out, n);
+    else if (a_dt == MCB_F32 && b_dt == MCB_F16 && out_dt == MCB_F32) launch_add_typed<float, __half, float>(ctx, a, b, out, n);
+    else if (a_dt == MCB_F16 && b_dt == MCB_F32 && out_dt == MCB_F32) launch_add_typed<__half, float, float>(ctx, a, b, out, n);
+    else if (a_dt == MCB_F16 && b_dt == MCB_F16 && out_dt == MCB_F16) launch_add_typed<__half, __half, __half>(ctx, a, b, out, n);
+    else if (a_dt == MCB_F16 && b_dt == MCB_F16 && out_dt == MCB_F32) launch_add_typed<__half, __half, float>(ctx, a, b, out, n);
     else return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "typed add: unsupported storage combination");
     MCB_LAUNCHED(ctx);
     return MCB_OK;
@@ -533,9 +551,21 @@ bool mcb_map_colsum_supported(const void *a, const void *b, const void *out, int
     return cols > 0 && cols % 8 == 0 && mcb_aligned16(a) && (!b || mcb_aligned16(b)) && mcb_aligned16(out);
 }
 
+namespace {
+template <typename T>
+cudaError_t launch_map_colsum(mcb_ctx *ctx, int mode, dim3 grid, const void *a, const void *b, void *out, long long rows, long long cols, float *scratch) {
+    T *o = (T *)out;
+    if (mode == 0) return mcb_launch_dep(ctx, map_colsum_kernel<0, T>, grid, dim3(256), 0, a, b, o, rows, cols, scratch);
+    if (mode == 1) return mcb_launch_dep(ctx, map_colsum_kernel<1, T>, grid, dim3(256), 0, a, b, o, rows, cols, scratch);
+    return mcb_launch_dep(ctx, map_colsum_kernel<2, T>, grid, dim3(256), 0, a, b, o, rows, cols, scratch);
+}
+} // namespace
+
 mcb_status mcb_map_colsum(mcb_ctx *ctx, int mode, const void *a, const void *b, void *out_bf16, int64_t rows, int64_t cols,
-                          float *colsum_out) {
+                          float *colsum_out, int32_t lp_dt) {
     if (!mcb_map_colsum_supported(a, b, out_bf16, cols)) return MCB_UNSUPPORTED;
+    if (mode < 0 || mode > 2) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "map_colsum: unknown mode %d", mode);
+    if (!mcb_is_lp(lp_dt)) return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "map_colsum writes bf16 or f16");
     if (rows == 0) return mcb_memset(ctx, colsum_out, 0, sizeof(float) * cols);
     double bytes = (double)rows * cols * (mode == 0 ? 6.0 : 6.0);
     ProfScope prof(ctx, MCB_PROF_ELEMENTWISE, 0.0, bytes);
@@ -546,11 +576,8 @@ mcb_status mcb_map_colsum(mcb_ctx *ctx, int mode, const void *a, const void *b, 
     void *scratch;
     MCB_TRY(mcb_scratch(ctx, sizeof(float) * (size_t)splits * cols, &scratch));
     dim3 grid(chunks, splits);
-    __nv_bfloat16 *o = (__nv_bfloat16 *)out_bf16;
-    if (mode == 0) MCB_CUDA(ctx, mcb_launch_dep(ctx, map_colsum_kernel<0>, grid, dim3(256), 0, a, b, o, (long long)rows, (long long)cols, (float *)scratch));
-    else if (mode == 1) MCB_CUDA(ctx, mcb_launch_dep(ctx, map_colsum_kernel<1>, grid, dim3(256), 0, a, b, o, (long long)rows, (long long)cols, (float *)scratch));
-    else if (mode == 2) MCB_CUDA(ctx, mcb_launch_dep(ctx, map_colsum_kernel<2>, grid, dim3(256), 0, a, b, o, (long long)rows, (long long)cols, (float *)scratch));
-    else return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "map_colsum: unknown mode %d", mode);
+    if (lp_dt == MCB_BF16) MCB_CUDA(ctx, launch_map_colsum<__nv_bfloat16>(ctx, mode, grid, a, b, out_bf16, rows, cols, (float *)scratch));
+    else MCB_CUDA(ctx, launch_map_colsum<__half>(ctx, mode, grid, a, b, out_bf16, rows, cols, (float *)scratch));
     MCB_LAUNCHED(ctx);
     return mcb_partial_sum_final(ctx, (const float *)scratch, splits, cols, colsum_out);
 }

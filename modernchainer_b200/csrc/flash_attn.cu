@@ -229,7 +229,8 @@ __global__ void __launch_bounds__(kThreads) flash_fwd_kernel(const bf16 *__restr
 }
 
 // ------------------------------------------------------------------ backward: delta
-__global__ void flash_delta_kernel(const bf16 *__restrict__ O, const bf16 *__restrict__ dO, float *__restrict__ delta, int S, int DO, int DG, int H,
+template <typename T>
+__global__ void flash_delta_kernel(const T *__restrict__ O, const T *__restrict__ dO, float *__restrict__ delta, int S, int DO, int DG, int H,
                                    long long total_chunks) {
     // eight lanes per (sample, row, head): 16 bytes of O and of dO each, so a warp reads 512 contiguous bytes of a row
     dep_wait();
@@ -243,11 +244,11 @@ __global__ void flash_delta_kernel(const bf16 *__restrict__ O, const bf16 *__res
     const int h = chunk >> 3;
     const uint4 a = *reinterpret_cast<const uint4 *>(O + srow * DO + chunk * 8);
     const uint4 b = *reinterpret_cast<const uint4 *>(dO + srow * DG + chunk * 8);
-    const __nv_bfloat162 *pa = reinterpret_cast<const __nv_bfloat162 *>(&a), *pb = reinterpret_cast<const __nv_bfloat162 *>(&b);
+    const uint32_t *pa = reinterpret_cast<const uint32_t *>(&a), *pb = reinterpret_cast<const uint32_t *>(&b);
     float v = 0.0f;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        const float2 x = __bfloat1622float2(pa[i]), y = __bfloat1622float2(pb[i]);
+        const float2 x = Lp<T>::unpack2(pa[i]), y = Lp<T>::unpack2(pb[i]);
         v = fmaf(x.x, y.x, fmaf(x.y, y.y, v));
     }
     v += __shfl_xor_sync(0xffffffffu, v, 1);
@@ -416,19 +417,20 @@ __global__ void __launch_bounds__(kThreads) flash_dkv_kernel(const bf16 *__restr
 
 } // namespace
 
-bool mcb_flash_supported(int64_t dim, int64_t heads, int32_t dt) { return dt == MCB_BF16 && heads > 0 && dim == heads * HD; }
+bool mcb_flash_supported(int64_t dim, int64_t heads, int32_t dt) { return mcb_is_lp(dt) && heads > 0 && dim == heads * HD; }
 
 mcb_status mcb_flash_forward(mcb_ctx *ctx, const void *q, const void *k, const void *v, void *out, float *lse, int64_t n, int64_t seq,
-                             int64_t dim, int64_t heads, int32_t causal, int64_t ldi, int64_t ldo) {
+                             int64_t dim, int64_t heads, int32_t causal, int64_t ldi, int64_t ldo, int32_t dt) {
     if (ldi % 8 || ldo % 8) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "fused attention needs row pitches that are multiples of 8");
     if (!mcb_aligned16(q) || !mcb_aligned16(k) || !mcb_aligned16(v) || !mcb_aligned16(out) || (dim % 8))
         return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "fused attention needs 16-byte aligned tensors");
     if (n * heads > 65535) return mcb_fail(ctx, MCB_UNSUPPORTED, "fused attention: n * heads > 65535");
     // the tcgen05 / TMEM forward first; MCB_FLASH_LEGACY (test knob) keeps the mma.sync kernel
-    if (!getenv("MCB_FLASH_LEGACY")) {
-        mcb_status tc = mcb_flash_tc_forward(ctx, q, k, v, out, lse, n, seq, dim, heads, causal, ldi, ldo);
+    if (!getenv("MCB_FLASH_LEGACY") || dt == MCB_F16) {
+        mcb_status tc = mcb_flash_tc_forward(ctx, q, k, v, out, lse, n, seq, dim, heads, causal, ldi, ldo, dt);
         if (tc != MCB_UNSUPPORTED) return tc;
     }
+    if (dt != MCB_BF16) return mcb_fail(ctx, MCB_UNSUPPORTED, "fused f16 attention: shape outside the tensor-core kernel's range");
     float scale_log2 = (1.0f / sqrtf((float)HD)) * 1.4426950408889634f;
     dim3 grid((unsigned)((seq + TILE - 1) / TILE), (unsigned)(n * heads));
     if (causal)
@@ -441,7 +443,7 @@ mcb_status mcb_flash_forward(mcb_ctx *ctx, const void *q, const void *k, const v
 
 mcb_status mcb_flash_backward(mcb_ctx *ctx, const void *q, const void *k, const void *v, const void *out, const void *gout, const float *lse,
                               void *dq, void *dk, void *dv, int64_t n, int64_t seq, int64_t dim, int64_t heads, int32_t causal,
-                              int64_t ldi, int64_t ldo, int64_t ldg, float *bias_partial, int64_t bias_ld, int *bias_done) {
+                              int64_t ldi, int64_t ldo, int64_t ldg, float *bias_partial, int64_t bias_ld, int *bias_done, int32_t dt) {
     (void)dim;
     if (bias_done) *bias_done = 0;
     if (ldi % 8 || ldo % 8 || ldg % 8) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "fused attention needs row pitches that are multiples of 8");
@@ -453,18 +455,26 @@ mcb_status mcb_flash_backward(mcb_ctx *ctx, const void *q, const void *k, const 
     MCB_TRY(mcb_alloc(ctx, sizeof(float) * rows, &delta));
     {
         const long long chunks = rows * (HD / 8);
-        MCB_CUDA(ctx, mcb_launch_dep(ctx, flash_delta_kernel, dim3((unsigned)((chunks + 255) / 256)), dim3(256), 0, (const bf16 *)out, (const bf16 *)gout, (float *)delta, (int)seq, (int)ldo, (int)ldo, (int)heads, chunks)); // gout has the pitch of out; ldg is the pitch of dq / dk / dv
+        // gout has the pitch of out; ldg is the pitch of dq / dk / dv
+        if (dt == MCB_F16)
+            MCB_CUDA(ctx, mcb_launch_dep(ctx, flash_delta_kernel<__half>, dim3((unsigned)((chunks + 255) / 256)), dim3(256), 0, (const __half *)out, (const __half *)gout, (float *)delta, (int)seq, (int)ldo, (int)ldo, (int)heads, chunks));
+        else
+            MCB_CUDA(ctx, mcb_launch_dep(ctx, flash_delta_kernel<bf16>, dim3((unsigned)((chunks + 255) / 256)), dim3(256), 0, (const bf16 *)out, (const bf16 *)gout, (float *)delta, (int)seq, (int)ldo, (int)ldo, (int)heads, chunks));
     }
     ctx->launches++;
     // the tcgen05 / TMEM kernels first; MCB_FLASH_LEGACY (test knob) keeps the mma.sync pair
-    if (!getenv("MCB_FLASH_LEGACY") && !getenv("MCB_FLASH_LEGACY_BWD")) {
+    if ((!getenv("MCB_FLASH_LEGACY") && !getenv("MCB_FLASH_LEGACY_BWD")) || dt == MCB_F16) {
         mcb_status tc = mcb_flash_tc_backward(ctx, q, k, v, gout, lse, (const float *)delta, dq, dk, dv, n, seq, dim, heads, causal, ldi, ldo, ldg,
-                                              bias_partial, bias_ld);
+                                              bias_partial, bias_ld, dt);
         if (tc != MCB_UNSUPPORTED) {
             if (bias_done && bias_partial && tc == MCB_OK) *bias_done = 1;
             mcb_free(ctx, delta); // stream-ordered reuse
             return tc;
         }
+    }
+    if (dt != MCB_BF16) {
+        mcb_free(ctx, delta);
+        return mcb_fail(ctx, MCB_UNSUPPORTED, "fused f16 attention backward: shape outside the tensor-core kernel's range");
     }
     dim3 grid((unsigned)((seq + TILE - 1) / TILE), (unsigned)(n * heads));
     if (causal) {

@@ -46,6 +46,7 @@ struct FwdArgs {
     unsigned int *err;
 };
 
+template <bool F16>
 __global__ void __launch_bounds__(kThreads, 2)
 flash_tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                     const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o, FwdArgs args) {
@@ -140,8 +141,8 @@ flash_tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            constexpr unsigned idesc_s = make_idesc(BM, BN, 0, 0);   // S = Q K^T: both operands K-major
-            constexpr unsigned idesc_o = make_idesc(BM, HD, 0, 1);   // O += P V: V is [keys, hd] = MN-major B
+            constexpr unsigned idesc_s = make_idesc(BM, BN, 0, 0, F16);   // S = Q K^T: both operands K-major
+            constexpr unsigned idesc_o = make_idesc(BM, HD, 0, 1, F16);   // O += P V: V is [keys, hd] = MN-major B
             const unsigned tmem_s = tmem_base + kColS, tmem_o = tmem_base + kColO;
             const unsigned a_q = smem_u32(sQ);
             bool ok = mbar_wait(q_full, 0, abort_flag, args.err);
@@ -246,7 +247,7 @@ flash_tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 sq[2] += p[4] + p[5];
                 sq[3] += p[6] + p[7];
 #pragma unroll
-                for (int t = 0; t < 4; ++t) r[(e >> 1) + t] = pack_bf16(p[2 * t], p[2 * t + 1]); // packed pairs fill the front of the same registers
+                for (int t = 0; t < 4; ++t) r[(e >> 1) + t] = pack16<F16>(p[2 * t], p[2 * t + 1]); // packed pairs fill the front of the same registers
             }
             const float sum = (sq[0] + sq[1]) + (sq[2] + sq[3]);
             l += sum;
@@ -290,10 +291,10 @@ flash_tc_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
                     uint4 piece;
-                    piece.x = pack_bf16(__uint_as_float(o[q * 8]) * inv, __uint_as_float(o[q * 8 + 1]) * inv);
-                    piece.y = pack_bf16(__uint_as_float(o[q * 8 + 2]) * inv, __uint_as_float(o[q * 8 + 3]) * inv);
-                    piece.z = pack_bf16(__uint_as_float(o[q * 8 + 4]) * inv, __uint_as_float(o[q * 8 + 5]) * inv);
-                    piece.w = pack_bf16(__uint_as_float(o[q * 8 + 6]) * inv, __uint_as_float(o[q * 8 + 7]) * inv);
+                    piece.x = pack16<F16>(__uint_as_float(o[q * 8]) * inv, __uint_as_float(o[q * 8 + 1]) * inv);
+                    piece.y = pack16<F16>(__uint_as_float(o[q * 8 + 2]) * inv, __uint_as_float(o[q * 8 + 3]) * inv);
+                    piece.z = pack16<F16>(__uint_as_float(o[q * 8 + 4]) * inv, __uint_as_float(o[q * 8 + 5]) * inv);
+                    piece.w = pack16<F16>(__uint_as_float(o[q * 8 + 6]) * inv, __uint_as_float(o[q * 8 + 7]) * inv);
                     int chunk = c * 4 + q;
                     *(uint4 *)(stage + lane * 128 + ((chunk ^ (lane & 7)) << 4)) = piece;
                 }
@@ -332,14 +333,14 @@ EncodeTiledFn get_encode() {
 
 // [n][seq][cols] bf16 view with row pitch `ld` elements; boxes of {64 columns, box_rows rows, 1 sample}.
 // Rows past the end of a sample are zero-filled on load and dropped on store.
-mcb_status make_map3(mcb_ctx *ctx, CUtensorMap *map, const void *base, long long cols, long long seq, long long n, long long ld, int box_rows) {
+mcb_status make_map3(mcb_ctx *ctx, CUtensorMap *map, const void *base, long long cols, long long seq, long long n, long long ld, int box_rows, bool f16) {
     EncodeTiledFn enc = get_encode();
     if (!enc) return mcb_fail(ctx, MCB_BACKEND, "cuTensorMapEncodeTiled is not available from the driver");
     cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)seq, (cuuint64_t)n};
     cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)ld * 2 * (cuuint64_t)seq};
     cuuint32_t box[3] = {64u, (cuuint32_t)box_rows, 1u};
     cuuint32_t estr[3] = {1, 1, 1};
-    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+    CUresult r = enc(map, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return mcb_fail(ctx, MCB_BACKEND, "cuTensorMapEncodeTiled (attention) failed with %d", (int)r);
     return MCB_OK;
@@ -353,15 +354,17 @@ bool mcb_flash_tc_supported(int64_t dim, int64_t heads, int64_t ldi, int64_t ldo
 }
 
 mcb_status mcb_flash_tc_forward(mcb_ctx *ctx, const void *q, const void *k, const void *v, void *out, float *lse, int64_t n, int64_t seq,
-                                int64_t dim, int64_t heads, int32_t causal, int64_t ldi, int64_t ldo) {
+                                int64_t dim, int64_t heads, int32_t causal, int64_t ldi, int64_t ldo, int32_t dt) {
+    if (!mcb_is_lp(dt)) return MCB_UNSUPPORTED;
+    const bool f16 = dt == MCB_F16;
     if (!mcb_flash_tc_supported(dim, heads, ldi, ldo, q, k, v, out)) return MCB_UNSUPPORTED;
     if (n * heads > 65535) return MCB_UNSUPPORTED;
     if (n == 0 || seq == 0) return MCB_OK;
     CUtensorMap mq, mk, mv, mo;
-    MCB_TRY(make_map3(ctx, &mq, q, dim, seq, n, ldi, BM));
-    MCB_TRY(make_map3(ctx, &mk, k, dim, seq, n, ldi, BN));
-    MCB_TRY(make_map3(ctx, &mv, v, dim, seq, n, ldi, BN));
-    MCB_TRY(make_map3(ctx, &mo, out, dim, seq, n, ldo, 32));
+    MCB_TRY(make_map3(ctx, &mq, q, dim, seq, n, ldi, BM, f16));
+    MCB_TRY(make_map3(ctx, &mk, k, dim, seq, n, ldi, BN, f16));
+    MCB_TRY(make_map3(ctx, &mv, v, dim, seq, n, ldi, BN, f16));
+    MCB_TRY(make_map3(ctx, &mo, out, dim, seq, n, ldo, 32, f16));
     FwdArgs a;
     a.lse = lse;
     a.seq = (int)seq;
@@ -371,11 +374,13 @@ mcb_status mcb_flash_tc_forward(mcb_ctx *ctx, const void *q, const void *k, cons
     a.err = ctx->d_err;
     static bool attr_set = false;
     if (!attr_set) {
-        MCB_CUDA(ctx, cudaFuncSetAttribute(flash_tc_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+        MCB_CUDA(ctx, cudaFuncSetAttribute(flash_tc_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+        MCB_CUDA(ctx, cudaFuncSetAttribute(flash_tc_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
         attr_set = true;
     }
     dim3 grid((unsigned)((seq + BM - 1) / BM), (unsigned)(n * heads));
-    MCB_CUDA(ctx, mcb_launch_dep(ctx, flash_tc_fwd_kernel, grid, dim3(kThreads), kSmemBytes, mq, mk, mv, mo, a));
+    if (f16) MCB_CUDA(ctx, mcb_launch_dep(ctx, flash_tc_fwd_kernel<true>, grid, dim3(kThreads), kSmemBytes, mq, mk, mv, mo, a));
+    else MCB_CUDA(ctx, mcb_launch_dep(ctx, flash_tc_fwd_kernel<false>, grid, dim3(kThreads), kSmemBytes, mq, mk, mv, mo, a));
     MCB_LAUNCHED(ctx);
     return MCB_OK;
 }

@@ -45,7 +45,7 @@ struct BwdArgs {
     int bias_ld, dim;
 };
 
-template <int MODE>
+template <int MODE, bool F16>
 __global__ void __launch_bounds__(kThreads, 1)
 flash_tc_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                     const __grid_constant__ CUtensorMap map_do, const __grid_constant__ CUtensorMap map_out0,
@@ -148,8 +148,8 @@ flash_tc_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            constexpr unsigned idesc_sd = make_idesc(BT, BT, 0, 0);                       // S, dP: both operands K-major
-            constexpr unsigned idesc_acc = make_idesc(BT, HD, MODE == 0 ? 1 : 0, 1);      // MODE 0: A = P^T / dS^T (MN-major); MODE 1: A = dS (K-major)
+            constexpr unsigned idesc_sd = make_idesc(BT, BT, 0, 0, F16);                       // S, dP: both operands K-major
+            constexpr unsigned idesc_acc = make_idesc(BT, HD, MODE == 0 ? 1 : 0, 1, F16);      // MODE 0: A = P^T / dS^T (MN-major); MODE 1: A = dS (K-major)
             const unsigned x0 = smem_u32(sX0), x1 = smem_u32(sX1), p_addr = smem_u32(sP), ds_addr = smem_u32(sDS);
             bool ok = mbar_wait(x_full, 0, abort_flag, args.err);
             auto issue_sd = [&](int t) {
@@ -264,8 +264,8 @@ flash_tc_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 float p0 = fast_exp2(fmaf(__uint_as_float(s[e]), args.scale_log2, neg_l));
                 float p1 = fast_exp2(fmaf(__uint_as_float(s[e + 1]), args.scale_log2, neg_l));
                 float g0 = p0 * (__uint_as_float(d[e]) - dl), g1 = p1 * (__uint_as_float(d[e + 1]) - dl);
-                s[e >> 1] = pack_bf16(p0, p1);   // packed pairs fill the front of the same registers
-                d[e >> 1] = pack_bf16(g0, g1);
+                s[e >> 1] = pack16<F16>(p0, p1);   // packed pairs fill the front of the same registers
+                d[e >> 1] = pack16<F16>(g0, g1);
             }
             if (t > 0) { // the previous pair's MMAs may still be reading P / dS
                 ok = mbar_wait(mma_done, (unsigned)(t - 1) & 1u, abort_flag, args.err);
@@ -316,10 +316,10 @@ flash_tc_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
                     uint4 piece;
-                    piece.x = pack_bf16(__uint_as_float(o[q * 8]) * f, __uint_as_float(o[q * 8 + 1]) * f);
-                    piece.y = pack_bf16(__uint_as_float(o[q * 8 + 2]) * f, __uint_as_float(o[q * 8 + 3]) * f);
-                    piece.z = pack_bf16(__uint_as_float(o[q * 8 + 4]) * f, __uint_as_float(o[q * 8 + 5]) * f);
-                    piece.w = pack_bf16(__uint_as_float(o[q * 8 + 6]) * f, __uint_as_float(o[q * 8 + 7]) * f);
+                    piece.x = pack16<F16>(__uint_as_float(o[q * 8]) * f, __uint_as_float(o[q * 8 + 1]) * f);
+                    piece.y = pack16<F16>(__uint_as_float(o[q * 8 + 2]) * f, __uint_as_float(o[q * 8 + 3]) * f);
+                    piece.z = pack16<F16>(__uint_as_float(o[q * 8 + 4]) * f, __uint_as_float(o[q * 8 + 5]) * f);
+                    piece.w = pack16<F16>(__uint_as_float(o[q * 8 + 6]) * f, __uint_as_float(o[q * 8 + 7]) * f);
                     int chunk = c * 4 + q;
                     *(uint4 *)(stage + lane * 128 + ((chunk ^ (lane & 7)) << 4)) = piece;
                 }
@@ -332,8 +332,14 @@ flash_tc_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 const int rows_live = min(32, args.seq - (o0 + wq * 32));
                 for (int rr = 0; rr < rows_live; ++rr) {
                     const unsigned w2 = *(const unsigned *)(stage + rr * 128 + (((lane >> 2) ^ (rr & 7)) << 4) + (lane & 3) * 4);
-                    c0 += __uint_as_float(w2 << 16);
-                    c1 += __uint_as_float(w2 & 0xFFFF0000u);
+                    if (F16) {
+                        const float2 pr = __half22float2(*reinterpret_cast<const __half2 *>(&w2));
+                        c0 += pr.x;
+                        c1 += pr.y;
+                    } else {
+                        c0 += __uint_as_float(w2 << 16);
+                        c1 += __uint_as_float(w2 & 0xFFFF0000u);
+                    }
                 }
                 const int which = MODE == 1 ? 0 : (hh == 1 ? 1 : 2); // dq, dk, dv column block of the packed gradient
                 float *dst = args.bias_partial + ((size_t)(n * tiles + own) * 4 + wq) * args.bias_ld + which * args.dim + h * HD + 2 * lane;
@@ -369,14 +375,14 @@ EncodeTiledFn get_encode() {
 }
 
 // [n][seq][cols] bf16 view with row pitch `ld` elements; boxes of {64 columns, box_rows rows, 1 sample}
-mcb_status make_map3(mcb_ctx *ctx, CUtensorMap *map, const void *base, long long cols, long long seq, long long n, long long ld, int box_rows) {
+mcb_status make_map3(mcb_ctx *ctx, CUtensorMap *map, const void *base, long long cols, long long seq, long long n, long long ld, int box_rows, bool f16) {
     EncodeTiledFn enc = get_encode();
     if (!enc) return mcb_fail(ctx, MCB_BACKEND, "cuTensorMapEncodeTiled is not available from the driver");
     cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)seq, (cuuint64_t)n};
     cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)ld * 2 * (cuuint64_t)seq};
     cuuint32_t box[3] = {64u, (cuuint32_t)box_rows, 1u};
     cuuint32_t estr[3] = {1, 1, 1};
-    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+    CUresult r = enc(map, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return mcb_fail(ctx, MCB_BACKEND, "cuTensorMapEncodeTiled (attention backward) failed with %d", (int)r);
     return MCB_OK;
@@ -388,20 +394,22 @@ mcb_status make_map3(mcb_ctx *ctx, CUtensorMap *map, const void *base, long long
 // MCB_UNSUPPORTED (nothing launched) outside the kernel's range.
 mcb_status mcb_flash_tc_backward(mcb_ctx *ctx, const void *q, const void *k, const void *v, const void *gout, const float *lse, const float *delta,
                                  void *dq, void *dk, void *dv, int64_t n, int64_t seq, int64_t dim, int64_t heads, int32_t causal, int64_t ldi,
-                                 int64_t ldo, int64_t ldg, float *bias_partial, int64_t bias_ld) {
+                                 int64_t ldo, int64_t ldg, float *bias_partial, int64_t bias_ld, int32_t dt) {
+    if (!mcb_is_lp(dt)) return MCB_UNSUPPORTED;
+    const bool f16 = dt == MCB_F16;
     if (heads <= 0 || dim != heads * HD || ldi % 8 || ldo % 8 || ldg % 8 || n * heads > 65535) return MCB_UNSUPPORTED;
     if (!mcb_aligned16(q) || !mcb_aligned16(k) || !mcb_aligned16(v) || !mcb_aligned16(gout) || !mcb_aligned16(dq) || !mcb_aligned16(dk) ||
         !mcb_aligned16(dv))
         return MCB_UNSUPPORTED;
     if (n == 0 || seq == 0) return MCB_OK;
     CUtensorMap mq, mk, mv, mdo, mdq, mdk, mdv;
-    MCB_TRY(make_map3(ctx, &mq, q, dim, seq, n, ldi, BT));
-    MCB_TRY(make_map3(ctx, &mk, k, dim, seq, n, ldi, BT));
-    MCB_TRY(make_map3(ctx, &mv, v, dim, seq, n, ldi, BT));
-    MCB_TRY(make_map3(ctx, &mdo, gout, dim, seq, n, ldo, BT));
-    MCB_TRY(make_map3(ctx, &mdq, dq, dim, seq, n, ldg, 32));
-    MCB_TRY(make_map3(ctx, &mdk, dk, dim, seq, n, ldg, 32));
-    MCB_TRY(make_map3(ctx, &mdv, dv, dim, seq, n, ldg, 32));
+    MCB_TRY(make_map3(ctx, &mq, q, dim, seq, n, ldi, BT, f16));
+    MCB_TRY(make_map3(ctx, &mk, k, dim, seq, n, ldi, BT, f16));
+    MCB_TRY(make_map3(ctx, &mv, v, dim, seq, n, ldi, BT, f16));
+    MCB_TRY(make_map3(ctx, &mdo, gout, dim, seq, n, ldo, BT, f16));
+    MCB_TRY(make_map3(ctx, &mdq, dq, dim, seq, n, ldg, 32, f16));
+    MCB_TRY(make_map3(ctx, &mdk, dk, dim, seq, n, ldg, 32, f16));
+    MCB_TRY(make_map3(ctx, &mdv, dv, dim, seq, n, ldg, 32, f16));
     BwdArgs a;
     a.lse = lse;
     a.delta = delta;
@@ -416,14 +424,18 @@ mcb_status mcb_flash_tc_backward(mcb_ctx *ctx, const void *q, const void *k, con
     a.dim = (int)dim;
     static bool attr_set = false;
     if (!attr_set) {
-        MCB_CUDA(ctx, cudaFuncSetAttribute(flash_tc_bwd_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-        MCB_CUDA(ctx, cudaFuncSetAttribute(flash_tc_bwd_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+        MCB_CUDA(ctx, cudaFuncSetAttribute(flash_tc_bwd_kernel<0, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+        MCB_CUDA(ctx, cudaFuncSetAttribute(flash_tc_bwd_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+        MCB_CUDA(ctx, cudaFuncSetAttribute(flash_tc_bwd_kernel<0, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+        MCB_CUDA(ctx, cudaFuncSetAttribute(flash_tc_bwd_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
         attr_set = true;
     }
     dim3 grid((unsigned)((seq + BT - 1) / BT), (unsigned)(n * heads));
-    MCB_CUDA(ctx, mcb_launch_dep(ctx, flash_tc_bwd_kernel<0>, grid, dim3(kThreads), kSmemBytes, mq, mk, mv, mdo, mdv, mdk, a));
+    if (f16) MCB_CUDA(ctx, mcb_launch_dep(ctx, flash_tc_bwd_kernel<0, true>, grid, dim3(kThreads), kSmemBytes, mq, mk, mv, mdo, mdv, mdk, a));
+    else MCB_CUDA(ctx, mcb_launch_dep(ctx, flash_tc_bwd_kernel<0, false>, grid, dim3(kThreads), kSmemBytes, mq, mk, mv, mdo, mdv, mdk, a));
     MCB_LAUNCHED(ctx);
-    MCB_CUDA(ctx, mcb_launch_dep(ctx, flash_tc_bwd_kernel<1>, grid, dim3(kThreads), kSmemBytes, mq, mk, mv, mdo, mdq, mdq, a));
+    if (f16) MCB_CUDA(ctx, mcb_launch_dep(ctx, flash_tc_bwd_kernel<1, true>, grid, dim3(kThreads), kSmemBytes, mq, mk, mv, mdo, mdq, mdq, a));
+    else MCB_CUDA(ctx, mcb_launch_dep(ctx, flash_tc_bwd_kernel<1, false>, grid, dim3(kThreads), kSmemBytes, mq, mk, mv, mdo, mdq, mdq, a));
     MCB_LAUNCHED(ctx);
     return MCB_OK;
 }

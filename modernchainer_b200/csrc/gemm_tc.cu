@@ -41,7 +41,8 @@ struct TcArgs {
     void *d_pre;
     const float *bias;
     long long m, n, k, ldd;
-    int out_bf16, accumulate, act, split_k, vec_red;
+    int out_bf16, accumulate, act, split_k, vec_red; // out_bf16: the output is a 16-bit type (bf16, or f16 when `f16` is set)
+    int f16;                                          // operands and 16-bit outputs are IEEE f16 instead of bf16
     int tma_out;  // 1: the epilogue stages output boxes in shared memory and TMA writes (or adds) them
     int bias_vec; // bias base is 16-byte aligned
     int a_mn, b_mn;
@@ -280,9 +281,23 @@ __device__ __forceinline__ void bulk_wait_read1() { asm volatile("cp.async.bulk.
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
-__device__ __forceinline__ unsigned pack_bf16(float a, float b) {
+// two f32 values rounded to nearest even and packed as bf16 (F16 = false) or f16 (F16 = true)
+template <bool F16> __device__ __forceinline__ unsigned pack16(float a, float b) {
+    if (F16) {
+        __half2 p = __floats2half2_rn(a, b);
+        return *(unsigned *)&p;
+    }
     __nv_bfloat162 p = __floats2bfloat162_rn(a, b);
     return *(unsigned *)&p;
+}
+template <bool F16, int N> __device__ __forceinline__ void pack_row(const float (&v)[N], unsigned (&w)[N / 2]) {
+#pragma unroll
+    for (int j = 0; j < N / 2; ++j) w[j] = pack16<F16>(v[2 * j], v[2 * j + 1]);
+}
+// the branch on the format is taken once per row chunk, outside the conversion loop
+template <int N> __device__ __forceinline__ void pack_row_any(const float (&v)[N], unsigned (&w)[N / 2], int f16) {
+    if (f16) pack_row<true, N>(v, w);
+    else pack_row<false, N>(v, w);
 }
 
 // Per-warp staging ring of two (or four) 4 KB boxes.  `issued` counts the boxes handed to TMA so far.
@@ -600,11 +615,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         }
                         if (args.d_pre) {
                             unsigned char *box = ring_acquire(rg, lane, args.ring);
+                            unsigned w[32];
+                            pack_row_any<64>(v, w, args.f16);
 #pragma unroll
-                            for (int j = 0; j < 8; ++j)
-                                ring_put(box, lane, j,
-                                         make_uint4(pack_bf16(v[8 * j], v[8 * j + 1]), pack_bf16(v[8 * j + 2], v[8 * j + 3]),
-                                                    pack_bf16(v[8 * j + 4], v[8 * j + 5]), pack_bf16(v[8 * j + 6], v[8 * j + 7])));
+                            for (int j = 0; j < 8; ++j) ring_put(box, lane, j, make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]));
                             ring_submit(rg, box, &map_pre, (int)col0, y0, false, lane);
                         }
                         if (args.act == MCB_ACT_GELU) {
@@ -615,11 +629,12 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                             for (int j = 0; j < 64; ++j) v[j] = v[j] > 0.0f ? v[j] : 0.0f;
                         }
                         unsigned char *box = ring_acquire(rg, lane, args.ring);
+                        {
+                            unsigned w[32];
+                            pack_row_any<64>(v, w, args.f16);
 #pragma unroll
-                        for (int j = 0; j < 8; ++j)
-                            ring_put(box, lane, j,
-                                     make_uint4(pack_bf16(v[8 * j], v[8 * j + 1]), pack_bf16(v[8 * j + 2], v[8 * j + 3]),
-                                                pack_bf16(v[8 * j + 4], v[8 * j + 5]), pack_bf16(v[8 * j + 6], v[8 * j + 7])));
+                            for (int j = 0; j < 8; ++j) ring_put(box, lane, j, make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]));
+                        }
                         ring_submit(rg, box, &map_d, (int)col0, y0, false, lane);
                     }
                 } else {
@@ -700,18 +715,14 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         __nv_bfloat16 *dst = (__nv_bfloat16 *)args.d + row * args.ldd + col0;
                         __nv_bfloat16 *pre = args.d_pre ? (__nv_bfloat16 *)args.d_pre + row * args.ldd + col0 : nullptr;
                         if (pre) {
+                            unsigned w[16];
+                            pack_row_any<32>(v, w, args.f16);
                             if (full) {
 #pragma unroll
-                                for (int j = 0; j < 32; j += 8) {
-                                    uint4 pk;
-                                    __nv_bfloat162 p0 = __floats2bfloat162_rn(v[j], v[j + 1]), p1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
-                                    __nv_bfloat162 p2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]), p3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
-                                    pk.x = *(unsigned *)&p0; pk.y = *(unsigned *)&p1; pk.z = *(unsigned *)&p2; pk.w = *(unsigned *)&p3;
-                                    *(uint4 *)(pre + j) = pk;
-                                }
+                                for (int j = 0; j < 4; ++j) *(uint4 *)(pre + 8 * j) = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
                             } else {
                                 for (int j = 0; j < 32; ++j)
-                                    if (col0 + j < args.n) pre[j] = __float2bfloat16_rn(v[j]);
+                                    if (col0 + j < args.n) ((unsigned short *)pre)[j] = (unsigned short)(w[j >> 1] >> ((j & 1) * 16));
                             }
                         }
                         if (args.act == MCB_ACT_GELU) {
@@ -721,18 +732,14 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
                             for (int j = 0; j < 32; ++j) v[j] = v[j] > 0.0f ? v[j] : 0.0f;
                         }
+                        unsigned w[16];
+                        pack_row_any<32>(v, w, args.f16);
                         if (full) {
 #pragma unroll
-                            for (int j = 0; j < 32; j += 8) {
-                                uint4 pk;
-                                __nv_bfloat162 p0 = __floats2bfloat162_rn(v[j], v[j + 1]), p1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
-                                __nv_bfloat162 p2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]), p3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
-                                pk.x = *(unsigned *)&p0; pk.y = *(unsigned *)&p1; pk.z = *(unsigned *)&p2; pk.w = *(unsigned *)&p3;
-                                *(uint4 *)(dst + j) = pk;
-                            }
+                            for (int j = 0; j < 4; ++j) *(uint4 *)(dst + 8 * j) = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
                         } else {
                             for (int j = 0; j < 32; ++j)
-                                if (col0 + j < args.n) dst[j] = __float2bfloat16_rn(v[j]);
+                                if (col0 + j < args.n) ((unsigned short *)dst)[j] = (unsigned short)(w[j >> 1] >> ((j & 1) * 16));
                         }
                     } else {
                         float *dst = (float *)args.d + row * args.ldd + col0;
@@ -796,14 +803,14 @@ EncodeTiledFn get_encode() {
 
 // 2-D bf16 tensor map: inner (contiguous) extent `inner`, outer extent `outer`, row pitch `ld` elements
 mcb_status make_map(mcb_ctx *ctx, CUtensorMap *map, const void *base, long long inner, long long outer, long long ld,
-                    int box_inner, int box_outer) {
+                    int box_inner, int box_outer, bool f16 = false) {
     EncodeTiledFn enc = get_encode();
     if (!enc) return mcb_fail(ctx, MCB_BACKEND, "cuTensorMapEncodeTiled is not available from the driver");
     cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
     cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
     cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
     cuuint32_t estr[2] = {1, 1};
-    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims, strides, box, estr,
+    CUresult r = enc(map, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims, strides, box, estr,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return mcb_fail(ctx, MCB_BACKEND, "cuTensorMapEncodeTiled failed with %d", (int)r);
@@ -811,7 +818,7 @@ mcb_status make_map(mcb_ctx *ctx, CUtensorMap *map, const void *base, long long 
 }
 
 // output matrix [m, n] with row pitch ldd, written in boxes of {128 bytes, 32 rows}
-mcb_status make_out_map(mcb_ctx *ctx, CUtensorMap *map, const void *base, bool bf16, long long n, long long m, long long ldd) {
+mcb_status make_out_map(mcb_ctx *ctx, CUtensorMap *map, const void *base, bool bf16, long long n, long long m, long long ldd, bool f16 = false) {
     EncodeTiledFn enc = get_encode();
     if (!enc) return mcb_fail(ctx, MCB_BACKEND, "cuTensorMapEncodeTiled is not available from the driver");
     const int es = bf16 ? 2 : 4;
@@ -819,7 +826,7 @@ mcb_status make_out_map(mcb_ctx *ctx, CUtensorMap *map, const void *base, bool b
     cuuint64_t strides[1] = {(cuuint64_t)ldd * es};
     cuuint32_t box[2] = {(cuuint32_t)(128 / es), 32u};
     cuuint32_t estr[2] = {1, 1};
-    CUresult r = enc(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void *>(base), dims,
+    CUresult r = enc(map, bf16 ? (f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16) : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void *>(base), dims,
                      strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return mcb_fail(ctx, MCB_BACKEND, "cuTensorMapEncodeTiled (output) failed with %d", (int)r);
@@ -856,22 +863,25 @@ template <int BN, bool PAIR> mcb_status launch(mcb_ctx *ctx, const TcGemmParams 
     using C = Cfg<BN, PAIR>;
     constexpr int kTileM = PAIR ? 2 * BM : BM;
     CUtensorMap map_a, map_b;
-    if (!p.a_mn_major) MCB_TRY(make_map(ctx, &map_a, p.a, p.k, p.m, p.lda, BK, BM));
-    else MCB_TRY(make_map(ctx, &map_a, p.a, p.m, p.k, p.lda, 64, BK));
-    if (!p.b_mn_major) MCB_TRY(make_map(ctx, &map_b, p.b, p.k, p.n, p.ldb, BK, C::kBRows));
-    else MCB_TRY(make_map(ctx, &map_b, p.b, p.n, p.k, p.ldb, 64, BK));
+    const bool f16 = p.in_dt == MCB_F16;
+    if (!p.a_mn_major) MCB_TRY(make_map(ctx, &map_a, p.a, p.k, p.m, p.lda, BK, BM, f16));
+    else MCB_TRY(make_map(ctx, &map_a, p.a, p.m, p.k, p.lda, 64, BK, f16));
+    if (!p.b_mn_major) MCB_TRY(make_map(ctx, &map_b, p.b, p.k, p.n, p.ldb, BK, C::kBRows, f16));
+    else MCB_TRY(make_map(ctx, &map_b, p.b, p.n, p.k, p.ldb, 64, BK, f16));
     TcArgs a;
     a.d = p.d;
     a.d_pre = p.d_pre;
     a.bias = p.bias;
     a.m = p.m; a.n = p.n; a.k = p.k; a.ldd = p.ldd;
-    a.out_bf16 = p.out_dt == MCB_BF16;
+    a.out_bf16 = mcb_is_lp(p.out_dt);
+    a.f16 = f16;
     a.accumulate = p.accumulate;
     a.vec_red = (p.ldd % 4 == 0) && mcb_aligned16(p.d);
     a.act = p.act;
     a.a_mn = p.a_mn_major;
     a.b_mn = p.b_mn_major;
-    a.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(p.a_mn_major ? 1 : 0) << 15) |
+    // kind::f16 instruction descriptor: f32 accumulator (bit 4); operand formats in bits 7-9 (A) and 10-12 (B): 0 = f16, 1 = bf16
+    a.idesc = (1u << 4) | (f16 ? 0u : ((1u << 7) | (1u << 10))) | ((unsigned)(p.a_mn_major ? 1 : 0) << 15) |
               ((unsigned)(p.b_mn_major ? 1 : 0) << 16) | ((unsigned)(BN >> 3) << 17) | ((unsigned)(kTileM >> 4) << 24);
     a.m_tiles = (int)((p.m + kTileM - 1) / kTileM);
     a.n_tiles = (int)((p.n + BN - 1) / BN);
@@ -913,8 +923,8 @@ template <int BN, bool PAIR> mcb_status launch(mcb_ctx *ctx, const TcGemmParams 
     memset(&map_d, 0, sizeof(map_d));
     memset(&map_pre, 0, sizeof(map_pre));
     if (a.tma_out) {
-        MCB_TRY(make_out_map(ctx, &map_d, p.d, a.out_bf16, p.n, p.m, p.ldd));
-        if (p.d_pre) MCB_TRY(make_out_map(ctx, &map_pre, p.d_pre, a.out_bf16, p.n, p.m, p.ldd));
+        MCB_TRY(make_out_map(ctx, &map_d, p.d, a.out_bf16, p.n, p.m, p.ldd, f16));
+        if (p.d_pre) MCB_TRY(make_out_map(ctx, &map_pre, p.d_pre, a.out_bf16, p.n, p.m, p.ldd, f16));
     }
     long long work = (long long)a.m_tiles * a.n_tiles * split;
     static bool attr_set = false;
@@ -1032,7 +1042,10 @@ template <int BN, bool PAIR> mcb_status launch(mcb_ctx *ctx, const TcGemmParams 
         const long long total4 = (p.m - r.row0) * ((r.col1 - r.col0) >> 2);
         const dim3 grid((unsigned)mcb_grid_for(ctx, total4, 256, 4)), block(256);
         cudaError_t e;
-        if (a.out_bf16)
+        if (a.out_bf16 && f16)
+            e = mcb_launch_dep(ctx, tc_split_tail_finish_kernel<__half>, grid, block, 0, (const float *)ws, (__half *)p.d, p.bias, p.act, r.row0,
+                               (long long)p.m, r.col0, r.col1, (long long)p.ldd);
+        else if (a.out_bf16)
             e = mcb_launch_dep(ctx, tc_split_tail_finish_kernel<__nv_bfloat16>, grid, block, 0, (const float *)ws, (__nv_bfloat16 *)p.d, p.bias, p.act,
                                r.row0, (long long)p.m, r.col0, r.col1, (long long)p.ldd);
         else
@@ -1053,18 +1066,19 @@ template <int BN, bool PAIR> mcb_status launch(mcb_ctx *ctx, const TcGemmParams 
 mcb_status mcb_tc_gemm(mcb_ctx *ctx, const TcGemmParams &p) {
     if (p.m == 0 || p.n == 0) return MCB_OK;
     ProfScope prof(ctx, MCB_PROF_GEMM_TC, 2.0 * (double)p.m * (double)p.n * (double)p.k,
-                   2.0 * ((double)p.m * p.k + (double)p.n * p.k) + (double)p.m * p.n * (p.out_dt == MCB_BF16 ? 2.0 : 4.0));
+                   2.0 * ((double)p.m * p.k + (double)p.n * p.k) + (double)p.m * p.n * (mcb_is_lp(p.out_dt) ? 2.0 : 4.0));
     if (p.k == 0) {
         if (p.accumulate) return MCB_OK;
         return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "tensor-core GEMM needs k > 0");
     }
     if ((p.lda % 8) || (p.ldb % 8) || !mcb_aligned16(p.a) || !mcb_aligned16(p.b))
         return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "tensor-core GEMM operands need 16-byte aligned bases and row pitches that are multiples of 8 elements");
-    if (p.out_dt != MCB_BF16 && p.out_dt != MCB_F32) return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "GEMM output must be bf16 or f32");
+    if (!mcb_is_lp(p.in_dt)) return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "tensor-core GEMM operands must be bf16 or f16");
+    if (p.out_dt != p.in_dt && p.out_dt != MCB_F32) return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "GEMM output must be f32 or the operands' 16-bit type");
     if (p.accumulate && p.out_dt != MCB_F32) return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "accumulating GEMM output must be f32");
     if (p.split_k > 1 && !p.accumulate) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "split-K needs the accumulating epilogue");
     // vector stores in the epilogue need ldd and d aligned; otherwise the scalar tail path is used per row
-    if ((p.out_dt == MCB_BF16 && ((p.ldd % 8) || !mcb_aligned16(p.d))) || (p.out_dt == MCB_F32 && !p.accumulate && ((p.ldd % 4) || !mcb_aligned16(p.d))))
+    if ((mcb_is_lp(p.out_dt) && ((p.ldd % 8) || !mcb_aligned16(p.d))) || (p.out_dt == MCB_F32 && !p.accumulate && ((p.ldd % 4) || !mcb_aligned16(p.d))))
         return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "GEMM output needs a 16-byte aligned base and row pitch");
     int bn = p.bn, split = p.split_k < 1 ? 1 : p.split_k;
     if (const char *force = getenv("MCB_TC_BN")) bn = atoi(force); // tuning knob: force the tile width
@@ -1178,8 +1192,15 @@ void mcb_tc_plan(mcb_ctx *ctx, int64_t m, int64_t n, int64_t k, bool allow_split
 extern "C" mcb_status mcb_gemm_bf16(mcb_ctx *ctx, const void *a, int32_t a_mn_major, const void *b, int32_t b_mn_major,
                                     void *d, int32_t out_dt, const float *bias, int64_t m, int64_t n, int64_t k,
                                     int32_t accumulate, int32_t split_k) {
+    return mcb_gemm_lowp(ctx, MCB_BF16, a, a_mn_major, b, b_mn_major, d, out_dt, bias, m, n, k, accumulate, split_k);
+}
+
+extern "C" mcb_status mcb_gemm_lowp(mcb_ctx *ctx, int32_t in_dt, const void *a, int32_t a_mn_major, const void *b, int32_t b_mn_major,
+                                    void *d, int32_t out_dt, const float *bias, int64_t m, int64_t n, int64_t k,
+                                    int32_t accumulate, int32_t split_k) {
     MCB_CHECK_CTX(ctx);
     TcGemmParams p;
+    p.in_dt = in_dt;
     p.a = a; p.b = b; p.d = d; p.bias = bias;
     p.a_mn_major = a_mn_major; p.b_mn_major = b_mn_major;
     p.out_dt = out_dt;

@@ -38,6 +38,7 @@ struct LnBulkArgs {
     void *out;           // forward: y (f32 or bf16); backward: dx (f32)
     float *mean_out, *rstd_out;
     float *partial;      // backward: [grid][2][dim], or [grid][3][dim] with dx_bf16
+    int f16;             // the 16-bit operands (out, res, g, dx_bf16) are f16 instead of bf16
     __nv_bfloat16 *dx_bf16; // backward, optional: dx rounded to bf16 (what the backward GEMMs of the Linear feeding this
                             // residual stream read); the third partial row then holds the column sums of those rounded values
     float *sum_out;      // forward with a residual operand (g): x + g, written beside the normalised rows
@@ -56,19 +57,29 @@ __device__ __forceinline__ void bulk_load(void *smem_dst, const void *gsrc, unsi
                  : "memory");
 }
 
-__device__ __forceinline__ float4 unpack4(float4 r) { return r; }
-__device__ __forceinline__ float4 unpack4(uint2 r) {
-    float2 a = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162 *>(&r.x));
-    float2 b = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162 *>(&r.y));
+// 16-bit operands are bf16 or, when `f16` is set (LnBulkArgs::f16, the same for every thread), IEEE f16;
+// the kernels are compiled once for "a 16-bit type" (the template parameter stays __nv_bfloat16)
+__device__ __forceinline__ float4 unpack4(float4 r, int) { return r; }
+__device__ __forceinline__ float4 unpack4(uint2 r, int f16) {
+    float2 a, b;
+    if (f16) {
+        a = Lp<__half>::unpack2(r.x);
+        b = Lp<__half>::unpack2(r.y);
+    } else {
+        a = Lp<__nv_bfloat16>::unpack2(r.x);
+        b = Lp<__nv_bfloat16>::unpack2(r.y);
+    }
     return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ uint2 pack4(float4 v, int f16) {
+    return f16 ? make_uint2(Lp<__half>::pack2(v.x, v.y), Lp<__half>::pack2(v.z, v.w))
+               : make_uint2(Lp<__nv_bfloat16>::pack2(v.x, v.y), Lp<__nv_bfloat16>::pack2(v.z, v.w));
 }
 template <typename T> struct Raw4 { typedef float4 type; };
 template <> struct Raw4<__nv_bfloat16> { typedef uint2 type; };
 
-__device__ __forceinline__ void store4(float *p, int idx, float4 v) { reinterpret_cast<float4 *>(p)[idx] = v; }
-__device__ __forceinline__ void store4(__nv_bfloat16 *p, int idx, float4 v) {
-    reinterpret_cast<uint2 *>(p)[idx] = make_uint2(pack_bf16(v.x, v.y), pack_bf16(v.z, v.w));
-}
+__device__ __forceinline__ void store4(float *p, int idx, float4 v, int) { reinterpret_cast<float4 *>(p)[idx] = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16 *p, int idx, float4 v, int f16) { reinterpret_cast<uint2 *>(p)[idx] = pack4(v, f16); }
 
 // The producer: one thread walks this CTA's row blocks and fills the ring.  NOPS operands per stage.
 template <int NOPS, int kRows>
@@ -157,7 +168,7 @@ __global__ void __launch_bounds__(kThreadsFwd, 1) ln_fwd_bulk_kernel(const LnBul
                 if (kRes && idx < dim4) {
                     const typename Raw4<RT>::type *sg =
                         reinterpret_cast<const typename Raw4<RT>::type *>(smem + (size_t)s * a.stage_bytes + a.off_g + (size_t)warp * a.dim * sizeof(RT));
-                    const float4 t = unpack4(sg[idx]);
+                    const float4 t = unpack4(sg[idx], a.f16);
                     v[j] = make_float4(v[j].x + t.x, v[j].y + t.y, v[j].z + t.z, v[j].w + t.w);
                     reinterpret_cast<float4 *>(a.sum_out + r * a.dim)[idx] = v[j];
                 }
@@ -183,7 +194,7 @@ __global__ void __launch_bounds__(kThreadsFwd, 1) ln_fwd_bulk_kernel(const LnBul
                 if (lane + 32 * j < dim4)
                     store4(d, lane + 32 * j,
                            make_float4((v[j].x - mean) * rstd * ga[j].x + be[j].x, (v[j].y - mean) * rstd * ga[j].y + be[j].y,
-                                       (v[j].z - mean) * rstd * ga[j].z + be[j].z, (v[j].w - mean) * rstd * ga[j].w + be[j].w));
+                                       (v[j].z - mean) * rstd * ga[j].z + be[j].z, (v[j].w - mean) * rstd * ga[j].w + be[j].w), a.f16);
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[s]);
@@ -247,7 +258,7 @@ __global__ void __maxnreg__(216) ln_bwd_bulk_kernel(const LnBulkArgs a) {
                     const int idx = lane + 32 * j;
                     if (idx < dim4) {
                         v[j] = sx[idx];
-                        gv[j] = unpack4(sg[idx]);
+                        gv[j] = unpack4(sg[idx], a.f16);
                     } else {
                         v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
                         gv[j] = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -308,9 +319,9 @@ __global__ void __maxnreg__(216) ln_bwd_bulk_kernel(const LnBulkArgs a) {
                         }
                         reinterpret_cast<float4 *>(d)[lane + 32 * j] = o;
                         if (AUX) { // the bf16 copy the next Linear's backward GEMMs read, and the column sums of exactly those values
-                            const uint2 h = make_uint2(pack_bf16(o.x, o.y), pack_bf16(o.z, o.w));
+                            const uint2 h = pack4(o, a.f16);
                             reinterpret_cast<uint2 *>(a.dx_bf16 + r * a.dim)[lane + 32 * j] = h;
-                            const float4 back = unpack4(h);
+                            const float4 back = unpack4(h, a.f16);
                             float4 &cs = dcs[AUX ? j : 0];
                             cs.x += back.x;
                             cs.y += back.y;
@@ -453,6 +464,8 @@ mcb_status mcb_ln_bulk_forward(mcb_ctx *ctx, const float *x, const float *gamma,
     const int grid = (int)(nblk < ctx->sm_count ? nblk : ctx->sm_count);
     const int nv = pick_nv(dim);
     if (out_dt == MCB_F32) return launch_fwd<float, void>(ctx, nv, a, grid);
+    if (!mcb_is_lp(out_dt)) return MCB_UNSUPPORTED;
+    a.f16 = out_dt == MCB_F16;
     return launch_fwd<__nv_bfloat16, void>(ctx, nv, a, grid);
 }
 
@@ -461,12 +474,14 @@ mcb_status mcb_ln_bulk_forward(mcb_ctx *ctx, const float *x, const float *gamma,
 mcb_status mcb_ln_bulk_add_forward(mcb_ctx *ctx, const float *x, const void *res, int32_t res_dt, const float *gamma, const float *beta, double eps,
                                    float *sum, void *out, int32_t out_dt, float *mean, float *rstd, int64_t rows, int64_t dim) {
     if (!eligible(rows, dim, x, gamma, beta, out) || !mcb_aligned16(res) || !mcb_aligned16(sum) || getenv("MCB_LN_NO_BULK")) return MCB_UNSUPPORTED;
-    if ((res_dt != MCB_F32 && res_dt != MCB_BF16) || (out_dt != MCB_F32 && out_dt != MCB_BF16)) return MCB_UNSUPPORTED;
+    if ((res_dt != MCB_F32 && !mcb_is_lp(res_dt)) || (out_dt != MCB_F32 && !mcb_is_lp(out_dt))) return MCB_UNSUPPORTED;
+    if (mcb_is_lp(res_dt) && mcb_is_lp(out_dt) && res_dt != out_dt) return MCB_UNSUPPORTED; // one 16-bit format per launch
     LnBulkArgs a = {};
     a.x = x; a.g = res; a.gamma = gamma; a.beta = beta; a.out = out; a.sum_out = sum; a.mean_out = mean; a.rstd_out = rstd;
     a.rows = rows; a.dim = (int)dim; a.eps = (float)eps; a.err = ctx->d_err;
+    a.f16 = res_dt == MCB_F16 || out_dt == MCB_F16;
     a.off_g = round128((size_t)kRowsFwd * dim * 4);
-    a.stage_bytes = a.off_g + round128((size_t)kRowsFwd * dim * (res_dt == MCB_BF16 ? 2 : 4));
+    a.stage_bytes = a.off_g + round128((size_t)kRowsFwd * dim * (mcb_is_lp(res_dt) ? 2 : 4));
     a.stages = plan_stages(a.stage_bytes);
     if (!a.stages) return MCB_UNSUPPORTED;
     const int64_t nblk = (rows + kRowsFwd - 1) / kRowsFwd;
@@ -482,14 +497,17 @@ mcb_status mcb_ln_bulk_add_forward(mcb_ctx *ctx, const float *x, const void *res
 
 mcb_status mcb_ln_bulk_backward(mcb_ctx *ctx, const float *x, const float *gamma, const void *g, int32_t g_dt, double eps, const float *mean,
                                 const float *rstd, const float *addend, float *dx, float *dgamma, float *dbeta, int64_t rows, int64_t dim,
-                                void *dx_bf16, float *dx_colsum) {
+                                void *dx_bf16, float *dx_colsum, int32_t aux_dt) {
+    if (g_dt != MCB_F32 && !mcb_is_lp(g_dt)) return MCB_UNSUPPORTED;
+    if (dx_bf16 && mcb_is_lp(g_dt) && aux_dt != g_dt) return MCB_UNSUPPORTED; // one 16-bit format per launch
     if (!eligible(rows, dim, x, gamma, g, dx) || (addend && !mcb_aligned16(addend)) || getenv("MCB_LN_NO_BULK")) return MCB_UNSUPPORTED;
     if ((dx_bf16 != nullptr) != (dx_colsum != nullptr) || (dx_bf16 && !mcb_aligned16(dx_bf16))) return MCB_UNSUPPORTED;
     LnBulkArgs a = {};
     a.x = x; a.gamma = gamma; a.g = g; a.mean_in = mean; a.rstd_in = rstd; a.addend = addend; a.out = dx;
     a.dx_bf16 = (__nv_bfloat16 *)dx_bf16;
     a.rows = rows; a.dim = (int)dim; a.eps = (float)eps; a.err = ctx->d_err;
-    const size_t gsz = g_dt == MCB_BF16 ? 2 : 4;
+    a.f16 = g_dt == MCB_F16 || (dx_bf16 && aux_dt == MCB_F16);
+    const size_t gsz = mcb_is_lp(g_dt) ? 2 : 4;
     a.off_g = round128((size_t)kRowsBwd * dim * 4);
     a.off_ad = a.off_g + round128((size_t)kRowsBwd * dim * gsz);
     a.stage_bytes = a.off_ad + (addend ? round128((size_t)kRowsBwd * dim * 4) : 0u);

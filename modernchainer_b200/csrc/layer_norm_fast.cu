@@ -300,6 +300,7 @@ bool eligible(int64_t dim, const void *a, const void *b, const void *c, const vo
 mcb_status mcb_ln_fast_forward(mcb_ctx *ctx, const float *x, const float *gamma, const float *beta, double eps, void *out, int32_t out_dt,
                                float *mean, float *rstd, int64_t rows, int64_t dim) {
     if (!eligible(dim, x, gamma, beta, out)) return MCB_UNSUPPORTED;
+    if (out_dt != MCB_F32 && out_dt != MCB_BF16) return MCB_UNSUPPORTED; // f16 rows take the generic kernel
     if (out_dt == MCB_BF16 && (dim % 8)) return MCB_UNSUPPORTED; // 8-byte bf16x4 stores need even row starts of 8 bytes: dim*2 % 8 == 0 holds; keep 16 B rows
     int nv = pick_nv(dim);
     int grid = mcb_grid_for(ctx, rows, kWarps, 2); // few persistent warps: gamma / beta are fetched once per warp, not once per row
@@ -313,6 +314,7 @@ mcb_status mcb_ln_fast_backward(mcb_ctx *ctx, const float *x, const float *gamma
                                 const float *rstd, const float *addend, float *dx, float *dgamma, float *dbeta, int64_t rows, int64_t dim) {
     if (!eligible(dim, x, gamma, g, dx) || rows == 0 || (addend && !mcb_aligned16(addend))) return MCB_UNSUPPORTED;
     if (g_dt == MCB_BF16 && (dim % 8)) return MCB_UNSUPPORTED;
+    if (g_dt != MCB_F32 && g_dt != MCB_BF16) return MCB_UNSUPPORTED; // f16 gradients take the generic kernel
     int nv = pick_nv(dim);
     int grid = mcb_grid_for(ctx, rows, kWarps, 2);
     void *scratch;

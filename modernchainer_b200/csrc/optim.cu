@@ -15,6 +15,7 @@ struct AdamK {
     float nlr = 0.0f;  // SGD forms: (f32)(-lr)
     float mom = 0.0f;  // MomentumSGD: (f32)momentum
     int first = 0;     // MomentumSGD: no velocity yet, so velocity = gradient
+    int shadow_f16 = 0; // the 16-bit copy of the parameters is f16 (else bf16)
 };
 
 // Rust f32::powi: repeated squaring in f32 (the reference computes 1 - beta^t this way,
@@ -71,6 +72,16 @@ __global__ void adam_update_kernel(const float *__restrict__ p, const float *__r
     }
 }
 
+// 16-bit copy of the updated parameters for the low-precision GEMMs: bf16, or f16 when the step runs under f16 autocast
+__device__ __forceinline__ void store_shadow4(__nv_bfloat16 *shadow, long long j, float4 v, int f16) {
+    if (f16) Elem<__half>::st4(reinterpret_cast<__half *>(shadow), j, v);
+    else Elem<__nv_bfloat16>::st4(shadow, j, v);
+}
+__device__ __forceinline__ void store_shadow(__nv_bfloat16 *shadow, long long j, float v, int f16) {
+    if (f16) reinterpret_cast<__half *>(shadow)[j] = __float2half_rn(v);
+    else shadow[j] = __float2bfloat16_rn(v);
+}
+
 // One element of the other update rules, in the reference's operation order and without FMA:
 //   AdamW        : next = adam(p, ...); p' = next - p * (f32)(wd * lr)          (lib.rs:196-211)
 //   SGD          : p' = p + g * (f32)(-lr)                                      (lib.rs:38-41)
@@ -112,14 +123,14 @@ sgd_flat_kernel(float *__restrict__ p, const GT *__restrict__ g, float *__restri
         opt_one<KIND>(k, gg.w * k.inv_scale, pp.w, mm.w, vv.w);
         reinterpret_cast<float4 *>(p)[j] = pp;
         if (KIND == MCB_OPT_MOMENTUM_SGD) reinterpret_cast<float4 *>(m)[j] = mm;
-        if (shadow) Elem<__nv_bfloat16>::st4(shadow, j, pp);
+        if (shadow) store_shadow4(shadow, j, pp, k.shadow_f16);
     }
     for (long long j = (n4 << 2) + i; j < n; j += stride) {
         float pp = p[j], mm = KIND == MCB_OPT_MOMENTUM_SGD ? m[j] : 0.0f, vv = 0.0f;
         opt_one<KIND>(k, Elem<GT>::ld(g, j) * k.inv_scale, pp, mm, vv);
         p[j] = pp;
         if (KIND == MCB_OPT_MOMENTUM_SGD) m[j] = mm;
-        if (shadow) shadow[j] = __float2bfloat16_rn(pp);
+        if (shadow) store_shadow(shadow, j, pp, k.shadow_f16);
     }
 }
 
@@ -159,7 +170,7 @@ adam_flat_kernel(float *__restrict__ p, const GT *__restrict__ g, float *__restr
         reinterpret_cast<float4 *>(p)[j] = pp;
         reinterpret_cast<float4 *>(m)[j] = mm;
         reinterpret_cast<float4 *>(v)[j] = vv;
-        if (shadow) Elem<__nv_bfloat16>::st4(shadow, j, pp);
+        if (shadow) store_shadow4(shadow, j, pp, k.shadow_f16);
     }
     for (long long j = (n4 << 2) + i; j < n; j += stride) {
         float pp = p[j], mm = m[j], vv = v[j];
@@ -167,7 +178,7 @@ adam_flat_kernel(float *__restrict__ p, const GT *__restrict__ g, float *__restr
         p[j] = pp;
         m[j] = mm;
         v[j] = vv;
-        if (shadow) shadow[j] = __float2bfloat16_rn(pp);
+        if (shadow) store_shadow(shadow, j, pp, k.shadow_f16);
     }
 }
 
@@ -186,7 +197,9 @@ __global__ void check_finite_f32_kernel(const float *__restrict__ g, long long n
         bad |= ((__float_as_uint(g[j]) & 0x7F800000u) == 0x7F800000u);
     if (__syncthreads_or(bad) && threadIdx.x == 0) atomicExch(flag, 1);
 }
-__global__ void check_finite_bf16_kernel(const unsigned short *__restrict__ g, long long n, int *__restrict__ flag, int vec) {
+// 16-bit gradients: `em` is the exponent mask of the format (bf16 0x7F80, f16 0x7C00)
+__global__ void check_finite_bf16_kernel(const unsigned short *__restrict__ g, long long n, int *__restrict__ flag, int vec, unsigned em) {
+    const unsigned emh = em << 16;
     long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     long long stride = (long long)gridDim.x * blockDim.x;
     unsigned bad = 0;
@@ -196,9 +209,9 @@ __global__ void check_finite_bf16_kernel(const unsigned short *__restrict__ g, l
         unsigned w[4] = {b.x, b.y, b.z, b.w};
 #pragma unroll
         for (int q = 0; q < 4; ++q)
-            bad |= ((w[q] & 0x7F80u) == 0x7F80u) | ((w[q] & 0x7F800000u) == 0x7F800000u);
+            bad |= ((w[q] & em) == em) | ((w[q] & emh) == emh);
     }
-    for (long long j = (n8 << 3) + i; j < n; j += stride) bad |= ((g[j] & 0x7F80u) == 0x7F80u);
+    for (long long j = (n8 << 3) + i; j < n; j += stride) bad |= ((g[j] & em) == em);
     if (__syncthreads_or(bad) && threadIdx.x == 0) atomicExch(flag, 1);
 }
 
@@ -229,13 +242,14 @@ mcb_status mcb_check_finite(mcb_ctx *ctx, const void *g, int32_t g_dt, int64_t n
     MCB_CHECK_CTX(ctx);
     if (n == 0) return MCB_OK;
     int vec = mcb_aligned16(g);
-    ProfScope prof(ctx, MCB_PROF_OPTIMIZER, 0.0, (double)n * (g_dt == MCB_BF16 ? 2.0 : 4.0));
+    ProfScope prof(ctx, MCB_PROF_OPTIMIZER, 0.0, (double)n * (mcb_is_lp(g_dt) ? 2.0 : 4.0));
     if (g_dt == MCB_F32)
         check_finite_f32_kernel<<<mcb_grid_for(ctx, (n + 3) / 4, kThreads, 8), kThreads, 0, ctx->stream>>>((const float *)g, n, flag, vec);
-    else if (g_dt == MCB_BF16)
-        check_finite_bf16_kernel<<<mcb_grid_for(ctx, (n + 7) / 8, kThreads, 8), kThreads, 0, ctx->stream>>>((const unsigned short *)g, n, flag, vec);
+    else if (mcb_is_lp(g_dt))
+        check_finite_bf16_kernel<<<mcb_grid_for(ctx, (n + 7) / 8, kThreads, 8), kThreads, 0, ctx->stream>>>((const unsigned short *)g, n, flag, vec,
+                                                                                                          g_dt == MCB_BF16 ? 0x7F80u : 0x7C00u);
     else
-        return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "check_finite supports f32 and bf16");
+        return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "check_finite supports f32, bf16 and f16");
     MCB_LAUNCHED(ctx);
     return MCB_OK;
 }
@@ -275,7 +289,7 @@ mcb_status mcb_increment_i32(mcb_ctx *ctx, int32_t *counter) {
 // count of this update (bias correction for Adam/AdamW, "no velocity yet" when 1 for MomentumSGD).
 mcb_status mcb_opt_flat(mcb_ctx *ctx, int32_t kind, float *p, const void *g, int32_t g_dt, float *m, float *v, void *p_bf16, int64_t n,
                         double lr, double beta1, double beta2, double eps, double weight_decay, int32_t step, double inv_scale,
-                        const float *inv_scale_dev, const int32_t *skip_flag, const int32_t *step_dev) {
+                        const float *inv_scale_dev, const int32_t *skip_flag, const int32_t *step_dev, int32_t shadow_dt) {
     if (kind < MCB_OPT_ADAM || kind > MCB_OPT_MOMENTUM_SGD) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "unknown optimizer kind %d", kind);
     if (step < 1) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "optimizer step must be >= 1");
     if (n == 0) return MCB_OK;
@@ -285,15 +299,18 @@ mcb_status mcb_opt_flat(mcb_ctx *ctx, int32_t kind, float *p, const void *g, int
     k.nlr = (float)(-lr);
     k.mom = (float)beta1;
     k.first = step == 1;
+    k.shadow_f16 = shadow_dt == MCB_F16;
     int vec = mcb_aligned16(p) && mcb_aligned16(g) && (!m || mcb_aligned16(m)) && (!v || mcb_aligned16(v)) && (!p_bf16 || mcb_aligned16(p_bf16));
     int grid = mcb_grid_for(ctx, (n + 3) / 4, kThreads, 8);
     // algorithmic bytes per parameter: read and write p plus the state the rule keeps, read g (+ the bf16 shadow)
     double state_bytes = adam ? 16.0 : (kind == MCB_OPT_MOMENTUM_SGD ? 8.0 : 0.0);
-    ProfScope prof(ctx, MCB_PROF_OPTIMIZER, 0.0, (double)n * (8.0 + state_bytes + (g_dt == MCB_BF16 ? 2.0 : 4.0) + (p_bf16 ? 2.0 : 0.0)));
+    ProfScope prof(ctx, MCB_PROF_OPTIMIZER, 0.0, (double)n * (8.0 + state_bytes + (mcb_is_lp(g_dt) ? 2.0 : 4.0) + (p_bf16 ? 2.0 : 0.0)));
     if (g_dt == MCB_F32) launch_opt<float>(ctx, kind, grid, p, (const float *)g, m, v, (__nv_bfloat16 *)p_bf16, n, k, inv_scale_dev, skip_flag, step_dev, vec);
     else if (g_dt == MCB_BF16)
         launch_opt<__nv_bfloat16>(ctx, kind, grid, p, (const __nv_bfloat16 *)g, m, v, (__nv_bfloat16 *)p_bf16, n, k, inv_scale_dev, skip_flag, step_dev, vec);
-    else return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "optimizer grads must be f32 or bf16");
+    else if (g_dt == MCB_F16)
+        launch_opt<__half>(ctx, kind, grid, p, (const __half *)g, m, v, (__nv_bfloat16 *)p_bf16, n, k, inv_scale_dev, skip_flag, step_dev, vec);
+    else return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "optimizer grads must be f32, bf16 or f16");
     MCB_LAUNCHED(ctx);
     return MCB_OK;
 }
@@ -319,12 +336,15 @@ __global__ void sumsq_partial_kernel(const float *__restrict__ g, long long n, d
         partial[blockIdx.x] = t;
     }
 }
-// out[0] = norm, out[1] = factor (max_norm / norm when the norm exceeds max_norm and is positive, else 1)
-__global__ void clip_final_kernel(const double *__restrict__ partial, int count, double max_norm, double *__restrict__ out) {
+// out[0] = norm, out[1] = factor (max_norm / norm when the norm exceeds max_norm and is positive, else 1).
+// `mean_factor` turns the norm of a gradient that is still a SUM over data-parallel ranks into the norm of the
+// mean the optimizer will use (1 / world; 1 on a single rank): the limit applies to the mean, and the factor
+// max_norm / norm scales the sum and the mean alike.
+__global__ void clip_final_kernel(const double *__restrict__ partial, int count, double max_norm, double mean_factor, double *__restrict__ out) {
     if (threadIdx.x != 0 || blockIdx.x != 0) return;
     double t = 0.0;
     for (int i = 0; i < count; ++i) t += partial[i];
-    double norm = sqrt(t);
+    double norm = sqrt(t) * mean_factor;
     out[0] = norm;
     out[1] = (norm > max_norm && norm > 0.0) ? max_norm / norm : 1.0;
 }
@@ -345,8 +365,8 @@ mcb_status mcb_sumsq_partial(mcb_ctx *ctx, const float *g, int64_t n, double *pa
     MCB_LAUNCHED(ctx);
     return MCB_OK;
 }
-mcb_status mcb_clip_finalize(mcb_ctx *ctx, const double *partial, int count, double max_norm, double *out2) {
-    clip_final_kernel<<<1, 32, 0, ctx->stream>>>(partial, count, max_norm, out2);
+mcb_status mcb_clip_finalize(mcb_ctx *ctx, const double *partial, int count, double max_norm, double *out2, double mean_factor) {
+    clip_final_kernel<<<1, 32, 0, ctx->stream>>>(partial, count, max_norm, mean_factor, out2);
     MCB_LAUNCHED(ctx);
     return MCB_OK;
 }

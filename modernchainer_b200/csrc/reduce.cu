@@ -333,6 +333,12 @@ __global__ void layer_norm_params_final_kernel(const float *__restrict__ partial
 template <typename T> __device__ __forceinline__ float row_exp(float v);
 template <> __device__ __forceinline__ float row_exp<float>(float v) { return expf(v); }
 template <> __device__ __forceinline__ float row_exp<__nv_bfloat16>(float v) { return __expf(v); }
+template <> __device__ __forceinline__ float row_exp<__half>(float v) { return __expf(v); }
+// pair of 16-bit logits packed in one word -> two floats (float rows never take these paths)
+template <typename T> __device__ __forceinline__ float2 lp_unpack(uint32_t w) { return Lp<T>::unpack2(w); }
+template <> __device__ __forceinline__ float2 lp_unpack<float>(uint32_t) { return make_float2(0.0f, 0.0f); }
+template <typename T> __device__ __forceinline__ uint32_t lp_pack(float a, float b) { return Lp<T>::pack2(a, b); }
+template <> __device__ __forceinline__ uint32_t lp_pack<float>(float, float) { return 0u; }
 
 // per-thread online (max, sum) merged across the block
 template <typename T>
@@ -352,8 +358,9 @@ __device__ __forceinline__ void row_max_sumexp(const T *__restrict__ row, long l
             unsigned wds[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
-                f[2 * q] = __uint_as_float(wds[q] << 16);
-                f[2 * q + 1] = __uint_as_float(wds[q] & 0xFFFF0000u);
+                const float2 pr = lp_unpack<T>(wds[q]);
+                f[2 * q] = pr.x;
+                f[2 * q + 1] = pr.y;
             }
             float gm = fmaxf(fmaxf(fmaxf(f[0], f[1]), fmaxf(f[2], f[3])), fmaxf(fmaxf(f[4], f[5]), fmaxf(f[6], f[7])));
             if (gm > m) {
@@ -481,8 +488,9 @@ __global__ void __launch_bounds__(512, 3) sce_fused_kernel(const T *x, T *out, c
             float p[8];
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
-                p[2 * q] = row_exp<T>(__uint_as_float(wds[q] << 16) - mx) * inv_sum;
-                p[2 * q + 1] = row_exp<T>(__uint_as_float(wds[q] & 0xFFFF0000u) - mx) * inv_sum;
+                const float2 pr = lp_unpack<T>(wds[q]);
+                p[2 * q] = row_exp<T>(pr.x - mx) * inv_sum;
+                p[2 * q + 1] = row_exp<T>(pr.y - mx) * inv_sum;
             }
             const long long b = j << 3;
             if (lab >= b && lab < b + 8) {
@@ -492,10 +500,7 @@ __global__ void __launch_bounds__(512, 3) sce_fused_kernel(const T *x, T *out, c
             }
             unsigned ow[4];
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                __nv_bfloat162 h = __floats2bfloat162_rn(p[2 * q] * k, p[2 * q + 1] * k);
-                ow[q] = *reinterpret_cast<unsigned *>(&h);
-            }
+            for (int q = 0; q < 4; ++q) ow[q] = lp_pack<T>(p[2 * q] * k, p[2 * q + 1] * k);
             o8[j] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
         }
     } else if (vec) {
@@ -526,6 +531,7 @@ __global__ void __launch_bounds__(512, 3) sce_fused_kernel(const T *x, T *out, c
 // segments of 1024 16-byte chunks and every thread streams four of them (all loads issued before the first
 // use).  g = (softmax - onehot) * up / n with the softmax as one FMA and one ex2 per logit:
 // p = 2^(v * log2e - (mx * log2e + log2(sum))).  `out` may alias `x`: a chunk is written by the thread that read it.
+template <typename T>
 __global__ void __launch_bounds__(256) sce_grad_stream_kernel(const uint4 *x, uint4 *out, const void *__restrict__ labels, int label_dt,
                                                               long long n, long long c8, const float *__restrict__ stats,
                                                               const float *__restrict__ upstream, unsigned int *err) {
@@ -555,8 +561,9 @@ __global__ void __launch_bounds__(256) sce_grad_stream_kernel(const uint4 *x, ui
         float p[8];
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-            asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p[2 * q]) : "f"(fmaf(__uint_as_float(wds[q] << 16), 1.4426950408889634f, c1)));
-            asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p[2 * q + 1]) : "f"(fmaf(__uint_as_float(wds[q] & 0xFFFF0000u), 1.4426950408889634f, c1)));
+            const float2 pr = Lp<T>::unpack2(wds[q]);
+            asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p[2 * q]) : "f"(fmaf(pr.x, 1.4426950408889634f, c1)));
+            asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p[2 * q + 1]) : "f"(fmaf(pr.y, 1.4426950408889634f, c1)));
         }
         const long long b = j << 3;
         if (lab >= b && lab < b + 8) {
@@ -566,10 +573,7 @@ __global__ void __launch_bounds__(256) sce_grad_stream_kernel(const uint4 *x, ui
         }
         unsigned ow[4];
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            __nv_bfloat162 h = __floats2bfloat162_rn(p[2 * q] * k, p[2 * q + 1] * k);
-            ow[q] = bad ? 0u : *reinterpret_cast<unsigned *>(&h);
-        }
+        for (int q = 0; q < 4; ++q) ow[q] = bad ? 0u : Lp<T>::pack2(p[2 * q] * k, p[2 * q + 1] * k);
         o8[j] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
     }
 }
@@ -636,8 +640,8 @@ mcb_status mcb_col_sum(mcb_ctx *ctx, const void *a, int32_t dt, int64_t rows, in
     MCB_CHECK_CTX(ctx);
     if (cols == 0) return MCB_OK;
     if (rows == 0) return mcb_memset(ctx, out, 0, sizeof(float) * cols);
-    ProfScope prof(ctx, MCB_PROF_REDUCE, 0.0, (double)rows * cols * (dt == MCB_BF16 ? 2.0 : 4.0));
-    if ((cols % 4) == 0 && mcb_aligned16(a) && (dt == MCB_F32 || dt == MCB_BF16)) {
+    ProfScope prof(ctx, MCB_PROF_REDUCE, 0.0, (double)rows * cols * (mcb_is_lp(dt) ? 2.0 : 4.0));
+    if ((cols % 4) == 0 && mcb_aligned16(a) && (dt == MCB_F32 || mcb_is_lp(dt))) {
         // wide path: each lane owns 4 consecutive columns (one 8/16-byte load per row), a warp 128 columns
         int chunks = (int)((cols + 127) / 128);
         int splits = (int)((ctx->sm_count * 4 + chunks - 1) / chunks);
@@ -648,9 +652,12 @@ mcb_status mcb_col_sum(mcb_ctx *ctx, const void *a, int32_t dt, int64_t rows, in
         dim3 grid(chunks, splits);
         if (dt == MCB_F32)
             MCB_CUDA(ctx, mcb_launch_dep(ctx, col_sum_vec_kernel<float>, grid, dim3(256), 0, (const float *)a, (long long)rows, (long long)cols, (float *)scratch));
-        else
+        else if (dt == MCB_BF16)
             MCB_CUDA(ctx, mcb_launch_dep(ctx, col_sum_vec_kernel<__nv_bfloat16>, grid, dim3(256), 0, (const __nv_bfloat16 *)a, (long long)rows,
                                          (long long)cols, (float *)scratch));
+        else
+            MCB_CUDA(ctx, mcb_launch_dep(ctx, col_sum_vec_kernel<__half>, grid, dim3(256), 0, (const __half *)a, (long long)rows, (long long)cols,
+                                         (float *)scratch));
         MCB_LAUNCHED(ctx);
         MCB_CUDA(ctx, mcb_launch_dep(ctx, partial_sum_final_kernel, dim3((unsigned)((cols + 31) / 32)), dim3(32, 32), 0, (const float *)scratch, splits,
                                      (long long)cols, out));
@@ -668,8 +675,10 @@ mcb_status mcb_col_sum(mcb_ctx *ctx, const void *a, int32_t dt, int64_t rows, in
         col_sum_partial_kernel<float><<<grid, block, 0, ctx->stream>>>((const float *)a, rows, cols, (float *)scratch);
     else if (dt == MCB_BF16)
         col_sum_partial_kernel<__nv_bfloat16><<<grid, block, 0, ctx->stream>>>((const __nv_bfloat16 *)a, rows, cols, (float *)scratch);
+    else if (dt == MCB_F16)
+        col_sum_partial_kernel<__half><<<grid, block, 0, ctx->stream>>>((const __half *)a, rows, cols, (float *)scratch);
     else
-        return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "col_sum supports f32 and bf16");
+        return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "col_sum supports f32, bf16 and f16");
     MCB_LAUNCHED(ctx);
     col_sum_final_kernel<<<(int)((cols + 255) / 256), 256, 0, ctx->stream>>>((const float *)scratch, splits, cols, out);
     MCB_LAUNCHED(ctx);
@@ -740,8 +749,8 @@ mcb_status mcb_layer_norm(mcb_ctx *ctx, const float *x, const float *gamma, cons
     if (rows == 0 || dim == 0) return MCB_OK;
     if (dim > INT32_MAX) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "layer_norm dim too large");
     int vec = (dim % 4 == 0) && mcb_aligned16(x) && mcb_aligned16(out) && mcb_aligned16(gamma) && mcb_aligned16(beta);
-    ProfScope prof(ctx, MCB_PROF_NORM, 0.0, (double)rows * dim * (4.0 + (out_dt == MCB_BF16 ? 2.0 : 4.0)) + 8.0 * rows);
-    if (out_dt == MCB_F32 || out_dt == MCB_BF16) {
+    ProfScope prof(ctx, MCB_PROF_NORM, 0.0, (double)rows * dim * (4.0 + (mcb_is_lp(out_dt) ? 2.0 : 4.0)) + 8.0 * rows);
+    if (out_dt == MCB_F32 || mcb_is_lp(out_dt)) {
         mcb_status bulk = mcb_ln_bulk_forward(ctx, x, gamma, beta, eps, out, out_dt, mean, rstd, rows, dim);
         if (bulk != MCB_UNSUPPORTED) return bulk; // enough rows to fill every SM: shared-memory pipeline
         mcb_status fast = mcb_ln_fast_forward(ctx, x, gamma, beta, eps, out, out_dt, mean, rstd, rows, dim);
@@ -752,8 +761,10 @@ mcb_status mcb_layer_norm(mcb_ctx *ctx, const float *x, const float *gamma, cons
         layer_norm_kernel<float><<<grid, kThreads, 0, ctx->stream>>>(x, gamma, beta, (float)eps, (float *)out, mean, rstd, rows, (int)dim, vec);
     else if (out_dt == MCB_BF16)
         layer_norm_kernel<__nv_bfloat16><<<grid, kThreads, 0, ctx->stream>>>(x, gamma, beta, (float)eps, (__nv_bfloat16 *)out, mean, rstd, rows, (int)dim, vec);
+    else if (out_dt == MCB_F16)
+        layer_norm_kernel<__half><<<grid, kThreads, 0, ctx->stream>>>(x, gamma, beta, (float)eps, (__half *)out, mean, rstd, rows, (int)dim, vec);
     else
-        return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "layer_norm output must be f32 or bf16");
+        return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "layer_norm output must be f32, bf16 or f16");
     MCB_LAUNCHED(ctx);
     return MCB_OK;
 }
@@ -779,8 +790,8 @@ mcb_status mcb_layer_norm_backward_ex(mcb_ctx *ctx, const float *x, const float 
     }
     // algorithmic bytes: read x and g, write dx, read the row statistics, write 2*dim parameter sums
     ProfScope prof(ctx, MCB_PROF_NORM, 0.0,
-                   (double)rows * dim * (8.0 + (g_dt == MCB_BF16 ? 2.0 : 4.0) + (addend ? 4.0 : 0.0)) + 8.0 * rows + 8.0 * dim);
-    if (g_dt == MCB_F32 || g_dt == MCB_BF16) {
+                   (double)rows * dim * (8.0 + (mcb_is_lp(g_dt) ? 2.0 : 4.0) + (addend ? 4.0 : 0.0)) + 8.0 * rows + 8.0 * dim);
+    if (g_dt == MCB_F32 || mcb_is_lp(g_dt)) {
         mcb_status bulk = mcb_ln_bulk_backward(ctx, x, gamma, g, g_dt, eps, mean, rstd, addend, dx, dgamma, dbeta, rows, dim);
         if (bulk != MCB_UNSUPPORTED) return bulk;
         mcb_status fast = mcb_ln_fast_backward(ctx, x, gamma, g, g_dt, eps, mean, rstd, addend, dx, dgamma, dbeta, rows, dim);
@@ -801,8 +812,11 @@ mcb_status mcb_layer_norm_backward_ex(mcb_ctx *ctx, const float *x, const float 
     } else if (g_dt == MCB_BF16) {
         MCB_CUDA(ctx, cudaFuncSetAttribute(layer_norm_backward_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_cap));
         layer_norm_backward_kernel<__nv_bfloat16><<<grid, warps * 32, smem, ctx->stream>>>(x, gamma, (const __nv_bfloat16 *)g, (float)eps, mean, rstd, dx, (float *)scratch, rows, (int)dim);
+    } else if (g_dt == MCB_F16) {
+        MCB_CUDA(ctx, cudaFuncSetAttribute(layer_norm_backward_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_cap));
+        layer_norm_backward_kernel<__half><<<grid, warps * 32, smem, ctx->stream>>>(x, gamma, (const __half *)g, (float)eps, mean, rstd, dx, (float *)scratch, rows, (int)dim);
     } else {
-        return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "layer_norm_backward grad must be f32 or bf16");
+        return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "layer_norm_backward grad must be f32, bf16 or f16");
     }
     MCB_LAUNCHED(ctx);
     layer_norm_params_final_kernel<<<(int)((2 * dim + 255) / 256), 256, 0, ctx->stream>>>((const float *)scratch, grid, (int)dim, dgamma, dbeta);
@@ -862,8 +876,10 @@ mcb_status mcb_embedding_backward(mcb_ctx *ctx, const void *ids, int32_t id_dt, 
         embedding_backward_kernel<float><<<grid, kThreads, 0, ctx->stream>>>(ids, id_dt, n, (const float *)g, vocab, (int)dim, out, ctx->d_err);
     else if (g_dt == MCB_BF16)
         embedding_backward_kernel<__nv_bfloat16><<<grid, kThreads, 0, ctx->stream>>>(ids, id_dt, n, (const __nv_bfloat16 *)g, vocab, (int)dim, out, ctx->d_err);
+    else if (g_dt == MCB_F16)
+        embedding_backward_kernel<__half><<<grid, kThreads, 0, ctx->stream>>>(ids, id_dt, n, (const __half *)g, vocab, (int)dim, out, ctx->d_err);
     else
-        return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "embedding grad must be f32 or bf16");
+        return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "embedding grad must be f32, bf16 or f16");
     MCB_LAUNCHED(ctx);
     return MCB_OK;
 }
@@ -880,14 +896,18 @@ mcb_status mcb_sce_grad(mcb_ctx *ctx, const void *logits, void *out, int32_t dt,
     if (loss_out) MCB_TRY(mcb_scratch(ctx, sizeof(float) * n, &scratch));
     int threads = c >= 4096 ? 512 : (c >= 256 ? 128 : 32);
     // algorithmic bytes: one read of the logits, one write of the gradient when requested
-    ProfScope prof(ctx, MCB_PROF_LOSS, 0.0, (double)n * c * (dt == MCB_BF16 ? 2.0 : 4.0) * (out ? 2.0 : 1.0) + 8.0 * n);
-    if (dt == MCB_BF16 && out && stats_in && !loss_out && !stats_out && (c % 8) == 0 && n <= 65535 && mcb_aligned16(logits) && mcb_aligned16(out) &&
+    ProfScope prof(ctx, MCB_PROF_LOSS, 0.0, (double)n * c * (mcb_is_lp(dt) ? 2.0 : 4.0) * (out ? 2.0 : 1.0) + 8.0 * n);
+    if (mcb_is_lp(dt) && out && stats_in && !loss_out && !stats_out && (c % 8) == 0 && n <= 65535 && mcb_aligned16(logits) && mcb_aligned16(out) &&
         !getenv("MCB_SCE_NO_STREAM")) {
         // gradient pass with known row statistics: pure streaming
         const long long c8 = c / 8;
         dim3 grid((unsigned)((c8 + 1023) / 1024), (unsigned)n);
-        MCB_CUDA(ctx, mcb_launch_dep(ctx, sce_grad_stream_kernel, grid, dim3(256), 0, (const uint4 *)logits, (uint4 *)out, labels, (int)label_dt, (long long)n,
-                                     c8, stats_in, upstream, ctx->d_err));
+        if (dt == MCB_BF16)
+            MCB_CUDA(ctx, mcb_launch_dep(ctx, sce_grad_stream_kernel<__nv_bfloat16>, grid, dim3(256), 0, (const uint4 *)logits, (uint4 *)out, labels,
+                                         (int)label_dt, (long long)n, c8, stats_in, upstream, ctx->d_err));
+        else
+            MCB_CUDA(ctx, mcb_launch_dep(ctx, sce_grad_stream_kernel<__half>, grid, dim3(256), 0, (const uint4 *)logits, (uint4 *)out, labels,
+                                         (int)label_dt, (long long)n, c8, stats_in, upstream, ctx->d_err));
         MCB_LAUNCHED(ctx);
         return MCB_OK;
     }
@@ -895,8 +915,10 @@ mcb_status mcb_sce_grad(mcb_ctx *ctx, const void *logits, void *out, int32_t dt,
         sce_fused_kernel<float><<<(unsigned)n, threads, 0, ctx->stream>>>((const float *)logits, (float *)out, labels, label_dt, n, c, (float *)scratch, upstream, ctx->d_err, stats_out, stats_in);
     else if (dt == MCB_BF16)
         sce_fused_kernel<__nv_bfloat16><<<(unsigned)n, threads, 0, ctx->stream>>>((const __nv_bfloat16 *)logits, (__nv_bfloat16 *)out, labels, label_dt, n, c, (float *)scratch, upstream, ctx->d_err, stats_out, stats_in);
+    else if (dt == MCB_F16)
+        sce_fused_kernel<__half><<<(unsigned)n, threads, 0, ctx->stream>>>((const __half *)logits, (__half *)out, labels, label_dt, n, c, (float *)scratch, upstream, ctx->d_err, stats_out, stats_in);
     else
-        return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "logits must be f32 or bf16");
+        return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "logits must be f32, bf16 or f16");
     MCB_LAUNCHED(ctx);
     if (loss_out) {
         sce_final_kernel<<<1, kThreads, 0, ctx->stream>>>((const float *)scratch, n, loss_out);

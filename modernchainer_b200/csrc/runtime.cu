@@ -202,10 +202,16 @@ mcb_status mcb_memcpy_h2d(mcb_ctx *ctx, void *dst, const void *host_src, size_t 
     return MCB_OK;
 }
 
+extern "C" mcb_status mcb_dp_bounded_wait(mcb_ctx *ctx); // dp.cu
+
 static mcb_status take_device_error(mcb_ctx *ctx) {
     unsigned int err = 0;
+    // With data-parallel collectives possibly in flight, an unbounded stream synchronise would wait for ever for a
+    // peer that died: wait with a limit first (an expired limit aborts the communicator, which releases the stream).
+    mcb_status dp_st = ctx->dp ? mcb_dp_bounded_wait(ctx) : MCB_OK;
     MCB_CUDA(ctx, cudaMemcpyAsync(&err, ctx->d_err, sizeof(err), cudaMemcpyDeviceToHost, ctx->stream));
     MCB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if (dp_st != MCB_OK) return dp_st;
     if (err) {
         MCB_CUDA(ctx, cudaMemsetAsync(ctx->d_err, 0, sizeof(err), ctx->stream));
         if (err & MCB_DEVERR_TIMEOUT) return mcb_fail(ctx, MCB_BACKEND, "device-side wait timed out");
@@ -348,7 +354,7 @@ mcb_status mcb_clock_trace_read(mcb_ctx *ctx, double *mhz_out, int32_t max_out, 
 
 mcb_status mcb_set_compute_type(mcb_ctx *ctx, int32_t compute) {
     MCB_CHECK_CTX(ctx);
-    if (compute != MCB_COMPUTE_F32 && compute != MCB_COMPUTE_BF16)
+    if (compute != MCB_COMPUTE_F32 && compute != MCB_COMPUTE_BF16 && compute != MCB_COMPUTE_F16)
         return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "unknown compute type %d", compute);
     ctx->compute = compute;
     return MCB_OK;

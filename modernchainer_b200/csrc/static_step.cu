@@ -125,7 +125,8 @@ mcb_status mcb_static_step_create(mcb_model *model, mcb_adam *opt, mcb_scaler *s
     if (ctx->prof_on) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "static step: switch per-kernel timing off before capturing");
     if (ctx->capture_id) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "static step: another capture is in progress");
     if (dt_size(x_dt) == 0 || dt_size(y_dt) == 0 || x_rank < 0 || y_rank < 0) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "static step: bad input description");
-    if (autocast_dt != -1 && autocast_dt != MCB_BF16) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "static step: autocast must be -1 (off) or bf16");
+    if (autocast_dt != -1 && autocast_dt != MCB_BF16 && autocast_dt != MCB_F16)
+        return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "static step: autocast must be -1 (off), bf16 or f16");
     // Data-parallel arenas are captured too: the bucket all-reduces are enqueued on the communication stream
     // behind an event of the capturing stream, which pulls that stream into the capture, and the optimizer's
     // wait on the communication stream joins it back.  NCCL must have run one eager step first (its lazy
@@ -157,7 +158,7 @@ mcb_status mcb_static_step_create(mcb_model *model, mcb_adam *opt, mcb_scaler *s
     // records the zero-fill / refresh kernels, it does not run them
     for (auto &p : s->model->params) {
         if (p->arena) {
-            MCB_TRY(arena_refresh_shadow(p->arena));
+            MCB_TRY(arena_refresh_shadow(p->arena, autocast_dt));
         } else {
             AdamState &as = s->opt->state[p.get()];
             if (!as.m.defined) {

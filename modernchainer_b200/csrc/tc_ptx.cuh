@@ -142,15 +142,24 @@ __device__ __forceinline__ unsigned long long make_desc(unsigned smem_addr, unsi
     d |= 2ull << 61;
     return d;
 }
-// instruction descriptor of kind::f16 with bf16 operands and f32 accumulation
-__host__ __device__ constexpr unsigned make_idesc(int m, int n, int a_mn_major, int b_mn_major) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(a_mn_major ? 1 : 0) << 15) | ((unsigned)(b_mn_major ? 1 : 0) << 16) |
+// instruction descriptor of kind::f16 with bf16 (or, f16 = true, IEEE f16) operands and f32 accumulation:
+// bit 4 = f32 accumulator; bits 7-9 and 10-12 = formats of A and B (0 = f16, 1 = bf16)
+__host__ __device__ constexpr unsigned make_idesc(int m, int n, int a_mn_major, int b_mn_major, bool f16 = false) {
+    return (1u << 4) | (f16 ? 0u : ((1u << 7) | (1u << 10))) | ((unsigned)(a_mn_major ? 1 : 0) << 15) | ((unsigned)(b_mn_major ? 1 : 0) << 16) |
            ((unsigned)(n >> 3) << 17) | ((unsigned)(m >> 4) << 24);
 }
 
 __device__ __forceinline__ unsigned pack_bf16(float a, float b) {
     __nv_bfloat162 p = __floats2bfloat162_rn(a, b);
     return *(unsigned *)&p;
+}
+// two f32 values rounded to nearest even and packed as bf16 (F16 = false) or f16 (F16 = true)
+template <bool F16> __device__ __forceinline__ unsigned pack16(float a, float b) {
+    if (F16) {
+        __half2 p = __floats2half2_rn(a, b);
+        return *(unsigned *)&p;
+    }
+    return pack_bf16(a, b);
 }
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;

@@ -154,6 +154,67 @@ void mco_round_bf16(const float *x, float *out, int64_t n) {
     for (int64_t i = 0; i < n; ++i) out[i] = mco_bf16_bits_to_f32(mco_f32_to_bf16_bits(x[i]));
 }
 
+/* f32 -> f16 bits, dtype.rs:75-108: round to nearest even for results in the normal range,
+ * overflow to inf, NaN to a quiet NaN (0x200 set), magnitudes below 2^-25 to a signed zero.
+ * Results in the f16 subnormal range follow the reference's own arithmetic: it adds
+ * 0xfff + bit(shift-1) before shifting by 14..24, which is round-half-even only for a shift
+ * of 13, so for subnormal results it is close to truncation. */
+uint16_t mco_f32_to_f16_bits(float v) {
+    uint32_t bits = f32_bits(v);
+    uint16_t sign = (uint16_t)((bits >> 16) & 0x8000u);
+    int32_t exp = (int32_t)((bits >> 23) & 0xffu);
+    uint32_t frac = bits & 0x7fffffu;
+    if (exp == 0xff) return (uint16_t)(sign | 0x7c00u | (frac == 0 ? 0u : 0x200u));
+    int32_t h_exp = exp - 112;
+    if (h_exp >= 0x1f) return (uint16_t)(sign | 0x7c00u);
+    if (h_exp <= 0) {
+        if (h_exp < -10) return sign;
+        uint32_t m = frac | 0x800000u;
+        uint32_t shift = (uint32_t)(14 - h_exp);
+        uint32_t rounding_bias = ((m >> (shift - 1)) & 1u) + 0xfffu;
+        uint16_t h = (uint16_t)((m + rounding_bias) >> shift);
+        return (uint16_t)(h | sign);
+    }
+    uint16_t h = (uint16_t)(sign | ((uint16_t)h_exp << 10) | (uint16_t)(frac >> 13));
+    uint32_t rounding = (frac >> 12) & 1u;
+    int sticky = (frac & 0xfffu) != 0;
+    uint16_t lsb = h & 1u;
+    if (rounding == 1 && (sticky || lsb == 1)) return (uint16_t)(h + 1);
+    return h;
+}
+/* dtype.rs:110-134 */
+float mco_f16_bits_to_f32(uint16_t b) {
+    uint32_t sign = ((uint32_t)(b & 0x8000u)) << 16;
+    uint32_t exp = (b >> 10) & 0x1fu, frac = b & 0x3ffu, out;
+    if (exp == 0x1f) {
+        out = sign | 0x7f800000u | (frac << 13);
+    } else if (exp == 0) {
+        if (frac == 0) {
+            out = sign;
+        } else {
+            uint32_t e = 0, f = frac;
+            while ((f & 0x400u) == 0) {
+                f <<= 1;
+                e += 1;
+            }
+            f &= 0x3ffu;
+            out = sign | ((0x7fu - 14u - e) << 23) | (f << 13);
+        }
+    } else {
+        out = sign | ((exp + 112u) << 23) | (frac << 13);
+    }
+    return bits_f32(out);
+}
+void mco_f32_to_f16(const float *x, uint16_t *out, int64_t n) {
+    for (int64_t i = 0; i < n; ++i) out[i] = mco_f32_to_f16_bits(x[i]);
+}
+void mco_f16_to_f32(const uint16_t *x, float *out, int64_t n) {
+    for (int64_t i = 0; i < n; ++i) out[i] = mco_f16_bits_to_f32(x[i]);
+}
+void mco_round_f16(const float *x, float *out, int64_t n) {
+    for (int64_t i = 0; i < n; ++i) out[i] = mco_f16_bits_to_f32(mco_f32_to_f16_bits(x[i]));
+}
+
 /* ------------------------------------------------------------------ */
 /* elementwise maps: kernels.rs:21-153, 390-423, 1384-1401              */
 /* ------------------------------------------------------------------ */
@@ -357,18 +418,67 @@ static int naive_path(int64_t m, int64_t n, int64_t k) {
  * timing runs; otherwise big GEMMs accumulate in f64 (parity policy above). */
 static int g_fast_gemm = 0;
 void mco_set_fast_gemm(int on) { g_fast_gemm = on; }
+/* In a build with OpenMP, mco_set_parallel(1) lets loops whose iterations are independent
+ * (one output element, one (sample, head), one sample or one output channel per iteration)
+ * run on several threads.  Every value is produced by the same operations in the same order
+ * as with one thread, so results are bit-identical; it only makes full-size parity cases
+ * affordable.  The reference runs these loops on one thread. */
+static int g_par = 0;
+void mco_set_parallel(int on) { g_par = on; }
 
 /* generic strided big GEMM: C[i,j] = sum_d A[i*as0 + d*as1] * B[d*bs0 + j*bs1] */
 static void big_gemm(int64_t m, int64_t n, int64_t k, const float *a, int64_t as0, int64_t as1, const float *b,
                      int64_t bs0, int64_t bs1, float *c) {
     if (!g_fast_gemm) {
+        /* f32 products summed in f64 in index order d = 0..k-1, one rounding at the end.  Operands
+         * are first copied so that d is contiguous, and four columns share one pass over a row of
+         * A; neither changes any sum. */
+        const float *ap = a, *bp = b;
+        float *apk = NULL, *bpk = NULL;
+        if (as1 != 1) {
+            apk = (float *)malloc(sizeof(float) * (size_t)m * (size_t)k);
 #pragma omp parallel for schedule(static)
-        for (int64_t i = 0; i < m; ++i)
-            for (int64_t j = 0; j < n; ++j) {
+            for (int64_t i = 0; i < m; ++i)
+                for (int64_t d = 0; d < k; ++d) apk[i * k + d] = a[i * as0 + d * as1];
+            ap = apk;
+            as0 = k;
+        }
+        if (bs0 != 1) {
+            bpk = (float *)malloc(sizeof(float) * (size_t)n * (size_t)k);
+#pragma omp parallel for schedule(static)
+            for (int64_t j = 0; j < n; ++j)
+                for (int64_t d = 0; d < k; ++d) bpk[j * k + d] = b[d * bs0 + j * bs1];
+            bp = bpk;
+            bs1 = k;
+        }
+#pragma omp parallel for schedule(static)
+        for (int64_t i = 0; i < m; ++i) {
+            const float *ar = ap + i * as0;
+            int64_t j = 0;
+            for (; j + 4 <= n; j += 4) {
+                const float *b0 = bp + j * bs1, *b1 = b0 + bs1, *b2 = b1 + bs1, *b3 = b2 + bs1;
+                double s0 = 0.0, s1 = 0.0, s2 = 0.0, s3 = 0.0;
+                for (int64_t d = 0; d < k; ++d) {
+                    float av = ar[d];
+                    s0 += (double)(av * b0[d]);
+                    s1 += (double)(av * b1[d]);
+                    s2 += (double)(av * b2[d]);
+                    s3 += (double)(av * b3[d]);
+                }
+                c[i * n + j] = (float)s0;
+                c[i * n + j + 1] = (float)s1;
+                c[i * n + j + 2] = (float)s2;
+                c[i * n + j + 3] = (float)s3;
+            }
+            for (; j < n; ++j) {
+                const float *b0 = bp + j * bs1;
                 double acc = 0.0;
-                for (int64_t d = 0; d < k; ++d) acc += (double)(a[i * as0 + d * as1] * b[d * bs0 + j * bs1]);
+                for (int64_t d = 0; d < k; ++d) acc += (double)(ar[d] * b0[d]);
                 c[i * n + j] = (float)acc;
             }
+        }
+        free(apk);
+        free(bpk);
         return;
     }
     /* timing build: pack B to [k,n] row-major and A to [m,k] row-major, then a
@@ -713,7 +823,7 @@ static int64_t out_extent(int64_t in, int64_t k, int64_t stride, int64_t pad) { 
 void mco_conv2d(const float *x, const float *w, const float *bias, float *out, int64_t n, int64_t c, int64_t h,
                 int64_t wd, int64_t o, int64_t kh, int64_t kw, int64_t stride, int64_t pad) {
     int64_t oh = out_extent(h, kh, stride, pad), ow = out_extent(wd, kw, stride, pad);
-#pragma omp parallel for collapse(2) schedule(static) if (g_fast_gemm)
+#pragma omp parallel for collapse(2) schedule(static) if (g_fast_gemm || g_par)
     for (int64_t ni = 0; ni < n; ++ni)
         for (int64_t oi = 0; oi < o; ++oi)
             for (int64_t y = 0; y < oh; ++y)
@@ -740,8 +850,31 @@ void mco_conv2d_backward(const float *x, const float *w, const float *g, float *
     memset(dx, 0, sizeof(float) * (size_t)(n * c * h * wd));
     memset(dw, 0, sizeof(float) * (size_t)(o * c * kh * kw));
     if (db) memset(db, 0, sizeof(float) * (size_t)o);
+    /* The reference runs one loop nest (n, o, y, x, ci, ky, kx) that adds into dx, dw and db.
+     * Here the same nest is walked twice: once per sample for dx (a sample's dx only receives
+     * terms of that sample, in the order o, y, x, ...) and once per output channel for dw and db
+     * (a channel's dw and db only receive terms of that channel, in the order n, y, x, ...).
+     * Each accumulator sees its terms in the reference's order; the two walks can be threaded. */
+#pragma omp parallel for schedule(static) if (g_fast_gemm || g_par)
     for (int64_t ni = 0; ni < n; ++ni)
         for (int64_t oi = 0; oi < o; ++oi)
+            for (int64_t y = 0; y < oh; ++y)
+                for (int64_t xi = 0; xi < ow; ++xi) {
+                    float gv = g[((ni * o + oi) * oh + y) * ow + xi];
+                    for (int64_t ci = 0; ci < c; ++ci)
+                        for (int64_t ky = 0; ky < kh; ++ky)
+                            for (int64_t kx = 0; kx < kw; ++kx) {
+                                int64_t iy = y * stride + ky, ix = xi * stride + kx;
+                                if (iy >= pad && ix >= pad && iy - pad < h && ix - pad < wd) {
+                                    int64_t iv = ((ni * c + ci) * h + (iy - pad)) * wd + (ix - pad);
+                                    int64_t wi = ((oi * c + ci) * kh + ky) * kw + kx;
+                                    dx[iv] += gv * w[wi];
+                                }
+                            }
+                }
+#pragma omp parallel for schedule(static) if (g_fast_gemm || g_par)
+    for (int64_t oi = 0; oi < o; ++oi)
+        for (int64_t ni = 0; ni < n; ++ni)
             for (int64_t y = 0; y < oh; ++y)
                 for (int64_t xi = 0; xi < ow; ++xi) {
                     float gv = g[((ni * o + oi) * oh + y) * ow + xi];
@@ -753,7 +886,6 @@ void mco_conv2d_backward(const float *x, const float *w, const float *g, float *
                                 if (iy >= pad && ix >= pad && iy - pad < h && ix - pad < wd) {
                                     int64_t iv = ((ni * c + ci) * h + (iy - pad)) * wd + (ix - pad);
                                     int64_t wi = ((oi * c + ci) * kh + ky) * kw + kx;
-                                    dx[iv] += gv * w[wi];
                                     dw[wi] += gv * x[iv];
                                 }
                             }
@@ -853,7 +985,7 @@ void mco_attention(const float *q, const float *k, const float *v, float *out, i
                    int64_t heads, int causal) {
     int64_t hd = dim / heads;
     float scale = 1.0f / sqrtf((float)hd);
-#pragma omp parallel for collapse(2) schedule(dynamic) if (g_fast_gemm)
+#pragma omp parallel for collapse(2) schedule(dynamic) if (g_fast_gemm || g_par)
     for (int64_t ni = 0; ni < n; ++ni)
         for (int64_t hi = 0; hi < heads; ++hi) {
             float *probs = (float *)malloc(sizeof(float) * (size_t)(seq * seq));
@@ -873,7 +1005,7 @@ void mco_attention_backward(const float *q, const float *k, const float *v, cons
                             float *dv, int64_t n, int64_t seq, int64_t dim, int64_t heads, int causal) {
     int64_t hd = dim / heads;
     float scale = 1.0f / sqrtf((float)hd);
-#pragma omp parallel for collapse(2) schedule(dynamic) if (g_fast_gemm)
+#pragma omp parallel for collapse(2) schedule(dynamic) if (g_fast_gemm || g_par)
     for (int64_t ni = 0; ni < n; ++ni)
         for (int64_t hi = 0; hi < heads; ++hi) {
             float *probs = (float *)malloc(sizeof(float) * (size_t)(seq * seq));

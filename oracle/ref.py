@@ -40,7 +40,7 @@ _libs = {}
 
 
 def lib(fast=False):
-    """Load the checker build (gcc -O2, single thread) or the timed build (-O3 -fopenmp)."""
+    """Load the checker build (gcc -O2, single thread) or the OpenMP build (-O3 -fopenmp)."""
     name = "libmc_oracle_fast.so" if fast else "libmc_oracle.so"
     if name not in _libs:
         path = os.path.join(_HERE, name)
@@ -56,23 +56,46 @@ def lib(fast=False):
         l.mco_f32_to_bf16_bits.argtypes = [C.c_float]
         l.mco_bf16_bits_to_f32.restype = C.c_float
         l.mco_bf16_bits_to_f32.argtypes = [C.c_uint16]
-        if fast:
-            l.mco_set_fast_gemm(1)
         _libs[name] = l
     return _libs[name]
 
 
-_FAST = False
+# "checker": one thread, big GEMMs summed in f64 (the parity reference)
+# "threaded": the same arithmetic, operation for operation, with independent loop iterations spread
+#             over OpenMP threads (bit-identical to "checker"; for full-size parity cases)
+# "fast": f32 blocked threaded GEMM (different summation order; the timed CPU baseline only)
+_MODE = "checker"
+
+
+def set_mode(mode):
+    global _MODE
+    assert mode in ("checker", "threaded", "fast")
+    _MODE = mode
 
 
 def use_fast(on=True):
     """Route every kernel through the threaded timing build (CPU baseline runs)."""
-    global _FAST
-    _FAST = bool(on)
+    set_mode("fast" if on else "checker")
+
+
+class threaded:
+    """`with threaded():` runs the checker arithmetic on all host cores (same bits, less waiting)."""
+
+    def __enter__(self):
+        self.prev = _MODE
+        set_mode("threaded")
+
+    def __exit__(self, *a):
+        set_mode(self.prev)
 
 
 def _l():
-    return lib(_FAST)
+    if _MODE == "checker":
+        return lib(False)
+    l = lib(True)
+    l.mco_set_fast_gemm(1 if _MODE == "fast" else 0)
+    l.mco_set_parallel(1)
+    return l
 
 
 def _f(a):
@@ -142,6 +165,59 @@ def bf16_bits_to_f32(b):
 
 def round_bf16(x):
     return bf16_bits_to_f32(f32_to_bf16_bits(x))
+
+
+def f32_to_f16_bits(x):
+    """core/src/dtype.rs:75-108 (see mco_f32_to_f16_bits for the subnormal range)."""
+    x = _f(x)
+    out = np.empty(x.shape, np.uint16)
+    lib().mco_f32_to_f16(_p(x), _p(out), _i(x.size))
+    return out
+
+
+def f16_bits_to_f32(b):
+    b = np.ascontiguousarray(b, dtype=np.uint16)
+    out = np.empty(b.shape, np.float32)
+    lib().mco_f16_to_f32(_p(b), _p(out), _i(b.size))
+    return out
+
+
+def round_f16(x):
+    return f16_bits_to_f32(f32_to_f16_bits(x))
+
+
+# ---------------------------------------------------------------- low-precision (AMP) oracle
+# The reference's CPU backend ignores autocast (only cuda/src/ops.rs reads it), so it has no
+# low-precision arithmetic to restate.  Under `with amp(BF16)` / `amp(F16)` this oracle keeps every
+# formula, accumulation type and loop order of the f32 oracle and rounds (to nearest even,
+# core/src/dtype.rs:75-146) each tensor that a 16-bit training path stores in 16 bits, at the point
+# where it is stored: LayerNorm outputs, Linear / linear_activation outputs and pre-activations,
+# attention outputs, and in backward the gradients of those tensors.  GEMM operands are therefore
+# 16-bit values, products are exact in f32 and sums are f32/f64 as before.  What stays in f32:
+# parameters' master copies, the residual stream, LayerNorm / softmax / loss arithmetic, weight and
+# bias gradients, optimizer state.  Comparing a 16-bit GPU step with this oracle isolates kernel
+# error (summation order, on-chip roundings) from the format error both sides share.
+_AMP = [None]
+
+
+class amp:
+    def __init__(self, dtype=BF16):
+        assert dtype in (BF16, F16)
+        self.dtype = dtype
+
+    def __enter__(self):
+        self.prev = _AMP[0]
+        _AMP[0] = self.dtype
+
+    def __exit__(self, *a):
+        _AMP[0] = self.prev
+
+
+def _lp(x, mode=None):
+    mode = _AMP[0] if mode is None else mode
+    if mode is None or x is None:
+        return x
+    return round_bf16(x) if mode == BF16 else round_f16(x)
 
 
 # ---------------------------------------------------------------- kernels
@@ -550,23 +626,29 @@ class F:
 
     @staticmethod
     def linear(x, w, b=None):
+        mode = _AMP[0]
+        xs, ws = _lp(x.data, mode), _lp(w.data, mode)
+
         def bwd(g):
-            dx, dw, db = linear_backward(g, x.data, w.data, b is not None)
-            return [dx, dw] + ([db] if b is not None else [])
+            dx, dw, db = linear_backward(_lp(g, mode), xs, ws, b is not None)
+            return [_lp(dx, mode), dw] + ([db] if b is not None else [])
         ins = [x, w] + ([b] if b is not None else [])
-        return _apply(linear(x.data, w.data, None if b is None else b.data), ins, bwd)
+        return _apply(_lp(linear(xs, ws, None if b is None else b.data), mode), ins, bwd)
 
     @staticmethod
     def linear_activation(x, w, b, act):
         fwd = {"relu": relu, "gelu": gelu}[act]
+        mode = _AMP[0]
+        xs, ws = _lp(x.data, mode), _lp(w.data, mode)
 
         def bwd(g):
-            pre = linear(x.data, w.data, None if b is None else b.data)
-            gp = relu_backward(pre, g) if act == "relu" else gelu_backward(pre, g)
-            dx, dw, db = linear_backward(gp, x.data, w.data, b is not None)
-            return [dx, dw] + ([db] if b is not None else [])
+            # the reference recomputes the pre-activation with a second forward product (ops.rs:936-1045)
+            pre = _lp(linear(xs, ws, None if b is None else b.data), mode)
+            gp = relu_backward(pre, _lp(g, mode)) if act == "relu" else gelu_backward(pre, _lp(g, mode))
+            dx, dw, db = linear_backward(_lp(gp, mode), xs, ws, b is not None)
+            return [_lp(dx, mode), dw] + ([db] if b is not None else [])
         ins = [x, w] + ([b] if b is not None else [])
-        return _apply(fwd(linear(x.data, w.data, None if b is None else b.data)), ins, bwd)
+        return _apply(_lp(fwd(linear(xs, ws, None if b is None else b.data)), mode), ins, bwd)
 
     @staticmethod
     def softmax(x):
@@ -574,15 +656,19 @@ class F:
 
     @staticmethod
     def layer_norm(x, gamma, beta, eps):
+        mode = _AMP[0]
+
         def bwd(g):
-            return list(layer_norm_backward(x.data, gamma.data, g, eps))
-        return _apply(layer_norm(x.data, gamma.data, beta.data, eps), [x, gamma, beta], bwd)
+            return list(layer_norm_backward(x.data, gamma.data, _lp(g, mode), eps))
+        return _apply(_lp(layer_norm(x.data, gamma.data, beta.data, eps), mode), [x, gamma, beta], bwd)
 
     @staticmethod
     def softmax_cross_entropy(logits, target):
+        mode = _AMP[0]
+
         def bwd(g):
             base = softmax_cross_entropy_backward(logits.data, target.data)
-            return [scale(base, float(g.reshape(-1)[0])), None]
+            return [_lp(scale(base, float(g.reshape(-1)[0])), mode), None]
         loss = softmax_cross_entropy(logits.data, target.data)
         return _apply(np.asarray(loss, np.float32).reshape(()), [logits, target], bwd)
 
@@ -634,9 +720,12 @@ class F:
 
     @staticmethod
     def multi_head_attention(q, k, v, heads, causal):
+        mode = _AMP[0]
+        qs, ks, vs = _lp(q.data, mode), _lp(k.data, mode), _lp(v.data, mode)
+
         def bwd(g):
-            return list(attention_backward(q.data, k.data, v.data, g, heads, causal))
-        return _apply(attention(q.data, k.data, v.data, heads, causal), [q, k, v], bwd)
+            return [_lp(t, mode) for t in attention_backward(qs, ks, vs, _lp(g, mode), heads, causal)]
+        return _apply(_lp(attention(qs, ks, vs, heads, causal), mode), [q, k, v], bwd)
 
 
 # ---------------------------------------------------------------- optimizers / AMP
