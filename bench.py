@@ -2,12 +2,13 @@
 """Benchmark of the training step: train samples/sec (fwd + bwd + GradScaler + Adam, device
 timed, max over ranks).
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c4|c2|c1|c5] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c4|c2|c3|c1|c5] [--impl ours|reference]
 
 Workloads (synthetic inputs from fixed seeds, random-init weights of the named architecture):
   c4  12-layer decoder d=768 h=12 ff=3072 vocab=32000 seq=1024 batch 8 per GPU, bf16 autocast  (default; the
       configuration the metric is quoted on)
   c2  one pre-LN encoder block d=512 h=8 ff=2048 seq=256 batch 32, bf16 autocast, MSE loss
+  c3  CNN conv3x3(3->32)-ReLU-pool-conv3x3(32->64)-ReLU-pool-Linear(4096->10) on 32x32x3 images, f32, batch 256
   c1  MLP 784-100-10, f32, batch 128
   c5  optimizer stress: flat 125M f32 parameters, bf16 gradients stored pre-multiplied by the loss scale
       2^16, inf/nan injected on odd steps; metric = HBM GB/s of the fused check + unscale + Adam pass
@@ -37,6 +38,7 @@ WORKLOADS = {
     "c4": dict(kind="decoder", vocab=32000, d=768, heads=12, ff=3072, layers=12, seq=1024, batch=8, amp=True),
     "c2": dict(kind="encoder", d=512, heads=8, ff=2048, seq=256, batch=32, amp=True),
     "c1": dict(kind="mlp", sizes=(784, 100, 10), batch=128, amp=False),
+    "c3": dict(kind="cnn", cin=3, c1=32, c2=64, hw=32, classes=10, batch=256, amp=False),
     "c5": dict(kind="optimizer", n=125_000_000),
     "gemm": dict(kind="gemm"),
 }
@@ -104,6 +106,9 @@ def make_inputs(name, cfg, rank):
         return rng.standard_normal(shape).astype(np.float32), rng.standard_normal(shape).astype(np.float32)
     if cfg["kind"] == "mlp":
         return rng.standard_normal((cfg["batch"], cfg["sizes"][0])).astype(np.float32), rng.integers(0, cfg["sizes"][-1], cfg["batch"]).astype(np.int64)
+    if cfg["kind"] == "cnn":
+        return (rng.random((cfg["batch"], cfg["cin"], cfg["hw"], cfg["hw"])).astype(np.float32),
+                rng.integers(0, cfg["classes"], cfg["batch"]).astype(np.int64))
     raise ValueError(name)
 
 
@@ -112,6 +117,8 @@ def model_cfg(cfg):
         return [cfg["vocab"], cfg["d"], cfg["heads"], cfg["ff"], cfg["layers"], 0]
     if cfg["kind"] == "encoder":
         return [cfg["d"], cfg["heads"], cfg["ff"], 0]
+    if cfg["kind"] == "cnn":
+        return [cfg["cin"], cfg["c1"], cfg["c2"], cfg["hw"], cfg["classes"]]
     return list(cfg["sizes"])
 
 
@@ -125,6 +132,12 @@ def step_flops(cfg):
     if cfg["kind"] == "encoder":
         t = cfg["batch"] * cfg["seq"]
         return 6.0 * (4 * cfg["d"] ** 2 + 2 * cfg["d"] * cfg["ff"]) * t + 14 * cfg["batch"] * cfg["heads"] * cfg["seq"] ** 2 * (cfg["d"] // cfg["heads"])
+    if cfg["kind"] == "cnn":
+        hw, c0, c1, c2 = cfg["hw"], cfg["cin"], cfg["c1"], cfg["c2"]
+        conv1 = 2.0 * hw * hw * c1 * c0 * 9            # per image: output positions x output channels x (C K K) MACs x 2
+        conv2 = 2.0 * (hw // 2) ** 2 * c2 * c1 * 9
+        fc = 2.0 * c2 * (hw // 4) ** 2 * cfg["classes"]
+        return 3.0 * cfg["batch"] * (conv1 + conv2 + fc)  # forward + data gradient + weight gradient
     s = cfg["sizes"]
     return 6.0 * cfg["batch"] * (s[0] * s[1] + s[1] * s[2])
 
@@ -355,7 +368,7 @@ def run_ours(args, dist):
                                   gbs=(r["bytes"] / sec / 1e9) if r["bytes"] and sec > 0 else None)
         dom = "gemm_tc" if "gemm_tc" in prof else max(prof, key=lambda c: prof[c]["ms"])
         r = prof[dom]
-        if dom in ("gemm_tc", "gemm_f32", "attention"):
+        if dom in ("gemm_tc", "gemm_f32", "attention", "conv"):
             achieved = r["flops"] / (r["ms"] / 1e3) / 1e12
             traffic = traffic_src = None
             if dom == "gemm_tc" and cfg["kind"] == "decoder" and (cfg["vocab"], cfg["d"], cfg["ff"], cfg["seq"], cfg["batch"]) == (32000, 768, 3072, 1024, 8):
@@ -543,7 +556,7 @@ def cpu_sample(name, threads_note=True):
         t_both = run(m1)
         t_layer = max(t_both - t_head, 1e-9)
         per_sample = cfg["layers"] * t_layer + t_head
-        desc = (f"oracle (C restatement of the reference CPU backend, {cores} OpenMP threads): fwd+bwd+Adam of 1 sequence of {seq} tokens through "
+        desc = (f"oracle (C restatement of the reference CPU backend, {cores} OpenMP threads), batch 1 of {cfg['batch']}: fwd+bwd+Adam of 1 sequence of {seq} tokens through "
                 f"1 layer ({t_layer:.2f} s) and through embedding+head+loss ({t_head:.2f} s), best of 3 each; samples/s = 1 / ({cfg['layers']}*layer + head)")
         return 1.0 / per_sample, cores, desc
     if cfg["kind"] == "encoder":
@@ -557,6 +570,19 @@ def cpu_sample(name, threads_note=True):
         opt.update(m.parameters())
         dt = time.perf_counter() - t
         return b / dt, cores, f"oracle, {cores} threads: one fwd+bwd+Adam step at batch {b} of {cfg['batch']}"
+    if cfg["kind"] == "cnn":
+        x, y = make_inputs(name, cfg, 0)
+        m, opt = ref.CNN(cfg["cin"], cfg["c1"], cfg["c2"], cfg["hw"], cfg["classes"]), ref.Adam(1e-3)
+        reps = 3
+        t = time.perf_counter()
+        for _ in range(reps):
+            ref.zero_grad(m.parameters())
+            loss = m.loss(ref.Variable.constant(x), ref.Variable.constant(y))
+            loss.backward()
+            opt.update(m.parameters())
+        dt = (time.perf_counter() - t) / reps
+        return cfg["batch"] / dt, cores, (f"oracle, {cores} threads over samples / output channels (the reference runs its conv and pool host ops on one thread): "
+                                          f"mean of {reps} full steps at batch {cfg['batch']}")
     if cfg["kind"] == "mlp":
         x, y = make_inputs(name, cfg, 0)
         m, opt = ref.MLP(cfg["sizes"]), ref.Adam(1e-3)
@@ -616,7 +642,7 @@ def main():
         res = run_reference(args, dist)
     else:
         res = run_ours(args, dist)
-        if res is not None and dist.world == 1 and not args.no_cpu_baseline and args.workload in ("c1", "c2", "c4", "c5"):
+        if res is not None and dist.world == 1 and not args.no_cpu_baseline and args.workload in ("c1", "c2", "c3", "c4", "c5"):
             v, cores, desc = cpu_sample(args.workload)
             res["cpu_baseline"] = {"value": v, "unit": res["unit"], "cores": cores, "kind": "port", "sample": desc}
     if dist.rank == 0 and res is not None:

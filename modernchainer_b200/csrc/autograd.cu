@@ -1501,6 +1501,19 @@ void AdamOpt::rollback_step(const std::vector<Var> &params) {
     }
 }
 
+void AdamOpt::rollback_steps(const std::vector<Var> &params, int64_t k) {
+    std::vector<Arena *> done;
+    for (auto &p : params) {
+        if (p->arena) {
+            int32_t &t = p->arena->step[p->arena_idx];
+            t = (int32_t)std::max<int64_t>(0, (int64_t)t - k);
+        } else {
+            auto it = state.find(p.get());
+            if (it != state.end()) it->second.t = (int32_t)std::max<int64_t>(0, (int64_t)it->second.t - k);
+        }
+    }
+}
+
 AdamOpt::~AdamOpt() {}
 
 mcb_status scaler_create(mcb_ctx *ctx, double init_scale, double growth, double backoff, int interval, Scaler **out) {
@@ -1551,14 +1564,29 @@ mcb_status scaler_step(Scaler *s, AdamOpt *opt, const std::vector<Var> &params, 
     MCB_TRY(opt->update(params, s->state_f() + 1, 1.0, s->state_i() + 1, sync ? nullptr : s->state_i() + 3));
     // 3. backoff / growth bookkeeping on the device
     MCB_TRY(mcb_scaler_update(ctx, s->state_f(), s->state_i(), (float)s->growth, (float)s->backoff, s->interval));
-    if (!sync) return MCB_OK;
+    if (!sync) {
+        s->issued_since++; // booked as applied; scaler_reconcile corrects the host counts if the device skipped it
+        return MCB_OK;
+    }
     int found = 0;
     MCB_TRY(mcb_memcpy_d2h(ctx, &found, s->state_i() + 2, sizeof(int)));
     if (found) {
         opt->rollback_step(params);
-        zero_grad(params); // the reference clears the gradients of a skipped step (amp.rs:71-76)
+        MCB_TRY(zero_grad(params)); // the reference clears the gradients of a skipped step (amp.rs:71-76)
+    } else {
+        s->issued_since++;
     }
     if (applied) *applied = found ? 0 : 1;
+    return MCB_OK;
+}
+
+mcb_status scaler_reconcile(Scaler *s, AdamOpt *opt, const std::vector<Var> &params) {
+    int32_t applied_now = 0;
+    MCB_TRY(mcb_memcpy_d2h(s->ctx, &applied_now, s->state_i() + 3, sizeof(int32_t)));
+    const int64_t skipped = s->issued_since - ((int64_t)applied_now - s->applied_seen);
+    if (skipped > 0 && opt) opt->rollback_steps(params, skipped);
+    s->issued_since = 0;
+    s->applied_seen = applied_now;
     return MCB_OK;
 }
 

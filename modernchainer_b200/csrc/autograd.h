@@ -140,6 +140,7 @@ struct AdamOpt {
     mcb_status update(const std::vector<Var> &params, const float *inv_scale_dev = nullptr, double inv_scale_host = 1.0,
                       const int32_t *skip = nullptr, const int32_t *step_dev = nullptr);
     void rollback_step(const std::vector<Var> &params);
+    void rollback_steps(const std::vector<Var> &params, int64_t k); // every listed parameter, k steps (not below zero)
     ~AdamOpt();
 };
 
@@ -148,11 +149,19 @@ struct Scaler {
     double growth = 2.0, backoff = 0.5;
     int interval = 2000;
     std::shared_ptr<Buf> state; // {scale, inv_scale} f32, {growth_tracker, found_inf, last_found_inf, applied_steps} i32
+    // Steps taken without reading the outcome back (mcb_scaler_step_async, replays of a captured step) advance the
+    // host's per-parameter step counts even when the device skipped them.  issued_since counts the steps whose
+    // outcome the host has booked as applied since the last reconciliation; applied_seen is the device's count of
+    // applied steps at that point: the difference of the two growths is the number of skipped steps still to undo.
+    int64_t issued_since = 0;
+    int32_t applied_seen = 0;
     float *state_f() const { return (float *)state->p; }
     int *state_i() const { return (int *)((float *)state->p + 2); }
 };
 mcb_status scaler_create(mcb_ctx *ctx, double init_scale, double growth, double backoff, int interval, Scaler **out);
 mcb_status scaler_step(Scaler *s, AdamOpt *opt, const std::vector<Var> &params, bool sync, int32_t *applied);
+// reads the device's count of applied steps (synchronises) and takes the skipped steps off the host's step counts
+mcb_status scaler_reconcile(Scaler *s, AdamOpt *opt, const std::vector<Var> &params);
 
 struct Model {
     mcb_ctx *ctx = nullptr;

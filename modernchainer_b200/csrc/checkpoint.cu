@@ -75,9 +75,28 @@ size_t tag_size(uint8_t tag) {
     }
 }
 
+mcb_status read_file_unchecked(mcb_ctx *ctx, const char *path, std::map<std::string, Entry> *out, std::vector<std::string> *order);
+
+// The file is untrusted input: sizes are checked against the bytes that are really there before anything is
+// allocated, products are checked for overflow, and an allocation failure becomes MCB_IO instead of leaving through
+// the C boundary as an exception.
 mcb_status read_file(mcb_ctx *ctx, const char *path, std::map<std::string, Entry> *out, std::vector<std::string> *order) {
+    try {
+        return read_file_unchecked(ctx, path, out, order);
+    } catch (const std::exception &e) {
+        return mcb_fail(ctx, MCB_IO, "reading %s failed: %s", path, e.what());
+    }
+}
+
+mcb_status read_file_unchecked(mcb_ctx *ctx, const char *path, std::map<std::string, Entry> *out, std::vector<std::string> *order) {
     FILE *f = fopen(path, "rb");
     if (!f) return mcb_fail(ctx, MCB_IO, "cannot open %s", path);
+    uint64_t file_size = 0;
+    if (fseek(f, 0, SEEK_END) == 0) {
+        long sz = ftell(f);
+        file_size = sz > 0 ? (uint64_t)sz : 0;
+    }
+    rewind(f);
     char magic[8];
     uint32_t count = 0;
     mcb_status st = MCB_OK;
@@ -102,13 +121,24 @@ mcb_status read_file(mcb_ctx *ctx, const char *path, std::map<std::string, Entry
         }
         e.dims.resize(rank);
         uint64_t numel = 1;
-        bool ok = true;
+        bool ok = true, overflow = false;
         for (uint32_t d = 0; d < rank && ok; ++d) {
             ok = get_u64(f, &e.dims[d]);
-            numel *= e.dims[d];
+            if (ok && e.dims[d] != 0 && numel > UINT64_MAX / e.dims[d]) overflow = true;
+            numel = overflow ? 0 : numel * e.dims[d];
         }
-        if (!ok || !get_u64(f, &blen) || blen != numel * tag_size(e.tag)) {
+        if (ok && !overflow && numel > UINT64_MAX / tag_size(e.tag)) overflow = true;
+        if (!ok || overflow || !get_u64(f, &blen) || blen != numel * tag_size(e.tag)) {
             st = mcb_fail(ctx, MCB_IO, "entry %s: byte length does not match its shape", e.name.c_str());
+            break;
+        }
+        const long here = ftell(f);
+        if (here < 0 || blen > file_size - (uint64_t)here) { // more bytes announced than the file still holds
+            st = mcb_fail(ctx, MCB_IO, "truncated .mcn entry %s", e.name.c_str());
+            break;
+        }
+        if (out->count(e.name)) {
+            st = mcb_fail(ctx, MCB_INVALID_ARGUMENT, "entry %s appears twice", e.name.c_str());
             break;
         }
         e.bytes.resize(blen);
@@ -154,6 +184,14 @@ mcb_status mcb_checkpoint_save(mcb_ctx *ctx, const char *path, const char *const
     MCB_CHECK_CTX(ctx);
     if (!path || n < 0 || (n > 0 && (!names || !params))) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "checkpoint_save: bad arguments");
     MCB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if (scaler && opt) {
+        // steps whose outcome was never read back (async scaler steps, graph replays) were booked as applied on the
+        // host; the device knows how many were skipped: opt_t below is the number of APPLIED steps, the value the
+        // reference's per-parameter t holds (a skipped step does not advance it, optim/src/amp.rs:66-76)
+        std::vector<Var> listed;
+        for (int32_t i = 0; i < n; ++i) listed.push_back(params[i]->v);
+        MCB_TRY(scaler_reconcile(scaler->s, &opt->opt, listed));
+    }
     std::map<Arena *, ArenaHost> arenas;
     std::vector<Entry> entries;
     for (int32_t i = 0; i < n; ++i) {
@@ -329,6 +367,10 @@ mcb_status mcb_checkpoint_load(mcb_ctx *ctx, const char *path, const char *const
     if (scaler) {
         MCB_TRY(mcb_memcpy_h2d(ctx, scaler->s->state_f(), file["grad_scaler.state"].bytes.data(), 8));
         MCB_TRY(mcb_memcpy_h2d(ctx, scaler->s->state_i(), file["grad_scaler.counters"].bytes.data(), 16));
+        int32_t counters[4];
+        memcpy(counters, file["grad_scaler.counters"].bytes.data(), 16);
+        scaler->s->issued_since = 0; // the loaded step counts are counts of applied steps
+        scaler->s->applied_seen = counters[3];
     }
     MCB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     return MCB_OK;

@@ -27,6 +27,7 @@ struct mcb_static_step {
     int capture_id = 0;
     Tensor x, y, loss;     // fixed input buffers and the (unscaled) scalar loss
     Tensor counter;        // applied steps, when no GradScaler keeps one
+    int32_t host_step_after = 0; // the host's step count as the last replay (or the creation) left it
     cudaGraphExec_t exec = nullptr;
     int64_t launches_per_step = 0;
 };
@@ -98,6 +99,18 @@ void restore_steps(Model *m, AdamOpt *opt, const std::vector<std::vector<int32_t
         ++i;
     }
 }
+// the optimizer's step count as the host knows it (largest over the model's parameters)
+int32_t host_step(Model *m, AdamOpt *opt) {
+    int32_t t0 = 0;
+    for (auto &p : m->params) {
+        if (p->arena) t0 = std::max(t0, p->arena->step[p->arena_idx]);
+        else {
+            auto it = opt->state.find(p.get());
+            if (it != opt->state.end()) t0 = std::max(t0, it->second.t);
+        }
+    }
+    return t0;
+}
 void bump_steps(Model *m, AdamOpt *opt) {
     std::vector<Arena *> seen;
     for (auto &p : m->params) {
@@ -144,15 +157,10 @@ mcb_status mcb_static_step_create(mcb_model *model, mcb_adam *opt, mcb_scaler *s
     if (!s->scaler) {
         MCB_TRY(new_tensor(ctx, MCB_I32, {1}, &s->counter));
         // continue the bias correction where the optimizer stands (0 for a fresh one)
-        int32_t t0 = 0;
-        for (auto &p : s->model->params) {
-            if (p->arena) t0 = std::max(t0, p->arena->step[p->arena_idx]);
-            else {
-                auto it = s->opt->state.find(p.get());
-                if (it != s->opt->state.end()) t0 = std::max(t0, it->second.t);
-            }
-        }
+        int32_t t0 = host_step(s->model, s->opt);
         MCB_TRY(mcb_memcpy_h2d(ctx, s->counter.ptr, &t0, sizeof(t0)));
+        MCB_TRY(mcb_sync(ctx)); // t0 is a stack object
+        s->host_step_after = t0;
     }
     // device state that the tape creates or refreshes lazily must exist before recording: a capture only
     // records the zero-fill / refresh kernels, it does not run them
@@ -249,6 +257,18 @@ mcb_status mcb_static_step_run(mcb_static_step *s, const void *host_x, const voi
     MCB_CHECK_CTX(ctx);
     if (host_x) MCB_TRY(mcb_memcpy_h2d(ctx, s->x.ptr, host_x, dt_size(s->x.dt) * (size_t)s->x.numel()));
     if (host_y) MCB_TRY(mcb_memcpy_h2d(ctx, s->y.ptr, host_y, dt_size(s->y.dt) * (size_t)s->y.numel()));
+    if (!s->scaler) {
+        // The bias correction of a step without a GradScaler reads the step's own device counter.  A checkpoint
+        // load or an eager optimizer update since the last replay moved the host's count: the counter follows.
+        const int32_t t_now = host_step(s->model, s->opt);
+        if (t_now != s->host_step_after) {
+            MCB_TRY(mcb_memcpy_h2d(ctx, s->counter.ptr, &t_now, sizeof(t_now)));
+            MCB_CUDA(ctx, cudaStreamSynchronize(ctx->stream)); // t_now is a stack object; this path is rare
+        }
+        s->host_step_after = t_now + 1;
+    } else {
+        s->scaler->issued_since++; // outcome not read back: see scaler_reconcile
+    }
     MCB_CUDA(ctx, cudaGraphLaunch(s->exec, ctx->stream));
     ctx->launches += s->launches_per_step;
     bump_steps(s->model, s->opt);

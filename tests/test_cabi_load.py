@@ -119,3 +119,52 @@ def test_chainer_facade_imports_without_a_gpu_and_refuses_to_compute():
     if not chainer.cuda_available():
         with pytest.raises(Exception):
             chainer.Variable(t)
+
+
+def test_rust_mirror_matches_the_header():
+    """include/mcb_sys.rs is generated from include/mcb.h: the committed file is what the generator gives today,
+    it declares every function of the header exactly once, and every mcb_* call in the hand-written trait
+    forwarding (include/mcb_ops.rs) names a declared function and passes as many arguments as the header lists.
+    All ten status codes appear in the status -> core::Error map."""
+    import re
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    gen = os.path.join(root, "include", "gen_rust_binding.py")
+    assert subprocess.run([sys.executable, gen, "--check"]).returncode == 0
+    from modernchainer_b200 import _lib
+    protos = _lib.parse_header()
+    sys_rs = open(os.path.join(root, "include", "mcb_sys.rs")).read()
+    declared = re.findall(r"pub fn (mcb_\w+)\(([^)]*)\)", sys_rs)
+    assert sorted(n for n, _ in declared) == sorted(protos)
+    arity = {n: (0 if not a.strip() else a.count(":")) for n, a in declared}
+    for n, (_, argtypes) in protos.items():
+        assert arity[n] == len(argtypes), n
+    ops_rs = open(os.path.join(root, "include", "mcb_ops.rs")).read()
+    ops_rs = re.sub(r"//[^\n]*", "", ops_rs)
+    calls = 0
+    for m in re.finditer(r"\b(mcb_[a-z0-9_]+)\s*\(", ops_rs):
+        name = m.group(1)
+        assert name in arity, name
+        depth, i, args, cur = 1, m.end(), 0, ""
+        while depth:
+            ch = ops_rs[i]
+            if ch in "([{":
+                depth += 1
+            elif ch in ")]}":
+                depth -= 1
+            elif ch == "," and depth == 1:
+                args += 1
+                cur = ""
+                i += 1
+                continue
+            cur += ch
+            i += 1
+        args += 1 if cur.strip(" \n)") or args else 0
+        assert args == arity[name], (name, args, arity[name])
+        calls += 1
+    assert calls >= 25
+    for code in ("MCB_OK", "MCB_SHAPE_MISMATCH", "MCB_BROADCAST", "MCB_DTYPE_MISMATCH", "MCB_UNSUPPORTED_DTYPE", "MCB_INVALID_ARGUMENT",
+                 "MCB_OUT_OF_BOUNDS", "MCB_UNSUPPORTED", "MCB_IO"):
+        assert re.search(code + r"\s*=>", ops_rs), code
+    assert "Error::Backend" in ops_rs

@@ -13,8 +13,13 @@ Tolerances (norm-wise per tensor, max |d| / max |ref|):
                  reference's sequential f32 accumulation over 10^4..10^5 terms, whose own rounding error is
                  a few 1e-6 of the result), the test also computes the same sum in f64 and requires the GPU
                  value to be at least as close to the f64 value as the oracle's is, plus 1e-5.
-  bf16/f16 AMP   2^-7 against the low-precision oracle (oracle.amp: same formulas, the tensors a 16-bit
-                 path stores in 16 bits rounded to nearest even at the same points).  The loss within 2e-3.
+  bf16/f16 AMP   against the low-precision oracle (oracle.amp: same formulas, the tensors a 16-bit path stores in
+                 16 bits rounded to nearest even at the same points, same loss scale), per tensor:
+                 ||g - o||_2 / ||o||_2 <= 2^-7 AND max |g - o| / max |o| <= 2^-6 for bf16, 2^-9 and 2^-8 for f16 (three
+                 more mantissa bits; measured errors are eight times smaller) (the single worst of up to 24.6M
+                 elements may be off by one bf16 step of the tensor's peak: on-chip roundings the oracle does not
+                 model - attention probabilities and dS in 16 bits, hardware exp2 / tanh - and the order of the
+                 f32 sums).  The loss within 2e-3.
   exact-zero gradients (the key-projection bias: softmax is shift invariant) hold only rounding noise on
                  both sides and are compared in absolute terms against the largest gradient of the model.
 """
@@ -40,15 +45,28 @@ def ctx(mc):
     c.close()
 
 
-def per_tensor_errors(ggrads, ograds, zero_grad_idx=()):
-    """max |g - o| / max |o| per tensor; the tensors in zero_grad_idx against the model's largest gradient."""
+def per_tensor_errors(ggrads, ograds, zero_grad_idx=(), l2=False):
+    """max |g - o| / max |o| per tensor (l2: ||g - o||_2 / ||o||_2); the tensors in zero_grad_idx against the
+    model's largest gradient (largest l2 norm per element count)."""
     top = max(float(np.abs(o).max()) for o in ograds)
+    top_rms = max(float(np.sqrt(np.mean(o.astype(np.float64) ** 2))) for o in ograds)
     errs = []
     for i, (g, o) in enumerate(zip(ggrads, ograds)):
         assert g is not None and g.shape == o.shape, i
-        den = top if i in zero_grad_idx else max(float(np.abs(o).max()), 1e-30)
-        errs.append(float(np.abs(g.astype(np.float64) - o).max()) / den)
+        d = g.astype(np.float64) - o
+        if l2:
+            den = top_rms if i in zero_grad_idx else max(float(np.sqrt(np.mean(o.astype(np.float64) ** 2))), 1e-30)
+            errs.append(float(np.sqrt(np.mean(d ** 2))) / den)
+        else:
+            den = top if i in zero_grad_idx else max(float(np.abs(o).max()), 1e-30)
+            errs.append(float(np.abs(d).max()) / den)
     return errs
+
+
+def check_amp(gg, og, zero_idx, what):
+    tol = AMP_TOL if "bf16" in what else AMP_TOL / 4
+    report(per_tensor_errors(gg, og, zero_idx, l2=True), tol, what + " (l2)")
+    report(per_tensor_errors(gg, og, zero_idx), 2 * tol, what + " (max)")
 
 
 def gpu_grads(mc, ctx, kind, cfg, x, y, autocast=None, scale=None):
@@ -71,17 +89,21 @@ def gpu_grads(mc, ctx, kind, cfg, x, y, autocast=None, scale=None):
     return out
 
 
-def oracle_grads(oracle, omodel, x, y, amp=None):
+def oracle_grads(oracle, omodel, x, y, amp=None, scale=None):
+    """amp: the 16-bit type of the low-precision oracle; the loss is scaled like the GPU step scales it (f16 gradients
+    of an unscaled loss underflow: that is what the GradScaler is for) and the gradients are unscaled afterwards."""
     ox, oy = oracle.Variable.constant(x), oracle.Variable.constant(y)
     with oracle.threaded():
         if amp is None:
             loss = omodel.loss(ox, oy)
             loss.backward()
+            grads = [p.grad for p in omodel.parameters()]
         else:
             with oracle.amp(amp):
                 loss = omodel.loss(ox, oy)
-                loss.backward()
-    return float(loss.data.reshape(-1)[0]), [p.grad for p in omodel.parameters()]
+                oracle.GradScaler(scale).scale_loss(loss).backward()
+            grads = [p.grad / np.float32(scale) for p in omodel.parameters()]
+    return float(loss.data.reshape(-1)[0]), grads
 
 
 def decoder_batch(rng, vocab, b, s):
@@ -97,6 +119,7 @@ def decoder_key_bias(layers):
 
 def report(errs, tol, what):
     worst = int(np.argmax(errs))
+    print("%s: worst tensor %d %.3e (limit %.3e); all: %s" % (what, worst, errs[worst], tol, ["%.1e" % e for e in errs]))
     assert errs[worst] <= tol, "%s: tensor %d off by %.3e > %.3e; all: %s" % (what, worst, errs[worst], tol, ["%.1e" % e for e in errs])
 
 
@@ -121,7 +144,7 @@ def test_c4_layer_and_head_f32_at_full_width(mc, ctx, oracle):
 def test_c4_layer_and_head_amp_at_full_width(mc, ctx, oracle, lowp):
     """The same model under autocast with two sequences (2048 rows: pair-tile GEMMs with the split tail,
     bulk-copy LayerNorm forward and backward with their by-products, packed q/k/v attention over eight
-    query tiles, streaming loss gradient) against the low-precision oracle at 2^-7."""
+    query tiles, streaming loss gradient) against the low-precision oracle."""
     rng = np.random.default_rng(1241)
     c = C4
     dt = mc.BF16 if lowp == "bf16" else mc.F16
@@ -129,9 +152,9 @@ def test_c4_layer_and_head_amp_at_full_width(mc, ctx, oracle, lowp):
     ids, tgt = decoder_batch(rng, c["vocab"], 2, c["seq"])
     cfg = [c["vocab"], c["d"], c["heads"], c["ff"], 1, 0]
     lg, gg, _ = gpu_grads(mc, ctx, "decoder", cfg, ids, tgt, autocast=dt, scale=65536.0)
-    lo, og = oracle_grads(oracle, oracle.Decoder(*cfg), ids, tgt, amp=odt)
+    lo, og = oracle_grads(oracle, oracle.Decoder(*cfg), ids, tgt, amp=odt, scale=65536.0)
     assert abs(lg - lo) <= 2e-3 * abs(lo), (lg, lo)
-    report(per_tensor_errors(gg, og, decoder_key_bias(1)), AMP_TOL, "c4 " + lowp)
+    check_amp(gg, og, decoder_key_bias(1), "c4 " + lowp)
 
 
 # ------------------------------------------------------------------ C2: encoder block d=512 / 8 heads / ff 2048 / seq 256
@@ -163,9 +186,9 @@ def test_c2_block_amp_at_full_size(mc, ctx, oracle, lowp):
     x, t = encoder_batch(rng, 32, 256, 512)
     cfg = [512, 8, 2048, 0]
     lg, gg, _ = gpu_grads(mc, ctx, "encoder", cfg, x, t, autocast=dt, scale=65536.0)
-    lo, og = oracle_grads(oracle, oracle.EncoderBlock(512, 8, 2048), x, t, amp=odt)
+    lo, og = oracle_grads(oracle, oracle.EncoderBlock(512, 8, 2048), x, t, amp=odt, scale=65536.0)
     assert abs(lg - lo) <= 2e-3 * abs(lo), (lg, lo)
-    report(per_tensor_errors(gg, og, ENC_KEY_BIAS), AMP_TOL, "c2 " + lowp)
+    check_amp(gg, og, ENC_KEY_BIAS, "c2 " + lowp)
 
 
 # ------------------------------------------------------------------ C3: the CNN at 32x32x3, channels 32/64, batch 256

@@ -5,9 +5,16 @@ the reference's own test programs restated call for call:
   crates/modern-chainer-cuda/tests/cuda.rs:110-153, 764-803 (training loops: loss decreases)
 and full fwd+bwd+Adam steps of the four benchmark models at reduced sizes.
 
-f32 tolerance: 1e-5 relative, norm-wise per tensor (2e-5 where two reductions chain).
-bf16 autocast tolerance: gradients within 5e-2 and the loss within 2e-2 relative of the f32
-oracle (stated for AMP; bf16 has 8 significant bits and the block chains ~10 rounded GEMMs)."""
+f32 tolerance: 1e-5 relative, norm-wise per tensor (max |d| / max |ref|), for single ops (2e-5 where two
+reductions chain) and for whole training steps alike.  Gradients that are zero in exact arithmetic (the
+key-projection bias: softmax is shift invariant) hold rounding noise on both sides and are measured against
+the model's largest gradient.
+bf16 autocast tolerance at these reduced sizes: per tensor ||g - o||_2 / ||o||_2 <= 2^-5 and max |g - o| / max |o| <= 2^-4
+(2^-7 / 2^-6 at the benchmark widths, tests/test_gpu_parity_full.py; f16 four times tighter) against
+the LOW-PRECISION oracle (oracle.amp(BF16): same formulas, 16-bit rounding at the points where the GPU path
+stores 16 bits, same loss scale), which separates kernel error from the format error both sides share; the
+loss within 2e-3.  Against the f32 oracle only the loose bound of the reference's own mixed-precision tests
+is kept (loss within 2e-2; its bars are absolute 0.15 / 0.3 on outputs, cuda/tests/cuda.rs:643,711)."""
 import numpy as np
 import pytest
 
@@ -255,7 +262,7 @@ def test_adam_fits_linear_regression(mc, ctx):
 
 
 # ------------------------------------------------------------------ full training steps of the benchmark models
-def run_step(mc, ctx, oracle, kind, cfg, omodel, x, y, y_is_label, arena, steps=2, lr=1e-3):
+def run_step(mc, ctx, oracle, kind, cfg, omodel, x, y, y_is_label, arena, steps=2, lr=1e-3, zero_idx=()):
     gm = mc.Model(ctx, kind, cfg)
     gparams, oparams = gm.parameters(), omodel.parameters()
     assert len(gparams) == len(oparams)
@@ -276,13 +283,13 @@ def run_step(mc, ctx, oracle, kind, cfg, omodel, x, y, y_is_label, arena, steps=
         ol.backward()
         ggrads = [a.grad for a in gparams]
         assert all(g is not None for g in ggrads)
-        # norm-wise per tensor, with a floor of 1e-2 of the largest gradient in the model: some
-        # gradients are exactly zero in exact arithmetic (the key-projection bias: softmax is
-        # shift invariant), so both sides hold only rounding noise there
-        floor = 1e-2 * max(float(np.abs(b.grad).max()) for b in oparams)
+        # norm-wise per tensor at 1e-5; tensors whose gradient is exactly zero in exact arithmetic (zero_idx: the
+        # key-projection biases) hold only rounding noise on both sides and are measured against the model's peak
+        top = max(float(np.abs(b.grad).max()) for b in oparams)
         for i, (g, b) in enumerate(zip(ggrads, oparams)):
-            err = np.abs(g.astype(np.float64) - b.grad).max() / max(float(np.abs(b.grad).max()), floor)
-            assert err <= 5e-5, (i, err)
+            den = top if i in zero_idx else max(float(np.abs(b.grad).max()), 1e-30)
+            err = np.abs(g.astype(np.float64) - b.grad).max() / den
+            assert err <= 1e-5, (i, err)
         gopt.update(gparams)
         # Adam's first steps move every weight by ~lr whatever the gradient's size, so a 1e-5
         # difference in a near-zero gradient is amplified; the optimizer itself is checked bit-exactly
@@ -308,7 +315,7 @@ def test_encoder_block_step_f32(mc, ctx, oracle, arena):
     d, heads, ff, s, b = 64, 4, 128, 24, 3
     x = rng.standard_normal((b, s, d)).astype(np.float32)
     t = rng.standard_normal((b, s, d)).astype(np.float32)
-    run_step(mc, ctx, oracle, "encoder", [d, heads, ff, 0], oracle.EncoderBlock(d, heads, ff), x, t, False, arena)
+    run_step(mc, ctx, oracle, "encoder", [d, heads, ff, 0], oracle.EncoderBlock(d, heads, ff), x, t, False, arena, zero_idx={5})
 
 
 def test_cnn_step_c3_reduced(mc, ctx, oracle):
@@ -323,54 +330,74 @@ def test_decoder_step_f32_reduced(mc, ctx, oracle):
     vocab, d, heads, ff, layers, s, b = 97, 32, 4, 64, 2, 16, 2
     ids = rng.integers(0, vocab, (b, s)).astype(np.int64)
     tgt = np.concatenate([ids[:, 1:], rng.integers(0, vocab, (b, 1))], 1).astype(np.int64)
-    run_step(mc, ctx, oracle, "decoder", [vocab, d, heads, ff, layers, 0], oracle.Decoder(vocab, d, heads, ff, layers, 0), ids, tgt, True, True)
+    run_step(mc, ctx, oracle, "decoder", [vocab, d, heads, ff, layers, 0], oracle.Decoder(vocab, d, heads, ff, layers, 0), ids, tgt, True, True,
+             zero_idx={1 + 16 * l + 5 for l in range(layers)})
 
 
-def amp_step(mc, ctx, oracle, kind, cfg, omodel, x, y, steps=3):
+def amp_step(mc, ctx, oracle, kind, cfg, make_omodel, x, y, zero_idx, steps=3, lowp="bf16"):
+    dt, odt = (mc.BF16, oracle.BF16) if lowp == "bf16" else (mc.F16, oracle.F16)
+    # 2^-7 (bf16) / 2^-9 (f16: three more mantissa bits, errors eight times smaller) is what the steps at the benchmark
+    # widths hold (tests/test_gpu_parity_full.py).  At these toy sizes a bias gradient is a sum over 128 rows of
+    # values of both signs: the 16-bit rounding noise of its terms does not average out against so small a sum
+    # (measured: 2.7 times the limit on the query bias of the second layer), hence four times the limits here.
+    l2_tol = 4 * (2.0 ** -7 if lowp == "bf16" else 2.0 ** -9)
     gm = mc.Model(ctx, kind, cfg)
-    gparams, oparams = gm.parameters(), omodel.parameters()
+    gparams = gm.parameters()
     keep = mc.Arena(ctx, gparams)
     gopt, gs = mc.Adam(ctx, 1e-3), mc.GradScaler(ctx, 65536.0)
     gx, gy = mc.Variable.constant(ctx, x), mc.Variable.constant(ctx, y)
     ox, oy = oracle.Variable.constant(x), oracle.Variable.constant(y)
-    ol = omodel.loss(ox, oy)
-    ol.backward()
+    of32 = make_omodel()
+    lf32 = float(of32.loss(ox, oy).data.reshape(-1)[0])
+    olow = make_omodel()
+    with oracle.amp(odt):
+        ol = olow.loss(ox, oy)
+        oracle.GradScaler(65536.0).scale_loss(ol).backward()
+    ograds = [p.grad / np.float32(65536.0) for p in olow.parameters()]
     losses = []
     for step in range(steps):
         mc.zero_grad(gparams)
-        with mc.autocast(mc.BF16):
+        with mc.autocast(dt):
             gl = gm.loss(gx, gy)
         gs.scale_loss(gl).backward()
         if step == 0:
             lg, lo = float(gl.data.reshape(-1)[0]), float(ol.data.reshape(-1)[0])
-            assert abs(lg - lo) <= 2e-2 * abs(lo), (lg, lo)
-            # floor: the key-projection bias has a zero gradient in exact arithmetic; under bf16 both
-            # sides hold rounding noise there, a few 1e-4 of the model's largest gradient
-            floor = 5e-2 * max(float(np.abs(b.grad).max()) for b in oparams)
-            for i, (a, b) in enumerate(zip(gparams, oparams)):
-                g = a.grad / np.float32(65536.0)
-                err = np.abs(g - b.grad).max() / max(float(np.abs(b.grad).max()), floor)
-                assert err <= 5e-2, (i, err)
+            assert abs(lg - lo) <= 2e-3 * abs(lo), (lg, lo)
+            assert abs(lg - lf32) <= 2e-2 * abs(lf32), (lg, lf32)  # the loose bound against plain f32
+            top = max(float(np.abs(o).max()) for o in ograds)
+            top_rms = max(float(np.sqrt(np.mean(o.astype(np.float64) ** 2))) for o in ograds)
+            worst = (0.0, 0.0, -1)
+            for i, (a, o) in enumerate(zip(gparams, ograds)):
+                d = a.grad.astype(np.float64) / 65536.0 - o
+                zero = i in zero_idx
+                e_max = float(np.abs(d).max()) / (top if zero else max(float(np.abs(o).max()), 1e-30))
+                e_l2 = float(np.sqrt(np.mean(d ** 2))) / (top_rms if zero else max(float(np.sqrt(np.mean(o.astype(np.float64) ** 2))), 1e-30))
+                worst = max(worst, (e_l2 / l2_tol, e_max / (2 * l2_tol), i))
+            print("amp parity %s %s: worst tensor %d at %.2f of its l2 limit, %.2f of its max limit" % (kind, lowp, worst[2], worst[0], worst[1]))
+            assert worst[0] <= 1.0 and worst[1] <= 1.0, worst
         assert gs.step(gopt, gparams) is True
         losses.append(float(gl.data.reshape(-1)[0]))
     assert losses[-1] < losses[0]  # every step applied and the loss goes down (cuda.rs:764-803)
     return losses
 
 
-def test_encoder_block_amp_c2_reduced(mc, ctx, oracle):
+@pytest.mark.parametrize("lowp", ["bf16", "f16"])
+def test_encoder_block_amp_c2_reduced(mc, ctx, oracle, lowp):
     rng = np.random.default_rng(1238)
     d, heads, ff, s, b = 128, 2, 256, 64, 4
     x = rng.standard_normal((b, s, d)).astype(np.float32)
     t = rng.standard_normal((b, s, d)).astype(np.float32)
-    amp_step(mc, ctx, oracle, "encoder", [d, heads, ff, 0], oracle.EncoderBlock(d, heads, ff), x, t)
+    amp_step(mc, ctx, oracle, "encoder", [d, heads, ff, 0], lambda: oracle.EncoderBlock(d, heads, ff), x, t, {5}, lowp=lowp)
 
 
-def test_decoder_amp_c4_reduced(mc, ctx, oracle):
+@pytest.mark.parametrize("lowp", ["bf16", "f16"])
+def test_decoder_amp_c4_reduced(mc, ctx, oracle, lowp):
     rng = np.random.default_rng(1239)
     vocab, d, heads, ff, layers, s, b = 512, 128, 2, 256, 2, 64, 2
     ids = rng.integers(0, vocab, (b, s)).astype(np.int64)
     tgt = np.concatenate([ids[:, 1:], rng.integers(0, vocab, (b, 1))], 1).astype(np.int64)
-    amp_step(mc, ctx, oracle, "decoder", [vocab, d, heads, ff, layers, 0], oracle.Decoder(vocab, d, heads, ff, layers, 0), ids, tgt)
+    amp_step(mc, ctx, oracle, "decoder", [vocab, d, heads, ff, layers, 0], lambda: oracle.Decoder(vocab, d, heads, ff, layers, 0), ids, tgt,
+             {1 + 16 * l + 5 for l in range(layers)}, lowp=lowp)
 
 
 @pytest.mark.parametrize("cfg", [(1000, 256, 4, 512, 2, 192, 2), (2048, 768, 12, 3072, 2, 1024, 8)])

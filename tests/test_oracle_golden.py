@@ -308,3 +308,82 @@ def test_oracle_mcn_container_roundtrip_and_byte_layout(tmp_path):
     open(path, "wb").write(b"NOTMCHN1" + raw[8:])
     with pytest.raises(ValueError):
         oracle.mcn_load(path)
+
+
+def test_threaded_oracle_is_bit_identical(oracle):
+    """The "threaded" oracle mode (full-size parity cases) spreads independent loop iterations over host
+    cores; every value is produced by the same operations in the same order as in the one-thread checker:
+    a decoder step, a >= 1M-MAC GEMM family, attention and the convolution pair, bit for bit."""
+    rng = np.random.default_rng(3)
+
+    def run():
+        out = []
+        m = oracle.Decoder(160, 64, 2, 128, 1, 0)
+        ids = np.random.default_rng(1).integers(0, 160, (2, 48)).astype(np.int64)
+        loss = m.loss(oracle.Variable.constant(ids), oracle.Variable.constant(ids))
+        loss.backward()
+        out += [loss.data] + [p.grad for p in m.parameters()]
+        x, w, g = (np.random.default_rng(s).standard_normal(sh).astype(np.float32) for s, sh in ((4, (130, 200)), (5, (70, 200)), (6, (130, 70))))
+        out += [oracle.linear(x, w), oracle.matmul(x, np.ascontiguousarray(w.T))] + [t for t in oracle.linear_backward(g, x, w) if t is not None]
+        xi = np.random.default_rng(7).random((3, 4, 9, 9)).astype(np.float32)
+        wc = np.random.default_rng(8).standard_normal((5, 4, 3, 3)).astype(np.float32)
+        gc = np.random.default_rng(9).standard_normal((3, 5, 9, 9)).astype(np.float32)
+        out += [oracle.conv2d(xi, wc, None, 1, 1)] + list(oracle.conv2d_backward(xi, wc, gc, 1, 1))
+        return out
+
+    a = run()
+    with oracle.threaded():
+        b = run()
+    assert len(a) == len(b) and all(np.array_equal(p, q) for p, q in zip(a, b))
+
+
+def test_f16_conversion_follows_the_reference_rule(oracle):
+    """core/src/dtype.rs:75-134.  In the normal range of f16, for overflow, infinities and NaN the reference rule
+    is IEEE round-to-nearest-even, so numpy's float16 gives the expected bits; in the subnormal range the
+    reference's own bias arithmetic is restated as written (it is close to truncation there), pinned by hand-worked cases."""
+    rng = np.random.default_rng(12)
+    x = np.concatenate([rng.standard_normal(20000).astype(np.float32) * 30, np.array([65504.0, 65519.99, 65520.0, 1e9, -1e9, np.inf, -np.inf, 0.0, -0.0, 1.0009765625,
+                                                                                      1.00048828125, 1.00146484375, 6.103515625e-05, 1e-10], np.float32)])
+    normal = (np.abs(x) >= 2.0 ** -14) | (x == 0) | (np.abs(x) < 2.0 ** -25)
+    with np.errstate(over="ignore"):
+        want = x.astype(np.float16).view(np.uint16)
+    got = oracle.f32_to_f16_bits(x)
+    assert np.array_equal(got[normal], want[normal])
+    assert np.array_equal(oracle.f16_bits_to_f32(want), want.view(np.float16).astype(np.float32))  # widening is exact
+    nan_bits = int(oracle.f32_to_f16_bits(np.array([np.nan], np.float32))[0])
+    assert (nan_bits & 0x7c00) == 0x7c00 and (nan_bits & 0x200)  # quiet NaN
+    # subnormal results, worked through the reference's arithmetic: m = frac | 0x800000, shift = 14 - h_exp,
+    # h = (m + ((m >> (shift - 1)) & 1) + 0xfff) >> shift
+    #   2^-15            exp 112, h_exp 0, shift 14, m = 0x800000: bit 13 of m is 0 -> (0x800000 + 0xfff) >> 14 = 0x200
+    #   1.5 * 2^-24      exp 103, h_exp -9, shift 23, m = 0xC00000: bit 22 is 1 -> (0xC00000 + 0x1000) >> 23 = 1
+    #   1.999 * 2^-24    truncates to 1 as well (IEEE would round it to 2)
+    sub = np.array([2.0 ** -15, 1.5 * 2.0 ** -24, 1.999 * 2.0 ** -24], np.float32)
+    assert oracle.f32_to_f16_bits(sub).tolist() == [0x200, 1, 1]
+    assert float(oracle.round_f16(np.array([2.0 ** -26], np.float32))[0]) == 0.0  # below 2^-25: signed zero
+
+
+def test_low_precision_oracle_rounds_where_a_16_bit_step_stores(oracle):
+    """oracle.amp(): every Linear output is a 16-bit value, GEMM operands are 16-bit values, the result differs
+    from the f32 oracle by format error only, and f16 (11 bits) lands about 8 times closer than bf16 (8 bits)."""
+    rng = np.random.default_rng(21)
+    x = oracle.Variable.constant(rng.standard_normal((2, 16, 32)).astype(np.float32))
+    t = oracle.Variable.constant(rng.standard_normal((2, 16, 32)).astype(np.float32))
+
+    def grads(mode):
+        m = oracle.EncoderBlock(32, 2, 64)
+        if mode is None:
+            m.loss(x, t).backward()
+        else:
+            with oracle.amp(mode):
+                y = oracle.F.linear(oracle.Variable.constant(x.data.reshape(32, 32)), m.w1.W, m.w1.b)
+                rounded = oracle.round_bf16(y.data) if mode == oracle.BF16 else oracle.round_f16(y.data)
+                assert np.array_equal(y.data, rounded)
+                oracle.GradScaler(1024.0).scale_loss(m.loss(x, t)).backward()
+            for p in m.parameters():
+                p.grad = p.grad / np.float32(1024.0)
+        return [p.grad for p in m.parameters()]
+
+    f32, b16, h16 = grads(None), grads(oracle.BF16), grads(oracle.F16)
+    eb = max(np.abs(a - r).max() / np.abs(r).max() for a, r in zip(b16, f32) if np.abs(r).max() > 1e-6)
+    eh = max(np.abs(a - r).max() / np.abs(r).max() for a, r in zip(h16, f32) if np.abs(r).max() > 1e-6)
+    assert 1e-4 < eb < 5e-2 and eh < eb / 3
