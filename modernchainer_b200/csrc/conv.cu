@@ -2,7 +2,7 @@
 // (host loops on every backend in the reference, autograd/src/host_ops.rs:40-180,341-476).
 // Direct kernels: one thread per output element for forward / dx, one block per weight
 // element for dw (tree reduction over n*oh*ow terms), column sums for db.
-#include "common.cuh"
+#include "internal.h"
 
 namespace {
 
@@ -89,18 +89,26 @@ __global__ void conv2d_dw_kernel(const float *__restrict__ x, const float *__res
     if (threadIdx.x == 0) dw[wi] = sum;
 }
 
-// one block per output channel
-__global__ void conv2d_db_kernel(const float *__restrict__ g, float *__restrict__ db, ConvDims d) {
+// bias gradient: block (channel, part) sums the planes of the samples part, part + parts, ...; a second kernel adds the
+// parts of each channel in a fixed order
+__global__ void conv2d_db_partial_kernel(const float *__restrict__ g, float *__restrict__ partial, ConvDims d) {
     __shared__ float red[32];
-    int oi = blockIdx.x;
-    long long plane = (long long)d.oh * d.ow, terms = (long long)d.n * plane;
+    const int oi = blockIdx.x, part = blockIdx.y, parts = gridDim.y;
+    const int plane = d.oh * d.ow;
     float sum = 0.0f;
-    for (long long t = threadIdx.x; t < terms; t += blockDim.x) {
-        long long ni = t / plane, r = t % plane;
-        sum += g[(ni * d.o + oi) * plane + r];
+    for (int ni = part; ni < d.n; ni += parts) {
+        const float *src = g + ((long long)ni * d.o + oi) * plane;
+        for (int r = threadIdx.x; r < plane; r += blockDim.x) sum += src[r];
     }
     sum = block_sum(sum, red);
-    if (threadIdx.x == 0) db[oi] = sum;
+    if (threadIdx.x == 0) partial[(long long)part * d.o + oi] = sum;
+}
+__global__ void conv2d_db_final_kernel(const float *__restrict__ partial, int parts, int o, float *__restrict__ db) {
+    int oi = blockIdx.x * blockDim.x + threadIdx.x;
+    if (oi >= o) return;
+    float t = 0.0f;
+    for (int p = 0; p < parts; ++p) t += partial[(long long)p * o + oi];
+    db[oi] = t;
 }
 
 struct PoolDims {
@@ -192,6 +200,9 @@ mcb_status mcb_conv2d(mcb_ctx *ctx, const float *x, const float *w, const float 
     MCB_TRY(make_conv_dims(ctx, d, n, c, h, wd, o, kh, kw, stride, pad));
     long long total = (long long)d.n * d.o * d.oh * d.ow;
     if (total == 0) return MCB_OK;
+    // large convolutions: column matrix + tensor-core GEMMs at f32 accuracy (conv_tc.cu); small ones: direct kernels
+    if (mcb_conv_tc_eligible(n, c, h, wd, o, kh, kw, stride, pad)) return mcb_conv_tc_forward(ctx, x, w, bias, out, n, c, h, wd, o, kh, kw, stride, pad);
+    ProfScope prof(ctx, MCB_PROF_CONV, 2.0 * (double)total * d.c * d.kh * d.kw, 4.0 * ((double)n * c * h * wd + (double)total));
     conv2d_fwd_kernel<<<mcb_grid_for(ctx, total, 256, 16), 256, 0, ctx->stream>>>(x, w, bias, out, d);
     MCB_LAUNCHED(ctx);
     return MCB_OK;
@@ -204,6 +215,13 @@ mcb_status mcb_conv2d_backward(mcb_ctx *ctx, const float *x, const float *w, con
     ConvDims d;
     MCB_TRY(make_conv_dims(ctx, d, n, c, h, wd, o, kh, kw, stride, pad));
     long long nx = (long long)d.n * d.c * d.h * d.w, nw = (long long)d.o * d.c * d.kh * d.kw;
+    if (mcb_conv_tc_eligible(n, c, h, wd, o, kh, kw, stride, pad) && nx && nw) {
+        MCB_TRY(mcb_conv_tc_backward(ctx, x, w, g, dx, dw, n, c, h, wd, o, kh, kw, stride, pad));
+        dx = nullptr;
+        dw = nullptr; // the bias gradient below is a plain reduction in either case
+    }
+    ProfScope prof(ctx, MCB_PROF_CONV, 2.0 * (double)d.n * d.o * d.oh * d.ow * d.c * d.kh * d.kw * ((dx ? 1 : 0) + (dw ? 1 : 0)),
+                   4.0 * ((double)nx * (dx ? 2 : 1) + (double)d.n * d.o * d.oh * d.ow));
     if (dx && nx) {
         conv2d_dx_kernel<<<mcb_grid_for(ctx, nx, 256, 16), 256, 0, ctx->stream>>>(g, w, dx, d);
         MCB_LAUNCHED(ctx);
@@ -213,7 +231,14 @@ mcb_status mcb_conv2d_backward(mcb_ctx *ctx, const float *x, const float *w, con
         MCB_LAUNCHED(ctx);
     }
     if (db && d.o) {
-        conv2d_db_kernel<<<(unsigned)d.o, 256, 0, ctx->stream>>>(g, db, d);
+        int parts = (ctx->sm_count * 4 + d.o - 1) / d.o;
+        if (parts > d.n) parts = d.n;
+        if (parts < 1) parts = 1;
+        void *scratch;
+        MCB_TRY(mcb_scratch(ctx, sizeof(float) * (size_t)parts * d.o, &scratch));
+        conv2d_db_partial_kernel<<<dim3((unsigned)d.o, (unsigned)parts), 256, 0, ctx->stream>>>(g, (float *)scratch, d);
+        MCB_LAUNCHED(ctx);
+        conv2d_db_final_kernel<<<(d.o + 127) / 128, 128, 0, ctx->stream>>>((const float *)scratch, parts, d.o, db);
         MCB_LAUNCHED(ctx);
     }
     return MCB_OK;

@@ -401,6 +401,32 @@ def test_conv2d(ops, oracle, shape, wshape, stride, pad):
         close(a, r, 2e-5)
 
 
+@pytest.mark.parametrize("shape,wshape,stride,pad", [((32, 16, 16, 16), (32, 16, 3, 3), 1, 1), ((64, 8, 33, 31), (16, 8, 3, 3), 2, 1),
+                                                     ((16, 4, 24, 24), (24, 4, 5, 5), 1, 2)])
+def test_conv2d_tensor_core_path(ops, oracle, shape, wshape, stride, pad):
+    """From about 2^24 multiply-adds on, convolution runs as a column matrix and tensor-core GEMMs over f16 hi / lo
+    pieces of the f32 operands (three GEMMs per product: exact f16 products, f32 accumulation, the dropped lo x lo
+    term is 2^-22 of the result).  Against the oracle at the f32 bar, and against the direct f32 kernels
+    (MCB_CONV_DIRECT) much closer than that; strides, paddings, a 5x5 kernel whose column count (100) is padded to 104."""
+    import os
+    x, w, b = randn(*shape), randn(*wshape) * 0.2, randn(wshape[0])
+    out = ops.conv2d(x, w, b, stride, pad)
+    g = randn(*out.shape)
+    with oracle.threaded():
+        close(out, oracle.conv2d(x, w, b, stride, pad), 1e-5)
+        ref = oracle.conv2d_backward(x, w, g, stride, pad)
+    got = ops.conv2d_backward(x, w, g, stride, pad)
+    for a, r in zip(got, ref):
+        close(a, r, 1e-5)
+    os.environ["MCB_CONV_DIRECT"] = "1"
+    try:
+        close(out, ops.conv2d(x, w, b, stride, pad), 2e-6)
+        for a, r in zip(got, ops.conv2d_backward(x, w, g, stride, pad)):
+            close(a, r, 2e-6)
+    finally:
+        os.environ.pop("MCB_CONV_DIRECT", None)
+
+
 def test_max_pool_tie_rule(ops, oracle):
     x = randn(3, 4, 8, 8)
     x[0, 0, 0:2, 0:2] = 1.5   # four equal maxima: first of each window row gets the gradient

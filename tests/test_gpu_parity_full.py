@@ -193,33 +193,83 @@ def test_c2_block_amp_at_full_size(mc, ctx, oracle, lowp):
 
 # ------------------------------------------------------------------ C3: the CNN at 32x32x3, channels 32/64, batch 256
 def test_c3_cnn_f32_at_full_size(mc, ctx, oracle):
-    """Configuration 3 as stated.  The oracle follows the reference's single loop nest, which adds the
-    262144 terms of every conv1 weight gradient one after the other in f32; its own rounding error is
-    of the order of the 1e-5 bar, so each gradient is also formed in f64 (numpy, exact to 1e-15) from the oracle's
-    upstream gradients, and the GPU value has to be within 1e-5 of the oracle OR at least as close to the
-    f64 value as the oracle is, plus 1e-5."""
+    """Configuration 3 as stated, with the convolutions on their tensor-core path (column matrix + f16 hi/lo GEMMs).
+
+    ReLU and max-pooling make the gradient a discontinuous function of the forward values: where a pre-activation is
+    within rounding distance of zero, or the two largest entries of a pooling window within rounding distance of each
+    other, two correct f32 implementations route the gradient differently and a single such flip moves a weight
+    gradient by about 1 / sqrt(#terms) of its size.  The test therefore separates the two questions:
+      (1) gating: the GPU's ReLU masks and pooling choices agree with the oracle's except for at most 1e-5 of the
+          decisions, and the loss agrees to 1e-5;
+      (2) arithmetic: with the GPU's own gating decisions imposed, every parameter gradient is within 1e-5 (norm-wise)
+          of the same backward pass carried out in f64.
+    When no decision differs at all, the gradients are also compared with the oracle directly at 1e-5 (or, where the
+    oracle's sequential f32 sums of 262144 terms are themselves further from f64 than that, the GPU must be at least
+    as close to f64 as the oracle is, plus 1e-5)."""
     rng = np.random.default_rng(1244)
     x = rng.random((256, 3, 32, 32)).astype(np.float32)
     y = rng.integers(0, 10, 256).astype(np.int64)
-    cfg = [3, 32, 64, 32, 10]
-    lg, gg, _ = gpu_grads(mc, ctx, "cnn", cfg, x, y)
+    F = mc.F
+    gm = mc.Model(ctx, "cnn", [3, 32, 64, 32, 10])   # the model's seeded parameters; the tape below is the model's own op sequence
+    w1, b1, w2, b2, wf, bf = gm.parameters()
+    keep = mc.Arena(ctx, gm.parameters())
+    gx, gy = mc.Variable.constant(ctx, x), mc.Variable.constant(ctx, y)
+    z1 = F.conv2d(gx, w1, b1, 1, 1)
+    a1 = F.relu(z1)
+    p1 = F.max_pool2d(a1, 2, 2, 0)
+    z2 = F.conv2d(p1, w2, b2, 1, 1)
+    a2 = F.relu(z2)
+    p2 = F.max_pool2d(a2, 2, 2, 0)
+    loss = F.softmax_cross_entropy(F.linear(F.reshape(p2, (256, 4096)), wf, bf), gy)
+    model_loss = gm.loss(gx, gy)
+    assert float(loss.data) == float(model_loss.data)  # same ops as the model's own forward
+    loss.backward()
+    gg = [p.grad for p in (w1, b1, w2, b2, wf, bf)]
+    gating = [(z1.data > 0), pool_choice(a1.data), (z2.data > 0), pool_choice(a2.data)]
+
     om = oracle.CNN(3, 32, 64, 32, 10)
-    lo, og = oracle_grads(oracle, om, x, y)
+    ox, oy = oracle.Variable.constant(x), oracle.Variable.constant(y)
+    with oracle.threaded():
+        oz1 = oracle.F.conv2d(ox, om.c1.W, om.c1.b, 1, 1)
+        oa1 = oracle.F.relu(oz1)
+        op1 = oracle.F.max_pool2d(oa1, 2, 2, 0)
+        oz2 = oracle.F.conv2d(op1, om.c2.W, om.c2.b, 1, 1)
+        oa2 = oracle.F.relu(oz2)
+        op2 = oracle.F.max_pool2d(oa2, 2, 2, 0)
+        ol = oracle.F.softmax_cross_entropy(oracle.F.linear(oracle.F.reshape(op2, (256, 4096)), om.fc.W, om.fc.b), oy)
+        ol.backward()
+    og = [p.grad for p in om.parameters()]
+    lg, lo = float(loss.data), float(ol.data)
     assert abs(lg - lo) <= F32_TOL * abs(lo), (lg, lo)
-    errs = per_tensor_errors(gg, og)
-    exact = cnn_grads_f64(om, x, y)
-    for i, e in enumerate(errs):
-        if e <= F32_TOL:
-            continue
-        den = max(float(np.abs(exact[i]).max()), 1e-30)
-        e_gpu = float(np.abs(gg[i] - exact[i]).max()) / den
-        e_orc = float(np.abs(og[i] - exact[i]).max()) / den
-        assert e_gpu <= e_orc + F32_TOL, "c3 tensor %d: gpu %.3e from f64, oracle %.3e from f64 (gpu vs oracle %.3e)" % (i, e_gpu, e_orc, e)
+    ogating = [(oz1.data > 0), pool_choice(oa1.data), (oz2.data > 0), pool_choice(oa2.data)]
+    flips = [int((a != b).sum()) for a, b in zip(gating, ogating)]
+    sizes = [a.size for a in gating]
+    print("c3 gating decisions that differ from the oracle's:", flips, "of", sizes)
+    assert all(f <= 1e-5 * n for f, n in zip(flips, sizes)), (flips, sizes)
+
+    exact = cnn_grads_f64(om, x, y, gating)
+    errs = per_tensor_errors(gg, exact)
+    report(errs, F32_TOL, "c3 f32 vs f64 under the GPU's gating")
+    if not any(flips):
+        exact_o = cnn_grads_f64(om, x, y, ogating)
+        for i, e in enumerate(per_tensor_errors(gg, og)):
+            if e > F32_TOL:
+                den = max(float(np.abs(exact_o[i]).max()), 1e-30)
+                e_orc = float(np.abs(og[i] - exact_o[i]).max()) / den
+                assert errs[i] <= e_orc + F32_TOL, (i, e, errs[i], e_orc)
+    del keep
 
 
-def cnn_grads_f64(om, x, y):
-    """The CNN's parameter gradients in f64 with numpy (im2col products): the exact value that both the
-    oracle's sequential f32 sums and the GPU's tree sums approximate."""
+def pool_choice(a):
+    """Index (0..3, row-major in the 2x2 window) of the first maximum of every pooling window of a [n, c, h, w] array."""
+    n, c, h, w = a.shape
+    win = a.reshape(n, c, h // 2, 2, w // 2, 2).transpose(0, 1, 2, 4, 3, 5).reshape(n, c, h // 2, w // 2, 4)
+    return win.argmax(-1).astype(np.int8)
+
+
+def cnn_grads_f64(om, x, y, gating):
+    """The CNN's parameter gradients in f64 with numpy (im2col products), with the ReLU masks and pooling choices given
+    (gating = [relu1 mask, pool1 choice, relu2 mask, pool2 choice]): the backward pass as a smooth function of its inputs."""
     def im2col(a):  # [n, c, h, w] -> [n, h, w, c*9] for a 3x3 kernel with padding 1
         n, c, h, w = a.shape
         p = np.pad(a, ((0, 0), (0, 0), (1, 1), (1, 1)))
@@ -233,18 +283,15 @@ def cnn_grads_f64(om, x, y):
         o = wt.shape[0]
         return (im2col(a) @ wt.reshape(o, -1).T + b).transpose(0, 3, 1, 2)
 
-    def pool(a):
+    def pool(a, choice):
         n, c, h, w = a.shape
         win = a.reshape(n, c, h // 2, 2, w // 2, 2).transpose(0, 1, 2, 4, 3, 5).reshape(n, c, h // 2, w // 2, 4)
-        return win.max(-1), win
+        return np.take_along_axis(win, choice[..., None].astype(np.int64), -1)[..., 0]
 
-    def pool_back(g, win, shape):
-        # the reference routes to the first maximum of each ky row that holds one (host_ops.rs:359-476); with U(0,1)
-        # inputs through a convolution, ties inside a window do not occur, so argmax is the same choice
+    def pool_back(g, choice, shape):
         n, c, h, w = shape
-        idx = win.argmax(-1)
-        out = np.zeros(win.shape, g.dtype)
-        np.put_along_axis(out, idx[..., None], g[..., None], -1)
+        out = np.zeros((n, c, h // 2, w // 2, 4), g.dtype)
+        np.put_along_axis(out, choice[..., None].astype(np.int64), g[..., None], -1)
         return out.reshape(n, c, h // 2, w // 2, 2, 2).transpose(0, 1, 2, 4, 3, 5).reshape(n, c, h, w)
 
     def conv_back(a, wt, g):
@@ -261,12 +308,13 @@ def cnn_grads_f64(om, x, y):
         return dp[:, :, 1:-1, 1:-1], dw, db
 
     f = np.float64
+    relu1, choice1, relu2, choice2 = gating
     w1, b1, w2, b2, wf, bf = (p.data.astype(f) for p in om.parameters())
     a0 = x.astype(f)
     z1 = conv(a0, w1, b1)
-    p1, win1 = pool(np.maximum(z1, 0))
+    p1 = pool(z1 * relu1, choice1)
     z2 = conv(p1, w2, b2)
-    p2, win2 = pool(np.maximum(z2, 0))
+    p2 = pool(z2 * relu2, choice2)
     flat = p2.reshape(p2.shape[0], -1)
     logits = flat @ wf.T + bf
     e = np.exp(logits - logits.max(1, keepdims=True))
@@ -275,8 +323,8 @@ def cnn_grads_f64(om, x, y):
     gl = prob / len(y)
     dwf, dbf = gl.T @ flat, gl.sum(0)
     g = (gl @ wf).reshape(p2.shape)
-    g = pool_back(g, win2, z2.shape) * (z2 > 0)
+    g = pool_back(g, choice2, z2.shape) * relu2
     g, dw2, db2 = conv_back(p1, w2, g)
-    g = pool_back(g, win1, z1.shape) * (z1 > 0)
+    g = pool_back(g, choice1, z1.shape) * relu1
     _, dw1, db1 = conv_back(a0, w1, g)
     return [dw1, db1, dw2, db2, dwf, dbf]
