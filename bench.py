@@ -403,6 +403,11 @@ def run_ours(args, dist):
             "model_tflops": step_flops(cfg) / (ms_step / 1e3) / 1e12, "loss_first": first_loss, "loss_last": last_loss,
             "replicas_in_sync": in_sync, "cuda_graph_step": graph,
         }
+        if "optimizer" in kernels and kernels["optimizer"]["gbs"]:
+            # the GradScaler scan + unscale + Adam pass of THIS step (28 bytes per parameter with f32 gradients, 26 with 16-bit ones),
+            # against the measured HBM copy peak: the c5 workload's figure at this model's parameter count
+            result["fused_update_hbm"] = {"achieved": kernels["optimizer"]["gbs"], "peak": pk["hbm"], "unit": "GB/s",
+                                          "frac": kernels["optimizer"]["gbs"] / pk["hbm"], "peak_source": pk["src"]}
     if dist.world > 1:
         ctx.check(lib.mcb_dp_shutdown(ctx.h))
     return result
@@ -637,6 +642,11 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="c4 only: override the layer count (small cases for ncu captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    # stdout carries exactly one JSON line: whatever libraries print on file descriptor 1 while the run lasts
+    # (NCCL's version banner, for one) goes to stderr instead
+    sys.stdout.flush()
+    out_fd = os.dup(1)
+    os.dup2(2, 1)
     dist = Dist(args.gpus)
     if args.impl == "reference":
         res = run_reference(args, dist)
@@ -645,9 +655,12 @@ def main():
         if res is not None and dist.world == 1 and not args.no_cpu_baseline and args.workload in ("c1", "c2", "c3", "c4", "c5"):
             v, cores, desc = cpu_sample(args.workload)
             res["cpu_baseline"] = {"value": v, "unit": res["unit"], "cores": cores, "kind": "port", "sample": desc}
-    if dist.rank == 0 and res is not None:
-        print(json.dumps(res))
     dist.close()
+    sys.stdout.flush()
+    os.dup2(out_fd, 1)
+    os.close(out_fd)
+    if dist.rank == 0 and res is not None:
+        print(json.dumps(res), flush=True)
 
 
 if __name__ == "__main__":

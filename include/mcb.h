@@ -76,6 +76,14 @@ typedef struct mcb_ctx mcb_ctx;
 /* CudaBackend::new(ordinal), crates/modern-chainer-cuda/src/backend.rs:460-468 */
 mcb_status mcb_ctx_create(int32_t ordinal, mcb_ctx **out);
 void mcb_ctx_destroy(mcb_ctx *ctx);
+/* Test and tuning knobs.  Each has the name of an environment variable (MCB_DETERMINISTIC, MCB_UNFUSED_BWD,
+ * MCB_CONV_DIRECT, MCB_TC_BN ...); the environment is read ONCE, when the context is created, and no entry point
+ * reads it afterwards.  mcb_set_knob changes one knob of one context: value >= 0 sets it, value < 0 clears it.
+ * MCB_DETERMINISTIC makes a step reproducible bit for bit from run to run: the embedding gradient is added in
+ * position order (the order of crates/modern-chainer-cpu/src/kernels.rs:1783-1815) instead of by float atomics,
+ * tensor-core GEMMs run without split reductions (whose slices meet the output in arrival order), and max-pool
+ * gradients of overlapping windows are gathered per input element.  It costs time, not accuracy. */
+mcb_status mcb_set_knob(mcb_ctx *ctx, const char *name, int32_t value);
 const char *mcb_last_error(mcb_ctx *ctx);
 /* number of usable CUDA devices (0 when the driver is missing); probe(), cuda/src/lib.rs:54-66 */
 int32_t mcb_device_count(void);
@@ -159,6 +167,10 @@ mcb_status mcb_col_sum(mcb_ctx *ctx, const void *a, int32_t dt, int64_t rows, in
 mcb_status mcb_softmax(mcb_ctx *ctx, const float *x, float *out, int64_t rows, int64_t cols);
 mcb_status mcb_softmax_backward(mcb_ctx *ctx, const float *x, const float *g, float *out, int64_t rows,
                                 int64_t cols);
+/* the same gradient from the forward's OUTPUT y instead of its input (what a tape that keeps y uses: no
+ * exponentials, dx = y (g - sum(y g))) */
+mcb_status mcb_softmax_backward_from_output(mcb_ctx *ctx, const float *y, const float *g, float *out, int64_t rows,
+                                            int64_t cols);
 /* Ops::layer_norm / layer_norm_backward, ops.rs:1200-1305.  x is f32; out_dt selects the
  * storage of the normalised output (f32, or bf16 when it only feeds a bf16 GEMM).
  * mean/rstd ([rows] f32, may be NULL) are saved by forward and reused by backward. */
@@ -172,10 +184,13 @@ mcb_status mcb_layer_norm_backward(mcb_ctx *ctx, const float *x, const float *ga
  * cudaMalloc / cudaFree for good: a control loop with a latency budget, a process whose device
  * memory is carved up once at start-up, a section that is being recorded and may not touch the
  * address space.  mcb_layer_norm_backward is unusable there because its per-block partial sums of
- * dgamma / dbeta live in scratch memory the context allocates on demand.  This variant runs the
- * same kernels with those partial sums in a 2 MiB array that is part of the library image (every
- * GPU that loads the library holds it until the process exits).  It takes no context, allocates
- * nothing, and calls no allocating routine.
+ * dgamma / dbeta live in scratch memory the context allocates on demand.  This variant keeps those
+ * partial sums in a 2 MiB array that is part of the library image (every GPU that loads the
+ * library holds it until the process exits).  It takes no context, allocates nothing, and calls no
+ * allocating routine.  It always runs the general row-sweeping kernel on at most 64 blocks (the
+ * array has room for 64 partial results), not the pipelined kernels that mcb_layer_norm_backward
+ * picks for most shapes: same results up to the order of the f32 partial sums, but at 8192 x 768 it
+ * occupies fewer than half of the SMs.  It is for callers that cannot allocate, not a fast path.
  *   stream      the cudaStream_t to enqueue on; its device must be the current device
  *   arguments   as mcb_layer_norm_backward; mean / rstd may be NULL (recomputed from x)
  *   limit       dim <= 4096; larger dims return MCB_INVALID_ARGUMENT and enqueue nothing

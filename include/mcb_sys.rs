@@ -91,6 +91,7 @@ pub const MCB_OPT_MOMENTUM_SGD: i32 = 3;
 unsafe extern "C" {
     pub fn mcb_ctx_create(ordinal: i32, out: *mut *mut McbCtx) -> Status;
     pub fn mcb_ctx_destroy(ctx: *mut McbCtx);
+    pub fn mcb_set_knob(ctx: *mut McbCtx, name: *const c_char, value: i32) -> Status;
     pub fn mcb_last_error(ctx: *mut McbCtx) -> *const c_char;
     pub fn mcb_device_count() -> i32;
     pub fn mcb_alloc(ctx: *mut McbCtx, bytes: usize, out: *mut *mut c_void) -> Status;
@@ -132,6 +133,7 @@ unsafe extern "C" {
     pub fn mcb_col_sum(ctx: *mut McbCtx, a: *const c_void, dt: i32, rows: i64, cols: i64, out: *mut f32) -> Status;
     pub fn mcb_softmax(ctx: *mut McbCtx, x: *const f32, out: *mut f32, rows: i64, cols: i64) -> Status;
     pub fn mcb_softmax_backward(ctx: *mut McbCtx, x: *const f32, g: *const f32, out: *mut f32, rows: i64, cols: i64) -> Status;
+    pub fn mcb_softmax_backward_from_output(ctx: *mut McbCtx, y: *const f32, g: *const f32, out: *mut f32, rows: i64, cols: i64) -> Status;
     pub fn mcb_layer_norm(ctx: *mut McbCtx, x: *const f32, gamma: *const f32, beta: *const f32, eps: f64, out: *mut c_void, out_dt: i32, mean: *mut f32, rstd: *mut f32, rows: i64, dim: i64) -> Status;
     pub fn mcb_layer_norm_backward(ctx: *mut McbCtx, x: *const f32, gamma: *const f32, g: *const c_void, g_dt: i32, eps: f64, mean: *const f32, rstd: *const f32, dx: *mut f32, dgamma: *mut f32, dbeta: *mut f32, rows: i64, dim: i64) -> Status;
     pub fn mcb_layer_norm_backward_noalloc(stream: *mut c_void, x: *const f32, gamma: *const f32, g: *const c_void, g_dt: i32, eps: f64, mean: *const f32, rstd: *const f32, dx: *mut f32, dgamma: *mut f32, dbeta: *mut f32, rows: i64, dim: i64) -> Status;

@@ -15,6 +15,9 @@ STATUS_NAMES = {0: "Ok", 1: "ShapeMismatch", 2: "Broadcast", 3: "DTypeMismatch",
                 5: "InvalidArgument", 6: "OutOfBounds", 7: "Unsupported", 8: "Backend", 9: "Io"}
 
 
+GUARD_BYTE = 0xA5  # canary pattern of Context.guard
+
+
 class McbError(RuntimeError):
     """Mirrors core::Error of the reference; `.status` is the C status code."""
 
@@ -67,6 +70,24 @@ class Context:
     def launch_count(self):
         return self.lib.mcb_launch_count(self.h)
 
+    def set_knob(self, name, value=1):
+        """Sets (value >= 0) or clears (value < 0 or None) one test / tuning knob of this context, by the name of its
+        environment variable.  The library reads the environment only while a context is created."""
+        self.check(self.lib.mcb_set_knob(self.h, name.encode(), -1 if value is None else int(value)))
+
+    def knob(self, name, value=1):
+        """`with ctx.knob("MCB_UNFUSED_BWD"):` -- the knob is set inside the block and cleared after it."""
+        ctx = self
+
+        class _Scope:
+            def __enter__(self):
+                ctx.set_knob(name, value)
+
+            def __exit__(self, *exc):
+                ctx.set_knob(name, None)
+                return False
+        return _Scope()
+
     def set_compute_type(self, compute):
         self.check(self.lib.mcb_set_compute_type(self.h, compute))
 
@@ -83,6 +104,17 @@ class Context:
         ms = C.c_float()
         self.check(self.lib.mcb_event_elapsed_ms(self.h, a, b, C.byref(ms)))
         return ms.value
+
+    # ---- canary bands around every array made from here on (a debugging aid: out-of-bounds writes of a kernel show
+    # up as a changed band; the library itself is not involved)
+    def guard(self, nbytes=256, shift=0):
+        self.guard_bytes, self.guard_shift, self.guard_checked, self.guard_broken = int(nbytes), int(shift), 0, []
+
+    def check_guards(self):
+        """Number of guarded arrays checked so far (each when it was released); raises if a band of any was written."""
+        if self.guard_broken:
+            raise AssertionError(f"a kernel wrote outside arrays (shape, dtype): {self.guard_broken}")
+        return self.guard_checked
 
     # ---- memory
     def empty(self, shape, dtype=F32):
@@ -112,13 +144,43 @@ class DeviceArray:
         self.size = int(np.prod(self.shape)) if self.shape else 1
         self.nbytes = self.size * np.dtype(_NP_OF[dtype]).itemsize
         p = C.c_void_p()
-        ctx.check(ctx.lib.mcb_alloc(ctx.h, max(self.nbytes, 1), C.byref(p)))
-        self.ptr = p
+        guard = getattr(ctx, "guard_bytes", 0)
+        if not guard:
+            ctx.check(ctx.lib.mcb_alloc(ctx.h, max(self.nbytes, 1), C.byref(p)))
+            self.ptr = self._base = p
+            self._guard = None
+            return
+        # canary bands: `guard` bytes of a fixed pattern before and after the array (and `guard_shift` bytes of it in
+        # front, to move the array off its 16-byte alignment); Context.check_guards() reads them back
+        item = np.dtype(_NP_OF[dtype]).itemsize
+        shift = (ctx.guard_shift + item - 1) // item * item  # never below the element's own alignment
+        total = guard + shift + self.nbytes + guard
+        ctx.check(ctx.lib.mcb_alloc(ctx.h, total, C.byref(p)))
+        band = np.full(total, GUARD_BYTE, np.uint8)
+        ctx.check(ctx.lib.mcb_memcpy_h2d(ctx.h, p, band.ctypes.data_as(C.c_void_p), total))
+        ctx.sync()
+        self._base = p
+        self.ptr = C.c_void_p(p.value + guard + shift)
+        self._guard = (guard + shift, guard)
+
+    def guards_intact(self):
+        front, back = self._guard
+        for start, n in ((self._base.value, front), (self.ptr.value + self.nbytes, back)):
+            got = np.empty(n, np.uint8)
+            self.ctx.check(self.ctx.lib.mcb_memcpy_d2h(self.ctx.h, got.ctypes.data_as(C.c_void_p), C.c_void_p(start), n))
+            if not (got == GUARD_BYTE).all():
+                return False
+        return True
 
     def __del__(self):
         try:
-            if self.ptr and self.ctx.h:
-                self.ctx.lib.mcb_free(self.ctx.h, self.ptr)
+            if self._base and self.ctx.h:
+                if self._guard:  # the bands are read when the array dies; Context.check_guards() reports
+                    self.ctx.sync()
+                    self.ctx.guard_checked += 1
+                    if not self.guards_intact():
+                        self.ctx.guard_broken.append((self.shape, self.dtype))
+                self.ctx.lib.mcb_free(self.ctx.h, self._base)
         except Exception:
             pass
 
@@ -238,6 +300,12 @@ class _Ops:
         d, e = self._a(np.asarray(x, np.float32)), self._a(np.asarray(g, np.float32))
         out = self.ctx.empty(d.shape)
         self.ctx.check(self.lib.mcb_softmax_backward(self.ctx.h, d.ptr, e.ptr, out.ptr, d.shape[0], d.shape[1]))
+        return out.numpy()
+
+    def softmax_backward_from_output(self, y, g):
+        d, e = self._a(np.asarray(y, np.float32)), self._a(np.asarray(g, np.float32))
+        out = self.ctx.empty(d.shape)
+        self.ctx.check(self.lib.mcb_softmax_backward_from_output(self.ctx.h, d.ptr, e.ptr, out.ptr, d.shape[0], d.shape[1]))
         return out.numpy()
 
     def layer_norm(self, x, gamma, beta, eps, out_dt=F32, with_stats=False):

@@ -361,7 +361,7 @@ static mcb_status like_input(mcb_ctx *ctx, const Tensor &g, const Var &in, Tenso
 // rounds its incoming gradient to bf16 as its first step anyway (same values), and does so in the
 // pass that also produces the bias gradient, so rounding here would only add a kernel.
 static mcb_status like_input_lazy(mcb_ctx *ctx, const Tensor &g, const Var &in, Tensor *out) {
-    if (g.dt == MCB_F32 && is_lp(in->data.dt) && in->node && !getenv("MCB_UNFUSED_BWD") &&
+    if (g.dt == MCB_F32 && is_lp(in->data.dt) && in->node && !knob_on(ctx, K_UNFUSED_BWD) &&
         (!strcmp(in->node->name, "Linear") || !strcmp(in->node->name, "LinearActivation"))) {
         *out = g;
         return MCB_OK;
@@ -632,7 +632,7 @@ static mcb_status linear_backward_impl(mcb_ctx *ctx, const Tensor &g_in, const L
     // The bias gradient is the column sum of the bf16 gradient the GEMMs below read.  Whenever a
     // pass over that gradient is needed anyway (a cast from f32, the activation's backward), the
     // same pass leaves the column sums, and no separate reduction reads the matrix again.
-    const bool fuse = getenv("MCB_UNFUSED_BWD") == nullptr; // test knob: separate cast / activation-backward / column-sum kernels
+    const bool fuse = !knob_on(ctx, K_UNFUSED_BWD); // test knob: separate cast / activation-backward / column-sum kernels
     const bool want_db = b && b->requires_grad;
     bool db_done = false;
     if (fuse && sv.bf16 && sv.act == MCB_ACT_NONE && g_in.dt == MCB_F32 && g_in.aux && g_in.aux->bf16.numel() == g_in.numel() && g_in.aux->bf16.dt == sv.lp &&
@@ -862,11 +862,12 @@ mcb_status f_softmax(const Var &x, Var *out) {
     int64_t rows = xf.shape[0], cols = xf.shape[1];
     MCB_TRY(mcb_softmax(ctx, (const float *)xf.ptr, (float *)res.ptr, rows, cols));
     Var xv = x;
-    *out = apply(ctx, "Softmax", res, {x}, [ctx, xf, xv, rows, cols](const Tensor &g, std::vector<Tensor> &gi) -> mcb_status {
+    // the node keeps the probabilities it already has (the reference keeps x and rebuilds them, ops.rs:495-517)
+    *out = apply(ctx, "Softmax", res, {x}, [ctx, res, xv, rows, cols](const Tensor &g, std::vector<Tensor> &gi) -> mcb_status {
         Tensor gf, t;
         MCB_TRY(to_dtype(ctx, g, MCB_F32, &gf));
-        MCB_TRY(new_tensor(ctx, MCB_F32, xf.shape, &t));
-        MCB_TRY(mcb_softmax_backward(ctx, (const float *)xf.ptr, (const float *)gf.ptr, (float *)t.ptr, rows, cols));
+        MCB_TRY(new_tensor(ctx, MCB_F32, res.shape, &t));
+        MCB_TRY(mcb_softmax_backward_from_output(ctx, (const float *)res.ptr, (const float *)gf.ptr, (float *)t.ptr, rows, cols));
         return like_input(ctx, t, xv, &gi[0]);
     });
     return MCB_OK;
@@ -909,8 +910,8 @@ void layer_norm_node(mcb_ctx *ctx, const Var &x, const Var &gamma, const Var &be
         bool d1, d2;
         MCB_TRY(grad_dst(gv, &dg, &d1));
         MCB_TRY(grad_dst(bv, &db, &d2));
-        const bool fuse = getenv("MCB_UNFUSED_BWD") == nullptr; // test knob: separate fan-in add, cast and column sums
-        const bool want_aux = fuse && lowp && xv->data.dt == MCB_F32 && (g.dt == MCB_F32 || g.dt == lpdt) && !getenv("MCB_LN_NO_AUX");
+        const bool fuse = !knob_on(ctx, K_UNFUSED_BWD); // test knob: separate fan-in add, cast and column sums
+        const bool want_aux = fuse && lowp && xv->data.dt == MCB_F32 && (g.dt == MCB_F32 || g.dt == lpdt) && !knob_on(ctx, K_LN_NO_AUX);
         // the pipeline kernel with the by-products; MCB_UNSUPPORTED (nothing launched) where it does not apply
         auto with_aux = [&](const float *addend, float *dst, std::shared_ptr<GradAux> *aux_out) -> mcb_status {
             if (!want_aux) return MCB_UNSUPPORTED;
@@ -964,7 +965,7 @@ mcb_status f_add_layer_norm(const Var &a, const Var &b, const Var &gamma, const 
     MCB_TRY(check_same_ctx(a, b));
     mcb_ctx *ctx = a->ctx;
     const std::vector<int64_t> &sh = a->data.shape;
-    if (!getenv("MCB_UNFUSED_ADD_LN") && sh.size() >= 2 && sh == b->data.shape && a->data.dt == MCB_F32 &&
+    if (!knob_on(ctx, K_UNFUSED_ADD_LN) && sh.size() >= 2 && sh == b->data.shape && a->data.dt == MCB_F32 &&
         (b->data.dt == MCB_F32 || is_lp(b->data.dt)) && gamma->data.numel() == sh.back() && beta->data.numel() == sh.back() &&
         gamma->data.dt == MCB_F32 && beta->data.dt == MCB_F32) {
         const int64_t dim = sh.back(), rows = dim ? a->data.numel() / dim : 0;
@@ -1174,7 +1175,7 @@ mcb_status f_qkv_attention(const Var &x, const Var &wq, const Var &bq, const Var
     mcb_ctx *ctx = x->ctx;
     const int lp = lowp_dtype(ctx);
     if (lp < 0 || x->data.shape.size() != 2) return MCB_UNSUPPORTED;
-    if (getenv("MCB_UNFUSED_QKV")) return MCB_UNSUPPORTED; // test knob: run the composed ops instead
+    if (knob_on(ctx, K_UNFUSED_QKV)) return MCB_UNSUPPORTED; // test knob: run the composed ops instead
     int64_t d = x->data.shape[1], m = x->data.shape[0];
     if (m != n * s || !mcb_flash_supported(d, heads, lp) || !tc_shape_ok(m, 3 * d, d)) return MCB_UNSUPPORTED;
     for (const Var &w : {wq, wk, wv})
@@ -1216,7 +1217,7 @@ mcb_status f_qkv_attention(const Var &x, const Var &wq, const Var &bq, const Var
             ProfScope prof(ctx, MCB_PROF_ATTENTION, 10.0 * (double)n * heads * s * s * 64 * (causal ? 0.5 : 1.0), 16.0 * (double)m * d);
             // the attention backward kernels can leave per-warp column sums of dq | dk | dv (the rounded values they write): the bias
             // gradients then need only the final reduction over those rows instead of another pass over dqkv
-            const int64_t brows = getenv("MCB_UNFUSED_BWD") ? 0 : mcb_flash_bias_rows(n, s);
+            const int64_t brows = knob_on(ctx, K_UNFUSED_BWD) ? 0 : mcb_flash_bias_rows(n, s);
             if (brows > 0) MCB_TRY(new_tensor(ctx, MCB_F32, {brows, 3 * d}, &bias_part));
             MCB_TRY(mcb_flash_backward(ctx, qp, qp + d, qp + 2 * d, o.ptr, g.ptr, (const float *)lse.ptr, dp, dp + d, dp + 2 * d, n, s, d, heads,
                                        causal, 3 * d, d, 3 * d, brows > 0 ? (float *)bias_part.ptr : nullptr, 3 * d, &bias_done, lp));

@@ -177,6 +177,45 @@ __global__ void max_pool_bwd_kernel(const float *__restrict__ x, const float *__
     }
 }
 
+// The same rule read from the input's side, for reproducible runs with overlapping windows (stride < kernel): one
+// thread per input element visits the windows that cover it in (yo, xo) order and takes a window's gradient when the
+// element is that window's maximum and the first such element of its window row.  One writer per element, additions in
+// a fixed order, no zero fill.
+__global__ void max_pool_bwd_gather_kernel(const float *__restrict__ x, const float *__restrict__ g, float *__restrict__ dx, PoolDims d) {
+    long long total = (long long)d.nc * d.h * d.w;
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    long long step = (long long)gridDim.x * blockDim.x;
+    for (; i < total; i += step) {
+        const int ix = (int)(i % d.w), iy = (int)((i / d.w) % d.h);
+        const long long nc = i / ((long long)d.w * d.h);
+        const float v = x[i];
+        int yo0 = iy + d.pad - d.k + 1, xo0 = ix + d.pad - d.k + 1;
+        yo0 = yo0 <= 0 ? 0 : (yo0 + d.stride - 1) / d.stride;
+        xo0 = xo0 <= 0 ? 0 : (xo0 + d.stride - 1) / d.stride;
+        const int yo1 = min((iy + d.pad) / d.stride, d.oh - 1), xo1 = min((ix + d.pad) / d.stride, d.ow - 1);
+        float acc = 0.0f;
+        for (int yo = yo0; yo <= yo1; ++yo)
+            for (int xo = xo0; xo <= xo1; ++xo) {
+                float best = -INFINITY;
+                for (int ky = 0; ky < d.k; ++ky) {
+                    const int wy = yo * d.stride + ky - d.pad;
+                    if (wy < 0 || wy >= d.h) continue;
+                    for (int kx = 0; kx < d.k; ++kx) {
+                        const int wx = xo * d.stride + kx - d.pad;
+                        if (wx < 0 || wx >= d.w) continue;
+                        const float u = x[(nc * d.h + wy) * d.w + wx];
+                        best = u > best ? u : best;
+                    }
+                }
+                if (!(v == best)) continue;
+                bool first = true;
+                for (int wx = max(xo * d.stride - d.pad, 0); wx < ix; ++wx) first = first && !(x[(nc * d.h + iy) * d.w + wx] == best);
+                if (first) acc += g[(nc * d.oh + yo) * d.ow + xo];
+            }
+        dx[i] = acc;
+    }
+}
+
 mcb_status make_conv_dims(mcb_ctx *ctx, ConvDims &d, int64_t n, int64_t c, int64_t h, int64_t wd, int64_t o, int64_t kh,
                           int64_t kw, int64_t stride, int64_t pad) {
     if (stride <= 0 || pad < 0 || h + 2 * pad < kh || wd + 2 * pad < kw)
@@ -201,7 +240,7 @@ mcb_status mcb_conv2d(mcb_ctx *ctx, const float *x, const float *w, const float 
     long long total = (long long)d.n * d.o * d.oh * d.ow;
     if (total == 0) return MCB_OK;
     // large convolutions: column matrix + tensor-core GEMMs at f32 accuracy (conv_tc.cu); small ones: direct kernels
-    if (mcb_conv_tc_eligible(n, c, h, wd, o, kh, kw, stride, pad)) return mcb_conv_tc_forward(ctx, x, w, bias, out, n, c, h, wd, o, kh, kw, stride, pad);
+    if (mcb_conv_tc_eligible(ctx, n, c, h, wd, o, kh, kw, stride, pad)) return mcb_conv_tc_forward(ctx, x, w, bias, out, n, c, h, wd, o, kh, kw, stride, pad);
     ProfScope prof(ctx, MCB_PROF_CONV, 2.0 * (double)total * d.c * d.kh * d.kw, 4.0 * ((double)n * c * h * wd + (double)total));
     conv2d_fwd_kernel<<<mcb_grid_for(ctx, total, 256, 16), 256, 0, ctx->stream>>>(x, w, bias, out, d);
     MCB_LAUNCHED(ctx);
@@ -215,7 +254,7 @@ mcb_status mcb_conv2d_backward(mcb_ctx *ctx, const float *x, const float *w, con
     ConvDims d;
     MCB_TRY(make_conv_dims(ctx, d, n, c, h, wd, o, kh, kw, stride, pad));
     long long nx = (long long)d.n * d.c * d.h * d.w, nw = (long long)d.o * d.c * d.kh * d.kw;
-    if (mcb_conv_tc_eligible(n, c, h, wd, o, kh, kw, stride, pad) && nx && nw) {
+    if (mcb_conv_tc_eligible(ctx, n, c, h, wd, o, kh, kw, stride, pad) && nx && nw) {
         MCB_TRY(mcb_conv_tc_backward(ctx, x, w, g, dx, dw, n, c, h, wd, o, kh, kw, stride, pad));
         dx = nullptr;
         dw = nullptr; // the bias gradient below is a plain reduction in either case
@@ -263,6 +302,13 @@ mcb_status mcb_max_pool2d_backward(mcb_ctx *ctx, const float *x, const float *g,
     if (stride <= 0 || h + 2 * pad < kernel || w + 2 * pad < kernel) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "pool2d: window larger than the padded input");
     PoolDims d{(int)(n * c), (int)h, (int)w, (int)kernel, (int)stride, (int)pad, (int)((h + 2 * pad - kernel) / stride + 1),
                (int)((w + 2 * pad - kernel) / stride + 1)};
+    if (knob_on(ctx, K_DETERMINISTIC) && stride < kernel) { // overlapping windows would meet in float atomics
+        const long long cells = (long long)d.nc * d.h * d.w;
+        if (cells == 0) return MCB_OK;
+        max_pool_bwd_gather_kernel<<<mcb_grid_for(ctx, cells, 256, 16), 256, 0, ctx->stream>>>(x, g, dx, d);
+        MCB_LAUNCHED(ctx);
+        return MCB_OK;
+    }
     MCB_TRY(mcb_memset(ctx, dx, 0, sizeof(float) * n * c * h * w));
     long long total = (long long)d.nc * d.oh * d.ow;
     if (total == 0) return MCB_OK;

@@ -302,8 +302,8 @@ void fill_dims(ConvDims &d, int64_t n, int64_t c, int64_t h, int64_t wd, int64_t
 
 // Worth the column matrix and three GEMM launches from about 2^24 multiply-adds on; the output channel count must
 // give 16-byte rows ([M, O] f16: O % 8 == 0) and the extents must fit the kernels' 32-bit indices.
-bool mcb_conv_tc_eligible(int64_t n, int64_t c, int64_t h, int64_t wd, int64_t o, int64_t kh, int64_t kw, int64_t stride, int64_t pad) {
-    if (getenv("MCB_CONV_DIRECT")) return false; // test knob: keep the direct kernels
+bool mcb_conv_tc_eligible(mcb_ctx *ctx, int64_t n, int64_t c, int64_t h, int64_t wd, int64_t o, int64_t kh, int64_t kw, int64_t stride, int64_t pad) {
+    if (knob_on(ctx, K_CONV_DIRECT)) return false; // test knob: keep the direct kernels
     if (stride <= 0 || pad < 0 || h + 2 * pad < kh || wd + 2 * pad < kw || o % 8) return false;
     ConvDims d;
     fill_dims(d, n, c, h, wd, o, kh, kw, stride, pad);

@@ -426,7 +426,7 @@ mcb_status mcb_flash_forward(mcb_ctx *ctx, const void *q, const void *k, const v
         return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "fused attention needs 16-byte aligned tensors");
     if (n * heads > 65535) return mcb_fail(ctx, MCB_UNSUPPORTED, "fused attention: n * heads > 65535");
     // the tcgen05 / TMEM forward first; MCB_FLASH_LEGACY (test knob) keeps the mma.sync kernel
-    if (!getenv("MCB_FLASH_LEGACY") || dt == MCB_F16) {
+    if (!knob_on(ctx, K_FLASH_LEGACY) || dt == MCB_F16) {
         mcb_status tc = mcb_flash_tc_forward(ctx, q, k, v, out, lse, n, seq, dim, heads, causal, ldi, ldo, dt);
         if (tc != MCB_UNSUPPORTED) return tc;
     }
@@ -448,7 +448,8 @@ mcb_status mcb_flash_backward(mcb_ctx *ctx, const void *q, const void *k, const 
     if (bias_done) *bias_done = 0;
     if (ldi % 8 || ldo % 8 || ldg % 8) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "fused attention needs row pitches that are multiples of 8");
     if (n * heads > 65535) return mcb_fail(ctx, MCB_UNSUPPORTED, "fused attention: n * heads > 65535");
-    if ((((uintptr_t)out) | ((uintptr_t)gout)) & 15) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "fused attention needs 16-byte aligned tensors");
+    if ((((uintptr_t)out) | ((uintptr_t)gout) | ((uintptr_t)q) | ((uintptr_t)k) | ((uintptr_t)v) | ((uintptr_t)dq) | ((uintptr_t)dk) | ((uintptr_t)dv)) & 15)
+        return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "fused attention needs 16-byte aligned tensors");
     float scale = 1.0f / sqrtf((float)HD), scale_log2 = scale * 1.4426950408889634f;
     long long rows = n * heads * seq;
     void *delta = nullptr;
@@ -463,7 +464,7 @@ mcb_status mcb_flash_backward(mcb_ctx *ctx, const void *q, const void *k, const 
     }
     ctx->launches++;
     // the tcgen05 / TMEM kernels first; MCB_FLASH_LEGACY (test knob) keeps the mma.sync pair
-    if ((!getenv("MCB_FLASH_LEGACY") && !getenv("MCB_FLASH_LEGACY_BWD")) || dt == MCB_F16) {
+    if ((!knob_on(ctx, K_FLASH_LEGACY) && !knob_on(ctx, K_FLASH_LEGACY_BWD)) || dt == MCB_F16) {
         mcb_status tc = mcb_flash_tc_backward(ctx, q, k, v, gout, lse, (const float *)delta, dq, dk, dv, n, seq, dim, heads, causal, ldi, ldo, ldg,
                                               bias_partial, bias_ld, dt);
         if (tc != MCB_UNSUPPORTED) {

@@ -128,7 +128,7 @@ mcb_status mcb_sgemm(mcb_ctx *ctx, const SgemmParams &p_in) {
     // whole reduction: cut the reduction into slices, one block each, and add the slices afterwards in a fixed order.
     const long long tiles = (long long)grid.x * grid.y;
     p.splits = 1;
-    if (p.batch == 1 && tiles * 2 <= ctx->sm_count && p.k >= 512 && !getenv("MCB_SGEMM_NO_SPLIT")) {
+    if (p.batch == 1 && tiles * 2 <= ctx->sm_count && p.k >= 512 && !knob_on(ctx, K_SGEMM_NO_SPLIT)) {
         long long s = (2ll * ctx->sm_count) / tiles;
         if (s > p.k / 128) s = p.k / 128;
         if (s > 64) s = 64;

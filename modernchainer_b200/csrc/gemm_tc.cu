@@ -902,22 +902,22 @@ template <int BN, bool PAIR> mcb_status launch(mcb_ctx *ctx, const TcGemmParams 
     // (8192x3072x768: 34.8 -> 32.6 us; with K = 8192 or more the sixth stage is worth more: 323 -> 347 us.)
     // The room of that stage goes either to four boxes per warp or to a second group of four epilogue warps (two boxes
     // each) that takes every other chunk; MCB_TC_EPI=1 keeps the single group (tuning knob).
-    static const bool one_group = getenv("MCB_TC_EPI") && atoi(getenv("MCB_TC_EPI")) == 1;
+    const bool one_group = knob_val(ctx, K_TC_EPI, 0) == 1;
     a.epi_groups = 1;
-    static const int short_kb = getenv("MCB_TC_EPI_KB") ? atoi(getenv("MCB_TC_EPI_KB")) : 16; // tuning knob: k-blocks per item up to which the stage is traded
-    if (PAIR && BN == 256 && a.kb_per_split <= short_kb && C::kStageBytes * 1 >= 4 * 2 * 4096 && !getenv("MCB_TC_STAGES")) {
+    const int short_kb = knob_val(ctx, K_TC_EPI_KB, 16); // tuning knob: k-blocks per item up to which the stage is traded
+    if (PAIR && BN == 256 && a.kb_per_split <= short_kb && C::kStageBytes * 1 >= 4 * 2 * 4096 && !knob_on(ctx, K_TC_STAGES)) {
         a.stages = C::kStages - 1;
         if (one_group) a.ring = 4;
         else a.epi_groups = 2;
     }
     if (BN == 192 && !PAIR && !one_group) a.epi_groups = 2; // 128 x 192 tiles: room for both groups beside the four stages
-    if (const char *st = getenv("MCB_TC_STAGES")) {
-        int v = atoi(st);
+    if (knob_on(ctx, K_TC_STAGES)) {
+        int v = knob_val(ctx, K_TC_STAGES, 0);
         if (v >= 2 && v < C::kStages) a.stages = v;
     }
     // TMA output needs a 16-byte aligned base and row pitch; only an accumulating f32 output may lack them
     a.tma_out = mcb_aligned16(p.d) && (p.ldd * (a.out_bf16 ? 2 : 4)) % 16 == 0 && (!p.d_pre || mcb_aligned16(p.d_pre));
-    static const bool no_tma_out = getenv("MCB_TC_DIRECT_OUT") != nullptr; // tuning knob: per-lane global stores
+    const bool no_tma_out = knob_on(ctx, K_TC_DIRECT_OUT); // tuning knob: per-lane global stores
     if (no_tma_out) a.tma_out = 0;
     CUtensorMap map_d, map_pre;
     memset(&map_d, 0, sizeof(map_d));
@@ -1081,7 +1081,10 @@ mcb_status mcb_tc_gemm(mcb_ctx *ctx, const TcGemmParams &p) {
     if ((mcb_is_lp(p.out_dt) && ((p.ldd % 8) || !mcb_aligned16(p.d))) || (p.out_dt == MCB_F32 && !p.accumulate && ((p.ldd % 4) || !mcb_aligned16(p.d))))
         return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "GEMM output needs a 16-byte aligned base and row pitch");
     int bn = p.bn, split = p.split_k < 1 ? 1 : p.split_k;
-    if (const char *force = getenv("MCB_TC_BN")) bn = atoi(force); // tuning knob: force the tile width
+    // reproducible runs: slices of one reduction reach the output in arrival order, so there are none
+    const bool fixed_order = knob_on(ctx, K_DETERMINISTIC);
+    if (fixed_order) split = 1;
+    bn = knob_val(ctx, K_TC_BN, bn); // tuning knob: force the tile width
     if (bn != 128 && bn != 192 && bn != 256) {
         int s2 = split;
         mcb_tc_plan(ctx, p.m, p.n, p.k, false, p.accumulate, split, &bn, &s2);
@@ -1089,16 +1092,17 @@ mcb_status mcb_tc_gemm(mcb_ctx *ctx, const TcGemmParams &p) {
     TcGemmParams q = p;
     q.split_k = split;
     int pair = p.pair;
-    if (const char *force = getenv("MCB_TC_PAIR")) pair = atoi(force); // tuning knob: 0 single CTA, 1 CTA pair
+    pair = knob_val(ctx, K_TC_PAIR, pair); // tuning knob: 0 single CTA, 1 CTA pair
     if (pair < 0) pair = (bn != 192 && p.m > 128) ? 1 : 0;
     if (bn == 192) pair = 0; // half of 192 columns is not a whole number of 64-column boxes
     // Split tail on 256 x 256 pair tiles against the planned form, by the same cycle estimate as mcb_tc_plan
     // plus 14000 cycles for the workspace memset, the finishing kernel and the f32 epilogue of the slices (measured at
     // 8192 x 768: K = 3072 loses 1-5 us with the split tail, K = 32000 gains 90 us)
     int tail = p.split_tail;
-    if (const char *force = getenv("MCB_TC_SPLIT_TAIL")) tail = atoi(force); // tuning knob: 0 never, 1 whenever it applies
+    tail = knob_val(ctx, K_TC_SPLIT_TAIL, tail); // tuning knob: 0 never, 1 whenever it applies
+    if (fixed_order) tail = 0;
     const bool tail_ok = (p.accumulate ? (p.bias == nullptr) : (split == 1 && !p.d_pre && p.ldd % 4 == 0 && p.n % 4 == 0)) && p.m > 128 &&
-                         !getenv("MCB_TC_BN");
+                         !knob_on(ctx, K_TC_BN);
     if (tail < 0 && tail_ok) {
         const long long kb = (p.k + BK - 1) / BK, workers = ctx->sm_count / 2;
         const long long tiles = ((p.m + 255) / 256) * ((p.n + 255) / 256), rem = tiles % workers;

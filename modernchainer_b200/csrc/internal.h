@@ -88,11 +88,13 @@ mcb_status mcb_layer_norm_backward_ex(mcb_ctx *ctx, const float *x, const float 
                                       float *dbeta, int64_t rows, int64_t dim);
 // conv_tc.cu: convolution as column matrix + tensor-core GEMMs at f32 accuracy (f16 hi/lo pieces); _eligible says whether a
 // problem is large and regular enough for it
-bool mcb_conv_tc_eligible(int64_t n, int64_t c, int64_t h, int64_t wd, int64_t o, int64_t kh, int64_t kw, int64_t stride, int64_t pad);
+bool mcb_conv_tc_eligible(mcb_ctx *ctx, int64_t n, int64_t c, int64_t h, int64_t wd, int64_t o, int64_t kh, int64_t kw, int64_t stride, int64_t pad);
 mcb_status mcb_conv_tc_forward(mcb_ctx *ctx, const float *x, const float *w, const float *bias, float *out, int64_t n, int64_t c, int64_t h,
                                int64_t wd, int64_t o, int64_t kh, int64_t kw, int64_t stride, int64_t pad);
 mcb_status mcb_conv_tc_backward(mcb_ctx *ctx, const float *x, const float *w, const float *g, float *dx, float *dw, int64_t n, int64_t c, int64_t h,
                                 int64_t wd, int64_t o, int64_t kh, int64_t kw, int64_t stride, int64_t pad);
+// reduce.cu: row softmax (mode 0), its backward from x (1) or from the forward's output y (2)
+mcb_status mcb_softmax_rows(mcb_ctx *ctx, int mode, const float *a, const float *b, float *out, int64_t rows, int64_t cols);
 // reduce.cu
 mcb_status mcb_sce_grad(mcb_ctx *ctx, const void *logits, void *out, int32_t dt, const void *labels, int32_t label_dt,
                         int64_t n, int64_t c, float *loss_out, const float *upstream, float *stats_out = nullptr,

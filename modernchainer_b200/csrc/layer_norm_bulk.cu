@@ -453,7 +453,7 @@ bool eligible(int64_t rows, int64_t dim, const void *p0, const void *p1, const v
 
 mcb_status mcb_ln_bulk_forward(mcb_ctx *ctx, const float *x, const float *gamma, const float *beta, double eps, void *out, int32_t out_dt,
                                float *mean, float *rstd, int64_t rows, int64_t dim) {
-    if (!eligible(rows, dim, x, gamma, beta, out) || getenv("MCB_LN_NO_BULK")) return MCB_UNSUPPORTED;
+    if (!eligible(rows, dim, x, gamma, beta, out) || knob_on(ctx, K_LN_NO_BULK)) return MCB_UNSUPPORTED;
     LnBulkArgs a = {};
     a.x = x; a.gamma = gamma; a.beta = beta; a.out = out; a.mean_out = mean; a.rstd_out = rstd;
     a.rows = rows; a.dim = (int)dim; a.eps = (float)eps; a.err = ctx->d_err;
@@ -473,7 +473,7 @@ mcb_status mcb_ln_bulk_forward(mcb_ctx *ctx, const float *x, const float *gamma,
 // pre-norm block, in one pass over the rows.  Same arithmetic as mcb_add_typed followed by mcb_layer_norm.
 mcb_status mcb_ln_bulk_add_forward(mcb_ctx *ctx, const float *x, const void *res, int32_t res_dt, const float *gamma, const float *beta, double eps,
                                    float *sum, void *out, int32_t out_dt, float *mean, float *rstd, int64_t rows, int64_t dim) {
-    if (!eligible(rows, dim, x, gamma, beta, out) || !mcb_aligned16(res) || !mcb_aligned16(sum) || getenv("MCB_LN_NO_BULK")) return MCB_UNSUPPORTED;
+    if (!eligible(rows, dim, x, gamma, beta, out) || !mcb_aligned16(res) || !mcb_aligned16(sum) || knob_on(ctx, K_LN_NO_BULK)) return MCB_UNSUPPORTED;
     if ((res_dt != MCB_F32 && !mcb_is_lp(res_dt)) || (out_dt != MCB_F32 && !mcb_is_lp(out_dt))) return MCB_UNSUPPORTED;
     if (mcb_is_lp(res_dt) && mcb_is_lp(out_dt) && res_dt != out_dt) return MCB_UNSUPPORTED; // one 16-bit format per launch
     LnBulkArgs a = {};
@@ -500,7 +500,7 @@ mcb_status mcb_ln_bulk_backward(mcb_ctx *ctx, const float *x, const float *gamma
                                 void *dx_bf16, float *dx_colsum, int32_t aux_dt) {
     if (g_dt != MCB_F32 && !mcb_is_lp(g_dt)) return MCB_UNSUPPORTED;
     if (dx_bf16 && mcb_is_lp(g_dt) && aux_dt != g_dt) return MCB_UNSUPPORTED; // one 16-bit format per launch
-    if (!eligible(rows, dim, x, gamma, g, dx) || (addend && !mcb_aligned16(addend)) || getenv("MCB_LN_NO_BULK")) return MCB_UNSUPPORTED;
+    if (!eligible(rows, dim, x, gamma, g, dx) || (addend && !mcb_aligned16(addend)) || knob_on(ctx, K_LN_NO_BULK)) return MCB_UNSUPPORTED;
     if ((dx_bf16 != nullptr) != (dx_colsum != nullptr) || (dx_bf16 && !mcb_aligned16(dx_bf16))) return MCB_UNSUPPORTED;
     LnBulkArgs a = {};
     a.x = x; a.gamma = gamma; a.g = g; a.mean_in = mean; a.rstd_in = rstd; a.addend = addend; a.out = dx;

@@ -167,35 +167,106 @@ __global__ void sum_to_walk_kernel(const float *__restrict__ a, SumToWalk w, lon
 }
 
 // ------------------------------------------------------------------ softmax
-__global__ void softmax_kernel(const float *__restrict__ x, float *__restrict__ out, long long cols) {
-    __shared__ float red[32];
-    const float *s = x + (long long)blockIdx.x * cols;
-    float *d = out + (long long)blockIdx.x * cols;
-    float mx = -INFINITY;
-    for (long long j = threadIdx.x; j < cols; j += blockDim.x) mx = fmaxf(mx, s[j]);
-    mx = block_max(mx, red);
-    float sum = 0.0f;
-    for (long long j = threadIdx.x; j < cols; j += blockDim.x) sum += expf(s[j] - mx);
-    sum = block_sum(sum, red);
-    float inv = 1.0f / sum;
-    for (long long j = threadIdx.x; j < cols; j += blockDim.x) d[j] = expf(s[j] - mx) * inv;
+// Row softmax and its backward with ONE pass over global memory per operand: a row is read once with 128-bit loads
+// into shared memory, reduced there (warp shuffles for rows of up to 1024 columns, one warp each, while eight such rows
+// fit 48 KB; a whole block for wider rows) and written once.  The backward takes either x (the trait's signature: the probabilities are
+// rebuilt in shared memory, one exp per element) or the forward's output y, which the tape keeps, so that
+// dx = y (g - sum(y g)) costs no exponential at all.
+template <int GROUP> __device__ __forceinline__ float group_sum(float v, float *red) {
+    if (GROUP == 32) return warp_sum(v);
+    return block_sum(v, red);
 }
-__global__ void softmax_backward_kernel(const float *__restrict__ x, const float *__restrict__ g,
-                                        float *__restrict__ out, long long cols) {
+template <int GROUP> __device__ __forceinline__ float group_max(float v, float *red) {
+    if (GROUP == 32) return warp_max(v);
+    return block_max(v, red);
+}
+// copies row `src` (cols floats) into shared `dst`; `vec`: 16-byte aligned and cols % 4 == 0
+template <int GROUP> __device__ __forceinline__ void load_row(float *dst, const float *__restrict__ src, int cols, int lane, bool vec) {
+    if (vec) {
+        const float4 *s4 = reinterpret_cast<const float4 *>(src);
+        float4 *d4 = reinterpret_cast<float4 *>(dst);
+        for (int j = lane; j < (cols >> 2); j += GROUP) d4[j] = s4[j];
+    } else {
+        for (int j = lane; j < cols; j += GROUP) dst[j] = src[j];
+    }
+}
+template <int GROUP> __device__ __forceinline__ void store_row(float *__restrict__ dst, const float *src, int cols, int lane, bool vec) {
+    if (vec) {
+        const float4 *s4 = reinterpret_cast<const float4 *>(src);
+        float4 *d4 = reinterpret_cast<float4 *>(dst);
+        for (int j = lane; j < (cols >> 2); j += GROUP) d4[j] = s4[j];
+    } else {
+        for (int j = lane; j < cols; j += GROUP) dst[j] = src[j];
+    }
+}
+
+// MODE 0: out = softmax(a);  MODE 1: out = backward from x (a = x, b = g);  MODE 2: backward from y (a = y, b = g)
+// GROUP 32: one warp per row, 8 rows per block; GROUP 256: one block per row.  Shared memory: rows_per_block * pitch floats
+// for a (and the same again for g in the backward modes).
+template <int GROUP, int MODE>
+__global__ void __launch_bounds__(256) softmax_rows_kernel(const float *__restrict__ a, const float *__restrict__ b, float *__restrict__ out,
+                                                           long long rows, int cols, int pitch, int vec) {
+    extern __shared__ __align__(16) float srow[];
+    __shared__ float red[32];
+    constexpr int kRowsPerBlock = 256 / GROUP;
+    const int sub = threadIdx.x / GROUP, lane = threadIdx.x % GROUP;
+    const long long row = (long long)blockIdx.x * kRowsPerBlock + sub;
+    const bool live = row < rows; // a block-wide group (GROUP 256) always has a live row; idle warps of the last block skip
+    if (GROUP == 32 && !live) return;
+    float *sa = srow + (size_t)sub * pitch, *sg = srow + (size_t)(kRowsPerBlock + sub) * pitch;
+    load_row<GROUP>(sa, a + row * cols, cols, lane, vec);
+    if (MODE != 0) load_row<GROUP>(sg, b + row * cols, cols, lane, vec);
+    if (GROUP == 32) __syncwarp();
+    else __syncthreads();
+    if (MODE != 2) { // probabilities from the scores, in place in shared memory
+        float mx = -INFINITY;
+        for (int j = lane; j < cols; j += GROUP) mx = fmaxf(mx, sa[j]);
+        mx = group_max<GROUP>(mx, red);
+        float sum = 0.0f;
+        for (int j = lane; j < cols; j += GROUP) {
+            const float e = expf(sa[j] - mx);
+            sa[j] = e;
+            sum += e;
+        }
+        sum = group_sum<GROUP>(sum, red);
+        const float inv = 1.0f / sum;
+        for (int j = lane; j < cols; j += GROUP) sa[j] *= inv;
+    }
+    if (MODE != 0) {
+        float dot = 0.0f;
+        for (int j = lane; j < cols; j += GROUP) dot = fmaf(sa[j], sg[j], dot);
+        dot = group_sum<GROUP>(dot, red);
+        for (int j = lane; j < cols; j += GROUP) sa[j] = sa[j] * (sg[j] - dot);
+    }
+    if (GROUP == 32) __syncwarp();
+    else __syncthreads();
+    store_row<GROUP>(out + row * cols, sa, cols, lane, vec);
+}
+
+// rows wider than the shared-memory staging allows: three sweeps over global memory (block per row)
+__global__ void softmax_wide_kernel(const float *__restrict__ x, const float *__restrict__ g, float *__restrict__ out, long long cols, int mode) {
     __shared__ float red[32];
     const float *s = x + (long long)blockIdx.x * cols;
-    const float *gr = g + (long long)blockIdx.x * cols;
+    const float *gr = g ? g + (long long)blockIdx.x * cols : nullptr;
     float *d = out + (long long)blockIdx.x * cols;
-    float mx = -INFINITY;
-    for (long long j = threadIdx.x; j < cols; j += blockDim.x) mx = fmaxf(mx, s[j]);
-    mx = block_max(mx, red);
-    float sum = 0.0f;
-    for (long long j = threadIdx.x; j < cols; j += blockDim.x) sum += expf(s[j] - mx);
-    sum = block_sum(sum, red);
+    float mx = 0.0f, inv = 1.0f;
+    if (mode != 2) {
+        mx = -INFINITY;
+        for (long long j = threadIdx.x; j < cols; j += blockDim.x) mx = fmaxf(mx, s[j]);
+        mx = block_max(mx, red);
+        float sum = 0.0f;
+        for (long long j = threadIdx.x; j < cols; j += blockDim.x) sum += expf(s[j] - mx);
+        inv = 1.0f / block_sum(sum, red);
+    }
+    auto prob = [&](long long j) { return mode == 2 ? s[j] : expf(s[j] - mx) * inv; };
+    if (mode == 0) {
+        for (long long j = threadIdx.x; j < cols; j += blockDim.x) d[j] = prob(j);
+        return;
+    }
     float dot = 0.0f;
-    for (long long j = threadIdx.x; j < cols; j += blockDim.x) dot += (expf(s[j] - mx) / sum) * gr[j];
+    for (long long j = threadIdx.x; j < cols; j += blockDim.x) dot = fmaf(prob(j), gr[j], dot);
     dot = block_sum(dot, red);
-    for (long long j = threadIdx.x; j < cols; j += blockDim.x) d[j] = (expf(s[j] - mx) / sum) * (gr[j] - dot);
+    for (long long j = threadIdx.x; j < cols; j += blockDim.x) d[j] = prob(j) * (gr[j] - dot);
 }
 
 // ------------------------------------------------------------------ layer norm
@@ -618,9 +689,78 @@ __global__ void embedding_backward_kernel(const void *__restrict__ ids, int id_d
     }
 }
 
+// Position-ordered scatter for reproducible runs.  The block of token i acts only when no earlier token carries the
+// same id; it then adds the gradient rows of every token with that id in position order, which is the order of the
+// reference's CPU loop (crates/modern-chainer-cpu/src/kernels.rs:1783-1815).  Every output element has one writer and
+// a fixed order of additions, so the result does not depend on scheduling.  Each block reads all n ids: a mode for
+// reproducibility, not for speed.  The positions that match are kept as a bit mask in shared memory (n / 8 bytes).
+constexpr long long kOrderedEmbeddingMaxTokens = 262144; // 32 KB of mask
+template <typename GT>
+__global__ void __launch_bounds__(256) embedding_backward_ordered_kernel(const void *__restrict__ ids, int id_dt, long long n, const GT *__restrict__ g,
+                                                                         long long vocab, int dim, float *__restrict__ out, unsigned int *err) {
+    extern __shared__ unsigned int match_bits[];
+    const long long i = blockIdx.x;
+    const long long id = load_index(ids, id_dt, i);
+    if (id < 0 || id >= vocab) {
+        if (threadIdx.x == 0) atomicOr(err, MCB_DEVERR_INDEX);
+        return;
+    }
+    int seen = 0;
+    for (long long r = threadIdx.x; r < i && !seen; r += blockDim.x) seen = load_index(ids, id_dt, r) == id;
+    if (__syncthreads_or(seen)) return;
+    const long long words = (n - i + 31) / 32; // bit b of word w: position i + 32 w + b
+    for (long long w = threadIdx.x; w < words; w += blockDim.x) {
+        unsigned int bits = 0;
+        for (int b = 0; b < 32; ++b) {
+            const long long r = i + 32 * w + b;
+            if (r < n && load_index(ids, id_dt, r) == id) bits |= 1u << b;
+        }
+        match_bits[w] = bits;
+    }
+    __syncthreads();
+    for (int j = threadIdx.x; j < dim; j += blockDim.x) {
+        float acc = out[id * dim + j];
+        for (long long w = 0; w < words; ++w) {
+            unsigned int bits = match_bits[w];
+            while (bits) {
+                const int b = __ffs(bits) - 1;
+                bits &= bits - 1;
+                acc += Elem<GT>::ld(g, (i + 32 * w + b) * dim + j);
+            }
+        }
+        out[id * dim + j] = acc;
+    }
+}
+
 bool index_dtype_ok(int dt) { return dt == MCB_I64 || dt == MCB_I32 || dt == MCB_U8; }
 
 } // namespace
+
+// mode 0: softmax; 1: backward from x; 2: backward from the forward's output
+mcb_status mcb_softmax_rows(mcb_ctx *ctx, int mode, const float *a, const float *b, float *out, int64_t rows, int64_t cols) {
+    if (rows == 0 || cols == 0) return MCB_OK;
+    const int operands = mode == 0 ? 1 : 2;
+    ProfScope prof(ctx, MCB_PROF_REDUCE, 0.0, 4.0 * (double)rows * cols * (operands + 1));
+    const int vec = (cols % 4 == 0) && mcb_aligned16(a) && mcb_aligned16(out) && (!b || mcb_aligned16(b));
+    const int pitch = (int)((cols + 3) / 4 * 4);
+    constexpr size_t kStage = 48 * 1024 - 256; // dynamic shared memory beside the kernel's static 128 bytes
+    if (cols <= 1024 && sizeof(float) * 8 * (size_t)pitch * operands <= kStage) { // one warp per row, eight rows per block
+        const size_t smem = sizeof(float) * 8 * (size_t)pitch * operands;
+        const unsigned grid = (unsigned)((rows + 7) / 8);
+        if (mode == 0) softmax_rows_kernel<32, 0><<<grid, 256, smem, ctx->stream>>>(a, b, out, rows, (int)cols, pitch, vec);
+        else if (mode == 1) softmax_rows_kernel<32, 1><<<grid, 256, smem, ctx->stream>>>(a, b, out, rows, (int)cols, pitch, vec);
+        else softmax_rows_kernel<32, 2><<<grid, 256, smem, ctx->stream>>>(a, b, out, rows, (int)cols, pitch, vec);
+    } else if ((size_t)pitch * operands * sizeof(float) <= kStage) { // one block per row
+        const size_t smem = sizeof(float) * (size_t)pitch * operands;
+        if (mode == 0) softmax_rows_kernel<256, 0><<<(unsigned)rows, 256, smem, ctx->stream>>>(a, b, out, rows, (int)cols, pitch, vec);
+        else if (mode == 1) softmax_rows_kernel<256, 1><<<(unsigned)rows, 256, smem, ctx->stream>>>(a, b, out, rows, (int)cols, pitch, vec);
+        else softmax_rows_kernel<256, 2><<<(unsigned)rows, 256, smem, ctx->stream>>>(a, b, out, rows, (int)cols, pitch, vec);
+    } else {
+        softmax_wide_kernel<<<(unsigned)rows, 256, 0, ctx->stream>>>(a, b, out, cols, mode);
+    }
+    MCB_LAUNCHED(ctx);
+    return MCB_OK;
+}
 
 extern "C" {
 
@@ -728,19 +868,15 @@ mcb_status mcb_sum_to(mcb_ctx *ctx, const float *a, const int64_t *ad, int32_t a
 
 mcb_status mcb_softmax(mcb_ctx *ctx, const float *x, float *out, int64_t rows, int64_t cols) {
     MCB_CHECK_CTX(ctx);
-    if (rows == 0 || cols == 0) return MCB_OK;
-    int threads = cols >= 1024 ? 256 : (cols >= 128 ? 128 : 32);
-    softmax_kernel<<<(unsigned)rows, threads, 0, ctx->stream>>>(x, out, cols);
-    MCB_LAUNCHED(ctx);
-    return MCB_OK;
+    return mcb_softmax_rows(ctx, 0, x, nullptr, out, rows, cols);
 }
 mcb_status mcb_softmax_backward(mcb_ctx *ctx, const float *x, const float *g, float *out, int64_t rows, int64_t cols) {
     MCB_CHECK_CTX(ctx);
-    if (rows == 0 || cols == 0) return MCB_OK;
-    int threads = cols >= 1024 ? 256 : (cols >= 128 ? 128 : 32);
-    softmax_backward_kernel<<<(unsigned)rows, threads, 0, ctx->stream>>>(x, g, out, cols);
-    MCB_LAUNCHED(ctx);
-    return MCB_OK;
+    return mcb_softmax_rows(ctx, 1, x, g, out, rows, cols);
+}
+mcb_status mcb_softmax_backward_from_output(mcb_ctx *ctx, const float *y, const float *g, float *out, int64_t rows, int64_t cols) {
+    MCB_CHECK_CTX(ctx);
+    return mcb_softmax_rows(ctx, 2, y, g, out, rows, cols);
 }
 
 mcb_status mcb_layer_norm(mcb_ctx *ctx, const float *x, const float *gamma, const float *beta, double eps, void *out,
@@ -871,6 +1007,20 @@ mcb_status mcb_embedding_backward(mcb_ctx *ctx, const void *ids, int32_t id_dt, 
     if (!index_dtype_ok(id_dt)) return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "ids must be i64, i32 or u8");
     if (!accumulate) MCB_TRY(mcb_memset(ctx, out, 0, sizeof(float) * vocab * dim));
     if (n == 0 || dim == 0) return MCB_OK;
+    if (g_dt != MCB_F32 && g_dt != MCB_BF16 && g_dt != MCB_F16) return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "embedding grad must be f32, bf16 or f16");
+    if (knob_on(ctx, K_DETERMINISTIC)) {
+        if (n > kOrderedEmbeddingMaxTokens)
+            return mcb_fail(ctx, MCB_UNSUPPORTED, "deterministic embedding backward takes at most %lld tokens per call", kOrderedEmbeddingMaxTokens);
+        const size_t smem = sizeof(unsigned int) * (size_t)((n + 31) / 32);
+        if (g_dt == MCB_F32)
+            embedding_backward_ordered_kernel<float><<<(unsigned)n, 256, smem, ctx->stream>>>(ids, id_dt, n, (const float *)g, vocab, (int)dim, out, ctx->d_err);
+        else if (g_dt == MCB_BF16)
+            embedding_backward_ordered_kernel<__nv_bfloat16><<<(unsigned)n, 256, smem, ctx->stream>>>(ids, id_dt, n, (const __nv_bfloat16 *)g, vocab, (int)dim, out, ctx->d_err);
+        else
+            embedding_backward_ordered_kernel<__half><<<(unsigned)n, 256, smem, ctx->stream>>>(ids, id_dt, n, (const __half *)g, vocab, (int)dim, out, ctx->d_err);
+        MCB_LAUNCHED(ctx);
+        return MCB_OK;
+    }
     int grid = mcb_grid_for(ctx, n * dim, kThreads);
     if (g_dt == MCB_F32)
         embedding_backward_kernel<float><<<grid, kThreads, 0, ctx->stream>>>(ids, id_dt, n, (const float *)g, vocab, (int)dim, out, ctx->d_err);
@@ -898,7 +1048,7 @@ mcb_status mcb_sce_grad(mcb_ctx *ctx, const void *logits, void *out, int32_t dt,
     // algorithmic bytes: one read of the logits, one write of the gradient when requested
     ProfScope prof(ctx, MCB_PROF_LOSS, 0.0, (double)n * c * (mcb_is_lp(dt) ? 2.0 : 4.0) * (out ? 2.0 : 1.0) + 8.0 * n);
     if (mcb_is_lp(dt) && out && stats_in && !loss_out && !stats_out && (c % 8) == 0 && n <= 65535 && mcb_aligned16(logits) && mcb_aligned16(out) &&
-        !getenv("MCB_SCE_NO_STREAM")) {
+        !knob_on(ctx, K_SCE_NO_STREAM)) {
         // gradient pass with known row statistics: pure streaming
         const long long c8 = c / 8;
         dim3 grid((unsigned)((c8 + 1023) / 1024), (unsigned)n);

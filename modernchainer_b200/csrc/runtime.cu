@@ -55,6 +55,12 @@ __global__ void clock_trace_kernel(unsigned long long *buf, int cap, unsigned lo
     buf[0] = (unsigned long long)n;
 }
 
+// the environment names of McbKnob, in its order
+static const char *const kKnobNames[K_COUNT] = {
+    "MCB_UNFUSED_BWD", "MCB_LN_NO_AUX", "MCB_UNFUSED_ADD_LN", "MCB_UNFUSED_QKV", "MCB_CONV_DIRECT", "MCB_FLASH_LEGACY", "MCB_FLASH_LEGACY_BWD",
+    "MCB_SGEMM_NO_SPLIT", "MCB_LN_NO_BULK", "MCB_SCE_NO_STREAM", "MCB_TC_EPI", "MCB_TC_EPI_KB", "MCB_TC_STAGES", "MCB_TC_DIRECT_OUT", "MCB_TC_BN",
+    "MCB_TC_PAIR", "MCB_TC_SPLIT_TAIL", "MCB_GRAPH_INFO", "MCB_DETERMINISTIC", "MCB_NO_DEP_LAUNCH"};
+
 extern "C" {
 
 int32_t mcb_device_count(void) {
@@ -90,9 +96,25 @@ mcb_status mcb_ctx_create(int32_t ordinal, mcb_ctx **out) {
         int v = atoi(lim);
         if (v >= 8 && v < ctx->sm_count) ctx->sm_count = v;
     }
-    ctx->dep_launch = getenv("MCB_NO_DEP_LAUNCH") == nullptr; // test knob: plain stream-ordered launches
+    for (int k = 0; k < K_COUNT; ++k) {
+        const char *v = getenv(kKnobNames[k]);
+        ctx->knobs[k] = !v ? -1 : ((*v >= '0' && *v <= '9') ? atoi(v) : 1);
+    }
+    ctx->dep_launch = !knob_on(ctx, K_NO_DEP_LAUNCH); // test knob: plain stream-ordered launches
     *out = ctx;
     return MCB_OK;
+}
+
+mcb_status mcb_set_knob(mcb_ctx *ctx, const char *name, int32_t value) {
+    MCB_CHECK_CTX(ctx);
+    if (!name) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "mcb_set_knob: no name");
+    for (int k = 0; k < K_COUNT; ++k)
+        if (!strcmp(name, kKnobNames[k])) {
+            ctx->knobs[k] = value < 0 ? -1 : value;
+            if (k == K_NO_DEP_LAUNCH) ctx->dep_launch = value < 0;
+            return MCB_OK;
+        }
+    return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "mcb_set_knob: unknown knob %s", name);
 }
 
 void mcb_ctx_destroy(mcb_ctx *ctx) {

@@ -212,7 +212,7 @@ mcb_status mcb_static_step_create(mcb_model *model, mcb_adam *opt, mcb_scaler *s
             graph = g;
         }
     }
-    if (st == MCB_OK && getenv("MCB_GRAPH_INFO")) { // diagnostic: how many recorded edges are programmatic (dependent launch)
+    if (st == MCB_OK && knob_on(ctx, K_GRAPH_INFO)) { // diagnostic: how many recorded edges are programmatic (dependent launch)
         size_t ne = 0, prog = 0;
         if (cudaGraphGetEdges_v2(graph, nullptr, nullptr, nullptr, &ne) == cudaSuccess && ne) {
             std::vector<cudaGraphNode_t> from(ne), to(ne);

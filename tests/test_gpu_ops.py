@@ -151,11 +151,16 @@ def test_col_sum_bf16(ops, oracle):
     close(ops.col_sum(a, dt=5), a.astype(np.float64).sum(0), 1e-5)
 
 
-@pytest.mark.parametrize("rows,cols", [(2, 3), (1, 1), (7, 129), (64, 1000), (5, 5000)])
+# widths on both sides of each kernel choice: a warp per row up to 1024 columns, a block per row while the row fits
+# shared memory, three sweeps beyond; multiples of four (128-bit loads) and not; a last block with idle warps
+@pytest.mark.parametrize("rows,cols", [(2, 3), (1, 1), (7, 129), (64, 1000), (13, 1023), (9, 1024), (3, 1025), (5, 5000), (4, 6144),
+                                       (3, 6145), (2, 12288), (2, 13001), (4099, 64)])
 def test_softmax_and_backward(ops, oracle, rows, cols):
     x, g = randn(rows, cols) * 3, randn(rows, cols)
-    close(ops.softmax(x), oracle.softmax(x))
+    y = ops.softmax(x)
+    close(y, oracle.softmax(x))
     close(ops.softmax_backward(x, g), oracle.softmax_backward(x, g))
+    close(ops.softmax_backward_from_output(y, g), oracle.softmax_backward(x, g))
 
 
 def test_reference_backward_literals(ops, oracle):
@@ -323,7 +328,7 @@ def test_tc_gemm_split_tail(ops, oracle, m, n, k, a_mn, b_mn):
     outs = {}
     try:
         for knob in ("1", "0"):
-            os.environ["MCB_TC_SPLIT_TAIL"] = knob
+            ops.ctx.set_knob("MCB_TC_SPLIT_TAIL", int(knob))
             out = ops.gemm_bf16(a, a_mn, b, b_mn, m, n, k, out_dt=0, bias=bias)
             close(out, ref, 2e-5)
             out16 = ops.gemm_bf16(a, a_mn, b, b_mn, m, n, k, out_dt=5, bias=bias)
@@ -333,7 +338,7 @@ def test_tc_gemm_split_tail(ops, oracle, m, n, k, a_mn, b_mn):
             init = randn(m, n)
             close(ops.gemm_bf16(a, a_mn, b, b_mn, m, n, k, out_dt=0, accumulate=True, split_k=1, init=init), ref - bias + init, 2e-5)
     finally:
-        os.environ.pop("MCB_TC_SPLIT_TAIL", None)
+        ops.ctx.set_knob("MCB_TC_SPLIT_TAIL", None)
     close(outs["1"][0], outs["0"][0], 2e-6)  # same products, another grouping of the f32 sums
 
 
@@ -418,13 +423,13 @@ def test_conv2d_tensor_core_path(ops, oracle, shape, wshape, stride, pad):
     got = ops.conv2d_backward(x, w, g, stride, pad)
     for a, r in zip(got, ref):
         close(a, r, 1e-5)
-    os.environ["MCB_CONV_DIRECT"] = "1"
+    ops.ctx.set_knob("MCB_CONV_DIRECT", 1)
     try:
         close(out, ops.conv2d(x, w, b, stride, pad), 2e-6)
         for a, r in zip(got, ops.conv2d_backward(x, w, g, stride, pad)):
             close(a, r, 2e-6)
     finally:
-        os.environ.pop("MCB_CONV_DIRECT", None)
+        ops.ctx.set_knob("MCB_CONV_DIRECT", None)
 
 
 def test_max_pool_tie_rule(ops, oracle):

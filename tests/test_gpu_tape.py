@@ -414,9 +414,9 @@ def test_fused_qkv_attention_matches_composed_ops(mc, ctx, cfg):
 
     def run(unfused):
         if unfused:
-            os.environ["MCB_UNFUSED_QKV"] = "1"
+            ctx.set_knob("MCB_UNFUSED_QKV", 1)
         else:
-            os.environ.pop("MCB_UNFUSED_QKV", None)
+            ctx.set_knob("MCB_UNFUSED_QKV", None)
         try:
             m = mc.Model(ctx, "decoder", [vocab, d, heads, ff, layers, 0])
             ps = m.parameters()
@@ -426,7 +426,7 @@ def test_fused_qkv_attention_matches_composed_ops(mc, ctx, cfg):
             loss.backward()
             return float(loss.data.reshape(-1)[0]), [p.grad for p in ps]
         finally:
-            os.environ.pop("MCB_UNFUSED_QKV", None)
+            ctx.set_knob("MCB_UNFUSED_QKV", None)
 
     lf, gf = run(False)
     lu, gu = run(True)
@@ -452,9 +452,9 @@ def test_fused_backward_passes_match_separate_kernels(mc, ctx, cfg):
 
     def run(unfused):
         if unfused:
-            os.environ["MCB_UNFUSED_BWD"] = "1"
+            ctx.set_knob("MCB_UNFUSED_BWD", 1)
         else:
-            os.environ.pop("MCB_UNFUSED_BWD", None)
+            ctx.set_knob("MCB_UNFUSED_BWD", None)
         try:
             m = mc.Model(ctx, "decoder", [vocab, d, heads, ff, layers, 0])
             ps = m.parameters()
@@ -464,7 +464,7 @@ def test_fused_backward_passes_match_separate_kernels(mc, ctx, cfg):
             loss.backward()
             return float(loss.data.reshape(-1)[0]), [p.grad for p in ps], [p.data.shape for p in ps]
         finally:
-            os.environ.pop("MCB_UNFUSED_BWD", None)
+            ctx.set_knob("MCB_UNFUSED_BWD", None)
 
     lf, gf, shapes = run(False)
     lu, gu, _ = run(True)
@@ -491,9 +491,9 @@ def test_layer_norm_pipeline_kernels_match_register_kernels_on_the_tape(mc, ctx,
 
     def run(no_bulk):
         if no_bulk:
-            os.environ[knob] = "1"
+            ctx.set_knob(knob, 1)
         else:
-            os.environ.pop(knob, None)
+            ctx.set_knob(knob, None)
         try:
             m = mc.Model(ctx, "decoder", [vocab, d, heads, ff, layers, 0])
             ps = m.parameters()
@@ -503,7 +503,7 @@ def test_layer_norm_pipeline_kernels_match_register_kernels_on_the_tape(mc, ctx,
             loss.backward()
             return float(loss.data.reshape(-1)[0]), [p.grad for p in ps], [p.data.shape for p in ps]
         finally:
-            os.environ.pop(knob, None)
+            ctx.set_knob(knob, None)
 
     lp, gp, shapes = run(False)
     lr, gr, _ = run(True)
@@ -525,7 +525,7 @@ def test_streaming_loss_gradient_matches_row_kernel(mc, ctx):
 
     def run(row_kernel):
         if row_kernel:
-            os.environ["MCB_SCE_NO_STREAM"] = "1"
+            ctx.set_knob("MCB_SCE_NO_STREAM", 1)
         try:
             m = mc.Model(ctx, "decoder", [vocab, d, heads, ff, layers, 0])
             ps = m.parameters()
@@ -535,7 +535,7 @@ def test_streaming_loss_gradient_matches_row_kernel(mc, ctx):
             loss.backward()
             return float(loss.data.reshape(-1)[0]), [p.grad for p in ps]
         finally:
-            os.environ.pop("MCB_SCE_NO_STREAM", None)
+            ctx.set_knob("MCB_SCE_NO_STREAM", None)
 
     ls, gs = run(False)
     lr, gr = run(True)

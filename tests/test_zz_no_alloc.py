@@ -8,9 +8,10 @@ mcb_layer_norm_backward_noalloc keeps them in a fixed array inside the library i
 
 The test calls the new entry point through the C ABI twice in a row, with different sizes, so the
 second call runs over whatever the first one left in the shared array, and compares each result
-with the regular entry point on the same inputs (2e-5 relative per tensor, the tolerance the other
-LayerNorm tests use; the two paths sum the partials in a different order).  The file is named so
-pytest collects it last.
+with the regular entry point on the same inputs and, as a second and independent comparand, with the
+CPU oracle (2e-5 relative per tensor, the tolerance the other LayerNorm tests use; the paths sum the
+partials in a different order), so a defect shared by both device entry points cannot hide.  The file
+is named so pytest collects it last.
 """
 import ctypes as C
 
@@ -27,7 +28,7 @@ def close(a, b, tol=2e-5):
     assert err <= tol, f"relative error {err:.3e} > {tol}"
 
 
-def run_pair(mc, ctx, rng, rows, dim, g_dt, use_stats):
+def run_pair(mc, ctx, rng, rows, dim, g_dt, use_stats, oracle):
     lib = ctx.lib
     x = (rng.standard_normal((rows, dim)) * 2 + 0.5).astype(np.float32)
     g = rng.standard_normal((rows, dim)).astype(np.float32)
@@ -48,9 +49,12 @@ def run_pair(mc, ctx, rng, rows, dim, g_dt, use_stats):
     assert st == 0, lib.mcb_noalloc_last_error()
     for a, b in zip(out, ref):
         close(a.numpy(), b.numpy())
+    g_seen = oracle.round_bf16(g) if g_dt == mc.BF16 else g  # the gradient values the device read
+    for a, b in zip(out, oracle.layer_norm_backward(x, gamma, g_seen, 1e-5)):
+        close(a.numpy(), b)
 
 
-def test_noalloc_layer_norm_backward_matches_regular_entry_point():
+def test_noalloc_layer_norm_backward_matches_regular_entry_point(oracle):
     import modernchainer_b200 as mc
     ctx = mc.Context(0)
     try:
@@ -58,9 +62,9 @@ def test_noalloc_layer_norm_backward_matches_regular_entry_point():
         rng = np.random.default_rng(77)
         # two calls in a row; the second is smaller and narrower, so stale partial sums of the first
         # stay in the shared array next to the ones it writes
-        run_pair(mc, ctx, rng, 1000, 768, mc.F32, use_stats=True)
-        run_pair(mc, ctx, rng, 37, 130, mc.BF16, use_stats=False)
-        run_pair(mc, ctx, rng, 1, 4096, mc.F32, use_stats=False)
+        run_pair(mc, ctx, rng, 1000, 768, mc.F32, True, oracle)
+        run_pair(mc, ctx, rng, 37, 130, mc.BF16, False, oracle)
+        run_pair(mc, ctx, rng, 1, 4096, mc.F32, False, oracle)
         # sizes beyond the built-in array are refused with a message and nothing is enqueued
         stream = C.c_void_p(lib.mcb_stream(ctx.h))
         st = lib.mcb_layer_norm_backward_noalloc(stream, None, None, None, mc.F32, 1e-5, None, None, None, None, None, 4, 4097)
