@@ -8,7 +8,7 @@ argument names, so that code written against the reference's package runs on thi
 There is one compute backend here, the sm_100a library.  Device strings ("cpu", "cuda", "cuda:0") are
 accepted and remembered for source compatibility, but every operation executes on the GPU of the
 process-wide context; nothing is computed on the host.  Parts of the reference's surface that lie
-outside the training-step path (BatchNorm, ConvTranspose2d, RMSNorm, dropout, clamp, average pooling,
+outside the training-step path (ConvTranspose2d, RMSNorm, dropout, clamp, average pooling,
 Vulkan) raise NotImplementedError.
 """
 from contextlib import contextmanager
@@ -293,7 +293,20 @@ def _outside(name):
     return _Missing
 
 
-BatchNorm = _outside("BatchNorm")
+class BatchNorm(_Link):
+    """nn::BatchNorm (nn/src/lib.rs:395-423): gamma ones, beta zeros, batch statistics."""
+
+    def __init__(self, channels, eps=1e-5, device="cpu"):
+        self.gamma = Variable(Tensor(np.ones(channels, np.float32), device))
+        self.beta = Variable(Tensor(np.zeros(channels, np.float32), device))
+        self.eps = eps
+        self._params = [self.gamma, self.beta]
+
+    def forward(self, x):
+        from . import functions as F
+        return F.batch_norm(x, self.gamma, self.beta, self.eps)
+
+
 ConvTranspose2d = _outside("ConvTranspose2d")
 RMSNorm = _outside("RMSNorm")
 

@@ -129,8 +129,28 @@ def _outside(name):
     return f
 
 
+def batch_norm(x, gamma, beta, eps=1e-5):
+    """Batch statistics per channel over (N, spatial...), as host_ops.rs:488-532 (a host op in the reference).  Composed
+    from ops of the path: with channels moved to the rows of a [C, N * spatial] matrix it is a LayerNorm of each row
+    with unit scale, then a per-row scale and shift; the tape differentiates the composition."""
+    import numpy as np
+    from . import Tensor
+    dims = list(x.shape)
+    if len(dims) < 2:
+        raise ValueError("batch_norm expects rank >= 2")
+    n, c = dims[0], dims[1]
+    if list(gamma.shape) != [c] or list(beta.shape) != [c]:
+        raise ValueError("batch_norm gamma/beta size mismatch")
+    m = int(np.prod([n] + dims[2:]))
+    axes = [1, 0] + list(range(2, len(dims)))
+    rows = reshape(permute(x, axes), [c, m])
+    one = Variable.constant(Tensor(np.ones(m, np.float32), x.device))
+    zero = Variable.constant(Tensor(np.zeros(m, np.float32), x.device))
+    y = add(mul(layer_norm(rows, one, zero, eps), reshape(gamma, [c, 1])), reshape(beta, [c, 1]))
+    return permute(reshape(y, [c, n] + dims[2:]), axes)
+
+
 average_pool2d = _outside("average_pool2d")
-batch_norm = _outside("batch_norm")
 clamp = _outside("clamp")
 conv_transpose2d = _outside("conv_transpose2d")
 dropout = _outside("dropout")

@@ -63,6 +63,10 @@ struct mcb_ctx {
     // Programmatic dependent launch: kernels launched through mcb_launch_dep may be scheduled while the
     // previous kernel of the stream drains; they call dep_wait() before touching global memory.
     bool dep_launch = true;
+    // counters of the tensor-core GEMM's in-kernel split-tail fix-up (148 tiles x 2 pair halves x 8 warps x 2); zero
+    // between launches: the slice that finishes a tile resets them
+    unsigned *tc_fix_cnt = nullptr;
+    static constexpr size_t kTcFixCntBytes = 148 * 2 * 8 * 2 * sizeof(unsigned);
     // Test and tuning knobs (McbKnob): -1 = not set.  Each is read from the environment once, when the context is created;
     // afterwards only mcb_set_knob changes it, for this context alone.  No entry point reads the environment.
     int knobs[32];
@@ -71,7 +75,7 @@ struct mcb_ctx {
 enum McbKnob {
     K_UNFUSED_BWD, K_LN_NO_AUX, K_UNFUSED_ADD_LN, K_UNFUSED_QKV, K_CONV_DIRECT, K_FLASH_LEGACY, K_FLASH_LEGACY_BWD, K_SGEMM_NO_SPLIT,
     K_LN_NO_BULK, K_SCE_NO_STREAM, K_TC_EPI, K_TC_EPI_KB, K_TC_STAGES, K_TC_DIRECT_OUT, K_TC_BN, K_TC_PAIR, K_TC_SPLIT_TAIL,
-    K_GRAPH_INFO, K_DETERMINISTIC, K_NO_DEP_LAUNCH, K_COUNT
+    K_GRAPH_INFO, K_DETERMINISTIC, K_NO_DEP_LAUNCH, K_FLASH_DQ_RECOMPUTE, K_COUNT
 };
 static_assert(K_COUNT <= 32, "mcb_ctx::knobs is too small");
 inline bool knob_on(const mcb_ctx *ctx, McbKnob k) { return ctx->knobs[k] >= 0; } // flag knobs: set at all

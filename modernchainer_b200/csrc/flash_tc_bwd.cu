@@ -1,6 +1,10 @@
-// Fused attention backward on the tcgen05 tensor cores (bf16, head_dim 64), two kernels from one template:
+// Fused attention backward on the tcgen05 tensor cores (bf16 / f16, head_dim 64): two kernels from one template and a third:
 //   MODE 0 (dK, dV): one CTA per 128-key tile; K_j, V_j stay in shared memory, the query tiles stream through.
-//   MODE 1 (dQ)    : one CTA per 128-query tile; Q_i, dO_i stay, the key tiles stream through.
+//   MODE 1 (dQ)    : one CTA per 128-query tile; Q_i, dO_i stay, the key tiles stream through (recomputes S, dP, dS).
+//   flash_tc_dq_kernel: dQ += dS K from the dS tiles that MODE 0 leaves in a scratch buffer as it goes (32 KB per pair,
+//                    the bytes of its shared-memory tile), so dQ costs 8 MMAs per pair and no exponentials instead of 16
+//                    MMAs and a second evaluation of P and dS.  The default; MODE 1 stays for sequences whose dS would
+//                    not fit the scratch limit and as a cross-check (knob MCB_FLASH_DQ_RECOMPUTE).
 // Per (query tile, key tile) pair, with rows = queries (TMEM lanes) and columns = keys:
 //   S  = Q K^T, dP = dO V^T         tcgen05.mma M=128 N=128 K=64 each, both into TMEM
 //   P  = exp2(S * scale*log2e - lse*log2e),  dS = P * (dP - delta)     (masked pairs give 0)
@@ -43,7 +47,11 @@ struct BwdArgs {
     // their final reduction): row (sample * tiles + tile) * 4 + lane quarter of [.., bias_ld], columns which * dim + head * 64
     float *bias_partial;
     int bias_ld, dim;
+    // MODE 0 only, optional: where to leave dS of every pair for flash_tc_dq_kernel, [sample * heads + head][query tile][key tile]
+    // blocks of kDsBytes (the shared-memory tile as it is)
+    unsigned char *ds_out;
 };
+constexpr int kDsBytes = 2 * kTileBytes;
 
 template <int MODE, bool F16>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -183,6 +191,12 @@ flash_tc_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 tc_fence_after();
                 const unsigned y0 = smem_u32(smem + kSmemY + st * 2 * kTileBytes), y1 = y0 + kTileBytes;
                 const unsigned acc = (t > 0) ? 1u : 0u;
+                const bool spill = MODE == 0 && args.ds_out != nullptr;
+                if (spill) { // dS of this pair to the scratch of the dQ kernel, while the MMAs below read the same tile
+                    const size_t slot = ((size_t)nh * tiles + (size_t)(t_first + t)) * tiles + (size_t)own;
+                    bulk_store(args.ds_out + slot * kDsBytes, sDS, kDsBytes);
+                    bulk_commit();
+                }
                 if (MODE == 0) {
                     // dV += P^T dO, dK += dS^T Q: A is MN-major over [key block (16 KB)][query block (8 KB)] atoms,
                     // 16 queries per step = 2048 bytes inside a query block; B = dO / Q as loaded ([queries, hd]: MN-major)
@@ -206,9 +220,11 @@ flash_tc_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                         tc_mma_ta(tmem_base + kColAcc0, tmem_base + kColDSt + ks * 8, make_desc(y0 + ks * 2048, 8192, 1024), idesc_acc,
                                   (ks > 0) ? 1u : acc);
                 }
+                if (spill) bulk_wait_read0(); // mma_done also tells the rows that dS may be overwritten
                 tc_commit(mma_done);
                 tc_commit(&y_empty[st]);
             }
+            if (MODE == 0 && args.ds_out) bulk_wait_all();
         }
     } else {
         // ------------------------------------------------------------ pair arithmetic and epilogue (warps 2..9)
@@ -358,6 +374,169 @@ flash_tc_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     if (MODE == 1) dep_wait();
 }
 
+// ------------------------------------------------------------------ dQ from the dS tiles of the dK/dV kernel
+// One CTA per (128-query tile, sample, head), two per SM.  Per key tile: one 32 KB bulk copy of dS (two [128 queries x 64
+// keys] K-major tiles with the 128-byte swizzle, exactly as the dK/dV kernel's rows wrote them) and the K tile, then
+// dQ += dS K as eight M=128 N=64 K=16 MMAs into 64 TMEM columns.  Roles (192 threads): warp 0 copies, warp 1 MMAs,
+// warps 2..5 the epilogue (scale, round, TMA store, column sums for the q bias gradient).  Every wait is bounded.
+constexpr int kDqThreads = 192;
+constexpr int kDqStages = 2;
+constexpr int kDqStageBytes = kDsBytes + kTileBytes; // 48 KB
+constexpr int kDqSmemOut = kDqStages * kDqStageBytes, kDqSmemBar = kDqSmemOut + 4 * 4096;
+constexpr int kDqSmemBytes = kDqSmemBar + 128 + 768;
+static_assert(2 * (kDqSmemBytes + 1024) <= 228 * 1024, "two CTAs per SM");
+
+struct DqArgs {
+    const unsigned char *ds;
+    int seq, heads, causal;
+    float scale;
+    unsigned int *err;
+    float *bias_partial;
+    int bias_ld, dim;
+};
+
+template <bool F16>
+__global__ void __launch_bounds__(kDqThreads, 2)
+flash_tc_dq_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_dq, DqArgs args) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char *smem = (unsigned char *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    unsigned long long *bars = (unsigned long long *)(smem + kDqSmemBar);
+    unsigned long long *full = bars, *empty = bars + kDqStages, *acc_done = bars + 2 * kDqStages;
+    unsigned *tmem_slot = (unsigned *)(acc_done + 1);
+    volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int lin = (int)(blockIdx.y * gridDim.x + blockIdx.x), rank = lin / (int)gridDim.y, nh = lin - rank * (int)gridDim.y;
+    const int n = nh / args.heads, h = nh % args.heads;
+    const int tiles = (args.seq + BT - 1) / BT;
+    const int own = args.causal ? (int)gridDim.x - 1 - rank : rank; // late query tiles walk the most key tiles: first
+    const int nt = args.causal ? own + 1 : tiles;
+    const int o0 = own * BT;
+    if ((uintptr_t)(smem + kDqSmemBar + 128) > (uintptr_t)smem_raw + kDqSmemBytes) { // the dynamic segment started less aligned than assumed
+        if (threadIdx.x == 0) atomicOr(args.err, MCB_DEVERR_TIMEOUT);
+        return;
+    }
+    if (threadIdx.x == 0) {
+        prefetch_map(&map_k);
+        prefetch_map(&map_dq);
+        for (int s = 0; s < kDqStages; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        mbar_init(acc_done, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, 64);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const unsigned tmem_base = *tmem_slot;
+    dep_wait(); // the dS tiles come from the kernel before this one
+    dep_trigger();
+
+    if (warp == 0) {
+        if (lane == 0) {
+            const unsigned char *src = args.ds + ((size_t)nh * tiles + (size_t)own) * tiles * kDsBytes;
+            bool ok = true;
+            for (int t = 0; t < nt && ok; ++t) {
+                const int st = t % kDqStages;
+                ok = mbar_wait(&empty[st], ((unsigned)(t / kDqStages) & 1u) ^ 1u, abort_flag, args.err);
+                if (!ok) break;
+                unsigned char *sd = smem + st * kDqStageBytes;
+                mbar_expect_tx(&full[st], kDqStageBytes);
+                bulk_load(sd, src + (size_t)t * kDsBytes, kDsBytes, &full[st]);
+                tma_load_3d(sd + kDsBytes, &map_k, &full[st], h * HD, t * BT, n);
+            }
+            for (int st = 0; st < kDqStages && ok; ++st) { // drain: nothing is still landing in shared memory at exit
+                const int fills = (nt > st) ? ((nt - 1 - st) / kDqStages + 1) : 0;
+                if (fills) ok = mbar_wait(&empty[st], (unsigned)(fills - 1) & 1u, abort_flag, args.err);
+            }
+            if (*abort_flag) {
+                unsigned long long t0 = global_ns();
+                while (global_ns() - t0 < 200000ull) {
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr unsigned idesc = make_idesc(BT, HD, 0, 1, F16); // A = dS (K-major), B = K as loaded ([keys, hd]: MN-major)
+            bool ok = true;
+            for (int t = 0; t < nt && ok; ++t) {
+                const int st = t % kDqStages;
+                ok = mbar_wait(&full[st], (unsigned)(t / kDqStages) & 1u, abort_flag, args.err);
+                if (!ok) break;
+                tc_fence_after();
+                const unsigned ds_addr = smem_u32(smem + st * kDqStageBytes), k_addr = ds_addr + kDsBytes;
+#pragma unroll
+                for (int ks = 0; ks < BT / 16; ++ks) // 16 keys per step: 32 bytes inside a 64-key block of 16 KB
+                    tc_mma(tmem_base, make_desc(ds_addr + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024), make_desc(k_addr + ks * 2048, 8192, 1024), idesc,
+                           (t > 0 || ks > 0) ? 1u : 0u);
+                tc_commit(&empty[st]);
+            }
+            if (ok) tc_commit(acc_done);
+        }
+    } else {
+        const int wq = warp & 3;
+        const unsigned lane_addr = ((unsigned)(wq * 32) << 16);
+        bool ok = nt > 0 ? mbar_wait(acc_done, 0, abort_flag, args.err) : true;
+        if (ok) {
+            tc_fence_after();
+            unsigned char *stage = smem + kDqSmemOut + wq * 4096; // this warp's [32 rows x 128 bytes] box
+#pragma unroll 1
+            for (int c = 0; c < HD / 32; ++c) {
+                unsigned o[32];
+                if (nt > 0) {
+                    tmem_ld32(tmem_base + lane_addr + c * 32, o);
+                    tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) o[e] = 0u;
+                }
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    uint4 piece;
+                    piece.x = pack16<F16>(__uint_as_float(o[q * 8]) * args.scale, __uint_as_float(o[q * 8 + 1]) * args.scale);
+                    piece.y = pack16<F16>(__uint_as_float(o[q * 8 + 2]) * args.scale, __uint_as_float(o[q * 8 + 3]) * args.scale);
+                    piece.z = pack16<F16>(__uint_as_float(o[q * 8 + 4]) * args.scale, __uint_as_float(o[q * 8 + 5]) * args.scale);
+                    piece.w = pack16<F16>(__uint_as_float(o[q * 8 + 6]) * args.scale, __uint_as_float(o[q * 8 + 7]) * args.scale);
+                    const int chunk = c * 4 + q;
+                    *(uint4 *)(stage + lane * 128 + ((chunk ^ (lane & 7)) << 4)) = piece;
+                }
+            }
+            fence_async_smem();
+            __syncwarp();
+            if (args.bias_partial) { // lane l sums columns 2l, 2l+1 of this warp's 32 staged rows (the rounded values)
+                float c0 = 0.0f, c1 = 0.0f;
+                const int rows_live = min(32, args.seq - (o0 + wq * 32));
+                for (int rr = 0; rr < rows_live; ++rr) {
+                    const unsigned w2 = *(const unsigned *)(stage + rr * 128 + (((lane >> 2) ^ (rr & 7)) << 4) + (lane & 3) * 4);
+                    if (F16) {
+                        const float2 pr = __half22float2(*reinterpret_cast<const __half2 *>(&w2));
+                        c0 += pr.x;
+                        c1 += pr.y;
+                    } else {
+                        c0 += __uint_as_float(w2 << 16);
+                        c1 += __uint_as_float(w2 & 0xFFFF0000u);
+                    }
+                }
+                float *dst = args.bias_partial + ((size_t)(n * tiles + own) * 4 + wq) * args.bias_ld + h * HD + 2 * lane;
+                *(float2 *)dst = make_float2(c0, c1);
+            }
+            if (lane == 0 && o0 + wq * 32 < args.seq) {
+                tma_store_3d(&map_dq, stage, h * HD, o0 + wq * 32, n);
+                bulk_commit();
+                bulk_wait_read0();
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, 64);
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
                                   const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
                                   CUtensorMapFloatOOBfill);
@@ -422,20 +601,51 @@ mcb_status mcb_flash_tc_backward(mcb_ctx *ctx, const void *q, const void *k, con
     a.bias_partial = bias_partial;
     a.bias_ld = (int)bias_ld;
     a.dim = (int)dim;
+    a.ds_out = nullptr;
+    // dQ from the dS tiles the dK/dV kernel leaves (32 KB per pair of tiles), unless that scratch would pass 1 GiB
+    const long long tiles = (seq + BT - 1) / BT;
+    const size_t ds_bytes = (size_t)n * heads * tiles * tiles * kDsBytes;
+    void *ds = nullptr;
+    if (!knob_on(ctx, K_FLASH_DQ_RECOMPUTE) && ds_bytes <= ((size_t)1 << 30)) {
+        MCB_TRY(mcb_alloc(ctx, ds_bytes, &ds));
+        a.ds_out = (unsigned char *)ds;
+    }
     static bool attr_set = false;
     if (!attr_set) {
         MCB_CUDA(ctx, cudaFuncSetAttribute(flash_tc_bwd_kernel<0, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
         MCB_CUDA(ctx, cudaFuncSetAttribute(flash_tc_bwd_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
         MCB_CUDA(ctx, cudaFuncSetAttribute(flash_tc_bwd_kernel<0, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
         MCB_CUDA(ctx, cudaFuncSetAttribute(flash_tc_bwd_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+        MCB_CUDA(ctx, cudaFuncSetAttribute(flash_tc_dq_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDqSmemBytes));
+        MCB_CUDA(ctx, cudaFuncSetAttribute(flash_tc_dq_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDqSmemBytes));
         attr_set = true;
     }
-    dim3 grid((unsigned)((seq + BT - 1) / BT), (unsigned)(n * heads));
-    if (f16) MCB_CUDA(ctx, mcb_launch_dep(ctx, flash_tc_bwd_kernel<0, true>, grid, dim3(kThreads), kSmemBytes, mq, mk, mv, mdo, mdv, mdk, a));
-    else MCB_CUDA(ctx, mcb_launch_dep(ctx, flash_tc_bwd_kernel<0, false>, grid, dim3(kThreads), kSmemBytes, mq, mk, mv, mdo, mdv, mdk, a));
-    MCB_LAUNCHED(ctx);
-    if (f16) MCB_CUDA(ctx, mcb_launch_dep(ctx, flash_tc_bwd_kernel<1, true>, grid, dim3(kThreads), kSmemBytes, mq, mk, mv, mdo, mdq, mdq, a));
-    else MCB_CUDA(ctx, mcb_launch_dep(ctx, flash_tc_bwd_kernel<1, false>, grid, dim3(kThreads), kSmemBytes, mq, mk, mv, mdo, mdq, mdq, a));
+    dim3 grid((unsigned)tiles, (unsigned)(n * heads));
+    cudaError_t e;
+    if (f16) e = mcb_launch_dep(ctx, flash_tc_bwd_kernel<0, true>, grid, dim3(kThreads), kSmemBytes, mq, mk, mv, mdo, mdv, mdk, a);
+    else e = mcb_launch_dep(ctx, flash_tc_bwd_kernel<0, false>, grid, dim3(kThreads), kSmemBytes, mq, mk, mv, mdo, mdv, mdk, a);
+    if (e == cudaSuccess) {
+        ctx->launches++;
+        if (ds) {
+            DqArgs d;
+            d.ds = (const unsigned char *)ds;
+            d.seq = (int)seq;
+            d.heads = (int)heads;
+            d.causal = causal;
+            d.scale = a.scale;
+            d.err = ctx->d_err;
+            d.bias_partial = bias_partial;
+            d.bias_ld = (int)bias_ld;
+            d.dim = (int)dim;
+            if (f16) e = mcb_launch_dep(ctx, flash_tc_dq_kernel<true>, grid, dim3(kDqThreads), kDqSmemBytes, mk, mdq, d);
+            else e = mcb_launch_dep(ctx, flash_tc_dq_kernel<false>, grid, dim3(kDqThreads), kDqSmemBytes, mk, mdq, d);
+        } else {
+            if (f16) e = mcb_launch_dep(ctx, flash_tc_bwd_kernel<1, true>, grid, dim3(kThreads), kSmemBytes, mq, mk, mv, mdo, mdq, mdq, a);
+            else e = mcb_launch_dep(ctx, flash_tc_bwd_kernel<1, false>, grid, dim3(kThreads), kSmemBytes, mq, mk, mv, mdo, mdq, mdq, a);
+        }
+    }
+    if (ds) mcb_free(ctx, ds); // stream-ordered reuse: whoever gets the block next is enqueued behind the dQ kernel
+    MCB_CUDA(ctx, e);
     MCB_LAUNCHED(ctx);
     return MCB_OK;
 }

@@ -51,12 +51,26 @@ struct TcArgs {
     int stages; // depth of the operand ring actually used (tuning knob; at most the compiled depth)
     int ring;   // output boxes per epilogue warp: 2, or 4 when one operand stage is given up for them
     int epi_groups; // epilogue groups of four warps in use: 1 or 2
-    // Split tail (sk_splits > 1): work items [0, sk_full) are whole tiles; the sk_rem tiles that would form a
-    // mostly empty last wave are each cut into sk_splits slices of sk_kb k-blocks, whose f32 partial sums are
-    // added into a workspace (map_pre) that a finishing kernel converts into the output.
+    // Split tail (sk_splits > 1): the sk_rem tiles that would form a mostly empty last wave (tile indices from sk_full
+    // on) are each cut into sk_splits slices of sk_kb k-blocks; the slices are the first work items, the sk_full whole
+    // tiles follow.  An accumulating output takes the
+    // slices' f32 partial sums directly (TMA reduce-add through map_pre = the output).  Any other output is finished
+    // inside the kernel: slices 1 .. S-1 leave their partial sums in fix_ws, slice 0 adds them to its own accumulator in
+    // slice order and runs the normal epilogue (bias, activation, rounding, second output).
     int sk_full, sk_rem, sk_splits, sk_kb;
+    // [sk_rem][2 (pair half)][sk_splits - 1][4 lane quarters][BN / 32 column blocks][8][32 lanes] float4: the 32 x 32 block a warp
+    // reads from TMEM at once, laid out so that one warp-wide store or load covers 512 contiguous bytes; nullptr unless
+    // slices are finished in the kernel
+    float *fix_ws;
+    unsigned *fix_cnt; // [sk_rem][2][8 epilogue warps]: slices that have left their partial sums; zero between launches
     unsigned int *err;
 };
+
+constexpr int kFixTiles = 148;        // split-tail tiles a launch may finish in the kernel (size of mcb_ctx::tc_fix_cnt)
+// planner's charge for leaving and collecting the partial sums of a split tail.  Measured on 8192-row problems with 768
+// output columns (96 tiles of 256 x 256 on 74 CTA pairs): K = 3072 gains 2 us over 128 x 192 tiles, K = 2304 loses 2 us,
+// K = 768 loses 8 us; 7000 cycles puts the line between the first two.
+constexpr double kFixCycles = 7000.0;
 
 struct WorkItem {
     unsigned t;   // tile index (tn-major: t = tn * m_tiles + tm)
@@ -67,14 +81,17 @@ struct WorkItem {
 __device__ __forceinline__ WorkItem decode_work(const TcArgs &args, unsigned w, unsigned tiles_mn, bool one_split) {
     WorkItem it;
     if (args.sk_splits > 1) {
-        if (w < (unsigned)args.sk_full) {
-            it.t = w;
+        // the slices come FIRST: what follows them in a worker's list (whole tiles) hides the time their partial sums
+        // take to meet, and the last item of every worker ends with a plain epilogue
+        const unsigned n_slices = (unsigned)args.sk_rem * (unsigned)args.sk_splits;
+        if (w >= n_slices) {
+            it.t = w - n_slices;
             it.kb0 = 0;
             it.kb1 = args.kb_total;
             it.split = 0;
             it.partial = false;
         } else {
-            const unsigned idx = w - (unsigned)args.sk_full, q = idx / (unsigned)args.sk_splits;
+            const unsigned idx = w, q = idx / (unsigned)args.sk_splits;
             it.split = (int)(idx - q * (unsigned)args.sk_splits);
             it.t = (unsigned)args.sk_full + q;
             it.kb0 = it.split * args.sk_kb;
@@ -125,6 +142,26 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long *bar, unsigned pari
     for (;;) {
         if (mbar_test(bar, parity)) return true;
         if (sleep_ns) __nanosleep(sleep_ns); // waits a whole tile long: leave the issue slots to the MMA warp
+        if ((++spins & 63u) == 0) {
+            if (*abort_flag) return false;
+            if (global_ns() - t0 > kWaitLimitNs) {
+                *abort_flag = 1;
+                atomicOr(err, MCB_DEVERR_TIMEOUT);
+                return false;
+            }
+        }
+    }
+}
+
+// Bounded wait until the counter at `flag` (written by other CTAs of this launch) has reached `want`.
+__device__ __forceinline__ bool flag_wait(const unsigned *flag, unsigned want, volatile int *abort_flag, unsigned int *err) {
+    unsigned long long t0 = global_ns();
+    unsigned spins = 0;
+    for (;;) {
+        unsigned v;
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+        if (v >= want) return true;
+        __nanosleep(64);
         if ((++spins & 63u) == 0) {
             if (*abort_flag) return false;
             if (global_ns() - t0 > kWaitLimitNs) {
@@ -578,12 +615,63 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (!mbar_wait(&acc_full[acc], acc_ph, abort_flag, args.err, 100u)) break;
             tc_fence_after();
             long long row = m0 + q * 32 + lane;
-            bool add_bias = args.bias != nullptr && split == 0 && !part;
+            // ---- slice of a split-tail tile whose output is finished in the kernel.  Each epilogue warp settles its own
+            // elements with the warps of the same index in the other slices.  Slices 1 .. S-1 leave their partial sums
+            // (slot = slice - 1) and count themselves done; slice 0 waits (bounded) for that count, adds the partial
+            // sums to its accumulator in slice order -- so the result does not depend on who finished first -- and runs
+            // the normal epilogue.  All slices of a launch are first items of distinct workers, so the ones slice 0
+            // waits for are running at the same time and depend on nothing.
+            int others = 0;
+            const float *pbase = nullptr;
+            if (part && args.fix_ws) {
+                const unsigned ridx = t - (unsigned)args.sk_full;
+                unsigned *cnt = args.fix_cnt + ((ridx * 2u + crank) * 8u + (unsigned)ew);
+                const int n_other = args.sk_splits - 1;
+                float *mine = args.fix_ws + (size_t)(ridx * 2u + crank) * (size_t)n_other * (size_t)(BM * BN) + (size_t)(q * 32) * BN + lane * 4;
+                if (split > 0) {
+                    float *dst = mine + (size_t)(split - 1) * (size_t)(BM * BN);
+                    const int cw = args.out_bf16 ? 64 : 32; // the chunks this warp owns in the finishing pass of this launch
+#pragma unroll 1
+                    for (int c0 = grp * cw; c0 < BN; c0 += cw * groups) {
+#pragma unroll 1
+                        for (int h = 0; h < cw; h += 32) {
+                            unsigned r[32];
+                            tmem_ld32(tmem_base + ((unsigned)(q * 32) << 16) + (unsigned)(acc * BN + c0 + h), r);
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) *(uint4 *)(dst + (c0 + h) * 32 + j * 128) = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+                        }
+                    }
+                    __threadfence();
+                    __syncwarp();
+                    if (lane == 0) atomicAdd(cnt, 1u);
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (PAIR) mbar_arrive_leader(&acc_empty[acc]);
+                        else mbar_arrive(&acc_empty[acc]);
+                    }
+                    continue;
+                }
+                int okw = 1;
+                if (lane == 0) {
+                    okw = flag_wait(cnt, (unsigned)n_other, abort_flag, args.err) ? 1 : 0;
+                    *cnt = 0; // every other slice has counted itself: ready for the next launch
+                }
+                okw = __shfl_sync(0xffffffffu, okw, 0);
+                __threadfence();
+                if (!okw) break;
+                others = n_other;
+                pbase = mine;
+            }
+            const bool fin = others > 0;         // finishes a split tile: behaves as a whole tile from here on
+            const bool part_out = part && !fin;  // partial sums go straight into an accumulating output
+            bool add_bias = args.bias != nullptr && ((split == 0 && !part) || fin);
             if (args.tma_out) {
                 // ---- staged output: rows of this warp's 32-row slab go out as 128-byte swizzled boxes
                 const int y0 = (int)(m0 + q * 32);
                 const bool live = has_k && (long long)y0 < args.m;
-                if (args.out_bf16 && !part) {
+                if (args.out_bf16 && !part_out) {
 #pragma unroll 1
                     for (int c0 = grp * 64; c0 < BN; c0 += 64 * groups) {
                         unsigned r0[32], r1[32];
@@ -598,6 +686,16 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         for (int j = 0; j < 32; ++j) {
                             v[j] = __uint_as_float(r0[j]);
                             v[32 + j] = __uint_as_float(r1[j]);
+                        }
+                        for (int s = 0; s < others; ++s) {
+                            const float4 *pp = (const float4 *)(pbase + (size_t)s * (size_t)(BM * BN) + c0 * 32);
+                            float4 p4[16];
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) p4[j] = __ldcg(pp + j * 32); // 32-column block c0 (j < 8), then block c0 + 32
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) {
+                                v[4 * j] += p4[j].x; v[4 * j + 1] += p4[j].y; v[4 * j + 2] += p4[j].z; v[4 * j + 3] += p4[j].w;
+                            }
                         }
                         if (add_bias) {
                             if (args.bias_vec && col0 + 64 <= args.n) {
@@ -649,12 +747,22 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         float v[32];
 #pragma unroll
                         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+                        for (int s = 0; s < others; ++s) {
+                            const float4 *pp = (const float4 *)(pbase + (size_t)s * (size_t)(BM * BN) + c0 * 32);
+                            float4 p4[8];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) p4[j] = __ldcg(pp + j * 32);
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                v[4 * j] += p4[j].x; v[4 * j + 1] += p4[j].y; v[4 * j + 2] += p4[j].z; v[4 * j + 3] += p4[j].w;
+                            }
+                        }
                         if (add_bias) {
 #pragma unroll
                             for (int j = 0; j < 32; ++j)
                                 if (col0 + j < args.n) v[j] += args.bias[col0 + j];
                         }
-                        if (!args.accumulate && !part) {
+                        if (!args.accumulate && !part_out) {
                             if (args.act == MCB_ACT_GELU) {
 #pragma unroll
                                 for (int j = 0; j < 32; ++j) v[j] = gelu_f(v[j]);
@@ -669,7 +777,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                             ring_put(box, lane, j,
                                      make_uint4(__float_as_uint(v[4 * j]), __float_as_uint(v[4 * j + 1]), __float_as_uint(v[4 * j + 2]),
                                                 __float_as_uint(v[4 * j + 3])));
-                        ring_submit(rg, box, part ? &map_pre : &map_d, (int)col0, y0, args.accumulate != 0 || part, lane);
+                        ring_submit(rg, box, part_out ? &map_pre : &map_d, (int)col0, y0, args.accumulate != 0 || part_out, lane);
                     }
                 }
                 tc_fence_before();
@@ -833,32 +941,6 @@ mcb_status make_out_map(mcb_ctx *ctx, CUtensorMap *map, const void *base, bool b
     return MCB_OK;
 }
 
-// Finishes the tiles of a split tail: out[r][c] = act(ws[r][c] + bias[c]) over rows [row0, m) and columns
-// [col0, col1) (col0, col1, ld multiples of 4), four columns per thread.
-template <typename OutT>
-__global__ void tc_split_tail_finish_kernel(const float *__restrict__ ws, OutT *__restrict__ out, const float *__restrict__ bias, int act,
-                                            long long row0, long long m, long long col0, long long col1, long long ld) {
-    const long long w4 = (col1 - col0) >> 2, total = (m - row0) * w4;
-    dep_wait();
-    dep_trigger();
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-        const long long r = row0 + i / w4, c = col0 + ((i % w4) << 2);
-        float4 v = *reinterpret_cast<const float4 *>(ws + r * ld + c);
-        if (bias) {
-            v.x += bias[c];
-            v.y += bias[c + 1];
-            v.z += bias[c + 2];
-            v.w += bias[c + 3];
-        }
-        if (act == MCB_ACT_GELU) {
-            v.x = gelu_f(v.x); v.y = gelu_f(v.y); v.z = gelu_f(v.z); v.w = gelu_f(v.w);
-        } else if (act == MCB_ACT_RELU) {
-            v.x = fmaxf(v.x, 0.0f); v.y = fmaxf(v.y, 0.0f); v.z = fmaxf(v.z, 0.0f); v.w = fmaxf(v.w, 0.0f);
-        }
-        Elem<OutT>::st4(out + r * ld, c >> 2, v);
-    }
-}
-
 template <int BN, bool PAIR> mcb_status launch(mcb_ctx *ctx, const TcGemmParams &p) {
     using C = Cfg<BN, PAIR>;
     constexpr int kTileM = PAIR ? 2 * BM : BM;
@@ -952,19 +1034,17 @@ template <int BN, bool PAIR> mcb_status launch(mcb_ctx *ctx, const TcGemmParams 
         attr_set = true;
     }
     // Split tail: when the tiles do not fill the last wave, the tiles of that wave are cut along K so that every
-    // worker gets one slice; their f32 partial sums meet in a workspace and a small kernel finishes those tiles.
-    struct Region {
-        long long row0, col0, col1;
-    };
-    Region regions[4];
-    int n_regions = 0;
+    // worker gets one slice.  An accumulating output takes the slices directly; any other output is finished inside
+    // the kernel by slice 0 of each tile (TcArgs::fix_ws).
     void *ws = nullptr;
     a.sk_full = a.sk_rem = a.sk_kb = 0;
     a.sk_splits = 1;
+    a.fix_ws = nullptr;
+    a.fix_cnt = nullptr;
     const int workers = PAIR ? max_pairs : ctx->sm_count;
     const long long tiles = (long long)a.m_tiles * a.n_tiles;
-    if (p.split_tail && a.tma_out && p.accumulate && !p.bias && split == 1 && tiles > workers) {
-        // accumulating f32 output: the slices add straight into it (no workspace, nothing to finish)
+    const bool direct = p.accumulate && !p.bias; // slices add straight into the f32 output
+    if (p.split_tail && a.tma_out && split == 1 && tiles > workers && (direct || !p.accumulate)) {
         const long long rem = tiles % workers, full = tiles - rem;
         int s = rem > 0 ? (int)(workers / rem) : 1;
         if (s > 8) s = 8;
@@ -972,40 +1052,14 @@ template <int BN, bool PAIR> mcb_status launch(mcb_ctx *ctx, const TcGemmParams 
         if (s >= 2) {
             const int kb = (a.kb_total + s - 1) / s;
             s = (a.kb_total + kb - 1) / kb;
-            if (s >= 2) {
-                map_pre = map_d;
-                a.sk_full = (int)full;
-                a.sk_rem = (int)rem;
-                a.sk_splits = s;
-                a.sk_kb = kb;
-                work = full + rem * s;
-            }
-        }
-    } else if (p.split_tail && a.tma_out && !p.accumulate && split == 1 && !p.d_pre && tiles > workers && p.ldd % 4 == 0 && p.n % 4 == 0) {
-        const long long rem = tiles % workers, full = tiles - rem;
-        int s = rem > 0 ? (int)(workers / rem) : 1;
-        if (s > 8) s = 8;
-        if (s > a.kb_total / 4) s = a.kb_total / 4;
-        const long long tn0 = full / a.m_tiles;
-        if (s >= 2 && a.n_tiles - tn0 <= 4) {
-            const int kb = (a.kb_total + s - 1) / s;
-            s = (a.kb_total + kb - 1) / kb;
-            if (s >= 2) {
-                MCB_TRY(mcb_alloc(ctx, sizeof(float) * (size_t)p.m * (size_t)p.ldd, &ws));
-                mcb_status st = make_out_map(ctx, &map_pre, ws, false, p.n, p.m, p.ldd);
-                for (long long tn = tn0; tn < a.n_tiles && st == MCB_OK; ++tn) {
-                    Region r;
-                    r.row0 = (tn == tn0 ? full % a.m_tiles : 0) * (long long)kTileM;
-                    r.col0 = tn * BN;
-                    r.col1 = (tn + 1) * (long long)BN < p.n ? (tn + 1) * (long long)BN : p.n;
-                    regions[n_regions++] = r;
-                    cudaError_t e = cudaMemset2DAsync((float *)ws + r.row0 * p.ldd + r.col0, (size_t)p.ldd * 4, 0, (size_t)(r.col1 - r.col0) * 4,
-                                                      (size_t)(p.m - r.row0), ctx->stream);
-                    if (e != cudaSuccess) st = mcb_cuda_check(ctx, e, "split tail: workspace memset");
-                }
-                if (st != MCB_OK) {
-                    mcb_free(ctx, ws);
-                    return st;
+            const size_t ws_bytes = direct ? 0 : sizeof(float) * (size_t)rem * 2 * (size_t)(s - 1) * BM * BN;
+            if (s >= 2 && ws_bytes <= ((size_t)96 << 20) && rem <= kFixTiles) {
+                if (direct) {
+                    map_pre = map_d;
+                } else {
+                    MCB_TRY(mcb_alloc(ctx, ws_bytes, &ws));
+                    a.fix_ws = (float *)ws;
+                    a.fix_cnt = ctx->tc_fix_cnt;
                 }
                 a.sk_full = (int)full;
                 a.sk_rem = (int)rem;
@@ -1015,9 +1069,10 @@ template <int BN, bool PAIR> mcb_status launch(mcb_ctx *ctx, const TcGemmParams 
             }
         }
     }
+    cudaError_t le;
     if (!PAIR) {
         int grid = (int)(work < ctx->sm_count ? work : ctx->sm_count);
-        MCB_CUDA(ctx, mcb_launch_dep(ctx, tc_gemm_kernel<BN, false>, dim3(grid), dim3(kThreads), C::kSmemBytes, map_a, map_b, map_d, map_pre, a));
+        le = mcb_launch_dep(ctx, tc_gemm_kernel<BN, false>, dim3(grid), dim3(kThreads), C::kSmemBytes, map_a, map_b, map_d, map_pre, a);
     } else {
         int pairs = (int)(work < max_pairs ? work : max_pairs);
         cudaLaunchConfig_t cfg = {};
@@ -1034,30 +1089,11 @@ template <int BN, bool PAIR> mcb_status launch(mcb_ctx *ctx, const TcGemmParams 
         at[1].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = at;
         cfg.numAttrs = ctx->dep_launch ? 2 : 1;
-        MCB_CUDA(ctx, cudaLaunchKernelEx(&cfg, tc_gemm_kernel<BN, true>, map_a, map_b, map_d, map_pre, a));
+        le = cudaLaunchKernelEx(&cfg, tc_gemm_kernel<BN, true>, map_a, map_b, map_d, map_pre, a);
     }
+    if (ws) mcb_free(ctx, ws); // stream-ordered reuse: whoever gets the block next is enqueued behind this kernel
+    MCB_CUDA(ctx, le);
     MCB_LAUNCHED(ctx);
-    for (int i = 0; i < n_regions; ++i) {
-        const Region &r = regions[i];
-        const long long total4 = (p.m - r.row0) * ((r.col1 - r.col0) >> 2);
-        const dim3 grid((unsigned)mcb_grid_for(ctx, total4, 256, 4)), block(256);
-        cudaError_t e;
-        if (a.out_bf16 && f16)
-            e = mcb_launch_dep(ctx, tc_split_tail_finish_kernel<__half>, grid, block, 0, (const float *)ws, (__half *)p.d, p.bias, p.act, r.row0,
-                               (long long)p.m, r.col0, r.col1, (long long)p.ldd);
-        else if (a.out_bf16)
-            e = mcb_launch_dep(ctx, tc_split_tail_finish_kernel<__nv_bfloat16>, grid, block, 0, (const float *)ws, (__nv_bfloat16 *)p.d, p.bias, p.act,
-                               r.row0, (long long)p.m, r.col0, r.col1, (long long)p.ldd);
-        else
-            e = mcb_launch_dep(ctx, tc_split_tail_finish_kernel<float>, grid, block, 0, (const float *)ws, (float *)p.d, p.bias, p.act, r.row0,
-                               (long long)p.m, r.col0, r.col1, (long long)p.ldd);
-        if (e != cudaSuccess) {
-            mcb_free(ctx, ws);
-            return mcb_cuda_check(ctx, e, "split tail: finishing kernel");
-        }
-        ctx->launches++;
-    }
-    if (ws) mcb_free(ctx, ws); // stream-ordered reuse: later users are enqueued behind the finishing kernels
     return MCB_OK;
 }
 
@@ -1096,13 +1132,11 @@ mcb_status mcb_tc_gemm(mcb_ctx *ctx, const TcGemmParams &p) {
     if (pair < 0) pair = (bn != 192 && p.m > 128) ? 1 : 0;
     if (bn == 192) pair = 0; // half of 192 columns is not a whole number of 64-column boxes
     // Split tail on 256 x 256 pair tiles against the planned form, by the same cycle estimate as mcb_tc_plan
-    // plus 14000 cycles for the workspace memset, the finishing kernel and the f32 epilogue of the slices (measured at
-    // 8192 x 768: K = 3072 loses 1-5 us with the split tail, K = 32000 gains 90 us)
+    // plus kFixCycles for leaving and collecting the partial sums of the slices
     int tail = p.split_tail;
     tail = knob_val(ctx, K_TC_SPLIT_TAIL, tail); // tuning knob: 0 never, 1 whenever it applies
-    if (fixed_order) tail = 0;
-    const bool tail_ok = (p.accumulate ? (p.bias == nullptr) : (split == 1 && !p.d_pre && p.ldd % 4 == 0 && p.n % 4 == 0)) && p.m > 128 &&
-                         !knob_on(ctx, K_TC_BN);
+    if (fixed_order && p.accumulate) tail = 0; // (a tail finished in the kernel adds in slice order: reproducible as it is)
+    const bool tail_ok = (p.accumulate ? (p.bias == nullptr) : (split == 1)) && p.m > 128 && !knob_on(ctx, K_TC_BN);
     if (tail < 0 && tail_ok) {
         const long long kb = (p.k + BK - 1) / BK, workers = ctx->sm_count / 2;
         const long long tiles = ((p.m + 255) / 256) * ((p.n + 255) / 256), rem = tiles % workers;
@@ -1113,7 +1147,7 @@ mcb_status mcb_tc_gemm(mcb_ctx *ctx, const TcGemmParams &p) {
         if (tiles > workers && s >= 2) {
             const double per_tail = 4.0 * 128.0 + 60.0;
             // an accumulating output takes the slices directly; otherwise workspace memset + finishing kernel
-            const double cost_tail = (double)((tiles / workers) * kb + (kb + s - 1) / s) * per_tail + 12.0 * 256 + (p.accumulate ? 1000.0 : 14000.0);
+            const double cost_tail = (double)((tiles / workers) * kb + (kb + s - 1) / s) * per_tail + 12.0 * 256 + (p.accumulate ? 1000.0 : kFixCycles);
             // the planned form: `split` slices of every tile
             const long long w_now = pair ? ctx->sm_count / 2 : ctx->sm_count;
             const long long t_now = ((p.m + (pair ? 255 : 127)) / (pair ? 256 : 128)) * ((p.n + bn - 1) / bn);
@@ -1178,7 +1212,7 @@ void mcb_tc_plan(mcb_ctx *ctx, int64_t m, int64_t n, int64_t k, bool allow_split
                 if (st > kb_total / 4) st = kb_total / 4;
                 if (t256 > workers && st >= 2) {
                     const double tail = (double)((t256 / workers) * kb_total + (kb_total + st - 1) / st) * (4.0 * 128.0 + 60.0) + 12.0 * 256 +
-                                        (atomic_out ? 1000.0 : 14000.0);
+                                        (atomic_out ? 1000.0 : kFixCycles);
                     if (tail < 0.9 * cost) cost = tail;
                 }
             }

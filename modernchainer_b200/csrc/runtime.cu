@@ -59,7 +59,7 @@ __global__ void clock_trace_kernel(unsigned long long *buf, int cap, unsigned lo
 static const char *const kKnobNames[K_COUNT] = {
     "MCB_UNFUSED_BWD", "MCB_LN_NO_AUX", "MCB_UNFUSED_ADD_LN", "MCB_UNFUSED_QKV", "MCB_CONV_DIRECT", "MCB_FLASH_LEGACY", "MCB_FLASH_LEGACY_BWD",
     "MCB_SGEMM_NO_SPLIT", "MCB_LN_NO_BULK", "MCB_SCE_NO_STREAM", "MCB_TC_EPI", "MCB_TC_EPI_KB", "MCB_TC_STAGES", "MCB_TC_DIRECT_OUT", "MCB_TC_BN",
-    "MCB_TC_PAIR", "MCB_TC_SPLIT_TAIL", "MCB_GRAPH_INFO", "MCB_DETERMINISTIC", "MCB_NO_DEP_LAUNCH"};
+    "MCB_TC_PAIR", "MCB_TC_SPLIT_TAIL", "MCB_GRAPH_INFO", "MCB_DETERMINISTIC", "MCB_NO_DEP_LAUNCH", "MCB_FLASH_DQ_RECOMPUTE"};
 
 extern "C" {
 
@@ -83,6 +83,8 @@ mcb_status mcb_ctx_create(int32_t ordinal, mcb_ctx **out) {
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaMalloc(&ctx->d_err, sizeof(unsigned int));
     if (e == cudaSuccess) e = cudaMemset(ctx->d_err, 0, sizeof(unsigned int));
+    if (e == cudaSuccess) e = cudaMalloc(&ctx->tc_fix_cnt, mcb_ctx::kTcFixCntBytes);
+    if (e == cudaSuccess) e = cudaMemset(ctx->tc_fix_cnt, 0, mcb_ctx::kTcFixCntBytes);
     cudaDeviceProp prop;
     if (e == cudaSuccess) e = cudaGetDeviceProperties(&prop, ordinal);
     if (e != cudaSuccess) {
@@ -133,6 +135,7 @@ void mcb_ctx_destroy(mcb_ctx *ctx) {
     }
     if (ctx->trace_buf) cudaFree(ctx->trace_buf);
     cudaFree(ctx->d_err);
+    cudaFree(ctx->tc_fix_cnt);
     cudaStreamDestroy(ctx->stream);
     delete ctx;
 }
@@ -236,7 +239,11 @@ static mcb_status take_device_error(mcb_ctx *ctx) {
     if (dp_st != MCB_OK) return dp_st;
     if (err) {
         MCB_CUDA(ctx, cudaMemsetAsync(ctx->d_err, 0, sizeof(err), ctx->stream));
-        if (err & MCB_DEVERR_TIMEOUT) return mcb_fail(ctx, MCB_BACKEND, "device-side wait timed out");
+        if (err & MCB_DEVERR_TIMEOUT) {
+            // a GEMM that gave up may have left its split-tail counters half counted
+            MCB_CUDA(ctx, cudaMemsetAsync(ctx->tc_fix_cnt, 0, mcb_ctx::kTcFixCntBytes, ctx->stream));
+            return mcb_fail(ctx, MCB_BACKEND, "device-side wait timed out");
+        }
         if (err & MCB_DEVERR_LABEL) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "class index negative or out of range");
         return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "embedding index negative or out of range");
     }

@@ -70,6 +70,16 @@ __device__ __forceinline__ void tma_reduce_add_3d(const CUtensorMap *map, const 
                  : "memory");
 }
 // fetches a tensor map (a kernel parameter) into the descriptor cache ahead of the first copy that uses it
+// untiled bulk copies: both addresses 16-byte aligned, size a multiple of 16 bytes
+__device__ __forceinline__ void bulk_load(void *smem_dst, const void *gsrc, unsigned bytes, unsigned long long *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 :
+                 : "r"(smem_u32(smem_dst)), "l"((unsigned long long)gsrc), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_store(void *gdst, const void *smem_src, unsigned bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" : : "l"((unsigned long long)gdst), "r"(smem_u32(smem_src)), "r"(bytes) : "memory");
+}
 __device__ __forceinline__ void prefetch_map(const CUtensorMap *map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)map) : "memory");
 }

@@ -104,7 +104,7 @@ def test_elementwise_and_layout_functions(chainer):
     x = chainer.Variable(chainer.Tensor.from_numpy(np.arange(6, dtype=np.float32).reshape(2, 3)))
     assert F.reshape(x, [3, 2]).shape == [3, 2] and F.permute(x, [1, 0]).shape == [3, 2]
     assert np.allclose(F.silu(x).array, x.array / (1.0 + np.exp(-x.array)), rtol=1e-6)
-    for name in ("batch_norm", "dropout", "clamp", "rms_norm", "average_pool2d", "conv_transpose2d"):
+    for name in ("dropout", "clamp", "rms_norm", "average_pool2d", "conv_transpose2d"):
         with pytest.raises(NotImplementedError):
             getattr(F, name)(x)
 
@@ -168,9 +168,33 @@ def test_links_shapes_and_seeds(chainer, oracle):
     attn = L.MultiHeadAttention(4, 2)
     assert len(attn.parameters()) == 8 and np.array_equal(attn.wk.W.array, oracle.he_normal((4, 4), 4, 2))
     assert attn(chainer.Variable(chainer.Tensor.from_numpy(np.ones((2, 3, 4), np.float32)))).shape == [2, 3, 4]
-    for name in ("BatchNorm", "RMSNorm", "ConvTranspose2d"):
+    assert L.BatchNorm(2)(y).shape == y.shape and len(L.BatchNorm(2).parameters()) == 2
+    for name in ("RMSNorm", "ConvTranspose2d"):
         with pytest.raises(NotImplementedError):
             getattr(L, name)(2)
+
+
+def test_batch_norm_values_and_gradients(chainer):
+    """F.batch_norm (a host op of the reference, host_ops.rs:478-600) composed from ops of the path: values against the
+    closed form in f64, gradients against the closed-form batch-norm backward."""
+    import chainer.functions as F
+    rng = np.random.default_rng(5)
+    x = rng.standard_normal((4, 3, 5, 2)).astype(np.float32) * 2 + 1
+    gamma, beta = rng.standard_normal(3).astype(np.float32), rng.standard_normal(3).astype(np.float32)
+    up = rng.standard_normal(x.shape).astype(np.float32)
+    xv, gv, bv = (chainer.Variable(chainer.Tensor.from_numpy(a)) for a in (x, gamma, beta))
+    y = F.batch_norm(xv, gv, bv)
+    x64 = x.astype(np.float64)
+    mean, var = x64.mean((0, 2, 3), keepdims=True), x64.var((0, 2, 3), keepdims=True)
+    xhat = (x64 - mean) / np.sqrt(var + 1e-5)
+    want = xhat * gamma.reshape(1, 3, 1, 1) + beta.reshape(1, 3, 1, 1)
+    assert np.abs(y.array - want).max() <= 1e-5 * np.abs(want).max()
+    F.sum(F.mul(y, chainer.Variable.constant(chainer.Tensor.from_numpy(up)))).backward()
+    g = up.astype(np.float64)
+    dxhat = g * gamma.reshape(1, 3, 1, 1)
+    dx = (dxhat - dxhat.mean((0, 2, 3), keepdims=True) - xhat * (dxhat * xhat).mean((0, 2, 3), keepdims=True)) / np.sqrt(var + 1e-5)
+    for got, ref in ((xv.grad.numpy(), dx), (gv.grad.numpy(), (g * xhat).sum((0, 2, 3))), (bv.grad.numpy(), g.sum((0, 2, 3)))):
+        assert np.abs(got - ref).max() <= 2e-5 * max(np.abs(ref).max(), 1e-30)
 
 
 def test_mlp_training_loop_learns(chainer):

@@ -470,9 +470,13 @@ def test_fused_backward_passes_match_separate_kernels(mc, ctx, cfg):
     lu, gu, _ = run(True)
     assert lf == lu
     # sums over rows (bias, LayerNorm vectors) group their partial sums differently, and the weight
-    # gradients' split-K partial tiles are added in whatever order the CTAs finish: 1e-5 of the peak
+    # gradients' split-K partial tiles are added in whatever order the CTAs finish: 1e-5 of the peak.  The key
+    # projection's bias has a gradient of exactly zero in exact arithmetic (softmax ignores a shift of all scores of a
+    # row); what is left there is rounding residue a million times smaller than the other gradients, so no tensor is
+    # measured against less than a thousandth of the model's largest gradient.
+    floor = 1e-3 * max(float(np.abs(r).max()) for r in gu)
     for i, (a, r) in enumerate(zip(gf, gu)):
-        assert np.abs(a - r).max() <= 1e-5 * max(float(np.abs(r).max()), 1e-30), (i, shapes[i])
+        assert np.abs(a - r).max() <= 1e-5 * max(float(np.abs(r).max()), floor), (i, shapes[i])
 
 
 @pytest.mark.parametrize("knob", ["MCB_LN_NO_BULK", "MCB_UNFUSED_ADD_LN"])
