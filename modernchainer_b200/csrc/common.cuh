@@ -75,7 +75,7 @@ struct mcb_ctx {
 enum McbKnob {
     K_UNFUSED_BWD, K_LN_NO_AUX, K_UNFUSED_ADD_LN, K_UNFUSED_QKV, K_CONV_DIRECT, K_FLASH_LEGACY, K_FLASH_LEGACY_BWD, K_SGEMM_NO_SPLIT,
     K_LN_NO_BULK, K_SCE_NO_STREAM, K_TC_EPI, K_TC_EPI_KB, K_TC_STAGES, K_TC_DIRECT_OUT, K_TC_BN, K_TC_PAIR, K_TC_SPLIT_TAIL,
-    K_GRAPH_INFO, K_DETERMINISTIC, K_NO_DEP_LAUNCH, K_FLASH_DQ_RECOMPUTE, K_COUNT
+    K_GRAPH_INFO, K_DETERMINISTIC, K_NO_DEP_LAUNCH, K_FLASH_DQ_RECOMPUTE, K_FLASH_BWD_ONE_JOB, K_COUNT
 };
 static_assert(K_COUNT <= 32, "mcb_ctx::knobs is too small");
 inline bool knob_on(const mcb_ctx *ctx, McbKnob k) { return ctx->knobs[k] >= 0; } // flag knobs: set at all

@@ -48,6 +48,7 @@ struct TcArgs {
     int a_mn, b_mn;
     unsigned idesc;
     int m_tiles, n_tiles, kb_total, kb_per_split;
+    int n_fast; // tile order: 0 = row blocks fastest, 1 = column blocks fastest (see tile_coords)
     int stages; // depth of the operand ring actually used (tuning knob; at most the compiled depth)
     int ring;   // output boxes per epilogue warp: 2, or 4 when one operand stage is given up for them
     int epi_groups; // epilogue groups of four warps in use: 1 or 2
@@ -106,6 +107,20 @@ __device__ __forceinline__ WorkItem decode_work(const TcArgs &args, unsigned w, 
     it.kb1 = min(it.kb0 + args.kb_per_split, args.kb_total);
     it.partial = false;
     return it;
+}
+
+// Tile index -> (column block, row block).  Consecutive indices run at the same time, so the order decides which operand
+// they share in L2: rows fastest (the default) shares the B block of one column block; columns fastest (n_fast) makes
+// the few column blocks of one row block run together and read that row block's A slab once -- the order for a huge A
+// against a small B (the lm_head gradients: a 524 MB logit-gradient matrix against 768 columns).
+__device__ __forceinline__ void tile_coords(const TcArgs &args, unsigned t, unsigned m_tiles, unsigned &tn, unsigned &tm) {
+    if (args.n_fast) {
+        tm = t / (unsigned)args.n_tiles;
+        tn = t - tm * (unsigned)args.n_tiles;
+    } else {
+        tn = t / m_tiles;
+        tm = t - tn * m_tiles;
+    }
 }
 
 // ------------------------------------------------------------------ PTX wrappers
@@ -492,7 +507,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             for (unsigned w = w_first; w < work_total && ok; w += w_stride) {
                 const WorkItem wi = decode_work(args, w, tiles_mn, one_split);
                 const unsigned t = wi.t;
-                const unsigned tn = t / m_tiles, tm = t - tn * m_tiles;
+                unsigned tn, tm;
+                tile_coords(args, t, m_tiles, tn, tm);
                 int r0 = is_a ? (int)tm * kTileM + (int)crank * BM : (int)tn * BN + (int)crank * (PAIR ? BN / 2 : 0);
                 const int kb0 = wi.kb0, kb1 = wi.kb1;
                 for (int kb = kb0; kb < kb1; ++kb, ++it) {
@@ -608,7 +624,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const bool part = wi.partial; // slice of a split-tail tile: plain f32 partial sum, added into the workspace
             bool has_k = wi.kb0 < args.kb_total;
             // a pair's CTA holds its own 128 rows of the 256-row tile in its TMEM lanes, all BN columns
-            const unsigned tn = t / m_tiles, tm = t - tn * m_tiles;
+            unsigned tn, tm;
+            tile_coords(args, t, m_tiles, tn, tm);
             long long m0 = (long long)tm * kTileM + (long long)crank * BM, n0 = (long long)tn * BN;
             int acc = tile_it & 1;
             unsigned acc_ph = (tile_it >> 1) & 1u;
@@ -968,6 +985,8 @@ template <int BN, bool PAIR> mcb_status launch(mcb_ctx *ctx, const TcGemmParams 
     a.m_tiles = (int)((p.m + kTileM - 1) / kTileM);
     a.n_tiles = (int)((p.n + BN - 1) / BN);
     a.kb_total = (int)((p.k + BK - 1) / BK);
+    // A that cannot stay in L2 (126 MB) beside a B that can: walk the column blocks of a row block together
+    a.n_fast = ((double)p.m * (double)p.k * 2.0 > 96.0e6 && (double)p.n * (double)p.k * 2.0 < 64.0e6 && a.n_tiles > 1) ? 1 : 0;
     int split = p.split_k < 1 ? 1 : p.split_k;
     if (split > a.kb_total) split = a.kb_total > 0 ? a.kb_total : 1;
     a.kb_per_split = (a.kb_total + split - 1) / split;

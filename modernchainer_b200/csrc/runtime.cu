@@ -59,7 +59,7 @@ __global__ void clock_trace_kernel(unsigned long long *buf, int cap, unsigned lo
 static const char *const kKnobNames[K_COUNT] = {
     "MCB_UNFUSED_BWD", "MCB_LN_NO_AUX", "MCB_UNFUSED_ADD_LN", "MCB_UNFUSED_QKV", "MCB_CONV_DIRECT", "MCB_FLASH_LEGACY", "MCB_FLASH_LEGACY_BWD",
     "MCB_SGEMM_NO_SPLIT", "MCB_LN_NO_BULK", "MCB_SCE_NO_STREAM", "MCB_TC_EPI", "MCB_TC_EPI_KB", "MCB_TC_STAGES", "MCB_TC_DIRECT_OUT", "MCB_TC_BN",
-    "MCB_TC_PAIR", "MCB_TC_SPLIT_TAIL", "MCB_GRAPH_INFO", "MCB_DETERMINISTIC", "MCB_NO_DEP_LAUNCH", "MCB_FLASH_DQ_RECOMPUTE"};
+    "MCB_TC_PAIR", "MCB_TC_SPLIT_TAIL", "MCB_GRAPH_INFO", "MCB_DETERMINISTIC", "MCB_NO_DEP_LAUNCH", "MCB_FLASH_DQ_RECOMPUTE", "MCB_FLASH_BWD_ONE_JOB"};
 
 extern "C" {
 
