@@ -53,6 +53,29 @@ def peaks():
     return dict(hbm=6650.0, tf_burst=1590.0, tf_sustained=1400.0, src="fallback")
 
 
+# DRAM bytes of the c4 step's GEMM launches, measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum of every tc_gemm launch
+# of one tape step of the 2-layer model): the three lm_head launches together, and the twelve launches of one layer together.  Traffic
+# grows in proportion to the layer count (every layer launches the same twelve shapes).  The figure belongs to the GEMM source it was
+# measured with: `kernel_sha256` is the SHA-256 of modernchainer_b200/csrc/gemm_tc.cu at capture time, and a build whose source differs
+# reports traffic null (with the reason) instead of a stale number.
+GEMM_TRAFFIC = {"lm_head_bytes": 1937.0e6, "per_layer_bytes": 513.6e6,
+                "kernel_sha256": "476cc0e63e751d54f594cee7ae7d9be1c93d72ea9ea1cc0d0ec91f786fee064e"}
+
+
+def gemm_traffic(layers):
+    import hashlib
+    src = os.path.join(ROOT, "modernchainer_b200", "csrc", "gemm_tc.cu")
+    try:
+        sha = hashlib.sha256(open(src, "rb").read()).hexdigest()
+    except OSError:
+        return None, "GEMM source not found beside the library: the ncu capture cannot be matched to this build"
+    if sha != GEMM_TRAFFIC["kernel_sha256"]:
+        return None, "the GEMM kernel source has changed since the ncu capture of its DRAM traffic was taken"
+    per_launch = (GEMM_TRAFFIC["lm_head_bytes"] + GEMM_TRAFFIC["per_layer_bytes"] * layers) / (3 + 12 * layers)
+    return per_launch, ("ncu dram__bytes_read.sum + dram__bytes_write.sum of every GEMM launch of a 2-layer step of this kernel source, "
+                        "scaled by the layer count; bytes per launch, mean over the step's GEMMs")
+
+
 class ClockSampler:
     """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
     Q = "index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown," \
@@ -399,10 +422,7 @@ def run_ours(args, dist):
             achieved = r["flops"] / (r["ms"] / 1e3) / 1e12
             traffic = traffic_src = None
             if dom == "gemm_tc" and cfg["kind"] == "decoder" and (cfg["vocab"], cfg["d"], cfg["ff"], cfg["seq"], cfg["batch"]) == (32000, 768, 3072, 1024, 8):
-                # ncu dram__bytes_read + dram__bytes_write of every GEMM launch of one step (the GEMM traffic summary under profiles/):
-                # 3180.4 MB for the three lm_head launches + 501.6 MB per layer, averaged over the step's GEMM launches
-                traffic = (3180.4e6 + 501.6e6 * cfg["layers"]) / (3 + 12 * cfg["layers"])
-                traffic_src = "ncu capture of every GEMM launch of a 2-layer step, scaled by the layer count; bytes per launch, mean over the step's GEMMs"
+                traffic, traffic_src = gemm_traffic(cfg["layers"])
             roof = dict(bound="tensor", kernel=dom, achieved=achieved, peak=pk["tf_sustained"], unit="TFLOP/s", frac=achieved / pk["tf_sustained"],
                         traffic=traffic, traffic_source=traffic_src, peak_source=pk["src"] + " (sustained cuBLAS bf16)",
                         avg_launch_ms=r["ms"] / r["launches"])

@@ -301,6 +301,40 @@ def run_step(mc, ctx, oracle, kind, cfg, omodel, x, y, y_is_label, arena, steps=
             assert np.array_equal(a.data, b.data), i
 
 
+@pytest.mark.parametrize("name", ["mlp", "encoder", "cnn", "decoder"])
+def test_step_matches_committed_vectors(mc, ctx, name):
+    """The CUDA path against tests/golden/step_vectors.npz (two steps of four toy models by the single-threaded oracle,
+    written by tests/golden/make_step_vectors.py; no oracle runs here): losses at 2e-5, gradients norm-wise per tensor
+    at 1e-5 (the key-projection biases, listed in the fixture, have a gradient of exactly zero in exact arithmetic and hold
+    rounding residue only: they are measured against the model's largest gradient), and -- given the fixture's gradients --
+    Adam's parameters bit for bit."""
+    import os
+    vec = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "step_vectors.npz"))
+    kind = {"mlp": "mlp", "encoder": "encoder", "cnn": "cnn", "decoder": "decoder"}[name]
+    m = mc.Model(ctx, kind, [int(v) for v in vec[f"{name}/cfg"]])
+    ps = m.parameters()
+    keep = mc.Arena(ctx, ps)
+    opt = mc.Adam(ctx, 1e-3)
+    x, y = mc.Variable.constant(ctx, vec[f"{name}/x"]), mc.Variable.constant(ctx, vec[f"{name}/y"])
+    for step in range(2):
+        mc.zero_grad(ps)
+        loss = m.loss(x, y)
+        close(loss.data.reshape(-1), vec[f"{name}/loss{step}"], 2e-5)
+        loss.backward()
+        want = [vec[f"{name}/grad{step}/{i}"] for i in range(len(ps))]
+        top = max(float(np.abs(w).max()) for w in want)
+        zero_idx = set(int(i) for i in vec[f"{name}/zero_idx"])
+        for i, (p, w) in enumerate(zip(ps, want)):
+            den = top if i in zero_idx else max(float(np.abs(w).max()), 1e-30)
+            err = np.abs(p.grad.astype(np.float64) - w).max() / den
+            assert err <= 1e-5, (step, i, err)
+            p.set_grad(w)
+        opt.update(ps)
+    for i, p in enumerate(ps):
+        assert np.array_equal(p.data, vec[f"{name}/param/{i}"]), i
+    del keep
+
+
 @pytest.mark.parametrize("arena", [False, True])
 def test_mlp_step_c1(mc, ctx, oracle, arena):
     rng = np.random.default_rng(1234)

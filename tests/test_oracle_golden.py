@@ -387,3 +387,22 @@ def test_low_precision_oracle_rounds_where_a_16_bit_step_stores(oracle):
     eb = max(np.abs(a - r).max() / np.abs(r).max() for a, r in zip(b16, f32) if np.abs(r).max() > 1e-6)
     eh = max(np.abs(a - r).max() / np.abs(r).max() for a, r in zip(h16, f32) if np.abs(r).max() > 1e-6)
     assert 1e-4 < eb < 5e-2 and eh < eb / 3
+
+
+def test_oracle_reproduces_the_committed_step_vectors(oracle):
+    """tests/golden/step_vectors.npz was written by the single-threaded oracle (tests/golden/make_step_vectors.py); a
+    restatement that drifts shows up here before it moves the target of the GPU tests."""
+    import importlib.util
+    import os
+    here = os.path.dirname(os.path.abspath(__file__))
+    spec = importlib.util.spec_from_file_location("make_step_vectors", os.path.join(here, "golden", "make_step_vectors.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    try:
+        vec = mod.run(oracle)
+    finally:
+        oracle.set_mode("checker")
+    old = np.load(mod.OUT)
+    assert sorted(old.files) == sorted(vec)
+    for k in vec:
+        assert np.array_equal(old[k], vec[k]), k
