@@ -430,6 +430,15 @@ mcb_status mcb_static_step_create(mcb_model *model, mcb_adam *opt, mcb_scaler *s
 mcb_status mcb_static_step_inputs(mcb_static_step *s, void **x_dev_out, void **y_dev_out);
 mcb_status mcb_static_step_run(mcb_static_step *s, const void *host_x_or_null, const void *host_y_or_null);
 mcb_status mcb_static_step_loss(mcb_static_step *s, float *loss_out); /* synchronises; the unscaled loss of the last run */
+/* Pipelined form for loops that read every step's loss.  Launches this step, queues the copy of ITS loss to pinned
+ * host memory behind it, and returns the loss of the PREVIOUS pipelined run (*have_prev_out = 0 on the first call),
+ * waiting only for that one: the device always has the next step queued, where run + loss leaves it idle while the
+ * host launches.  The host buffers of call i may be rewritten once call i + 1 has returned.  mcb_static_step_drain
+ * returns the loss of the last pipelined run (*have_out = 0 if none is outstanding).  The waits are bounded like
+ * every host wait of the data-parallel path when collectives are in flight. */
+mcb_status mcb_static_step_run_pipelined(mcb_static_step *s, const void *host_x_or_null, const void *host_y_or_null,
+                                         float *prev_loss_out, int32_t *have_prev_out);
+mcb_status mcb_static_step_drain(mcb_static_step *s, float *loss_out, int32_t *have_out);
 mcb_status mcb_static_step_launches(mcb_static_step *s, int64_t *kernels_per_step_out);
 void mcb_static_step_release(mcb_static_step *s);
 

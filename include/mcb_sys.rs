@@ -227,6 +227,8 @@ unsafe extern "C" {
     pub fn mcb_static_step_inputs(s: *mut McbStaticStep, x_dev_out: *mut *mut c_void, y_dev_out: *mut *mut c_void) -> Status;
     pub fn mcb_static_step_run(s: *mut McbStaticStep, host_x_or_null: *const c_void, host_y_or_null: *const c_void) -> Status;
     pub fn mcb_static_step_loss(s: *mut McbStaticStep, loss_out: *mut f32) -> Status;
+    pub fn mcb_static_step_run_pipelined(s: *mut McbStaticStep, host_x_or_null: *const c_void, host_y_or_null: *const c_void, prev_loss_out: *mut f32, have_prev_out: *mut i32) -> Status;
+    pub fn mcb_static_step_drain(s: *mut McbStaticStep, loss_out: *mut f32, have_out: *mut i32) -> Status;
     pub fn mcb_static_step_launches(s: *mut McbStaticStep, kernels_per_step_out: *mut i64) -> Status;
     pub fn mcb_static_step_release(s: *mut McbStaticStep);
     pub fn mcb_dp_unique_id(host_id_out_128: *mut c_void) -> Status;

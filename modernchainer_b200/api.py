@@ -987,6 +987,23 @@ class StaticStep:
         self.ctx.check(self.ctx.lib.mcb_static_step_loss(self.h, C.byref(v)))
         return v.value
 
+    def run_pipelined(self, x=None, y=None):
+        """Launches this step and returns the loss of the PREVIOUS pipelined run (None on the first call), waiting only
+        for that one; `drain()` returns the last run's loss.  The host arrays of a call may be rewritten once the next
+        call has returned."""
+        hx = self._host(x, self._xs) if x is not None else None
+        hy = self._host(y, self._ys) if y is not None else None
+        v, have = C.c_float(), C.c_int32()
+        self.ctx.check(self.ctx.lib.mcb_static_step_run_pipelined(self.h, hx.ctypes.data if hx is not None else None,
+                                                                  hy.ctypes.data if hy is not None else None, C.byref(v), C.byref(have)))
+        self._prev, self._last = getattr(self, "_last", None), (hx, hy)
+        return v.value if have.value else None
+
+    def drain(self):
+        v, have = C.c_float(), C.c_int32()
+        self.ctx.check(self.ctx.lib.mcb_static_step_drain(self.h, C.byref(v), C.byref(have)))
+        return v.value if have.value else None
+
     @property
     def kernels_per_step(self):
         v = C.c_int64()

@@ -350,6 +350,28 @@ extern "C" mcb_status mcb_dp_bounded_wait(mcb_ctx *ctx) {
     return dp_host_wait(ctx, dp, dp->timeout_ms);
 }
 
+// Waits for one event of the compute stream.  With collectives possibly in flight the wait is bounded and watches the
+// communicator for asynchronous errors, like every other host wait of the data-parallel path.
+extern "C" mcb_status mcb_dp_wait_event(mcb_ctx *ctx, void *event) {
+    cudaEvent_t ev = (cudaEvent_t)event;
+    DpState *dp = (DpState *)ctx->dp;
+    if (!dp || dp->world <= 1 || dp->failed) {
+        MCB_CUDA(ctx, cudaEventSynchronize(ev));
+        return MCB_OK;
+    }
+    MCB_TRY(dp_check_alive(ctx, dp));
+    const auto t0 = std::chrono::steady_clock::now();
+    for (;;) {
+        const cudaError_t q = cudaEventQuery(ev);
+        if (q == cudaSuccess) return MCB_OK;
+        if (q != cudaErrorNotReady) return mcb_cuda_check(ctx, q, "waiting for a step's result");
+        if (int e = dp->ops.async_error()) return dp_fail(ctx, dp, "asynchronous error", e);
+        const auto ms = std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t0).count();
+        if (ms >= dp->timeout_ms) return dp_fail(ctx, dp, "timed out waiting for a step that holds gradient all-reduces: a peer rank did not take part", 0);
+        if (ms >= 20) std::this_thread::sleep_for(std::chrono::microseconds(200));
+    }
+}
+
 extern "C" {
 
 mcb_status mcb_dp_plan_buckets(const int64_t *sizes, int32_t n, int64_t bucket_elems, int32_t *bucket_of,

@@ -57,7 +57,7 @@ constexpr int kDsBytes = 2 * kTileBytes;
 
 // One job = one (owned tile, sample, head).  Jobs are numbered heaviest first (job / nh_total is the weight rank: under a
 // causal mask the owned tile that walks the most streamed tiles) and dealt to the persistent CTAs in boustrophedon order
-// (round 0: CTA c takes job c, round 1: job 2G-1-c, ...), which balances the step counts as well as longest-first list
+// (first pass: CTA c takes job c, second pass: job 2G-1-c, ...), which balances the step counts as well as longest-first list
 // scheduling does (24 against an average of 23.4 steps on 148 CTAs for 8 x 12 heads of 8 tiles).
 struct Job {
     int n, h, nh, own, t_first, nt, o0;

@@ -30,7 +30,14 @@ struct mcb_static_step {
     int32_t host_step_after = 0; // the host's step count as the last replay (or the creation) left it
     cudaGraphExec_t exec = nullptr;
     int64_t launches_per_step = 0;
+    // pipelined runs: the loss of run i goes to pinned slot i & 1 behind the graph; run i + 1 returns it
+    float *h_loss = nullptr;
+    cudaEvent_t loss_ev[2] = {nullptr, nullptr};
+    int64_t piped = 0; // pipelined runs whose loss has been requested so far
+    bool loss_pending = false;
 };
+
+extern "C" mcb_status mcb_dp_wait_event(mcb_ctx *ctx, void *event); // dp.cu
 
 namespace {
 
@@ -282,6 +289,49 @@ mcb_status mcb_static_step_run(mcb_static_step *s, const void *host_x, const voi
     return MCB_OK;
 }
 
+static mcb_status take_pending_loss(mcb_static_step *s, float *loss_out, int32_t *have_out) {
+    if (have_out) *have_out = s->loss_pending ? 1 : 0;
+    if (!s->loss_pending) return MCB_OK;
+    const int slot = (int)((s->piped - 1) & 1);
+    MCB_TRY(mcb_dp_wait_event(s->ctx, s->loss_ev[slot]));
+    if (loss_out) *loss_out = s->h_loss[slot];
+    s->loss_pending = false;
+    return MCB_OK;
+}
+
+mcb_status mcb_static_step_run_pipelined(mcb_static_step *s, const void *host_x, const void *host_y, float *prev_loss_out,
+                                         int32_t *have_prev_out) {
+    if (!s) return MCB_INVALID_ARGUMENT;
+    mcb_ctx *ctx = s->ctx;
+    MCB_CHECK_CTX(ctx);
+    if (!s->h_loss) {
+        MCB_CUDA(ctx, cudaHostAlloc((void **)&s->h_loss, 2 * sizeof(float), cudaHostAllocDefault));
+        for (int i = 0; i < 2; ++i) MCB_CUDA(ctx, cudaEventCreateWithFlags(&s->loss_ev[i], cudaEventDisableTiming));
+    }
+    // this step first, so that the device has it queued while the host waits for the one before
+    MCB_TRY(mcb_static_step_run(s, host_x, host_y));
+    const int slot = (int)(s->piped & 1);
+    const bool had = s->loss_pending;
+    MCB_CUDA(ctx, cudaMemcpyAsync(&s->h_loss[slot], s->loss.ptr, sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
+    MCB_CUDA(ctx, cudaEventRecord(s->loss_ev[slot], ctx->stream));
+    s->piped++;
+    s->loss_pending = true;
+    float prev = 0.0f;
+    if (had) { // the previous run's loss: its copy sits in the other slot, behind the previous graph
+        MCB_TRY(mcb_dp_wait_event(ctx, s->loss_ev[slot ^ 1]));
+        prev = s->h_loss[slot ^ 1];
+    }
+    if (have_prev_out) *have_prev_out = had ? 1 : 0;
+    if (prev_loss_out && had) *prev_loss_out = prev;
+    return MCB_OK;
+}
+
+mcb_status mcb_static_step_drain(mcb_static_step *s, float *loss_out, int32_t *have_out) {
+    if (!s) return MCB_INVALID_ARGUMENT;
+    MCB_CHECK_CTX(s->ctx);
+    return take_pending_loss(s, loss_out, have_out);
+}
+
 mcb_status mcb_static_step_loss(mcb_static_step *s, float *loss_out) {
     if (!s || !loss_out) return MCB_INVALID_ARGUMENT;
     return mcb_memcpy_d2h(s->ctx, loss_out, s->loss.ptr, sizeof(float));
@@ -298,6 +348,9 @@ void mcb_static_step_release(mcb_static_step *s) {
     mcb_ctx *ctx = s->ctx;
     cudaStreamSynchronize(ctx->stream);
     if (s->exec) cudaGraphExecDestroy(s->exec);
+    if (s->h_loss) cudaFreeHost(s->h_loss);
+    for (int i = 0; i < 2; ++i)
+        if (s->loss_ev[i]) cudaEventDestroy(s->loss_ev[i]);
     s->x = Tensor();
     s->y = Tensor();
     s->loss = Tensor();

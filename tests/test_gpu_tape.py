@@ -831,3 +831,40 @@ def test_static_step_graph_replay_equals_the_tape_step(mc, ctx, case):
         tol = 2e-6 if amp else 0.0
         assert np.abs(a.data - b.data).max() <= tol * max(float(np.abs(a.data).max()), 1e-30), j
     step.close()
+
+
+def test_static_step_pipelined_run_returns_every_loss_one_call_later(mc, ctx):
+    """mcb_static_step_run_pipelined launches step i and hands back the loss of step i - 1 (nothing on the first call);
+    mcb_static_step_drain hands back the last one.  Same losses, same parameters as run + loss on a twin model, for
+    fresh inputs on every call (each call's host arrays are rewritten after the next call has returned)."""
+    rng = np.random.default_rng(31)
+    xs = [rng.standard_normal((16, 20)).astype(np.float32) for _ in range(5)]
+    ys = [rng.integers(0, 5, 16).astype(np.int64) for _ in range(5)]
+
+    def make():
+        m = mc.Model(ctx, "mlp", [20, 16, 5])
+        ps = m.parameters()
+        return m, ps, mc.Arena(ctx, ps), mc.Adam(ctx, 1e-2)
+
+    m, ps, keep, opt = make()
+    step = mc.StaticStep(m, opt, xs[0], ys[0])
+    want = []
+    for x, y in zip(xs, ys):
+        step.run(x, y)
+        want.append(step.loss())
+    m2, ps2, keep2, opt2 = make()
+    step2 = mc.StaticStep(m2, opt2, xs[0], ys[0])
+    assert step2.drain() is None
+    got = []
+    for x, y in zip(xs, ys):
+        prev = step2.run_pipelined(x.copy(), y.copy())
+        if prev is not None:
+            got.append(prev)
+    assert len(got) == len(xs) - 1
+    got.append(step2.drain())
+    assert step2.drain() is None
+    assert got == want
+    for a, b in zip(ps, ps2):
+        assert np.array_equal(a.data, b.data)
+    step.close()
+    step2.close()
