@@ -186,3 +186,30 @@ def test_no_kernel_writes_outside_its_arrays(mc, ctx, shift):
             ops.max_pool2d_backward(x, randn(*p.shape), 3, 1, 1)
         checked = ctx.check_guards()
     assert checked > 0
+
+
+def test_knobs_are_per_context_and_unknown_names_are_refused(mc, ctx):
+    """The environment is read once, when a context is created; afterwards a knob changes only through mcb_set_knob,
+    for that context alone."""
+    import os
+    with pytest.raises(mc.McbError):
+        ctx.set_knob("MCB_NO_SUCH_KNOB", 1)
+    ops = mc.ops(ctx)
+    x = randn(64, 8, 16, 16)  # 38 M multiply-adds: large enough for the tensor-core convolution
+    w, b = randn(32, 8, 3, 3) * 0.2, randn(32)
+    tc = ops.conv2d(x, w, b, 1, 1)
+    os.environ["MCB_CONV_DIRECT"] = "1"  # too late for this context: it keeps the tensor-core path
+    try:
+        assert np.array_equal(ops.conv2d(x, w, b, 1, 1), tc)
+        other = mc.Context(0)  # a context created now reads it
+        try:
+            direct = mc.ops(other).conv2d(x, w, b, 1, 1)
+        finally:
+            other.close()
+    finally:
+        os.environ.pop("MCB_CONV_DIRECT", None)
+    ctx.set_knob("MCB_CONV_DIRECT", 1)
+    assert np.array_equal(ops.conv2d(x, w, b, 1, 1), direct)  # the same kernels as the other context ran
+    ctx.set_knob("MCB_CONV_DIRECT", None)
+    assert np.array_equal(ops.conv2d(x, w, b, 1, 1), tc)
+    assert not np.array_equal(direct, tc) and np.abs(direct - tc).max() <= 2e-6 * np.abs(tc).max()  # two different kernels
