@@ -868,3 +868,39 @@ def test_static_step_pipelined_run_returns_every_loss_one_call_later(mc, ctx):
         assert np.array_equal(a.data, b.data)
     step.close()
     step2.close()
+
+
+@pytest.mark.parametrize("act", ["gelu", "relu"])
+def test_linear_activation_on_split_tail_tiles_matches_unsplit(mc, ctx, act):
+    """Linear + activation at 8192 x 768 <- 3072 under autocast: 96 output tiles of 256 x 256 on 74 CTA pairs, so 22 tiles are
+    cut in three along K and finished inside the kernel by slice 0 (partial sums added in slice order, then bias,
+    activation, rounding and the pre-activation as second output).  Against the same GEMM without the split
+    (MCB_TC_SPLIT_TAIL=0): the f32 sums group differently, so values agree to bf16 rounding, not bit for bit; the
+    backward pass reads the saved pre-activation of both."""
+    rng = np.random.default_rng(2718)
+    m, k, n = 8192, 3072, 768
+    x = (rng.standard_normal((m, k)) * 0.5).astype(np.float32)
+    w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+    b = rng.standard_normal(n).astype(np.float32) * 0.1
+    up = rng.standard_normal((m, n)).astype(np.float32)
+
+    def run():
+        xv, wv, bv = mc.Variable(ctx, x), mc.Variable(ctx, w), mc.Variable(ctx, b)
+        with mc.autocast(mc.BF16):
+            y = mc.F.linear_activation(xv, wv, bv, act)
+            loss = mc.F.sum(mc.F.mul(y, mc.Variable.constant(ctx, up)))
+        loss.backward()
+        return y.data.astype(np.float32), xv.grad, wv.grad, bv.grad
+
+    split = run()
+    ctx.set_knob("MCB_TC_SPLIT_TAIL", 0)
+    try:
+        plain = run()
+    finally:
+        ctx.set_knob("MCB_TC_SPLIT_TAIL", None)
+    again = run()
+    for a, c in zip(split, again):
+        assert np.array_equal(a, c)  # slice order is fixed: the same bits every time
+    for i, (a, r) in enumerate(zip(split, plain)):
+        tol = 2.0 ** -7 if i == 0 else 2.0 ** -6
+        assert np.abs(a - r).max() <= tol * float(np.abs(r).max()), (i, np.abs(a - r).max() / np.abs(r).max())
