@@ -54,7 +54,10 @@ def peaks():
 
 
 # DRAM bytes of the c4 step's GEMM launches, measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum of every tc_gemm launch
-# of one tape step of the 2-layer model): the three lm_head launches together, and the twelve launches of one layer together.  Traffic
+# of one tape step of the 2-layer model:
+#   ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum --clock-control none -k regex:tc_gemm_kernel -s 81 -c 27 --csv \
+#       python bench.py --workload c4 --layers 2 --steps 1 --warmup 3 --no-cpu-baseline --no-graph
+# ): the three lm_head launches together, and the twelve launches of one layer together.  Traffic
 # grows in proportion to the layer count (every layer launches the same twelve shapes).  The figure belongs to the GEMM source it was
 # measured with: `kernel_sha256` is the SHA-256 of modernchainer_b200/csrc/gemm_tc.cu at capture time, and a build whose source differs
 # reports traffic null (with the reason) instead of a stale number.
@@ -450,7 +453,7 @@ def run_ours(args, dist):
             "unit": "samples/s", "n_gpus": dist.world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
             "step_path": path, "tape_step": tape,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16" if cfg["amp"] else "f32", "data": "synthetic",
-            "config": {"workload": f"{name}: " + json.dumps({k: v for k, v in cfg.items()}), "global_batch": global_batch,
+            "config": {"workload": workload_string(name, cfg), "global_batch": global_batch,
                        "parallelism": f"dp{dist.world}", "l2": "per-step working set (activations + 3.8 GB optimizer state) exceeds the 126 MB L2",
                        "grad_bucket_mb": args.bucket_mb},
             "e2e": {"value": global_batch / (ms_step_e2e / 1e3), "unit": "samples/s", "h2d_bytes_per_step": int(x_np.nbytes + y_np.nbytes),
@@ -582,7 +585,7 @@ def run_c5(args, dist, mc, ctx, pk):
     return {
         "metric": "fused GradScaler check + unscale + Adam, HBM GB/s", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-        "data": "synthetic", "config": {"workload": "c5: flat 125M f32 params, bf16 grads pre-multiplied by 2^16, inf/nan on odd steps",
+        "data": "synthetic", "config": {"workload": workload_string("c5", WORKLOADS["c5"]),
                                         "l2": "3.5 GB working set exceeds the 126 MB L2"},
         "e2e": {"value": alg / (ms_e2e / 1e3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 4},
         "gpu_launches": int(launches), "clocks": clocks,
@@ -676,6 +679,13 @@ def cpu_sample(name, threads_note=True):
     return 28.0 * n / dt / 1e9, cores, f"oracle, {cores} threads: scan + unscale + Adam over {n} parameters"
 
 
+def workload_string(name, cfg):
+    """The `config.workload` of a line: the same for this library's arm and for the reference arm."""
+    if name == "c5":
+        return "c5: flat 125M f32 params, bf16 grads pre-multiplied by 2^16, inf/nan on odd steps"
+    return f"{name}: " + json.dumps({k: v for k, v in cfg.items()})
+
+
 def run_reference(args, dist):
     if dist.rank != 0:
         return None
@@ -688,7 +698,9 @@ def run_reference(args, dist):
     return {"impl": "reference", "metric": "train samples/sec (fwd+bwd+Adam, device-timed, max over ranks)" if unit != "GB/s" else "fused GradScaler check + unscale + Adam, HBM GB/s",
             "value": v, "unit": unit, "n_gpus": dist.world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": None,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": args.workload, "note": "the reference is Rust and cannot be built here; this arm times the C restatement of its CPU backend"},
+            "config": {"workload": workload_string(args.workload, WORKLOADS[args.workload]),
+                       "note": "the reference is Rust and cannot be built here; this arm times the C restatement of its CPU backend on the host cores, "
+                               "on a bounded sample of the same workload (cpu_baseline.sample)"},
             "cpu_baseline": {"value": v, "unit": unit, "cores": cores, "kind": "port", "sample": desc},
             "e2e": {"value": v, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
 
