@@ -61,8 +61,8 @@ def peaks():
 # grows in proportion to the layer count (every layer launches the same twelve shapes).  The figure belongs to the GEMM source it was
 # measured with: `kernel_sha256` is the SHA-256 of modernchainer_b200/csrc/gemm_tc.cu at capture time, and a build whose source differs
 # reports traffic null (with the reason) instead of a stale number.
-GEMM_TRAFFIC = {"lm_head_bytes": 1937.0e6, "per_layer_bytes": 513.6e6,
-                "kernel_sha256": "476cc0e63e751d54f594cee7ae7d9be1c93d72ea9ea1cc0d0ec91f786fee064e"}
+GEMM_TRAFFIC = {"lm_head_bytes": 1937.8e6, "per_layer_bytes": 529.0e6,
+                "kernel_sha256": "6e5ee17be7035caf1b498eb35888caa66ca361f7d11f5ac3834d653d9ab78f11"}
 
 
 def gemm_traffic(layers):

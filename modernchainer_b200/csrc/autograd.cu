@@ -668,6 +668,25 @@ static mcb_status linear_backward_impl(mcb_ctx *ctx, const Tensor &g_in, const L
         g = gp;
     }
     if (sv.bf16) {
+        // The weight gradient first in the books: where it goes and whether its reduction is split.  A split one adds its
+        // slices into an output that must be zero: the data-gradient GEMM in front of it clears that buffer on the side
+        // (its epilogue warps are idle until the first tile is done), which saves a fill of its own per Linear.
+        TcGemmParams pw; // dw[n,k] = g^T[n,m] * x[m,k]
+        bool clear_dw = false;
+        if (w->requires_grad) {
+            bool direct;
+            MCB_TRY(grad_dst(w, &gi[1], &direct));
+            pw.in_dt = sv.lp;
+            pw.a = g.ptr; pw.a_mn_major = 1; pw.lda = n;
+            pw.b = sv.x.ptr; pw.b_mn_major = 1; pw.ldb = k;
+            pw.d = gi[1].ptr; pw.out_dt = MCB_F32; pw.ldd = k;
+            pw.m = n; pw.n = k; pw.k = m;
+            mcb_tc_plan(ctx, n, k, m, true, false, 1, &pw.bn, &pw.split_k);
+            if (pw.split_k > 1) {
+                pw.accumulate = 1;
+                clear_dw = true;
+            }
+        }
         if (x->requires_grad) {
             Tensor wb;
             MCB_TRY(lowp_of(w, sv.lp, &wb));
@@ -679,23 +698,16 @@ static mcb_status linear_backward_impl(mcb_ctx *ctx, const Tensor &g_in, const L
             p.b = wb.ptr; p.b_mn_major = 1; p.ldb = k;
             p.d = gi[0].ptr; p.out_dt = xdt; p.ldd = k;
             p.m = m; p.n = k; p.k = n;
+            if (clear_dw && m > 0 && mcb_aligned16(gi[1].ptr) && (sizeof(float) * n * k) % 16 == 0) {
+                p.zero_ptr = gi[1].ptr;
+                p.zero_bytes = sizeof(float) * n * k;
+                clear_dw = false;
+            }
             MCB_TRY(mcb_tc_gemm(ctx, p));
         }
         if (w->requires_grad) {
-            bool direct;
-            MCB_TRY(grad_dst(w, &gi[1], &direct));
-            TcGemmParams p; // dw[n,k] = g^T[n,m] * x[m,k]
-            p.in_dt = sv.lp;
-            p.a = g.ptr; p.a_mn_major = 1; p.lda = n;
-            p.b = sv.x.ptr; p.b_mn_major = 1; p.ldb = k;
-            p.d = gi[1].ptr; p.out_dt = MCB_F32; p.ldd = k;
-            p.m = n; p.n = k; p.k = m;
-            mcb_tc_plan(ctx, n, k, m, true, false, 1, &p.bn, &p.split_k);
-            if (p.split_k > 1) {
-                p.accumulate = 1;
-                MCB_TRY(mcb_memset(ctx, gi[1].ptr, 0, sizeof(float) * n * k));
-            }
-            MCB_TRY(mcb_tc_gemm(ctx, p));
+            if (clear_dw) MCB_TRY(mcb_memset(ctx, gi[1].ptr, 0, sizeof(float) * n * k));
+            MCB_TRY(mcb_tc_gemm(ctx, pw));
         }
     } else {
         float *dx = nullptr, *dw = nullptr;
@@ -1222,17 +1234,6 @@ mcb_status f_qkv_attention(const Var &x, const Var &wq, const Var &bq, const Var
             MCB_TRY(mcb_flash_backward(ctx, qp, qp + d, qp + 2 * d, o.ptr, g.ptr, (const float *)lse.ptr, dp, dp + d, dp + 2 * d, n, s, d, heads,
                                        causal, 3 * d, d, 3 * d, brows > 0 ? (float *)bias_part.ptr : nullptr, 3 * d, &bias_done, lp));
         }
-        if (xv->requires_grad) {
-            int xdt = xv->data.dt == lp ? lp : MCB_F32;
-            MCB_TRY(new_tensor(ctx, xdt, xv->data.shape, &gi[0]));
-            TcGemmParams p; // dx[m, d] = dqkv[m, 3d] * Wqkv[3d, d]
-            p.in_dt = lp;
-            p.a = dqkv.ptr; p.lda = 3 * d;
-            p.b = wb.ptr; p.b_mn_major = 1; p.ldb = d;
-            p.d = gi[0].ptr; p.out_dt = xdt; p.ldd = d;
-            p.m = m; p.n = d; p.k = 3 * d;
-            MCB_TRY(mcb_tc_gemm(ctx, p));
-        }
         // weight gradients: one [3d, d] product, straight into the three adjacent arena slots when they are free
         bool dq_, dk_, dv_;
         Tensor tw[3], tb[3];
@@ -1261,20 +1262,36 @@ mcb_status f_qkv_attention(const Var &x, const Var &wq, const Var &bq, const Var
                 tb[i].shape = {d};
             }
         }
-        {
-            TcGemmParams p; // dWqkv[3d, d] = dqkv^T[3d, m] * x[m, d]
+        TcGemmParams pw; // dWqkv[3d, d] = dqkv^T[3d, m] * x[m, d]
+        pw.in_dt = lp;
+        pw.a = dqkv.ptr; pw.a_mn_major = 1; pw.lda = 3 * d;
+        pw.b = xb.ptr; pw.b_mn_major = 1; pw.ldb = d;
+        pw.d = dw.ptr; pw.out_dt = MCB_F32; pw.ldd = d;
+        pw.m = 3 * d; pw.n = d; pw.k = m;
+        mcb_tc_plan(ctx, pw.m, pw.n, pw.k, true, false, 1, &pw.bn, &pw.split_k);
+        bool clear_dw = false; // a split reduction adds its slices into a zero output: cleared by the GEMM in front where there is one
+        if (pw.split_k > 1) {
+            pw.accumulate = 1;
+            clear_dw = true;
+        }
+        if (xv->requires_grad) {
+            int xdt = xv->data.dt == lp ? lp : MCB_F32;
+            MCB_TRY(new_tensor(ctx, xdt, xv->data.shape, &gi[0]));
+            TcGemmParams p; // dx[m, d] = dqkv[m, 3d] * Wqkv[3d, d]
             p.in_dt = lp;
-            p.a = dqkv.ptr; p.a_mn_major = 1; p.lda = 3 * d;
-            p.b = xb.ptr; p.b_mn_major = 1; p.ldb = d;
-            p.d = dw.ptr; p.out_dt = MCB_F32; p.ldd = d;
-            p.m = 3 * d; p.n = d; p.k = m;
-            mcb_tc_plan(ctx, p.m, p.n, p.k, true, false, 1, &p.bn, &p.split_k);
-            if (p.split_k > 1) {
-                p.accumulate = 1;
-                MCB_TRY(mcb_memset(ctx, dw.ptr, 0, sizeof(float) * 3 * d * d));
+            p.a = dqkv.ptr; p.lda = 3 * d;
+            p.b = wb.ptr; p.b_mn_major = 1; p.ldb = d;
+            p.d = gi[0].ptr; p.out_dt = xdt; p.ldd = d;
+            p.m = m; p.n = d; p.k = 3 * d;
+            if (clear_dw && m > 0 && mcb_aligned16(dw.ptr)) {
+                p.zero_ptr = dw.ptr;
+                p.zero_bytes = sizeof(float) * 3 * d * d;
+                clear_dw = false;
             }
             MCB_TRY(mcb_tc_gemm(ctx, p));
         }
+        if (clear_dw) MCB_TRY(mcb_memset(ctx, dw.ptr, 0, sizeof(float) * 3 * d * d));
+        MCB_TRY(mcb_tc_gemm(ctx, pw));
         if (bias_done) MCB_TRY(mcb_partial_sum_final(ctx, (const float *)bias_part.ptr, (int)bias_part.shape[0], 3 * d, (float *)db.ptr));
         else MCB_TRY(mcb_col_sum(ctx, dqkv.ptr, lp, m, 3 * d, (float *)db.ptr));
         gi[1] = tw[0]; gi[3] = tw[1]; gi[5] = tw[2];

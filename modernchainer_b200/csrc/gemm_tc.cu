@@ -64,6 +64,8 @@ struct TcArgs {
     // slices are finished in the kernel
     float *fix_ws;
     unsigned *fix_cnt; // [sk_rem][2][8 epilogue warps]: slices that have left their partial sums; zero between launches
+    uint4 *zero_ptr;   // side job of the epilogue warps before their first tile: zero_n16 16-byte pieces of zeros from here
+    long long zero_n16;
     unsigned int *err;
 };
 
@@ -617,6 +619,14 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         StageRing rg;
         rg.base = out_stage + ew * (args.ring * 4096);
         rg.issued = 0;
+        if (args.zero_n16 > 0 && grp < groups) {
+            // nothing to drain until the first accumulator is complete: clear the buffer the caller named (the output of the
+            // accumulating GEMM that comes next in the stream), every epilogue thread of the grid its share
+            const long long per_cta = 128ll * groups, me = (long long)blockIdx.x * per_cta + (long long)ew * 32 + lane;
+            const long long all = (long long)gridDim.x * per_cta;
+            const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+            for (long long i = me; i < args.zero_n16; i += all) args.zero_ptr[i] = z;
+        }
         for (unsigned w = w_first; w < work_total && grp < groups; w += w_stride, ++tile_it) {
             const WorkItem wi = decode_work(args, w, tiles_mn, one_split);
             const int split = wi.split;
@@ -1060,6 +1070,8 @@ template <int BN, bool PAIR> mcb_status launch(mcb_ctx *ctx, const TcGemmParams 
     a.sk_splits = 1;
     a.fix_ws = nullptr;
     a.fix_cnt = nullptr;
+    a.zero_ptr = (uint4 *)p.zero_ptr;
+    a.zero_n16 = p.zero_ptr ? (long long)(p.zero_bytes / 16) : 0;
     const int workers = PAIR ? max_pairs : ctx->sm_count;
     const long long tiles = (long long)a.m_tiles * a.n_tiles;
     const bool direct = p.accumulate && !p.bias; // slices add straight into the f32 output
@@ -1119,6 +1131,7 @@ template <int BN, bool PAIR> mcb_status launch(mcb_ctx *ctx, const TcGemmParams 
 } // namespace
 
 mcb_status mcb_tc_gemm(mcb_ctx *ctx, const TcGemmParams &p) {
+    if (p.zero_ptr && (p.m == 0 || p.n == 0 || p.k == 0)) MCB_TRY(mcb_memset(ctx, p.zero_ptr, 0, p.zero_bytes)); // no kernel will run: clear it here
     if (p.m == 0 || p.n == 0) return MCB_OK;
     ProfScope prof(ctx, MCB_PROF_GEMM_TC, 2.0 * (double)p.m * (double)p.n * (double)p.k,
                    2.0 * ((double)p.m * p.k + (double)p.n * p.k) + (double)p.m * p.n * (mcb_is_lp(p.out_dt) ? 2.0 : 4.0));
@@ -1131,6 +1144,8 @@ mcb_status mcb_tc_gemm(mcb_ctx *ctx, const TcGemmParams &p) {
     if (!mcb_is_lp(p.in_dt)) return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "tensor-core GEMM operands must be bf16 or f16");
     if (p.out_dt != p.in_dt && p.out_dt != MCB_F32) return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "GEMM output must be f32 or the operands' 16-bit type");
     if (p.accumulate && p.out_dt != MCB_F32) return mcb_fail(ctx, MCB_UNSUPPORTED_DTYPE, "accumulating GEMM output must be f32");
+    if (p.zero_ptr && (!mcb_aligned16(p.zero_ptr) || p.zero_bytes % 16))
+        return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "the buffer a GEMM clears on the side must be 16-byte aligned and a multiple of 16 bytes long");
     if (p.split_k > 1 && !p.accumulate) return mcb_fail(ctx, MCB_INVALID_ARGUMENT, "split-K needs the accumulating epilogue");
     // vector stores in the epilogue need ldd and d aligned; otherwise the scalar tail path is used per row
     if ((mcb_is_lp(p.out_dt) && ((p.ldd % 8) || !mcb_aligned16(p.d))) || (p.out_dt == MCB_F32 && !p.accumulate && ((p.ldd % 4) || !mcb_aligned16(p.d))))

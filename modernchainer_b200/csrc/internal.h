@@ -39,6 +39,11 @@ struct TcGemmParams {
     int pair = -1; // 1 = two CTAs share a 256-row tile (cta_group::2), 0 = one CTA per 128-row tile, -1 = choose
     int act = MCB_ACT_NONE;
     void *d_pre = nullptr; // optional second output: value before the activation (same dtype/ld as d)
+    // optional side job: fill zero_bytes (a multiple of 16) at zero_ptr (16-byte aligned) with zeros while the first tiles are
+    // in flight (the epilogue warps have nothing to do until then).  The tape uses it to clear the output of the split
+    // weight-gradient GEMM that follows a data-gradient GEMM, instead of a fill of its own.
+    void *zero_ptr = nullptr;
+    size_t zero_bytes = 0;
     int split_tail = -1;   // 1 = cut the tiles of a mostly empty last wave along K (f32 workspace + finishing kernel), 0 = never, -1 = choose
 };
 mcb_status mcb_tc_gemm(mcb_ctx *ctx, const TcGemmParams &p);
