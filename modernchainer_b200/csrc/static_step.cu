@@ -228,6 +228,26 @@ mcb_status mcb_static_step_create(mcb_model *model, mcb_adam *opt, mcb_scaler *s
                 for (size_t i = 0; i < ne; ++i) prog += ed[i].type == cudaGraphDependencyTypeProgrammatic;
         }
         fprintf(stderr, "static step graph: %zu edges, %zu programmatic\n", ne, prog);
+        // node kinds, and the bytes the fill nodes clear: fills and copies do not show in a kernel launch list
+        size_t nn = 0;
+        if (cudaGraphGetNodes(graph, nullptr, &nn) == cudaSuccess && nn) {
+            std::vector<cudaGraphNode_t> nodes(nn);
+            size_t kernels = 0, fills = 0, copies = 0, other = 0;
+            double fill_bytes = 0.0;
+            if (cudaGraphGetNodes(graph, nodes.data(), &nn) == cudaSuccess)
+                for (size_t i = 0; i < nn; ++i) {
+                    cudaGraphNodeType t;
+                    if (cudaGraphNodeGetType(nodes[i], &t) != cudaSuccess) continue;
+                    if (t == cudaGraphNodeTypeKernel) ++kernels;
+                    else if (t == cudaGraphNodeTypeMemcpy) ++copies;
+                    else if (t == cudaGraphNodeTypeMemset) {
+                        ++fills;
+                        cudaMemsetParams mp;
+                        if (cudaGraphMemsetNodeGetParams(nodes[i], &mp) == cudaSuccess) fill_bytes += (double)mp.width * mp.elementSize * (mp.height ? mp.height : 1);
+                    } else ++other;
+                }
+            fprintf(stderr, "static step graph: %zu kernel, %zu fill (%.1f MB), %zu copy, %zu other nodes\n", kernels, fills, fill_bytes / 1e6, copies, other);
+        }
         (void)cudaGetLastError();
     }
     if (st == MCB_OK) {
